@@ -1,0 +1,201 @@
+"""Headline benchmark: training throughput of a GPT-2-small-shaped decoder (12 layers, d 768,
+12 heads, FFN 3072 GELU, vocab 50257, context 1024), bf16 compute, AdamW with sharded
+parameters / gradients / optimizer state, 64 x 1024 tokens per GPU per step (512 x 1024 on 8 GPUs).
+
+    python bench.py --gpus N --steps K --warmup W            # this framework
+    python bench.py --impl reference ...                     # the reference (see below)
+
+One JSON line is printed by rank 0. ``value`` is device-timed tokens/s of the whole job (CUDA events,
+max over ranks); ``e2e`` repeats the measurement through ``Trainer.train_step`` with the host-to-device
+copy of every batch from pinned memory and a device-to-host read of every loss inside the timed
+region. Token ids are synthetic (Zipf 1.1 over the vocabulary, seeded); weights are random-init.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+BASELINE_PUBLISHED = None  # the reference publishes no number for this configuration
+
+REFERENCE_UNAVAILABLE = (
+    "reference is a C++20/CMake CPU-only project with no Python package (pip install: 'Neither setup.py nor pyproject.toml found'), "
+    "no CUDA/NCCL path and a Windows-only distributed backend; its single-thread CPU trainer would need hours per 64x1024-token step")
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch-per-gpu", type=int, default=64)
+    ap.add_argument("--seq-len", type=int, default=1024)
+    ap.add_argument("--layers", type=int, default=12, help="for debugging only; the reported config is 12")
+    return ap.parse_args()
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU every 200 ms through NVML (read-only)."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.stop_flag, self.max_mhz = index, [], set(), False, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.2)
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from innova_b200.models import DenseModel, gpt2_small
+    from innova_b200.ops import runtime as rt
+    from innova_b200.training.trainer import Trainer, TrainConfig
+    from innova_b200.utils.data import zipf_tokens
+
+    cfg = gpt2_small(num_layers=args.layers)
+    B, S = args.batch_per_gpu, args.seq_len
+    model = DenseModel(cfg, dtype=torch.bfloat16, device=dev)
+    tcfg = TrainConfig(lr=3e-4, weight_decay=0.1, max_grad_norm=1.0)
+    engine = None
+    parallelism = "single"
+    if world > 1:
+        from innova_b200.parallel.fsdp import ShardedFlatEngine
+        engine = ShardedFlatEngine(model, lr=tcfg.lr, weight_decay=tcfg.weight_decay, max_grad_norm=tcfg.max_grad_norm)
+        parallelism = f"fsdp{world}"
+    trainer = Trainer(model, tcfg, engine=engine)
+
+    n_batches = args.warmup + args.steps
+    toks = zipf_tokens(n_batches * B * S + 1, cfg.vocab_size, 1.1, seed=1234 + rank)
+    host = []
+    for i in range(n_batches):
+        lo = i * B * S
+        host.append((toks[lo:lo + B * S].view(B, S).pin_memory(), toks[lo + 1:lo + B * S + 1].view(B, S).pin_memory()))
+    dev_batches = [(a.to(dev), b.to(dev)) for a, b in host]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(region):
+        barrier()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0 = rt.launch_count()
+        e0.record()
+        region()
+        e1.record()
+        barrier()
+        sampler.stop_flag = True
+        ms = e0.elapsed_time(e1)
+        launches = rt.launch_count() - c0
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), launches, sampler.summary()
+
+    losses = []
+    for i in range(args.warmup):
+        losses.append(trainer.train_step(*dev_batches[i]))
+    rt.check_status()
+
+    def device_region():
+        for i in range(args.warmup, n_batches):
+            losses.append(trainer.train_step(*dev_batches[i]))
+
+    ms, launches, clocks = timed(device_region)
+    rt.check_status()
+
+    e2e_losses = []
+
+    def e2e_region():
+        for i in range(args.warmup, n_batches):
+            ids = host[i][0].to(dev, non_blocking=True)
+            lab = host[i][1].to(dev, non_blocking=True)
+            e2e_losses.append(float(trainer.train_step(ids, lab)))  # float() is the device-to-host read
+
+    ms_e2e, _, _ = timed(e2e_region)
+    rt.check_status()
+
+    tokens_per_step = B * S * world
+    value = tokens_per_step * args.steps / (ms / 1e3)
+    e2e_value = tokens_per_step * args.steps / (ms_e2e / 1e3)
+    if rank == 0:
+        out = {
+            "metric": "train_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": (value / BASELINE_PUBLISHED) if BASELINE_PUBLISHED else None, "dtype": "bf16",
+            "data": "synthetic Zipf(1.1) token ids, random-init weights", "impl": "ours",
+            "config": {"model": "gpt2-small-shaped (12L d768 12h ffn3072 gelu vocab50257 ctx1024)" if args.layers == 12 else f"DEBUG {args.layers} layers",
+                       "global_batch": B * world, "seq_len": S, "parallelism": parallelism, "optimizer": "AdamW fp32 master, clip 1.0",
+                       "l2": "inputs and activations larger than L2 (multi-GB working set per step)"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": 2 * B * S * 8,
+                    "d2h_bytes_per_step": 4},
+            "gpu_launches": launches,
+            "loss_first": float(losses[0]), "loss_last": e2e_losses[-1] if e2e_losses else float(losses[-1]),
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+    run_ours(args)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

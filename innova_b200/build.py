@@ -1,0 +1,121 @@
+"""In-tree build of the native libraries.
+
+``libinnova_cuda.so``  — every ``csrc/*.cu`` compiled for sm_100a (tcgen05 / TMA need the ``a`` target).
+``libinnova_host.so``  — the C++ host runtime in ``csrc/host`` (.oil container, block codecs, format
+registry and planner, codebooks, paged-KV page tables, CPU sampler).
+
+Both expose a C ABI and are loaded with ctypes (see ``_native.py``), so a build takes seconds and
+needs no Python headers. ``python -m innova_b200.build`` rebuilds what is out of date.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+CSRC = ROOT / "csrc"
+LIB = ROOT / "lib"
+OBJ = LIB / "obj"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-O3",
+]
+CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function", "-pthread"]
+
+
+def _nvcc() -> str | None:
+    cand = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    return cand if os.path.exists(cand) else None
+
+
+def _newer(src_list, target: Path) -> bool:
+    if not target.exists():
+        return True
+    t = target.stat().st_mtime
+    return any(Path(s).stat().st_mtime > t for s in src_list)
+
+
+def _run(cmd):
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("build failed: %s\n%s\n%s" % (" ".join(map(str, cmd)), r.stdout, r.stderr))
+    return r.stdout + r.stderr
+
+
+def cuda_sources():
+    return sorted(CSRC.glob("*.cu"))
+
+
+def host_sources():
+    return sorted((CSRC / "host").glob("*.cpp"))
+
+
+def build_cuda(force: bool = False, verbose: bool = False) -> Path:
+    out = LIB / "libinnova_cuda.so"
+    srcs = cuda_sources()
+    headers = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
+    nvcc = _nvcc()
+    if nvcc is None:
+        if out.exists():
+            return out
+        raise RuntimeError("nvcc not found and %s is not built" % out)
+    OBJ.mkdir(parents=True, exist_ok=True)
+    jobs = []
+    for s in srcs:
+        o = OBJ / (s.stem + ".o")
+        if force or _newer([s] + headers, o):
+            cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(s), "-o", str(o)]
+            if verbose:
+                cmd.insert(1, "-Xptxas=-v")
+            jobs.append(cmd)
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            logs = list(ex.map(_run, jobs))
+        if verbose:
+            print("\n".join(logs))
+    objs = [OBJ / (s.stem + ".o") for s in srcs]
+    if force or jobs or _newer(objs, out):
+        _run([nvcc, "-shared", "-o", str(out), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"])
+    return out
+
+
+def build_host(force: bool = False) -> Path:
+    out = LIB / "libinnova_host.so"
+    srcs = host_sources()
+    if not srcs:
+        return out
+    headers = list((CSRC / "host").glob("*.h"))
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if cxx is None:
+        if out.exists():
+            return out
+        raise RuntimeError("no C++ compiler found and %s is not built" % out)
+    OBJ.mkdir(parents=True, exist_ok=True)
+    jobs = []
+    for s in srcs:
+        o = OBJ / ("host_" + s.stem + ".o")
+        if force or _newer([s] + headers, o):
+            jobs.append([cxx, *CXX_FLAGS, "-I", str(CSRC / "host"), "-c", str(s), "-o", str(o)])
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            list(ex.map(_run, jobs))
+    objs = [OBJ / ("host_" + s.stem + ".o") for s in srcs]
+    if force or jobs or _newer(objs, out):
+        _run([cxx, "-shared", "-pthread", "-o", str(out), *map(str, objs)])
+    return out
+
+
+def build_all(force: bool = False, verbose: bool = False):
+    LIB.mkdir(exist_ok=True)
+    return build_cuda(force, verbose), build_host(force)
+
+
+if __name__ == "__main__":
+    paths = build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    for p in paths:
+        print(p)

@@ -1,0 +1,438 @@
+// Flash attention backward on tcgen05 tensor cores (causal or full, MHA or GQA, head_dim 64 or 128).
+//
+// Replaces the reference's attention backward (include/oil/autograd_functions.h:82-94,
+// src/autograd_grad.cpp attention branch); the reference's memory-efficient backward is a
+// placeholder (src/zero_optimizer_mem.cpp:496-574), so the oracle is plain fp32 attention.
+//
+// One CTA per (batch, kv head, 128-key block). K and V tiles stay in shared memory; the CTA walks
+// the query blocks that can see its keys (and, for GQA, every query head of the group) and
+// accumulates dK and dV in TMEM. Per query block, five MMAs:
+//   S^T  = K Q^T            dP^T = V dO^T            (both 128 keys x 128 queries, fp32 in TMEM)
+//   dV  += P^T dO           dK  += dS^T Q            dQ_blk = dS K
+// 8 softmax warps (thread <-> key row, two halves of the query columns) turn S^T, dP^T into
+// P^T = exp(S^T*scale - lse) and dS^T = P^T * (dP^T - D) as bf16 tiles in swizzled shared memory.
+// The same dS^T tile serves as a K-major A operand (dK) and as an MN-major A operand (dQ), and the
+// Q / dO / K tiles serve as K-major B operands (S^T, dP^T) and MN-major B operands (dK, dV, dQ), so
+// nothing is transposed in memory. dQ blocks are added to an fp32 buffer with vector reductions.
+// Every wait is bounded and reports through *status.
+#include "sm100_common.cuh"
+#include "inv_api.h"
+
+namespace inv {
+
+int make_tmap_tokens_bf16(CUtensorMap* out, const void* ptr, int cols, int S, int B, int ld, int box_rows);
+
+constexpr int FB_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 softmax
+
+struct FlashBwdParams {
+  const float* lse;    // [B, H, S]
+  const float* delta;  // [B, H, S]  rowsum(dO * O)
+  float* dq_acc;       // [B*S, H*D] fp32, zero on entry
+  __nv_bfloat16* dk;   // token-major, ld_dk
+  __nv_bfloat16* dv;
+  int ld_dk, ld_dv;
+  int B, S, H, Hkv;
+  float scale;
+  int causal;
+  int* status;
+};
+
+template <int ND>
+struct BwdSmem {
+  static constexpr int TILE = ND * 16384;
+  static constexpr int STAGES = ND == 1 ? 2 : 1;
+  static constexpr int K_OFF = 0;
+  static constexpr int V_OFF = TILE;
+  static constexpr int Q_OFF = 2 * TILE;
+  static constexpr int DO_OFF = Q_OFF + STAGES * TILE;
+  static constexpr int PT_OFF = DO_OFF + STAGES * TILE;
+  static constexpr int DST_OFF = PT_OFF + 32768;
+  static constexpr int BAR_OFF = DST_OFF + 32768;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+template <int ND>
+__global__ void __launch_bounds__(FB_THREADS, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do, const FlashBwdParams p) {
+  constexpr int D = 64 * ND;
+  using L = BwdSmem<ND>;
+  constexpr int STAGES = L::STAGES;
+  constexpr bool OVERLAP = (ND == 1);  // D = 128 has no spare TMEM: dQ reuses the S^T columns
+  constexpr uint32_t ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 256 + D, DQ_COL = OVERLAP ? 384 : 0;
+  constexpr uint32_t TMEM_COLS = 512;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem + L::K_OFF;
+  uint8_t* sV = smem + L::V_OFF;
+  uint8_t* sQ = smem + L::Q_OFF;
+  uint8_t* sdO = smem + L::DO_OFF;
+  uint8_t* sPt = smem + L::PT_OFF;
+  uint8_t* sdSt = smem + L::DST_OFF;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* kv_full = bars;        // 1
+  uint64_t* q_full = bars + 1;     // STAGES
+  uint64_t* q_empty = bars + 3;    // STAGES
+  uint64_t* s_full = bars + 5;     // S^T and dP^T are in TMEM
+  uint64_t* s_empty = bars + 6;    // 256 arrivals: both have been read
+  uint64_t* pds_full = bars + 7;   // 256 arrivals: P^T and dS^T are in shared memory
+  uint64_t* mma2_done = bars + 8;  // dV, dK, dQ MMAs of this block finished
+  uint64_t* dq_empty = bars + 9;   // 256 arrivals: dQ has been read out of TMEM
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int G = p.H / p.Hkv;
+  const int k0 = j * 128;
+  const int nqb = (p.S + 127) / 128;
+  const int i0 = p.causal ? j : 0;
+  const int nq_it = nqb - i0;
+  const int n_it = G * nq_it;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(s_empty, 256);
+    mbar_init(pds_full, 256);
+    mbar_init(mma2_done, 1);
+    mbar_init(dq_empty, 256);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+    tma_prefetch_desc(&tmap_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * L::TILE);
+#pragma unroll
+      for (int a = 0; a < ND; ++a) {
+        tma_load_3d(sK + a * 16384, &tmap_k, kv_full, hk * D + a * 64, k0, b);
+        tma_load_3d(sV + a * 16384, &tmap_v, kv_full, hk * D + a * 64, k0, b);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(&q_empty[st], ph ^ 1, abort_flag, p.status, ERR_WAIT_EMPTY)) break;
+        const int h = hk * G + it / nq_it;
+        const int q0 = (i0 + it % nq_it) * 128;
+        mbar_expect_tx(&q_full[st], 2 * L::TILE);
+#pragma unroll
+        for (int a = 0; a < ND; ++a) {
+          tma_load_3d(sQ + st * L::TILE + a * 16384, &tmap_q, &q_full[st], h * D + a * 64, q0, b);
+          tma_load_3d(sdO + st * L::TILE + a * 16384, &tmap_do, &q_full[st], h * D + a * 64, q0, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);   // K-major x K-major
+      const uint32_t idesc_kv = make_idesc_bf16(128, D, 0, 1);    // K-major A, MN-major B
+      const uint32_t idesc_dq = make_idesc_bf16(128, D, 1, 1);    // MN-major A and B
+      const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV);
+      const uint32_t pt_base = smem_u32(sPt), dst_base = smem_u32(sdSt);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, ERR_WAIT_FULL);
+      auto issue_s = [&](int it) -> bool {
+        const int st = it % STAGES;
+        if (!mbar_wait(&q_full[st], (it / STAGES) & 1, abort_flag, p.status, ERR_WAIT_FULL)) return false;
+        if (it > 0 && !mbar_wait(s_empty, (it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) return false;
+        if (!OVERLAP && it > 0 && !mbar_wait(dq_empty, (it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) return false;
+        tc_fence_after();
+        const uint32_t q_base = smem_u32(sQ + st * L::TILE), do_base = smem_u32(sdO + st * L::TILE);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
+          umma_bf16(tmem_base + ST_COL, make_smem_desc(k_base + off, 16, 1024, 2), make_smem_desc(q_base + off, 16, 1024, 2), idesc_s, ks > 0);
+        }
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
+          umma_bf16(tmem_base + DPT_COL, make_smem_desc(v_base + off, 16, 1024, 2), make_smem_desc(do_base + off, 16, 1024, 2), idesc_s, ks > 0);
+        }
+        umma_commit(s_full);
+        return true;
+      };
+      if (ok && OVERLAP) ok = issue_s(0);
+      for (int it = 0; ok && it < n_it; ++it) {
+        if (OVERLAP) {
+          if (it + 1 < n_it && !issue_s(it + 1)) break;
+        } else {
+          if (!issue_s(it)) break;
+        }
+        const int st = it % STAGES;
+        if (!mbar_wait(pds_full, it & 1, abort_flag, p.status, ERR_WAIT_MISC)) break;
+        if (OVERLAP && it > 0 && !mbar_wait(dq_empty, (it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t q_base = smem_u32(sQ + st * L::TILE), do_base = smem_u32(sdO + st * L::TILE);
+        // dV += P^T dO ; dK += dS^T Q   (A: [keys x queries] K-major, B: [queries x d] MN-major)
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t a_off = (ks / 4) * 16384 + (ks % 4) * 32;
+          umma_bf16(tmem_base + DV_COL, make_smem_desc(pt_base + a_off, 16, 1024, 2), make_smem_desc(do_base + ks * 2048, 16384, 1024, 2),
+                    idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t a_off = (ks / 4) * 16384 + (ks % 4) * 32;
+          umma_bf16(tmem_base + DK_COL, make_smem_desc(dst_base + a_off, 16, 1024, 2), make_smem_desc(q_base + ks * 2048, 16384, 1024, 2),
+                    idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
+        }
+        // dQ_blk = dS K   (A: dS^T tile read MN-major, B: K tile read MN-major; reduction over keys)
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          umma_bf16(tmem_base + DQ_COL, make_smem_desc(dst_base + ks * 2048, 16384, 1024, 2), make_smem_desc(k_base + ks * 2048, 16384, 1024, 2),
+                    idesc_dq, ks > 0);
+        }
+        umma_commit(mma2_done);
+        umma_commit(&q_empty[st]);
+      }
+    }
+  } else {
+    // ---------------- softmax warps ----------------
+    const int q = warp & 3;            // TMEM lane quarter
+    const int hf = (warp - 2) >> 2;    // which half of the columns
+    const int r = q * 32 + lane;       // row inside a tile
+    const int key = k0 + r;
+    const uint32_t t_lane = tmem_base + (uint32_t(q * 32) << 16);
+    const float c = p.scale * 1.4426950408889634f;
+    const float LOG2E = 1.4426950408889634f;
+    uint8_t* pt_row = sPt + hf * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
+    uint8_t* dst_row = sdSt + hf * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int h = hk * G + it / nq_it;
+      const int q0 = (i0 + it % nq_it) * 128;
+      if (!mbar_wait_warp(s_full, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const float* lse_row = p.lse + ((size_t)b * p.H + h) * p.S;
+      const float* dl_row = p.delta + ((size_t)b * p.H + h) * p.S;
+      const bool need_mask = (p.causal && q0 < k0 + 127) || (q0 + 128 > p.S) || (k0 + 128 > p.S);
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        const int col0 = hf * 64 + cc * 32;
+        uint32_t s_r[32], dp_r[32];
+        tmem_ld_32x32(t_lane + ST_COL + col0, s_r);
+        tmem_ld_32x32(t_lane + DPT_COL + col0, dp_r);
+        tmem_ld_wait();
+        float pv[32], ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int qi = q0 + col0 + i;
+          const int qc = min(qi, p.S - 1);
+          const float lse = __ldg(lse_row + qc);
+          const float dl = __ldg(dl_row + qc);
+          float e = exp2f(__uint_as_float(s_r[i]) * c - lse * LOG2E);
+          if (need_mask && ((p.causal && key > qi) || qi >= p.S || key >= p.S)) e = 0.f;
+          pv[i] = e;
+          ds[i] = e * (__uint_as_float(dp_r[i]) - dl);
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = (cc * 4 + g) ^ (r & 7);
+          uint4 o;
+          o.x = pack_bf16x2(pv[g * 8 + 0], pv[g * 8 + 1]);
+          o.y = pack_bf16x2(pv[g * 8 + 2], pv[g * 8 + 3]);
+          o.z = pack_bf16x2(pv[g * 8 + 4], pv[g * 8 + 5]);
+          o.w = pack_bf16x2(pv[g * 8 + 6], pv[g * 8 + 7]);
+          *reinterpret_cast<uint4*>(pt_row + chunk * 16) = o;
+          o.x = pack_bf16x2(ds[g * 8 + 0], ds[g * 8 + 1]);
+          o.y = pack_bf16x2(ds[g * 8 + 2], ds[g * 8 + 3]);
+          o.z = pack_bf16x2(ds[g * 8 + 4], ds[g * 8 + 5]);
+          o.w = pack_bf16x2(ds[g * 8 + 6], ds[g * 8 + 7]);
+          *reinterpret_cast<uint4*>(dst_row + chunk * 16) = o;
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(s_empty);
+      fence_proxy_async_smem();
+      mbar_arrive(pds_full);
+      // dQ block: TMEM lanes are query rows now; this thread adds D/2 columns of row q0 + r.
+      if (!mbar_wait_warp(mma2_done, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int qrow = q0 + r;
+#pragma unroll
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int col0 = hf * (D / 2) + cc * 32;
+        uint32_t rr[32];
+        tmem_ld_32x32(t_lane + DQ_COL + col0, rr);
+        tmem_ld_wait();
+        if (qrow < p.S) {
+          float* dst = p.dq_acc + ((size_t)b * p.S + qrow) * ((size_t)p.H * D) + h * D + col0;
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + g * 4), "f"(__uint_as_float(rr[g * 4])),
+                         "f"(__uint_as_float(rr[g * 4 + 1])), "f"(__uint_as_float(rr[g * 4 + 2])), "f"(__uint_as_float(rr[g * 4 + 3]))
+                         : "memory");
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(dq_empty);
+    }
+    // dK, dV: the last mma2_done covers every accumulation. TMEM lanes are key rows.
+    if (ok && n_it > 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t colbase = which == 0 ? DV_COL : DK_COL;
+        __nv_bfloat16* outp = which == 0 ? p.dv : p.dk;
+        const int ld = which == 0 ? p.ld_dv : p.ld_dk;
+        const float sc = which == 0 ? 1.f : p.scale;
+#pragma unroll
+        for (int cc = 0; cc < D / 64; ++cc) {
+          const int col0 = hf * (D / 2) + cc * 32;
+          uint32_t rr[32];
+          tmem_ld_32x32(t_lane + colbase + col0, rr);
+          tmem_ld_wait();
+          if (key < p.S) {
+            __nv_bfloat16* dst = outp + ((size_t)b * p.S + key) * ld + hk * D + col0;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(rr[g * 8 + 0]) * sc, __uint_as_float(rr[g * 8 + 1]) * sc);
+              o.y = pack_bf16x2(__uint_as_float(rr[g * 8 + 2]) * sc, __uint_as_float(rr[g * 8 + 3]) * sc);
+              o.z = pack_bf16x2(__uint_as_float(rr[g * 8 + 4]) * sc, __uint_as_float(rr[g * 8 + 5]) * sc);
+              o.w = pack_bf16x2(__uint_as_float(rr[g * 8 + 6]) * sc, __uint_as_float(rr[g * 8 + 7]) * sc);
+              *reinterpret_cast<uint4*>(dst + g * 8) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+    }
+  }
+
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// delta[b,h,s] = sum_d O[b,s,h,d] * dO[b,s,h,d]. One warp per 32/(D/8) (token, head) pairs.
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta, int B,
+                                  int S, int H, int D, int ld_o, int ld_do) {
+  const int lanes_per = D / 8;  // 8 or 16
+  const long gid = blockIdx.x * (long)blockDim.x + threadIdx.x;
+  const long pair = gid / lanes_per;
+  const int v = (int)(gid % lanes_per);
+  const long total = (long)B * S * H;
+  float s = 0.f;
+  if (pair < total) {
+    const int h = (int)(pair % H);
+    const long t = pair / H;
+    uint4 a = *reinterpret_cast<const uint4*>(o + t * ld_o + h * D + v * 8);
+    uint4 g = *reinterpret_cast<const uint4*>(d_o + t * ld_do + h * D + v * 8);
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 x = __bfloat1622float2(a2[i]), y = __bfloat1622float2(g2[i]);
+      s += x.x * y.x + x.y * y.y;
+    }
+  }
+  for (int off = lanes_per / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (pair < total && v == 0) {
+    const int h = (int)(pair % H);
+    const long t = pair / H;
+    const long bb = t / S, ss = t % S;
+    delta[(bb * H + h) * S + ss] = s;
+  }
+}
+
+// dq[t, :] = bf16(dq_acc[t, :] * scale), written into a token-major buffer with row pitch ld.
+__global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long T, int cols, int ld, float scale) {
+  const int vec = cols / 8;
+  const long total = T * vec;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long t = i / vec;
+    const int cidx = (int)(i % vec) * 8;
+    const float4 a = *reinterpret_cast<const float4*>(acc + t * cols + cidx);
+    const float4 b2 = *reinterpret_cast<const float4*>(acc + t * cols + cidx + 4);
+    uint4 o;
+    o.x = pack_bf16x2(a.x * scale, a.y * scale);
+    o.y = pack_bf16x2(a.z * scale, a.w * scale);
+    o.z = pack_bf16x2(b2.x * scale, b2.y * scale);
+    o.w = pack_bf16x2(b2.z * scale, b2.w * scale);
+    *reinterpret_cast<uint4*>(dq + t * ld + cidx) = o;
+  }
+}
+
+}  // namespace inv
+
+using namespace inv;
+
+// Scratch needed by inv_flash_attn_bwd: delta [B,H,S] fp32 followed by dq_acc [B*S, H*D] fp32.
+extern "C" long inv_flash_attn_bwd_scratch_bytes(int B, int S, int H, int head_dim) {
+  long delta = (((long)B * H * S * 4) + 255) & ~255L;
+  return delta + (long)B * S * H * head_dim * 4;
+}
+
+// q,k,v,o,do: token-major bf16. dq,dk,dv: token-major bf16 outputs (may point into one dqkv buffer).
+extern "C" int inv_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, void* dq,
+                                  void* dk, void* dv, void* scratch, int B, int S, int H, int Hkv, int head_dim, int ld_q, int ld_k, int ld_v,
+                                  int ld_o, int ld_do, int ld_dq, int ld_dk, int ld_dv, float scale, int causal, int* status, void* stream) {
+  if ((head_dim != 64 && head_dim != 128) || H % Hkv || (ld_q % 8) || (ld_k % 8) || (ld_v % 8) || (ld_o % 8) || (ld_do % 8) ||
+      (ld_dq % 8) || (ld_dk % 8) || (ld_dv % 8))
+    return -ERR_BAD_ARG;
+  if (B <= 0 || S <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  float* delta = reinterpret_cast<float*>(scratch);
+  const long delta_bytes = (((long)B * H * S * 4) + 255) & ~255L;
+  float* dq_acc = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + delta_bytes);
+  const long T = (long)B * S;
+  cudaError_t e = cudaMemsetAsync(dq_acc, 0, (size_t)T * H * head_dim * 4, st);
+  if (e != cudaSuccess) return -(int)e;
+  {
+    const long threads = T * H * (head_dim / 8);
+    attn_delta_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, B, S, H,
+                                                                        head_dim, ld_o, ld_do);
+  }
+  CUtensorMap tq, tk, tv, tdo;
+  int rc;
+  if ((rc = make_tmap_tokens_bf16(&tq, q, H * head_dim, S, B, ld_q, 128))) return rc;
+  if ((rc = make_tmap_tokens_bf16(&tk, k, Hkv * head_dim, S, B, ld_k, 128))) return rc;
+  if ((rc = make_tmap_tokens_bf16(&tv, v, Hkv * head_dim, S, B, ld_v, 128))) return rc;
+  if ((rc = make_tmap_tokens_bf16(&tdo, d_o, H * head_dim, S, B, ld_do, 128))) return rc;
+  FlashBwdParams p;
+  p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
+  p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv; p.ld_dk = ld_dk; p.ld_dv = ld_dv;
+  p.B = B; p.S = S; p.H = H; p.Hkv = Hkv; p.scale = scale; p.causal = causal; p.status = status;
+  dim3 grid((S + 127) / 128, Hkv, B);
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(flash_bwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<1>::TOTAL);
+    cudaFuncSetAttribute(flash_bwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<2>::TOTAL);
+    configured = true;
+  }
+  if (head_dim == 64) flash_bwd_kernel<1><<<grid, FB_THREADS, BwdSmem<1>::TOTAL, st>>>(tq, tk, tv, tdo, p);
+  else flash_bwd_kernel<2><<<grid, FB_THREADS, BwdSmem<2>::TOTAL, st>>>(tq, tk, tv, tdo, p);
+  {
+    const long n = T * H * head_dim / 8;
+    long g = (n + 255) / 256;
+    if (g > 148 * 16) g = 148 * 16;
+    attn_dq_convert_kernel<<<(unsigned)g, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dq, T, H * head_dim, ld_dq, scale);
+  }
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}

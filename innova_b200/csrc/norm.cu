@@ -1,0 +1,259 @@
+// LayerNorm and RMSNorm, forward and backward, bf16 activations with fp32 statistics.
+//
+// Replaces the reference's math::layer_norm / layer_norm_grad (src/math_avx2.cpp:349-412,
+// src/autograd_grad.cpp:142-181), math::rms_norm / rms_norm_grad (src/math_avx2.cpp:414-457,
+// src/autograd_grad.cpp:183-218) and the fused residual-add RMSNorm (src/gpu_compute_vulkan.cpp:1232-1245).
+//
+// One warp owns one row and reads it with 16-byte loads (8 bf16). Re-reads of a row hit L1. The
+// backward kernels are persistent; each CTA keeps its share of the gamma/beta gradient on chip and
+// writes one partial row per CTA to a scratch buffer [grid, 2, D] (fp32) that a second kernel folds
+// into the fp32 gradient (+=).
+#include "sm100_common.cuh"
+#include "inv_api.h"
+
+namespace inv {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* f) {
+  uint4 v = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 t = __bfloat1622float2(h[j]);
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float* f) {
+  uint4 o;
+  o.x = pack_bf16x2(f[0], f[1]);
+  o.y = pack_bf16x2(f[2], f[3]);
+  o.z = pack_bf16x2(f[4], f[5]);
+  o.w = pack_bf16x2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = o;
+}
+
+// ----------------------------------------------------------------------------------------------
+// Forward. RMS = true: y = x * rsqrt(mean(x^2) + eps) * gamma. Otherwise LayerNorm with beta.
+// If `res` is given, the row normalised is x + res and `xsum` receives that sum (residual stream).
+// ----------------------------------------------------------------------------------------------
+template <bool RMS>
+__global__ void __launch_bounds__(256) norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                                                       const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
+                                                       __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ xsum,
+                                                       float* __restrict__ mean_out, float* __restrict__ rstd_out, int T, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  if (row >= T) return;
+  const __nv_bfloat16* xr = x + (size_t)row * D;
+  const __nv_bfloat16* rr = res ? res + (size_t)row * D : nullptr;
+  float s = 0.f;
+  if (rr) {
+    __nv_bfloat16* xs = xsum + (size_t)row * D;
+    for (int c = lane * 8; c < D; c += 256) {
+      float a[8], b[8];
+      load8(xr + c, a);
+      load8(rr + c, b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] += b[j];
+      store8(xs + c, a);
+      // statistics use the rounded sum so that backward sees the same row
+      float t[8];
+      load8(xs + c, t);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += RMS ? t[j] * t[j] : t[j];
+    }
+    xr = xs;
+  } else {
+    for (int c = lane * 8; c < D; c += 256) {
+      float a[8];
+      load8(xr + c, a);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += RMS ? a[j] * a[j] : a[j];
+    }
+  }
+  s = warp_sum(s);
+  float mean = 0.f, rstd;
+  if (RMS) {
+    rstd = rsqrtf(s / D + eps);
+  } else {
+    mean = s / D;
+    float v = 0.f;
+    for (int c = lane * 8; c < D; c += 256) {
+      float a[8];
+      load8(xr + c, a);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float d = a[j] - mean;
+        v += d * d;
+      }
+    }
+    v = warp_sum(v);
+    rstd = rsqrtf(v / D + eps);
+  }
+  if (lane == 0) {
+    if (mean_out) mean_out[row] = mean;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+  __nv_bfloat16* yr = y + (size_t)row * D;
+  for (int c = lane * 8; c < D; c += 256) {
+    float a[8], g[8], o[8];
+    load8(xr + c, a);
+    load8(gamma + c, g);
+    if (!RMS && beta) {
+      float b[8];
+      load8(beta + c, b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (a[j] - mean) * rstd * g[j] + b[j];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (a[j] - mean) * rstd * g[j];
+    }
+    store8(yr + c, o);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// Backward. dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) for LayerNorm (g = dy * gamma),
+// dx = rstd * (g - xhat * mean(g * xhat)) for RMSNorm. If `dres` is given it is added to dx
+// (gradient arriving on the residual stream). Per-CTA partial dgamma/dbeta go to `partial`.
+// ----------------------------------------------------------------------------------------------
+template <bool RMS>
+__global__ void __launch_bounds__(256) norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                       const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                                                       const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
+                                                       __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int T, int D) {
+  // [2][Dp]: dgamma, dbeta. Column c lives at slot(c), which spreads the 8 columns a lane owns
+  // over 8 different 32-float rows so that a warp's atomics fall into 32 distinct banks.
+  extern __shared__ float acc[];
+  const int Dp = (D + 255) & ~255;
+  for (int i = threadIdx.x; i < 2 * Dp; i += blockDim.x) acc[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int gw = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int nw = gridDim.x * warps_per_block;
+  for (int row = gw; row < T; row += nw) {
+    const __nv_bfloat16* xr = x + (size_t)row * D;
+    const __nv_bfloat16* dyr = dy + (size_t)row * D;
+    const float mean = RMS ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = lane * 8; c < D; c += 256) {
+      float a[8], d[8], g[8];
+      load8(xr + c, a);
+      load8(dyr + c, d);
+      load8(gamma + c, g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float xh = (a[j] - mean) * rstd;
+        float gg = d[j] * g[j];
+        s1 += gg;
+        s2 += gg * xh;
+      }
+    }
+    s1 = warp_sum(s1) / D;
+    s2 = warp_sum(s2) / D;
+    if (RMS) s1 = 0.f;
+    __nv_bfloat16* dxr = dx + (size_t)row * D;
+    const __nv_bfloat16* drr = dres ? dres + (size_t)row * D : nullptr;
+    for (int c = lane * 8; c < D; c += 256) {
+      float a[8], d[8], g[8], o[8];
+      load8(xr + c, a);
+      load8(dyr + c, d);
+      load8(gamma + c, g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float xh = (a[j] - mean) * rstd;
+        o[j] = rstd * (d[j] * g[j] - s1 - xh * s2);
+        const int slot = (c & ~255) + j * 32 + lane;
+        atomicAdd(&acc[slot], d[j] * xh);
+        if (!RMS) atomicAdd(&acc[Dp + slot], d[j]);
+      }
+      if (drr) {
+        float r[8];
+        load8(drr + c, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += r[j];
+      }
+      store8(dxr + c, o);
+    }
+  }
+  __syncthreads();
+  float* out = partial + (size_t)blockIdx.x * 2 * D;
+  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) {
+    const int col = i < D ? i : i - D;
+    const int slot = (col & ~255) + (col & 7) * 32 + ((col & 255) >> 3);
+    out[i] = acc[(i < D ? 0 : Dp) + slot];
+  }
+}
+
+// dgamma[D] += sum_b partial[b][0][:], dbeta[D] += sum_b partial[b][1][:]
+__global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dgamma, float* __restrict__ dbeta,
+                                       int nblocks, int D) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= 2 * D) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += partial[(size_t)b * 2 * D + c];
+  if (c < D) dgamma[c] += s;
+  else if (dbeta) dbeta[c - D] += s;
+}
+
+}  // namespace inv
+
+using namespace inv;
+
+extern "C" int inv_norm_fwd(const void* x, const void* res, const void* gamma, const void* beta, void* y, void* xsum, float* mean,
+                            float* rstd, int T, int D, float eps, int rms, void* stream) {
+  if (D % 8) return -ERR_BAD_ARG;
+  if (T <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int wpb = 8;
+  dim3 grid((T + wpb - 1) / wpb), block(wpb * 32);
+  auto X = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto R = reinterpret_cast<const __nv_bfloat16*>(res);
+  auto G = reinterpret_cast<const __nv_bfloat16*>(gamma);
+  auto B = reinterpret_cast<const __nv_bfloat16*>(beta);
+  auto Y = reinterpret_cast<__nv_bfloat16*>(y);
+  auto XS = reinterpret_cast<__nv_bfloat16*>(xsum);
+  if (rms) norm_fwd_kernel<true><<<grid, block, 0, st>>>(X, R, G, B, Y, XS, mean, rstd, T, D, eps);
+  else norm_fwd_kernel<false><<<grid, block, 0, st>>>(X, R, G, B, Y, XS, mean, rstd, T, D, eps);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+// Number of CTAs the backward launches for T rows; scratch must hold grid*2*D floats.
+extern "C" int inv_norm_bwd_grid(int T) {
+  int g = (T + 7) / 8;
+  return g < 296 ? (g < 1 ? 1 : g) : 296;
+}
+
+extern "C" int inv_norm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, const void* dres,
+                            void* dx, float* dgamma, float* dbeta, float* scratch, int T, int D, int rms, void* stream) {
+  if (D % 8 || D > 12288) return -ERR_BAD_ARG;
+  if (T <= 0) return 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = inv_norm_bwd_grid(T);
+  const size_t smem = (size_t)2 * ((D + 255) & ~255) * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(norm_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 12288 * 4);
+    cudaFuncSetAttribute(norm_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 12288 * 4);
+    configured = true;
+  }
+  auto DY = reinterpret_cast<const __nv_bfloat16*>(dy);
+  auto X = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto G = reinterpret_cast<const __nv_bfloat16*>(gamma);
+  auto DR = reinterpret_cast<const __nv_bfloat16*>(dres);
+  auto DX = reinterpret_cast<__nv_bfloat16*>(dx);
+  if (rms) norm_bwd_kernel<true><<<grid, 256, smem, st>>>(DY, X, G, mean, rstd, DR, DX, scratch, T, D);
+  else norm_bwd_kernel<false><<<grid, 256, smem, st>>>(DY, X, G, mean, rstd, DR, DX, scratch, T, D);
+  norm_bwd_reduce_kernel<<<(2 * D + 255) / 256, 256, 0, st>>>(scratch, dgamma, rms ? nullptr : dbeta, grid, D);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}

@@ -1,0 +1,81 @@
+"""Flash attention (tcgen05) over a fused, token-major qkv buffer.
+
+``flash_attention(qkv, n_heads, n_kv_heads, head_dim)`` takes the output of the fused qkv projection
+``[B, S, (H + 2*Hkv) * D]`` as it is (q heads, then k heads, then v heads along the last dim) and
+returns ``[B, S, H*D]``, so no head transposes are materialised on either side. Reference
+behaviour covered: Attention::forward with GQA and causal masking (src/transformer.cpp:174-352),
+flash_attention_forward (src/flash_attention.cpp:38-191).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from . import runtime as rt
+from .. import _native
+
+_native.register_cuda_sigs({
+    "inv_flash_attn_fwd": [_native.vp] * 5 + [_native.i32] * 9 + [_native.f32, _native.i32, _native.vp, _native.vp],
+    "inv_flash_attn_bwd": [_native.vp] * 10 + [_native.i32] * 13 + [_native.f32, _native.i32, _native.vp, _native.vp],
+})
+
+
+def _scratch_bytes(B, S, H, D):
+    delta = (B * H * S * 4 + 255) & ~255
+    return delta + B * S * H * D * 4
+
+
+class _FlashAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, H, Hkv, D, causal, scale):
+        B, S, ld = qkv.shape
+        assert ld == (H + 2 * Hkv) * D and qkv.is_contiguous() and qkv.dtype == torch.bfloat16
+        out = torch.empty((B, S, H * D), dtype=torch.bfloat16, device=qkv.device)
+        lse = torch.empty((B, H, S), dtype=torch.float32, device=qkv.device)
+        base = qkv.data_ptr()
+        rc = rt.lib().inv_flash_attn_fwd(base, base + H * D * 2, base + (H + Hkv) * D * 2, out.data_ptr(), lse.data_ptr(), B, S, H, Hkv, D,
+                                         ld, ld, ld, H * D, float(scale), int(causal), rt.status_tensor(qkv.device).data_ptr(),
+                                         rt.stream_ptr())
+        rt.check(rc, "inv_flash_attn_fwd")
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.cfg = (H, Hkv, D, causal, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse = ctx.saved_tensors
+        H, Hkv, D, causal, scale = ctx.cfg
+        B, S, ld = qkv.shape
+        dout = dout.contiguous()
+        dqkv = torch.empty_like(qkv)
+        scr = rt.scratch("flash_bwd", _scratch_bytes(B, S, H, D), qkv.device)
+        base, dbase = qkv.data_ptr(), dqkv.data_ptr()
+        rc = rt.lib().inv_flash_attn_bwd(base, base + H * D * 2, base + (H + Hkv) * D * 2, out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+                                         dbase, dbase + H * D * 2, dbase + (H + Hkv) * D * 2, scr.data_ptr(), B, S, H, Hkv, D, ld, ld, ld,
+                                         H * D, H * D, ld, ld, ld, float(scale), int(causal), rt.status_tensor(qkv.device).data_ptr(),
+                                         rt.stream_ptr())
+        rt.check(rc, "inv_flash_attn_bwd")
+        return dqkv, None, None, None, None, None
+
+
+def attention_reference(qkv, H, Hkv, D, causal=True, scale=None):
+    """Plain PyTorch attention on the same fused layout (CPU path and test oracle)."""
+    B, S, _ = qkv.shape
+    q, k, v = qkv.split([H * D, Hkv * D, Hkv * D], dim=-1)
+    q = q.view(B, S, H, D).transpose(1, 2)
+    k = k.view(B, S, Hkv, D).transpose(1, 2)
+    v = v.view(B, S, Hkv, D).transpose(1, 2)
+    if Hkv != H:
+        k = k.repeat_interleave(H // Hkv, dim=1)
+        v = v.repeat_interleave(H // Hkv, dim=1)
+    o = F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale)
+    return o.transpose(1, 2).reshape(B, S, H * D)
+
+
+def flash_attention(qkv, n_heads, n_kv_heads, head_dim, causal=True, scale=None):
+    scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
+    if not qkv.is_cuda:
+        return attention_reference(qkv, n_heads, n_kv_heads, head_dim, causal, scale)
+    return _FlashAttnFn.apply(qkv, n_heads, n_kv_heads, head_dim, causal, scale)

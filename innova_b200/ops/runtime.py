@@ -1,0 +1,71 @@
+"""Small helpers shared by the op wrappers: current stream, device status word, scratch buffers."""
+from __future__ import annotations
+
+import torch
+
+from .. import _native
+
+_status = {}
+_scratch = {}
+
+ERR_NAMES = {
+    0: "ok", 1: "wait_full", 2: "wait_empty", 3: "wait_tmem_full", 4: "wait_tmem_empty", 5: "wait_peer", 6: "wait_misc", 7: "bad_arg",
+}
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def status_tensor(device=None) -> torch.Tensor:
+    """One int32 word per device into which kernels write a code when a bounded wait runs out."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    t = _status.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=dev)
+        _status[key] = t
+    return t
+
+
+def check_status(device=None):
+    """Synchronises and raises if any kernel reported a wait that ran out."""
+    code = int(status_tensor(device).item())
+    if code != 0:
+        status_tensor(device).zero_()
+        raise RuntimeError(f"innova_b200 kernel reported error {code} ({ERR_NAMES.get(code, '?')})")
+
+
+def scratch(name: str, nbytes: int, device) -> torch.Tensor:
+    """A grow-only per-device byte buffer for kernels that need global scratch memory."""
+    dev = torch.device(device)
+    key = (name, dev.index)
+    t = _scratch.get(key)
+    if t is None or t.numel() < nbytes:
+        t = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
+        _scratch[key] = t
+    return t
+
+
+def ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def lib():
+    return _native.cuda()
+
+
+_launches = 0
+
+
+def check(rc: int, what: str):
+    """Every native entry point that launches kernels reports through here, which also counts it."""
+    global _launches
+    _launches += 1
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")
+
+
+def launch_count() -> int:
+    """Number of native kernel-launching calls made so far (each launches at least one kernel)."""
+    return _launches

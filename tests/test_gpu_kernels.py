@@ -1,0 +1,342 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / (b.norm() + 1e-12))
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    from innova_b200.ops import runtime as rt
+    rt.check_status()
+
+
+# ------------------------------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 776, 200), (1000, 264, 1032), (77, 8, 72)])
+def test_gemm_layouts(a_mn, b_mn, M, N, K):
+    from innova_b200 import ops
+    torch.manual_seed(0)
+    dev = _dev()
+    if a_mn and M % 8:
+        M = (M + 7) // 8 * 8
+    A = torch.randn(M, K, device=dev).bfloat16()
+    B = torch.randn(N, K, device=dev).bfloat16()
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    out = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    ref = A.float() @ B.float().t()
+    assert out.shape == (M, N)
+    assert _rel_err(out, ref) < 1e-2
+
+
+def test_gemm_epilogues():
+    from innova_b200 import ops
+    torch.manual_seed(1)
+    dev = _dev()
+    M, N, K = 512, 768, 320
+    A = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
+    B = (torch.randn(N, K, device=dev) * 0.1).bfloat16()
+    bias = torch.randn(N, device=dev).bfloat16()
+    aux = torch.randn(M, N, device=dev).bfloat16()
+    ref = A.float() @ B.float().t()
+    # bias
+    out = ops.gemm(A, B, bias=bias)
+    assert _rel_err(out, ref + bias.float()) < 1e-2
+    # gelu with pre-activation output
+    pre = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    out = ops.gemm(A, B, epilogue=ops.EPI_GELU, bias=bias, aux_out=pre)
+    assert _rel_err(pre, ref + bias.float()) < 1e-2
+    assert _rel_err(out, F.gelu(ref + bias.float(), approximate="tanh")) < 1e-2
+    # dgelu
+    x = aux.float().requires_grad_(True)
+    F.gelu(x, approximate="tanh").sum().backward()
+    out = ops.gemm(A, B, epilogue=ops.EPI_DGELU, aux_in=aux)
+    assert _rel_err(out, ref * x.grad) < 2e-2
+    # residual add (aliasing the output)
+    res = aux.clone()
+    ops.gemm(A, B, out=res, epilogue=ops.EPI_ADD, bias=bias, aux_in=res)
+    assert _rel_err(res, ref + bias.float() + aux.float()) < 1e-2
+    # fp32 output and split-K accumulation
+    out32 = ops.gemm(A, B, out_dtype=torch.float32)
+    assert _rel_err(out32, ref) < 1e-2
+    acc = torch.ones(M, N, device=dev, dtype=torch.float32)
+    ops.gemm(A, B, out=acc, epilogue=ops.EPI_ATOMIC, split_k=3)
+    assert _rel_err(acc, ref + 1.0) < 1e-2
+
+
+def test_gemm_wgrad_shape():
+    """dW[N,K] += dY[T,N]^T X[T,K] with a long reduction and split-K chosen by the wrapper."""
+    from innova_b200 import ops
+    torch.manual_seed(2)
+    dev = _dev()
+    T, N, K = 4096, 768, 256
+    dy = (torch.randn(T, N, device=dev) * 0.1).bfloat16()
+    x = (torch.randn(T, K, device=dev) * 0.1).bfloat16()
+    g = torch.zeros(N, K, device=dev, dtype=torch.float32)
+    ops.gemm(dy, x, out=g, a_mn=True, b_mn=True, epilogue=ops.EPI_ATOMIC)
+    assert _rel_err(g, dy.float().t() @ x.float()) < 1e-2
+
+
+def test_linear_autograd():
+    from innova_b200 import ops
+    torch.manual_seed(3)
+    dev = _dev()
+    x = (torch.randn(4, 96, 256, device=dev) * 0.5).bfloat16().requires_grad_(True)
+    w = (torch.randn(512, 256, device=dev) * 0.05).bfloat16().requires_grad_(True)
+    b = torch.randn(512, device=dev).bfloat16().requires_grad_(True)
+    y = ops.linear(x, w, b)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr, wr, br = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True), b.detach().float().requires_grad_(True)
+    yr = F.linear(xr, wr, br)
+    yr.backward(gy.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 1e-2
+    assert _rel_err(w.grad, wr.grad) < 1e-2
+    assert _rel_err(b.grad, br.grad) < 1e-2
+
+
+def test_mlp_gelu_autograd():
+    from innova_b200 import ops
+    torch.manual_seed(4)
+    dev = _dev()
+    T, E, Fh = 384, 256, 1024
+    x = (torch.randn(T, E, device=dev) * 0.5).bfloat16().requires_grad_(True)
+    res = torch.randn(T, E, device=dev).bfloat16().requires_grad_(True)
+    w1 = (torch.randn(Fh, E, device=dev) * 0.05).bfloat16().requires_grad_(True)
+    b1 = (torch.randn(Fh, device=dev) * 0.1).bfloat16().requires_grad_(True)
+    w2 = (torch.randn(E, Fh, device=dev) * 0.05).bfloat16().requires_grad_(True)
+    b2 = (torch.randn(E, device=dev) * 0.1).bfloat16().requires_grad_(True)
+    y = ops.mlp_gelu(x, w1, b1, w2, b2, res)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    ps = [t.detach().float().requires_grad_(True) for t in (x, res, w1, b1, w2, b2)]
+    yr = F.linear(F.gelu(F.linear(ps[0], ps[2], ps[3]), approximate="tanh"), ps[4], ps[5]) + ps[1]
+    yr.backward(gy.float())
+    assert _rel_err(y, yr) < 1e-2
+    for t, r in zip((x, res, w1, b1, w2, b2), ps):
+        assert _rel_err(t.grad, r.grad) < 2e-2
+
+
+# ------------------------------------------------------------------------------------------ norms
+@pytest.mark.parametrize("rms", [False, True])
+@pytest.mark.parametrize("T,D", [(64, 768), (333, 1024), (16, 5120), (100, 264)])
+def test_norm(rms, T, D):
+    from innova_b200 import ops
+    torch.manual_seed(5)
+    dev = _dev()
+    x = torch.randn(T, D, device=dev).bfloat16().requires_grad_(True)
+    g = (1 + 0.1 * torch.randn(D, device=dev)).bfloat16().requires_grad_(True)
+    b = (0.1 * torch.randn(D, device=dev)).bfloat16().requires_grad_(True)
+    y = ops.rms_norm(x, g, 1e-5) if rms else ops.layer_norm(x, g, b, 1e-5)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr, gr, br = (t.detach().float().requires_grad_(True) for t in (x, g, b))
+    if rms:
+        yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * gr
+    else:
+        yr = F.layer_norm(xr, (D,), gr, br, 1e-5)
+    yr.backward(gy.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 2e-2
+    assert _rel_err(g.grad, gr.grad) < 2e-2
+    if not rms:
+        assert _rel_err(b.grad, br.grad) < 2e-2
+
+
+# ------------------------------------------------------------------------------------------ elementwise
+def test_embedding_and_grad():
+    from innova_b200 import ops
+    torch.manual_seed(6)
+    dev = _dev()
+    V, D, B, S = 1000, 128, 3, 64
+    wte = torch.randn(V, D, device=dev).bfloat16().requires_grad_(True)
+    wpe = torch.randn(S, D, device=dev).bfloat16().requires_grad_(True)
+    ids = torch.randint(0, V, (B, S), device=dev)
+    ids[0, 0] = V + 5  # out of range -> row 0
+    y = ops.embedding(ids, wte, wpe)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    a, p = wte.detach().float().requires_grad_(True), wpe.detach().float().requires_grad_(True)
+    safe = torch.where(ids < V, ids, torch.zeros_like(ids))
+    yr = F.embedding(safe, a) + p[:S]
+    yr.backward(gy.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(wte.grad, a.grad) < 1e-2
+    assert _rel_err(wpe.grad, p.grad) < 1e-2
+
+
+def test_activations():
+    from innova_b200 import ops
+    torch.manual_seed(7)
+    dev = _dev()
+    x = torch.randn(200, 512, device=dev).bfloat16().requires_grad_(True)
+    y = ops.gelu(x)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr = x.detach().float().requires_grad_(True)
+    yr = F.gelu(xr, approximate="tanh")
+    yr.backward(gy.float())
+    assert _rel_err(y, yr) < 1e-2 and _rel_err(x.grad, xr.grad) < 2e-2
+    gu = torch.randn(200, 1024, device=dev).bfloat16().requires_grad_(True)
+    y = ops.swiglu(gu)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    gr = gu.detach().float().requires_grad_(True)
+    g_, u_ = gr.chunk(2, -1)
+    yr = F.silu(g_) * u_
+    yr.backward(gy.float())
+    assert _rel_err(y, yr) < 1e-2 and _rel_err(gu.grad, gr.grad) < 2e-2
+
+
+def test_rope():
+    from innova_b200 import ops
+    torch.manual_seed(8)
+    dev = _dev()
+    B, S, H, Hkv, D = 2, 48, 4, 2, 64
+    qkv = torch.randn(B, S, (H + 2 * Hkv) * D, device=dev).bfloat16()
+    cos, sin = ops.rope_tables(128, D, 10000.0, dev)
+    ref = ops.rope_qk(qkv.cpu().float(), cos.cpu(), sin.cpu(), H, Hkv, D)
+    x = qkv.clone().requires_grad_(True)
+    y = ops.rope_qk(x * 1.0, cos, sin, H, Hkv, D)
+    assert _rel_err(y.cpu(), ref) < 1e-2
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr = qkv.cpu().float().requires_grad_(True)
+    ops.rope_qk(xr, cos.cpu(), sin.cpu(), H, Hkv, D).backward(gy.cpu().float())
+    assert _rel_err(x.grad.cpu(), xr.grad) < 1e-2
+
+
+def test_cross_entropy():
+    from innova_b200 import ops
+    torch.manual_seed(9)
+    dev = _dev()
+    T, V, Vp = 300, 50257, 50304
+    logits = (torch.randn(T, Vp, device=dev) * 2).bfloat16()
+    labels = torch.randint(0, V, (T,), device=dev)
+    labels[5] = -100
+    lr = logits[:, :V].float().requires_grad_(True)
+    ref = F.cross_entropy(lr, labels, ignore_index=-100)
+    ref.backward()
+    lg = logits.clone().requires_grad_(True)
+    loss = ops.cross_entropy(lg * 1.0, labels, vocab=V)
+    loss.backward()
+    assert abs(float(loss) - float(ref)) < 2e-3 * max(1.0, abs(float(ref)))
+    assert _rel_err(lg.grad[:, :V], lr.grad) < 2e-2
+    assert float(lg.grad[:, V:].abs().max()) == 0.0
+
+
+def test_lm_head_ce_fused():
+    from innova_b200 import ops
+    torch.manual_seed(10)
+    dev = _dev()
+    T, E, V, Vp = 640, 256, 1000, 1024
+    x = (torch.randn(T, E, device=dev)).bfloat16().requires_grad_(True)
+    w = (torch.randn(Vp, E, device=dev) * 0.05).bfloat16().requires_grad_(True)
+    labels = torch.randint(0, V, (T,), device=dev)
+    loss = ops.lm_head_cross_entropy(x, w, labels, vocab=V, chunk=256)
+    loss.backward()
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    ref = F.cross_entropy(F.linear(xr, wr)[:, :V], labels)
+    ref.backward()
+    assert abs(float(loss) - float(ref)) < 5e-3
+    assert _rel_err(x.grad, xr.grad) < 3e-2
+    assert _rel_err(w.grad[:V], wr.grad[:V]) < 3e-2
+
+
+def test_adamw_matches_torch():
+    from innova_b200.training.flat_engine import FlatParamEngine
+    torch.manual_seed(11)
+    dev = _dev()
+    lin = torch.nn.Linear(96, 160).to(dev).bfloat16()
+    ref = torch.nn.Linear(96, 160).to(dev).float()
+    ref.load_state_dict({k: v.float() for k, v in lin.state_dict().items()})
+    eng = FlatParamEngine(lin, lr=1e-2, weight_decay=0.1, max_grad_norm=0.0)
+    opt = torch.optim.AdamW([{"params": [ref.weight], "weight_decay": 0.1}, {"params": [ref.bias], "weight_decay": 0.0}], lr=1e-2, eps=1e-8)
+    for _ in range(5):
+        gw, gb = torch.randn_like(ref.weight), torch.randn_like(ref.bias)
+        lin.weight.main_grad.copy_(gw)
+        lin.bias.main_grad.copy_(gb)
+        ref.weight.grad, ref.bias.grad = gw.clone(), gb.clone()
+        eng.step()
+        opt.step()
+    w_master = eng.master[: ref.weight.numel()].view_as(ref.weight)
+    assert _rel_err(w_master, ref.weight) < 1e-4
+    assert _rel_err(lin.weight, ref.weight) < 1e-2
+    assert float(eng.flat_grad.abs().max()) == 0.0
+
+
+# ------------------------------------------------------------------------------------------ attention
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("B,S,H,Hkv,causal", [(2, 256, 4, 4, True), (1, 384, 4, 2, True), (2, 200, 2, 2, True), (1, 256, 2, 1, False),
+                                              (1, 1024, 2, 2, True)])
+def test_flash_attention(D, B, S, H, Hkv, causal):
+    from innova_b200 import ops
+    torch.manual_seed(12)
+    dev = _dev()
+    qkv = (torch.randn(B, S, (H + 2 * Hkv) * D, device=dev) * 0.7).bfloat16().requires_grad_(True)
+    out = ops.flash_attention(qkv, H, Hkv, D, causal=causal)
+    go = torch.randn_like(out)
+    out.backward(go)
+    qr = qkv.detach().float().requires_grad_(True)
+    ref = ops.attention_reference(qr, H, Hkv, D, causal=causal, scale=1.0 / math.sqrt(D))
+    ref.backward(go.float())
+    assert _rel_err(out, ref) < 2e-2
+    dq, dk, dv = qkv.grad.split([H * D, Hkv * D, Hkv * D], dim=-1)
+    rq, rk, rv = qr.grad.split([H * D, Hkv * D, Hkv * D], dim=-1)
+    assert _rel_err(dv, rv) < 3e-2
+    assert _rel_err(dk, rk) < 3e-2
+    assert _rel_err(dq, rq) < 3e-2
+
+
+# ------------------------------------------------------------------------------------------ model
+def test_dense_model_matches_cpu_reference():
+    from innova_b200.models import DenseModel, gpt2_small
+    torch.manual_seed(13)
+    dev = _dev()
+    cfg = gpt2_small(num_layers=2, hidden_size=256, num_heads=4, ffn_hidden_size=512, vocab_size=1000, max_seq_len=256)
+    cpu = DenseModel(cfg, dtype=torch.float32)
+    gpu = DenseModel(cfg, dtype=torch.bfloat16)
+    gpu.load_state_dict({k: v.bfloat16() for k, v in cpu.state_dict().items()})
+    gpu.to(dev)
+    ids = torch.randint(0, 1000, (2, 256))
+    labels = torch.randint(0, 1000, (2, 256))
+    lc = cpu(ids, labels)
+    lg = gpu(ids.to(dev), labels.to(dev))
+    assert abs(float(lc) - float(lg)) < 3e-2
+    lc.backward()
+    lg.backward()
+    for (n, pc), (_, pg) in zip(cpu.named_parameters(), gpu.named_parameters()):
+        assert pg.grad is not None, n
+        assert _rel_err(pg.grad, pc.grad) < 8e-2, n
+
+
+def test_llama_style_model_trains():
+    from innova_b200.models import DenseModel, TransformerConfig
+    from innova_b200.training.trainer import Trainer, TrainConfig
+    torch.manual_seed(14)
+    dev = _dev()
+    cfg = TransformerConfig(vocab_size=512, hidden_size=256, num_layers=2, num_heads=4, head_dim=64, ffn_hidden_size=512, num_kv_heads=2,
+                            max_seq_len=128)
+    model = DenseModel(cfg, dtype=torch.bfloat16, device=dev)
+    tr = Trainer(model, TrainConfig(lr=2e-3))
+    ids = torch.randint(0, 512, (4, 128), device=dev)
+    labels = torch.roll(ids, -1, dims=1)
+    first = float(tr.train_step(ids, labels))
+    for _ in range(10):
+        last = float(tr.train_step(ids, labels))
+    assert last < first - 0.5
