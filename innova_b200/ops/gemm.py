@@ -104,19 +104,23 @@ class _LinearFn(torch.autograd.Function):
             x2 = x2.contiguous()
         N = weight.shape[0]
         pre = None
+        # the result is allocated in its final shape: returning a view made here would forbid
+        # in-place consumers (RoPE rotates the qkv projection in place)
+        y = torch.empty((*shp[:-1], N), dtype=torch.bfloat16, device=x.device)
+        y2 = y.view(-1, N)
         if mode == "gelu":
             pre = torch.empty((x2.shape[0], N), dtype=torch.bfloat16, device=x.device)
-            y = gemm(x2, weight, epilogue=EPI_GELU, bias=bias, aux_out=pre)
+            gemm(x2, weight, out=y2, epilogue=EPI_GELU, bias=bias, aux_out=pre)
         elif mode == "add":
             r2 = residual.reshape(-1, N)
-            y = gemm(x2, weight, epilogue=EPI_ADD, bias=bias, aux_in=r2)
+            gemm(x2, weight, out=y2, epilogue=EPI_ADD, bias=bias, aux_in=r2)
         else:
-            y = gemm(x2, weight, bias=bias)
+            gemm(x2, weight, out=y2, bias=bias)
         ctx.mode = mode
         ctx.has_bias = bias is not None
         ctx.save_for_backward(x2, weight, bias, pre)
         ctx.xshape = shp
-        return y.view(*shp[:-1], N)
+        return y
 
     @staticmethod
     def backward(ctx, dy):
@@ -170,14 +174,15 @@ class _MlpGeluFn(torch.autograd.Function):
         Fdim, N = w1.shape[0], w2.shape[0]
         pre = torch.empty((T, Fdim), dtype=torch.bfloat16, device=x.device)
         act = gemm(x2, w1, epilogue=EPI_GELU, bias=b1, aux_out=pre)
+        y = torch.empty((*shp[:-1], N), dtype=torch.bfloat16, device=x.device)
         if residual is not None:
-            y = gemm(act, w2, epilogue=EPI_ADD, bias=b2, aux_in=residual.reshape(-1, N))
+            gemm(act, w2, out=y.view(-1, N), epilogue=EPI_ADD, bias=b2, aux_in=residual.reshape(-1, N))
         else:
-            y = gemm(act, w2, bias=b2)
+            gemm(act, w2, out=y.view(-1, N), bias=b2)
         ctx.save_for_backward(x2, pre, act, w1, b1, w2, b2)
         ctx.has_res = residual is not None
         ctx.xshape = shp
-        return y.view(*shp[:-1], N)
+        return y
 
     @staticmethod
     def backward(ctx, dy):
