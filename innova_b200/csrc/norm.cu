@@ -257,3 +257,63 @@ extern "C" int inv_norm_bwd(const void* dy, const void* x, const void* gamma, co
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }
+
+// ----------------------------------------------------------------------------------------------
+// No-allocation variant of the backward (declared and documented in inv_noalloc.h).
+// The partial sums go to a file-scope device array instead of caller-provided scratch. In host code
+// the array's name is only a handle: its device address comes from cudaGetSymbolAddress, looked up
+// once per device with that device current, and that address is what the kernels receive.
+// ----------------------------------------------------------------------------------------------
+#include "inv_noalloc.h"
+
+#include <mutex>
+
+static __device__ __align__(256) float g_norm_bwd_partials[INV_NOALLOC_NORM_MAX_GRID * 2 * INV_NOALLOC_NORM_MAX_D];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_partials_addr[kMaxDevices] = {nullptr};
+std::mutex g_partials_mutex;
+
+// Device address of the static array on the current device, or nullptr with *err set.
+float* noalloc_partials(cudaError_t* err) {
+  int dev = -1;
+  *err = cudaGetDevice(&dev);
+  if (*err != cudaSuccess) return nullptr;
+  if (dev < 0 || dev >= kMaxDevices) {
+    *err = cudaErrorInvalidDevice;
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_partials_mutex);
+  if (g_partials_addr[dev] == nullptr) {
+    void* p = nullptr;
+    *err = cudaGetSymbolAddress(&p, g_norm_bwd_partials);
+    if (*err != cudaSuccess) return nullptr;
+    g_partials_addr[dev] = static_cast<float*>(p);
+  }
+  return g_partials_addr[dev];
+}
+}  // namespace
+
+extern "C" int inv_norm_bwd_noalloc(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, const void* dres,
+                                    void* dx, float* dgamma, float* dbeta, int T, int D, int rms, void* stream) {
+  if (D <= 0 || (D % 8) != 0 || D > INV_NOALLOC_NORM_MAX_D) return -ERR_BAD_ARG;  // beyond the static scratch
+  if (T <= 0) return 0;
+  cudaError_t err = cudaSuccess;
+  float* partials = noalloc_partials(&err);
+  if (partials == nullptr) return -(int)err;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int grid = (T + 7) / 8;
+  if (grid > INV_NOALLOC_NORM_MAX_GRID) grid = INV_NOALLOC_NORM_MAX_GRID;
+  const size_t smem = (size_t)2 * ((D + 255) & ~255) * sizeof(float);  // at most 16 KiB: no opt-in needed
+  auto DY = reinterpret_cast<const __nv_bfloat16*>(dy);
+  auto X = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto G = reinterpret_cast<const __nv_bfloat16*>(gamma);
+  auto DR = reinterpret_cast<const __nv_bfloat16*>(dres);
+  auto DX = reinterpret_cast<__nv_bfloat16*>(dx);
+  if (rms) norm_bwd_kernel<true><<<grid, 256, smem, st>>>(DY, X, G, mean, rstd, DR, DX, partials, T, D);
+  else norm_bwd_kernel<false><<<grid, 256, smem, st>>>(DY, X, G, mean, rstd, DR, DX, partials, T, D);
+  norm_bwd_reduce_kernel<<<(2 * D + 255) / 256, 256, 0, st>>>(partials, dgamma, rms ? nullptr : dbeta, grid, D);
+  err = cudaGetLastError();
+  return err == cudaSuccess ? 0 : -(int)err;
+}
