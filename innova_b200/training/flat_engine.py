@@ -54,8 +54,9 @@ class FlatParamEngine:
         self.total = _round_up(off, total_pad_to)
         first = params[0][1]
         self.device, self.dtype = first.device, first.dtype
-        self.flat_param = torch.zeros(self.total, dtype=self.dtype, device=self.device)
-        self.flat_grad = torch.zeros(self.total, dtype=torch.float32, device=self.device)
+        self._pre_alloc()
+        self.flat_param = self._alloc(self.total, self.dtype, "param")
+        self.flat_grad = self._alloc(self.total, torch.float32, "grad")
         for n, p, o, k in self.entries:
             self.flat_param[o:o + k].copy_(p.data.reshape(-1))
             p.data = self.flat_param[o:o + k].view(p.shape)
@@ -67,6 +68,13 @@ class FlatParamEngine:
         self._hyper_host = torch.zeros(16, dtype=torch.float32)
         if self.device.type == "cuda":
             self._hyper_host = self._hyper_host.pin_memory()
+
+    def _pre_alloc(self):
+        pass
+
+    def _alloc(self, n, dtype, kind):
+        """Storage of the flat buffers; the sharded engine overrides this with symmetric memory."""
+        return torch.zeros(n, dtype=dtype, device=self.device)
 
     # shard = [lo, hi) of the flat index space whose master weights and moments this rank owns
     def _init_state(self, lo, hi):
