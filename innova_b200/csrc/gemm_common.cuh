@@ -1,0 +1,141 @@
+// Shared pieces of the tcgen05 GEMM kernels: launch parameters and the register-level epilogue.
+#pragma once
+#include "sm100_common.cuh"
+#include "inv_api.h"
+
+namespace inv {
+
+struct GemmParams {
+  int M, N, K;
+  int split_k;
+  void* C;
+  int ldc;
+  int c_f32;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* aux_in;
+  int ld_aux;
+  __nv_bfloat16* aux_out;
+  int epilogue;
+  float alpha;
+  int* status;
+  int swap_lbo_sbo;  // debug aid for MN-major descriptors
+};
+
+// 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows of `ld` elements; 128B swizzle.
+int make_tmap_2d_bf16(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld, uint32_t box_inner,
+                      uint32_t box_outer);
+
+// One thread's 32 consecutive accumulator columns (row `row`, columns col0..col0+31) through the
+// fused epilogue and out to memory. `r` holds the raw fp32 bits read from TMEM.
+// bf16 results go either straight to global memory (stg_c == nullptr) or into this thread's 128-byte
+// row of a 32-row x 64-column staging box in shared memory (128B swizzle), from which the warp
+// issues one TMA store; `sub` says which 32-column half of the box these columns are.
+__device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& p, int row, bool row_ok, int col0, const uint32_t* r,
+                                                    uint8_t* stg_c = nullptr, uint8_t* stg_aux = nullptr, int sub = 0, int lane = 0) {
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+    if (p.bias != nullptr) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (col0 + g * 8 < p.N) {
+          uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + g * 8));
+          const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 f = __bfloat1622float2(b2[j]);
+            v[g * 8 + 2 * j] += f.x;
+            v[g * 8 + 2 * j + 1] += f.y;
+          }
+        }
+      }
+    }
+    if (row_ok) {
+      if (p.epilogue == EPI_GELU) {
+        if (p.aux_out != nullptr) {
+          __nv_bfloat16* ap = p.aux_out + (size_t)row * p.ld_aux + col0;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (col0 + g * 8 < p.N) {
+              uint4 o;
+              o.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
+              o.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
+              o.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
+              o.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
+              if (stg_aux) *reinterpret_cast<uint4*>(stg_aux + (((sub * 4 + g) ^ (lane & 7)) << 4)) = o;
+              else *reinterpret_cast<uint4*>(ap + g * 8) = o;
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+      } else if (p.epilogue == EPI_DGELU || p.epilogue == EPI_ADD) {
+        const __nv_bfloat16* ap = p.aux_in + (size_t)row * p.ld_aux + col0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (col0 + g * 8 < p.N) {
+            uint4 av = *reinterpret_cast<const uint4*>(ap + g * 8);
+            const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float2 f = __bfloat1622float2(a2[j]);
+              if (p.epilogue == EPI_DGELU) {
+                v[g * 8 + 2 * j] *= gelu_tanh_grad(f.x);
+                v[g * 8 + 2 * j + 1] *= gelu_tanh_grad(f.y);
+              } else {
+                v[g * 8 + 2 * j] += f.x;
+                v[g * 8 + 2 * j + 1] += f.y;
+              }
+            }
+          }
+        }
+      }
+      if (p.c_f32) {
+        float* cp = reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc + col0;
+        if (p.epilogue == EPI_ATOMIC) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            if (col0 + g * 4 < p.N) {
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + g * 4), "f"(v[g * 4]),
+                           "f"(v[g * 4 + 1]), "f"(v[g * 4 + 2]), "f"(v[g * 4 + 3])
+                           : "memory");
+            }
+          }
+        } else {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            if (col0 + g * 4 < p.N)
+              *reinterpret_cast<float4*>(cp + g * 4) = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+          }
+        }
+      } else {
+        __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + col0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (col0 + g * 8 < p.N) {
+            uint4 o;
+            o.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
+            o.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
+            o.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
+            o.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
+            if (stg_c) *reinterpret_cast<uint4*>(stg_c + (((sub * 4 + g) ^ (lane & 7)) << 4)) = o;
+            else *reinterpret_cast<uint4*>(cp + g * 8) = o;
+          }
+        }
+      }
+    }
+}
+
+// TMA store of a shared-memory box (128B swizzle) into a 2-D bf16 tensor; rows / columns outside
+// the tensor are clipped by the hardware.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* smem_src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until the shared memory of every committed store group of this thread has been read.
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+}  // namespace inv

@@ -3,21 +3,20 @@
 // Replaces the reference's CPU GEMMs (src/kernel_gemm.cpp:13-118, src/math_avx2_tiled.cpp:308-527:
 // GEMM + bias + activation) and its 16x16 shader GEMM (src/gpu_compute_full.cpp:29-69).
 //
-// Design (one persistent CTA per SM, 192 threads, warp-specialised):
+// Design (one persistent CTA per SM, 320 threads, warp-specialised):
 //   warp 0   : TMA producer. Streams 128x64 A tiles and 256x64 B tiles into a 4-stage ring of
 //              128B-swizzled shared memory.
 //   warp 1   : allocates all 512 TMEM columns and issues tcgen05.mma (M=128, N=256, K=16) from one
 //              thread. Two 128x256 fp32 accumulators live in TMEM, so that the mainloop of tile i+1
 //              overlaps the epilogue of tile i.
-//   warps 2-5: epilogue. tcgen05.ld the accumulator (one row per thread), apply bias / GELU /
+//   warps 2-9: epilogue. tcgen05.ld the accumulator (one row per thread), apply bias / GELU /
 //              GELU-backward / residual add, and store bf16 or fp32; a split-K unit instead adds
 //              its partial sums into an fp32 C with vector reductions.
 // Either operand may be K-major ([rows, K] row-major) or MN-major ([K, rows] row-major); the latter
 // lets the backward GEMMs (dgrad reads W[N,K] along N, wgrad reads X and dY along tokens) run with no
 // transposes in memory.
 // All waits are bounded; a wait that runs out writes a code into *status and the CTA unwinds.
-#include "sm100_common.cuh"
-#include "inv_api.h"
+#include "gemm_common.cuh"
 
 #include <mutex>
 
@@ -26,25 +25,10 @@ namespace inv {
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
 constexpr int GEMM_SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int TMEM_COLS = 512;
 
-struct GemmParams {
-  int M, N, K;
-  int split_k;
-  void* C;
-  int ldc;
-  int c_f32;
-  const __nv_bfloat16* bias;
-  const __nv_bfloat16* aux_in;
-  int ld_aux;
-  __nv_bfloat16* aux_out;
-  int epilogue;
-  float alpha;
-  int* status;
-  int swap_lbo_sbo;  // debug aid for MN-major descriptors
-};
 
 struct WorkUnit {
   int m0, n0, kb_begin, kb_end;
@@ -92,7 +76,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 4);
+      mbar_init(&tmem_empty[a], 8);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -183,7 +167,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else {
     // ---------------- epilogue (4 warps; warp w may touch TMEM lanes 32*(w%4)..+31) ----------------
+    // 8 warps: warp w reads TMEM lanes 32*(w%4)..+31; warps 2-5 take columns 0-127, warps 6-9 columns 128-255
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
     int tile_i = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++tile_i) {
       WorkUnit u = decode_work(w, m_tiles, n_tiles, kb_total, kb_per_split);
@@ -195,102 +181,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * 4; c < half * 4 + 4; c += 2) {
         const int col0 = u.n0 + c * 32;
         if (col0 >= p.N) break;  // uniform across the warp
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c * 32, r);
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(t_row + c * 32, r0);
+        tmem_ld_32x32(t_row + c * 32 + 32, r1);
         tmem_ld_wait();
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
-        if (p.bias != nullptr) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (col0 + g * 8 < p.N) {
-              uint4 bv = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + g * 8));
-              const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float2 f = __bfloat1622float2(b2[j]);
-                v[g * 8 + 2 * j] += f.x;
-                v[g * 8 + 2 * j + 1] += f.y;
-              }
-            }
-          }
-        }
-        if (row_ok) {
-          if (p.epilogue == EPI_GELU) {
-            if (p.aux_out != nullptr) {
-              __nv_bfloat16* ap = p.aux_out + (size_t)row * p.ld_aux + col0;
-#pragma unroll
-              for (int g = 0; g < 4; ++g) {
-                if (col0 + g * 8 < p.N) {
-                  uint4 o;
-                  o.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
-                  o.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
-                  o.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
-                  o.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
-                  *reinterpret_cast<uint4*>(ap + g * 8) = o;
-                }
-              }
-            }
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
-          } else if (p.epilogue == EPI_DGELU || p.epilogue == EPI_ADD) {
-            const __nv_bfloat16* ap = p.aux_in + (size_t)row * p.ld_aux + col0;
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (col0 + g * 8 < p.N) {
-                uint4 av = *reinterpret_cast<const uint4*>(ap + g * 8);
-                const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  float2 f = __bfloat1622float2(a2[j]);
-                  if (p.epilogue == EPI_DGELU) {
-                    v[g * 8 + 2 * j] *= gelu_tanh_grad(f.x);
-                    v[g * 8 + 2 * j + 1] *= gelu_tanh_grad(f.y);
-                  } else {
-                    v[g * 8 + 2 * j] += f.x;
-                    v[g * 8 + 2 * j + 1] += f.y;
-                  }
-                }
-              }
-            }
-          }
-          if (p.c_f32) {
-            float* cp = reinterpret_cast<float*>(p.C) + (size_t)row * p.ldc + col0;
-            if (p.epilogue == EPI_ATOMIC) {
-#pragma unroll
-              for (int g = 0; g < 8; ++g) {
-                if (col0 + g * 4 < p.N) {
-                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + g * 4), "f"(v[g * 4]),
-                               "f"(v[g * 4 + 1]), "f"(v[g * 4 + 2]), "f"(v[g * 4 + 3])
-                               : "memory");
-                }
-              }
-            } else {
-#pragma unroll
-              for (int g = 0; g < 8; ++g) {
-                if (col0 + g * 4 < p.N)
-                  *reinterpret_cast<float4*>(cp + g * 4) = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-              }
-            }
-          } else {
-            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.C) + (size_t)row * p.ldc + col0;
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (col0 + g * 8 < p.N) {
-                uint4 o;
-                o.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
-                o.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
-                o.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
-                o.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
-                *reinterpret_cast<uint4*>(cp + g * 8) = o;
-              }
-            }
-          }
-        }
+        gemm_epilogue_chunk(p, row, row_ok, col0, r0);
+        if (col0 + 32 < p.N) gemm_epilogue_chunk(p, row, row_ok, col0 + 32, r1);
       }
       tc_fence_before();
       __syncwarp();
@@ -362,6 +261,9 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
 
 static int g_num_sms = 0;
 
+int gemm_2cta_dispatch(const void* A, const void* B, const GemmParams& p0, int lda, int ldb, int a_mn, int b_mn, int num_sms,
+                       cudaStream_t stream);
+
 }  // namespace inv
 
 using namespace inv;
@@ -381,6 +283,21 @@ extern "C" int inv_gemm_bf16(const void* A, const void* B, void* C, int M, int N
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
     if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  if (!(debug_flags & 2) && M > 128 && N > 128) {
+    // large problems: 256x256 tiles on CTA pairs (gemm_tcgen05_2cta.cu)
+    GemmParams q;
+    q.M = M; q.N = N; q.K = K; q.split_k = split_k;
+    q.C = C; q.ldc = ldc; q.c_f32 = c_f32;
+    q.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+    q.aux_in = reinterpret_cast<const __nv_bfloat16*>(aux_in);
+    q.ld_aux = ld_aux;
+    q.aux_out = reinterpret_cast<__nv_bfloat16*>(aux_out);
+    q.epilogue = epilogue;
+    q.alpha = alpha;
+    q.status = status;
+    q.swap_lbo_sbo = debug_flags;
+    return gemm_2cta_dispatch(A, B, q, lda, ldb, a_mn, b_mn, g_num_sms, reinterpret_cast<cudaStream_t>(stream));
   }
   CUtensorMap ta, tb;
   int rc;

@@ -260,13 +260,15 @@ struct Ranked {
   float mag;
   int idx;
 };
-// Largest `keep` magnitudes, descending; equal magnitudes keep ascending index order.
+// Largest `keep` magnitudes, descending. Ties are left to std::partial_sort on the index-ordered
+// input, which is what the reference does, so equal magnitudes come out in the same order as there
+// when both are built against the same standard library.
 void top_magnitudes(const float* w, int n, int keep, std::vector<Ranked>& r) {
   r.resize((size_t)n);
   for (int i = 0; i < n; ++i) r[(size_t)i] = {std::fabs(w[i]), i};
   if (keep > 0)
     std::partial_sort(r.begin(), r.begin() + keep, r.end(),
-                      [](const Ranked& a, const Ranked& b) { return a.mag > b.mag || (a.mag == b.mag && a.idx < b.idx); });
+                      [](const Ranked& a, const Ranked& b) { return a.mag > b.mag; });
 }
 inline void put_record(std::vector<uint8_t>& out, int slot, int idx, float normalised) {
   int q = (int)std::lround(normalised * 127.0f);

@@ -193,6 +193,104 @@ __global__ void __launch_bounds__(256) norm_bwd_kernel(const __nv_bfloat16* __re
   }
 }
 
+
+// Rows of at most 1024 elements: the row (x and dy) and this thread's share of the gamma/beta
+// gradient stay in registers; no shared-memory atomics. NCH = ceil(D / 256) chunks of 8 per lane.
+template <bool RMS, int NCH>
+__global__ void __launch_bounds__(256) norm_bwd_small_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                             const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                                                             const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
+                                                             __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int T, int D) {
+  __shared__ float red[8][256];  // one 256-column slab at a time
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gw = blockIdx.x * 8 + warp;
+  const int nw = gridDim.x * 8;
+  float g[NCH][8], dg[NCH][8], db[NCH][8];
+#pragma unroll
+  for (int k = 0; k < NCH; ++k) {
+    const int c = k * 256 + lane * 8;
+    if (c < D) load8(gamma + c, g[k]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      dg[k][j] = 0.f;
+      db[k][j] = 0.f;
+      if (c >= D) g[k][j] = 0.f;
+    }
+  }
+  for (int row = gw; row < T; row += nw) {
+    const __nv_bfloat16* xr = x + (size_t)row * D;
+    const __nv_bfloat16* dyr = dy + (size_t)row * D;
+    const float mean = RMS ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float xh[NCH][8], d[NCH][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < D) {
+        load8(xr + c, xh[k]);
+        load8(dyr + c, d[k]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) xh[k][j] = mean, d[k][j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        xh[k][j] = (xh[k][j] - mean) * rstd;
+        const float gg = d[k][j] * g[k][j];
+        s1 += gg;
+        s2 += gg * xh[k][j];
+      }
+    }
+    s1 = RMS ? 0.f : warp_sum(s1) / D;
+    s2 = warp_sum(s2) / D;
+    __nv_bfloat16* dxr = dx + (size_t)row * D;
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const int c = k * 256 + lane * 8;
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j] = rstd * (d[k][j] * g[k][j] - s1 - xh[k][j] * s2);
+        dg[k][j] += d[k][j] * xh[k][j];
+        db[k][j] += d[k][j];
+      }
+      if (c < D) {
+        if (dres) {
+          float r[8];
+          load8(dres + (size_t)row * D + c, r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += r[j];
+        }
+        store8(dxr + c, o);
+      }
+    }
+  }
+  // fold the 8 warps of the CTA, one 256-column slab at a time, and write this CTA's partial row
+  float* out = partial + (size_t)blockIdx.x * 2 * D;
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    if (RMS && which == 1) break;
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < 8; ++j) red[warp][lane * 8 + j] = which == 0 ? dg[k][j] : db[k][j];
+      __syncthreads();
+      const int c = k * 256 + threadIdx.x;
+      if (c < D) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) s += red[w][threadIdx.x];
+        out[which * D + c] = s;
+      }
+    }
+  }
+  if (RMS) {
+    for (int c = threadIdx.x; c < D; c += 256) out[D + c] = 0.f;
+  }
+}
+
 // dgamma[D] += sum_b partial[b][0][:], dbeta[D] += sum_b partial[b][1][:]
 __global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dgamma, float* __restrict__ dbeta,
                                        int nblocks, int D) {
@@ -251,8 +349,20 @@ extern "C" int inv_norm_bwd(const void* dy, const void* x, const void* gamma, co
   auto G = reinterpret_cast<const __nv_bfloat16*>(gamma);
   auto DR = reinterpret_cast<const __nv_bfloat16*>(dres);
   auto DX = reinterpret_cast<__nv_bfloat16*>(dx);
-  if (rms) norm_bwd_kernel<true><<<grid, 256, smem, st>>>(DY, X, G, mean, rstd, DR, DX, scratch, T, D);
-  else norm_bwd_kernel<false><<<grid, 256, smem, st>>>(DY, X, G, mean, rstd, DR, DX, scratch, T, D);
+  const int nch = (D + 255) / 256;
+#define INV_NB_SMALL(R, N) norm_bwd_small_kernel<R, N><<<grid, 256, 0, st>>>(DY, X, G, mean, rstd, DR, DX, scratch, T, D)
+  if (nch <= 4) {  // register path
+    if (rms) {
+      if (nch == 1) INV_NB_SMALL(true, 1); else if (nch == 2) INV_NB_SMALL(true, 2); else if (nch == 3) INV_NB_SMALL(true, 3); else INV_NB_SMALL(true, 4);
+    } else {
+      if (nch == 1) INV_NB_SMALL(false, 1); else if (nch == 2) INV_NB_SMALL(false, 2); else if (nch == 3) INV_NB_SMALL(false, 3); else INV_NB_SMALL(false, 4);
+    }
+  } else if (rms) {
+    norm_bwd_kernel<true><<<grid, 256, smem, st>>>(DY, X, G, mean, rstd, DR, DX, scratch, T, D);
+  } else {
+    norm_bwd_kernel<false><<<grid, 256, smem, st>>>(DY, X, G, mean, rstd, DR, DX, scratch, T, D);
+  }
+#undef INV_NB_SMALL
   norm_bwd_reduce_kernel<<<(2 * D + 255) / 256, 256, 0, st>>>(scratch, dgamma, rms ? nullptr : dbeta, grid, D);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;

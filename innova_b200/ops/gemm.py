@@ -17,15 +17,19 @@ from . import runtime as rt
 
 EPI_NONE, EPI_GELU, EPI_DGELU, EPI_ADD, EPI_ATOMIC = 0, 1, 2, 3, 4
 NUM_SMS = 148
-_debug_flags = 0
+import os
+_debug_flags = int(os.environ.get("INV_GEMM_DEBUG", "0"))
 
 
 def _split_k_for(M, N, K):
-    tiles = ((M + 127) // 128) * ((N + 255) // 256)
     kb = (K + 63) // 64
-    if tiles >= NUM_SMS:
+    if M > 128 and N > 128:  # 256x256 tiles on CTA pairs
+        tiles, units = ((M + 255) // 256) * ((N + 255) // 256), NUM_SMS // 2
+    else:
+        tiles, units = ((M + 127) // 128) * ((N + 255) // 256), NUM_SMS
+    if tiles >= units:
         return 1
-    return max(1, min(kb, (2 * NUM_SMS) // tiles))
+    return max(1, min(kb, (2 * units) // tiles))
 
 
 def gemm(a, b, out=None, *, a_mn=False, b_mn=False, M=None, N=None, K=None, epilogue=EPI_NONE, bias=None, aux_in=None,

@@ -73,7 +73,7 @@ class ShardedFlatEngine(FlatParamEngine):
 
     def _hyper_for_shard(self, grad_scale):
         h = self._fill_hyper(self.weight_decay, grad_scale)
-        self.hyper.copy_(h, non_blocking=False)
+        self.hyper.copy_(h, non_blocking=True)
         return self.hyper
 
     def _step_p2p(self, grad_scale):

@@ -65,9 +65,12 @@ class FlatParamEngine:
         self._init_state(0, self.total)
         self.gnorm_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.hyper = torch.zeros(16, dtype=torch.float32, device=self.device)
-        self._hyper_host = torch.zeros(16, dtype=torch.float32)
+        # ring of pinned staging rows: the copy to the device is asynchronous, so a row must not be
+        # rewritten before the stream has consumed it (the host never runs more than a few steps ahead)
+        self._hyper_ring = torch.zeros(32, 16, dtype=torch.float32)
+        self._hyper_slot = 0
         if self.device.type == "cuda":
-            self._hyper_host = self._hyper_host.pin_memory()
+            self._hyper_ring = self._hyper_ring.pin_memory()
 
     def _pre_alloc(self):
         pass
@@ -93,7 +96,8 @@ class FlatParamEngine:
         lr = self.current_lr()
         bc1, bc2 = 1.0 - b1 ** t, 1.0 - b2 ** t
         lr_adj = lr * math.sqrt(bc2) / bc1 if self.reference_formula else lr / bc1
-        h = self._hyper_host
+        self._hyper_slot = (self._hyper_slot + 1) % self._hyper_ring.shape[0]
+        h = self._hyper_ring[self._hyper_slot]
         h[0], h[1], h[2], h[3], h[4], h[5] = lr_adj, b1, b2, self.eps, lr * wd, 1.0 / bc2
         h[6], h[7], h[8] = self.max_grad_norm or 0.0, grad_scale, 1.0 if self.reference_formula else 0.0
         return h
@@ -117,7 +121,7 @@ class FlatParamEngine:
             from ..ops import runtime as rt
             h = self._fill_hyper(wd, grad_scale)
             hyper = self.hyper if wd == self.weight_decay else self._hyper_nd
-            hyper.copy_(h, non_blocking=False)
+            hyper.copy_(h, non_blocking=True)
             rt.check(rt.lib().inv_adamw(p.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(),
                                         p16.data_ptr() if self.dtype == torch.bfloat16 else 0, n, hyper.data_ptr(), gnorm_sq.data_ptr(), 1,
                                         rt.stream_ptr()), "inv_adamw")
