@@ -25,7 +25,7 @@ int make_tmap_tokens_bf16(CUtensorMap* out, const void* ptr, int cols, int S, in
 constexpr int FB_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 softmax
 
 struct FlashBwdParams {
-  const float* lse;    // [B, H, S]
+  const float* lse;    // [B, H, S], log2 domain: log2(sum exp(scores))
   const float* delta;  // [B, H, S]  rowsum(dO * O)
   float* dq_acc;       // [B*S, H*D] fp32, zero on entry
   __nv_bfloat16* dk;   // token-major, ld_dk
@@ -87,7 +87,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int G = p.H / p.Hkv;
   const int k0 = j * 128;
   const int nqb = (p.S + 127) / 128;
-  const int i0 = p.causal ? j : 0;
+  const int i0 = (p.causal & 1) ? j : 0;
   const int nq_it = nqb - i0;
   const int n_it = G * nq_it;
 
@@ -211,7 +211,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const int key = k0 + r;
     const uint32_t t_lane = tmem_base + (uint32_t(q * 32) << 16);
     const float c = p.scale * 1.4426950408889634f;
-    const float LOG2E = 1.4426950408889634f;
+    const bool vec_ok = (p.S & 3) == 0;  // rows of lse / delta start 16-byte aligned
     uint8_t* pt_row = sPt + hf * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
     uint8_t* dst_row = sdSt + hf * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
     bool ok = true;
@@ -222,7 +222,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       tc_fence_after();
       const float* lse_row = p.lse + ((size_t)b * p.H + h) * p.S;
       const float* dl_row = p.delta + ((size_t)b * p.H + h) * p.S;
-      const bool need_mask = (p.causal && q0 < k0 + 127) || (q0 + 128 > p.S) || (k0 + 128 > p.S);
+      const bool need_mask = ((p.causal & 1) && q0 < k0 + 127) || (q0 + 128 > p.S) || (k0 + 128 > p.S);
 #pragma unroll 1
       for (int cc = 0; cc < 2; ++cc) {
         const int col0 = hf * 64 + cc * 32;
@@ -231,16 +231,34 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tmem_ld_32x32(t_lane + DPT_COL + col0, dp_r);
         tmem_ld_wait();
         float pv[32], ds[32];
+        if (!need_mask && vec_ok) {
+          // interior block: no predicates, statistics fetched as 16-byte broadcast loads
+          const float4* l4 = reinterpret_cast<const float4*>(lse_row + q0 + col0);
+          const float4* d4 = reinterpret_cast<const float4*>(dl_row + q0 + col0);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int qi = q0 + col0 + i;
-          const int qc = min(qi, p.S - 1);
-          const float lse = __ldg(lse_row + qc);
-          const float dl = __ldg(dl_row + qc);
-          float e = exp2f(__uint_as_float(s_r[i]) * c - lse * LOG2E);
-          if (need_mask && ((p.causal && key > qi) || qi >= p.S || key >= p.S)) e = 0.f;
-          pv[i] = e;
-          ds[i] = e * (__uint_as_float(dp_r[i]) - dl);
+          for (int i4 = 0; i4 < 8; ++i4) {
+            const float4 l = __ldg(l4 + i4), dl = __ldg(d4 + i4);
+            const float ls[4] = {l.x, l.y, l.z, l.w}, dls[4] = {dl.x, dl.y, dl.z, dl.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int i = i4 * 4 + k;
+              const float e = exp2f(__uint_as_float(s_r[i]) * c - ls[k]);
+              pv[i] = e;
+              ds[i] = e * (__uint_as_float(dp_r[i]) - dls[k]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int qi = q0 + col0 + i;
+            const int qc = min(qi, p.S - 1);
+            const float lse = __ldg(lse_row + qc);
+            const float dl = __ldg(dl_row + qc);
+            float e = exp2f(__uint_as_float(s_r[i]) * c - lse);
+            if (((p.causal & 1) && key > qi) || qi >= p.S || key >= p.S) e = 0.f;
+            pv[i] = e;
+            ds[i] = e * (__uint_as_float(dp_r[i]) - dl);
+          }
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -272,7 +290,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         uint32_t rr[32];
         tmem_ld_32x32(t_lane + DQ_COL + col0, rr);
         tmem_ld_wait();
-        if (qrow < p.S) {
+        if (qrow < p.S && !(p.causal & 2)) {
           float* dst = p.dq_acc + ((size_t)b * p.S + qrow) * ((size_t)p.H * D) + h * D + col0;
 #pragma unroll
           for (int g = 0; g < 8; ++g)

@@ -28,7 +28,7 @@ constexpr int FA_THREADS = 192;
 struct FlashFwdParams {
   __nv_bfloat16* out;
   int ld_o;
-  float* lse;  // [B, H, S]
+  float* lse;  // [B, H, S], log2 of the softmax denominator (scores scaled by scale*log2 e)
   int B, S, H, Hkv;
   float scale;
   int causal;
@@ -206,12 +206,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tmem_ld_32x32(t_lane + cc * 32, rr);
         tmem_ld_wait();
         float pv[32];
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = exp2f(__uint_as_float(rr[i]) * c - mc);
-          if (need_mask && (k0 + cc * 32 + i > kmax)) e = 0.f;
-          pv[i] = e;
-          rs += e;
+          for (int i = 0; i < 32; ++i) {
+            float e = exp2f(__uint_as_float(rr[i]) * c - mc);
+            if (k0 + cc * 32 + i > kmax) e = 0.f;
+            pv[i] = e;
+            rs += e;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            pv[i] = exp2f(__uint_as_float(rr[i]) * c - mc);
+            rs += pv[i];
+          }
         }
         uint8_t* dst = p_row + (cc >> 1) * 16384;
 #pragma unroll
@@ -257,7 +265,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         o.w = pack_bf16x2(o_acc[g * 8 + 6] * inv_l, o_acc[g * 8 + 7] * inv_l);
         *reinterpret_cast<uint4*>(dst + g * 8) = o;
       }
-      if (p.lse) p.lse[((size_t)b * p.H + h) * p.S + row] = m * p.scale + __logf(l);
+      if (p.lse) p.lse[((size_t)b * p.H + h) * p.S + row] = m * c + log2f(l);  // log2 domain, consumed by the backward
     }
   }
 

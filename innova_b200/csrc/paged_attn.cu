@@ -1,0 +1,301 @@
+// Paged KV cache on the device: append (with OIL4 quantisation) and single-query decode attention.
+//
+// Replaces the reference's PagedAttention::forward (src/inference_opt.cpp:60-112: block-table walk
+// with online softmax per query row), the OIL4 KV cache (src/kv_cache_oil4.cpp:207-362) and the
+// int8 block KV quantiser (src/kv_cache.cpp:15-44). The reference fits a 16-entry Lloyd codebook per
+// block on the CPU at append time; here every block of 32 values stores an fp16 abs-max scale and
+// 4-bit indices into one fixed 16-level Gaussian codebook, which a GPU can produce at append time
+// without iterations and read back with a 16-entry register LUT.
+//
+// Pools (page = 16 tokens): KV_OIL4: idx [pages, Hkv, 16, D/2] bytes, scale [pages, Hkv, 16, D/32] fp16.
+//                           KV_BF16: data [pages, Hkv, 16, D] bf16 (scale pool unused).
+// page_table [B, max_pages] int32 maps a sequence's logical page to a pool page.
+#include "sm100_common.cuh"
+#include "inv_api.h"
+
+#include <cuda_fp16.h>
+
+namespace inv {
+
+constexpr int PAGE = 16;
+__constant__ float c_kv_levels[16] = {-1.0f, -0.755096f, -0.588527f, -0.455957f, -0.341269f, -0.239458f, -0.146295f, -0.046361f,
+                                      0.046361f, 0.146295f, 0.239458f, 0.341269f, 0.455957f, 0.588527f, 0.755096f, 1.0f};
+
+__device__ __forceinline__ int nearest_level16(float x) {
+  int lo = 0;
+#pragma unroll
+  for (int step = 8; step > 0; step >>= 1)
+    if (c_kv_levels[lo + step] <= x) lo += step;
+  if (lo < 15 && (c_kv_levels[lo + 1] - x) < (x - c_kv_levels[lo])) ++lo;
+  return lo;
+}
+
+// One warp per (token, kv head, k-or-v): lane handles D/32 consecutive... each lane owns the elements
+// e = lane + 32*j (one per 32-block j), so a block's abs-max is a warp reduction and nibble pairs are
+// formed with a shuffle.
+template <bool OIL4>
+__global__ void __launch_bounds__(256) kv_append_kernel(const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new, int ld_k,
+                                                        int ld_v, const int* __restrict__ page_table, int max_pages,
+                                                        const int* __restrict__ start_pos, int B, int S_new, int Hkv, int D,
+                                                        uint8_t* __restrict__ k_pool, uint8_t* __restrict__ v_pool, __half* __restrict__ k_scale,
+                                                        __half* __restrict__ v_scale) {
+  const int lane = threadIdx.x & 31;
+  const long warp_id = blockIdx.x * (long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long total = (long)B * S_new * Hkv * 2;
+  if (warp_id >= total) return;
+  const int which = (int)(warp_id & 1);
+  long r = warp_id >> 1;
+  const int hk = (int)(r % Hkv);
+  r /= Hkv;
+  const int s = (int)(r % S_new);
+  const int b = (int)(r / S_new);
+  const int pos = start_pos[b] + s;
+  const int page = page_table[(long)b * max_pages + pos / PAGE];
+  const int slot = pos % PAGE;
+  const __nv_bfloat16* src = (which ? v_new : k_new) + ((long)b * S_new + s) * (which ? ld_v : ld_k) + hk * D;
+  uint8_t* pool = which ? v_pool : k_pool;
+  const long row = ((long)page * Hkv + hk) * PAGE + slot;
+  if (!OIL4) {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(pool) + row * D;
+    for (int e = lane; e < D; e += 32) dst[e] = src[e];
+    return;
+  }
+  __half* sc = (which ? v_scale : k_scale) + row * (D / 32);
+  uint8_t* dst = pool + row * (D / 2);
+  for (int j = 0; j < D / 32; ++j) {
+    const float w = __bfloat162float(src[j * 32 + lane]);
+    float amax = fabsf(w);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = amax < 1e-10f ? 1.f : amax;
+    const int code = nearest_level16(w / scale);
+    const int hi = __shfl_down_sync(0xffffffffu, code, 1);
+    if ((lane & 1) == 0) dst[j * 16 + (lane >> 1)] = (uint8_t)(code | (hi << 4));
+    if (lane == 0) sc[j] = __float2half_rn(scale);
+  }
+}
+
+// Decode attention: one query token per sequence. grid = (splits, Hkv, B), 128 threads.
+// Writes partial (m, l, o[G][D]) per (b, hk, split) to scratch; attn_combine_kernel finishes.
+template <bool OIL4, int D>
+__global__ void __launch_bounds__(128) paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int ld_q, const int* __restrict__ page_table,
+                                                           int max_pages, const int* __restrict__ seq_lens, int H, int Hkv,
+                                                           const uint8_t* __restrict__ k_pool, const uint8_t* __restrict__ v_pool,
+                                                           const __half* __restrict__ k_scale, const __half* __restrict__ v_scale, float scale,
+                                                           float* __restrict__ part, int splits) {
+  constexpr int MAXG = 8;
+  constexpr int EPL = D / 32;  // output elements per lane
+  constexpr int HALF = D / 2;  // elements per lane in the QK phase (two lanes per token)
+  __shared__ float sq[MAXG][D];
+  __shared__ float sm_m[4][MAXG], sm_l[4][MAXG];
+  __shared__ float sm_o[4][MAXG][D];
+  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int G = H / Hkv;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int len = seq_lens[b];
+  const int npages = (len + PAGE - 1) / PAGE;
+  const int per = (npages + splits - 1) / splits;
+  const int p0 = split * per, p1 = min(npages, p0 + per);
+  const float c = scale * 1.4426950408889634f;
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+    const int g = i / D, e = i % D;
+    sq[g][e] = __bfloat162float(q[(long)b * ld_q + (hk * G + g) * D + e]) * c;
+  }
+  __syncthreads();
+  float m[MAXG], l[MAXG], o[MAXG][EPL];
+#pragma unroll
+  for (int g = 0; g < MAXG; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) o[g][e] = 0.f;
+  }
+  const int t = lane & 15, hf = lane >> 4;
+  for (int pg = p0 + warp; pg < p1; pg += 4) {
+    const int page = page_table[(long)b * max_pages + pg];
+    const long row0 = ((long)page * Hkv + hk) * PAGE;
+    // ---- scores: lane = (token t, half hf) ----
+    float kf[HALF];
+    if (OIL4) {
+      const uint8_t* kp = k_pool + (row0 + t) * (D / 2) + hf * (HALF / 2);
+      const __half* ks = k_scale + (row0 + t) * (D / 32) + hf * (HALF / 32);
+#pragma unroll
+      for (int j = 0; j < HALF / 32; ++j) {
+        const float s = __half2float(ks[j]);
+        const uint4 raw = *reinterpret_cast<const uint4*>(kp + j * 16);
+        const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+#pragma unroll
+          for (int n = 0; n < 8; ++n) kf[j * 32 + w * 8 + n] = c_kv_levels[(wds[w] >> (4 * n)) & 15] * s;
+      }
+    } else {
+      const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(k_pool) + (row0 + t) * D + hf * HALF;
+#pragma unroll
+      for (int j = 0; j < HALF / 8; ++j) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(kp + j * 8);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+          const float2 f = __bfloat1622float2(h2[n]);
+          kf[j * 8 + 2 * n] = f.x;
+          kf[j * 8 + 2 * n + 1] = f.y;
+        }
+      }
+    }
+    const bool valid = pg * PAGE + t < len;
+    float pr[MAXG], alpha[MAXG];
+#pragma unroll
+    for (int g = 0; g < MAXG; ++g) {
+      if (g < G) {
+        float s = 0.f;
+        const float* qg = &sq[g][hf * HALF];
+#pragma unroll
+        for (int e = 0; e < HALF; ++e) s += kf[e] * qg[e];
+        s += __shfl_xor_sync(0xffffffffu, s, 16);
+        s = valid ? s : -INFINITY;
+        float mx = s;
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+        const float m_new = fmaxf(m[g], mx);
+        alpha[g] = m[g] == -INFINITY ? 0.f : exp2f(m[g] - m_new);
+        pr[g] = (s == -INFINITY) ? 0.f : exp2f(s - m_new);
+        float ps = pr[g];
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
+        l[g] = l[g] * alpha[g] + ps;
+        m[g] = m_new;
+      }
+    }
+    // ---- values: lane owns output elements [lane*EPL, lane*EPL+EPL) ----
+#pragma unroll
+    for (int g = 0; g < MAXG; ++g)
+      if (g < G)
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) o[g][e] *= alpha[g];
+    const int ntok = min(PAGE, len - pg * PAGE);
+    for (int tt = 0; tt < ntok; ++tt) {
+      float vf[EPL];
+      if (OIL4) {
+        const uint8_t* vp = v_pool + (row0 + tt) * (D / 2) + (lane * EPL) / 2;
+        const float s = __half2float(v_scale[(row0 + tt) * (D / 32) + (lane * EPL) / 32]);
+        uint32_t bits = EPL == 4 ? *reinterpret_cast<const uint16_t*>(vp) : *vp;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) vf[e] = c_kv_levels[(bits >> (4 * e)) & 15] * s;
+      } else {
+        const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(v_pool) + (row0 + tt) * D + lane * EPL;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) vf[e] = __bfloat162float(vp[e]);
+      }
+#pragma unroll
+      for (int g = 0; g < MAXG; ++g)
+        if (g < G) {
+          const float pt = __shfl_sync(0xffffffffu, pr[g], tt);
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) o[g][e] += pt * vf[e];
+        }
+    }
+  }
+  // ---- fold the 4 warps ----
+  for (int g = 0; g < G; ++g) {
+    if (lane == 0) {
+      sm_m[warp][g] = m[g];
+      sm_l[warp][g] = l[g];
+    }
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) sm_o[warp][g][lane * EPL + e] = o[g][e];
+  }
+  __syncthreads();
+  float* out = part + (((long)b * Hkv + hk) * splits + split) * (long)G * (D + 2);
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+    const int g = i / D, e = i % D;
+    float mm = -INFINITY;
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_m[w][g]);
+    float acc = 0.f, ll = 0.f;
+    for (int w = 0; w < 4; ++w) {
+      const float f = sm_m[w][g] == -INFINITY ? 0.f : exp2f(sm_m[w][g] - mm);
+      acc += sm_o[w][g][e] * f;
+      ll += sm_l[w][g] * f;
+    }
+    out[g * (D + 2) + 2 + e] = acc;
+    if (e == 0) {
+      out[g * (D + 2)] = mm;
+      out[g * (D + 2) + 1] = ll;
+    }
+  }
+}
+
+// out[b, h*D + e] = sum_s o_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m)
+__global__ void attn_combine_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int ld_o, int B, int H, int Hkv, int D,
+                                    int splits) {
+  const int G = H / Hkv;
+  const long total = (long)B * H * D;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int e = (int)(i % D);
+    const int h = (int)((i / D) % H);
+    const int b = (int)(i / ((long)D * H));
+    const int hk = h / G, g = h % G;
+    const float* base = part + (((long)b * Hkv + hk) * splits) * (long)G * (D + 2) + g * (D + 2);
+    float mm = -INFINITY;
+    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, base[(long)s * G * (D + 2)]);
+    float acc = 0.f, ll = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float* ps = base + (long)s * G * (D + 2);
+      const float f = ps[0] == -INFINITY ? 0.f : exp2f(ps[0] - mm);
+      acc += ps[2 + e] * f;
+      ll += ps[1] * f;
+    }
+    out[(long)b * ld_o + h * D + e] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+  }
+}
+
+}  // namespace inv
+
+using namespace inv;
+
+extern "C" int inv_kv_append(const void* k_new, const void* v_new, int ld_k, int ld_v, const int* page_table, int max_pages, const int* start_pos,
+                             int B, int S_new, int Hkv, int D, void* k_pool, void* v_pool, void* k_scale, void* v_scale, int oil4,
+                             void* stream) {
+  if (D % 32 || B <= 0 || S_new <= 0) return B <= 0 || S_new <= 0 ? 0 : -ERR_BAD_ARG;
+  const long warps = (long)B * S_new * Hkv * 2;
+  const int grid = (int)((warps + 7) / 8);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (oil4)
+    kv_append_kernel<true><<<grid, 256, 0, st>>>((const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, ld_k, ld_v, page_table, max_pages,
+                                                 start_pos, B, S_new, Hkv, D, (uint8_t*)k_pool, (uint8_t*)v_pool, (__half*)k_scale,
+                                                 (__half*)v_scale);
+  else
+    kv_append_kernel<false><<<grid, 256, 0, st>>>((const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, ld_k, ld_v, page_table, max_pages,
+                                                  start_pos, B, S_new, Hkv, D, (uint8_t*)k_pool, (uint8_t*)v_pool, (__half*)k_scale,
+                                                  (__half*)v_scale);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+// Scratch floats needed by inv_paged_decode.
+extern "C" long inv_paged_decode_scratch_floats(int B, int H, int D, int splits) { return (long)B * H * splits * (D + 2); }
+
+extern "C" int inv_paged_decode(const void* q, int ld_q, const int* page_table, int max_pages, const int* seq_lens, int B, int H, int Hkv, int D,
+                                const void* k_pool, const void* v_pool, const void* k_scale, const void* v_scale, int oil4, float scale,
+                                void* out, int ld_o, float* scratch, int splits, void* stream) {
+  if ((D != 64 && D != 128) || H % Hkv || H / Hkv > 8 || splits < 1) return -ERR_BAD_ARG;
+  if (B <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid(splits, Hkv, B);
+#define INV_PD(O, DD)                                                                                                                      \
+  paged_decode_kernel<O, DD><<<grid, 128, 0, st>>>((const __nv_bfloat16*)q, ld_q, page_table, max_pages, seq_lens, H, Hkv,                 \
+                                                   (const uint8_t*)k_pool, (const uint8_t*)v_pool, (const __half*)k_scale,                 \
+                                                   (const __half*)v_scale, scale, scratch, splits)
+  if (oil4) {
+    if (D == 64) INV_PD(true, 64); else INV_PD(true, 128);
+  } else {
+    if (D == 64) INV_PD(false, 64); else INV_PD(false, 128);
+  }
+#undef INV_PD
+  const long n = (long)B * H * D;
+  long g = (n + 255) / 256;
+  if (g > 148 * 8) g = 148 * 8;
+  attn_combine_kernel<<<(int)g, 256, 0, st>>>(scratch, (__nv_bfloat16*)out, ld_o, B, H, Hkv, D, splits);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}

@@ -22,6 +22,10 @@ _native.register_cuda_sigs({
 })
 
 
+import os
+_BWD_DEBUG = int(os.environ.get('INV_ATTN_DEBUG', '0'))
+
+
 def _scratch_bytes(B, S, H, D):
     delta = (B * H * S * 4 + 255) & ~255
     return delta + B * S * H * D * 4
@@ -54,7 +58,7 @@ class _FlashAttnFn(torch.autograd.Function):
         base, dbase = qkv.data_ptr(), dqkv.data_ptr()
         rc = rt.lib().inv_flash_attn_bwd(base, base + H * D * 2, base + (H + Hkv) * D * 2, out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
                                          dbase, dbase + H * D * 2, dbase + (H + Hkv) * D * 2, scr.data_ptr(), B, S, H, Hkv, D, ld, ld, ld,
-                                         H * D, H * D, ld, ld, ld, float(scale), int(causal), rt.status_tensor(qkv.device).data_ptr(),
+                                         H * D, H * D, ld, ld, ld, float(scale), int(causal) | _BWD_DEBUG, rt.status_tensor(qkv.device).data_ptr(),
                                          rt.stream_ptr())
         rt.check(rc, "inv_flash_attn_bwd")
         return dqkv, None, None, None, None, None

@@ -225,8 +225,12 @@ def rope_qk(qkv, cos, sin, n_q_heads, n_kv_heads, head_dim, positions=None):
             c, s = cos[:S], sin[:S]
         else:
             c, s = cos[positions.long()], sin[positions.long()]
-        c = c.view(*([1] * (x.dim() - 3)), -1, 1, half).to(x.dtype)
-        s = s.view(*([1] * (x.dim() - 3)), -1, 1, half).to(x.dtype)
+        if positions is None:
+            c = c.view(*([1] * (x.dim() - 3)), -1, 1, half).to(x.dtype)
+            s = s.view(*([1] * (x.dim() - 3)), -1, 1, half).to(x.dtype)
+        else:  # one position per token, in the order of the leading dims
+            c = c.reshape(*lead, 1, half).to(x.dtype)
+            s = s.reshape(*lead, 1, half).to(x.dtype)
         x1, x2 = x[..., :half], x[..., half:]
         rot = torch.cat([x1 * c - x2 * s, x1 * s + x2 * c], dim=-1).reshape(*lead, n_rot * head_dim)
         return torch.cat([rot, qkv[..., n_rot * head_dim:]], dim=-1)

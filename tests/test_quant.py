@@ -1,0 +1,64 @@
+"""Block-32 codebook compute formats and the STE op (CPU arithmetic; the GPU kernel is checked against it)."""
+import pytest
+import torch
+
+from innova_b200.ops import quant
+
+
+def test_oil8_beats_oil4_beats_spark_and_codebook_training_helps():
+    torch.manual_seed(0)
+    w = torch.randn(64, 128) * 0.05
+    snr = {}
+    for fmt in ("oil8", "oil4", "spark", "oil1"):
+        idx, sc, q = quant.quantize_blockwise(w, fmt, want_dequant=True)
+        assert idx.numel() == w.numel() and sc.numel() == w.numel() // 32
+        snr[fmt] = quant.snr_db(w, q)
+        back = quant.dequantize_blockwise(idx, sc, fmt).view_as(w)
+        assert torch.allclose(back, q, atol=1e-6)
+    assert snr["oil8"] > snr["oil4"] > snr["spark"] > 0
+    cb = quant.train_codebook(w, "oil4")
+    assert cb.numel() == 16 and bool((cb[1:] >= cb[:-1]).all())
+    _, _, q2 = quant.quantize_blockwise(w, "oil4", codebook=cb, want_dequant=True)
+    assert quant.snr_db(w, q2) >= snr["oil4"] - 0.5
+    cb2 = quant.ema_update_codebook(cb, w, decay=0.9)
+    assert cb2.shape == cb.shape
+
+
+def test_ste_gradient_is_identity_and_values_are_on_the_grid():
+    torch.manual_seed(1)
+    w = (torch.randn(8, 64) * 0.1).requires_grad_(True)
+    q = quant.ste_fake_quant(w, "oil8")
+    assert not torch.equal(q, w) and (q - w).abs().max() < 0.01
+    g = torch.randn_like(q)
+    q.backward(g)
+    assert torch.equal(w.grad, g)
+    # every block holds its abs-max exactly (codebook ends are -1 and +1)
+    blk = w.detach().view(-1, 32)
+    qb = q.detach().view(-1, 32)
+    assert torch.allclose(qb.abs().amax(1), blk.abs().amax(1), atol=1e-7)
+
+
+def test_nibble_packing():
+    idx = torch.arange(32, dtype=torch.uint8) % 16
+    p = quant.pack_nibbles(idx)
+    assert p.numel() == 16 and int(p[0]) == (0 | (1 << 4)) and int(p[7]) == (14 | (15 << 4))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["oil8", "oil4", "spark", "oil1"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gpu_kernel_matches_cpu_arithmetic(fmt, dtype):
+    torch.manual_seed(2)
+    w = (torch.randn(37, 100) * 0.07).to(dtype)
+    idx_c, sc_c, q_c = quant.quantize_blockwise(w.float(), fmt, want_dequant=True)
+    idx_g, sc_g, q_g = quant.quantize_blockwise(w.cuda(), fmt, want_dequant=True)
+    assert torch.allclose(sc_g.cpu(), sc_c, rtol=1e-5, atol=1e-8)
+    assert (idx_g.cpu() != idx_c).float().mean() < 0.01  # ties may flip
+    assert torch.allclose(q_g.float().cpu(), q_c.view_as(w), atol=2e-3 if dtype == torch.bfloat16 else 1e-4)
+    if fmt in ("oil8", "oil4"):
+        back = quant.dequantize_blockwise(idx_g, sc_g, fmt)
+        assert torch.allclose(back.float().cpu().view_as(w), q_c.view_as(w), atol=2e-3)
+    wg = w.cuda().requires_grad_(True)
+    out = quant.ste_fake_quant(wg, fmt)
+    out.sum().backward()
+    assert torch.equal(wg.grad, torch.ones_like(wg))
