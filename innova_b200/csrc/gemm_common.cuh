@@ -19,6 +19,19 @@ struct GemmParams {
   float alpha;
   int* status;
   int swap_lbo_sbo;  // debug aid for MN-major descriptors
+  // Grouped (mixture-of-experts) operation, single-CTA kernel only. Rows of A are grouped in
+  // segments that start on multiples of 128 rows (csrc/moe.cu).
+  //   1: C[rows of group e] = A[rows of group e] * B_e^T. tile_expert[m_tile] gives e (-1: unused tile);
+  //      B_e starts group_rows_b rows further into the stacked B per group; bias likewise (group_stride_bias).
+  //   2: C_e[M, N] += A[rows of e]^T-style reduction over the rows of group e only (expert weight
+  //      gradients): the k range of group e comes from group_offsets[e..e+1]; C_e = C + e * group_stride_c.
+  int group_mode;
+  int num_groups;
+  const int* tile_expert;
+  const int* group_offsets;
+  int group_rows_b;
+  int group_stride_bias;
+  long group_stride_c;
 };
 
 // 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows of `ld` elements; 128B swizzle.

@@ -32,17 +32,42 @@ constexpr int TMEM_COLS = 512;
 
 struct WorkUnit {
   int m0, n0, kb_begin, kb_end;
+  int b_row_off;   // extra row offset into the stacked B (grouped mode 1)
+  int bias_off;
+  long c_off;      // element offset of this unit's C (grouped mode 2)
+  bool skip;
 };
-__device__ __forceinline__ WorkUnit decode_work(int w, int m_tiles, int n_tiles, int kb_total, int kb_per_split) {
+__device__ __forceinline__ WorkUnit decode_work(int w, const GemmParams& p, int m_tiles, int n_tiles, int kb_total, int kb_per_split) {
   WorkUnit u;
-  int n_blk = w % n_tiles;
+  u.b_row_off = 0;
+  u.bias_off = 0;
+  u.c_off = 0;
+  u.skip = false;
+  const int n_blk = w % n_tiles;
   int rest = w / n_tiles;
-  int m_blk = rest % m_tiles;
-  int ks = rest / m_tiles;
+  const int m_blk = rest % m_tiles;
+  rest /= m_tiles;
   u.m0 = m_blk * BM;
   u.n0 = n_blk * BN;
+  if (p.group_mode == 2) {
+    const int ks = rest % p.split_k, e = rest / p.split_k;
+    const int off = p.group_offsets[e], len = p.group_offsets[e + 1] - off;
+    const int nkb = len / BK, per = (nkb + p.split_k - 1) / p.split_k;
+    u.kb_begin = off / BK + ks * per;
+    u.kb_end = min(off / BK + nkb, u.kb_begin + per);
+    u.c_off = (long)e * p.group_stride_c;
+    u.skip = u.kb_begin >= u.kb_end;
+    return u;
+  }
+  const int ks = rest;
   u.kb_begin = ks * kb_per_split;
   u.kb_end = min(kb_total, u.kb_begin + kb_per_split);
+  if (p.group_mode == 1) {
+    const int e = p.tile_expert[m_blk];
+    u.skip = e < 0;
+    u.b_row_off = e < 0 ? 0 : e * p.group_rows_b;
+    u.bias_off = e < 0 ? 0 : e * p.group_stride_bias;
+  }
   return u;
 }
 
@@ -67,7 +92,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int n_tiles = (p.N + BN - 1) / BN;
   const int kb_total = (p.K + BK - 1) / BK;
   const int kb_per_split = (kb_total + p.split_k - 1) / p.split_k;
-  const int total_work = m_tiles * n_tiles * p.split_k;
+  const int total_work = m_tiles * n_tiles * p.split_k * (p.group_mode == 2 ? p.num_groups : 1);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -97,7 +122,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (lane == 0) {
       int it = 0;
       for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
-        WorkUnit u = decode_work(w, m_tiles, n_tiles, kb_total, kb_per_split);
+        WorkUnit u = decode_work(w, p, m_tiles, n_tiles, kb_total, kb_per_split);
+        if (u.skip) continue;
         bool ok = true;
         for (int kb = u.kb_begin; kb < u.kb_end; ++kb, ++it) {
           const int s = it % STAGES;
@@ -115,9 +141,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmap_b, &full_bar[s], u.n0 + j * 64, k0);
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * 8192, &tmap_b, &full_bar[s], u.n0 + j * 64, k0 + u.b_row_off);
           } else {
-            tma_load_2d(b_dst, &tmap_b, &full_bar[s], k0, u.n0);
+            tma_load_2d(b_dst, &tmap_b, &full_bar[s], k0, u.n0 + u.b_row_off);
           }
         }
         if (!ok) break;
@@ -138,8 +164,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t a_kstep = A_MN ? 2048u : 32u;
       const uint32_t b_kstep = B_MN ? 2048u : 32u;
       int it = 0, tile_i = 0;
-      for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++tile_i) {
-        WorkUnit u = decode_work(w, m_tiles, n_tiles, kb_total, kb_per_split);
+      for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+        WorkUnit u = decode_work(w, p, m_tiles, n_tiles, kb_total, kb_per_split);
+        if (u.skip) continue;
         const int acc = tile_i & 1;
         const uint32_t acc_ph = (tile_i >> 1) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) break;
@@ -163,6 +190,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         if (!ok) break;
         umma_commit(&tmem_full[acc]);
+        ++tile_i;
       }
     }
   } else {
@@ -171,8 +199,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
     int tile_i = 0;
-    for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++tile_i) {
-      WorkUnit u = decode_work(w, m_tiles, n_tiles, kb_total, kb_per_split);
+    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+      WorkUnit u = decode_work(w, p, m_tiles, n_tiles, kb_total, kb_per_split);
+      if (u.skip) continue;
+      GemmParams pe = p;  // this unit's view of the outputs (grouped modes shift bias / C)
+      if (p.group_mode) {
+        if (pe.bias) pe.bias += u.bias_off;
+        pe.C = p.c_f32 ? (void*)(reinterpret_cast<float*>(p.C) + u.c_off) : (void*)(reinterpret_cast<__nv_bfloat16*>(p.C) + u.c_off);
+      }
       const int acc = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
       if (!mbar_wait_warp(&tmem_full[acc], acc_ph, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) break;
@@ -188,12 +222,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tmem_ld_32x32(t_row + c * 32, r0);
         tmem_ld_32x32(t_row + c * 32 + 32, r1);
         tmem_ld_wait();
-        gemm_epilogue_chunk(p, row, row_ok, col0, r0);
-        if (col0 + 32 < p.N) gemm_epilogue_chunk(p, row, row_ok, col0 + 32, r1);
+        gemm_epilogue_chunk(pe, row, row_ok, col0, r0);
+        if (col0 + 32 < p.N) gemm_epilogue_chunk(pe, row, row_ok, col0 + 32, r1);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      ++tile_i;
     }
   }
 
@@ -297,6 +332,8 @@ extern "C" int inv_gemm_bf16(const void* A, const void* B, void* C, int M, int N
     q.alpha = alpha;
     q.status = status;
     q.swap_lbo_sbo = debug_flags;
+    q.group_mode = 0; q.num_groups = 1; q.tile_expert = nullptr; q.group_offsets = nullptr; q.group_rows_b = 0;
+    q.group_stride_bias = 0; q.group_stride_c = 0;
     return gemm_2cta_dispatch(A, B, q, lda, ldb, a_mn, b_mn, g_num_sms, reinterpret_cast<cudaStream_t>(stream));
   }
   CUtensorMap ta, tb;
@@ -327,6 +364,8 @@ extern "C" int inv_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   p.alpha = alpha;
   p.status = status;
   p.swap_lbo_sbo = debug_flags & 1;
+  p.group_mode = 0; p.num_groups = 1; p.tile_expert = nullptr; p.group_offsets = nullptr; p.group_rows_b = 0;
+  p.group_stride_bias = 0; p.group_stride_c = 0;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
   const long total = (long)m_tiles * n_tiles * split_k;
   int grid = (int)(total < g_num_sms ? total : g_num_sms);
@@ -334,5 +373,58 @@ extern "C" int inv_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   if (a_mn && b_mn) return launch_gemm<true, true>(ta, tb, p, grid, st);
   if (a_mn && !b_mn) return launch_gemm<true, false>(ta, tb, p, grid, st);
   if (!a_mn && b_mn) return launch_gemm<false, true>(ta, tb, p, grid, st);
+  return launch_gemm<false, false>(ta, tb, p, grid, st);
+}
+
+
+// Grouped GEMM over expert segments (see GemmParams::group_mode), always on the single-CTA kernel.
+//   mode 1: C[R, N] = A[R, K] * B_e^T per 128-row tile, e = tile_expert[tile]; B stacked [E * rows_b, ...].
+//           M = R is the static row capacity of the permuted buffer.
+//   mode 2: C_e[M, N] += sum over the rows of group e (A: [R, M] a_mn, B: [R, N] b_mn), fp32 atomics.
+extern "C" int inv_gemm_grouped(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn,
+                                int epilogue, const void* bias, const void* aux_in, int ld_aux, void* aux_out, int c_f32, int split_k,
+                                int group_mode, int num_groups, const int* tile_expert, const int* group_offsets, int group_rows_b,
+                                int group_stride_bias, long group_stride_c, int* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (ldc % (c_f32 ? 4 : 8)) || (N % 8)) return -ERR_BAD_ARG;
+  if (group_mode == 2 && (!a_mn || !b_mn || !c_f32 || epilogue != EPI_ATOMIC)) return -ERR_BAD_ARG;
+  if (group_mode == 1 && a_mn) return -ERR_BAD_ARG;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  CUtensorMap ta, tb;
+  int rc;
+  // the stacked B is addressed through one map: its outer extent covers all groups
+  const uint64_t b_rows_total = (uint64_t)group_rows_b * (group_mode == 1 ? num_groups : 1);
+  if (a_mn) rc = make_tmap_2d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK);
+  else rc = make_tmap_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM);
+  if (rc) return rc;
+  if (b_mn) rc = make_tmap_2d_bf16(&tb, B, (uint64_t)N, group_mode == 1 ? b_rows_total : (uint64_t)K, (uint64_t)ldb, 64, BK);
+  else rc = make_tmap_2d_bf16(&tb, B, (uint64_t)K, group_mode == 1 ? b_rows_total : (uint64_t)N, (uint64_t)ldb, BK, BN);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.split_k = group_mode == 2 ? (split_k < 1 ? 1 : split_k) : 1;
+  p.C = C; p.ldc = ldc; p.c_f32 = c_f32;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.aux_in = reinterpret_cast<const __nv_bfloat16*>(aux_in);
+  p.ld_aux = ld_aux;
+  p.aux_out = reinterpret_cast<__nv_bfloat16*>(aux_out);
+  p.epilogue = epilogue;
+  p.alpha = 1.0f;
+  p.status = status;
+  p.swap_lbo_sbo = 0;
+  p.group_mode = group_mode; p.num_groups = num_groups; p.tile_expert = tile_expert; p.group_offsets = group_offsets;
+  p.group_rows_b = group_rows_b; p.group_stride_bias = group_stride_bias; p.group_stride_c = group_stride_c;
+  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+  const long total = (long)m_tiles * n_tiles * p.split_k * (group_mode == 2 ? num_groups : 1);
+  const int grid = (int)(total < g_num_sms ? total : g_num_sms);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (a_mn && b_mn) return launch_gemm<true, true>(ta, tb, p, grid, st);
+  if (!a_mn && b_mn) return launch_gemm<false, true>(ta, tb, p, grid, st);
+  if (a_mn && !b_mn) return launch_gemm<true, false>(ta, tb, p, grid, st);
   return launch_gemm<false, false>(ta, tb, p, grid, st);
 }

@@ -1,0 +1,105 @@
+"""Linear layers whose weights stay in OIL4 / OIL8 form and are expanded inside the GEMM kernel.
+
+``QuantWeight`` holds one [N, K] matrix in the block-32 compute format (indices packed two per byte
+for OIL4, bf16 scale per 32 weights, shared codebook). ``oil_linear`` computes ``x W^T (+ b) (+ res)``
+through ``csrc/oil_gemm.cu`` on CUDA and through dequantise + matmul on the CPU. Reference
+behaviour covered: OIL8Engine / OIL4Engine ``quant_gemm`` (src/oil_engines_core.cpp:51-160),
+``oil4_gemm`` / ``oil8_gemm`` (src/kernel_oil4.cpp:31-128, src/kernel_oil8.cpp:14-79) and the
+production GEMVs (src/kernel_production.cpp:95-166).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from .. import _native
+from . import quant
+from . import runtime as rt
+
+_native.register_cuda_sigs({
+    "inv_oil_gemm": [_native.vp, _native.i32, _native.vp, _native.vp, _native.vp, _native.i32, _native.vp, _native.i32, _native.i32, _native.i32,
+                     _native.i32, _native.i32, _native.vp, _native.vp],
+    "inv_oil_gemm_finish": [_native.vp, _native.vp, _native.vp, _native.vp, _native.i64, _native.i32, _native.i32, _native.i32, _native.i32,
+                            _native.i32, _native.vp],
+})
+
+
+@dataclass
+class QuantWeight:
+    fmt: str                 # "oil4" | "oil8"
+    idx: torch.Tensor        # uint8: [N, K/2] (oil4) or [N, K] (oil8)
+    scales: torch.Tensor     # bf16 [N, K/32]
+    codebook: torch.Tensor   # fp32 [16] or [256]
+    N: int
+    K: int
+    bias: Optional[torch.Tensor] = None
+
+    @property
+    def bits(self) -> int:
+        return 4 if self.fmt == "oil4" else 8
+
+    def nbytes(self) -> int:
+        return self.idx.numel() + self.scales.numel() * 2
+
+    def to(self, device):
+        return QuantWeight(self.fmt, self.idx.to(device), self.scales.to(device), self.codebook.to(device), self.N, self.K,
+                           None if self.bias is None else self.bias.to(device))
+
+    def dequantize(self) -> torch.Tensor:
+        """[N, K] in the scales' dtype."""
+        if self.fmt == "oil4":
+            codes = torch.stack([self.idx & 15, self.idx >> 4], dim=-1).reshape(self.N, self.K)
+        else:
+            codes = self.idx
+        vals = self.codebook.to(self.idx.device)[codes.long()].to(torch.bfloat16)
+        return (vals.view(self.N, self.K // 32, 32) * self.scales.view(self.N, -1, 1)).view(self.N, self.K)
+
+
+def quantize_weight(w: torch.Tensor, fmt: str = "oil4", codebook: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> QuantWeight:
+    """[N, K] float weights -> QuantWeight (K must be a multiple of 64)."""
+    assert fmt in ("oil4", "oil8") and w.dim() == 2 and w.shape[1] % 64 == 0
+    N, K = w.shape
+    cb = (codebook if codebook is not None else quant.default_codebook(fmt, w.device)).float().to(w.device)
+    idx, sc, _ = quant.quantize_blockwise(w.contiguous(), fmt, cb)
+    idx = idx.view(N, K)
+    if fmt == "oil4":
+        idx = quant.pack_nibbles(idx.reshape(-1)).view(N, K // 2)
+    return QuantWeight(fmt, idx.contiguous(), sc.view(N, K // 32).to(torch.bfloat16).contiguous(), cb.contiguous(), N, K,
+                       None if bias is None else bias.to(torch.bfloat16))
+
+
+_acc = {}
+
+
+def oil_linear(x: torch.Tensor, qw: QuantWeight, residual: Optional[torch.Tensor] = None, split_k: int = 0) -> torch.Tensor:
+    """x [..., K] bf16 -> [..., N] bf16."""
+    shp = x.shape
+    x2 = x.reshape(-1, qw.K)
+    if not x2.is_cuda:
+        y = F.linear(x2.float(), qw.dequantize().float(), None if qw.bias is None else qw.bias.float())
+        if residual is not None:
+            y = y + residual.reshape(-1, qw.N).float()
+        return y.to(x.dtype).view(*shp[:-1], qw.N)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    M = x2.shape[0]
+    out = torch.empty((M, qw.N), dtype=torch.bfloat16, device=x.device)
+    key = (x.device.index, qw.N)
+    acc = _acc.get(key)
+    if acc is None or acc.shape[0] < min(M, 256):
+        acc = torch.zeros((256, qw.N), dtype=torch.float32, device=x.device)  # kept zero between calls by the finish kernel
+        _acc[key] = acc
+    res2 = None if residual is None else residual.reshape(-1, qw.N)
+    status = rt.status_tensor(x.device).data_ptr()
+    for m0 in range(0, M, 256):
+        m1 = min(M, m0 + 256)
+        xs = x2[m0:m1]
+        rt.check(rt.lib().inv_oil_gemm(xs.data_ptr(), xs.stride(0), qw.idx.data_ptr(), qw.scales.data_ptr(), qw.codebook.data_ptr(), qw.bits,
+                                       acc.data_ptr(), acc.stride(0), m1 - m0, qw.N, qw.K, split_k, status, rt.stream_ptr()), "inv_oil_gemm")
+        rs = None if res2 is None else res2[m0:m1]
+        rt.check(rt.lib().inv_oil_gemm_finish(acc.data_ptr(), rt.ptr(qw.bias), rt.ptr(rs), out[m0:m1].data_ptr(), m1 - m0, qw.N, acc.stride(0),
+                                              out.stride(0), 0 if rs is None else rs.stride(0), 1, rt.stream_ptr()), "inv_oil_gemm_finish")
+    return out.view(*shp[:-1], qw.N)

@@ -62,3 +62,37 @@ def test_gpu_kernel_matches_cpu_arithmetic(fmt, dtype):
     out = quant.ste_fake_quant(wg, fmt)
     out.sum().backward()
     assert torch.equal(wg.grad, torch.ones_like(wg))
+
+
+def test_quant_weight_cpu_linear():
+    from innova_b200.ops.oil_linear import quantize_weight, oil_linear
+    torch.manual_seed(3)
+    w = torch.randn(48, 128) * 0.05
+    x = torch.randn(5, 128)
+    for fmt, tol in (("oil8", 0.02), ("oil4", 0.15)):
+        qw = quantize_weight(w, fmt)
+        assert qw.nbytes() < w.numel() * (0.6 if fmt == "oil4" else 1.1)
+        y = oil_linear(x, qw)
+        ref = x @ w.t()
+        assert float((y - ref).norm() / ref.norm()) < tol
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["oil4", "oil8"])
+@pytest.mark.parametrize("M,N,K", [(64, 768, 4096), (1, 256, 128), (200, 1000, 1344), (300, 128, 64)])
+def test_gpu_oil_gemm_matches_dequantised_matmul(fmt, M, N, K):
+    from innova_b200.ops import runtime as rt
+    from innova_b200.ops.oil_linear import quantize_weight, oil_linear
+    torch.manual_seed(4)
+    dev = torch.device("cuda", 0)
+    w = (torch.randn(N, K, device=dev) * 0.05)
+    x = torch.randn(M, K, device=dev).bfloat16()
+    bias = torch.randn(N, device=dev).bfloat16()
+    res = torch.randn(M, N, device=dev).bfloat16()
+    qw = quantize_weight(w, fmt, bias=bias)
+    y = oil_linear(x, qw, residual=res)
+    rt.check_status()
+    ref = x.float() @ qw.dequantize().float().t() + bias.float() + res.float()
+    assert float((y.float() - ref).norm() / ref.norm()) < 1e-2
+    y2 = oil_linear(x, qw, residual=res)  # the accumulator was left clean
+    assert torch.equal(y, y2) or float((y2.float() - ref).norm() / ref.norm()) < 1e-2
