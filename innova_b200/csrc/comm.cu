@@ -64,6 +64,19 @@ __global__ void signal_peers_kernel(PeerPtrs peer_flags, int W, int rank, uint32
 }
 __global__ void wait_flags_kernel(const uint32_t* flags, int W, uint32_t epoch, int* status) { wait_all_flags(flags, W, epoch, status); }
 
+// Barrier over peer memory whose epoch lives on the device, so that it can sit inside a captured CUDA
+// graph and advance on every replay: bump this rank's counter, publish it to every peer, wait until
+// every peer has published a value at least as large.
+__global__ void device_barrier_kernel(PeerPtrs peer_flags, uint32_t* local_flags, uint32_t* counter, int W, int rank, int* status) {
+  __shared__ uint32_t s_epoch;
+  if (threadIdx.x == 0) s_epoch = atomicAdd(counter, 1u) + 1u;
+  __threadfence_system();
+  __syncthreads();
+  const uint32_t e = s_epoch;
+  if (threadIdx.x < W) st_release_sys(reinterpret_cast<uint32_t*>(peer_flags.p[threadIdx.x]) + rank, e);
+  wait_all_flags(local_flags, W, e, status);
+}
+
 // ------------------------------------------------------------------------------------------------
 // Reduce-scatter. grads: peer pointers to the full fp32 gradient buffers. This rank owns [lo, lo+n).
 // ------------------------------------------------------------------------------------------------
@@ -268,5 +281,13 @@ extern "C" int inv_allreduce_f32(const uint64_t* peer_bufs, int W, int rank, lon
   PeerPtrs b;
   if (fill_ptrs(b, peer_bufs, W)) return -ERR_BAD_ARG;
   allreduce_twoshot_kernel<<<148 * 2, 256, 0, (cudaStream_t)stream>>>(b, W, rank, n / 4);
+  RET_LAUNCH();
+}
+
+// counter: one device word per flag set, starts at 0 on every rank.
+extern "C" int inv_device_barrier(const uint64_t* peer_flags, void* local_flags, void* counter, int W, int rank, int* status, void* stream) {
+  PeerPtrs pf;
+  if (fill_ptrs(pf, peer_flags, W)) return -ERR_BAD_ARG;
+  device_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(pf, (uint32_t*)local_flags, (uint32_t*)counter, W, rank, status);
   RET_LAUNCH();
 }

@@ -16,6 +16,9 @@
 //             looks the values up in a shared-memory table of bf16 pairs (OIL4: indexed by the byte,
 //             i.e. two weights per lookup), multiplies by the block scale with packed bf16 math and
 //             writes its 64 bytes into the swizzled A-operand tile. The same warps run the epilogue.
+// With `multimem` set the output pointer is an NVLS multicast address and the epilogue's reductions are
+// multimem.red: the switch adds each partial sum into every rank's copy of the buffer, which turns a
+// row-parallel (tensor-parallel) linear layer into GEMM + all-reduce in one kernel.
 // Small N leaves most SMs idle, so the reduction dimension is split across CTAs (split-K) and the
 // partial sums are added to an fp32 output with reductions. Every wait is bounded.
 #include "sm100_common.cuh"
@@ -46,6 +49,7 @@ struct OilGemmParams {
   int ldo;
   int split_k;
   int* status;
+  int multimem;  // out is an NVLS multicast address: every partial sum is added into all ranks' copies
 };
 
 typedef CUresult (*EncodeTiledFnO)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -262,7 +266,11 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const int m = c * 16 + i;
-            if (m < p.M) atomicAdd(p.out + (size_t)m * p.ldo + row, __uint_as_float(v[i]));
+            if (m < p.M) {
+              float* dst = p.out + (size_t)m * p.ldo + row;
+              if (p.multimem) asm volatile("multimem.red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(dst), "f"(__uint_as_float(v[i])) : "memory");
+              else atomicAdd(dst, __uint_as_float(v[i]));
+            }
           }
         }
       }
@@ -304,7 +312,7 @@ using namespace inv;
 
 // acc (fp32 [M, ldo]) must be zero on entry or hold a partial sum to add to. M <= 256, K % 64 == 0.
 extern "C" int inv_oil_gemm(const void* x, int ldx, const void* idx, const void* scales, const float* codebook, int bits, float* acc, int ldo,
-                            int M, int N, int K, int split_k, int* status, void* stream) {
+                            int M, int N, int K, int split_k, int* status, void* stream, int multimem) {
   using namespace og;
   if ((bits != 4 && bits != 8) || M < 1 || M > MAXM || (K % 64) || (ldx % 8) || N < 1) return -ERR_BAD_ARG;
   static int num_sms = 0;
@@ -319,7 +327,7 @@ extern "C" int inv_oil_gemm(const void* x, int ldx, const void* idx, const void*
   p.Mpad = (M + 15) / 16 * 16;
   p.scales = (const __nv_bfloat16*)scales;
   p.codebook = codebook;
-  p.out = acc; p.ldo = ldo; p.status = status;
+  p.out = acc; p.ldo = ldo; p.status = status; p.multimem = multimem;
   const int n_tiles = (N + BN - 1) / BN, kb_total = K / BK;
   if (split_k <= 0) split_k = (num_sms + n_tiles - 1) / n_tiles;  // about one work unit per SM
   if (split_k > kb_total) split_k = kb_total;

@@ -21,7 +21,7 @@ from . import runtime as rt
 
 _native.register_cuda_sigs({
     "inv_oil_gemm": [_native.vp, _native.i32, _native.vp, _native.vp, _native.vp, _native.i32, _native.vp, _native.i32, _native.i32, _native.i32,
-                     _native.i32, _native.i32, _native.vp, _native.vp],
+                     _native.i32, _native.i32, _native.vp, _native.vp, _native.i32],
     "inv_oil_gemm_finish": [_native.vp, _native.vp, _native.vp, _native.vp, _native.i64, _native.i32, _native.i32, _native.i32, _native.i32,
                             _native.i32, _native.vp],
 })
@@ -98,7 +98,7 @@ def oil_linear(x: torch.Tensor, qw: QuantWeight, residual: Optional[torch.Tensor
         m1 = min(M, m0 + 256)
         xs = x2[m0:m1]
         rt.check(rt.lib().inv_oil_gemm(xs.data_ptr(), xs.stride(0), qw.idx.data_ptr(), qw.scales.data_ptr(), qw.codebook.data_ptr(), qw.bits,
-                                       acc.data_ptr(), acc.stride(0), m1 - m0, qw.N, qw.K, split_k, status, rt.stream_ptr()), "inv_oil_gemm")
+                                       acc.data_ptr(), acc.stride(0), m1 - m0, qw.N, qw.K, split_k, status, rt.stream_ptr(), 0), "inv_oil_gemm")
         rs = None if res2 is None else res2[m0:m1]
         rt.check(rt.lib().inv_oil_gemm_finish(acc.data_ptr(), rt.ptr(qw.bias), rt.ptr(rs), out[m0:m1].data_ptr(), m1 - m0, qw.N, acc.stride(0),
                                               out.stride(0), 0 if rs is None else rs.stride(0), 1, rt.stream_ptr()), "inv_oil_gemm_finish")

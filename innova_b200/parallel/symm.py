@@ -23,6 +23,7 @@ _native.register_cuda_sigs({
                         _native.vp, _native.vp, C.c_uint32, _native.vp, _native.vp],
     "inv_fsdp_adamw_push": [_native.vp] * 5 + [_native.i32, _native.i32, _native.i64, _native.i64, _native.i64] + [_native.vp] * 4 +
                            [_native.i64, _native.vp, _native.vp, _native.vp, C.c_uint32, _native.vp, _native.vp],
+    "inv_device_barrier": [_native.vp, _native.vp, _native.vp, _native.i32, _native.i32, _native.vp, _native.vp],
     "inv_allgather_pull": [_native.vp, _native.i32, _native.i64, _native.vp, _native.vp],
     "inv_allreduce_f32": [_native.vp, _native.i32, _native.i32, _native.i64, _native.vp],
 })

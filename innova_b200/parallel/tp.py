@@ -1,0 +1,270 @@
+"""Tensor-parallel inference over NVLink: column / row parallel OIL linears with the all-reduce fused
+into the row-parallel GEMM, and the decode engine built on them.
+
+Sharding follows the reference's TensorParallelManager (src/tensor_parallelism.cpp:213-267,334-447):
+q/k/v and gate/up are split by output rows (column parallel, heads stay whole), o and down by input
+columns (row parallel), lm_head by vocabulary. Where the reference runs a GEMM and then an
+all_reduce over the whole activation (src/tensor_parallelism.cpp:100-142), the row-parallel layer here
+is ONE kernel: the OIL GEMM's epilogue adds its partial sums into every rank's copy of the output
+with ``multimem.red`` through the NVSwitch (``csrc/oil_gemm.cu``), followed by a device-side barrier and
+a small finish kernel (bias, residual, bf16). The vocabulary-parallel lm_head uses the same path to
+all-gather the logits (disjoint column ranges of a zeroed replicated buffer). Without NVLS the
+partial sums go to each peer with plain P2P atomics instead.
+
+``TPDecoder`` generates with a paged OIL4 KV cache; the whole decode step (all layers, attention,
+sampling input) is captured once in a CUDA graph and replayed, because at batch 64 a step is a few
+hundred short kernels and would otherwise be bound by launch latency.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..inference.kv_cache import PagedKVCache, PAGE
+from ..models.config import TransformerConfig
+from ..ops import runtime as rt
+from ..ops.oil_linear import QuantWeight, oil_linear, quantize_weight
+
+
+class TPContext:
+    """Replicated fp32 accumulators in symmetric memory (two, used alternately) and a device barrier."""
+
+    def __init__(self, group=None, max_tokens: int = 256, max_n: int = 32768, device=None):
+        from .symm import PeerFlags, SymmBuffer
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.max_tokens, self.max_n = max_tokens, max_n
+        self.bufs = [SymmBuffer(max_tokens * max_n, torch.float32, self.group, device) for _ in range(2)]
+        self.flags = PeerFlags(n_sets=2, group=self.group)
+        self.counter = torch.zeros(2, dtype=torch.int32, device=self.bufs[0].tensor.device)
+        self.turn = 0
+        self.multimem = all(b.multicast_ptr != 0 for b in self.bufs)
+
+    def barrier(self):
+        f = self.flags
+        rc = rt.lib().inv_device_barrier(f.set_ptrs(0), f.set_ptr_local(0), self.counter.data_ptr(), self.world, self.rank,
+                                         rt.status_tensor().data_ptr(), rt.stream_ptr())
+        rt.check(rc, "inv_device_barrier")
+
+    def next_buffer(self):
+        b = self.bufs[self.turn]
+        self.turn ^= 1
+        return b
+
+
+def tp_reduce_linear(x: torch.Tensor, qw: QuantWeight, ctx: Optional[TPContext], residual=None, n_total: Optional[int] = None,
+                     n_offset: int = 0, out_fp32: bool = False) -> torch.Tensor:
+    """y[M, n_total] = sum over ranks of x_local @ W_local^T, every rank receiving the full result.
+
+    Row-parallel layers pass n_offset = 0 and n_total = qw.N (true reduction); the vocabulary-parallel
+    head passes its column offset, so that the "reduction" is an all-gather into disjoint columns."""
+    if ctx is None or ctx.world == 1:
+        y = oil_linear(x, qw, residual)
+        return y.float() if out_fp32 else y
+    x2 = x.reshape(-1, qw.K)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    M = x2.shape[0]
+    n_total = n_total or qw.N
+    assert M <= ctx.max_tokens and n_total <= ctx.max_n
+    buf = ctx.next_buffer()
+    lib, st = rt.lib(), rt.stream_ptr()
+    status = rt.status_tensor(x.device).data_ptr()
+    if ctx.multimem:
+        rt.check(lib.inv_oil_gemm(x2.data_ptr(), x2.stride(0), qw.idx.data_ptr(), qw.scales.data_ptr(), qw.codebook.data_ptr(), qw.bits,
+                                  buf.multicast_ptr + n_offset * 4, n_total, M, qw.N, qw.K, 0, status, st, 1), "inv_oil_gemm")
+    else:
+        for k in range(ctx.world):
+            peer = buf.peer_ptrs[(ctx.rank + k) % ctx.world]
+            rt.check(lib.inv_oil_gemm(x2.data_ptr(), x2.stride(0), qw.idx.data_ptr(), qw.scales.data_ptr(), qw.codebook.data_ptr(), qw.bits,
+                                      peer + n_offset * 4, n_total, M, qw.N, qw.K, 0, status, st, 0), "inv_oil_gemm")
+    ctx.barrier()
+    acc = buf.tensor
+    if out_fp32:
+        y = acc[: M * n_total].view(M, n_total).clone()
+        acc[: M * n_total].zero_()
+        return y
+    out = torch.empty((M, n_total), dtype=torch.bfloat16, device=x.device)
+    res2 = None if residual is None else residual.reshape(M, n_total)
+    rt.check(lib.inv_oil_gemm_finish(acc.data_ptr(), rt.ptr(qw.bias), rt.ptr(res2), out.data_ptr(), M, n_total, n_total, n_total,
+                                     0 if res2 is None else res2.stride(0), 1, st), "inv_oil_gemm_finish")
+    return out
+
+
+class TPDecoder:
+    """Llama-style decoder, OIL4 (or OIL8) weights sharded over the ranks of ``group``, random-init from
+    ``seed`` (every rank draws the full matrix on its GPU, keeps its shard, quantises it, drops the rest)."""
+
+    def __init__(self, cfg: TransformerConfig, group=None, fmt: str = "oil4", max_batch: int = 64, max_seq: int = 1024, seed: int = 0,
+                 kv_format: str = "oil4", device=None):
+        self.cfg = cfg
+        self.dev = device or torch.device("cuda", torch.cuda.current_device())
+        self.world = dist.get_world_size(group) if (dist.is_initialized() and (group is not None or True)) else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        W, r = self.world, self.rank
+        assert cfg.num_heads % W == 0 and cfg.kv_heads % W == 0 and cfg.ffn_hidden_size % W == 0
+        self.H, self.Hkv, self.D = cfg.num_heads // W, cfg.kv_heads // W, cfg.head_dim
+        E, Fh, D = cfg.hidden_size, cfg.ffn_hidden_size // W, cfg.head_dim
+        self.ctx = TPContext(group, max_tokens=256, max_n=max(cfg.padded_vocab, E), device=self.dev) if W > 1 else None
+        g = torch.Generator(device=self.dev)
+
+        def full(shape, k):
+            g.manual_seed(seed * 100003 + k)
+            return torch.randn(shape, generator=g, device=self.dev, dtype=torch.float32).mul_(0.02)
+
+        self.emb = full((cfg.padded_vocab, E), 1).bfloat16()
+        self.layers = []
+        nq, nkv = cfg.num_heads * D, cfg.kv_heads * D
+        for li in range(cfg.num_layers):
+            k0 = 10 + li * 8
+            wq, wk, wv = full((nq, E), k0), full((nkv, E), k0 + 1), full((nkv, E), k0 + 2)
+            qkv = torch.cat([wq[r * self.H * D:(r + 1) * self.H * D], wk[r * self.Hkv * D:(r + 1) * self.Hkv * D],
+                             wv[r * self.Hkv * D:(r + 1) * self.Hkv * D]], dim=0)
+            del wq, wk, wv
+            wo = full((E, nq), k0 + 3)[:, r * self.H * D:(r + 1) * self.H * D].contiguous()
+            wg, wu = full((cfg.ffn_hidden_size, E), k0 + 4), full((cfg.ffn_hidden_size, E), k0 + 5)
+            # the local FFN width is padded with zero rows / columns to the GEMM's 64-wide k-block
+            Fp = (Fh + 63) // 64 * 64
+            zr = torch.zeros((Fp - Fh, E), device=self.dev)
+            gu = torch.cat([wg[r * Fh:(r + 1) * Fh], zr, wu[r * Fh:(r + 1) * Fh], zr], dim=0)
+            del wg, wu
+            wd = torch.cat([full((E, cfg.ffn_hidden_size), k0 + 6)[:, r * Fh:(r + 1) * Fh], torch.zeros((E, Fp - Fh), device=self.dev)], dim=1).contiguous()
+            self.layers.append({
+                "qkv": quantize_weight(qkv, fmt), "o": quantize_weight(wo, fmt), "gu": quantize_weight(gu, fmt), "down": quantize_weight(wd, fmt),
+                "n1": torch.ones(E, dtype=torch.bfloat16, device=self.dev), "n2": torch.ones(E, dtype=torch.bfloat16, device=self.dev)})
+            del qkv, wo, gu, wd
+        Vs = cfg.padded_vocab // W
+        self.head = quantize_weight(full((cfg.padded_vocab, E), 5)[r * Vs:(r + 1) * Vs].contiguous(), fmt)
+        self.norm_w = torch.ones(E, dtype=torch.bfloat16, device=self.dev)
+        self.rope = ops.rope_tables(max_seq, D, cfg.rope_theta, self.dev)
+        self.cache = PagedKVCache(cfg.num_layers, self.Hkv, D, max_batch, max_seq, self.dev, kv_format)
+        self.max_batch, self.max_seq = max_batch, max_seq
+        self._graph = None
+        torch.cuda.synchronize()
+
+    def weight_bytes(self) -> int:
+        n = self.head.nbytes()
+        for l in self.layers:
+            n += sum(l[k].nbytes() for k in ("qkv", "o", "gu", "down"))
+        return n
+
+    # ------------------------------------------------------------------ prefill (large M: dequantise once per layer)
+    @torch.no_grad()
+    def prefill(self, ids: torch.Tensor) -> torch.Tensor:
+        cfg, c = self.cfg, self.cache
+        B, S = ids.shape
+        H, Hkv, D = self.H, self.Hkv, self.D
+        for b in range(c.max_batch):
+            c.free(b)
+        for b in range(B):
+            c.reserve(b, self.max_seq)  # every page a sequence can need, so that the decode graph never allocates
+        x = self.emb[ids]
+        start = [0] * B
+        for li, l in enumerate(self.layers):
+            h = ops.rms_norm(x, l["n1"], cfg.norm_eps)
+            qkv = ops.linear(h, l["qkv"].dequantize())
+            qkv = ops.rope_qk(qkv, self.rope[0], self.rope[1], H, Hkv, D)
+            c.append(li, qkv[..., H * D:(H + Hkv) * D], qkv[..., (H + Hkv) * D:], list(range(B)), start)
+            a = ops.flash_attention(qkv, H, Hkv, D, causal=True)
+            o = ops.linear(a, l["o"].dequantize())
+            if self.world > 1:
+                dist.all_reduce(o)
+            x = x + o
+            h = ops.rms_norm(x, l["n2"], cfg.norm_eps)
+            act = ops.swiglu(ops.linear(h, l["gu"].dequantize()))
+            d = ops.linear(act, l["down"].dequantize())
+            if self.world > 1:
+                dist.all_reduce(d)
+            x = x + d
+        c.commit(list(range(B)), [S] * B)
+        return self._logits(x[:, -1].contiguous())
+
+    def _logits(self, last: torch.Tensor) -> torch.Tensor:
+        h = ops.rms_norm(last, self.norm_w, self.cfg.norm_eps)
+        Vs = self.cfg.padded_vocab // self.world
+        lg = tp_reduce_linear(h, self.head, self.ctx, n_total=self.cfg.padded_vocab, n_offset=self.rank * Vs, out_fp32=True)
+        if self.ctx is not None:
+            # a step uses the two accumulators an odd number of times, so the next step starts on the
+            # buffer this one just read: nobody may add into it before every rank has taken its logits
+            self.ctx.barrier()
+        return lg[:, : self.cfg.vocab_size]
+
+    # ------------------------------------------------------------------ one decode step (capturable)
+    @torch.no_grad()
+    def _decode_step(self, tokens: torch.Tensor) -> torch.Tensor:
+        """tokens [B] -> logits [B, vocab]. Uses and advances the device-side sequence lengths."""
+        cfg, c = self.cfg, self.cache
+        B = tokens.shape[0]
+        H, Hkv, D = self.H, self.Hkv, self.D
+        lens = c.seq_lens[:B]
+        pos = lens.clone()                      # position of the new token
+        lens.add_(1)
+        x = self.emb[tokens]
+        scale = D ** -0.5
+        lib, st = rt.lib(), rt.stream_ptr()
+        for li, l in enumerate(self.layers):
+            h = ops.rms_norm(x, l["n1"], cfg.norm_eps)
+            qkv = oil_linear(h, l["qkv"]).view(B, 1, -1)
+            qkv = ops.rope_qk(qkv, self.rope[0], self.rope[1], H, Hkv, D, pos)
+            k, v = qkv[..., H * D:(H + Hkv) * D], qkv[..., (H + Hkv) * D:]
+            rt.check(lib.inv_kv_append(k.data_ptr(), v.data_ptr(), k.stride(1), v.stride(1), c.page_table.data_ptr(), c.max_pages, pos.data_ptr(),
+                                       B, 1, Hkv, D, c.k_pool[li].data_ptr(), c.v_pool[li].data_ptr(), rt.ptr(c.k_scale[li]),
+                                       rt.ptr(c.v_scale[li]), int(c.fmt == "oil4"), st), "inv_kv_append")
+            a = torch.empty(B, H * D, dtype=torch.bfloat16, device=self.dev)
+            q2 = qkv.view(B, -1)
+            rt.check(lib.inv_paged_decode(q2.data_ptr(), q2.stride(0), c.page_table.data_ptr(), c.max_pages, c.seq_lens.data_ptr(), B, H, Hkv, D,
+                                          c.k_pool[li].data_ptr(), c.v_pool[li].data_ptr(), rt.ptr(c.k_scale[li]), rt.ptr(c.v_scale[li]),
+                                          int(c.fmt == "oil4"), float(scale), a.data_ptr(), a.stride(0), self._scratch.data_ptr(),
+                                          self._splits, st), "inv_paged_decode")
+            x = tp_reduce_linear(a, l["o"], self.ctx, residual=x)
+            h = ops.rms_norm(x, l["n2"], cfg.norm_eps)
+            act = ops.swiglu(oil_linear(h, l["gu"]))
+            x = tp_reduce_linear(act, l["down"], self.ctx, residual=x)
+        return self._logits(x)
+
+    @torch.no_grad()
+    def generate(self, ids: torch.Tensor, max_new_tokens: int, use_graph: bool = True):
+        """Greedy generation. Returns (tokens [B, max_new_tokens], prefill seconds, decode seconds), device-timed."""
+        B, S = ids.shape
+        self._splits = max(1, min(8, (148 * 2) // max(1, B * self.Hkv)))
+        self._scratch = torch.empty(B * self.H * self._splits * (self.D + 2), dtype=torch.float32, device=self.dev)
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        logits = self.prefill(ids)
+        tok = logits.argmax(-1)
+        e[1].record()
+        out = [tok]
+        static_tok = tok.clone()
+        if use_graph:
+            # warm up on a side stream (allocations, lazy kernel attributes), restore the state, then capture
+            saved = self.cache.seq_lens.clone()
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._decode_step(static_tok)
+            torch.cuda.current_stream().wait_stream(s)
+            self.cache.seq_lens.copy_(saved)
+            if self.ctx is not None:
+                self.ctx.turn = 0
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_logits = self._decode_step(static_tok)
+                static_next = static_logits.argmax(-1)
+            self.cache.seq_lens.copy_(saved)
+            e[1].record()
+            for _ in range(max_new_tokens - 1):
+                graph.replay()
+                static_tok.copy_(static_next)
+                out.append(static_next.clone())
+        else:
+            for _ in range(max_new_tokens - 1):
+                tok = self._decode_step(tok).argmax(-1)
+                out.append(tok)
+        e[2].record()
+        torch.cuda.synchronize()
+        rt.check_status()
+        return torch.stack(out, dim=1), e[0].elapsed_time(e[1]) / 1e3, e[1].elapsed_time(e[2]) / 1e3
