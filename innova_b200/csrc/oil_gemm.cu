@@ -92,8 +92,8 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
   uint8_t* sA = smem;                                  // AB_STAGES x 16 KB
   uint8_t* sX = sA + AB_STAGES * A_TILE;               // AB_STAGES x 32 KB (sized for MAXM)
   uint8_t* sIdx = sX + AB_STAGES * (MAXM * BK * 2);    // IDX_STAGES x IDX_TILE
-  uint32_t* lut = reinterpret_cast<uint32_t*>(sIdx + IDX_STAGES * IDX_TILE);  // 256 entries
-  uint64_t* bars = reinterpret_cast<uint64_t*>(lut + 256);
+  uint32_t* lut = reinterpret_cast<uint32_t*>(sIdx + IDX_STAGES * IDX_TILE);  // 256 entries x 32 bank copies
+  uint64_t* bars = reinterpret_cast<uint64_t*>(lut + 256 * 32);
   uint64_t* idx_full = bars;
   uint64_t* idx_empty = idx_full + IDX_STAGES;
   uint64_t* a_full = idx_empty + IDX_STAGES;
@@ -111,9 +111,11 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
   const int total_work = n_tiles * p.split_k;
 
   // lookup table: OIL4 -> bf16 pair (codebook[low nibble], codebook[high nibble]) per byte; OIL8 -> one bf16
-  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
-    if (BITS == 4) lut[i] = pack_bf16x2(p.codebook[i & 15], p.codebook[i >> 4]);
-    else lut[i] = pack_bf16x2(p.codebook[i], 0.f);
+  // entry e for lane l lives at lut[e * 32 + l]: every lane reads its own bank, whatever the indices are
+  for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
+    const int e = i >> 5;
+    if (BITS == 4) lut[i] = pack_bf16x2(p.codebook[e & 15], p.codebook[e >> 4]);
+    else lut[i] = pack_bf16x2(p.codebook[e], 0.f);
   }
   if (threadIdx.x == 0) {
     for (int s = 0; s < IDX_STAGES; ++s) {
@@ -209,11 +211,13 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
       const int kb0 = (w / n_tiles) * kb_per, kb1 = min(kb_total, kb0 + kb_per);
       const int row = n0 + r;
       const __nv_bfloat16* srow = p.scales + (size_t)min(row, p.N - 1) * nsb;
+      __nv_bfloat16 sc_next = srow[kb0 * 2 + half];  // the scale is fetched one k-block ahead of its use
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const __nv_bfloat16 sc = sc_next;
+        if (kb + 1 < kb1) sc_next = srow[(kb + 1) * 2 + half];
         const int si = it % IDX_STAGES, sa = it % AB_STAGES;
         if (!mbar_wait_warp(&idx_full[si], (it / IDX_STAGES) & 1, abort_flag, p.status, ERR_WAIT_FULL)) { ok = false; break; }
         if (!mbar_wait_warp(&a_empty[sa], ((it / AB_STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
-        const __nv_bfloat16 sc = srow[kb * 2 + half];
         const __nv_bfloat162 sc2 = __halves2bfloat162(sc, sc);
         const uint8_t* src = sIdx + si * IDX_TILE + r * ROW_BYTES + half * (ROW_BYTES / 2);
         uint8_t* dst = sA + sa * A_TILE + (r >> 3) * 1024 + (r & 7) * 128;
@@ -225,7 +229,7 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
             uint32_t o[4];
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-              const uint32_t pair = lut[(wds[g] >> (8 * b)) & 255];
+              const uint32_t pair = lut[(((wds[g] >> (8 * b)) & 255) << 5) + lane];
               const __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&pair), sc2);
               o[b] = *reinterpret_cast<const uint32_t*>(&v);
             }
@@ -240,7 +244,7 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
               const uint32_t two = wds[g * 2 + (b >> 1)] >> (16 * (b & 1));
-              const uint32_t lo = lut[two & 255] & 0xffffu, hi = lut[(two >> 8) & 255] << 16;
+              const uint32_t lo = lut[((two & 255) << 5) + lane] & 0xffffu, hi = lut[(((two >> 8) & 255) << 5) + lane] << 16;
               const uint32_t pair = lo | hi;
               const __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&pair), sc2);
               o[b] = *reinterpret_cast<const uint32_t*>(&v);
@@ -294,10 +298,8 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
 // out_bf16[m, n] = bf16(acc[m, n] + bias[n] (+ residual[m, n])); clears acc for the next use.
 __global__ void oil_gemm_finish_kernel(float* __restrict__ acc, const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ residual,
                                        __nv_bfloat16* __restrict__ out, long M, int N, int ld_acc, int ld_out, int ld_res, int clear) {
-  const long total = M * N;
-  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-    const long m = i / N;
-    const int n = (int)(i % N);
+  const long m = blockIdx.y;
+  for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < N; n += gridDim.x * blockDim.x) {
     float v = acc[m * ld_acc + n];
     if (clear) acc[m * ld_acc + n] = 0.f;
     if (bias) v += __bfloat162float(bias[n]);
@@ -329,7 +331,10 @@ extern "C" int inv_oil_gemm(const void* x, int ldx, const void* idx, const void*
   p.codebook = codebook;
   p.out = acc; p.ldo = ldo; p.status = status; p.multimem = multimem;
   const int n_tiles = (N + BN - 1) / BN, kb_total = K / BK;
-  if (split_k <= 0) split_k = (num_sms + n_tiles - 1) / n_tiles;  // about one work unit per SM
+  if (split_k <= 0) {  // several work units per SM (balance), each at least 4 k-blocks long
+    split_k = (4 * num_sms + n_tiles - 1) / n_tiles;
+    if (split_k > kb_total / 4) split_k = kb_total / 4 > 0 ? kb_total / 4 : 1;
+  }
   if (split_k > kb_total) split_k = kb_total;
   {
     const int per = (kb_total + split_k - 1) / split_k;
@@ -342,7 +347,7 @@ extern "C" int inv_oil_gemm(const void* x, int ldx, const void* idx, const void*
   if ((rc = make_tmap_bytes(&ti, idx, (uint64_t)row_bytes, (uint64_t)N, BK * bits / 8, BN))) return rc;
   if ((rc = make_tmap_2d_bf16(&tx, x, (uint64_t)K, (uint64_t)M, (uint64_t)ldx, BK, (uint32_t)p.Mpad))) return rc;
   const int idx_tile = BN * BK * bits / 8;
-  const int smem = AB_STAGES * (A_TILE + MAXM * BK * 2) + IDX_STAGES * idx_tile + 1024 + 256 * 4 + 512 + 1024;
+  const int smem = AB_STAGES * (A_TILE + MAXM * BK * 2) + IDX_STAGES * idx_tile + 1024 + 256 * 32 * 4 + 512 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(oil_gemm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -361,9 +366,10 @@ extern "C" int inv_oil_gemm(const void* x, int ldx, const void* idx, const void*
 extern "C" int inv_oil_gemm_finish(float* acc, const void* bias, const void* residual, void* out, long M, int N, int ld_acc, int ld_out,
                                    int ld_res, int clear, void* stream) {
   if (M <= 0) return 0;
-  long g = (M * N + 255) / 256;
-  if (g > 148 * 8) g = 148 * 8;
-  oil_gemm_finish_kernel<<<(int)g, 256, 0, (cudaStream_t)stream>>>(acc, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)residual,
+  int gx = (N + 255) / 256;
+  if (gx > 32) gx = 32;
+  dim3 grid(gx, (unsigned)M);
+  oil_gemm_finish_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(acc, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)residual,
                                                                   (__nv_bfloat16*)out, M, N, ld_acc, ld_out, ld_res, clear);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;

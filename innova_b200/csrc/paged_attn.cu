@@ -89,6 +89,10 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const __nv_bfloat16* 
   __shared__ float sq[MAXG][D];
   __shared__ float sm_m[4][MAXG], sm_l[4][MAXG];
   __shared__ float sm_o[4][MAXG][D];
+  // the 16 levels, one copy per bank: lane l reads lv[code * 32 + l], so a warp never conflicts
+  // (a table in constant memory would serialise the 32 different indices of a warp)
+  __shared__ float lv[16 * 32];
+  for (int i = threadIdx.x; i < 16 * 32; i += blockDim.x) lv[i] = c_kv_levels[i >> 5];
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int G = H / Hkv;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -127,7 +131,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const __nv_bfloat16* 
 #pragma unroll
         for (int w = 0; w < 4; ++w)
 #pragma unroll
-          for (int n = 0; n < 8; ++n) kf[j * 32 + w * 8 + n] = c_kv_levels[(wds[w] >> (4 * n)) & 15] * s;
+          for (int n = 0; n < 8; ++n) kf[j * 32 + w * 8 + n] = lv[(((wds[w] >> (4 * n)) & 15) << 5) + lane] * s;
       }
     } else {
       const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(k_pool) + (row0 + t) * D + hf * HALF;
@@ -181,7 +185,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const __nv_bfloat16* 
         const float s = __half2float(v_scale[(row0 + tt) * (D / 32) + (lane * EPL) / 32]);
         uint32_t bits = EPL == 4 ? *reinterpret_cast<const uint16_t*>(vp) : *vp;
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) vf[e] = c_kv_levels[(bits >> (4 * e)) & 15] * s;
+        for (int e = 0; e < EPL; ++e) vf[e] = lv[(((bits >> (4 * e)) & 15) << 5) + lane] * s;
       } else {
         const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(v_pool) + (row0 + tt) * D + lane * EPL;
 #pragma unroll
