@@ -18,6 +18,7 @@ FORMATS = ["OIL1", "SPARK_Q0", "OIL2", "OIL4", "OIL8", "OIL16", "OIL32", "OIL1_G
            "OIL16_GRP", "SPARK_SPARSE", "SPARK_SPARSE_GRP"]
 FORMAT_ID = {n: i for i, n in enumerate(FORMATS)}
 OIL1, SPARK_Q0, OIL2, OIL4, OIL8, OIL16, OIL32 = range(7)
+OIL1_GRP, SPARK_Q0_GRP, OIL2_GRP, OIL4_GRP, OIL8_GRP, OIL16_GRP, SPARK_SPARSE, SPARK_SPARSE_GRP = range(7, 15)
 DEFAULT_BLOCK = 256  # the canonical codec / converter block (src/format_registry.cpp:17)
 
 _bound = False

@@ -100,11 +100,12 @@ class TPDecoder:
     ``seed`` (every rank draws the full matrix on its GPU, keeps its shard, quantises it, drops the rest)."""
 
     def __init__(self, cfg: TransformerConfig, group=None, fmt: str = "oil4", max_batch: int = 64, max_seq: int = 1024, seed: int = 0,
-                 kv_format: str = "oil4", device=None):
+                 kv_format: str = "oil4", device=None, single: bool = False):
         self.cfg = cfg
         self.dev = device or torch.device("cuda", torch.cuda.current_device())
-        self.world = dist.get_world_size(group) if (dist.is_initialized() and (group is not None or True)) else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        multi = dist.is_initialized() and not single  # single=True: the whole model on this GPU (reference for tests)
+        self.world = dist.get_world_size(group) if multi else 1
+        self.rank = dist.get_rank(group) if multi else 0
         W, r = self.world, self.rank
         assert cfg.num_heads % W == 0 and cfg.kv_heads % W == 0 and cfg.ffn_hidden_size % W == 0
         self.H, self.Hkv, self.D = cfg.num_heads // W, cfg.kv_heads // W, cfg.head_dim

@@ -64,3 +64,45 @@ def test_fused_fsdp_step_matches_collective_baseline(tmp_path):
     # wgrad uses fp32 atomics, so the two runs differ by summation order only
     assert float((m_a - m_b).norm() / m_b.norm()) < 2e-3
     assert float((p_a - p_b).norm() / p_b.norm()) < 5e-3
+
+
+def _tp_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from innova_b200.models import TransformerConfig
+    from innova_b200.ops import runtime as rt
+    from innova_b200.parallel.tp import TPDecoder
+    cfg = TransformerConfig(vocab_size=1024, hidden_size=512, num_layers=2, num_heads=8, head_dim=64, ffn_hidden_size=1408, num_kv_heads=4,
+                            max_seq_len=256)
+    ids = torch.randint(0, 1024, (4, 48), generator=torch.Generator().manual_seed(0)).to(dev)
+    res = {}
+    for name, single in (("tp", False), ("one", True)):
+        if single and rank != 0:
+            continue
+        dec = TPDecoder(cfg, max_batch=4, max_seq=128, seed=3, device=dev, single=single)
+        dec._splits = 1
+        dec._scratch = torch.empty(4 * dec.H * (dec.D + 2), dtype=torch.float32, device=dev)
+        l0 = dec.prefill(ids)
+        tok = l0.argmax(-1)
+        l1 = dec._decode_step(tok)
+        toks, _, _ = dec.generate(ids, 6, use_graph=True)
+        rt.check_status()
+        res[name] = (l0.float().cpu(), l1.float().cpu(), toks.cpu(), dec.ctx.multimem if dec.ctx is not None else None)
+    if rank == 0:
+        torch.save(res, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tensor_parallel_decode_matches_single_gpu(tmp_path):
+    _need_gpus(2)
+    out = str(tmp_path / "tp.pt")
+    mp.spawn(_tp_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    res = torch.load(out)
+    (a0, a1, ta, mm), (b0, b1, tb, _) = res["tp"], res["one"]
+    rel = lambda x, y: float((x - y).norm() / y.norm())
+    assert rel(a0, b0) < 2e-2, ("prefill", rel(a0, b0), mm)
+    assert rel(a1, b1) < 2e-2, ("decode", rel(a1, b1), mm)
+    assert (ta == tb).float().mean() > 0.7
