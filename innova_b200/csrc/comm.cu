@@ -216,6 +216,62 @@ __global__ void allreduce_twoshot_kernel(PeerPtrs bufs, int W, int rank, long n4
   }
 }
 
+// ---- stand-alone collectives through the switch (NVLS) ----
+// `mc` is the multicast address of a symmetric buffer: a load-reduce on it returns the sum over all
+// ranks' copies (added inside the switch), a store on it lands in every rank's copy. Each rank handles
+// 1/W of the vector, so every element crosses this GPU's links once in each direction.
+__device__ __forceinline__ float4 mc_ld_reduce_f32x4(const float* mc_addr) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc_addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void mc_st_f32x4(float* mc_addr, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+// In-place all-reduce (sum, optionally scaled) of n4 float4 on the symmetric buffer behind `mc`.
+__global__ void nvls_allreduce_kernel(float* mc, int W, int rank, long n4, float scale) {
+  const long per = (n4 + W - 1) / W;
+  const long lo = (long)rank * per, hi = lo + per < n4 ? lo + per : n4;
+  for (long i = lo + blockIdx.x * (long)blockDim.x + threadIdx.x; i < hi; i += (long)gridDim.x * blockDim.x) {
+    float4 v = mc_ld_reduce_f32x4(mc + i * 4);
+    v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+    mc_st_f32x4(mc + i * 4, v);
+  }
+}
+// out[0..per4) = sum over ranks of their buffer[rank*per4 ..]; the symmetric buffer is left untouched.
+__global__ void nvls_reduce_scatter_kernel(const float* mc, float* __restrict__ out, int rank, long per4) {
+  const float* base = mc + (long)rank * per4 * 4;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < per4; i += (long)gridDim.x * blockDim.x)
+    reinterpret_cast<float4*>(out)[i] = mc_ld_reduce_f32x4(base + i * 4);
+}
+// every rank's buffer[rank*per4 ..] <- this rank's src[0..per4)
+__global__ void nvls_allgather_kernel(float* mc, const float* __restrict__ src, int rank, long per4) {
+  float* base = mc + (long)rank * per4 * 4;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < per4; i += (long)gridDim.x * blockDim.x)
+    mc_st_f32x4(base + i * 4, reinterpret_cast<const float4*>(src)[i]);
+}
+// Reduce-scatter over plain peer loads: out = sum_r peer_r[rank*per4 ..].
+__global__ void p2p_reduce_scatter_kernel(PeerPtrs bufs, int W, int rank, long per4, float* __restrict__ out) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < per4; i += (long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < W; ++k) {
+      const float4 v = reinterpret_cast<const float4*>(bufs.p[(rank + k) % W])[(long)rank * per4 + i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    reinterpret_cast<float4*>(out)[i] = acc;
+  }
+}
+// All-to-all (pull): out[r*chunk16 ..] <- peer r's src[rank*chunk16 ..], 16-byte units.
+__global__ void alltoall_pull_kernel(PeerPtrs src, int W, int rank, long chunk16, uint4* __restrict__ out) {
+  for (int k = 0; k < W; ++k) {
+    const int r = (rank + k) % W;
+    const uint4* s = reinterpret_cast<const uint4*>(src.p[r]) + (long)rank * chunk16;
+    uint4* d = out + (long)r * chunk16;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < chunk16; i += (long)gridDim.x * blockDim.x) d[i] = s[i];
+  }
+}
+
 static int fill_ptrs(PeerPtrs& pp, const uint64_t* host_ptrs, int W) {
   if (W < 1 || W > MAX_RANKS) return -ERR_BAD_ARG;
   for (int i = 0; i < MAX_RANKS; ++i) pp.p[i] = i < W ? reinterpret_cast<void*>(host_ptrs[i]) : nullptr;
@@ -289,5 +345,37 @@ extern "C" int inv_device_barrier(const uint64_t* peer_flags, void* local_flags,
   PeerPtrs pf;
   if (fill_ptrs(pf, peer_flags, W)) return -ERR_BAD_ARG;
   device_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(pf, (uint32_t*)local_flags, (uint32_t*)counter, W, rank, status);
+  RET_LAUNCH();
+}
+
+// The callers bracket these with a device barrier over the peer flags: all ranks' inputs must be in place
+// before a kernel reads them, and nobody may overwrite a buffer until every rank has finished reading it.
+extern "C" int inv_nvls_allreduce_f32(void* mc_ptr, int W, int rank, long n, float scale, void* stream) {
+  if (n % 4 || W < 1 || !mc_ptr) return -ERR_BAD_ARG;
+  nvls_allreduce_kernel<<<148 * 2, 256, 0, (cudaStream_t)stream>>>((float*)mc_ptr, W, rank, n / 4, scale);
+  RET_LAUNCH();
+}
+extern "C" int inv_nvls_reduce_scatter_f32(const void* mc_ptr, float* out, int rank, long per, void* stream) {
+  if (per % 4 || !mc_ptr) return -ERR_BAD_ARG;
+  nvls_reduce_scatter_kernel<<<148 * 2, 256, 0, (cudaStream_t)stream>>>((const float*)mc_ptr, out, rank, per / 4);
+  RET_LAUNCH();
+}
+extern "C" int inv_nvls_allgather_f32(void* mc_ptr, const float* src, int rank, long per, void* stream) {
+  if (per % 4 || !mc_ptr) return -ERR_BAD_ARG;
+  nvls_allgather_kernel<<<148 * 2, 256, 0, (cudaStream_t)stream>>>((float*)mc_ptr, src, rank, per / 4);
+  RET_LAUNCH();
+}
+extern "C" int inv_p2p_reduce_scatter_f32(const uint64_t* peer_bufs, int W, int rank, long per, float* out, void* stream) {
+  if (per % 4) return -ERR_BAD_ARG;
+  PeerPtrs b;
+  if (fill_ptrs(b, peer_bufs, W)) return -ERR_BAD_ARG;
+  p2p_reduce_scatter_kernel<<<148 * 2, 256, 0, (cudaStream_t)stream>>>(b, W, rank, per / 4, out);
+  RET_LAUNCH();
+}
+extern "C" int inv_alltoall_pull(const uint64_t* peer_src, int W, int rank, long chunk_bytes, void* out, void* stream) {
+  if (chunk_bytes % 16) return -ERR_BAD_ARG;
+  PeerPtrs s;
+  if (fill_ptrs(s, peer_src, W)) return -ERR_BAD_ARG;
+  alltoall_pull_kernel<<<148 * 2, 256, 0, (cudaStream_t)stream>>>(s, W, rank, chunk_bytes / 16, (uint4*)out);
   RET_LAUNCH();
 }

@@ -396,6 +396,50 @@ int oilr_block_payload(void* r, uint32_t b, const uint8_t** cb, const uint8_t** 
   return 0;
 }
 
+// Device-decoder records (csrc/block_codec.cu, 32 bytes each) for the blocks of tensor i. Payload offsets are
+// relative to *base_off, the start of the file span [*base_off, *base_off + *span) that holds the tensor's
+// blocks; the caller uploads that span once and decodes the whole tensor in one launch.
+const uint8_t* oilr_base(void* r) { return static_cast<OilReader*>(r)->base(); }
+int oilr_tensor_descs(void* r, uint32_t i, void* descs, uint64_t* base_off, uint64_t* span) {
+  auto* rd = static_cast<OilReader*>(r);
+  if (i >= rd->tensors().size()) return -1;
+  const TensorRef& t = rd->tensors()[i];
+  size_t lo = (size_t)-1, hi = 0;
+  for (uint32_t b = 0; b < t.num_blocks; ++b) {
+    const BlockRef& br = rd->blocks()[t.block_start + b];
+    if (br.cb_bytes) { lo = std::min(lo, br.cb_off); hi = std::max(hi, br.cb_off + br.cb_bytes); }
+    if (br.idx_bytes) { lo = std::min(lo, br.idx_off); hi = std::max(hi, br.idx_off + br.idx_bytes); }
+  }
+  if (lo == (size_t)-1) lo = hi = 0;
+  if (hi - lo >= (1ull << 32)) return -2;
+  *base_off = lo;
+  *span = hi - lo;
+  if (!descs) return 0;
+  struct Desc {
+    uint64_t idx_off, out_off;
+    uint32_t idx_bytes, cb_off_lo;
+    uint16_t cb_bytes;
+    uint8_t fmt, pad;
+    uint32_t n;
+  };
+  static_assert(sizeof(Desc) == 32, "record layout");
+  Desc* d = static_cast<Desc*>(descs);
+  uint64_t out = 0;
+  for (uint32_t b = 0; b < t.num_blocks; ++b) {
+    const BlockRef& br = rd->blocks()[t.block_start + b];
+    d[b].idx_off = br.idx_bytes ? br.idx_off - lo : 0;
+    d[b].out_off = out;
+    d[b].idx_bytes = br.idx_bytes;
+    d[b].cb_off_lo = br.cb_bytes ? (uint32_t)(br.cb_off - lo) : 0;
+    d[b].cb_bytes = (uint16_t)std::min<uint32_t>(br.cb_bytes, 65535u);
+    d[b].fmt = (uint8_t)rd->effective_format(br);
+    d[b].pad = 0;
+    d[b].n = br.num_weights;
+    out += br.num_weights;
+  }
+  return 0;
+}
+
 // ---------------------------------------------------------------- .oilidx
 // names: n NUL-terminated strings back to back.
 int oilidx_write(const char* path, uint32_t version, const char* names, uint32_t n) {

@@ -6,7 +6,10 @@
 // production GEMVs gemv_oil4_* / gemv_oil8_* (src/kernel_production.cpp:95-166).
 //
 // Weight format (the block-32 compute format of csrc/quant.cu): index [N, K] (OIL8: one byte, OIL4:
-// two per byte, low nibble first), scale bf16 [N, K/32], one shared codebook over [-1, 1].
+// two per byte, low nibble first; 2-bit: four per byte, low bits first), scale bf16 [N, K/32], one shared
+// codebook over [-1, 1]. The 2-bit path serves the ternary weights (SPARK, OIL1: codebook {-1, 0, +1, 0})
+// and OIL2 (four levels) and replaces tl1/tl2_gemm and gemv_spark_* (src/kernel_tl.cpp:32-185,
+// src/kernel_production.cpp:79-93).
 //
 // The kernel is built for the decode shape (M = tokens in flight <= 256, N and K large) and runs
 // "swapped": the 128 weight rows of a tile are the M side of tcgen05.mma, the tokens its N side.
@@ -114,7 +117,8 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
   // entry e for lane l lives at lut[e * 32 + l]: every lane reads its own bank, whatever the indices are
   for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
     const int e = i >> 5;
-    if (BITS == 4) lut[i] = pack_bf16x2(p.codebook[e & 15], p.codebook[e >> 4]);
+    if (BITS == 2) lut[i] = 0;
+    else if (BITS == 4) lut[i] = pack_bf16x2(p.codebook[e & 15], p.codebook[e >> 4]);
     else lut[i] = pack_bf16x2(p.codebook[e], 0.f);
   }
   if (threadIdx.x == 0) {
@@ -221,7 +225,26 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
         const __nv_bfloat162 sc2 = __halves2bfloat162(sc, sc);
         const uint8_t* src = sIdx + si * IDX_TILE + r * ROW_BYTES + half * (ROW_BYTES / 2);
         uint8_t* dst = sA + sa * A_TILE + (r >> 3) * 1024 + (r & 7) * 128;
-        if (BITS == 4) {
+        if (BITS == 2) {
+          // 4-entry codebook (ternary {-1, 0, +1, 0} for SPARK / OIL1 weights, or the OIL2 levels): the four
+          // scaled entries sit in one 64-bit register and every 2-bit code selects 16 bits of it
+          const uint2 raw = *reinterpret_cast<const uint2*>(src);  // 32 weights
+          const __nv_bfloat162 e01 = __hmul2(__floats2bfloat162_rn(p.codebook[0], p.codebook[1]), sc2);
+          const __nv_bfloat162 e23 = __hmul2(__floats2bfloat162_rn(p.codebook[2], p.codebook[3]), sc2);
+          const uint64_t tbl = (uint64_t)(*reinterpret_cast<const uint32_t*>(&e01)) | ((uint64_t)(*reinterpret_cast<const uint32_t*>(&e23)) << 32);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {  // 8 weights = 16 bits of codes
+            const uint32_t codes = ((g < 2 ? raw.x : raw.y) >> (16 * (g & 1))) & 0xffffu;
+            uint32_t o[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              const uint32_t lo = (uint32_t)(tbl >> (16 * ((codes >> (4 * b)) & 3))) & 0xffffu;
+              const uint32_t hi = (uint32_t)(tbl >> (16 * ((codes >> (4 * b + 2)) & 3))) << 16;
+              o[b] = lo | hi;
+            }
+            *reinterpret_cast<uint4*>(dst + (((half * 4 + g) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        } else if (BITS == 4) {
           const uint4 raw = *reinterpret_cast<const uint4*>(src);  // 32 weights
           const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
@@ -316,7 +339,7 @@ using namespace inv;
 extern "C" int inv_oil_gemm(const void* x, int ldx, const void* idx, const void* scales, const float* codebook, int bits, float* acc, int ldo,
                             int M, int N, int K, int split_k, int* status, void* stream, int multimem) {
   using namespace og;
-  if ((bits != 4 && bits != 8) || M < 1 || M > MAXM || (K % 64) || (ldx % 8) || N < 1) return -ERR_BAD_ARG;
+  if ((bits != 2 && bits != 4 && bits != 8) || M < 1 || M > MAXM || (K % 64) || (ldx % 8) || N < 1) return -ERR_BAD_ARG;
   static int num_sms = 0;
   if (num_sms == 0) {
     int dev = 0;
@@ -350,6 +373,7 @@ extern "C" int inv_oil_gemm(const void* x, int ldx, const void* idx, const void*
   const int smem = AB_STAGES * (A_TILE + MAXM * BK * 2) + IDX_STAGES * idx_tile + 1024 + 256 * 32 * 4 + 512 + 1024;
   static bool configured = false;
   if (!configured) {
+    cudaFuncSetAttribute(oil_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(oil_gemm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     cudaFuncSetAttribute(oil_gemm_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     configured = true;
@@ -357,7 +381,8 @@ extern "C" int inv_oil_gemm(const void* x, int ldx, const void* idx, const void*
   const int total = n_tiles * split_k;
   const int grid = total < num_sms ? total : num_sms;
   cudaStream_t st = (cudaStream_t)stream;
-  if (bits == 4) oil_gemm_kernel<4><<<grid, THREADS, smem, st>>>(ti, tx, p);
+  if (bits == 2) oil_gemm_kernel<2><<<grid, THREADS, smem, st>>>(ti, tx, p);
+  else if (bits == 4) oil_gemm_kernel<4><<<grid, THREADS, smem, st>>>(ti, tx, p);
   else oil_gemm_kernel<8><<<grid, THREADS, smem, st>>>(ti, tx, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;

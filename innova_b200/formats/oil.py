@@ -47,6 +47,7 @@ def lib():
             "oilr_tensor_num_blocks": ([vp, C.c_uint32], C.c_uint32), "oilr_find": ([vp, C.c_char_p], C.c_int),
             "oilr_read_tensor": ([vp, C.c_uint32, vp], C.c_int), "oilr_block_info": ([vp, C.c_uint32, vp], C.c_int),
             "oilr_block_payload": ([vp, C.c_uint32, C.POINTER(vp), C.POINTER(vp)], C.c_int),
+            "oilr_base": ([vp], vp), "oilr_tensor_descs": ([vp, C.c_uint32, vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)], C.c_int),
             "oilidx_write": ([C.c_char_p, C.c_uint32, C.c_char_p, C.c_uint32], C.c_int),
             "oilidx_read": ([C.c_char_p, C.POINTER(C.c_uint32), vp, C.c_uint64], C.c_int),
         }
@@ -189,6 +190,24 @@ class OILReader:
         out = np.empty(self.numel(name), dtype=np.float32)
         lib().oilr_read_tensor(self._h, i, out.ctypes.data)
         return torch.from_numpy(out)
+
+    def read_tensor_device(self, name: str, device, dtype=torch.float32) -> torch.Tensor:
+        """Decode on the GPU: the tensor's file span and one 32-byte record per block are uploaded, one kernel
+        (csrc/block_codec.cu) expands every block straight into ``dtype`` (fp32 or bf16) device memory."""
+        from . import device_codec
+        return device_codec.decode_tensor(self, name, device, dtype)
+
+    def tensor_span(self, name: str):
+        """(descriptor bytes, span bytes) for ``read_tensor_device``; raises if the span exceeds 4 GiB."""
+        i = self.tensors[name]
+        base, span = C.c_uint64(), C.c_uint64()
+        nb = int(lib().oilr_tensor_num_blocks(self._h, i))
+        descs = np.empty(nb * 32, dtype=np.uint8)
+        rc = lib().oilr_tensor_descs(self._h, i, descs.ctypes.data, C.byref(base), C.byref(span))
+        if rc:
+            raise ValueError(f"{name}: tensor span not addressable by the device decoder (rc={rc})")
+        raw = np.ctypeslib.as_array(C.cast(lib().oilr_base(self._h) + base.value, C.POINTER(C.c_uint8)), shape=(max(span.value, 1),))
+        return descs, raw[: span.value]
 
     def block_range(self, name: str):
         i = self.tensors[name]

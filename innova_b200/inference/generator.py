@@ -50,9 +50,9 @@ class Generator:
 
     # ------------------------------------------------------------------ one forward over new tokens
     @torch.no_grad()
-    def _forward(self, ids: torch.Tensor, start: List[int]) -> torch.Tensor:
+    def _forward(self, ids: torch.Tensor, start: List[int], all_logits: bool = False) -> torch.Tensor:
         """ids [B, S_new]; sequences 0..B-1 continue at positions start[b]. Returns logits [B, vocab] of the
-        last new token."""
+        last new token, or [B, S_new, vocab] with ``all_logits`` (speculative verification)."""
         m, cfg, cache = self.model, self.cfg, self.cache
         B, S = ids.shape
         H, Hkv, D = cfg.num_heads, cfg.kv_heads, cfg.head_dim
@@ -96,7 +96,7 @@ class Generator:
                 x = x + self._ffn(blk, blk.ffn_norm(x))
         if prefill:
             cache.commit(batch_ids, [S] * B)
-        last = m.norm(x[:, -1])
+        last = m.norm(x if all_logits else x[:, -1])
         logits = ops.linear(last, m.lm_head.weight)
         return logits[..., : cfg.vocab_size]
 

@@ -1,0 +1,196 @@
+"""Speculative decoding: a small draft model proposes, the target model verifies a whole run at once.
+
+Reference: ``SpeculativeDecoder`` (rejection sampling with residual resampling and adaptive draft length,
+src/inference_opt.cpp:114-281), the exact-match decoder with KV rewind and ``SmallBatchVerifier``
+(src/speculative_decoder.cpp:67-236) and the ``Theorem13Result`` speed-up estimate
+(include/oil/speculative_decoder.h:129-155).
+
+One round: the draft generator extends its own KV cache by ``gamma`` tokens; the target scores the pending
+token plus the drafts in one forward pass (``gamma + 1`` rows of logits); ``verify`` (csrc/spec_verify.cu on
+CUDA) walks each sequence's rows, returns how many drafts survive and the replacement / bonus token;
+both KV caches are rewound to the accepted prefix.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+import torch
+
+from .. import _native
+from .generator import Generator
+from .sampler import Sampler, SamplingParams
+
+vp, i32, i64, f32 = _native.vp, _native.i32, _native.i64, _native.f32
+_native.register_cuda_sigs({"inv_spec_verify": [vp, vp, vp, vp, i32, i32, i32, i64, i64, f32, i32, vp, vp, vp]})
+
+REJECTION, EXACT = 0, 1
+
+
+def verify(target_logits: torch.Tensor, draft_tokens: torch.Tensor, uniforms: torch.Tensor, draft_logits: Optional[torch.Tensor] = None,
+           temperature: float = 1.0, mode: int = REJECTION):
+    """target_logits [B, G+1, V]; draft_tokens [B, G]; uniforms [B, G+1] in [0, 1); draft_logits [B, G, V] or
+    None (p_draft = 1/V). Returns (n_accept [B], next_token [B]) as int64 tensors."""
+    B, G1, V = target_logits.shape
+    G = G1 - 1
+    tl = target_logits.float().contiguous()
+    dl = None if draft_logits is None else draft_logits.float().contiguous()
+    toks = draft_tokens.to(torch.int32).contiguous()
+    u = uniforms.float().contiguous().to(tl.device)
+    if tl.is_cuda:
+        from ..ops import runtime as rt
+        n_acc = torch.empty(B, dtype=torch.int32, device=tl.device)
+        nxt = torch.empty(B, dtype=torch.int32, device=tl.device)
+        rt.check(rt.lib().inv_spec_verify(tl.data_ptr(), rt.ptr(dl), toks.data_ptr(), u.data_ptr(), B, G, V, V, V, float(temperature), int(mode),
+                                          n_acc.data_ptr(), nxt.data_ptr(), rt.stream_ptr()), "inv_spec_verify")
+        return n_acc.long(), nxt.long()
+    inv_t = 1.0 / temperature if temperature > 0 else 1.0
+    n_acc = torch.zeros(B, dtype=torch.int64)
+    nxt = torch.zeros(B, dtype=torch.int64)
+
+    def draw(weights, uu):
+        total = weights.sum()
+        if not total > 0:
+            return -1
+        cum = torch.cumsum(weights, 0)
+        hit = ((cum >= uu * total) & (weights > 0)).nonzero()
+        return int(hit[0]) if hit.numel() else int((weights > 0).nonzero()[-1])
+
+    for b in range(B):
+        i = 0
+        done = False
+        while i < G and not done:
+            t = int(toks[b, i].clamp(0, V - 1))
+            row = tl[b, i]
+            if mode == EXACT:
+                am = int(row.argmax())
+                if am != t:
+                    n_acc[b], nxt[b], done = i, am, True
+                    break
+                i += 1
+                continue
+            p = torch.softmax(row * inv_t, 0)
+            q = torch.softmax(dl[b, i] * inv_t, 0) if dl is not None else torch.full((V,), 1.0 / V)
+            if float(u[b, i]) <= min(1.0, float(p[t]) / (float(q[t]) + 1e-10)):
+                i += 1
+                continue
+            r = draw((p - q).clamp(min=0), float(u[b, G]))
+            if r < 0:
+                r = draw(p, float(u[b, G]))
+            n_acc[b], nxt[b], done = i, (t if r < 0 else r), True
+        if not done:
+            row = tl[b, G]
+            n_acc[b] = G
+            nxt[b] = int(row.argmax()) if mode == EXACT else max(0, draw(torch.softmax(row * inv_t, 0), float(u[b, G])))
+    return n_acc, nxt
+
+
+@dataclass
+class Theorem13Result:
+    speedup: float
+    optimal_k: int
+    acceptance_rate: float
+    cost_ratio: float
+
+    @staticmethod
+    def compute(alpha: float, cost_ratio: float) -> "Theorem13Result":
+        if alpha <= cost_ratio:
+            return Theorem13Result(1.0, 1, alpha, cost_ratio)
+        k = max(1, int(round(math.sqrt(2.0 / (1.0 - alpha))))) if alpha < 1.0 else 16
+        return Theorem13Result((1.0 + k * alpha) / (1.0 + k * cost_ratio), k, alpha, cost_ratio)
+
+
+@dataclass
+class RejectionStats:
+    proposed: int = 0
+    accepted: int = 0
+    rounds: int = 0
+    history: List[int] = field(default_factory=list)
+
+    @property
+    def acceptance_rate(self) -> float:
+        return self.accepted / self.proposed if self.proposed else 0.0
+
+    @property
+    def tokens_per_round(self) -> float:
+        return (self.accepted + self.rounds) / self.rounds if self.rounds else 0.0
+
+
+class SpeculativeDecoder:
+    """Single-sequence speculative generation over two ``Generator`` objects (their KV caches are used and
+    rewound). ``mode`` REJECTION reproduces the target distribution; EXACT accepts only argmax matches
+    (greedy decoding, identical output to the target alone)."""
+
+    def __init__(self, target: Generator, draft: Generator, gamma: int = 4, min_gamma: int = 1, max_gamma: int = 8, mode: int = REJECTION,
+                 temperature: float = 1.0, adaptive: bool = True, seed: int = 42):
+        self.target, self.draft = target, draft
+        self.gamma, self.min_gamma, self.max_gamma = gamma, min_gamma, max_gamma
+        self.mode, self.temperature, self.adaptive = mode, temperature, adaptive
+        self.gen = torch.Generator().manual_seed(seed)
+        self.stats = RejectionStats()
+        self.acc_ema = 0.5
+
+    def adapt_gamma(self, round_rate: float):
+        """gamma = round(5 * min(ema/(1-ema), 5)) clamped, as the reference adapts it."""
+        self.acc_ema = 0.9 * self.acc_ema + 0.1 * round_rate
+        ratio = self.acc_ema / max(1.0 - self.acc_ema, 1e-6)
+        self.gamma = int(max(self.min_gamma, min(self.max_gamma, round(5.0 * min(ratio, 5.0)))))
+
+    @torch.no_grad()
+    def generate_tokens(self, prompt, max_new_tokens: int = 64, eos_id: Optional[int] = None) -> List[int]:
+        tgt, drf = self.target, self.draft
+        dev = tgt.device
+        ids = torch.as_tensor(prompt, dtype=torch.long, device=dev).view(1, -1)
+        L = ids.shape[1]
+        for g in (tgt, drf):
+            for b in range(g.cache.max_batch):
+                g.cache.free(b)
+        greedy = self.mode == EXACT
+        sp = SamplingParams(temperature=0.0 if greedy else self.temperature)
+        sampler = Sampler(sp)
+        logits = tgt._forward(ids, [0])
+        drf._forward(ids.to(drf.device), [0])
+        pending = int(sampler.sample(logits)[0])
+        out = [pending]
+        t_len = d_len = L                   # tokens held by each cache
+        d_unfed: List[int] = []             # accepted tokens the draft has not consumed yet (besides `pending`)
+        while len(out) < max_new_tokens and (eos_id is None or out[-1] != eos_id):
+            G = max(1, min(self.gamma, max_new_tokens - len(out), tgt.max_seq - t_len - 2))
+            drafts, dlogits = [], []
+            feed = d_unfed + [pending]
+            for _ in range(G):
+                dl = drf._forward(torch.tensor([feed], device=drf.device), [d_len])
+                d_len += len(feed)
+                tok = int(sampler.sample(dl)[0])
+                drafts.append(tok)
+                dlogits.append(dl.float())
+                feed = [tok]
+            tl = tgt._forward(torch.tensor([[pending] + drafts], device=dev), [t_len], all_logits=True)
+            u = torch.rand(1, G + 1, generator=self.gen)
+            n_acc, nxt = verify(tl, torch.tensor([drafts], device=dev), u, None if greedy else torch.stack(dlogits, dim=1).to(dev),
+                                self.temperature, self.mode)
+            n, nxt = int(n_acc[0]), int(nxt[0])
+            t_len += 1 + n                  # pending + accepted drafts stay in the target cache
+            tgt.cache.truncate(0, t_len)
+            # the draft cache holds pending + drafts[:G-1]; keep what was accepted, remember what it still misses
+            keep = min(t_len, d_len)
+            drf.cache.truncate(0, keep)
+            d_len = keep
+            d_unfed = drafts[G - 1:G] if n == G else []
+            out.extend(drafts[:n])
+            out.append(nxt)
+            pending = nxt
+            self.stats.proposed += G
+            self.stats.accepted += n
+            self.stats.rounds += 1
+            self.stats.history.append(n)
+            if self.adaptive:
+                self.adapt_gamma(n / G)
+            if eos_id is not None and eos_id in out[-(n + 1):]:
+                out = out[: len(out) - (n + 1) + out[-(n + 1):].index(eos_id) + 1]
+                break
+        return out[:max_new_tokens]
+
+    def theorem13(self, cost_ratio: float) -> Theorem13Result:
+        return Theorem13Result.compute(self.stats.acceptance_rate, cost_ratio)

@@ -27,10 +27,14 @@ _native.register_cuda_sigs({
 })
 
 
+# value of each 2-bit code: spark codes are 0 = zero, 1 = +scale, 2 = -scale; oil1 codes are 0 = -scale, 1 = +scale
+TERNARY_TABLE = {"spark": [0.0, 1.0, -1.0, 0.0], "oil1": [-1.0, 1.0, 0.0, 0.0]}
+
+
 @dataclass
 class QuantWeight:
-    fmt: str                 # "oil4" | "oil8"
-    idx: torch.Tensor        # uint8: [N, K/2] (oil4) or [N, K] (oil8)
+    fmt: str                 # "oil4" | "oil8" | "spark" | "oil1"
+    idx: torch.Tensor        # uint8: [N, K/2] (oil4), [N, K] (oil8) or [N, K/4] (2-bit ternary / sign)
     scales: torch.Tensor     # bf16 [N, K/32]
     codebook: torch.Tensor   # fp32 [16] or [256]
     N: int
@@ -39,7 +43,7 @@ class QuantWeight:
 
     @property
     def bits(self) -> int:
-        return 4 if self.fmt == "oil4" else 8
+        return {"oil4": 4, "oil8": 8}.get(self.fmt, 2)
 
     def nbytes(self) -> int:
         return self.idx.numel() + self.scales.numel() * 2
@@ -52,6 +56,8 @@ class QuantWeight:
         """[N, K] in the scales' dtype."""
         if self.fmt == "oil4":
             codes = torch.stack([self.idx & 15, self.idx >> 4], dim=-1).reshape(self.N, self.K)
+        elif self.bits == 2:
+            codes = torch.stack([(self.idx >> s) & 3 for s in (0, 2, 4, 6)], dim=-1).reshape(self.N, self.K)
         else:
             codes = self.idx
         vals = self.codebook.to(self.idx.device)[codes.long()].to(torch.bfloat16)
@@ -60,13 +66,20 @@ class QuantWeight:
 
 def quantize_weight(w: torch.Tensor, fmt: str = "oil4", codebook: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> QuantWeight:
     """[N, K] float weights -> QuantWeight (K must be a multiple of 64)."""
-    assert fmt in ("oil4", "oil8") and w.dim() == 2 and w.shape[1] % 64 == 0
+    assert fmt in ("oil4", "oil8", "spark", "oil1") and w.dim() == 2 and w.shape[1] % 64 == 0
     N, K = w.shape
-    cb = (codebook if codebook is not None else quant.default_codebook(fmt, w.device)).float().to(w.device)
+    if fmt in ("spark", "oil1"):
+        # 2-bit codes, four per byte (low bits first); the 4-entry table maps the quantiser's codes to signs
+        cb = torch.tensor(TERNARY_TABLE[fmt], dtype=torch.float32, device=w.device)
+    else:
+        cb = (codebook if codebook is not None else quant.default_codebook(fmt, w.device)).float().to(w.device)
     idx, sc, _ = quant.quantize_blockwise(w.contiguous(), fmt, cb)
     idx = idx.view(N, K)
     if fmt == "oil4":
         idx = quant.pack_nibbles(idx.reshape(-1)).view(N, K // 2)
+    elif fmt in ("spark", "oil1"):
+        q = idx.view(N, K // 4, 4).to(torch.int32)
+        idx = (q[..., 0] | (q[..., 1] << 2) | (q[..., 2] << 4) | (q[..., 3] << 6)).to(torch.uint8)
     return QuantWeight(fmt, idx.contiguous(), sc.view(N, K // 32).to(torch.bfloat16).contiguous(), cb.contiguous(), N, K,
                        None if bias is None else bias.to(torch.bfloat16))
 

@@ -106,3 +106,58 @@ def test_tensor_parallel_decode_matches_single_gpu(tmp_path):
     assert rel(a0, b0) < 2e-2, ("prefill", rel(a0, b0), mm)
     assert rel(a1, b1) < 2e-2, ("decode", rel(a1, b1), mm)
     assert (ta == tb).float().mean() > 0.7
+
+
+def _coll_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from innova_b200.ops import runtime as rt
+    from innova_b200.parallel.collectives import Communicator
+    from innova_b200.parallel.ddp import DDPFlatEngine
+    comm = Communicator(capacity=1 << 20, device=dev)
+    n = 8 * 1024 * world
+    x = (torch.arange(n, dtype=torch.float32, device=dev) % 1000) * 0.001 + rank
+    res = {"multicast": bool(comm.mc)}
+    for algo in (["nvls"] if comm.mc else []) + ["p2p", "nccl"]:
+        res[algo] = {
+            "ar": comm.all_reduce(x.clone(), algo=algo).cpu(), "avg": comm.all_reduce(x.clone(), average=True, algo=algo).cpu(),
+            "rs": comm.reduce_scatter(x.clone(), algo=algo).cpu(), "ag": comm.all_gather(x[:4096].clone(), algo=algo).cpu(),
+            "a2a": comm.all_to_all(x.clone(), algo=algo).cpu(),
+        }
+    big = torch.randn(3 * (1 << 20) + 12, device=dev)       # larger than the staging buffer: chunked
+    ref = big.clone()
+    dist.all_reduce(ref)
+    res["big_err"] = float((comm.all_reduce(big.clone()) - ref).abs().max())
+    # data-parallel engine on the native collectives against the NCCL one
+    flats = {}
+    for backend in ("native", "nccl"):
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.Linear(512, 64)).to(dev)
+        eng = DDPFlatEngine(model, lr=1e-2, weight_decay=0.0, max_grad_norm=1.0, backend=backend, bucket_floats=1 << 16)
+        for step in range(3):
+            g = torch.Generator().manual_seed(10 * step + rank)
+            for p in model.parameters():
+                p.main_grad.copy_(torch.randn(p.shape, generator=g).to(dev))
+            eng.step()
+        flats[backend] = eng.flat_param.float().cpu()
+    res["ddp_diff"] = float((flats["native"] - flats["nccl"]).abs().max())
+    rt.check_status()
+    torch.save(res, out + f".{rank}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_native_collectives_match_nccl(tmp_path):
+    _need_gpus(2)
+    world = 2
+    out = str(tmp_path / "coll")
+    mp.spawn(_coll_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    for rank in range(world):
+        r = torch.load(out + f".{rank}")
+        ref = r["nccl"]
+        for algo in [a for a in ("nvls", "p2p") if a in r]:
+            for k in ("ar", "avg", "rs", "ag", "a2a"):
+                assert torch.allclose(r[algo][k], ref[k], atol=1e-5), (rank, algo, k)
+        assert r["big_err"] < 1e-4 and r["ddp_diff"] < 1e-5

@@ -1,0 +1,198 @@
+"""GPU numerics of the second kernel set: tensor ops, gradient compression, train-in-format store,
+speculative verification, the device block codec and the 2-bit (ternary) weight GEMM. Every kernel is
+compared against a plain PyTorch / host-codec computation of the same op."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def test_tensor_ops_match_torch():
+    from innova_b200.ops import tensor_ops as T
+    torch.manual_seed(0)
+    x = torch.randn(37, 1000, device=DEV)
+    y = torch.randn(37, 1000, device=DEV)
+    for op, ref in (("relu", torch.relu), ("tanh", torch.tanh), ("sigmoid", torch.sigmoid), ("silu", torch.nn.functional.silu),
+                    ("gelu", lambda t: torch.nn.functional.gelu(t, approximate="tanh")), ("exp", torch.exp), ("square", lambda t: t * t)):
+        assert torch.allclose(T.unary(x, op), ref(x), atol=2e-3, rtol=2e-3), op
+    assert torch.allclose(T.unary(x, "scale", 1.5), x * 1.5) and torch.allclose(T.unary(x, "add_scalar", -2.0), x - 2.0)
+    assert torch.allclose(T.binary(x, y, "add"), x + y) and torch.allclose(T.binary(x, y, "sub"), x - y)
+    assert torch.allclose(T.binary(x, y, "mul"), x * y) and torch.allclose(T.binary(x, y, "div"), x / y, rtol=1e-6)
+    yz = y.clone()
+    yz[0, :10] = 0
+    assert float(T.binary(x, yz, "div")[0, :10].abs().sum()) == 0.0
+    odd = torch.randn(1003, device=DEV)
+    assert torch.allclose(T.unary(odd, "relu"), torch.relu(odd))
+    for cols in (7, 1000, 50257):
+        z = torch.randn(5, cols, device=DEV) * 3
+        assert torch.allclose(T.softmax_rows(z), torch.softmax(z, -1), atol=1e-6, rtol=1e-4)
+    for shape in ((33, 65), (1000, 37), (64, 64)):
+        m = torch.randn(*shape, device=DEV)
+        assert torch.equal(T.transpose2d(m), m.t().contiguous())
+    big = torch.randn(3_000_001, device=DEV)
+    assert abs(float(T.reduce_all(big, "sum")) - float(big.double().sum())) < 0.5
+    assert float(T.reduce_all(big, "max")) == float(big.max()) and float(T.reduce_all(big, "min")) == float(big.min())
+    assert abs(float(T.reduce_all(big, "mean")) - float(big.double().mean())) < 1e-6
+    t3 = torch.randn(6, 50, 40, device=DEV)
+    for op in ("sum", "mean", "max", "min"):
+        ref = getattr(t3, op)(dim=1)
+        ref = ref.values if op in ("max", "min") else ref
+        assert torch.allclose(T.reduce_axis(t3, 1, op), ref, atol=1e-5), op
+    assert torch.allclose(T.reduce_axis(t3, 2, "sum"), t3.sum(2), atol=1e-4)
+    bn = torch.randn(16, 8, 10, device=DEV)
+    g, b = torch.randn(8, device=DEV), torch.randn(8, device=DEV)
+    mean, var = bn.mean(0, keepdim=True), bn.var(0, unbiased=False, keepdim=True)
+    ref = (bn - mean) * torch.rsqrt(var + 1e-5) * g.view(1, 8, 1) + b.view(1, 8, 1)
+    assert torch.allclose(T.batch_norm(bn, g, b), ref, atol=1e-4)
+    A, v = torch.randn(300, 1024, device=DEV), torch.randn(1024, device=DEV)
+    assert torch.allclose(T.gemv(A, v), A @ v, atol=1e-3)
+    A2, v2 = torch.randn(30, 77, device=DEV), torch.randn(77, device=DEV)
+    assert torch.allclose(T.gemv(A2, v2, torch.ones(30, device=DEV)), A2 @ v2 + 1, atol=1e-4)
+
+
+def test_topk_and_int8_compression():
+    from innova_b200.parallel import ddp
+    torch.manual_seed(1)
+    for n, k in ((1 << 20, 10485), (5000, 1), (4097, 4097), (100000, 50000)):
+        g = torch.randn(n, device=DEV)
+        ref = g.clone()
+        vals, idx = ddp.topk_compress(g, k)
+        top = torch.topk(ref.abs(), k).indices
+        assert torch.equal(torch.sort(idx).values, torch.sort(top).values), (n, k)
+        assert torch.equal(vals, ref[idx])
+        assert int((g != 0).sum()) == k and torch.equal(g[idx], vals)
+        z = torch.zeros(n, device=DEV)
+        ddp.topk_scatter(z, vals, idx)
+        assert torch.equal(z, g)
+    # ties at the threshold: exactly k survive
+    t = torch.ones(1000, device=DEV)
+    v, i = ddp.topk_compress(t, 10)
+    assert int((t != 0).sum()) == 10 and len(set(i.tolist())) == 10
+    x = torch.randn(1 << 18, device=DEV) * 0.01
+    q, s = ddp.int8_compress(x)
+    qc, sc = ddp.int8_compress(x.cpu())
+    assert abs(float(s) - float(sc)) < 1e-9 and (q.cpu().int() - qc.int()).abs().max() <= 1
+    assert (q.cpu() != qc).float().mean() < 1e-3
+    out = torch.empty_like(x)
+    ddp.int8_sum_dequant(torch.stack([q, q, q]), torch.cat([s, s, s]), out, 1.0 / 3)
+    assert (out - x).abs().max() <= float(s) * 0.5 + 1e-7
+
+
+def test_native_store_matches_sequential_reference():
+    from tests.test_native_spec_cpu import sequential_update
+    from innova_b200.training.native_oil import NativeOILWeightStore
+    torch.manual_seed(2)
+    n, bs = 24 * 128, 128
+    w = torch.randn(n) * 0.03
+    sens = torch.rand(n)
+    cpu = NativeOILWeightStore(n, bs, "cpu")
+    cpu.initialize(w, sens, 0.3, 0.3)
+    gpu = NativeOILWeightStore(n, bs, DEV)
+    gpu.initialize(w.to(DEV), sens.to(DEV), 0.3, 0.3)
+    assert torch.equal(gpu.formats.cpu(), cpu.formats)
+    assert torch.allclose(gpu.scales.cpu(), cpu.scales)
+    assert (gpu.indices.cpu() != cpu.indices).float().mean() < 1e-3
+    assert torch.allclose(gpu.dequantize().cpu(), cpu.dequantize(), atol=1e-2)
+    assert torch.allclose(gpu.dequantize(torch.bfloat16).float().cpu(), gpu.dequantize().cpu(), atol=2e-3)
+    cpu.indices, cpu.scales = gpu.indices.cpu().clone(), gpu.scales.cpu().clone()
+    g = torch.randn(n)
+    ref_idx, ref_sc = sequential_update(cpu.indices, cpu.scales, cpu.formats, g, bs, 1e-3, 2e-3, cpu.cb4, cpu.cb8)
+    gpu.apply_update(g.to(DEV), 1e-3, 2e-3)
+    assert torch.allclose(gpu.scales.cpu(), ref_sc, rtol=1e-5, atol=1e-8)
+    assert (gpu.indices.cpu() != ref_idx).float().mean() < 2e-3
+    assert int(gpu.changed) == int((gpu.indices.cpu() != cpu.indices).sum())
+    gpu.frozen = torch.ones(n, dtype=torch.uint8, device=DEV)
+    before = gpu.indices.clone()
+    gpu.apply_update(g.to(DEV), 1e-3, 2e-3)
+    assert torch.equal(gpu.indices, before)
+
+
+def test_spec_verify_matches_cpu():
+    from innova_b200.inference.speculative import EXACT, REJECTION, verify
+    torch.manual_seed(3)
+    B, G, V = 32, 5, 1777
+    tl = torch.randn(B, G + 1, V) * 2
+    dl = tl[:, :G] + torch.randn(B, G, V) * 0.7
+    toks = torch.softmax(dl, -1).view(-1, V).multinomial(1).view(B, G)
+    u = torch.rand(B, G + 1)
+    n_c, x_c = verify(tl, toks, u, dl, 1.0, REJECTION)
+    n_g, x_g = verify(tl.to(DEV), toks.to(DEV), u, dl.to(DEV), 1.0, REJECTION)
+    assert torch.equal(n_g.cpu(), n_c)
+    assert (x_g.cpu() == x_c).float().mean() >= 0.9
+    assert 0 < float(n_c.float().mean()) < G      # the case exercises both accepts and rejections
+    n_c2, x_c2 = verify(tl, toks, u, None, 0.7, REJECTION)
+    n_g2, x_g2 = verify(tl.to(DEV), toks.to(DEV), u, None, 0.7, REJECTION)
+    assert torch.equal(n_g2.cpu(), n_c2) and (x_g2.cpu() == x_c2).float().mean() >= 0.9
+    toks_e = tl[:, :G].argmax(-1)
+    toks_e[::3, 2] = (toks_e[::3, 2] + 1) % V
+    n_c3, x_c3 = verify(tl, toks_e, u, None, 1.0, EXACT)
+    n_g3, x_g3 = verify(tl.to(DEV), toks_e.to(DEV), u, None, 1.0, EXACT)
+    assert torch.equal(n_g3.cpu(), n_c3) and torch.equal(x_g3.cpu(), x_c3)
+
+
+def test_device_codec_decode_all_formats(tmp_path):
+    from innova_b200.formats import oil
+    rng = np.random.default_rng(4)
+    path = str(tmp_path / "all.oil")
+    names = []
+    with oil.OILWriter(path) as w:
+        for fid in range(15):
+            for n in (256 * 5, 256 * 2 + 100, 40, 7):
+                data = (rng.standard_normal(n) * rng.uniform(0.01, 2.0)).astype(np.float32)
+                name = f"t{fid}_{n}"
+                w.add_tensor(name, data, fid)
+                names.append(name)
+    with oil.OILReader(path) as r:
+        for name in names:
+            host = r.read_tensor(name)
+            dev = r.read_tensor_device(name, DEV)
+            assert torch.equal(dev.cpu(), host), name
+            dev16 = r.read_tensor_device(name, DEV, torch.bfloat16)
+            assert torch.equal(dev16.cpu(), host.bfloat16()), name
+
+
+def test_device_codec_encode_is_byte_identical():
+    from innova_b200.formats import device_codec, oil
+    rng = np.random.default_rng(5)
+    nb = 64
+    data = (rng.standard_normal(nb * 256) * np.repeat(rng.uniform(1e-3, 3.0, nb), 256)).astype(np.float32)
+    data[256:512] = 0.0                    # a dead block
+    data[512:576] = 1.25                   # a constant group
+    w = torch.from_numpy(data).to(DEV)
+    for name in ("OIL32", "OIL16", "OIL8", "OIL4", "OIL2", "OIL8_GRP", "OIL4_GRP", "OIL2_GRP", "OIL1_GRP", "SPARK_Q0", "SPARK_Q0_GRP", "OIL1"):
+        pay, cb = device_codec.encode_blocks(w, name)
+        pay = pay.cpu().numpy()
+        for b in range(nb):
+            idx_ref, cb_ref = oil.encode_block(name, data[b * 256:(b + 1) * 256])
+            assert pay[b].tobytes() == bytes(idx_ref), (name, b)
+            if name == "OIL1":
+                assert cb[b].cpu().numpy().tobytes() == bytes(cb_ref), (name, b)
+
+
+def test_ternary_weight_gemm():
+    from innova_b200.ops.oil_linear import oil_linear, quantize_weight
+    torch.manual_seed(6)
+    for fmt in ("spark", "oil1"):
+        for M, N, K in ((1, 512, 1024), (16, 1000, 2048), (200, 384, 512)):
+            w = torch.randn(N, K, device=DEV) * 0.05
+            qw = quantize_weight(w, fmt)
+            x = (torch.randn(M, K, device=DEV)).bfloat16()
+            y = oil_linear(x, qw)
+            ref = x.float() @ qw.dequantize().float().t()
+            err = (y.float() - ref).abs().max() / ref.abs().max()
+            assert err < 1.5e-2, (fmt, M, N, K, float(err))
+
+
+def test_speculative_decoder_gpu_exact_equals_greedy():
+    from innova_b200.inference.generator import Generator
+    from innova_b200.inference.speculative import EXACT, SpeculativeDecoder
+    from innova_b200.models import DenseModel, PRESETS
+    cfg = PRESETS["tiny"]()
+    target = DenseModel(cfg, dtype=torch.bfloat16, device=DEV, seed=5)
+    draft = DenseModel(cfg, dtype=torch.bfloat16, device=DEV, seed=6)
+    prompt = [1, 5, 9, 2, 7, 3, 3, 8]
+    ref = Generator(target, kv_format="bf16").generate_tokens([prompt], 16)[0]
+    dec = SpeculativeDecoder(Generator(target, kv_format="bf16"), Generator(draft, kv_format="bf16"), gamma=3, mode=EXACT, adaptive=False)
+    assert dec.generate_tokens(prompt, 16) == ref

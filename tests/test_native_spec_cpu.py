@@ -1,0 +1,126 @@
+"""Train-in-format store, speculative decoding and tensor-op wrappers on the CPU paths."""
+import math
+
+import torch
+
+from innova_b200.training.native_oil import (FMT_OIL1, FMT_OIL4, FMT_OIL8, NativeOILTrainer, NativeOILWeightStore, NativeTrainConfig,
+                                             uniform_codebook)
+
+
+def sequential_update(w_idx, scales, fmts, grad, bs, lr_s, lr_w, cb4, cb8):
+    """The reference's loop (src/native_weight.cpp:287-335) in plain Python, for a handful of blocks."""
+    idx, sc = w_idx.clone(), scales.clone()
+    dz = {FMT_OIL1: 0.5, FMT_OIL4: 0.0625, FMT_OIL8: 0.00390625}
+
+    def cen(f, i):
+        return float(i) - 1.0 if f == FMT_OIL1 else float(cb4[i]) if f == FMT_OIL4 else float(cb8[i])
+
+    def near(cb, v):
+        best, bd = 0, abs(v - float(cb[0]))
+        for i in range(1, len(cb)):
+            d = abs(v - float(cb[i]))
+            if d < bd:
+                best, bd = i, d
+        return best
+    for i in range(idx.numel()):
+        b = i // bs
+        f = int(fmts[b])
+        s = float(sc[b])
+        cv = cen(f, int(idx[i]))
+        w, g = s * cv, float(grad[i])
+        sc[b] = max(float(sc[b]) - lr_s * g * cv / bs, 1e-10)
+        wv = w - lr_w * g
+        if abs(wv - w) > dz[f] * s:
+            norm = wv / float(sc[b])
+            idx[i] = (2 if norm > 0.5 else 0 if norm < -0.5 else 1) if f == FMT_OIL1 else near(cb4 if f == FMT_OIL4 else cb8, norm)
+    return idx, sc
+
+
+def test_store_convert_dequant_and_update_cpu():
+    torch.manual_seed(0)
+    n, bs = 6 * 128, 128
+    st = NativeOILWeightStore(n, bs)
+    w = torch.randn(n) * 0.05
+    sens = torch.rand(n)
+    st.initialize(w, sens, frac_oil8=0.34, frac_spark=0.34)
+    c = st.counts()
+    assert c["oil8"] == 2 and c["oil1"] == 2 and c["oil4"] == 2
+    dq = st.dequantize()
+    blocks8 = (st.formats == FMT_OIL8).nonzero().view(-1)
+    for b in blocks8.tolist():
+        assert (dq[b * bs:(b + 1) * bs] - w[b * bs:(b + 1) * bs]).abs().max() <= float(st.scales[b]) / 256 + 1e-7
+    g = torch.randn(n)
+    ref_idx, ref_sc = sequential_update(st.indices, st.scales, st.formats, g, bs, 1e-3, 2e-3, st.cb4, st.cb8)
+    st.apply_update(g, 1e-3, 2e-3)
+    assert torch.allclose(st.scales, ref_sc, rtol=1e-4)
+    assert (st.indices != ref_idx).float().mean() < 0.01
+    assert int(st.changed) > 0
+
+
+def test_native_trainer_two_phases():
+    from innova_b200.models import DenseModel, PRESETS
+    cfg = PRESETS["tiny"]()
+    model = DenseModel(cfg, dtype=torch.float32, device="cpu", seed=3)
+    tr = NativeOILTrainer(model, NativeTrainConfig(warmup_steps=3, frac_oil8=0.5, frac_spark=0.0, lr_scale=1e-3, lr_weight=1e-3))
+    torch.manual_seed(0)
+    x = torch.randint(0, cfg.vocab_size, (2, 17))
+    losses = [float(tr.train_step(x[:, :-1].contiguous(), x[:, 1:].contiguous())) for _ in range(8)]
+    assert tr.store is not None and tr.engine.master is None
+    m = tr.metrics()
+    assert m["phase"] == "native" and m["oil8"] > 0 and m["bits_per_weight"] < 9
+    assert all(math.isfinite(l) for l in losses) and losses[-1] < losses[0] + 0.5
+
+
+def test_spec_verify_cpu_semantics():
+    from innova_b200.inference.speculative import EXACT, REJECTION, Theorem13Result, verify
+    torch.manual_seed(1)
+    B, G, V = 4, 3, 50
+    tl = torch.randn(B, G + 1, V)
+    toks = tl[:, :G].argmax(-1)
+    toks[1, 1] = (toks[1, 1] + 1) % V
+    n, nxt = verify(tl, toks, torch.rand(B, G + 1), mode=EXACT)
+    assert n.tolist() == [3, 1, 3, 3]
+    assert int(nxt[1]) == int(tl[1, 1].argmax()) and int(nxt[0]) == int(tl[0, G].argmax())
+    # identical draft and target distributions: everything is accepted whatever the uniforms are
+    n2, _ = verify(tl, torch.randint(0, V, (B, G)), torch.rand(B, G + 1) * 0.999, draft_logits=tl[:, :G].clone(), mode=REJECTION)
+    assert n2.tolist() == [G] * B
+    # a draft token the target gives ~zero probability is rejected and replaced by a token with p_t > p_d
+    tl3 = torch.zeros(1, 2, V)
+    tl3[0, 0, 7] = 30.0
+    dl3 = torch.zeros(1, 1, V)
+    dl3[0, 0, 3] = 30.0
+    n3, nx3 = verify(tl3, torch.tensor([[3]]), torch.tensor([[0.5, 0.5]]), draft_logits=dl3)
+    assert int(n3) == 0 and int(nx3) == 7
+    r = Theorem13Result.compute(0.8, 0.1)
+    assert r.optimal_k == 3 and abs(r.speedup - (1 + 3 * 0.8) / (1 + 3 * 0.1)) < 1e-12
+    assert Theorem13Result.compute(0.05, 0.1).speedup == 1.0
+
+
+def test_speculative_decoder_exact_matches_greedy():
+    from innova_b200.inference.generator import Generator
+    from innova_b200.inference.speculative import EXACT, SpeculativeDecoder
+    from innova_b200.models import DenseModel, PRESETS
+    cfg = PRESETS["tiny"]()
+    target = DenseModel(cfg, dtype=torch.float32, device="cpu", seed=5)
+    draft = DenseModel(cfg, dtype=torch.float32, device="cpu", seed=6)
+    prompt = [1, 5, 9, 2, 7]
+    ref = Generator(target, kv_format="bf16").generate_tokens([prompt], 12)[0]
+    for d in (draft, target):
+        dec = SpeculativeDecoder(Generator(target, kv_format="bf16"), Generator(d, kv_format="bf16"), gamma=3, mode=EXACT, adaptive=False)
+        got = dec.generate_tokens(prompt, 12)
+        assert got == ref
+        assert dec.stats.rounds > 0
+    assert dec.stats.acceptance_rate == 1.0     # the target drafting for itself is always accepted
+
+
+def test_tensor_ops_cpu():
+    from innova_b200.ops import tensor_ops as T
+    x = torch.randn(4, 6, 5)
+    assert torch.allclose(T.unary(x, "scale", 2.0), 2 * x)
+    assert torch.equal(T.binary(x, torch.zeros_like(x), "div"), torch.zeros_like(x))
+    assert torch.allclose(T.softmax_rows(x).sum(-1), torch.ones(4, 6))
+    assert torch.equal(T.transpose2d(x[0]), x[0].t())
+    assert torch.allclose(T.reduce_axis(x, 1, "mean"), x.mean(1))
+    y = T.batch_norm(x, torch.ones(6), torch.zeros(6))
+    assert torch.allclose(y.mean(0), torch.zeros(6, 5), atol=1e-5)
+    assert torch.allclose(T.gemv(x[0], x[0, 0]), x[0] @ x[0, 0])

@@ -1,0 +1,141 @@
+"""Data parallelism, gradient compression, collectives API and the parameter server on gloo ranks (CPU)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _model():
+    torch.manual_seed(0)
+    return torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.LayerNorm(64), torch.nn.Linear(64, 16))
+
+
+def _grads(step, rank, shapes):
+    g = torch.Generator().manual_seed(77 * step + rank)
+    return [torch.randn(s, generator=g) for s in shapes]
+
+
+def _ddp_worker(rank, world, port, out, compression):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from innova_b200.parallel.ddp import DDPFlatEngine
+    model = _model()
+    if rank == 1:  # broadcast_model must overwrite this
+        for p in model.parameters():
+            p.data.add_(1.0)
+    eng = DDPFlatEngine(model, lr=1e-2, weight_decay=0.0, max_grad_norm=0.0, bucket_floats=1024, compression=compression, topk_ratio=0.25)
+    shapes = [p.shape for p in model.parameters()]
+    for step in range(3):
+        for p, g in zip(model.parameters(), _grads(step, rank, shapes)):
+            p.main_grad.copy_(g)
+        eng.step()
+    if rank == 0:
+        torch.save({"flat": eng.flat_param.clone(), "bytes": eng.bytes_sent}, out)
+    dist.destroy_process_group()
+
+
+def _single_reference(world, transform=None):
+    from innova_b200.training.flat_engine import FlatParamEngine
+    model = _model()
+    eng = FlatParamEngine(model, lr=1e-2, weight_decay=0.0, max_grad_norm=0.0)
+    shapes = [p.shape for p in model.parameters()]
+    for step in range(3):
+        per = [_grads(step, r, shapes) for r in range(world)]
+        for i, p in enumerate(model.parameters()):
+            p.main_grad.copy_(sum(g[i] for g in per) / world)
+        eng.step()
+    return eng.flat_param.clone()
+
+
+def test_ddp_two_ranks_matches_averaged_gradient(tmp_path):
+    out = str(tmp_path / "o.pt")
+    mp.spawn(_ddp_worker, args=(2, _free_port(), out, "none"), nprocs=2, join=True)
+    got = torch.load(out)
+    assert torch.allclose(got["flat"], _single_reference(2), atol=1e-6)
+
+
+@pytest.mark.parametrize("compression", ["int8", "topk"])
+def test_ddp_compressed_runs_and_stays_close(tmp_path, compression):
+    out = str(tmp_path / "o.pt")
+    mp.spawn(_ddp_worker, args=(2, _free_port(), out, compression), nprocs=2, join=True)
+    got = torch.load(out)
+    ref = _single_reference(2)
+    # Adam normalises the step, so even sparse gradients move every touched weight by ~lr; bound the drift
+    assert (got["flat"] - ref).abs().max() < 0.08
+    assert got["bytes"] > 0
+
+
+def test_topk_and_int8_cpu_ops():
+    from innova_b200.parallel import ddp
+    g = torch.randn(1000)
+    ref = g.clone()
+    vals, idx = ddp.topk_compress(g, 10)
+    top = torch.topk(ref.abs(), 10).indices
+    assert set(idx.tolist()) == set(top.tolist())
+    assert torch.equal(vals, ref[idx]) and int((g != 0).sum()) == 10
+    z = torch.zeros(1000)
+    ddp.topk_scatter(z, vals, idx)
+    assert torch.equal(z, g)
+    q, s = ddp.int8_compress(ref)
+    assert q.abs().max() == 127 and abs(float(s) - float(ref.abs().max()) / 127) < 1e-7
+    out = torch.empty(1000)
+    ddp.int8_sum_dequant(torch.stack([q, q]), torch.cat([s, s]), out, 0.5)
+    assert (out - ref).abs().max() <= float(s) * 0.5 + 1e-6
+    qz, sz = ddp.int8_compress(torch.zeros(8))
+    assert float(sz) == 1.0 and int(qz.abs().sum()) == 0
+
+
+def _coll_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from innova_b200.parallel.collectives import Communicator, DistributedContext, ParameterServer, RingAllReduce
+    comm = Communicator(device="cpu")
+    x = torch.arange(16, dtype=torch.float32) + 100 * rank
+    res = {}
+    res["ar"] = comm.all_reduce(x.clone())
+    res["avg"] = RingAllReduce(comm=comm).allreduce(x.clone(), "avg")
+    res["max"] = RingAllReduce(comm=comm).allreduce(x.clone(), "max")
+    res["rs"] = comm.reduce_scatter(x.clone())
+    res["ag"] = comm.all_gather(x[:4].clone())
+    res["a2a"] = comm.all_to_all(x.clone())
+    ctx = DistributedContext(comm=comm)
+    b = torch.full((3,), float(rank))
+    ctx.broadcast(b, 1)
+    res["bc"] = b
+    ctx.barrier()
+    params = {"w": torch.nn.Parameter(torch.ones(4)), "v": torch.nn.Parameter(torch.ones(4))}
+    ps = ParameterServer(params, lr=0.1, momentum=0.0)
+    ps.push("w", torch.full((4,), float(rank + 1)))
+    ps.pull("w")
+    res["ps_w"] = params["w"].data.clone()
+    ps.push("w", torch.ones(4), version=ps.version["w"] - 1)        # one version stale -> half weight
+    ps.pull("w")
+    res["ps_w2"] = params["w"].data.clone()
+    torch.save(res, out + f".{rank}")
+    dist.destroy_process_group()
+
+
+def test_collectives_api_on_gloo(tmp_path):
+    out = str(tmp_path / "c")
+    mp.spawn(_coll_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    r0, r1 = torch.load(out + ".0"), torch.load(out + ".1")
+    base = torch.arange(16, dtype=torch.float32)
+    assert torch.equal(r0["ar"], 2 * base + 100) and torch.equal(r1["ar"], r0["ar"])
+    assert torch.equal(r0["avg"], base + 50) and torch.equal(r0["max"], base + 100)
+    assert torch.equal(r0["rs"], (2 * base + 100)[:8]) and torch.equal(r1["rs"], (2 * base + 100)[8:])
+    assert torch.equal(r0["ag"], torch.cat([base[:4], base[:4] + 100]))
+    assert torch.equal(r0["a2a"], torch.cat([base[:8], base[:8] + 100])) and torch.equal(r1["a2a"], torch.cat([base[8:], base[8:] + 100]))
+    assert torch.equal(r0["bc"], torch.ones(3)) and torch.equal(r1["bc"], torch.ones(3))
+    assert torch.allclose(r0["ps_w"], torch.full((4,), 1 - 0.1 * 3.0)) and torch.equal(r0["ps_w"], r1["ps_w"])
+    assert torch.allclose(r0["ps_w2"], r0["ps_w"] - 0.1 * (0.5 * 2))
