@@ -32,6 +32,24 @@ struct GemmParams {
   int group_rows_b;
   int group_stride_bias;
   long group_stride_c;
+  // Collectives fused into the single-CTA kernel (tensor / sequence parallel layers, sharded weights).
+  // All-gather -> GEMM: the gathered operand (ag_operand 0: A rows, 1: B rows) consists of ag_world shards of
+  // ag_shard_rows rows. This rank's shard is already in place in the local full-size buffer the tensor map
+  // covers (ag_dst); the first ag_copy_ctas CTAs of the grid pull the other shards out of the peers' buffers
+  // (ag_src[r], same layout) tile by tile and publish ag_flags[tile] = ag_epoch; the GEMM CTAs visit tiles
+  // local shard first, then in the order the copies arrive, and wait (bounded) on a tile's flag before its
+  // first TMA load. Each remote tile crosses NVLink once and is then read from local memory / L2.
+  int ag_world = 0, ag_rank = 0, ag_operand = 0, ag_shard_rows = 0, ag_copy_ctas = 0, ag_ld = 0;
+  const void* ag_src[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  void* ag_dst = nullptr;
+  uint32_t* ag_flags = nullptr;
+  uint32_t ag_epoch = 0;
+  // GEMM -> reduce-scatter: C's rows are rs_world shards of rs_shard_rows rows and shard r is owned by rank r.
+  // The fp32 epilogue adds (red.global.add) each tile into the owner's buffer rs_dst[r] ([rs_shard_rows, ldc]),
+  // over NVLink for remote owners; every rank's partial products meet there. Owners are visited starting
+  // after this rank so the ranks never all write to the same destination.
+  int rs_world = 0, rs_rank = 0, rs_shard_rows = 0;
+  float* rs_dst[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 
 // 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows of `ld` elements; 128B swizzle.

@@ -36,6 +36,7 @@ struct WorkUnit {
   int bias_off;
   long c_off;      // element offset of this unit's C (grouped mode 2)
   bool skip;
+  int ag_tile;     // tile index of the gathered operand this unit reads, -1 when it is local or nothing is gathered
 };
 __device__ __forceinline__ WorkUnit decode_work(int w, const GemmParams& p, int m_tiles, int n_tiles, int kb_total, int kb_per_split) {
   WorkUnit u;
@@ -43,10 +44,29 @@ __device__ __forceinline__ WorkUnit decode_work(int w, const GemmParams& p, int 
   u.bias_off = 0;
   u.c_off = 0;
   u.skip = false;
-  const int n_blk = w % n_tiles;
-  int rest = w / n_tiles;
-  const int m_blk = rest % m_tiles;
-  rest /= m_tiles;
+  u.ag_tile = -1;
+  int n_blk, m_blk, rest;
+  if (p.ag_world > 1 && p.ag_operand == 1) {  // B is gathered: walk all m-tiles of an n-tile before the next n-tile
+    m_blk = w % m_tiles;
+    rest = w / m_tiles;
+    n_blk = rest % n_tiles;
+    rest /= n_tiles;
+    const int per = p.ag_shard_rows / BN;
+    n_blk = (n_blk + p.ag_rank * per) % n_tiles;
+    if (n_blk / per != p.ag_rank) u.ag_tile = n_blk;
+  } else {
+    n_blk = w % n_tiles;
+    rest = w / n_tiles;
+    m_blk = rest % m_tiles;
+    rest /= m_tiles;
+    if (p.ag_world > 1) {
+      const int per = p.ag_shard_rows / BM;
+      m_blk = (m_blk + p.ag_rank * per) % m_tiles;
+      if (m_blk / per != p.ag_rank) u.ag_tile = m_blk;
+    } else if (p.rs_world > 1) {
+      m_blk = (m_blk + (p.rs_rank + 1) * (p.rs_shard_rows / BM)) % m_tiles;
+    }
+  }
   u.m0 = m_blk * BM;
   u.n0 = n_blk * BN;
   if (p.group_mode == 2) {
@@ -71,6 +91,68 @@ __device__ __forceinline__ WorkUnit decode_work(int w, const GemmParams& p, int 
   return u;
 }
 
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded wait for a gathered tile; afterwards the async proxy (TMA) may read what the copier's ordinary stores wrote.
+__device__ __forceinline__ bool ag_wait_tile(const GemmParams& p, int tile, volatile int* abort_flag) {
+  const uint64_t t0 = globaltimer_ns();
+  while (ld_acquire_gpu_u32(p.ag_flags + tile) != p.ag_epoch) {
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > INV_WAIT_LIMIT_NS) {
+      *abort_flag = 1;
+      if (p.status) atomicExch(p.status, ERR_WAIT_PEER);
+      return false;
+    }
+    __nanosleep(100);
+  }
+  asm volatile("fence.proxy.async;" ::: "memory");
+  return true;
+}
+// Copier CTAs: remote shards, nearest peer first, one tile (BM or BN rows of K elements) per step.
+__device__ void ag_copier(const GemmParams& p) {
+  const int tile_rows = p.ag_operand == 1 ? BN : BM;
+  const int per = p.ag_shard_rows / tile_rows;
+  const int remote_tiles = (p.ag_world - 1) * per;
+  const int row_vecs = (p.K * 2 + 15) / 16;  // 16-byte vectors per row
+  const size_t ld_bytes = (size_t)p.ag_ld * 2;
+  for (int c = blockIdx.x; c < remote_tiles; c += p.ag_copy_ctas) {
+    const int r = (p.ag_rank + 1 + c / per) % p.ag_world;
+    const int tile = r * per + c % per;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(p.ag_src[r]) + (size_t)tile * tile_rows * ld_bytes;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(p.ag_dst) + (size_t)tile * tile_rows * ld_bytes;
+    const int total = tile_rows * row_vecs;
+    int i = threadIdx.x;
+    for (; i + 3 * (int)blockDim.x < total; i += 4 * blockDim.x) {  // four loads in flight per thread
+      uint4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = i + j * blockDim.x;
+        v[j] = *reinterpret_cast<const uint4*>(src + (size_t)(e / row_vecs) * ld_bytes + (size_t)(e % row_vecs) * 16);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = i + j * blockDim.x;
+        *reinterpret_cast<uint4*>(dst + (size_t)(e / row_vecs) * ld_bytes + (size_t)(e % row_vecs) * 16) = v[j];
+      }
+    }
+    for (; i < total; i += blockDim.x)
+      *reinterpret_cast<uint4*>(dst + (size_t)(i / row_vecs) * ld_bytes + (size_t)(i % row_vecs) * 16) =
+          *reinterpret_cast<const uint4*>(src + (size_t)(i / row_vecs) * ld_bytes + (size_t)(i % row_vecs) * 16);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      asm volatile("fence.proxy.async;" ::: "memory");
+      st_release_gpu_u32(p.ag_flags + tile, p.ag_epoch);
+    }
+  }
+}
+
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
@@ -87,6 +169,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // with a fused all-gather the first CTAs of the grid only copy; they own no barriers and no TMEM
+  const int n_copy = p.ag_world > 1 ? p.ag_copy_ctas : 0;
+  if ((int)blockIdx.x < n_copy) {
+    ag_copier(p);
+    return;
+  }
+  const int bid = blockIdx.x - n_copy, gdim = gridDim.x - n_copy;
 
   const int m_tiles = (p.M + BM - 1) / BM;
   const int n_tiles = (p.N + BN - 1) / BN;
@@ -121,10 +210,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       int it = 0;
-      for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+      for (int w = bid; w < total_work; w += gdim) {
         WorkUnit u = decode_work(w, p, m_tiles, n_tiles, kb_total, kb_per_split);
         if (u.skip) continue;
         bool ok = true;
+        if (u.ag_tile >= 0 && !ag_wait_tile(p, u.ag_tile, abort_flag)) break;
         for (int kb = u.kb_begin; kb < u.kb_end; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -164,7 +254,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t a_kstep = A_MN ? 2048u : 32u;
       const uint32_t b_kstep = B_MN ? 2048u : 32u;
       int it = 0, tile_i = 0;
-      for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+      for (int w = bid; w < total_work; w += gdim) {
         WorkUnit u = decode_work(w, p, m_tiles, n_tiles, kb_total, kb_per_split);
         if (u.skip) continue;
         const int acc = tile_i & 1;
@@ -199,7 +289,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
     int tile_i = 0;
-    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+    for (int w = bid; w < total_work; w += gdim) {
       WorkUnit u = decode_work(w, p, m_tiles, n_tiles, kb_total, kb_per_split);
       if (u.skip) continue;
       GemmParams pe = p;  // this unit's view of the outputs (grouped modes shift bias / C)
@@ -211,8 +301,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t acc_ph = (tile_i >> 1) & 1;
       if (!mbar_wait_warp(&tmem_full[acc], acc_ph, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
-      const int row = u.m0 + q * 32 + lane;
+      int row = u.m0 + q * 32 + lane;
       const bool row_ok = row < p.M;
+      if (p.rs_world > 1) {  // this tile's rows belong to one owner: add into its buffer at the shard-relative row
+        const int owner = u.m0 / p.rs_shard_rows;
+        pe.C = p.rs_dst[owner];
+        row -= owner * p.rs_shard_rows;
+      }
       const uint32_t t_row = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
 #pragma unroll 1
       for (int c = half * 4; c < half * 4 + 4; c += 2) {
@@ -374,6 +469,89 @@ extern "C" int inv_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   if (a_mn && !b_mn) return launch_gemm<true, false>(ta, tb, p, grid, st);
   if (!a_mn && b_mn) return launch_gemm<false, true>(ta, tb, p, grid, st);
   return launch_gemm<false, false>(ta, tb, p, grid, st);
+}
+
+
+static void fill_plain(GemmParams& p, int M, int N, int K, void* C, int ldc, int c_f32, const void* bias, const void* aux_in, int ld_aux,
+                       void* aux_out, int epilogue, float alpha, int* status) {
+  p.M = M; p.N = N; p.K = K; p.split_k = 1;
+  p.C = C; p.ldc = ldc; p.c_f32 = c_f32;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.aux_in = reinterpret_cast<const __nv_bfloat16*>(aux_in);
+  p.ld_aux = ld_aux;
+  p.aux_out = reinterpret_cast<__nv_bfloat16*>(aux_out);
+  p.epilogue = epilogue; p.alpha = alpha; p.status = status; p.swap_lbo_sbo = 0;
+  p.group_mode = 0; p.num_groups = 1; p.tile_expert = nullptr; p.group_offsets = nullptr; p.group_rows_b = 0;
+  p.group_stride_bias = 0; p.group_stride_c = 0;
+}
+
+// All-gather fused into a GEMM: C[M, N] = A[M, K] * B[N, K]^T where the gathered operand (operand 0: A, 1: B)
+// is sharded by rows over W ranks. `peer_bufs[r]` is rank r's full-size buffer of that operand ([W * shard_rows, ld]
+// bf16) which holds at least rank r's own shard; this rank's buffer is peer_bufs[rank] and receives the other
+// shards. flags: >= (W * shard_rows / tile) device words on this GPU, epoch: a value not used on them before.
+// All ranks must have written their shard before the launch and must not overwrite it before every rank's
+// kernel has finished (the caller brackets the call with barriers).
+extern "C" int inv_gemm_ag_bf16(const uint64_t* peer_bufs, int W, int rank, int operand, int shard_rows, int ld_gathered, const void* other,
+                                int ld_other, void* C, int ldc, int M, int N, int K, int epilogue, const void* bias, const void* aux_in,
+                                int ld_aux, void* aux_out, int c_f32, uint32_t* flags, uint32_t epoch, int copy_ctas, int* status,
+                                void* stream) {
+  if (W < 1 || W > 8 || rank < 0 || rank >= W || (operand != 0 && operand != 1)) return -ERR_BAD_ARG;
+  const int tile_rows = operand ? BN : BM;
+  if (shard_rows % tile_rows || (operand ? N : M) != W * shard_rows) return -ERR_BAD_ARG;
+  if ((ld_gathered % 8) || (ld_other % 8) || (ldc % (c_f32 ? 4 : 8)) || (N % 8) || (K % 8)) return -ERR_BAD_ARG;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  GemmParams p;
+  fill_plain(p, M, N, K, C, ldc, c_f32, bias, aux_in, ld_aux, aux_out, epilogue, 1.0f, status);
+  if (epilogue == EPI_ATOMIC) return -ERR_BAD_ARG;
+  void* local = reinterpret_cast<void*>(peer_bufs[rank]);
+  const void* A = operand ? other : local;
+  const void* B = operand ? local : other;
+  CUtensorMap ta, tb;
+  int rc;
+  if ((rc = make_tmap_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)(operand ? ld_other : ld_gathered), BK, BM))) return rc;
+  if ((rc = make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)(operand ? ld_gathered : ld_other), BK, BN))) return rc;
+  p.ag_world = W; p.ag_rank = rank; p.ag_operand = operand; p.ag_shard_rows = shard_rows; p.ag_ld = ld_gathered;
+  for (int r = 0; r < W; ++r) p.ag_src[r] = reinterpret_cast<const void*>(peer_bufs[r]);
+  p.ag_dst = local; p.ag_flags = flags; p.ag_epoch = epoch;
+  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+  const long total = (long)m_tiles * n_tiles;
+  if (W == 1) copy_ctas = 0;
+  else if (copy_ctas < 1) copy_ctas = 8;
+  if (copy_ctas > g_num_sms / 4) copy_ctas = g_num_sms / 4;
+  p.ag_copy_ctas = copy_ctas;
+  long gemm_ctas = total < g_num_sms - copy_ctas ? total : g_num_sms - copy_ctas;
+  // the whole grid must be resident at once (the GEMM CTAs wait for the copier CTAs): one CTA per SM
+  return launch_gemm<false, false>(ta, tb, p, (int)gemm_ctas + copy_ctas, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// GEMM fused with a reduce-scatter: every rank computes the full [M, N] partial product of its K-slice and adds
+// row shard r (M / W rows) into rank r's fp32 buffer peer_out[r] ([M / W, ldc]), which must be zero (or hold a
+// value to add to) before any rank starts.
+extern "C" int inv_gemm_rs_bf16(const void* A, int lda, const void* B, int ldb, const uint64_t* peer_out, int W, int rank, int ldc, int M,
+                                int N, int K, float alpha, int* status, void* stream) {
+  if (W < 1 || W > 8 || rank < 0 || rank >= W || M % W || (M / W) % BM) return -ERR_BAD_ARG;
+  if ((lda % 8) || (ldb % 8) || (ldc % 4) || (N % 8)) return -ERR_BAD_ARG;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  GemmParams p;
+  fill_plain(p, M, N, K, reinterpret_cast<void*>(peer_out[rank]), ldc, 1, nullptr, nullptr, 0, nullptr, EPI_ATOMIC, alpha, status);
+  CUtensorMap ta, tb;
+  int rc;
+  if ((rc = make_tmap_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM))) return rc;
+  if ((rc = make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, BN))) return rc;
+  p.rs_world = W; p.rs_rank = rank; p.rs_shard_rows = M / W;
+  for (int r = 0; r < W; ++r) p.rs_dst[r] = reinterpret_cast<float*>(peer_out[r]);
+  const long total = (long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  return launch_gemm<false, false>(ta, tb, p, (int)(total < g_num_sms ? total : g_num_sms), reinterpret_cast<cudaStream_t>(stream));
 }
 
 
