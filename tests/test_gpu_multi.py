@@ -161,3 +161,59 @@ def test_native_collectives_match_nccl(tmp_path):
             for k in ("ar", "avg", "rs", "ag", "a2a"):
                 assert torch.allclose(r[algo][k], ref[k], atol=1e-5), (rank, algo, k)
         assert r["big_err"] < 1e-4 and r["ddp_diff"] < 1e-5
+
+
+def _fused_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from innova_b200.ops import runtime as rt
+    from innova_b200.parallel.fused import FusedGemmComm
+    comm = FusedGemmComm(device=dev)
+    assert comm.native
+    g = torch.Generator().manual_seed(7)
+    S, K, N = 512, 1024, 768                 # token rows per rank, features
+    x_all = (torch.randn(world * S, K, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    bias = (torch.randn(N, generator=g) * 0.1).bfloat16()
+    res = {}
+    # all-gather of the activations fused into the GEMM, run twice (buffer reuse) with and without bias + GELU
+    xs = x_all[rank * S:(rank + 1) * S].to(dev)
+    for it in range(2):
+        y = comm.all_gather_gemm(xs, w.to(dev))
+    ref = x_all.float() @ w.float().t()
+    res["ag"] = float((y.float().cpu() - ref).abs().max() / ref.abs().max())
+    y2 = comm.all_gather_gemm(xs, w.to(dev), bias.to(dev), gelu=True)
+    ref2 = torch.nn.functional.gelu(ref + bias.float(), approximate="tanh")
+    res["ag_gelu"] = float((y2.float().cpu() - ref2).abs().max() / ref2.abs().max())
+    # weight sharded by rows, gathered inside the GEMM
+    Nw = 512 * world
+    w_all = (torch.randn(Nw, K, generator=g) * 0.05).bfloat16()
+    xin = (torch.randn(384, K, generator=g) * 0.5).bfloat16()
+    y3 = comm.gather_weight_gemm(xin.to(dev), w_all[rank * 512:(rank + 1) * 512].to(dev))
+    ref3 = xin.float() @ w_all.float().t()
+    res["agw"] = float((y3.float().cpu() - ref3).abs().max() / ref3.abs().max())
+    # GEMM + reduce-scatter: every rank owns a slice of the reduction dimension
+    Kl = K // world
+    xr = x_all[:, rank * Kl:(rank + 1) * Kl].contiguous().to(dev)
+    wr = w[:, rank * Kl:(rank + 1) * Kl].contiguous().to(dev)
+    for it in range(2):
+        y4 = comm.gemm_reduce_scatter(xr, wr)
+    Sr = x_all.shape[0] // world
+    res["rs"] = float((y4.float().cpu() - ref[rank * Sr:(rank + 1) * Sr]).abs().max() / ref.abs().max())
+    rt.check_status()
+    torch.save(res, out + f".{rank}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_fused_gemm_collectives(tmp_path):
+    _need_gpus(2)
+    world = 2
+    out = str(tmp_path / "fused")
+    mp.spawn(_fused_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    for rank in range(world):
+        r = torch.load(out + f".{rank}")
+        for k in ("ag", "ag_gelu", "agw", "rs"):
+            assert r[k] < 1.5e-2, (rank, k, r[k])

@@ -139,3 +139,47 @@ def test_collectives_api_on_gloo(tmp_path):
     assert torch.equal(r0["bc"], torch.ones(3)) and torch.equal(r1["bc"], torch.ones(3))
     assert torch.allclose(r0["ps_w"], torch.full((4,), 1 - 0.1 * 3.0)) and torch.equal(r0["ps_w"], r1["ps_w"])
     assert torch.allclose(r0["ps_w2"], r0["ps_w"] - 0.1 * (0.5 * 2))
+
+
+def _tp_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from innova_b200.parallel.fused import FusedGemmComm
+    from innova_b200.parallel.tensor_parallel import ColumnParallelLinear, HeadPartitioner, RowParallelLinear, SequenceParallel
+    torch.manual_seed(0)
+    T, D, F = 8, 16, 32
+    w1, b1, w2, b2 = torch.randn(F, D) * 0.2, torch.randn(F) * 0.1, torch.randn(D, F) * 0.2, torch.randn(D) * 0.1
+    x = torch.randn(T, D)
+    comm = FusedGemmComm(device="cpu")
+    col = ColumnParallelLinear(D, F, comm, dtype=torch.float32, full_weight=w1, full_bias=b1)
+    row = RowParallelLinear(F, D, comm, dtype=torch.float32, full_weight=w2, full_bias=b2)
+    sp = SequenceParallel()
+    xs = sp.scatter(x, 0).clone().requires_grad_(True)
+    y = row(torch.tanh(col(xs)))
+    y.sum().backward()
+    full_y = sp.gather(y.detach(), 0)
+    res = {"y": full_y, "dx": sp.gather(xs.grad, 0), "gw1": col.weight.grad, "gw2": row.weight.grad, "gb1": col.bias.grad}
+    hp = HeadPartitioner(8, 2, 4)
+    res["kv"] = [list(hp.kv_heads(r)) for r in range(4)]
+    torch.save(res, out + f".{rank}")
+    dist.destroy_process_group()
+
+
+def test_tensor_parallel_layers_match_dense(tmp_path):
+    out = str(tmp_path / "tp")
+    mp.spawn(_tp_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    torch.manual_seed(0)
+    T, D, F = 8, 16, 32
+    w1, b1, w2, b2 = torch.randn(F, D) * 0.2, torch.randn(F) * 0.1, torch.randn(D, F) * 0.2, torch.randn(D) * 0.1
+    x = torch.randn(T, D).requires_grad_(True)
+    w1p, w2p, b1p = w1.clone().requires_grad_(True), w2.clone().requires_grad_(True), b1.clone().requires_grad_(True)
+    y = torch.tanh(x @ w1p.t() + b1p) @ w2p.t() + b2
+    y.sum().backward()
+    for rank in range(2):
+        r = torch.load(out + f".{rank}")
+        assert torch.allclose(r["y"], y.detach(), atol=1e-5)
+        assert torch.allclose(r["dx"], x.grad, atol=1e-5)
+        assert torch.allclose(r["gw1"], w1p.grad[rank * 16:(rank + 1) * 16], atol=1e-5)
+        assert torch.allclose(r["gw2"], w2p.grad[:, rank * 16:(rank + 1) * 16], atol=1e-5)
+        assert torch.allclose(r["gb1"], b1p.grad[rank * 16:(rank + 1) * 16], atol=1e-5)
+        assert r["kv"] == [[0], [0], [1], [1]]
