@@ -127,9 +127,14 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& p, int row
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             if (col0 + g * 4 < p.N) {
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + g * 4), "f"(v[g * 4]),
-                           "f"(v[g * 4 + 1]), "f"(v[g * 4 + 2]), "f"(v[g * 4 + 3])
-                           : "memory");
+              if (p.rs_world > 1)  // the destination may be another GPU's memory: system scope
+                asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + g * 4), "f"(v[g * 4]),
+                             "f"(v[g * 4 + 1]), "f"(v[g * 4 + 2]), "f"(v[g * 4 + 3])
+                             : "memory");
+              else
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(cp + g * 4), "f"(v[g * 4]),
+                             "f"(v[g * 4 + 1]), "f"(v[g * 4 + 2]), "f"(v[g * 4 + 3])
+                             : "memory");
             }
           }
         } else {

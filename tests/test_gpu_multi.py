@@ -217,3 +217,73 @@ def test_fused_gemm_collectives(tmp_path):
         r = torch.load(out + f".{rank}")
         for k in ("ag", "ag_gelu", "agw", "rs"):
             assert r[k] < 1.5e-2, (rank, k, r[k])
+
+
+def _ep_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from innova_b200.ops import runtime as rt
+    from innova_b200.parallel.expert_parallel import ExpertParallelMoE
+    g = torch.Generator().manual_seed(11)
+    E, D, Fh, T = 8, 256, 512, 300
+    router = torch.randn(E, D, generator=g) * D ** -0.5
+    w_gu = torch.randn(E, 2 * Fh, D, generator=g) * D ** -0.5
+    w_down = torch.randn(E, D, Fh, generator=g) * Fh ** -0.5
+    x_all = torch.randn(world * T, D, generator=g)
+    res_all = torch.randn(world * T, D, generator=g)
+    m = ExpertParallelMoE(D, Fh, E, top_k=2, max_tokens=T, device=dev, full_router=router, full_w_gu=w_gu, full_w_down=w_down, lb_coef=0.0,
+                          z_coef=0.0)
+    assert m.ep is not None
+    outs = {}
+    for it in range(2):      # second pass reuses the staging buffers
+        x = x_all[rank * T:(rank + 1) * T].to(dev).bfloat16().requires_grad_(True)
+        res = res_all[rank * T:(rank + 1) * T].to(dev).bfloat16()
+        for p in m.parameters():
+            p.grad = None
+        y, aux, counts = m(x, res)
+        (y.float() * torch.linspace(-1, 1, D, device=dev)).sum().backward()
+    rt.check_status()
+    outs = {"y": y.float().cpu(), "dx": x.grad.float().cpu(), "gw_gu": m.w_gu.grad.float().cpu(), "gw_down": m.w_down.grad.float().cpu(),
+            "gr": m.router.grad.float().cpu(), "counts": counts.cpu()}
+    torch.save(outs, out + f".{rank}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_dispatch_combine(tmp_path):
+    _need_gpus(2)
+    from innova_b200.ops.moe import moe_ffn_reference
+    world = 2
+    out = str(tmp_path / "ep")
+    mp.spawn(_ep_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    g = torch.Generator().manual_seed(11)
+    E, D, Fh, T = 8, 256, 512, 300
+    router = (torch.randn(E, D, generator=g) * D ** -0.5).bfloat16().float().requires_grad_(True)
+    w_gu = (torch.randn(E, 2 * Fh, D, generator=g) * D ** -0.5).bfloat16().float().requires_grad_(True)
+    w_down = (torch.randn(E, D, Fh, generator=g) * Fh ** -0.5).bfloat16().float().requires_grad_(True)
+    x_all = torch.randn(world * T, D, generator=g).bfloat16().float()
+    res_all = torch.randn(world * T, D, generator=g).bfloat16().float()
+    epr = E // world
+
+    def rel(a, b):
+        return float((a - b).norm() / (b.norm() + 1e-12))
+    gw_gu, gw_down = torch.zeros_like(w_gu), torch.zeros_like(w_down)
+    refs = []
+    for rank in range(world):            # each rank's tokens are routed independently (local router statistics)
+        x = x_all[rank * T:(rank + 1) * T].clone().requires_grad_(True)
+        y, _, counts = moe_ffn_reference(x, router, w_gu, w_down, res_all[rank * T:(rank + 1) * T], top_k=2)
+        for p in (router, w_gu, w_down):
+            p.grad = None
+        (y * torch.linspace(-1, 1, D)).sum().backward()
+        gw_gu += w_gu.grad
+        gw_down += w_down.grad
+        refs.append((y.detach(), x.grad, router.grad.clone(), counts))
+    for rank in range(world):
+        r = torch.load(out + f".{rank}")
+        y, dx, gr, counts = refs[rank]
+        assert torch.equal(r["counts"], counts)
+        assert rel(r["y"], y) < 2e-2 and rel(r["dx"], dx) < 3e-2 and rel(r["gr"], gr) < 5e-2
+        assert rel(r["gw_gu"], gw_gu[rank * epr:(rank + 1) * epr]) < 3e-2
+        assert rel(r["gw_down"], gw_down[rank * epr:(rank + 1) * epr]) < 3e-2

@@ -183,3 +183,91 @@ def test_tensor_parallel_layers_match_dense(tmp_path):
         assert torch.allclose(r["gw2"], w2p.grad[:, rank * 16:(rank + 1) * 16], atol=1e-5)
         assert torch.allclose(r["gb1"], b1p.grad[rank * 16:(rank + 1) * 16], atol=1e-5)
         assert r["kv"] == [[0], [0], [1], [1]]
+
+
+def _ep_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from innova_b200.parallel.expert_parallel import ExpertParallelMoE
+    g = torch.Generator().manual_seed(3)
+    E, D, Fh, T = 4, 16, 24, 10
+    router, w_gu, w_down = torch.randn(E, D, generator=g), torch.randn(E, 2 * Fh, D, generator=g) * 0.3, torch.randn(E, D, Fh, generator=g) * 0.3
+    x_all = torch.randn(world * T, D, generator=g)
+    m = ExpertParallelMoE(D, Fh, E, top_k=2, dtype=torch.float32, full_router=router, full_w_gu=w_gu, full_w_down=w_down, lb_coef=0.0, z_coef=0.0)
+    x = x_all[rank * T:(rank + 1) * T].clone().requires_grad_(True)
+    y, aux, counts = m(x)
+    (y * torch.arange(1, D + 1)).sum().backward()
+    m.sync_router_grad()
+    torch.save({"y": y.detach(), "dx": x.grad, "gw": m.w_gu.grad, "gr": m.router.grad, "counts": counts}, out + f".{rank}")
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_fallback_matches_single_process(tmp_path):
+    from innova_b200.ops.moe import moe_ffn_reference
+    out = str(tmp_path / "ep")
+    world = 2
+    mp.spawn(_ep_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    g = torch.Generator().manual_seed(3)
+    E, D, Fh, T = 4, 16, 24, 10
+    router, w_gu, w_down = torch.randn(E, D, generator=g), torch.randn(E, 2 * Fh, D, generator=g) * 0.3, torch.randn(E, D, Fh, generator=g) * 0.3
+    x_all = torch.randn(world * T, D, generator=g).requires_grad_(True)
+    router, w_gu = router.requires_grad_(True), w_gu.requires_grad_(True)
+    y, _, counts = moe_ffn_reference(x_all, router, w_gu, w_down, top_k=2)
+    (y * torch.arange(1, D + 1)).sum().backward()
+    for rank in range(world):
+        r = torch.load(out + f".{rank}")
+        assert torch.allclose(r["y"], y.detach()[rank * T:(rank + 1) * T], atol=1e-4)
+        assert torch.allclose(r["dx"], x_all.grad[rank * T:(rank + 1) * T], atol=1e-4)
+        assert torch.allclose(r["gw"], w_gu.grad[rank * 2:(rank + 1) * 2], atol=1e-4)
+        assert torch.allclose(r["gr"], router.grad / world, atol=1e-4)
+        assert torch.equal(r["counts"], counts)
+
+
+def _pp_worker(rank, world, port, out, schedule):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from innova_b200.models import DenseModel, PRESETS
+    from innova_b200.parallel.pipeline import DenseStage, PipelineParallel
+    cfg = PRESETS["tiny"]()
+    model = DenseModel(cfg, dtype=torch.float32, device="cpu", seed=9)
+    stage = DenseStage(model, rank, world)
+    torch.manual_seed(0)
+    ids = torch.randint(0, cfg.vocab_size, (8, 12))
+    labels = torch.roll(ids, -1, 1)
+    pp = PipelineParallel(stage, num_micro_batches=4, schedule=schedule, act_shape=[2, 12, cfg.hidden_size], act_dtype=torch.float32, device="cpu")
+    loss = pp.train_step(ids if rank == 0 else None, labels if rank == world - 1 else None)
+    grads = {n: p.grad.clone() for n, p in stage.named_parameters() if p.grad is not None}
+    torch.save({"loss": loss, "grads": grads}, out + f".{rank}")
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("schedule", ["gpipe", "1f1b"])
+def test_pipeline_two_stages_matches_full_model(tmp_path, schedule):
+    from innova_b200.models import DenseModel, PRESETS
+    from innova_b200.parallel.pipeline import stage_bounds
+    out = str(tmp_path / "pp")
+    mp.spawn(_pp_worker, args=(2, _free_port(), out, schedule), nprocs=2, join=True)
+    cfg = PRESETS["tiny"]()
+    model = DenseModel(cfg, dtype=torch.float32, device="cpu", seed=9)
+    torch.manual_seed(0)
+    ids = torch.randint(0, cfg.vocab_size, (8, 12))
+    labels = torch.roll(ids, -1, 1)
+    losses = []
+    for i, l in zip(ids.chunk(4), labels.chunk(4)):
+        loss = model(i, l)
+        (loss / 4).backward()
+        losses.append(loss.detach())
+    r0, r1 = torch.load(out + ".0"), torch.load(out + ".1")
+    assert r0["loss"] is None and abs(float(r1["loss"]) - float(torch.stack(losses).mean())) < 1e-5
+    full = dict(model.named_parameters())
+    lo1, _ = stage_bounds(cfg.num_layers, 2, 1)
+    checked = 0
+    for r, base in ((r0, 0), (r1, lo1)):
+        for n, g in r["grads"].items():
+            if n.startswith("layers."):
+                parts = n.split(".")
+                n = ".".join(["layers", str(int(parts[1]) + base)] + parts[2:])
+            if n in full and full[n].grad is not None:
+                assert torch.allclose(g, full[n].grad, atol=1e-5), n
+                checked += 1
+    assert checked >= 8
