@@ -1,0 +1,276 @@
+"""ZeRO stages, fully sharded layers, activation checkpointing and CPU offload.
+
+Reference: ``FullyShardedDataParallel`` with stages 1/2/3 (stage 3 keeps only the local shard of every parameter
+and all-gathers it for forward and backward; src/fsdp.cpp:31-186,188-273), ``FSDPBlock`` and
+``ActivationCheckpointing`` (src/fsdp.cpp:350-543), ``ZeroOptimizer`` with parameter ownership and sharded AdamW
+moments and its memory report (src/zero_optimizer_core.cpp:38-313), ``CPUOffloadEngine`` (pinned pool, worker
+copies, double buffering, prefetch), ``ZeROOffloadManager`` and ``GradientCheckpointManager``
+(src/zero_optimizer_core.cpp:357-564, src/zero_offload.cpp:23-237).
+
+Mapping on a B200 node:
+  stage 1 / 2   ``ShardedFlatEngine`` (parallel/fsdp.py): optimizer state and the reduction are sharded, the
+                bf16 compute copy of the parameters stays replicated because HBM is plentiful; gradients are
+                reduce-scattered by the fused peer-memory kernels.
+  stage 3       ``ShardedLinear``: only rows [rank*N/W, (rank+1)*N/W) of a weight are resident; the forward
+                GEMM gathers the other rows inside the kernel (all-gather -> GEMM over peer memory), the
+                backward pass re-gathers for dX and reduce-scatters dW so that each rank keeps the gradient of
+                its own rows only.
+"""
+from __future__ import annotations
+
+import threading
+from typing import Callable, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from torch.utils.checkpoint import checkpoint
+
+from .fused import FusedGemmComm
+
+
+class _ShardedLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_shard, comm: FusedGemmComm):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        y = comm.gather_weight_gemm(x2, w_shard)
+        ctx.save_for_backward(x2, w_shard)
+        ctx.comm, ctx.shp = comm, shp
+        return y.view(*shp[:-1], y.shape[-1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w_shard = ctx.saved_tensors
+        comm = ctx.comm
+        W, r = comm.world, comm.rank
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        S = w_shard.shape[0]
+        w_full = comm._all_gather_rows(w_shard) if W > 1 else w_shard           # re-gather for dX, freed right after
+        dx = (dy2.float() @ w_full.float()).to(dy.dtype) if not dy2.is_cuda else _mm(dy2, w_full)
+        del w_full
+        # dW rows of this rank: every rank contributes dY[:, rows]^T @ X from its own batch
+        if W > 1:
+            dw_local = dy2.float().t() @ x2.float() if not dy2.is_cuda else _mm_tn(dy2, x2)
+            dist.all_reduce(dw_local, group=comm.group) if not comm.native else None
+            dw = _reduce_scatter_rows(dw_local, comm) if comm.native else dw_local[r * S:(r + 1) * S]
+        else:
+            dw = dy2.float().t() @ x2.float()
+        mg = getattr(w_shard, "main_grad", None)
+        if mg is not None:
+            mg.add_(dw.view_as(mg))
+            dw = None
+        else:
+            dw = dw.to(w_shard.dtype)
+        return dx.view(ctx.shp), dw, None
+
+
+def _mm(a, b):
+    """a [M, N] @ b [N, K] on the tcgen05 GEMM (b is the MN-major operand)."""
+    from ..ops.gemm import gemm
+    return gemm(a.contiguous(), b.contiguous(), b_mn=True)
+
+
+def _mm_tn(dy, x):
+    """dy[T, N]^T @ x[T, K] -> fp32 [N, K]."""
+    from ..ops.gemm import EPI_ATOMIC, gemm
+    out = torch.zeros((dy.shape[1], x.shape[1]), dtype=torch.float32, device=dy.device)
+    gemm(dy.contiguous(), x.contiguous(), out=out, a_mn=True, b_mn=True, epilogue=EPI_ATOMIC)
+    return out
+
+
+_comms: Dict[int, object] = {}
+
+
+def _reduce_scatter_rows(full: torch.Tensor, comm: FusedGemmComm) -> torch.Tensor:
+    from .collectives import Communicator
+    key = id(comm)
+    if key not in _comms:
+        _comms[key] = Communicator(comm.group, capacity=1 << 24, device=comm.device)
+    c = _comms[key]
+    flat = full.reshape(-1)
+    per = flat.numel() // comm.world
+    if flat.numel() <= c.capacity and per % 4 == 0:
+        return c.reduce_scatter(flat).view(full.shape[0] // comm.world, full.shape[1])
+    out = torch.empty(per, dtype=full.dtype, device=full.device)
+    dist.reduce_scatter_tensor(out, flat.contiguous(), group=comm.group)
+    return out.view(full.shape[0] // comm.world, full.shape[1])
+
+
+class ShardedLinear(nn.Module):
+    """ZeRO-3 linear layer: holds 1/W of the rows of the ``[out, in]`` weight; no bias sharding (bias is small)."""
+
+    def __init__(self, in_features, out_features, comm: FusedGemmComm, bias=False, dtype=torch.bfloat16, device=None, full_weight=None):
+        super().__init__()
+        W, r = comm.world, comm.rank
+        assert out_features % W == 0
+        self.comm, self.rows = comm, out_features // W
+        w = full_weight if full_weight is not None else torch.randn(out_features, in_features) * in_features ** -0.5
+        self.weight = nn.Parameter(w[r * self.rows:(r + 1) * self.rows].to(device=device, dtype=dtype).contiguous())
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
+
+    def forward(self, x):
+        y = _ShardedLinearFn.apply(x, self.weight, self.comm)
+        return y if self.bias is None else y + self.bias
+
+    def resident_bytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size()
+
+
+class FullyShardedDataParallel:
+    """The reference's wrapper API over the engines above. ``stage`` 1 and 2 return a ``ShardedFlatEngine`` for the
+    model; stage 3 additionally replaces every ``nn.Linear`` whose output dimension divides by the world size
+    (and is at least ``min_rows`` per rank) with a ``ShardedLinear``."""
+
+    def __init__(self, model: nn.Module, stage: int = 2, group=None, min_rows: int = 256, **engine_kw):
+        from .fsdp import ShardedFlatEngine
+        assert stage in (1, 2, 3)
+        self.model, self.stage, self.group = model, stage, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.replaced: List[str] = []
+        if stage == 3 and self.world > 1:
+            dev = next(model.parameters()).device
+            comm = FusedGemmComm(group, dev)
+            for name, mod in list(model.named_modules()):
+                for child_name, child in list(mod.named_children()):
+                    if isinstance(child, nn.Linear) and child.out_features % self.world == 0 and \
+                            child.out_features // self.world >= min_rows and child.bias is None:
+                        tile_ok = dev.type != "cuda" or (child.out_features // self.world) % 256 == 0
+                        if tile_ok:
+                            setattr(mod, child_name, ShardedLinear(child.in_features, child.out_features, comm, False, child.weight.dtype, dev,
+                                                                   child.weight.data))
+                            self.replaced.append(f"{name}.{child_name}".strip("."))
+        self.engine = ShardedFlatEngine(model, group=group, **engine_kw) if dist.is_initialized() else None
+
+    def memory_report(self) -> dict:
+        """Bytes per rank for parameters, gradients and optimizer state against the unsharded total."""
+        n = sum(p.numel() for p in self.model.parameters())
+        W = max(1, self.world)
+        return {"params_resident": sum(p.numel() * p.element_size() for p in self.model.parameters()), "optimizer_state": 12 * n // W,
+                "unsharded_total": n * (2 + 4 + 12), "savings_ratio": 1.0 - (2 + 4 + 12 / W) / 18.0}
+
+
+ZeroOptimizer = FullyShardedDataParallel
+
+
+# ---------------------------------------------------------------------------------------------- checkpointing
+class ActivationCheckpointing:
+    """Recompute the wrapped blocks in the backward pass instead of keeping their activations."""
+
+    def __init__(self, every: int = 1):
+        self.every = every
+        self.saved_calls = 0
+
+    def wrap(self, blocks: List[nn.Module]) -> List[Callable]:
+        out = []
+        for i, b in enumerate(blocks):
+            if i % self.every == 0:
+                out.append(lambda *a, _b=b, **k: self._run(_b, *a, **k))
+            else:
+                out.append(b)
+        return out
+
+    def _run(self, block, *args, **kw):
+        self.saved_calls += 1
+        return checkpoint(block, *args, use_reentrant=False, **kw)
+
+
+GradientCheckpointManager = ActivationCheckpointing
+
+
+# ---------------------------------------------------------------------------------------------- CPU offload
+class CPUOffloadEngine:
+    """Pinned host pool with asynchronous copies on a side stream: ``offload`` starts a device->host copy and
+    returns a handle, ``prefetch`` starts the copy back, ``fetch`` waits for it. Double buffering falls out of the
+    side stream: copies of tensor i+1 overlap compute on tensor i."""
+
+    def __init__(self, pool_bytes: int = 8 << 30, device=None):
+        self.device = torch.device(device) if device is not None else (
+            torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
+        self.cuda = self.device.type == "cuda"
+        self.pool_bytes, self.used = pool_bytes, 0
+        self.stream = torch.cuda.Stream(self.device) if self.cuda else None
+        self.store: Dict[str, dict] = {}
+        self.lock = threading.Lock()
+        self.stats = {"offloaded_bytes": 0, "fetched_bytes": 0}
+
+    def offload(self, name: str, t: torch.Tensor, free_device: bool = True):
+        nbytes = t.numel() * t.element_size()
+        with self.lock:
+            if self.used + nbytes > self.pool_bytes:
+                raise MemoryError(f"offload pool exhausted ({self.used + nbytes} > {self.pool_bytes})")
+            self.used += nbytes
+        host = torch.empty(t.shape, dtype=t.dtype, pin_memory=self.cuda)
+        ev = None
+        if self.cuda:
+            self.stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self.stream):
+                host.copy_(t, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.stream)
+            t.record_stream(self.stream)
+        else:
+            host.copy_(t)
+        self.store[name] = {"host": host, "event": ev, "device": None, "shape": t.shape, "dtype": t.dtype}
+        self.stats["offloaded_bytes"] += nbytes
+        if free_device:
+            t.data = torch.empty(0, dtype=t.dtype, device=t.device)
+
+    def prefetch(self, name: str):
+        e = self.store[name]
+        if e["device"] is not None:
+            return
+        if self.cuda:
+            with torch.cuda.stream(self.stream):
+                if e["event"] is not None:
+                    e["event"].synchronize()
+                dev_t = torch.empty(e["shape"], dtype=e["dtype"], device=self.device)
+                dev_t.copy_(e["host"], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(self.stream)
+            e["device"], e["event"] = dev_t, ev
+        else:
+            e["device"] = e["host"].clone()
+
+    def fetch(self, name: str, release: bool = True) -> torch.Tensor:
+        self.prefetch(name)
+        e = self.store[name]
+        if self.cuda and e["event"] is not None:
+            torch.cuda.current_stream(self.device).wait_event(e["event"])
+        t = e["device"]
+        self.stats["fetched_bytes"] += t.numel() * t.element_size()
+        if release:
+            with self.lock:
+                self.used -= t.numel() * t.element_size()
+            del self.store[name]
+        return t
+
+
+class ZeROOffloadManager:
+    """Keeps the optimizer state of a ``FlatParamEngine`` in pinned host memory between steps: the moments come
+    back (prefetched) for the update and leave again afterwards. The fp32 master weights stay on the device."""
+
+    def __init__(self, engine, pool_bytes: int = 64 << 30):
+        self.engine = engine
+        self.off = CPUOffloadEngine(pool_bytes, engine.device)
+        self._out = False
+
+    def offload_state(self):
+        e = self.engine
+        self.off.offload("exp_avg", e.exp_avg)
+        self.off.offload("exp_avg_sq", e.exp_avg_sq)
+        self._out = True
+
+    def prefetch_state(self):
+        if self._out:
+            self.off.prefetch("exp_avg")
+            self.off.prefetch("exp_avg_sq")
+
+    def step(self, grad_scale: float = 1.0):
+        e = self.engine
+        if self._out:
+            e.exp_avg = self.off.fetch("exp_avg")
+            e.exp_avg_sq = self.off.fetch("exp_avg_sq")
+            self._out = False
+        e.step(grad_scale)
+        self.offload_state()

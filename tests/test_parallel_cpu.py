@@ -271,3 +271,69 @@ def test_pipeline_two_stages_matches_full_model(tmp_path, schedule):
                 assert torch.allclose(g, full[n].grad, atol=1e-5), n
                 checked += 1
     assert checked >= 8
+
+
+def _z3_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from innova_b200.parallel.fused import FusedGemmComm
+    from innova_b200.parallel.zero import FullyShardedDataParallel, ShardedLinear
+    torch.manual_seed(0)
+    w = torch.randn(32, 16) * 0.3
+    x_all = torch.randn(2 * 6, 16)
+    lin = ShardedLinear(16, 32, FusedGemmComm(device="cpu"), dtype=torch.float32, full_weight=w)
+    x = x_all[rank * 6:(rank + 1) * 6].clone().requires_grad_(True)
+    y = lin(x)
+    (y ** 2).sum().backward()
+    model = torch.nn.Sequential(torch.nn.Linear(16, 512, bias=False), torch.nn.Linear(512, 16, bias=False))
+    fs = FullyShardedDataParallel(model, stage=3, min_rows=256)
+    rep = fs.memory_report()
+    torch.save({"y": y.detach(), "dx": x.grad, "dw": lin.weight.grad, "replaced": fs.replaced, "rep": rep}, out + f".{rank}")
+    dist.destroy_process_group()
+
+
+def test_zero3_sharded_linear_and_wrapper(tmp_path):
+    out = str(tmp_path / "z3")
+    mp.spawn(_z3_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    torch.manual_seed(0)
+    w = (torch.randn(32, 16) * 0.3).requires_grad_(True)
+    x_all = torch.randn(12, 16).requires_grad_(True)
+    y = x_all @ w.t()
+    (y ** 2).sum().backward()
+    for rank in range(2):
+        r = torch.load(out + f".{rank}")
+        assert torch.allclose(r["y"], y.detach()[rank * 6:(rank + 1) * 6], atol=1e-5)
+        assert torch.allclose(r["dx"], x_all.grad[rank * 6:(rank + 1) * 6], atol=1e-5)
+        assert torch.allclose(r["dw"], w.grad[rank * 16:(rank + 1) * 16], atol=1e-4)
+        assert r["replaced"] == ["0"] and 0 < r["rep"]["savings_ratio"] < 1
+
+
+def test_cpu_offload_and_zero_offload_manager():
+    from innova_b200.parallel.zero import ActivationCheckpointing, CPUOffloadEngine, ZeROOffloadManager
+    from innova_b200.training.flat_engine import FlatParamEngine
+    off = CPUOffloadEngine(pool_bytes=1 << 20, device="cpu")
+    t = torch.arange(100, dtype=torch.float32)
+    ref = t.clone()
+    off.offload("a", t)
+    assert t.numel() == 0 and off.used == 400
+    off.prefetch("a")
+    assert torch.equal(off.fetch("a"), ref) and off.used == 0
+    with pytest.raises(MemoryError):
+        off.offload("big", torch.zeros(1 << 20))
+    model = _model()
+    e1, e2 = FlatParamEngine(_model(), lr=1e-2), FlatParamEngine(model, lr=1e-2)
+    mgr = ZeROOffloadManager(e2)
+    for step in range(3):
+        g = torch.Generator().manual_seed(step)
+        grad = torch.randn(e1.total, generator=g)
+        e1.flat_grad.copy_(grad)
+        e2.flat_grad.copy_(grad)
+        e1.step()
+        mgr.step()
+        mgr.prefetch_state()
+    assert torch.equal(e1.flat_param, e2.flat_param)
+    ck = ActivationCheckpointing(every=1)
+    blocks = ck.wrap([torch.nn.Linear(8, 8), torch.nn.Linear(8, 8)])
+    x = torch.randn(2, 8, requires_grad=True)
+    blocks[1](blocks[0](x)).sum().backward()
+    assert ck.saved_calls == 2 and x.grad is not None
