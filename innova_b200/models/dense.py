@@ -66,9 +66,22 @@ class FFN(nn.Module):
         else:
             self.up_proj = nn.Linear(E, Fh, bias=cfg.bias, dtype=dtype)
         self.down_proj = nn.Linear(Fh, E, bias=cfg.bias, dtype=dtype)
+        self.adapter = None   # optional callable act -> delta added to the down-projection (low-rank adapters)
+
+    def _forward_adapted(self, h, residual):
+        cfg = self.cfg
+        if self.gated:
+            act = ops.swiglu(ops.linear(h, _ste(self.gate_up_proj.weight, cfg), self.gate_up_proj.bias))
+        else:
+            pre = ops.linear(h, _ste(self.up_proj.weight, cfg), self.up_proj.bias)
+            act = ops.gelu(pre) if cfg.activation == "gelu" else torch.relu(pre)
+        out = ops.linear(act, _ste(self.down_proj.weight, cfg), self.down_proj.bias, residual=residual, mode="add")
+        return out + self.adapter(act).to(out.dtype)
 
     def forward(self, h, residual):
         cfg = self.cfg
+        if self.adapter is not None:
+            return self._forward_adapted(h, residual)
         if self.gated:
             gu = ops.linear(h, _ste(self.gate_up_proj.weight, cfg), self.gate_up_proj.bias)
             act = ops.swiglu(gu)
