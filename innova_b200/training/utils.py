@@ -1,0 +1,481 @@
+"""Training utilities, evaluation metrics, hyper-parameter / architecture search and log writers.
+
+Reference: ``MixedPrecisionScaler`` / ``EMA`` / ``ProgressTracker`` / ``EarlyStopping`` / ``GradientAccumulator``
+(include/oil/training_utils.h:10-208), evaluation (``eval_perplexity`` with a strided context window,
+``eval_accuracy``, ``eval_classification``, BLEU, ROUGE-L, ``eval_hellaswag``, ``ModelEvaluator``;
+include/oil/eval.h:10-82), ``HPOEngine`` (random search, surrogate-guided search, population based training,
+successive halving) and ``NASEngine`` (mutation search under hardware constraints; include/oil/hpo_nas.h:15-184),
+and the CSV / JSONL / TensorBoard-text log writers (include/oil/log_writer.h:10-36).
+"""
+from __future__ import annotations
+
+import json
+import math
+import random
+import time
+from collections import Counter
+from dataclasses import asdict, dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+import torch.nn.functional as F
+
+
+# ---------------------------------------------------------------------------------------------- training helpers
+class MixedPrecisionScaler:
+    """Dynamic loss scale: start at 128 (the reference's value), halve on overflow, double after ``growth_interval``
+    clean steps."""
+
+    def __init__(self, init_scale: float = 128.0, growth_interval: int = 1000, min_scale: float = 1.0, max_scale: float = 65536.0):
+        self.scale, self.growth_interval, self.min_scale, self.max_scale = init_scale, growth_interval, min_scale, max_scale
+        self.good, self.overflows = 0, 0
+
+    def update(self, found_inf: bool) -> bool:
+        """Returns True when the step may be applied."""
+        if found_inf:
+            self.scale = max(self.min_scale, self.scale * 0.5)
+            self.good = 0
+            self.overflows += 1
+            return False
+        self.good += 1
+        if self.good >= self.growth_interval:
+            self.scale = min(self.max_scale, self.scale * 2.0)
+            self.good = 0
+        return True
+
+
+class EMA:
+    def __init__(self, params: Sequence[torch.Tensor], decay: float = 0.999):
+        self.decay = decay
+        self.shadow = [p.detach().float().clone() for p in params]
+        self.params = list(params)
+
+    @torch.no_grad()
+    def update(self):
+        for s, p in zip(self.shadow, self.params):
+            s.mul_(self.decay).add_(p.detach().float(), alpha=1 - self.decay)
+
+    @torch.no_grad()
+    def copy_to(self, params: Optional[Sequence[torch.Tensor]] = None):
+        for s, p in zip(self.shadow, params or self.params):
+            p.copy_(s.to(p.dtype))
+
+
+class EarlyStopping:
+    def __init__(self, patience: int = 5, min_delta: float = 0.0, mode: str = "min"):
+        self.patience, self.min_delta, self.mode = patience, min_delta, mode
+        self.best, self.bad, self.should_stop = None, 0, False
+
+    def step(self, metric: float) -> bool:
+        better = self.best is None or (metric < self.best - self.min_delta if self.mode == "min" else metric > self.best + self.min_delta)
+        if better:
+            self.best, self.bad = metric, 0
+        else:
+            self.bad += 1
+            self.should_stop = self.bad >= self.patience
+        return self.should_stop
+
+
+class ProgressTracker:
+    def __init__(self, total_steps: int):
+        self.total, self.step, self.t0, self.tokens = total_steps, 0, time.time(), 0
+
+    def update(self, steps: int = 1, tokens: int = 0):
+        self.step += steps
+        self.tokens += tokens
+
+    def summary(self) -> dict:
+        el = max(time.time() - self.t0, 1e-9)
+        rate = self.step / el
+        return {"step": self.step, "progress": self.step / max(1, self.total), "elapsed_s": el, "tokens_per_sec": self.tokens / el,
+                "eta_s": (self.total - self.step) / rate if rate > 0 else float("inf")}
+
+
+class GradientAccumulator:
+    """Counts micro-batches; ``ready()`` is True on the one that completes an optimizer step."""
+
+    def __init__(self, steps: int):
+        self.steps, self.count = max(1, steps), 0
+
+    def ready(self) -> bool:
+        self.count += 1
+        if self.count >= self.steps:
+            self.count = 0
+            return True
+        return False
+
+    @property
+    def scale(self) -> float:
+        return 1.0 / self.steps
+
+
+# ---------------------------------------------------------------------------------------------- evaluation
+@dataclass
+class EvalResult:
+    task_name: str = ""
+    perplexity: float = 0.0
+    accuracy: float = 0.0
+    f1_score: float = 0.0
+    precision: float = 0.0
+    recall: float = 0.0
+    bleu: float = 0.0
+    rouge_l: float = 0.0
+    tokens_per_sec: float = 0.0
+    total_tokens: int = 0
+    correct: int = 0
+    total: int = 0
+
+
+@torch.no_grad()
+def eval_perplexity(model, tokens: Sequence[int], context_size: int = 512, stride: int = 256, device=None) -> EvalResult:
+    """Strided windows: every window scores only the tokens the previous window did not."""
+    device = device or next(model.parameters()).device
+    toks = torch.as_tensor(tokens, dtype=torch.long)
+    nll, count, t0 = 0.0, 0, time.time()
+    prev_end = 0
+    for start in range(0, max(1, len(toks) - 1), stride):
+        end = min(start + context_size, len(toks))
+        ids = toks[start:end].unsqueeze(0).to(device)
+        if ids.shape[1] < 2:
+            break
+        logits = model(ids[:, :-1]).float()
+        lp = F.log_softmax(logits, -1).gather(-1, ids[:, 1:].unsqueeze(-1)).squeeze(-1)[0]
+        new_from = max(prev_end - start - 1, 0)          # targets start at position start+1
+        nll -= float(lp[new_from:].sum())
+        count += lp.numel() - new_from
+        prev_end = end
+        if end == len(toks):
+            break
+    dt = max(time.time() - t0, 1e-9)
+    return EvalResult("perplexity", perplexity=math.exp(nll / max(1, count)), total_tokens=count, tokens_per_sec=count / dt)
+
+
+@torch.no_grad()
+def eval_accuracy(model, tokens: Sequence[int], context_size: int = 512, device=None) -> EvalResult:
+    device = device or next(model.parameters()).device
+    toks = torch.as_tensor(tokens, dtype=torch.long)
+    correct = total = 0
+    for start in range(0, len(toks) - 1, context_size):
+        ids = toks[start:start + context_size + 1].unsqueeze(0).to(device)
+        if ids.shape[1] < 2:
+            break
+        pred = model(ids[:, :-1]).argmax(-1)
+        correct += int((pred == ids[:, 1:]).sum())
+        total += pred.numel()
+    return EvalResult("accuracy", accuracy=correct / max(1, total), correct=correct, total=total, total_tokens=total)
+
+
+def eval_classification(predictions: torch.Tensor, labels: Sequence[int]) -> EvalResult:
+    """predictions [N, C] scores; macro-averaged precision / recall / F1."""
+    pred = predictions.argmax(-1).cpu()
+    lab = torch.as_tensor(labels)
+    C = predictions.shape[-1]
+    ps, rs, fs = [], [], []
+    for c in range(C):
+        tp = int(((pred == c) & (lab == c)).sum())
+        fp = int(((pred == c) & (lab != c)).sum())
+        fn = int(((pred != c) & (lab == c)).sum())
+        if tp + fp + fn == 0:
+            continue
+        p, r = tp / max(1, tp + fp), tp / max(1, tp + fn)
+        ps.append(p)
+        rs.append(r)
+        fs.append(2 * p * r / (p + r) if p + r > 0 else 0.0)
+    n = max(1, len(fs))
+    correct = int((pred == lab).sum())
+    return EvalResult("classification", accuracy=correct / max(1, len(lab)), precision=sum(ps) / n, recall=sum(rs) / n, f1_score=sum(fs) / n,
+                      correct=correct, total=len(lab))
+
+
+def compute_bleu(candidate: Sequence[int], reference: Sequence[int], max_n: int = 4) -> float:
+    if not candidate or not reference:
+        return 0.0
+    logs = 0.0
+    for n in range(1, max_n + 1):
+        c = Counter(tuple(candidate[i:i + n]) for i in range(len(candidate) - n + 1))
+        r = Counter(tuple(reference[i:i + n]) for i in range(len(reference) - n + 1))
+        tot = sum(c.values())
+        if tot == 0:
+            return 0.0
+        match = sum(min(v, r[k]) for k, v in c.items())
+        if match == 0:
+            return 0.0
+        logs += math.log(match / tot) / max_n
+    bp = 1.0 if len(candidate) > len(reference) else math.exp(1 - len(reference) / len(candidate))
+    return bp * math.exp(logs)
+
+
+def compute_rouge_l(candidate: Sequence[int], reference: Sequence[int]) -> float:
+    if not candidate or not reference:
+        return 0.0
+    m, n = len(candidate), len(reference)
+    prev = [0] * (n + 1)
+    for i in range(1, m + 1):
+        cur = [0] * (n + 1)
+        for j in range(1, n + 1):
+            cur[j] = prev[j - 1] + 1 if candidate[i - 1] == reference[j - 1] else max(prev[j], cur[j - 1])
+        prev = cur
+    lcs = prev[n]
+    if lcs == 0:
+        return 0.0
+    p, r = lcs / m, lcs / n
+    return 2 * p * r / (p + r)
+
+
+@torch.no_grad()
+def eval_hellaswag(model, contexts, correct_endings, wrong_endings, device=None) -> EvalResult:
+    """Picks the ending with the higher length-normalised log-likelihood."""
+    device = device or next(model.parameters()).device
+
+    def score(ctx, end):
+        ids = torch.tensor([list(ctx) + list(end)], device=device)
+        lp = F.log_softmax(model(ids[:, :-1]).float(), -1).gather(-1, ids[:, 1:].unsqueeze(-1)).squeeze(-1)[0]
+        return float(lp[len(ctx) - 1:].mean())
+    correct = sum(score(c, g) > score(c, w) for c, g, w in zip(contexts, correct_endings, wrong_endings))
+    return EvalResult("hellaswag", accuracy=correct / max(1, len(contexts)), correct=correct, total=len(contexts))
+
+
+def load_eval_tokens(path: str, max_tokens: int = 0) -> List[int]:
+    out = []
+    with open(path) as f:
+        for line in f:
+            line = line.strip()
+            if line:
+                out.append(int(line))
+                if max_tokens and len(out) >= max_tokens:
+                    break
+    return out
+
+
+class ModelEvaluator:
+    def __init__(self, model):
+        self.model, self.batch_size = model, 1
+
+    def evaluate_perplexity(self, tokens, name="perplexity", context=512, stride=256):
+        r = eval_perplexity(self.model, tokens, context, stride)
+        r.task_name = name
+        return r
+
+    def evaluate_accuracy(self, tokens, name="accuracy", context=512):
+        r = eval_accuracy(self.model, tokens, context)
+        r.task_name = name
+        return r
+
+    def evaluate_generation(self, prompt_len=32, gen_len=16, name="generation"):
+        from ..inference.generator import Generator
+        gen = Generator(self.model, kv_format="bf16", max_seq=prompt_len + gen_len + 1)
+        gen.generate_tokens([[1] * prompt_len], gen_len)
+        return EvalResult(name, tokens_per_sec=gen.stats.decode_tokens_per_sec, total_tokens=gen.stats.new_tokens)
+
+    def run_all(self, tokens):
+        ctx = min(512, max(8, len(tokens) // 2))
+        return [self.evaluate_perplexity(tokens, context=ctx, stride=max(1, ctx // 2)), self.evaluate_accuracy(tokens, context=ctx)]
+
+
+# ---------------------------------------------------------------------------------------------- HPO / NAS
+@dataclass
+class SearchSpace:
+    lr: tuple = (1e-5, 1e-2)                  # log-uniform
+    weight_decay: tuple = (0.0, 0.2)
+    warmup_steps: tuple = (0, 2000)
+    batch_size: Sequence[int] = (8, 16, 32, 64)
+    dropout: tuple = (0.0, 0.3)
+
+
+@dataclass
+class HPConfig:
+    lr: float = 3e-4
+    weight_decay: float = 0.1
+    warmup_steps: int = 100
+    batch_size: int = 16
+    dropout: float = 0.0
+    score: float = float("inf")
+
+
+class HPOEngine:
+    """``evaluate(config, budget) -> loss`` is supplied by the caller (lower is better)."""
+
+    def __init__(self, evaluate: Callable[[HPConfig, int], float], space: Optional[SearchSpace] = None, seed: int = 0):
+        self.evaluate, self.space, self.rng = evaluate, space or SearchSpace(), random.Random(seed)
+        self.history: List[HPConfig] = []
+
+    def random_sample(self) -> HPConfig:
+        s, r = self.space, self.rng
+        return HPConfig(lr=math.exp(r.uniform(math.log(s.lr[0]), math.log(s.lr[1]))), weight_decay=r.uniform(*s.weight_decay),
+                        warmup_steps=r.randint(*s.warmup_steps), batch_size=r.choice(list(s.batch_size)), dropout=r.uniform(*s.dropout))
+
+    def record_eval(self, cfg: HPConfig, score: float):
+        cfg.score = score
+        self.history.append(cfg)
+
+    def _run(self, cfg: HPConfig, budget: int) -> HPConfig:
+        self.record_eval(cfg, float(self.evaluate(cfg, budget)))
+        return cfg
+
+    def random_search(self, n_configs: int, budget: int = 1) -> List[HPConfig]:
+        return sorted((self._run(self.random_sample(), budget) for _ in range(n_configs)), key=lambda c: c.score)
+
+    def surrogate_predict(self, cfg: HPConfig) -> float:
+        """Distance-weighted mean of past scores in (log lr, wd, dropout) space."""
+        if not self.history:
+            return 0.0
+        num = den = 0.0
+        for h in self.history:
+            d = (math.log(cfg.lr) - math.log(h.lr)) ** 2 + 25 * (cfg.weight_decay - h.weight_decay) ** 2 + 10 * (cfg.dropout - h.dropout) ** 2
+            w = 1.0 / (d + 1e-3)
+            num += w * h.score
+            den += w
+        return num / den
+
+    def bayesian_optimization(self, n_initial: int = 5, n_iterations: int = 20, budget: int = 1) -> List[HPConfig]:
+        self.random_search(n_initial, budget)
+        for _ in range(n_iterations):
+            cands = [self.random_sample() for _ in range(32)]
+            self._run(min(cands, key=self.surrogate_predict), budget)
+        return sorted(self.history, key=lambda c: c.score)
+
+    def mutate_config(self, cfg: HPConfig, rate: float = 0.3) -> HPConfig:
+        r = self.rng
+        out = HPConfig(**{k: v for k, v in asdict(cfg).items() if k != "score"})
+        if r.random() < rate:
+            out.lr = min(self.space.lr[1], max(self.space.lr[0], cfg.lr * r.choice([0.8, 1.25])))
+        if r.random() < rate:
+            out.weight_decay = min(self.space.weight_decay[1], max(self.space.weight_decay[0], cfg.weight_decay * r.choice([0.8, 1.25])))
+        if r.random() < rate:
+            out.batch_size = r.choice(list(self.space.batch_size))
+        return out
+
+    def crossover(self, a: HPConfig, b: HPConfig) -> HPConfig:
+        r = self.rng
+        return HPConfig(**{k: (getattr(a, k) if r.random() < 0.5 else getattr(b, k)) for k in ("lr", "weight_decay", "warmup_steps", "batch_size",
+                                                                                                 "dropout")})
+
+    def population_based_training(self, n_population: int = 8, n_generations: int = 10, budget: int = 1) -> List[HPConfig]:
+        pop = [self._run(self.random_sample(), budget) for _ in range(n_population)]
+        for _ in range(n_generations):
+            pop.sort(key=lambda c: c.score)
+            cut = max(1, n_population // 4)
+            for i in range(n_population - cut, n_population):        # the bottom quarter copies and perturbs a top member
+                pop[i] = self._run(self.mutate_config(self.rng.choice(pop[:cut]), 1.0), budget)
+        return sorted(pop, key=lambda c: c.score)
+
+    def successive_halving(self, n_configs: int = 27, n_rungs: int = 3, eta: int = 3) -> List[HPConfig]:
+        pop = [self.random_sample() for _ in range(n_configs)]
+        budget = 1
+        for _ in range(n_rungs):
+            pop = sorted((self._run(c, budget) for c in pop), key=lambda c: c.score)[: max(1, len(pop) // eta)]
+            budget *= eta
+        return pop
+
+    def optimize(self, n_budget: int = 20, method: str = "pbt") -> HPConfig:
+        if method == "random":
+            return self.random_search(n_budget)[0]
+        if method == "bayes":
+            return self.bayesian_optimization(max(2, n_budget // 4), n_budget - max(2, n_budget // 4))[0]
+        if method == "halving":
+            return self.successive_halving(n_budget)[0]
+        return self.population_based_training(max(4, n_budget // 5), 4)[0]
+
+
+@dataclass
+class Architecture:
+    hidden_size: int = 256
+    num_layers: int = 4
+    num_heads: int = 4
+    ffn_mult: float = 4.0
+    score: float = float("inf")
+
+    def params(self, vocab: int = 32000) -> int:
+        d = self.hidden_size
+        return vocab * d + self.num_layers * int(4 * d * d + 2 * self.ffn_mult * d * d)
+
+
+@dataclass
+class HardwareConstraints:
+    max_params: int = 10 ** 12
+    max_memory_bytes: int = 180 * 2 ** 30          # one B200
+    bytes_per_param: float = 18.0                  # bf16 weight + fp32 grad + fp32 master and moments
+
+
+class NASEngine:
+    """Evolutionary search over (hidden, layers, heads, ffn multiplier) under a parameter / memory budget."""
+
+    def __init__(self, evaluate: Callable[[Architecture], float], constraints: Optional[HardwareConstraints] = None, seed: int = 0):
+        self.evaluate, self.hc, self.rng = evaluate, constraints or HardwareConstraints(), random.Random(seed)
+        self.history: List[Architecture] = []
+
+    def feasible(self, a: Architecture) -> bool:
+        return a.hidden_size % a.num_heads == 0 and a.params() <= self.hc.max_params and a.params() * self.hc.bytes_per_param <= \
+            self.hc.max_memory_bytes
+
+    def mutate(self, a: Architecture) -> Architecture:
+        r = self.rng
+        b = Architecture(a.hidden_size, a.num_layers, a.num_heads, a.ffn_mult)
+        op = r.choice(["wider", "narrower", "deeper", "shallower", "heads", "ffn"])
+        if op == "wider":
+            b.hidden_size += 64
+        elif op == "narrower":
+            b.hidden_size = max(64, b.hidden_size - 64)
+        elif op == "deeper":
+            b.num_layers += 1
+        elif op == "shallower":
+            b.num_layers = max(1, b.num_layers - 1)
+        elif op == "heads":
+            b.num_heads = r.choice([h for h in (1, 2, 4, 8, 16, 32) if b.hidden_size % h == 0])
+        else:
+            b.ffn_mult = r.choice([2.0, 2.67, 4.0])
+        return b
+
+    def search(self, start: Architecture, n_iterations: int = 20, population: int = 4) -> Architecture:
+        pop = [start]
+        start.score = self.evaluate(start)
+        self.history.append(start)
+        for _ in range(n_iterations):
+            child = self.mutate(self.rng.choice(pop))
+            if not self.feasible(child):
+                continue
+            child.score = self.evaluate(child)
+            self.history.append(child)
+            pop = sorted(pop + [child], key=lambda a: a.score)[:population]
+        return pop[0]
+
+
+# ---------------------------------------------------------------------------------------------- log writers
+class CSVLogWriter:
+    def __init__(self, path: str, fields: Sequence[str]):
+        self.fields = list(fields)
+        self.f = open(path, "w")
+        self.f.write(",".join(self.fields) + "\n")
+
+    def write(self, **row):
+        self.f.write(",".join(str(row.get(k, "")) for k in self.fields) + "\n")
+        self.f.flush()
+
+    def close(self):
+        self.f.close()
+
+
+class JSONLLogWriter:
+    def __init__(self, path: str):
+        self.f = open(path, "w")
+
+    def write(self, **row):
+        self.f.write(json.dumps(row) + "\n")
+        self.f.flush()
+
+    def close(self):
+        self.f.close()
+
+
+class ScalarLogWriter:
+    """``tag step value wall_time`` lines, the text form a TensorBoard importer reads."""
+
+    def __init__(self, path: str):
+        self.f = open(path, "w")
+
+    def add_scalar(self, tag: str, value: float, step: int):
+        self.f.write(f"{tag} {step} {value:.8g} {time.time():.3f}\n")
+        self.f.flush()
+
+    def close(self):
+        self.f.close()
