@@ -50,15 +50,16 @@ class Generator:
 
     # ------------------------------------------------------------------ one forward over new tokens
     @torch.no_grad()
-    def _forward(self, ids: torch.Tensor, start: List[int], all_logits: bool = False) -> torch.Tensor:
+    def _forward(self, ids: torch.Tensor, start: List[int], all_logits: bool = False, slots: Optional[List[int]] = None) -> torch.Tensor:
         """ids [B, S_new]; sequences 0..B-1 continue at positions start[b]. Returns logits [B, vocab] of the
         last new token, or [B, S_new, vocab] with ``all_logits`` (speculative verification)."""
         m, cfg, cache = self.model, self.cfg, self.cache
         B, S = ids.shape
         H, Hkv, D = cfg.num_heads, cfg.kv_heads, cfg.head_dim
         pos = (torch.tensor(start, device=self.device).view(B, 1) + torch.arange(S, device=self.device).view(1, S))
-        for b in range(B):
-            cache.reserve(b, start[b] + S)
+        batch_ids = list(range(B)) if slots is None else list(slots)   # cache rows of the B sequences
+        for i, b in enumerate(batch_ids):
+            cache.reserve(b, start[i] + S)
         x = m.tok_embeddings.weight[ids.clamp(0, cfg.padded_vocab - 1)]
         if m.pos_embeddings is not None:
             x = x + m.pos_embeddings.weight[pos.clamp(max=cfg.max_seq_len - 1)]
@@ -66,7 +67,6 @@ class Generator:
         pos32 = pos.reshape(-1).to(torch.int32).contiguous()
         prefill = S > 1 and all(s == 0 for s in start)
         scale = D ** -0.5
-        batch_ids = list(range(B))
         for li, blk in enumerate(m.layers):
             h = blk.attention_norm(x)
             qkv = self.linear(h, blk.attention.qkv_proj)
@@ -96,6 +96,7 @@ class Generator:
                 x = x + self._ffn(blk, blk.ffn_norm(x))
         if prefill:
             cache.commit(batch_ids, [S] * B)
+        assert prefill or slots is None, "decoding runs on cache rows 0..B-1"
         last = m.norm(x if all_logits else x[:, -1])
         logits = ops.linear(last, m.lm_head.weight)
         return logits[..., : cfg.vocab_size]

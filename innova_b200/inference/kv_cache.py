@@ -86,6 +86,16 @@ class PagedKVCache:
         self._host_lens[b] = new_len
         self.seq_lens[b] = new_len
 
+    def swap(self, a: int, b: int):
+        """Exchange two sequences' rows (keeps the active sequences of a continuous batch in rows 0..n-1)."""
+        if a == b:
+            return
+        self._host_pages[a], self._host_pages[b] = self._host_pages[b], self._host_pages[a]
+        self._host_lens[a], self._host_lens[b] = self._host_lens[b], self._host_lens[a]
+        rows = self.page_table[[b, a]].clone()
+        self.page_table[[a, b]] = rows
+        self.seq_lens[: len(self._host_lens)] = torch.tensor(self._host_lens, dtype=torch.int32, device=self.device)
+
     def lengths(self) -> List[int]:
         return list(self._host_lens)
 
