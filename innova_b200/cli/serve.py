@@ -1,0 +1,61 @@
+"""oil-serve: HTTP serving of a saved model (tools/serve.cpp:18-110, default port 8080; the reference's second
+server binary listens on 9090, ``--port 9090`` gives the same)."""
+from __future__ import annotations
+
+import argparse
+import sys
+import time
+
+
+def build_server(model_path: str, port: int = 8080, host: str = "127.0.0.1", device=None, rate_limit: float = 0.0, max_new_tokens: int = 256):
+    from ..inference.serving import EmbeddingEndpoint, InferenceEngine
+    from ..serving.http_server import HTTPServer
+    state = {"engine": InferenceEngine(model_path, device=device)}
+    srv = HTTPServer(port, host)
+    srv.set_model_name(model_path.rsplit("/", 1)[-1])
+
+    def generate(prompt, n, stream):
+        eng = state["engine"]
+        n = min(n, max_new_tokens)
+        return eng.stream(prompt, n) if stream else eng.generate(prompt, n)
+
+    def embed(text):
+        eng = state["engine"]
+        return EmbeddingEndpoint(eng.model, eng.tok).embed(text).tolist()
+
+    def load(path):
+        try:
+            state["engine"] = InferenceEngine(path, device=device)
+            srv.set_model_name(path.rsplit("/", 1)[-1])
+            return True
+        except Exception:
+            return False
+    srv.set_generate_callback(generate)
+    srv.set_embeddings_callback(embed)
+    srv.set_load_model_callback(load)
+    if rate_limit > 0:
+        srv.set_rate_limit(rate_limit, int(max(1, rate_limit)))
+    return srv
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="oil-serve")
+    ap.add_argument("--model", required=True)
+    ap.add_argument("--port", type=int, default=8080)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--rate-limit", type=float, default=0.0)
+    ap.add_argument("--device", default=None)
+    a = ap.parse_args(argv)
+    srv = build_server(a.model, a.port, a.host, a.device, a.rate_limit)
+    srv.start()
+    print(f"serving {a.model} on http://{a.host}:{srv.port}", flush=True)
+    try:
+        while srv.is_running():
+            time.sleep(0.5)
+    except KeyboardInterrupt:
+        srv.stop()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

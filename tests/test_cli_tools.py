@@ -1,0 +1,69 @@
+"""oil-quantize / oil-finetune / oil-evaluate / oil-bench / oil-serve on a tiny model trained here (CPU)."""
+import json
+import os
+import subprocess
+import sys
+import urllib.request
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(mod, *args):
+    r = subprocess.run([sys.executable, "-m", mod, *args], capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    return r.stdout
+
+
+@pytest.fixture(scope="module")
+def tiny(tmp_path_factory):
+    d = tmp_path_factory.mktemp("cli")
+    corpus = d / "corpus.txt"
+    corpus.write_text("the quick brown fox jumps over the lazy dog. " * 200)
+    model = str(d / "m.oil")
+    _run("innova_b200.cli.train", "--model", model, "--data", str(corpus), "--batch-size", "4", "--seq-length", "32", "--hidden-size", "64",
+         "--num-layers", "2", "--num-heads", "2", "--max-steps", "25", "--lr", "3e-3", "--device", "cpu", "--vocab-size", "256")
+    return d, model, str(corpus)
+
+
+def test_quantize_evaluate_finetune_bench(tiny):
+    d, model, corpus = tiny
+    q = str(d / "q.oil")
+    res = json.loads(_run("innova_b200.cli.quantize", "--input", model, "--output", q, "--format", "OIL8", "--per-layer",
+                          "lm_head=OIL16").splitlines()[-1])
+    assert res["bytes_after"] < 0.5 * res["bytes_before"] and 8.0 < res["bpw"] < 14
+    ev = json.loads(_run("innova_b200.cli.evaluate", "--model", model, "--data", corpus, "--context", "32", "--stride", "16", "--max-tokens",
+                         "600", "--device", "cpu").splitlines()[-1])
+    evq = json.loads(_run("innova_b200.cli.evaluate", "--model", q, "--data", corpus, "--context", "32", "--stride", "16", "--max-tokens", "600",
+                          "--device", "cpu").splitlines()[-1])
+    assert ev[0]["task_name"] == "perplexity" and ev[0]["perplexity"] < 200
+    assert abs(evq[0]["perplexity"] / ev[0]["perplexity"] - 1) < 0.1          # OIL8 keeps the model
+    for method, out in (("full", "ft.oil"), ("rank", "a.nrad"), ("slots", "k.kexp")):
+        r = json.loads(_run("innova_b200.cli.finetune", "--model", model, "--data", corpus, "--output", str(d / out), "--method", method, "--lr",
+                            "1e-3", "--batch-size", "2", "--seq-length", "32", "--max-steps", "4", "--device", "cpu", "--rank", "4").splitlines()[-1])
+        assert r["steps"] == 4 and os.path.exists(d / out)
+    b = json.loads(_run("innova_b200.cli.bench", "--suite", "train", "--hidden-size", "64", "--num-layers", "2", "--num-heads", "2", "--vocab-size",
+                        "512", "--batch-size", "2", "--seq-length", "32", "--steps", "2", "--warmup", "1", "--device", "cpu").splitlines()[-1])
+    assert b["tokens_per_sec"] > 0
+    n = json.loads(_run("innova_b200.cli.bench", "--suite", "native", "--hidden-size", "64", "--num-layers", "2", "--num-heads", "2", "--vocab-size",
+                        "512", "--batch-size", "2", "--seq-length", "32", "--steps", "2", "--warmup", "1", "--device", "cpu").splitlines()[-1])
+    assert n["phase"] == "native" and n["bits_per_weight"] < 9
+
+
+def test_serve_answers_over_http(tiny):
+    d, model, corpus = tiny
+    from innova_b200.cli.serve import build_server
+    srv = build_server(model, port=0, device="cpu")
+    srv.start()
+    try:
+        req = urllib.request.Request(f"http://127.0.0.1:{srv.port}/v1/completions", data=json.dumps({"prompt": "the quick", "max_tokens": 5}).encode(),
+                                     method="POST")
+        with urllib.request.urlopen(req, timeout=60) as r:
+            obj = json.loads(r.read())
+        assert obj["object"] == "text_completion" and isinstance(obj["choices"][0]["text"], str)
+        req = urllib.request.Request(f"http://127.0.0.1:{srv.port}/v1/embeddings", data=json.dumps({"input": "fox"}).encode(), method="POST")
+        with urllib.request.urlopen(req, timeout=60) as r:
+            assert len(json.loads(r.read())["data"][0]["embedding"]) == 64
+    finally:
+        srv.stop()
