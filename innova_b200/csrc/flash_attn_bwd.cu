@@ -22,7 +22,7 @@ namespace inv {
 
 int make_tmap_tokens_bf16(CUtensorMap* out, const void* ptr, int cols, int S, int B, int ld, int box_rows);
 
-constexpr int FB_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 softmax
+constexpr int FB_THREADS = 448;  // warp 0 TMA, warp 1 MMA, warps 2-9 softmax, warps 10-13 dQ writers (head_dim 64)
 
 struct FlashBwdParams {
   const float* lse;    // [B, H, S], log2 domain: log2(sum exp(scores))
@@ -101,7 +101,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     mbar_init(s_empty, 256);
     mbar_init(pds_full, 256);
     mbar_init(mma2_done, 1);
-    mbar_init(dq_empty, 256);
+    mbar_init(dq_empty, OVERLAP ? 128 : 256);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_q);
@@ -203,6 +203,37 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         umma_commit(&q_empty[st]);
       }
     }
+  } else if (warp >= 10) {
+    // ---------------- dQ writers (head_dim 64): drain each block's dQ to the fp32 accumulator while the
+    // softmax warps already work on the next block ----------------
+    if (OVERLAP) {
+      const int q = warp & 3;
+      const int r = q * 32 + lane;
+      const uint32_t t_lane = tmem_base + (uint32_t(q * 32) << 16);
+      for (int it = 0; it < n_it; ++it) {
+        const int h = hk * G + it / nq_it;
+        const int q0 = (i0 + it % nq_it) * 128;
+        if (!mbar_wait_warp(mma2_done, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) break;
+        tc_fence_after();
+        const int qrow = q0 + r;
+#pragma unroll 1
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t rr[32];
+          tmem_ld_32x32(t_lane + DQ_COL + cc * 32, rr);
+          tmem_ld_wait();
+          if (qrow < p.S && !(p.causal & 2)) {
+            float* dst = p.dq_acc + ((size_t)b * p.S + qrow) * ((size_t)p.H * D) + h * D + cc * 32;
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + g * 4), "f"(__uint_as_float(rr[g * 4])),
+                           "f"(__uint_as_float(rr[g * 4 + 1])), "f"(__uint_as_float(rr[g * 4 + 2])), "f"(__uint_as_float(rr[g * 4 + 3]))
+                           : "memory");
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(dq_empty);
+      }
+    }
   } else {
     // ---------------- softmax warps ----------------
     const int q = warp & 3;            // TMEM lane quarter
@@ -230,56 +261,61 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tmem_ld_32x32(t_lane + ST_COL + col0, s_r);
         tmem_ld_32x32(t_lane + DPT_COL + col0, dp_r);
         tmem_ld_wait();
-        float pv[32], ds[32];
+        if (OVERLAP && cc == 0 && it > 0) {
+          // the P^T / dS^T tiles are still operands of the previous block's second MMA group until it completes
+          if (!mbar_wait_warp(mma2_done, (it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        }
+        uint32_t pk[16], dk[16];  // P^T and dS^T of this chunk as packed bf16 pairs
         if (!need_mask && vec_ok) {
-          // interior block: no predicates, statistics fetched as 16-byte broadcast loads
+          // interior block: no predicates, statistics fetched as 16-byte broadcast loads; exponentials run two
+          // per MUFU instruction on packed bf16 and dS = P * (dP - D) is one packed multiply per pair
           const float4* l4 = reinterpret_cast<const float4*>(lse_row + q0 + col0);
           const float4* d4 = reinterpret_cast<const float4*>(dl_row + q0 + col0);
 #pragma unroll
           for (int i4 = 0; i4 < 8; ++i4) {
             const float4 l = __ldg(l4 + i4), dl = __ldg(d4 + i4);
-            const float ls[4] = {l.x, l.y, l.z, l.w}, dls[4] = {dl.x, dl.y, dl.z, dl.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const int i = i4 * 4 + k;
-              const float e = exp2f(__uint_as_float(s_r[i]) * c - ls[k]);
-              pv[i] = e;
-              ds[i] = e * (__uint_as_float(dp_r[i]) - dls[k]);
-            }
+            const int i = i4 * 4;
+            const uint32_t p01 = ex2_bf16x2(cvt_bf16x2(fmaf(__uint_as_float(s_r[i]), c, -l.x), fmaf(__uint_as_float(s_r[i + 1]), c, -l.y)));
+            const uint32_t p23 = ex2_bf16x2(cvt_bf16x2(fmaf(__uint_as_float(s_r[i + 2]), c, -l.z), fmaf(__uint_as_float(s_r[i + 3]), c, -l.w)));
+            const uint32_t t01 = cvt_bf16x2(__uint_as_float(dp_r[i]) - dl.x, __uint_as_float(dp_r[i + 1]) - dl.y);
+            const uint32_t t23 = cvt_bf16x2(__uint_as_float(dp_r[i + 2]) - dl.z, __uint_as_float(dp_r[i + 3]) - dl.w);
+            pk[i4 * 2] = p01;
+            pk[i4 * 2 + 1] = p23;
+            dk[i4 * 2] = mul_bf16x2(p01, t01);
+            dk[i4 * 2 + 1] = mul_bf16x2(p23, t23);
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int qi = q0 + col0 + i;
-            const int qc = min(qi, p.S - 1);
-            const float lse = __ldg(lse_row + qc);
-            const float dl = __ldg(dl_row + qc);
-            float e = exp2f(__uint_as_float(s_r[i]) * c - lse);
-            if (((p.causal & 1) && key > qi) || qi >= p.S || key >= p.S) e = 0.f;
-            pv[i] = e;
-            ds[i] = e * (__uint_as_float(dp_r[i]) - dl);
+          for (int i = 0; i < 32; i += 2) {
+            float pe[2], de[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int qi = q0 + col0 + i + u;
+              const int qc = min(qi, p.S - 1);
+              const float lse = __ldg(lse_row + qc);
+              const float dl = __ldg(dl_row + qc);
+              float e = exp2f(__uint_as_float(s_r[i + u]) * c - lse);
+              if (((p.causal & 1) && key > qi) || qi >= p.S || key >= p.S) e = 0.f;
+              pe[u] = e;
+              de[u] = e * (__uint_as_float(dp_r[i + u]) - dl);
+            }
+            pk[i >> 1] = pack_bf16x2(pe[0], pe[1]);
+            dk[i >> 1] = pack_bf16x2(de[0], de[1]);
           }
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           const int chunk = (cc * 4 + g) ^ (r & 7);
-          uint4 o;
-          o.x = pack_bf16x2(pv[g * 8 + 0], pv[g * 8 + 1]);
-          o.y = pack_bf16x2(pv[g * 8 + 2], pv[g * 8 + 3]);
-          o.z = pack_bf16x2(pv[g * 8 + 4], pv[g * 8 + 5]);
-          o.w = pack_bf16x2(pv[g * 8 + 6], pv[g * 8 + 7]);
-          *reinterpret_cast<uint4*>(pt_row + chunk * 16) = o;
-          o.x = pack_bf16x2(ds[g * 8 + 0], ds[g * 8 + 1]);
-          o.y = pack_bf16x2(ds[g * 8 + 2], ds[g * 8 + 3]);
-          o.z = pack_bf16x2(ds[g * 8 + 4], ds[g * 8 + 5]);
-          o.w = pack_bf16x2(ds[g * 8 + 6], ds[g * 8 + 7]);
-          *reinterpret_cast<uint4*>(dst_row + chunk * 16) = o;
+          *reinterpret_cast<uint4*>(pt_row + chunk * 16) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+          *reinterpret_cast<uint4*>(dst_row + chunk * 16) = make_uint4(dk[g * 4], dk[g * 4 + 1], dk[g * 4 + 2], dk[g * 4 + 3]);
         }
       }
+      if (!ok) break;
       tc_fence_before();
       mbar_arrive(s_empty);
       fence_proxy_async_smem();
       mbar_arrive(pds_full);
+      if (OVERLAP) continue;  // the dQ writers take it from here
       // dQ block: TMEM lanes are query rows now; this thread adds D/2 columns of row q0 + r.
       if (!mbar_wait_warp(mma2_done, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
@@ -303,6 +339,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       mbar_arrive(dq_empty);
     }
     // dK, dV: the last mma2_done covers every accumulation. TMEM lanes are key rows.
+    if (ok && n_it > 0 && OVERLAP) ok = mbar_wait_warp(mma2_done, (n_it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
     if (ok && n_it > 0) {
       tc_fence_after();
 #pragma unroll

@@ -281,6 +281,288 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Second-generation forward kernel (the default). Same roles and ring as above; what changed is the
+// softmax / accumulation scheme, which is where the first kernel spent its time:
+//   * O stays in TMEM for the whole key loop: every PV MMA accumulates into it. The running maximum
+//     is only raised when a block's maximum exceeds it by more than 8 (log2 units), so the rescale of
+//     O (TMEM load, multiply, TMEM store) is rare after the first blocks; until then P may reach 2^8,
+//     which bf16 / fp32 hold without loss.
+//   * the row sums are produced by the tensor core too: a second, 16-column MMA multiplies P by a tile
+//     of ones, so l accumulates next to O in TMEM from exactly the bf16 values the PV MMA consumed.
+//   * exponentials run two per MUFU instruction on packed bf16 (cvt.rn.bf16x2 + ex2.approx.bf16x2),
+//     whose result is already the A-operand format; the row maximum uses 3-input max with four
+//     independent chains.
+// ------------------------------------------------------------------------------------------------
+template <int ND>
+struct Fwd2Smem {
+  static constexpr int TILE = ND * 16384;
+  static constexpr int Q_OFF = 0;
+  static constexpr int KV_OFF = TILE;
+  static constexpr int P_OFF = KV_OFF + 3 * TILE;
+  static constexpr int ONES_OFF = P_OFF + 32768;      // 16 rows x 128 keys of bf16 1.0 (K-major, any swizzle: all equal)
+  static constexpr int BAR_OFF = ONES_OFF + 4096;
+  static constexpr int TOTAL = BAR_OFF + 128 + 1024;
+};
+
+template <int ND>
+__global__ void __launch_bounds__(FA_THREADS, ND == 1 ? 2 : 1)
+flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                  const __grid_constant__ CUtensorMap tmap_v, const FlashFwdParams p) {
+  constexpr int D = 64 * ND;
+  using L = Fwd2Smem<ND>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + L::Q_OFF;
+  uint8_t* sKV = smem + L::KV_OFF;
+  uint8_t* sP = smem + L::P_OFF;
+  uint8_t* sOnes = smem + L::ONES_OFF;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* q_full = bars;          // 1
+  uint64_t* kv_full = bars + 1;     // 3
+  uint64_t* kv_empty = bars + 4;    // 3
+  uint64_t* s_full = bars + 7;      // 1
+  uint64_t* s_empty = bars + 8;     // 1 (128 arrivals)
+  uint64_t* p_full = bars + 9;      // 1 (128 arrivals)
+  uint64_t* o_full = bars + 10;     // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = (p.S + FA_BM - 1) / FA_BM;
+  const int q_blk = nqb - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+  const int q0 = q_blk * FA_BM;
+  const int nkb_all = (p.S + FA_BN - 1) / FA_BN;
+  const int nkb = p.causal ? min(nkb_all, q_blk + 1) : nkb_all;
+  constexpr uint32_t TMEM_COLS = ND == 1 ? 256 : 512;
+  constexpr uint32_t O_COL = 128, L_COL = 128 + D;
+
+  for (int i = threadIdx.x; i < 4096 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(sOnes)[i] = 0x3f803f80u;  // bf16 1.0 pairs
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(s_empty, 128);
+    mbar_init(p_full, 128);
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  fence_proxy_async_smem();  // the ones tile is read by the tensor core
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, L::TILE);
+#pragma unroll
+      for (int a = 0; a < ND; ++a) tma_load_3d(sQ + a * 16384, &tmap_q, q_full, h * D + a * 64, q0, b);
+      for (int n = 0; n < 2 * nkb; ++n) {
+        const int slot = n % 3;
+        const uint32_t ph = (n / 3) & 1;
+        if (!mbar_wait(&kv_empty[slot], ph ^ 1, abort_flag, p.status, ERR_WAIT_EMPTY)) break;
+        mbar_expect_tx(&kv_full[slot], L::TILE);
+        const int j = n >> 1;
+        const CUtensorMap* tm = (n & 1) ? &tmap_v : &tmap_k;
+#pragma unroll
+        for (int a = 0; a < ND; ++a) tma_load_3d(sKV + slot * L::TILE + a * 16384, tm, &kv_full[slot], hk * D + a * 64, j * FA_BN, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_qk = make_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_pv = make_idesc_bf16(128, D, 0, 1);
+      const uint32_t idesc_l = make_idesc_bf16(128, 16, 0, 0);
+      const uint32_t q_base = smem_u32(sQ), p_base = smem_u32(sP), ones_base = smem_u32(sOnes);
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, ERR_WAIT_FULL);
+      auto issue_qk = [&](int j) -> bool {
+        const int n = 2 * j, slot = n % 3;
+        if (!mbar_wait(&kv_full[slot], (n / 3) & 1, abort_flag, p.status, ERR_WAIT_FULL)) return false;
+        if (j > 0 && !mbar_wait(s_empty, (j - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) return false;
+        tc_fence_after();
+        const uint32_t k_base = smem_u32(sKV + slot * L::TILE);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
+          umma_bf16(tmem_base, make_smem_desc(q_base + off, 16, 1024, 2), make_smem_desc(k_base + off, 16, 1024, 2), idesc_qk, ks > 0);
+        }
+        umma_commit(s_full);
+        umma_commit(&kv_empty[slot]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; ok && j < nkb; ++j) {
+        if (j + 1 < nkb) {
+          if (!issue_qk(j + 1)) break;
+        }
+        const int n = 2 * j + 1, slot = n % 3;
+        if (!mbar_wait(p_full, j & 1, abort_flag, p.status, ERR_WAIT_MISC)) break;
+        if (!mbar_wait(&kv_full[slot], (n / 3) & 1, abort_flag, p.status, ERR_WAIT_FULL)) break;
+        tc_fence_after();
+        const uint32_t v_base = smem_u32(sKV + slot * L::TILE);
+#pragma unroll
+        for (int ks = 0; ks < FA_BN / 16; ++ks) {
+          const uint64_t da = make_smem_desc(p_base + (ks / 4) * 16384 + (ks % 4) * 32, 16, 1024, 2);
+          const uint64_t db = make_smem_desc(v_base + ks * 2048, 16384, 1024, 2);
+          const uint32_t acc = (j > 0 || ks > 0) ? 1u : 0u;
+          umma_bf16(tmem_base + O_COL, da, db, idesc_pv, acc);
+          umma_bf16(tmem_base + L_COL, da, make_smem_desc(ones_base + (ks / 4) * 2048 + (ks % 4) * 32, 16, 1024, 2), idesc_l, acc);
+        }
+        umma_commit(o_full);
+        umma_commit(&kv_empty[slot]);
+      }
+    }
+  } else {
+    // ---------------- softmax warps: thread <-> query row ----------------
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const int row = q0 + r;
+    const uint32_t t_lane = tmem_base + (uint32_t(q * 32) << 16);
+    const float c = p.scale * 1.4426950408889634f;
+    float m_used = -INFINITY;  // the maximum the exponentials are taken against (scores, not yet scaled by c)
+    uint8_t* p_row = sP + (r >> 3) * 1024 + (r & 7) * 128;
+    bool ok = true;
+    for (int j = 0; j < nkb; ++j) {
+      if (!mbar_wait_warp(s_full, j & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int k0 = j * FA_BN;
+      const bool need_mask = (p.causal && k0 + FA_BN - 1 > q0) || (k0 + FA_BN > p.S);
+      const int kmax = p.causal ? min(row, p.S - 1) : p.S - 1;
+      // pass 1: block maximum, four independent chains
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t rr[32];
+        tmem_ld_32x32(t_lane + cc * 32, rr);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (k0 + cc * 32 + i > kmax) rr[i] = 0xff800000u;  // -inf
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          mx0 = fmax3(mx0, __uint_as_float(rr[i + 0]), __uint_as_float(rr[i + 1]));
+          mx1 = fmax3(mx1, __uint_as_float(rr[i + 2]), __uint_as_float(rr[i + 3]));
+          mx2 = fmax3(mx2, __uint_as_float(rr[i + 4]), __uint_as_float(rr[i + 5]));
+          mx3 = fmax3(mx3, __uint_as_float(rr[i + 6]), __uint_as_float(rr[i + 7]));
+        }
+      }
+      const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      // raise the working maximum only when the block exceeds it by more than 2^8
+      const bool raise = j == 0 || (m_blk - m_used) * c > 8.0f;
+      const float m_new = raise ? fmaxf(m_used, m_blk) : m_used;
+      const float alpha = (j == 0 || !raise) ? 1.0f : exp2f((m_used - m_new) * c);
+      m_used = m_new;
+      const bool any_rescale = __any_sync(0xffffffffu, j > 0 && raise);
+      if (j > 0) {
+        // PV of the previous block is complete: the P buffer is free and O / l are stable
+        if (!mbar_wait_warp(o_full, (j - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        if (any_rescale) {
+#pragma unroll 1
+          for (int cc = 0; cc < D / 32; ++cc) {
+            uint32_t rr[32];
+            tmem_ld_32x32(t_lane + O_COL + cc * 32, rr);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * alpha);
+            tmem_st_32x32(t_lane + O_COL + cc * 32, rr);
+          }
+          uint32_t ll[16];
+          tmem_ld_32x16(t_lane + L_COL, ll);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) ll[i] = __float_as_uint(__uint_as_float(ll[i]) * alpha);
+          tmem_st_32x16(t_lane + L_COL, ll);
+          tmem_st_wait();
+        }
+      }
+      const float mc = m_used * c;
+      // pass 2: P = exp2(S*c - m*c) as packed bf16 straight into the swizzled A-operand tile
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t rr[32];
+        tmem_ld_32x32(t_lane + cc * 32, rr);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (k0 + cc * 32 + i > kmax) rr[i] = 0xff800000u;
+        }
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          pk[i] = ex2_bf16x2(cvt_bf16x2(fmaf(__uint_as_float(rr[2 * i]), c, -mc), fmaf(__uint_as_float(rr[2 * i + 1]), c, -mc)));
+        uint8_t* dst = p_row + (cc >> 1) * 16384;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = ((cc & 1) * 4 + g) ^ (r & 7);
+          *reinterpret_cast<uint4*>(dst + chunk * 16) = make_uint4(pk[g * 4 + 0], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(s_empty);
+      fence_proxy_async_smem();
+      mbar_arrive(p_full);
+    }
+    if (ok) ok = mbar_wait_warp(o_full, (nkb - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+    if (ok) {
+      tc_fence_after();
+      uint32_t ll[16];
+      tmem_ld_32x16(t_lane + L_COL, ll);
+      tmem_ld_wait();
+      const float l = __uint_as_float(ll[0]);
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = p.out + ((size_t)b * p.S + row) * p.ld_o + h * D;
+#pragma unroll 1
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t rr[32];
+        tmem_ld_32x32(t_lane + O_COL + cc * 32, rr);
+        tmem_ld_wait();
+        if (row < p.S) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(rr[g * 8 + 0]) * inv_l, __uint_as_float(rr[g * 8 + 1]) * inv_l);
+            o.y = pack_bf16x2(__uint_as_float(rr[g * 8 + 2]) * inv_l, __uint_as_float(rr[g * 8 + 3]) * inv_l);
+            o.z = pack_bf16x2(__uint_as_float(rr[g * 8 + 4]) * inv_l, __uint_as_float(rr[g * 8 + 5]) * inv_l);
+            o.w = pack_bf16x2(__uint_as_float(rr[g * 8 + 6]) * inv_l, __uint_as_float(rr[g * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(dst + cc * 32 + g * 8) = o;
+          }
+        }
+      }
+      if (p.lse && row < p.S) p.lse[((size_t)b * p.H + h) * p.S + row] = m_used * c + log2f(l);
+      tc_fence_before();
+    }
+  }
+
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 // 3-D bf16 tensor map over a token-major buffer: dims {cols, S, B}, box {64, rows, 1}, 128B swizzle.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -334,10 +616,19 @@ extern "C" int inv_flash_attn_fwd(const void* q, const void* k, const void* v, v
   if (!configured) {
     cudaFuncSetAttribute(flash_fwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<1>::TOTAL);
     cudaFuncSetAttribute(flash_fwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<2>::TOTAL);
+    cudaFuncSetAttribute(flash_fwd2_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Smem<1>::TOTAL);
+    cudaFuncSetAttribute(flash_fwd2_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Smem<2>::TOTAL);
     configured = true;
   }
-  if (head_dim == 64) flash_fwd_kernel<1><<<grid, FA_THREADS, FwdSmem<1>::TOTAL, st>>>(tq, tk, tv, p);
-  else flash_fwd_kernel<2><<<grid, FA_THREADS, FwdSmem<2>::TOTAL, st>>>(tq, tk, tv, p);
+  const bool legacy = (causal & 8) != 0;  // bit 3 selects the first-generation kernel (A/B comparisons)
+  p.causal = causal & 1;
+  if (legacy) {
+    if (head_dim == 64) flash_fwd_kernel<1><<<grid, FA_THREADS, FwdSmem<1>::TOTAL, st>>>(tq, tk, tv, p);
+    else flash_fwd_kernel<2><<<grid, FA_THREADS, FwdSmem<2>::TOTAL, st>>>(tq, tk, tv, p);
+  } else {
+    if (head_dim == 64) flash_fwd2_kernel<1><<<grid, FA_THREADS, Fwd2Smem<1>::TOTAL, st>>>(tq, tk, tv, p);
+    else flash_fwd2_kernel<2><<<grid, FA_THREADS, Fwd2Smem<2>::TOTAL, st>>>(tq, tk, tv, p);
+  }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }

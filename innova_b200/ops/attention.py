@@ -24,6 +24,7 @@ _native.register_cuda_sigs({
 
 import os
 _BWD_DEBUG = int(os.environ.get('INV_ATTN_DEBUG', '0'))
+_FWD_DEBUG = int(os.environ.get('INV_ATTN_FWD_DEBUG', '0'))   # 8: first-generation forward kernel
 
 
 def _scratch_bytes(B, S, H, D):
@@ -40,7 +41,7 @@ class _FlashAttnFn(torch.autograd.Function):
         lse = torch.empty((B, H, S), dtype=torch.float32, device=qkv.device)
         base = qkv.data_ptr()
         rc = rt.lib().inv_flash_attn_fwd(base, base + H * D * 2, base + (H + Hkv) * D * 2, out.data_ptr(), lse.data_ptr(), B, S, H, Hkv, D,
-                                         ld, ld, ld, H * D, float(scale), int(causal), rt.status_tensor(qkv.device).data_ptr(),
+                                         ld, ld, ld, H * D, float(scale), int(causal) | _FWD_DEBUG, rt.status_tensor(qkv.device).data_ptr(),
                                          rt.stream_ptr())
         rt.check(rc, "inv_flash_attn_fwd")
         ctx.save_for_backward(qkv, out, lse)
