@@ -66,7 +66,7 @@ def test_fused_fsdp_step_matches_collective_baseline(tmp_path):
     assert float((p_a - p_b).norm() / p_b.norm()) < 5e-3
 
 
-def _tp_worker(rank, world, port, out):
+def _tp_worker(rank, world, port, out, variant=0):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
@@ -76,6 +76,9 @@ def _tp_worker(rank, world, port, out):
     from innova_b200.parallel.tp import TPDecoder
     cfg = TransformerConfig(vocab_size=1024, hidden_size=512, num_layers=2, num_heads=8, head_dim=64, ffn_hidden_size=1408, num_kv_heads=4,
                             max_seq_len=256)
+    if variant == 1:   # one KV head per rank, a vocabulary shard that is not a whole number of 128-row tiles, padded FFN shard
+        cfg = TransformerConfig(vocab_size=1152, hidden_size=512, num_layers=2, num_heads=8, head_dim=64, ffn_hidden_size=2752, num_kv_heads=2,
+                                max_seq_len=256)
     ids = torch.randint(0, 1024, (4, 48), generator=torch.Generator().manual_seed(0)).to(dev)
     res = {}
     for name, single in (("tp", False), ("one", True)):
@@ -96,10 +99,11 @@ def _tp_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_tensor_parallel_decode_matches_single_gpu(tmp_path):
+@pytest.mark.parametrize("variant", [0, 1])
+def test_tensor_parallel_decode_matches_single_gpu(tmp_path, variant):
     _need_gpus(2)
     out = str(tmp_path / "tp.pt")
-    mp.spawn(_tp_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    mp.spawn(_tp_worker, args=(2, _free_port(), out, variant), nprocs=2, join=True)
     res = torch.load(out)
     (a0, a1, ta, mm), (b0, b1, tb, _) = res["tp"], res["one"]
     rel = lambda x, y: float((x - y).norm() / y.norm())
