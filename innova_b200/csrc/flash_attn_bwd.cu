@@ -22,7 +22,7 @@ namespace inv {
 
 int make_tmap_tokens_bf16(CUtensorMap* out, const void* ptr, int cols, int S, int B, int ld, int box_rows);
 
-constexpr int FB_THREADS = 448;  // warp 0 TMA, warp 1 MMA, warps 2-9 softmax, warps 10-13 dQ writers (head_dim 64)
+constexpr int FB_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 softmax
 
 struct FlashBwdParams {
   const float* lse;    // [B, H, S], log2 domain: log2(sum exp(scores))
@@ -101,7 +101,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     mbar_init(s_empty, 256);
     mbar_init(pds_full, 256);
     mbar_init(mma2_done, 1);
-    mbar_init(dq_empty, OVERLAP ? 128 : 256);
+    mbar_init(dq_empty, 256);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_q);
@@ -203,37 +203,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         umma_commit(&q_empty[st]);
       }
     }
-  } else if (warp >= 10) {
-    // ---------------- dQ writers (head_dim 64): drain each block's dQ to the fp32 accumulator while the
-    // softmax warps already work on the next block ----------------
-    if (OVERLAP) {
-      const int q = warp & 3;
-      const int r = q * 32 + lane;
-      const uint32_t t_lane = tmem_base + (uint32_t(q * 32) << 16);
-      for (int it = 0; it < n_it; ++it) {
-        const int h = hk * G + it / nq_it;
-        const int q0 = (i0 + it % nq_it) * 128;
-        if (!mbar_wait_warp(mma2_done, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) break;
-        tc_fence_after();
-        const int qrow = q0 + r;
-#pragma unroll 1
-        for (int cc = 0; cc < D / 32; ++cc) {
-          uint32_t rr[32];
-          tmem_ld_32x32(t_lane + DQ_COL + cc * 32, rr);
-          tmem_ld_wait();
-          if (qrow < p.S && !(p.causal & 2)) {
-            float* dst = p.dq_acc + ((size_t)b * p.S + qrow) * ((size_t)p.H * D) + h * D + cc * 32;
-#pragma unroll
-            for (int g = 0; g < 8; ++g)
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + g * 4), "f"(__uint_as_float(rr[g * 4])),
-                           "f"(__uint_as_float(rr[g * 4 + 1])), "f"(__uint_as_float(rr[g * 4 + 2])), "f"(__uint_as_float(rr[g * 4 + 3]))
-                           : "memory");
-          }
-        }
-        tc_fence_before();
-        mbar_arrive(dq_empty);
-      }
-    }
   } else {
     // ---------------- softmax warps ----------------
     const int q = warp & 3;            // TMEM lane quarter
@@ -254,17 +223,22 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       const float* lse_row = p.lse + ((size_t)b * p.H + h) * p.S;
       const float* dl_row = p.delta + ((size_t)b * p.H + h) * p.S;
       const bool need_mask = ((p.causal & 1) && q0 < k0 + 127) || (q0 + 128 > p.S) || (k0 + 128 > p.S);
-#pragma unroll 1
+      // both 32-column chunks of S^T and dP^T come in with four back-to-back TMEM loads and one wait; the columns
+      // are handed back to the tensor core before the arithmetic starts, so the next block's first MMAs overlap it
+      uint32_t s_all[64], dp_all[64];
+      tmem_ld_32x32(t_lane + ST_COL + hf * 64, s_all);
+      tmem_ld_32x32(t_lane + DPT_COL + hf * 64, dp_all);
+      tmem_ld_32x32(t_lane + ST_COL + hf * 64 + 32, s_all + 32);
+      tmem_ld_32x32(t_lane + DPT_COL + hf * 64 + 32, dp_all + 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(s_empty);
+#pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int col0 = hf * 64 + cc * 32;
-        uint32_t s_r[32], dp_r[32];
-        tmem_ld_32x32(t_lane + ST_COL + col0, s_r);
-        tmem_ld_32x32(t_lane + DPT_COL + col0, dp_r);
-        tmem_ld_wait();
-        if (OVERLAP && cc == 0 && it > 0) {
-          // the P^T / dS^T tiles are still operands of the previous block's second MMA group until it completes
-          if (!mbar_wait_warp(mma2_done, (it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
-        }
+        const uint32_t* s_r = s_all + cc * 32;
+        const uint32_t* dp_r = dp_all + cc * 32;
+
         uint32_t pk[16], dk[16];  // P^T and dS^T of this chunk as packed bf16 pairs
         if (!need_mask && vec_ok) {
           // interior block: no predicates, statistics fetched as 16-byte broadcast loads; exponentials run two
@@ -310,12 +284,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           *reinterpret_cast<uint4*>(dst_row + chunk * 16) = make_uint4(dk[g * 4], dk[g * 4 + 1], dk[g * 4 + 2], dk[g * 4 + 3]);
         }
       }
-      if (!ok) break;
-      tc_fence_before();
-      mbar_arrive(s_empty);
       fence_proxy_async_smem();
       mbar_arrive(pds_full);
-      if (OVERLAP) continue;  // the dQ writers take it from here
       // dQ block: TMEM lanes are query rows now; this thread adds D/2 columns of row q0 + r.
       if (!mbar_wait_warp(mma2_done, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
@@ -339,7 +309,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       mbar_arrive(dq_empty);
     }
     // dK, dV: the last mma2_done covers every accumulation. TMEM lanes are key rows.
-    if (ok && n_it > 0 && OVERLAP) ok = mbar_wait_warp(mma2_done, (n_it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
     if (ok && n_it > 0) {
       tc_fence_after();
 #pragma unroll

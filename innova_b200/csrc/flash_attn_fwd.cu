@@ -442,25 +442,28 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       const int k0 = j * FA_BN;
       const bool need_mask = (p.causal && k0 + FA_BN - 1 > q0) || (k0 + FA_BN > p.S);
       const int kmax = p.causal ? min(row, p.S - 1) : p.S - 1;
-      // pass 1: block maximum, four independent chains
+      // the whole score row moves into registers with four back-to-back TMEM loads and one wait (the load latency
+      // is paid once per block, not once per 32 columns), and S is handed back to the tensor core right away
+      uint32_t sr[128];
+      tmem_ld_32x32(t_lane, sr);
+      tmem_ld_32x32(t_lane + 32, sr + 32);
+      tmem_ld_32x32(t_lane + 64, sr + 64);
+      tmem_ld_32x32(t_lane + 96, sr + 96);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(s_empty);
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (k0 + i > kmax) sr[i] = 0xff800000u;  // -inf
+      }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t rr[32];
-        tmem_ld_32x32(t_lane + cc * 32, rr);
-        tmem_ld_wait();
-        if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (k0 + cc * 32 + i > kmax) rr[i] = 0xff800000u;  // -inf
-        }
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          mx0 = fmax3(mx0, __uint_as_float(rr[i + 0]), __uint_as_float(rr[i + 1]));
-          mx1 = fmax3(mx1, __uint_as_float(rr[i + 2]), __uint_as_float(rr[i + 3]));
-          mx2 = fmax3(mx2, __uint_as_float(rr[i + 4]), __uint_as_float(rr[i + 5]));
-          mx3 = fmax3(mx3, __uint_as_float(rr[i + 6]), __uint_as_float(rr[i + 7]));
-        }
+      for (int i = 0; i < 128; i += 8) {
+        mx0 = fmax3(mx0, __uint_as_float(sr[i + 0]), __uint_as_float(sr[i + 1]));
+        mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+        mx2 = fmax3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
+        mx3 = fmax3(mx3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
       }
       const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       // raise the working maximum only when the block exceeds it by more than 2^8
@@ -490,24 +493,17 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           for (int i = 0; i < 16; ++i) ll[i] = __float_as_uint(__uint_as_float(ll[i]) * alpha);
           tmem_st_32x16(t_lane + L_COL, ll);
           tmem_st_wait();
+          tc_fence_before();
         }
       }
       const float mc = m_used * c;
-      // pass 2: P = exp2(S*c - m*c) as packed bf16 straight into the swizzled A-operand tile
-#pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t rr[32];
-        tmem_ld_32x32(t_lane + cc * 32, rr);
-        tmem_ld_wait();
-        if (need_mask) {
+      // P = exp2(S*c - m*c) as packed bf16 straight into the swizzled A-operand tile
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (k0 + cc * 32 + i > kmax) rr[i] = 0xff800000u;
-        }
+      for (int cc = 0; cc < 4; ++cc) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i)
-          pk[i] = ex2_bf16x2(cvt_bf16x2(fmaf(__uint_as_float(rr[2 * i]), c, -mc), fmaf(__uint_as_float(rr[2 * i + 1]), c, -mc)));
+          pk[i] = ex2_bf16x2(cvt_bf16x2(fmaf(__uint_as_float(sr[cc * 32 + 2 * i]), c, -mc), fmaf(__uint_as_float(sr[cc * 32 + 2 * i + 1]), c, -mc)));
         uint8_t* dst = p_row + (cc >> 1) * 16384;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -515,8 +511,6 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           *reinterpret_cast<uint4*>(dst + chunk * 16) = make_uint4(pk[g * 4 + 0], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
         }
       }
-      tc_fence_before();
-      mbar_arrive(s_empty);
       fence_proxy_async_smem();
       mbar_arrive(p_full);
     }

@@ -50,11 +50,13 @@ __global__ void __launch_bounds__(256) block_quant_kernel(const TIn* __restrict_
     const bool ok = i < n;
     const float w = ok ? (float)in[i] : 0.f;
     const float amax = warp_max(fabsf(w));
-    float scale = amax < 1e-10f ? 1.f : amax;
+    const bool dead = amax < 1e-10f;  // an all-zero block keeps scale 0, so that it dequantises to exactly zero
+    float scale = dead ? 1.f : amax;
     float q;
     int code;
     if (mode <= 1) {
       code = nearest_sorted(cb, K, w / scale);
+      if (dead) scale = 0.f;
       q = cb[code] * scale;
     } else if (mode == 2) {
       const bool keep = fabsf(w) > 0.5f * amax && amax > 0.f;

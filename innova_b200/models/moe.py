@@ -20,20 +20,30 @@ from .dense import Attention, FFN, Norm, _ste
 
 
 class MoELayer(nn.Module):
-    def __init__(self, cfg: TransformerConfig, dtype):
+    """``ep_world`` > 1: only ``num_experts / ep_world`` experts are resident (expert parallelism); the model sets
+    ``ep`` (the shared ``EPContext``) once the parameters are on their device."""
+
+    def __init__(self, cfg: TransformerConfig, dtype, ep_world: int = 1):
         super().__init__()
         self.cfg = cfg
         E, D, Fh = cfg.num_experts, cfg.hidden_size, cfg.moe_ffn_hidden_size or cfg.ffn_hidden_size
+        assert E % ep_world == 0
         self.router = nn.Linear(D, E, bias=False, dtype=dtype)
-        self.w_gate_up = nn.Parameter(torch.empty(E, 2 * Fh, D, dtype=dtype))
-        self.w_down = nn.Parameter(torch.empty(E, D, Fh, dtype=dtype))
+        self.w_gate_up = nn.Parameter(torch.empty(E // ep_world, 2 * Fh, D, dtype=dtype))
+        self.w_down = nn.Parameter(torch.empty(E // ep_world, D, Fh, dtype=dtype))
         self.shared = FFN(cfg, dtype, hidden=Fh) if cfg.shared_expert else None
         self.last_counts = None
+        self.ep = None
 
     def forward(self, h, residual):
         cfg = self.cfg
-        y, aux, counts = moe_ffn(h, self.router.weight, _ste(self.w_gate_up, cfg), _ste(self.w_down, cfg), residual, cfg.top_k, cfg.lb_coef,
-                                 cfg.z_coef)
+        if self.ep is not None:
+            from ..parallel.expert_parallel import _EPMoEFn
+            y, aux, counts = _EPMoEFn.apply(h, self.router.weight, _ste(self.w_gate_up, cfg), _ste(self.w_down, cfg), residual, self.ep, cfg.top_k,
+                                            cfg.lb_coef, cfg.z_coef)
+        else:
+            y, aux, counts = moe_ffn(h, self.router.weight, _ste(self.w_gate_up, cfg), _ste(self.w_down, cfg), residual, cfg.top_k, cfg.lb_coef,
+                                     cfg.z_coef)
         self.last_counts = counts
         if self.shared is not None:
             y = self.shared(h, y)
@@ -41,12 +51,12 @@ class MoELayer(nn.Module):
 
 
 class MoEBlock(nn.Module):
-    def __init__(self, cfg: TransformerConfig, dtype):
+    def __init__(self, cfg: TransformerConfig, dtype, ep_world: int = 1):
         super().__init__()
         self.attention_norm = Norm(cfg.hidden_size, cfg.norm, cfg.norm_eps, dtype)
         self.attention = Attention(cfg, dtype)
         self.ffn_norm = Norm(cfg.hidden_size, cfg.norm, cfg.norm_eps, dtype)
-        self.moe = MoELayer(cfg, dtype)
+        self.moe = MoELayer(cfg, dtype, ep_world)
 
     def forward(self, x, rope, positions=None):
         x = self.attention(self.attention_norm(x), x, rope, positions)
@@ -54,27 +64,47 @@ class MoEBlock(nn.Module):
 
 
 class MoEModel(nn.Module):
-    def __init__(self, cfg: TransformerConfig, dtype=torch.bfloat16, device=None, seed=42):
+    def __init__(self, cfg: TransformerConfig, dtype=torch.bfloat16, device=None, seed=42, ep_group=None, ep_max_tokens: int = 0,
+                 ep_capacity_factor=None):
+        """``ep_group``: process group over which the experts are sharded (expert e on rank e // (E / W)); tokens are
+        exchanged over peer memory (parallel/expert_parallel.py). ``ep_max_tokens``: tokens per rank per step;
+        ``ep_capacity_factor``: receive capacity per rank in units of its average load (None = dropless)."""
         super().__init__()
         assert cfg.num_experts > 0
         self.cfg = cfg
+        import torch.distributed as dist
+        self.ep_group = ep_group
+        self.ep_world = dist.get_world_size(ep_group) if (ep_group is not None and dist.is_initialized()) else 1
+        self.ep_rank = dist.get_rank(ep_group) if self.ep_world > 1 else 0
         Vp, E = cfg.padded_vocab, cfg.hidden_size
         self.tok_embeddings = nn.Embedding(Vp, E, dtype=dtype)
         self.pos_embeddings = nn.Embedding(cfg.max_seq_len, E, dtype=dtype) if cfg.positions == "learned" else None
-        self.layers = nn.ModuleList([MoEBlock(cfg, dtype) for _ in range(cfg.num_layers)])
+        self.layers = nn.ModuleList([MoEBlock(cfg, dtype, self.ep_world) for _ in range(cfg.num_layers)])
         self.norm = Norm(E, cfg.norm, cfg.norm_eps, dtype)
         self.lm_head = nn.Linear(E, Vp, bias=False, dtype=dtype)
         self._rope = None
         self.reset_parameters(seed)
         if device is not None:
             self.to(device)
+        if self.ep_world > 1:
+            from ..parallel.expert_parallel import EPContext
+            dev = next(self.parameters()).device
+            ep = EPContext(ep_group, cfg.num_experts, cfg.hidden_size, ep_max_tokens or cfg.max_seq_len, cfg.top_k, dev, ep_capacity_factor)
+            for blk in self.layers:
+                blk.moe.ep = ep
+
+    def expert_parameters(self):
+        """Parameters that exist once per expert (sharded under expert parallelism, never all-reduced)."""
+        return [p for n, p in self.named_parameters() if n.endswith("moe.w_gate_up") or n.endswith("moe.w_down")]
 
     @torch.no_grad()
     def reset_parameters(self, seed=42):
         g = torch.Generator().manual_seed(seed)
+        g_local = torch.Generator().manual_seed(seed * 1000 + 17 + self.ep_rank)    # experts differ between ranks
         for name, p in self.named_parameters():
             if p.dim() >= 2:
-                w = torch.empty(p.shape, dtype=torch.float32).normal_(0.0, 0.02, generator=g)
+                local = self.ep_world > 1 and (name.endswith("moe.w_gate_up") or name.endswith("moe.w_down"))
+                w = torch.empty(p.shape, dtype=torch.float32).normal_(0.0, 0.02, generator=g_local if local else g)
                 if name.endswith("o_proj.weight") or name.endswith("down_proj.weight") or name.endswith("w_down"):
                     w.mul_(1.0 / math.sqrt(2.0 * self.cfg.num_layers))
                 p.copy_(w.to(p.dtype))

@@ -104,8 +104,8 @@ def _quant_cpu(w, fmt, cb, block):
     blk, scale, n = _normalise(w, block)
     if fmt in ("oil8", "oil4"):
         idx = _nearest(cb, blk / scale)
-        q = cb[idx] * scale
-        sc = scale
+        sc = torch.where(blk.abs().amax(dim=1, keepdim=True) < 1e-10, torch.zeros_like(scale), scale)   # all-zero blocks stay zero
+        q = cb[idx] * sc
     elif fmt == "spark":
         amax = blk.abs().amax(dim=1, keepdim=True)
         keep = (blk.abs() > 0.5 * amax) & (amax > 0)

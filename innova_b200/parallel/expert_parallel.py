@@ -295,3 +295,56 @@ class _AllGatherRows(torch.autograd.Function):
         dist.all_reduce(g, group=ctx.group)
         r = dist.get_rank(ctx.group)
         return g[r * ctx.T:(r + 1) * ctx.T], None
+
+
+class _ParamBag(nn.Module):
+    def __init__(self, named):
+        super().__init__()
+        for i, (n, p) in enumerate(named):
+            self.register_parameter(f"p{i}_" + n.replace(".", "_"), p)
+
+
+class ExpertParallelEngine:
+    """Optimizer for a model whose experts are sharded over the group and whose other parameters are replicated:
+    replicated gradients are averaged over the ranks (``DDPFlatEngine``), expert gradients stay local (they already
+    hold every rank's contribution), and both parts are clipped by the one global norm."""
+
+    def __init__(self, model, group=None, **kw):
+        from ..training.flat_engine import FlatParamEngine
+        from .ddp import DDPFlatEngine
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        expert_ids = {id(p) for p in model.expert_parameters()}
+        named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        self.rep = DDPFlatEngine(_ParamBag([(n, p) for n, p in named if id(p) not in expert_ids]), group=group, **kw)
+        self.exp = FlatParamEngine(_ParamBag([(n, p) for n, p in named if id(p) in expert_ids]), **kw)
+        self.entries = self.rep.entries + self.exp.entries
+        self.step_count = 0
+
+    @property
+    def flat_grad(self):
+        return self.rep.flat_grad
+
+    @property
+    def flat_param(self):
+        return self.rep.flat_param
+
+    def current_lr(self):
+        return self.rep.current_lr()
+
+    def zero_grad(self):
+        self.rep.zero_grad()
+        self.exp.zero_grad()
+
+    def step(self, grad_scale: float = 1.0):
+        self.step_count += 1
+        self.rep.sync_gradients()                       # replicated part: SUM over ranks
+        a = self.rep.compute_gnorm_sq().clone()
+        b = self.exp.compute_gnorm_sq().clone()
+        if self.world > 1:
+            dist.all_reduce(b, group=self.group)       # every rank holds different experts
+        total = a + b
+        gs = grad_scale / self.world
+        FlatParamEngineStep = type(self.exp).step
+        FlatParamEngineStep(self.rep, gs, total)        # skip the DDP engine's own sync: already done above
+        self.exp.step(gs, total)

@@ -162,10 +162,12 @@ class FlatParamEngine:
             self.gnorm_sq.add_((g * g).sum())
         return self.gnorm_sq
 
-    def step(self, grad_scale: float = 1.0):
-        """Clip by global norm, AdamW on the owned shard, write the compute copy, clear gradients."""
+    def step(self, grad_scale: float = 1.0, gnorm_sq: Optional[torch.Tensor] = None):
+        """Clip by global norm, AdamW on the owned shard, write the compute copy, clear gradients.
+        ``gnorm_sq`` (device scalar) overrides the squared gradient norm used for clipping when this engine
+        holds only part of the parameters."""
         self.step_count += 1
-        gn = self.compute_gnorm_sq()
+        gn = gnorm_sq if gnorm_sq is not None else self.compute_gnorm_sq()
         lo, hi = self.shard_lo, self.shard_hi
         d_hi = min(hi, self.decay_end)
         self._adamw_range(lo, d_hi, self.weight_decay, grad_scale, gn)

@@ -337,3 +337,51 @@ def test_cpu_offload_and_zero_offload_manager():
     x = torch.randn(2, 8, requires_grad=True)
     blocks[1](blocks[0](x)).sum().backward()
     assert ck.saved_calls == 2 and x.grad is not None
+
+
+class _ToyEP(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        torch.manual_seed(0)
+        self.shared = torch.nn.Linear(8, 8)
+        self.local = torch.nn.Parameter(torch.randn(4, 8))
+
+    def expert_parameters(self):
+        return [self.local]
+
+
+def _epeng_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from innova_b200.parallel.expert_parallel import ExpertParallelEngine
+    m = _ToyEP()
+    eng = ExpertParallelEngine(m, lr=1e-2, weight_decay=0.0, max_grad_norm=1.0)
+    g = torch.Generator().manual_seed(10 + rank)
+    m.shared.weight.main_grad.copy_(torch.randn(8, 8, generator=g))
+    m.shared.bias.main_grad.copy_(torch.randn(8, generator=g))
+    m.local.main_grad.copy_(torch.randn(4, 8, generator=g))
+    grads = {n: p.main_grad.clone() for n, p in m.named_parameters()}
+    before = {n: p.detach().clone() for n, p in m.named_parameters()}
+    eng.step()
+    torch.save({"grads": grads, "before": before, "after": {n: p.detach().clone() for n, p in m.named_parameters()}}, out + f".{rank}")
+    dist.destroy_process_group()
+
+
+def test_expert_parallel_engine_syncs_only_replicated_and_clips_jointly(tmp_path):
+    out = str(tmp_path / "epe")
+    mp.spawn(_epeng_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    r = [torch.load(out + f".{k}") for k in range(2)]
+    W = 2
+    rep = {n: (r[0]["grads"][n] + r[1]["grads"][n]) / W for n in ("shared.weight", "shared.bias")}
+    loc = [r[k]["grads"]["local"] / W for k in range(2)]
+    norm = torch.sqrt(sum(v.pow(2).sum() for v in rep.values()) + sum(v.pow(2).sum() for v in loc))
+    clip = min(1.0, 1.0 / float(norm + 1e-6))
+    for k in range(2):
+        assert torch.equal(r[0]["after"]["shared.weight"], r[1]["after"]["shared.weight"])       # replicas stay identical
+        # first Adam step moves every weight by lr * sign(g) (bias-corrected m / sqrt(v)), independent of the clip factor,
+        # so check the direction against the gradient each part should have seen
+        d = r[k]["after"]["local"] - r[k]["before"]["local"]
+        assert torch.equal(torch.sign(d), -torch.sign(loc[k])) and float(d.abs().max()) <= 1e-2 + 1e-6
+        ds = r[k]["after"]["shared.weight"] - r[k]["before"]["shared.weight"]
+        assert torch.equal(torch.sign(ds), -torch.sign(rep["shared.weight"]))
+    assert 0 < clip <= 1
