@@ -127,6 +127,79 @@ def bench_ce(a):
             "hbm_peak_gbs_%s" % kind: hbm}
 
 
+def bench_decode_parts(a):
+    """The kernels of one decode layer at the 7B shape with ``--batch`` tokens in flight. Every operator is captured
+    32 times into a CUDA graph (eight rotating weight copies, so the weights stream from HBM as they do across the
+    layers of a model) and the graph replay is timed: no launch gaps, no cache flush artefacts."""
+    from innova_b200 import ops
+    from innova_b200.inference.kv_cache import PagedKVCache
+    from innova_b200.ops import runtime as rt
+    from innova_b200.ops.oil_linear import oil_linear, quantize_weight
+    B, E, H, Hkv, D, F = a.batch, 4096, 32, 8, 128, 11008
+    ctx_len, REP, COPIES = a.seq, 32, 8
+    hbm, _, kind = peaks()
+    out = {"kernel": "decode_parts", "batch": B, "context": ctx_len, "method": "cuda graph of 32 calls, 8 rotating operand copies"}
+
+    def timed(fns):
+        if a.eager:   # plain launches (for profilers); the reported time then includes launch gaps
+            for f in fns[:COPIES]:
+                f()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(REP):
+                fns[i % len(fns)]()
+            e1.record()
+            torch.cuda.synchronize()
+            return 1e3 * e0.elapsed_time(e1) / REP
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for f in fns[:COPIES]:
+                f()
+        torch.cuda.current_stream().wait_stream(s)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(REP):
+                fns[i % len(fns)]()
+        ts = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        rt.check_status()
+        return 1e3 * sorted(ts)[2] / REP
+
+    x = (torch.randn(B, E, device="cuda") * 0.5).bfloat16()
+    for name, (N, K) in {"qkv": ((H + 2 * Hkv) * D, E), "o": (E, H * D), "gate_up": (2 * F, E), "down": (E, F // 64 * 64)}.items():
+        qws = [quantize_weight(torch.randn(N, K, device="cuda") * 0.02, "oil4") for _ in range(COPIES)]
+        xin = (torch.randn(B, K, device="cuda") * 0.5).bfloat16()
+        us = timed([(lambda q=q: oil_linear(xin, q)) for q in qws])
+        out[name + "_us"] = us
+        out[name + "_frac_of_%s_hbm" % kind] = (N * K / 2 + N * K / 32 * 2) / (us * 1e-6) / 1e9 / hbm
+        del qws
+    w = torch.ones(E, device="cuda", dtype=torch.bfloat16)
+    out["rms_norm_us"] = timed([lambda: ops.rms_norm(x, w, 1e-5)])
+    caches = []
+    k = (torch.randn(B, ctx_len, Hkv * D, device="cuda") * 0.5).bfloat16()
+    for _ in range(COPIES):
+        c = PagedKVCache(1, Hkv, D, B, ctx_len + 16, "cuda", "oil4")
+        for b in range(B):
+            c.reserve(b, ctx_len + 1)
+        c.append(0, k, k, list(range(B)), [0] * B)
+        c.commit(list(range(B)), [ctx_len] * B)
+        caches.append(c)
+    q = (torch.randn(B, H * D, device="cuda") * 0.5).bfloat16()
+    o = torch.empty(B, H * D, dtype=torch.bfloat16, device="cuda")
+    us = timed([(lambda c=c: c.decode_attention(0, q, H, D ** -0.5, out=o)) for c in caches])
+    out["paged_decode_us"] = us
+    out["paged_decode_frac_of_%s_hbm" % kind] = (B * ctx_len * caches[0].bytes_per_token()) / (us * 1e-6) / 1e9 / hbm
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default="gemm")
@@ -144,10 +217,11 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--compare", action="store_true", help="also time the library GEMM")
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="decode parts: plain launches instead of a CUDA graph")
     a = ap.parse_args()
     a.causal = bool(a.causal)
-    kernels = {"gemm": bench_gemm, "attn": bench_attn, "norm": bench_norm, "ce": bench_ce}
-    names = list(kernels) if a.kernel == "all" else [a.kernel]
+    kernels = {"gemm": bench_gemm, "attn": bench_attn, "norm": bench_norm, "ce": bench_ce, "decode": bench_decode_parts}
+    names = [k for k in kernels if k != "decode"] if a.kernel == "all" else [a.kernel]
     for n in names:
         if n == "norm" and a.kernel == "all":
             a.m, a.n = 65536, 768

@@ -43,14 +43,20 @@ __device__ bool wait_all_flags(const uint32_t* flags, int W, uint32_t epoch, int
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
   if (threadIdx.x < W) {
-    const uint64_t t0 = globaltimer_ns();
+    // tight polling; the (slow) global timer is read only every 256 polls
+    uint64_t t0 = 0;
+    uint32_t spins = 0;
     while ((int32_t)(ld_acquire_sys(flags + threadIdx.x) - epoch) < 0) {
-      if (globaltimer_ns() - t0 > PEER_WAIT_NS) {
-        s_ok = 0;
-        if (status) atomicCAS(status, 0, ERR_WAIT_PEER);
-        break;
+      if ((++spins & 0xffu) == 0) {
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > PEER_WAIT_NS) {
+          s_ok = 0;
+          if (status) atomicCAS(status, 0, ERR_WAIT_PEER);
+          break;
+        }
       }
-      __nanosleep(200);
     }
   }
   __syncthreads();

@@ -47,7 +47,8 @@ struct BwdSmem {
   static constexpr int DO_OFF = Q_OFF + STAGES * TILE;
   static constexpr int PT_OFF = DO_OFF + STAGES * TILE;
   static constexpr int DST_OFF = PT_OFF + 32768;
-  static constexpr int BAR_OFF = DST_OFF + 32768;
+  static constexpr int STAT_OFF = DST_OFF + 32768;     // lse and delta of the current query block, two stages
+  static constexpr int BAR_OFF = STAT_OFF + 2 * 2 * 128 * 4;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
@@ -70,6 +71,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint8_t* sdO = smem + L::DO_OFF;
   uint8_t* sPt = smem + L::PT_OFF;
   uint8_t* sdSt = smem + L::DST_OFF;
+  float* sStat = reinterpret_cast<float*>(smem + L::STAT_OFF);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* kv_full = bars;        // 1
   uint64_t* q_full = bars + 1;     // STAGES
@@ -218,10 +220,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     for (int it = 0; it < n_it; ++it) {
       const int h = hk * G + it / nq_it;
       const int q0 = (i0 + it % nq_it) * 128;
-      if (!mbar_wait_warp(s_full, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
-      tc_fence_after();
       const float* lse_row = p.lse + ((size_t)b * p.H + h) * p.S;
       const float* dl_row = p.delta + ((size_t)b * p.H + h) * p.S;
+      // the block's row statistics go to shared memory first (one global load per thread, issued before the wait
+      // for the MMAs so that its latency is hidden): the inner loop then reads them as broadcast 16-byte loads
+      float* stat = sStat + (it & 1) * 256;
+      {
+        const int st = threadIdx.x - 64;  // 0..255 over the softmax warps
+        const int qi = min(q0 + (st & 127), p.S - 1);
+        stat[st] = (st < 128) ? __ldg(lse_row + qi) : __ldg(dl_row + qi);
+      }
+      if (!mbar_wait_warp(s_full, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      asm volatile("bar.sync 1, 256;" ::: "memory");  // the statistics of this block are in place (softmax warps only)
       const bool need_mask = ((p.causal & 1) && q0 < k0 + 127) || (q0 + 128 > p.S) || (k0 + 128 > p.S);
       // both 32-column chunks of S^T and dP^T come in with four back-to-back TMEM loads and one wait; the columns
       // are handed back to the tensor core before the arithmetic starts, so the next block's first MMAs overlap it
@@ -240,23 +251,21 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const uint32_t* dp_r = dp_all + cc * 32;
 
         uint32_t pk[16], dk[16];  // P^T and dS^T of this chunk as packed bf16 pairs
-        if (!need_mask && vec_ok) {
-          // interior block: no predicates, statistics fetched as 16-byte broadcast loads; exponentials run two
-          // per MUFU instruction on packed bf16 and dS = P * (dP - D) is one packed multiply per pair
-          const float4* l4 = reinterpret_cast<const float4*>(lse_row + q0 + col0);
-          const float4* d4 = reinterpret_cast<const float4*>(dl_row + q0 + col0);
+        if (!need_mask) {
+          // interior block: no predicates, statistics fetched as 16-byte broadcast loads; one MUFU op per element,
+          // bf16 packing on the integer pipe
+          const float4* l4 = reinterpret_cast<const float4*>(stat + col0);
+          const float4* d4 = reinterpret_cast<const float4*>(stat + 128 + col0);
 #pragma unroll
           for (int i4 = 0; i4 < 8; ++i4) {
-            const float4 l = __ldg(l4 + i4), dl = __ldg(d4 + i4);
+            const float4 l = l4[i4], dl = d4[i4];
             const int i = i4 * 4;
-            const uint32_t p01 = ex2_bf16x2(cvt_bf16x2(fmaf(__uint_as_float(s_r[i]), c, -l.x), fmaf(__uint_as_float(s_r[i + 1]), c, -l.y)));
-            const uint32_t p23 = ex2_bf16x2(cvt_bf16x2(fmaf(__uint_as_float(s_r[i + 2]), c, -l.z), fmaf(__uint_as_float(s_r[i + 3]), c, -l.w)));
-            const uint32_t t01 = cvt_bf16x2(__uint_as_float(dp_r[i]) - dl.x, __uint_as_float(dp_r[i + 1]) - dl.y);
-            const uint32_t t23 = cvt_bf16x2(__uint_as_float(dp_r[i + 2]) - dl.z, __uint_as_float(dp_r[i + 3]) - dl.w);
-            pk[i4 * 2] = p01;
-            pk[i4 * 2 + 1] = p23;
-            dk[i4 * 2] = mul_bf16x2(p01, t01);
-            dk[i4 * 2 + 1] = mul_bf16x2(p23, t23);
+            const float e0 = exp2f(fmaf(__uint_as_float(s_r[i]), c, -l.x)), e1 = exp2f(fmaf(__uint_as_float(s_r[i + 1]), c, -l.y));
+            const float e2 = exp2f(fmaf(__uint_as_float(s_r[i + 2]), c, -l.z)), e3 = exp2f(fmaf(__uint_as_float(s_r[i + 3]), c, -l.w));
+            pk[i4 * 2] = pack_bf16x2_int(e0, e1);
+            pk[i4 * 2 + 1] = pack_bf16x2_int(e2, e3);
+            dk[i4 * 2] = pack_bf16x2_int(e0 * (__uint_as_float(dp_r[i]) - dl.x), e1 * (__uint_as_float(dp_r[i + 1]) - dl.y));
+            dk[i4 * 2 + 1] = pack_bf16x2_int(e2 * (__uint_as_float(dp_r[i + 2]) - dl.z), e3 * (__uint_as_float(dp_r[i + 3]) - dl.w));
           }
         } else {
 #pragma unroll
@@ -273,8 +282,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
               pe[u] = e;
               de[u] = e * (__uint_as_float(dp_r[i + u]) - dl);
             }
-            pk[i >> 1] = pack_bf16x2(pe[0], pe[1]);
-            dk[i >> 1] = pack_bf16x2(de[0], de[1]);
+            pk[i >> 1] = pack_bf16x2_int(pe[0], pe[1]);
+            dk[i >> 1] = pack_bf16x2_int(de[0], de[1]);
           }
         }
 #pragma unroll

@@ -557,6 +557,259 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Third-generation forward kernel (the default). Cycle stamps of the second generation showed where a
+// key block's ~4000 cycles went: ~1500 waiting for a K tile (three ring slots: the load of K_{j+1} could
+// not start before P_{j-1}V_{j-1} had finished), ~1000 waiting for the previous PV MMA before the
+// exponentials even started, ~1200 in the PV MMA plus a separate row-sum MMA, and ~1800 in the
+// exponential phase itself (MUFU-bound). This version
+//   * keeps P in tensor memory: the softmax threads write packed bf16 pairs with tcgen05.st and the PV MMA
+//     reads its A operand from TMEM, so the 32 KB shared-memory P tile, its stores and the proxy fence are
+//     gone and the K/V ring grows to five slots (loads run two key blocks ahead);
+//   * computes the exponentials into registers *before* it waits for the previous PV MMA, which is only
+//     needed for the TMEM store of P (and the rare rescale of O);
+//   * sums the exponentials on the FMA pipe: packed bf16 adds over groups of four, then fp32.
+// TMEM columns per CTA: S [0,128) fp32, O [128,128+D) fp32, P [128+D, 192+D) packed bf16.
+// ------------------------------------------------------------------------------------------------
+template <int ND>
+struct Fwd3Smem {
+  static constexpr int TILE = ND * 16384;
+  static constexpr int SLOTS = ND == 1 ? 5 : 4;
+  static constexpr int Q_OFF = 0;
+  static constexpr int KV_OFF = TILE;
+  static constexpr int BAR_OFF = KV_OFF + SLOTS * TILE;
+  static constexpr int TOTAL = BAR_OFF + 256 + 1024;
+};
+
+template <int ND>
+__global__ void __launch_bounds__(FA_THREADS, ND == 1 ? 2 : 1)
+flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                  const __grid_constant__ CUtensorMap tmap_v, const FlashFwdParams p) {
+  constexpr int D = 64 * ND;
+  using L = Fwd3Smem<ND>;
+  constexpr int SLOTS = L::SLOTS;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + L::Q_OFF;
+  uint8_t* sKV = smem + L::KV_OFF;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* q_full = bars;              // 1
+  uint64_t* kv_full = bars + 1;         // SLOTS
+  uint64_t* kv_empty = bars + 1 + SLOTS;  // SLOTS
+  uint64_t* s_full = bars + 1 + 2 * SLOTS;
+  uint64_t* s_empty = s_full + 1;       // 128 arrivals
+  uint64_t* p_full = s_full + 2;        // 128 arrivals
+  uint64_t* o_full = s_full + 3;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = (p.S + FA_BM - 1) / FA_BM;
+  const int q_blk = nqb - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+  const int q0 = q_blk * FA_BM;
+  const int nkb_all = (p.S + FA_BN - 1) / FA_BN;
+  const int nkb = p.causal ? min(nkb_all, q_blk + 1) : nkb_all;
+  constexpr uint32_t TMEM_COLS = ND == 1 ? 256 : 512;
+  constexpr uint32_t O_COL = 128, P_COL = 128 + D;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < SLOTS; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(s_empty, 128);
+    mbar_init(p_full, 128);
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, L::TILE);
+#pragma unroll
+      for (int a = 0; a < ND; ++a) tma_load_3d(sQ + a * 16384, &tmap_q, q_full, h * D + a * 64, q0, b);
+      for (int n = 0; n < 2 * nkb; ++n) {
+        const int slot = n % SLOTS;
+        const uint32_t ph = (n / SLOTS) & 1;
+        if (!mbar_wait(&kv_empty[slot], ph ^ 1, abort_flag, p.status, ERR_WAIT_EMPTY)) break;
+        mbar_expect_tx(&kv_full[slot], L::TILE);
+        const int j = n >> 1;
+        const CUtensorMap* tm = (n & 1) ? &tmap_v : &tmap_k;
+#pragma unroll
+        for (int a = 0; a < ND; ++a) tma_load_3d(sKV + slot * L::TILE + a * 16384, tm, &kv_full[slot], hk * D + a * 64, j * FA_BN, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_qk = make_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_pv = make_idesc_bf16(128, D, 0, 1);
+      const uint32_t q_base = smem_u32(sQ);
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, ERR_WAIT_FULL);
+      auto issue_qk = [&](int j) -> bool {
+        const int n = 2 * j, slot = n % SLOTS;
+        if (!mbar_wait(&kv_full[slot], (n / SLOTS) & 1, abort_flag, p.status, ERR_WAIT_FULL)) return false;
+        if (j > 0 && !mbar_wait(s_empty, (j - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) return false;
+        tc_fence_after();
+        const uint32_t k_base = smem_u32(sKV + slot * L::TILE);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
+          umma_bf16(tmem_base, make_smem_desc(q_base + off, 16, 1024, 2), make_smem_desc(k_base + off, 16, 1024, 2), idesc_qk, ks > 0);
+        }
+        umma_commit(s_full);
+        umma_commit(&kv_empty[slot]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; ok && j < nkb; ++j) {
+        if (j + 1 < nkb) {
+          if (!issue_qk(j + 1)) break;
+        }
+        const int n = 2 * j + 1, slot = n % SLOTS;
+        if (!mbar_wait(p_full, j & 1, abort_flag, p.status, ERR_WAIT_MISC)) break;
+        if (!mbar_wait(&kv_full[slot], (n / SLOTS) & 1, abort_flag, p.status, ERR_WAIT_FULL)) break;
+        tc_fence_after();
+        const uint32_t v_base = smem_u32(sKV + slot * L::TILE);
+#pragma unroll
+        for (int ks = 0; ks < FA_BN / 16; ++ks)  // 16 keys = 8 packed columns of P per step
+          umma_bf16_tmem_a(tmem_base + O_COL, tmem_base + P_COL + ks * 8, make_smem_desc(v_base + ks * 2048, 16384, 1024, 2), idesc_pv,
+                           (j > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(o_full);
+        umma_commit(&kv_empty[slot]);
+      }
+    }
+  } else {
+    // ---------------- softmax warps: thread <-> query row ----------------
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const int row = q0 + r;
+    const uint32_t t_lane = tmem_base + (uint32_t(q * 32) << 16);
+    const float c = p.scale * 1.4426950408889634f;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nkb; ++j) {
+      if (!mbar_wait_warp(s_full, j & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const int k0 = j * FA_BN;
+      const bool need_mask = (p.causal && k0 + FA_BN - 1 > q0) || (k0 + FA_BN > p.S);
+      const int kmax = p.causal ? min(row, p.S - 1) : p.S - 1;
+      uint32_t sr[128];
+      tmem_ld_32x32(t_lane, sr);
+      tmem_ld_32x32(t_lane + 32, sr + 32);
+      tmem_ld_32x32(t_lane + 64, sr + 64);
+      tmem_ld_32x32(t_lane + 96, sr + 96);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(s_empty);  // the scores live in registers now: the next QK^T may start
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (k0 + i > kmax) sr[i] = 0xff800000u;  // -inf
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 128; i += 8) {
+        mx0 = fmax3(mx0, __uint_as_float(sr[i + 0]), __uint_as_float(sr[i + 1]));
+        mx1 = fmax3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+        mx2 = fmax3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
+        mx3 = fmax3(mx3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
+      }
+      const float m_blk = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      const bool raise = j == 0 || (m_blk - m_used) * c > 8.0f;  // lazy: tolerate exponents up to 2^8
+      const float m_new = raise ? fmaxf(m_used, m_blk) : m_used;
+      const float alpha = (j == 0 || !raise) ? 1.0f : exp2f((m_used - m_new) * c);
+      m_used = m_new;
+      const bool any_rescale = __any_sync(0xffffffffu, j > 0 && raise);
+      const float mc = m_used * c;
+      // exponentials into registers (packed bf16 pairs overwrite the scores) and their sum. One MUFU op per
+      // element and nothing else on that unit: the bf16 packing is done with integer instructions.
+      float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 128; i += 2) {
+        const float e0 = exp2f(fmaf(__uint_as_float(sr[i]), c, -mc));
+        const float e1 = exp2f(fmaf(__uint_as_float(sr[i + 1]), c, -mc));
+        rs0 += e0;
+        rs1 += e1;
+        sr[i >> 1] = pack_bf16x2_int(e0, e1);  // slot i/2 <= i: never read again as a score
+      }
+      l = l * alpha + (rs0 + rs1);
+      if (j > 0) {
+        // PV of the previous block is complete: P may be overwritten, O is stable
+        if (!mbar_wait_warp(o_full, (j - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        if (any_rescale) {
+#pragma unroll 1
+          for (int cc = 0; cc < D / 32; ++cc) {
+            uint32_t rr[32];
+            tmem_ld_32x32(t_lane + O_COL + cc * 32, rr);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * alpha);
+            tmem_st_32x32(t_lane + O_COL + cc * 32, rr);
+          }
+        }
+      }
+      tmem_st_32x32(t_lane + P_COL, sr);
+      tmem_st_32x32(t_lane + P_COL + 32, sr + 32);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    if (ok) ok = mbar_wait_warp(o_full, (nkb - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
+    if (ok) {
+      tc_fence_after();
+      const float inv_l = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* dst = p.out + ((size_t)b * p.S + row) * p.ld_o + h * D;
+#pragma unroll 1
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t rr[32];
+        tmem_ld_32x32(t_lane + O_COL + cc * 32, rr);
+        tmem_ld_wait();
+        if (row < p.S) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(rr[g * 8 + 0]) * inv_l, __uint_as_float(rr[g * 8 + 1]) * inv_l);
+            o.y = pack_bf16x2(__uint_as_float(rr[g * 8 + 2]) * inv_l, __uint_as_float(rr[g * 8 + 3]) * inv_l);
+            o.z = pack_bf16x2(__uint_as_float(rr[g * 8 + 4]) * inv_l, __uint_as_float(rr[g * 8 + 5]) * inv_l);
+            o.w = pack_bf16x2(__uint_as_float(rr[g * 8 + 6]) * inv_l, __uint_as_float(rr[g * 8 + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(dst + cc * 32 + g * 8) = o;
+          }
+        }
+      }
+      if (p.lse && row < p.S) p.lse[((size_t)b * p.H + h) * p.S + row] = m_used * c + log2f(l);
+      tc_fence_before();
+    }
+  }
+
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 // 3-D bf16 tensor map over a token-major buffer: dims {cols, S, B}, box {64, rows, 1}, 128B swizzle.
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -612,16 +865,22 @@ extern "C" int inv_flash_attn_fwd(const void* q, const void* k, const void* v, v
     cudaFuncSetAttribute(flash_fwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<2>::TOTAL);
     cudaFuncSetAttribute(flash_fwd2_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Smem<1>::TOTAL);
     cudaFuncSetAttribute(flash_fwd2_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Smem<2>::TOTAL);
+    cudaFuncSetAttribute(flash_fwd3_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd3Smem<1>::TOTAL);
+    cudaFuncSetAttribute(flash_fwd3_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd3Smem<2>::TOTAL);
     configured = true;
   }
-  const bool legacy = (causal & 8) != 0;  // bit 3 selects the first-generation kernel (A/B comparisons)
+  const bool legacy = (causal & 8) != 0;  // bit 3 selects the first-generation kernel, bit 5 the second (A/B comparisons)
+  const bool gen2 = (causal & 32) != 0;
   p.causal = causal & 1;
-  if (legacy) {
+  if (gen2) {
+    if (head_dim == 64) flash_fwd2_kernel<1><<<grid, FA_THREADS, Fwd2Smem<1>::TOTAL, st>>>(tq, tk, tv, p);
+    else flash_fwd2_kernel<2><<<grid, FA_THREADS, Fwd2Smem<2>::TOTAL, st>>>(tq, tk, tv, p);
+  } else if (legacy) {
     if (head_dim == 64) flash_fwd_kernel<1><<<grid, FA_THREADS, FwdSmem<1>::TOTAL, st>>>(tq, tk, tv, p);
     else flash_fwd_kernel<2><<<grid, FA_THREADS, FwdSmem<2>::TOTAL, st>>>(tq, tk, tv, p);
   } else {
-    if (head_dim == 64) flash_fwd2_kernel<1><<<grid, FA_THREADS, Fwd2Smem<1>::TOTAL, st>>>(tq, tk, tv, p);
-    else flash_fwd2_kernel<2><<<grid, FA_THREADS, Fwd2Smem<2>::TOTAL, st>>>(tq, tk, tv, p);
+    if (head_dim == 64) flash_fwd3_kernel<1><<<grid, FA_THREADS, Fwd3Smem<1>::TOTAL, st>>>(tq, tk, tv, p);
+    else flash_fwd3_kernel<2><<<grid, FA_THREADS, Fwd3Smem<2>::TOTAL, st>>>(tq, tk, tv, p);
   }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;

@@ -101,15 +101,20 @@ __device__ __forceinline__ void st_release_gpu_u32(uint32_t* p, uint32_t v) {
 }
 // Bounded wait for a gathered tile; afterwards the async proxy (TMA) may read what the copier's ordinary stores wrote.
 __device__ __forceinline__ bool ag_wait_tile(const GemmParams& p, int tile, volatile int* abort_flag) {
-  const uint64_t t0 = globaltimer_ns();
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
   while (ld_acquire_gpu_u32(p.ag_flags + tile) != p.ag_epoch) {
-    if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > INV_WAIT_LIMIT_NS) {
-      *abort_flag = 1;
-      if (p.status) atomicExch(p.status, ERR_WAIT_PEER);
-      return false;
+    if ((++spins & 0xffu) == 0) {  // the global timer is slow to read: look at it only now and then
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > INV_WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        if (p.status) atomicExch(p.status, ERR_WAIT_PEER);
+        return false;
+      }
     }
-    __nanosleep(100);
   }
   asm volatile("fence.proxy.async;" ::: "memory");
   return true;

@@ -84,13 +84,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = globaltimer_ns();
+  // %globaltimer is slow to read, so the clock is consulted only after many failed polls (each try_wait already
+  // blocks for a hardware-defined slice); a wait that is satisfied quickly never touches it.
+  uint64_t t0 = 0;
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0xffu) == 0) {
+    if ((++spins & 0x3ffu) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > INV_WAIT_LIMIT_NS) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > INV_WAIT_LIMIT_NS) {
         *abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;
@@ -152,6 +157,17 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
       "}\n"
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Same with the A operand read from tensor memory (row i of A in TMEM lane i, two bf16 per 32-bit column).
+__device__ __forceinline__ void umma_bf16_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // Arrive on an mbarrier once every MMA issued so far by this thread has completed.
@@ -236,9 +252,20 @@ __device__ __forceinline__ uint32_t ex2_bf16x2(uint32_t x) {
   asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(d) : "r"(x));
   return d;
 }
+// Two fp32 -> packed bf16 (first argument in the low half) with integer instructions only: add half an ulp of
+// bf16 to the bit pattern and keep the upper 16 bits (round half away from zero). The cvt.rn.bf16x2.f32 form goes
+// through the conversion unit, which shares its issue rate with the MUFU; this one runs on the integer pipe.
+__device__ __forceinline__ uint32_t pack_bf16x2_int(float lo, float hi) {
+  return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+}
 __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
   uint32_t d;
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t add_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
