@@ -100,10 +100,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       mbar_init(&q_empty[s], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(s_empty, 256);
-    mbar_init(pds_full, 256);
+    mbar_init(s_empty, 8);
+    mbar_init(pds_full, 8);
     mbar_init(mma2_done, 1);
-    mbar_init(dq_empty, 256);
+    mbar_init(dq_empty, 8);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_q);
@@ -243,7 +243,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       tmem_ld_32x32(t_lane + DPT_COL + hf * 64 + 32, dp_all + 32);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(s_empty);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty);  // one arrival per warp: arrivals on one mbarrier are serialised
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int col0 = hf * 64 + cc * 32;
@@ -294,7 +295,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
       }
       fence_proxy_async_smem();
-      mbar_arrive(pds_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
       // dQ block: TMEM lanes are query rows now; this thread adds D/2 columns of row q0 + r.
       if (!mbar_wait_warp(mma2_done, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
@@ -315,7 +317,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
       }
       tc_fence_before();
-      mbar_arrive(dq_empty);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_empty);
     }
     // dK, dV: the last mma2_done covers every accumulation. TMEM lanes are key rows.
     if (ok && n_it > 0) {

@@ -621,8 +621,8 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       mbar_init(&kv_empty[i], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(s_empty, 128);
-    mbar_init(p_full, 128);
+    mbar_init(s_empty, 4);
+    mbar_init(p_full, 4);
     mbar_init(o_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -716,7 +716,8 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       tmem_ld_32x32(t_lane + 96, sr + 96);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(s_empty);  // the scores live in registers now: the next QK^T may start
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty);  // the scores live in registers now: the next QK^T may start (one arrival per warp)
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 128; ++i)
@@ -769,7 +770,8 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       tmem_st_32x32(t_lane + P_COL + 32, sr + 32);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
     }
     if (ok) ok = mbar_wait_warp(o_full, (nkb - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL);
     if (ok) {

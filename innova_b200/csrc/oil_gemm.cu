@@ -13,17 +13,19 @@
 //
 // The kernel is built for the decode shape (M = tokens in flight <= 256, N and K large) and runs
 // "swapped": the 128 weight rows of a tile are the M side of tcgen05.mma, the tokens its N side.
-//   warp 0    TMA: raw index tiles (128 rows x 64 k) and activation tiles (M x 64 k, 128B swizzle)
-//   warp 1    MMA issuer, accumulator [128 weight rows x M tokens] fp32 in TMEM
-//   warps 2-9 dequantise: each thread owns one scale block (row, 32 k): reads 16 or 32 index bytes,
-//             looks the values up in a shared-memory table of bf16 pairs (OIL4: indexed by the byte,
-//             i.e. two weights per lookup), multiplies by the block scale with packed bf16 math and
-//             writes its 64 bytes into the swizzled A-operand tile. The same warps run the epilogue.
+//   warp 0    TMA: raw index tiles (128 rows x 256 k, swizzled) and activation tiles (M x 64 k, 128B swizzle)
+//   warp 1    MMA issuer: A operand from tensor memory, B (activations) from shared memory, two accumulators
+//             [128 weight rows x M tokens] fp32 in TMEM
+//   warps 2-9 dequantise, two groups of four warps on alternate index tiles: a thread owns a weight row, looks
+//             the values up in a shared-memory table of bf16 pairs (OIL4: indexed by the byte, i.e. two weights
+//             per lookup), multiplies by the block scale with packed bf16 math and stores the row's 64 values
+//             per k-block into its lane of an A stage in tensor memory. The same warps run the epilogue.
 // With `multimem` set the output pointer is an NVLS multicast address and the epilogue's reductions are
 // multimem.red: the switch adds each partial sum into every rank's copy of the buffer, which turns a
 // row-parallel (tensor-parallel) linear layer into GEMM + all-reduce in one kernel.
-// Small N leaves most SMs idle, so the reduction dimension is split across CTAs (split-K) and the
-// partial sums are added to an fp32 output with reductions. Every wait is bounded.
+// Work is split stream-K: the (tile, k-block) pairs are cut into one equal contiguous range per SM, so every SM
+// streams the same number of index bytes whatever N and K are, and the partial sums of a range are added to the
+// fp32 output with reductions. Every wait is bounded.
 #include "sm100_common.cuh"
 #include "inv_api.h"
 
@@ -36,21 +38,25 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_
 
 namespace og {
 constexpr int BN = 128;     // weight rows per tile (MMA M)
-constexpr int BK = 64;
-constexpr int IDX_STAGES = 6, AB_STAGES = 3;
+constexpr int BK = 64;      // k-block: one A stage, one activation tile
+constexpr int MAX_A_STAGES = 8; // dequantised A stages in tensor memory (32 columns each), also the depth of the activation ring
+constexpr int STG_PITCH = 132;  // floats per token row of the epilogue staging tile (128 weight rows + 4: conflict-free both ways)
+constexpr int MAX_IDX_STAGES = 6;
 constexpr int THREADS = 320;
-constexpr int MAXM = 256;   // tokens per launch (MMA N)
-constexpr int A_TILE = BN * BK * 2;  // 16 KB dequantised weights
+constexpr int MAXM = 128;   // tokens per launch (MMA N); the host entry point splits larger M
+constexpr int ACC_COLS = 128, A_COL0 = 256;  // TMEM: two accumulators [0,128) [128,256), A ring [256,512)
 }  // namespace og
 
 struct OilGemmParams {
-  int M, N, K, bits;  // bits = 4 or 8
+  int M, N, K, bits;  // bits = 2, 4 or 8
   int Mpad;           // M rounded up to 16
   const __nv_bfloat16* scales;
   const float* codebook;
   float* out;  // [M, N] fp32
   int ldo;
-  int split_k;
+  int idx_stages;  // depth of the raw index ring: whatever shared memory is left, at most MAX_IDX_STAGES
+  int a_stages;    // A stages in tensor memory = activation tiles in shared memory: 8, or 4 when M > 64
+  int dp_rounds;   // whole tiles per CTA before the stream-K tail (tile = round * gridDim.x + blockIdx.x)
   int* status;
   int multimem;  // out is an NVLS multicast address: every partial sum is added into all ranks' copies
 };
@@ -70,7 +76,7 @@ static EncodeTiledFnO og_encode_fn() {
   });
   return fn;
 }
-// Plain (unswizzled) byte tensor map: `inner` bytes per row, `outer` rows.
+// Byte tensor map: `inner` bytes per row, `outer` rows; the box is one swizzle span wide (64 or 128 bytes).
 static int make_tmap_bytes(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer) {
   EncodeTiledFnO enc = og_encode_fn();
   if (!enc) return -1;
@@ -78,68 +84,176 @@ static int make_tmap_bytes(CUtensorMap* out, const void* ptr, uint64_t inner, ui
   cuuint64_t strides[1] = {inner};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapSwizzle sw = box_inner == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
 }
+
+// Expands one k-block of one weight row (64 weights) into 32 packed bf16 pairs, scaled. `raw` holds the row's
+// index bytes for the k-block (16 B per 2-bit, 32 B per 4-bit, 64 B per 8-bit), `s0` / `s1` the two block scales.
+template <int BITS>
+__device__ __forceinline__ void expand_row(const uint4* raw, __nv_bfloat16 s0, __nv_bfloat16 s1, const uint32_t* lut, const float* cb, int lane,
+                                           uint32_t* o) {
+  if (BITS == 2) {
+    // 4-entry codebook (ternary {-1, 0, +1, 0} for SPARK / OIL1 weights, or the OIL2 levels): the four scaled
+    // entries sit in one 64-bit register and every 2-bit code selects 16 bits of it
+    const uint32_t w[4] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const __nv_bfloat162 sc2 = __halves2bfloat162(h ? s1 : s0, h ? s1 : s0);
+      const __nv_bfloat162 e01 = __hmul2(__floats2bfloat162_rn(cb[0], cb[1]), sc2);
+      const __nv_bfloat162 e23 = __hmul2(__floats2bfloat162_rn(cb[2], cb[3]), sc2);
+      const uint64_t tbl = (uint64_t)(*reinterpret_cast<const uint32_t*>(&e01)) | ((uint64_t)(*reinterpret_cast<const uint32_t*>(&e23)) << 32);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {  // a 32-bit word = 16 codes = 8 output pairs
+        const uint32_t codes = w[h * 2 + j];
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+          const uint32_t lo = (uint32_t)(tbl >> (16 * ((codes >> (4 * b)) & 3))) & 0xffffu;
+          const uint32_t hi = (uint32_t)(tbl >> (16 * ((codes >> (4 * b + 2)) & 3))) << 16;
+          o[h * 16 + j * 8 + b] = lo | hi;
+        }
+      }
+    }
+  } else if (BITS == 4) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const __nv_bfloat162 sc2 = __halves2bfloat162(h ? s1 : s0, h ? s1 : s0);
+      const uint32_t w[4] = {raw[h].x, raw[h].y, raw[h].z, raw[h].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const uint32_t pair = lut[(((w[j] >> (8 * b)) & 255) << 5) + lane];
+          const __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&pair), sc2);
+          o[h * 16 + j * 4 + b] = *reinterpret_cast<const uint32_t*>(&v);
+        }
+    }
+  } else {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const __nv_bfloat162 sc2 = __halves2bfloat162(h ? s1 : s0, h ? s1 : s0);
+      const uint32_t w[8] = {raw[h * 2].x, raw[h * 2].y, raw[h * 2].z, raw[h * 2].w, raw[h * 2 + 1].x, raw[h * 2 + 1].y, raw[h * 2 + 1].z, raw[h * 2 + 1].w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+          const uint32_t two = w[j] >> (16 * b);
+          const uint32_t lo = lut[((two & 255) << 5) + lane] & 0xffffu, hi = lut[(((two >> 8) & 255) << 5) + lane] << 16;
+          const uint32_t pair = lo | hi;
+          const __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&pair), sc2);
+          o[h * 16 + j * 2 + b] = *reinterpret_cast<const uint32_t*>(&v);
+        }
+    }
+  }
+}
+
+// Walks a CTA's work in order: `dp_rounds` whole tiles (tile = round * grid + cta, every batch of K), then its share of
+// the stream-K tail: the (tile, batch) pairs of the remaining tiles, tile-major, cut into one equal contiguous range
+// per CTA. One step = one batch (index tile). A segment is a maximal run of batches inside one tile.
+struct OgCursor {
+  int nb, grid, cta, dp_rounds, sk_tile0, sk_b1;
+  int round, sk_b;
+  int tile, bb, bb0, bb1;
+  bool valid;
+  __device__ __forceinline__ void next_segment() {
+    if (round < dp_rounds) {
+      tile = round * grid + cta;
+      bb0 = 0; bb1 = nb;
+      ++round;
+      valid = true;
+    } else if (sk_b < sk_b1) {
+      const int t = sk_b / nb;
+      bb0 = sk_b - t * nb;
+      const int end = min(sk_b1, (t + 1) * nb);
+      bb1 = bb0 + (end - sk_b);
+      tile = sk_tile0 + t;
+      sk_b = end;
+      valid = true;
+    } else {
+      valid = false;
+    }
+    bb = bb0;
+  }
+  __device__ __forceinline__ OgCursor(int n_tiles, int nb_, int dp_rounds_) {
+    nb = nb_; grid = gridDim.x; cta = blockIdx.x; dp_rounds = dp_rounds_;
+    sk_tile0 = dp_rounds * grid;
+    const long long total = (long long)(n_tiles - sk_tile0) * nb;
+    sk_b = (int)(total * cta / grid);
+    sk_b1 = (int)(total * (cta + 1) / grid);
+    round = 0;
+    next_segment();
+  }
+  __device__ __forceinline__ void advance() {
+    if (++bb == bb1) next_segment();
+  }
+  __device__ __forceinline__ bool seg_first() const { return bb == bb0; }
+  __device__ __forceinline__ bool seg_last() const { return bb + 1 == bb1; }
+  __device__ __forceinline__ bool seg_full() const { return bb0 == 0 && bb1 == nb; }
+};
 
 template <int BITS>
 __global__ void __launch_bounds__(og::THREADS, 1)
 oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_constant__ CUtensorMap tmap_x, const OilGemmParams p) {
   using namespace og;
-  constexpr int IDX_TILE = BN * BK * BITS / 8;  // 4 KB (OIL4) or 8 KB (OIL8)
-  constexpr int ROW_BYTES = BK * BITS / 8;      // 32 or 64
-  const int X_TILE = p.Mpad * BK * 2;
+  constexpr int KBB = BITS == 8 ? 2 : 4;           // k-blocks per index tile ("batch")
+  constexpr int KB_BYTES = BK * BITS / 8;          // index bytes of one row in one k-block: 16, 32 or 64
+  constexpr int KB_CHUNKS = KB_BYTES / 16;
+  constexpr int ROWB = KBB * KB_BYTES;             // bytes per row of an index tile: 64 (2-bit) or 128
+  constexpr int ROW_CHUNKS = ROWB / 16;
+  constexpr int IDX_TILE = BN * ROWB;              // 8 or 16 KB
+  const int X_TILE = p.Mpad * BK * 2;              // activation tile, also the stride of its ring
+  const int IDX_STAGES = p.idx_stages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sA = smem;                                  // AB_STAGES x 16 KB
-  uint8_t* sX = sA + AB_STAGES * A_TILE;               // AB_STAGES x 32 KB (sized for MAXM)
-  uint8_t* sIdx = sX + AB_STAGES * (MAXM * BK * 2);    // IDX_STAGES x IDX_TILE
+  const int A_STAGES = p.a_stages;
+  uint8_t* sX = smem;                                  // A_STAGES x X_TILE (a multiple of 2 KB)
+  uint8_t* sIdx = sX + A_STAGES * X_TILE;              // IDX_STAGES x IDX_TILE (swizzled by TMA: 1 KB aligned)
   uint32_t* lut = reinterpret_cast<uint32_t*>(sIdx + IDX_STAGES * IDX_TILE);  // 256 entries x 32 bank copies
-  uint64_t* bars = reinterpret_cast<uint64_t*>(lut + 256 * 32);
+  float* stage = reinterpret_cast<float*>(lut + 256 * 32);  // epilogue staging: per group 32 tokens x STG_PITCH
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage + 2 * 32 * STG_PITCH);
   uint64_t* idx_full = bars;
-  uint64_t* idx_empty = idx_full + IDX_STAGES;
-  uint64_t* a_full = idx_empty + IDX_STAGES;
-  uint64_t* a_empty = a_full + AB_STAGES;
-  uint64_t* x_full = a_empty + AB_STAGES;
-  uint64_t* acc_full = x_full + AB_STAGES;
-  uint64_t* acc_empty = acc_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+  uint64_t* idx_empty = idx_full + MAX_IDX_STAGES;
+  uint64_t* a_full = idx_empty + MAX_IDX_STAGES;
+  uint64_t* a_empty = a_full + MAX_A_STAGES;
+  uint64_t* x_full = a_empty + MAX_A_STAGES;
+  uint64_t* acc_full = x_full + MAX_A_STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* cb = reinterpret_cast<float*>(tmem_slot + 2);  // codebook copy, 256 entries
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tiles = (p.N + BN - 1) / BN;
   const int kb_total = p.K / BK;
-  const int kb_per = (kb_total + p.split_k - 1) / p.split_k;
-  const int total_work = n_tiles * p.split_k;
+  const int nb = (kb_total + KBB - 1) / KBB;  // batches per tile
+  // Work split: whole tiles first (their result is stored), then a stream-K tail over the tiles that do not fill
+  // another round of the grid (a CTA walks down K inside a tile and adds the finished segment into the fp32 output
+  // with reductions). Every role below walks the same OgCursor.
 
-  // lookup table: OIL4 -> bf16 pair (codebook[low nibble], codebook[high nibble]) per byte; OIL8 -> one bf16
-  // entry e for lane l lives at lut[e * 32 + l]: every lane reads its own bank, whatever the indices are
-  for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
-    const int e = i >> 5;
-    if (BITS == 2) lut[i] = 0;
-    else if (BITS == 4) lut[i] = pack_bf16x2(p.codebook[e & 15], p.codebook[e >> 4]);
-    else lut[i] = pack_bf16x2(p.codebook[e], 0.f);
-  }
+  if (threadIdx.x < (BITS == 8 ? 256 : (1 << BITS))) cb[threadIdx.x] = p.codebook[threadIdx.x];
   if (threadIdx.x == 0) {
     for (int s = 0; s < IDX_STAGES; ++s) {
       mbar_init(&idx_full[s], 1);
-      mbar_init(&idx_empty[s], 256);
+      mbar_init(&idx_empty[s], 4);  // the four warps of the group that expanded the tile
     }
-    for (int s = 0; s < AB_STAGES; ++s) {
-      mbar_init(&a_full[s], 256);
+    for (int s = 0; s < A_STAGES; ++s) {
+      mbar_init(&a_full[s], 4);
       mbar_init(&a_empty[s], 1);
       mbar_init(&x_full[s], 1);
     }
-    mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 256);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full[s], 1);
+      mbar_init(&acc_empty[s], 4);
+    }
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_idx);
     tma_prefetch_desc(&tmap_x);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 256);
+    tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -150,159 +264,191 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
   if (warp == 0) {
     // lane 0 streams index tiles, lane 1 streams activation tiles; each runs ahead on its own ring
     if (lane == 0) {
-      int it = 0;
-      bool ok = true;
-      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-        const int n0 = (w % n_tiles) * BN;
-        const int kb0 = (w / n_tiles) * kb_per, kb1 = min(kb_total, kb0 + kb_per);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int si = it % IDX_STAGES;
-          if (!mbar_wait(&idx_empty[si], ((it / IDX_STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
-          mbar_expect_tx(&idx_full[si], IDX_TILE);
-          tma_load_2d(sIdx + si * IDX_TILE, &tmap_idx, &idx_full[si], kb * ROW_BYTES, n0);
-        }
+      int si = 0;
+      uint32_t ph = 1;
+      for (OgCursor c(n_tiles, nb, p.dp_rounds); c.valid; c.advance()) {
+        if (!mbar_wait(&idx_empty[si], ph, abort_flag, p.status, ERR_WAIT_EMPTY)) break;
+        mbar_expect_tx(&idx_full[si], IDX_TILE);  // bytes past the end of K are filled with zeros and counted
+        tma_load_2d(sIdx + si * IDX_TILE, &tmap_idx, &idx_full[si], c.bb * ROWB, c.tile * BN);
+        if (++si == IDX_STAGES) { si = 0; ph ^= 1; }
       }
     } else if (lane == 1) {
       int it = 0;
       bool ok = true;
-      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-        const int kb0 = (w / n_tiles) * kb_per, kb1 = min(kb_total, kb0 + kb_per);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int sx = it % AB_STAGES;
+      for (OgCursor c(n_tiles, nb, p.dp_rounds); ok && c.valid; c.advance()) {
+        const int kb0 = c.bb * KBB, nkb = min(KBB, kb_total - kb0);
+        for (int kk = 0; kk < nkb; ++kk, ++it) {
+          const int sx = it % A_STAGES;
           // the x stage is released together with the A stage (same MMA commit)
-          if (!mbar_wait(&a_empty[sx], ((it / AB_STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+          if (!mbar_wait(&a_empty[sx], ((it / A_STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
           mbar_expect_tx(&x_full[sx], X_TILE);
-          tma_load_2d(sX + sx * (MAXM * BK * 2), &tmap_x, &x_full[sx], kb * BK, 0);
+          tma_load_2d(sX + sx * X_TILE, &tmap_x, &x_full[sx], (kb0 + kk) * BK, 0);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc_bf16(128, p.Mpad, 0, 0);
-      int it = 0, tile_i = 0;
+      int it = 0, seg = 0;
       bool ok = true;
-      for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x, ++tile_i) {
-        const int kb0 = (w / n_tiles) * kb_per, kb1 = min(kb_total, kb0 + kb_per);
-        if (!mbar_wait(acc_empty, (tile_i & 1) ^ 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) break;
-        tc_fence_after();
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % AB_STAGES;
-          const uint32_t ph = (it / AB_STAGES) & 1;
+      for (OgCursor c(n_tiles, nb, p.dp_rounds); ok && c.valid; c.advance()) {
+        const int kb0 = c.bb * KBB, nkb = min(KBB, kb_total - kb0);
+        bool first = c.seg_first();
+        if (first) {
+          if (!mbar_wait(&acc_empty[seg & 1], ((seg >> 1) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) break;
+          tc_fence_after();
+        }
+        const uint32_t acc = tmem_base + (seg & 1) * ACC_COLS;
+        for (int kk = 0; kk < nkb; ++kk, ++it) {
+          const int s = it % A_STAGES;
+          const uint32_t ph = (it / A_STAGES) & 1;
           if (!mbar_wait(&a_full[s], ph, abort_flag, p.status, ERR_WAIT_FULL)) { ok = false; break; }
           if (!mbar_wait(&x_full[s], ph, abort_flag, p.status, ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_base = smem_u32(sA + s * A_TILE), x_base = smem_u32(sX + s * (MAXM * BK * 2));
+          const uint32_t x_base = smem_u32(sX + s * X_TILE);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma_bf16(tmem_base, make_smem_desc(a_base + k * 32, 16, 1024, 2), make_smem_desc(x_base + k * 32, 16, 1024, 2), idesc,
-                      (kb > kb0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / 16; ++k)  // 16 k = 8 packed columns of the A stage
+            umma_bf16_tmem_a(acc, tmem_base + A_COL0 + s * 32 + k * 8, make_smem_desc(x_base + k * 32, 16, 1024, 2), idesc,
+                             (!first || k > 0) ? 1u : 0u);
           umma_commit(&a_empty[s]);
+          first = false;
         }
         if (!ok) break;
-        umma_commit(acc_full);
+        if (c.seg_last()) {
+          umma_commit(&acc_full[seg & 1]);
+          ++seg;
+        }
       }
     }
   } else {
+    // lookup table: OIL4 -> bf16 pair (codebook[low nibble], codebook[high nibble]) per byte; OIL8 -> one bf16
+    // entry e for lane l lives at lut[e * 32 + l]: every lane reads its own bank, whatever the indices are
+    if (BITS != 2) {
+      for (int i = threadIdx.x - 64; i < 256 * 32; i += 256) {
+        const int e = i >> 5;
+        lut[i] = (BITS == 4) ? pack_bf16x2(cb[e & 15], cb[e >> 4]) : pack_bf16x2(cb[e], 0.f);
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+    }
     // ---------------- dequantise + epilogue ----------------
+    // Two groups of four warps take alternate batches, so that one group's waits and barrier traffic overlap the
+    // other group's table lookups. A thread owns weight row r of the tile: it reads the row's index bytes of the
+    // whole batch, expands one k-block at a time into 32 registers of packed bf16 and stores them into its lane
+    // of the A stage in tensor memory (the MMA reads A from there: no shared-memory round trip).
     const int q = warp & 3;
-    const int half = (warp - 2) >> 2;   // which 32-wide scale block of the 64-deep k-block
-    const int r = q * 32 + lane;        // weight row inside the tile
+    const int grp = (warp - 2) >> 2;
+    const int r = q * 32 + lane;        // weight row inside the tile = TMEM lane
     const int nsb = p.K / 32;           // scale blocks per weight row
-    int it = 0, tile_i = 0;
+    const unsigned short* scales = reinterpret_cast<const unsigned short*>(p.scales);
+    const uint32_t t_lane = tmem_base + (uint32_t(q * 32) << 16);
+    // block scales of a batch are fetched one own batch (two batches) ahead of their use
+    unsigned short sc_next[2 * KBB];
+    auto fetch_scales = [&](int t, int bbx) {
+      const int kb0 = bbx * KBB;
+      const unsigned short* row = scales + (size_t)min(t * BN + r, p.N - 1) * nsb + kb0 * 2;
+#pragma unroll
+      for (int j = 0; j < 2 * KBB; ++j) sc_next[j] = (kb0 * 2 + j < nsb) ? __ldg(row + j) : (unsigned short)0;
+    };
+    OgCursor pc(n_tiles, nb, p.dp_rounds);  // runs one own batch ahead of the main cursor
+    if (grp == 1 && pc.valid) pc.advance();
+    if (pc.valid) fetch_scales(pc.tile, pc.bb);
+    float* stg = stage + grp * (32 * STG_PITCH);
+    const int gt = threadIdx.x - 64 - grp * 128;  // thread index inside the group
+    const bool vec_ok = ((p.ldo & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    int it = 0, seg = 0, lb = 0;
     bool ok = true;
-    for (int w = blockIdx.x; ok && w < total_work; w += gridDim.x, ++tile_i) {
-      const int n0 = (w % n_tiles) * BN;
-      const int kb0 = (w / n_tiles) * kb_per, kb1 = min(kb_total, kb0 + kb_per);
-      const int row = n0 + r;
-      const __nv_bfloat16* srow = p.scales + (size_t)min(row, p.N - 1) * nsb;
-      __nv_bfloat16 sc_next = srow[kb0 * 2 + half];  // the scale is fetched one k-block ahead of its use
-      for (int kb = kb0; kb < kb1; ++kb, ++it) {
-        const __nv_bfloat16 sc = sc_next;
-        if (kb + 1 < kb1) sc_next = srow[(kb + 1) * 2 + half];
-        const int si = it % IDX_STAGES, sa = it % AB_STAGES;
-        if (!mbar_wait_warp(&idx_full[si], (it / IDX_STAGES) & 1, abort_flag, p.status, ERR_WAIT_FULL)) { ok = false; break; }
-        if (!mbar_wait_warp(&a_empty[sa], ((it / AB_STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
-        const __nv_bfloat162 sc2 = __halves2bfloat162(sc, sc);
-        const uint8_t* src = sIdx + si * IDX_TILE + r * ROW_BYTES + half * (ROW_BYTES / 2);
-        uint8_t* dst = sA + sa * A_TILE + (r >> 3) * 1024 + (r & 7) * 128;
-        if (BITS == 2) {
-          // 4-entry codebook (ternary {-1, 0, +1, 0} for SPARK / OIL1 weights, or the OIL2 levels): the four
-          // scaled entries sit in one 64-bit register and every 2-bit code selects 16 bits of it
-          const uint2 raw = *reinterpret_cast<const uint2*>(src);  // 32 weights
-          const __nv_bfloat162 e01 = __hmul2(__floats2bfloat162_rn(p.codebook[0], p.codebook[1]), sc2);
-          const __nv_bfloat162 e23 = __hmul2(__floats2bfloat162_rn(p.codebook[2], p.codebook[3]), sc2);
-          const uint64_t tbl = (uint64_t)(*reinterpret_cast<const uint32_t*>(&e01)) | ((uint64_t)(*reinterpret_cast<const uint32_t*>(&e23)) << 32);
+    for (OgCursor c(n_tiles, nb, p.dp_rounds); ok && c.valid; c.advance(), ++lb) {
+      const int kb0 = c.bb * KBB, nkb = min(KBB, kb_total - kb0);
+      const bool seg_end = c.seg_last();
+      if ((lb & 1) == grp) {
+        unsigned short sc[2 * KBB];
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {  // 8 weights = 16 bits of codes
-            const uint32_t codes = ((g < 2 ? raw.x : raw.y) >> (16 * (g & 1))) & 0xffffu;
-            uint32_t o[4];
+        for (int j = 0; j < 2 * KBB; ++j) sc[j] = sc_next[j];
+        if (pc.valid) pc.advance();
+        if (pc.valid) pc.advance();
+        if (pc.valid) fetch_scales(pc.tile, pc.bb);
+        const int si = lb % IDX_STAGES;
+        if (!mbar_wait_warp(&idx_full[si], (lb / IDX_STAGES) & 1, abort_flag, p.status, ERR_WAIT_FULL)) { ok = false; break; }
+        uint4 raw[ROW_CHUNKS];
+        {
+          const uint8_t* src = sIdx + si * IDX_TILE + r * ROWB;
+          const int swz = (ROWB == 128) ? (r & 7) : ((r >> 1) & 3);  // the TMA swizzle of a 128- / 64-byte row
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-              const uint32_t lo = (uint32_t)(tbl >> (16 * ((codes >> (4 * b)) & 3))) & 0xffffu;
-              const uint32_t hi = (uint32_t)(tbl >> (16 * ((codes >> (4 * b + 2)) & 3))) << 16;
-              o[b] = lo | hi;
-            }
-            *reinterpret_cast<uint4*>(dst + (((half * 4 + g) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-          }
-        } else if (BITS == 4) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(src);  // 32 weights
-          const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+          for (int ch = 0; ch < ROW_CHUNKS; ++ch) raw[ch] = *reinterpret_cast<const uint4*>(src + ((ch ^ swz) << 4));
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&idx_empty[si]);  // the tile lives in registers now
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {  // 8 weights = 4 bytes = one 16-byte chunk of bf16
-            uint32_t o[4];
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-              const uint32_t pair = lut[(((wds[g] >> (8 * b)) & 255) << 5) + lane];
-              const __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&pair), sc2);
-              o[b] = *reinterpret_cast<const uint32_t*>(&v);
-            }
-            *reinterpret_cast<uint4*>(dst + (((half * 4 + g) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-          }
-        } else {
-          const uint4 raw0 = *reinterpret_cast<const uint4*>(src), raw1 = *reinterpret_cast<const uint4*>(src + 16);
-          const uint32_t wds[8] = {raw0.x, raw0.y, raw0.z, raw0.w, raw1.x, raw1.y, raw1.z, raw1.w};
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint32_t o[4];
-#pragma unroll
-            for (int b = 0; b < 4; ++b) {
-              const uint32_t two = wds[g * 2 + (b >> 1)] >> (16 * (b & 1));
-              const uint32_t lo = lut[((two & 255) << 5) + lane] & 0xffffu, hi = lut[(((two >> 8) & 255) << 5) + lane] << 16;
-              const uint32_t pair = lo | hi;
-              const __nv_bfloat162 v = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&pair), sc2);
-              o[b] = *reinterpret_cast<const uint32_t*>(&v);
-            }
-            *reinterpret_cast<uint4*>(dst + (((half * 4 + g) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        for (int kk = 0; kk < KBB; ++kk) {
+          if (kk < nkb) {
+            const int s = (it + kk) % A_STAGES;
+            if (!mbar_wait_warp(&a_empty[s], (((it + kk) / A_STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t o[32];
+            const __nv_bfloat16_raw r0{sc[2 * kk]}, r1{sc[2 * kk + 1]};
+            expand_row<BITS>(raw + kk * KB_CHUNKS, __nv_bfloat16(r0), __nv_bfloat16(r1), lut, cb, lane, o);
+            tmem_st_32x32(t_lane + A_COL0 + s * 32, o);
           }
         }
-        mbar_arrive(&idx_empty[si]);
-        fence_proxy_async_smem();
-        mbar_arrive(&a_full[sa]);
-      }
-      if (!ok) break;
-      // ---- epilogue: accumulator [weight row (lane), token (column)] -> out[token][n0 + row] ----
-      if (!mbar_wait_warp(acc_full, tile_i & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) break;
-      tc_fence_after();
-      const uint32_t t_row = tmem_base + (uint32_t(q * 32) << 16);
-      const int chunks = p.Mpad / 16;
-      for (int c = half; c < chunks; c += 2) {  // the two halves split the token columns
-        uint32_t v[16];
-        tmem_ld_32x16(t_row + c * 16, v);
-        tmem_ld_wait();
-        if (row < p.N) {
+        if (!ok) break;
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {  // one arrival per warp and stage
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int m = c * 16 + i;
-            if (m < p.M) {
-              float* dst = p.out + (size_t)m * p.ldo + row;
-              if (p.multimem) asm volatile("multimem.red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(dst), "f"(__uint_as_float(v[i])) : "memory");
-              else atomicAdd(dst, __uint_as_float(v[i]));
+          for (int kk = 0; kk < KBB; ++kk)
+            if (kk < nkb) mbar_arrive(&a_full[(it + kk) % A_STAGES]);
+        }
+        if (seg_end) {
+          // ---- segment end: accumulator [weight row (lane), token (column)] -> out[token][tile * 128 + row] ----
+          // The tile is transposed through shared memory 32 tokens at a time, so that a thread ends up with four
+          // consecutive weight rows of one token: one 16-byte store (whole tile) or vector reduction per thread.
+          const bool full = c.seg_full() && !p.multimem;
+          if (!mbar_wait_warp(&acc_full[seg & 1], (seg >> 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t t_acc = t_lane + (seg & 1) * ACC_COLS;
+          for (int mh = 0; mh < p.Mpad; mh += 32) {
+            uint32_t v[32];
+            tmem_ld_32x16(t_acc + mh, v);
+            if (mh + 16 < p.Mpad) tmem_ld_32x16(t_acc + mh + 16, v + 16);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) stg[j * STG_PITCH + r] = __uint_as_float(v[j]);
+            asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const int e = k * 128 + gt, m = e >> 5, n4 = (e & 31) * 4;
+              const int gm = mh + m, n = c.tile * BN + n4;
+              if (gm < p.M && n < p.N) {
+                const float4 val = *reinterpret_cast<const float4*>(stg + m * STG_PITCH + n4);
+                float* o = p.out + (size_t)gm * p.ldo + n;
+                if (vec_ok && n + 3 < p.N) {
+                  if (p.multimem)
+                    asm volatile("multimem.red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(val.x), "f"(val.y), "f"(val.z), "f"(val.w) : "memory");
+                  else if (full)
+                    *reinterpret_cast<float4*>(o) = val;
+                  else
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(val.x), "f"(val.y), "f"(val.z), "f"(val.w) : "memory");
+                } else {
+                  const float vv[4] = {val.x, val.y, val.z, val.w};
+#pragma unroll
+                  for (int z = 0; z < 4; ++z)
+                    if (n + z < p.N) {
+                      if (p.multimem) asm volatile("multimem.red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(o + z), "f"(vv[z]) : "memory");
+                      else atomicAdd(o + z, vv[z]);
+                    }
+                }
+              }
             }
+            asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
           }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[seg & 1]);
         }
       }
-      tc_fence_before();
-      mbar_arrive(acc_empty);
+      it += nkb;
+      if (seg_end) ++seg;
     }
   }
 
@@ -314,14 +460,32 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
   }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, 512);
   }
 }
 
-// out_bf16[m, n] = bf16(acc[m, n] + bias[n] (+ residual[m, n])); clears acc for the next use.
+// out_bf16[m, n] = bf16(acc[m, n] + bias[n] (+ residual[m, n])); clears acc for the next use. Four columns per thread.
 __global__ void oil_gemm_finish_kernel(float* __restrict__ acc, const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ residual,
-                                       __nv_bfloat16* __restrict__ out, long M, int N, int ld_acc, int ld_out, int ld_res, int clear) {
+                                       __nv_bfloat16* __restrict__ out, long M, int N, int ld_acc, int ld_out, int ld_res, int clear, int vec) {
   const long m = blockIdx.y;
+  if (vec) {
+    for (int n = (blockIdx.x * blockDim.x + threadIdx.x) * 4; n < N; n += gridDim.x * blockDim.x * 4) {
+      float4 v = *reinterpret_cast<float4*>(acc + m * ld_acc + n);
+      if (clear) *reinterpret_cast<float4*>(acc + m * ld_acc + n) = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (bias) {
+        const uint2 b = *reinterpret_cast<const uint2*>(bias + n);
+        v.x += __uint_as_float(b.x << 16); v.y += __uint_as_float(b.x & 0xffff0000u);
+        v.z += __uint_as_float(b.y << 16); v.w += __uint_as_float(b.y & 0xffff0000u);
+      }
+      if (residual) {
+        const uint2 b = *reinterpret_cast<const uint2*>(residual + m * ld_res + n);
+        v.x += __uint_as_float(b.x << 16); v.y += __uint_as_float(b.x & 0xffff0000u);
+        v.z += __uint_as_float(b.y << 16); v.w += __uint_as_float(b.y & 0xffff0000u);
+      }
+      *reinterpret_cast<uint2*>(out + m * ld_out + n) = make_uint2(pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+    }
+    return;
+  }
   for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < N; n += gridDim.x * blockDim.x) {
     float v = acc[m * ld_acc + n];
     if (clear) acc[m * ld_acc + n] = 0.f;
@@ -331,15 +495,95 @@ __global__ void oil_gemm_finish_kernel(float* __restrict__ acc, const __nv_bfloa
   }
 }
 
+// out[m, f] = bf16(silu(g) * u) with g = acc[m, f] (+ bias[f]), u = acc[m, F + f] (+ bias[F + f]); clears acc.
+// The gate / up projection's finish and the SwiGLU in one pass. F % 4 == 0.
+__global__ void oil_gemm_finish_swiglu_kernel(float* __restrict__ acc, const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int F,
+                                              int ld_acc, int ld_out) {
+  const long m = blockIdx.y;
+  for (int f = (blockIdx.x * blockDim.x + threadIdx.x) * 4; f < F; f += gridDim.x * blockDim.x * 4) {
+    float4 g = *reinterpret_cast<float4*>(acc + m * ld_acc + f);
+    float4 u = *reinterpret_cast<float4*>(acc + m * ld_acc + F + f);
+    *reinterpret_cast<float4*>(acc + m * ld_acc + f) = make_float4(0.f, 0.f, 0.f, 0.f);
+    *reinterpret_cast<float4*>(acc + m * ld_acc + F + f) = make_float4(0.f, 0.f, 0.f, 0.f);
+    float gv[4] = {g.x, g.y, g.z, g.w}, uv[4] = {u.x, u.y, u.z, u.w}, r[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (bias) {
+        gv[i] += __bfloat162float(bias[f + i]);
+        uv[i] += __bfloat162float(bias[F + f + i]);
+      }
+      // the unfused path rounds the projection to bf16 before the activation: same here
+      const float gb = __bfloat162float(__float2bfloat16_rn(gv[i])), ub = __bfloat162float(__float2bfloat16_rn(uv[i]));
+      r[i] = gb / (1.f + __expf(-gb)) * ub;
+    }
+    *reinterpret_cast<uint2*>(out + m * ld_out + f) = make_uint2(pack_bf16x2(r[0], r[1]), pack_bf16x2(r[2], r[3]));
+  }
+}
+
+// x[m, :] = bf16(acc[m, :] + bias + residual[m, :]);  h[m, :] = bf16(rms_norm(x[m, :]) * w): the finish of a
+// row-parallel projection with the next block's RMSNorm. One CTA of 256 threads per token; N % 4 == 0, N <= 16384.
+__global__ void __launch_bounds__(256) oil_gemm_finish_norm_kernel(float* __restrict__ acc, const __nv_bfloat16* __restrict__ bias,
+                                                                   const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ x_out,
+                                                                   const __nv_bfloat16* __restrict__ w, float eps, __nv_bfloat16* __restrict__ h_out,
+                                                                   int N, int ld_acc, int ld_x, int ld_res, int ld_h) {
+  constexpr int MAXV = 16;  // float4 groups per thread: 256 * 16 * 4 = 16384 columns
+  const long m = blockIdx.x;
+  __shared__ float red[8];
+  float4 xs[MAXV];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int n = (i * 256 + threadIdx.x) * 4;
+    if (n < N) {
+      float4 v = *reinterpret_cast<float4*>(acc + m * ld_acc + n);
+      *reinterpret_cast<float4*>(acc + m * ld_acc + n) = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (bias) {
+        const uint2 b = *reinterpret_cast<const uint2*>(bias + n);
+        v.x += __uint_as_float(b.x << 16); v.y += __uint_as_float(b.x & 0xffff0000u);
+        v.z += __uint_as_float(b.y << 16); v.w += __uint_as_float(b.y & 0xffff0000u);
+      }
+      if (residual) {
+        const uint2 b = *reinterpret_cast<const uint2*>(residual + m * ld_res + n);
+        v.x += __uint_as_float(b.x << 16); v.y += __uint_as_float(b.x & 0xffff0000u);
+        v.z += __uint_as_float(b.y << 16); v.w += __uint_as_float(b.y & 0xffff0000u);
+      }
+      const uint32_t p0 = pack_bf16x2(v.x, v.y), p1 = pack_bf16x2(v.z, v.w);
+      *reinterpret_cast<uint2*>(x_out + m * ld_x + n) = make_uint2(p0, p1);
+      // the norm sees the rounded residual stream, as it does when it runs as a kernel of its own
+      v.x = __uint_as_float(p0 << 16); v.y = __uint_as_float(p0 & 0xffff0000u);
+      v.z = __uint_as_float(p1 << 16); v.w = __uint_as_float(p1 & 0xffff0000u);
+      xs[i] = v;
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float rstd = rsqrtf(tot / N + eps);
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int n = (i * 256 + threadIdx.x) * 4;
+    if (n < N) {
+      const uint2 wb = *reinterpret_cast<const uint2*>(w + n);
+      const float4 v = xs[i];
+      const float r0 = v.x * rstd * __uint_as_float(wb.x << 16), r1 = v.y * rstd * __uint_as_float(wb.x & 0xffff0000u);
+      const float r2 = v.z * rstd * __uint_as_float(wb.y << 16), r3 = v.w * rstd * __uint_as_float(wb.y & 0xffff0000u);
+      *reinterpret_cast<uint2*>(h_out + m * ld_h + n) = make_uint2(pack_bf16x2(r0, r1), pack_bf16x2(r2, r3));
+    }
+  }
+}
+
 }  // namespace inv
 
 using namespace inv;
 
-// acc (fp32 [M, ldo]) must be zero on entry or hold a partial sum to add to. M <= 256, K % 64 == 0.
-extern "C" int inv_oil_gemm(const void* x, int ldx, const void* idx, const void* scales, const float* codebook, int bits, float* acc, int ldo,
-                            int M, int N, int K, int split_k, int* status, void* stream, int multimem) {
+static int oil_gemm_launch(const void* x, int ldx, const void* idx, const void* scales, const float* codebook, int bits, float* acc, int ldo,
+                           int M, int N, int K, int* status, cudaStream_t st, int multimem) {
   using namespace og;
-  if ((bits != 2 && bits != 4 && bits != 8) || M < 1 || M > MAXM || (K % 64) || (ldx % 8) || N < 1) return -ERR_BAD_ARG;
   static int num_sms = 0;
   if (num_sms == 0) {
     int dev = 0;
@@ -353,24 +597,21 @@ extern "C" int inv_oil_gemm(const void* x, int ldx, const void* idx, const void*
   p.scales = (const __nv_bfloat16*)scales;
   p.codebook = codebook;
   p.out = acc; p.ldo = ldo; p.status = status; p.multimem = multimem;
-  const int n_tiles = (N + BN - 1) / BN, kb_total = K / BK;
-  if (split_k <= 0) {  // several work units per SM (balance), each at least 4 k-blocks long
-    split_k = (4 * num_sms + n_tiles - 1) / n_tiles;
-    if (split_k > kb_total / 4) split_k = kb_total / 4 > 0 ? kb_total / 4 : 1;
-  }
-  if (split_k > kb_total) split_k = kb_total;
-  {
-    const int per = (kb_total + split_k - 1) / split_k;
-    split_k = (kb_total + per - 1) / per;
-  }
-  p.split_k = split_k;
+  const int kbb = bits == 8 ? 2 : 4;
+  const int n_tiles = (N + BN - 1) / BN, kb_total = K / BK, nb = (kb_total + kbb - 1) / kbb;
   CUtensorMap ti, tx;
   int rc;
-  const int row_bytes = K * bits / 8;
-  if ((rc = make_tmap_bytes(&ti, idx, (uint64_t)row_bytes, (uint64_t)N, BK * bits / 8, BN))) return rc;
+  const int row_bytes = K * bits / 8, rowb = kbb * BK * bits / 8;
+  if ((rc = make_tmap_bytes(&ti, idx, (uint64_t)row_bytes, (uint64_t)N, rowb, BN))) return rc;
   if ((rc = make_tmap_2d_bf16(&tx, x, (uint64_t)K, (uint64_t)M, (uint64_t)ldx, BK, (uint32_t)p.Mpad))) return rc;
-  const int idx_tile = BN * BK * bits / 8;
-  const int smem = AB_STAGES * (A_TILE + MAXM * BK * 2) + IDX_STAGES * idx_tile + 1024 + 256 * 32 * 4 + 512 + 1024;
+  const int idx_tile = BN * rowb;
+  p.a_stages = p.Mpad <= 64 ? MAX_A_STAGES : 4;
+  const int fixed = 1024 + p.a_stages * p.Mpad * BK * 2 + 256 * 32 * 4 + 2 * 32 * STG_PITCH * 4 + (2 * MAX_IDX_STAGES + 3 * MAX_A_STAGES + 4) * 8 + 16 + 1024 + 64;
+  int stages = (227 * 1024 - fixed) / idx_tile;
+  if (stages > MAX_IDX_STAGES) stages = MAX_IDX_STAGES;
+  if (stages < 2) return -ERR_BAD_ARG;
+  p.idx_stages = stages;
+  const int smem = fixed + stages * idx_tile;
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(oil_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -378,9 +619,12 @@ extern "C" int inv_oil_gemm(const void* x, int ldx, const void* idx, const void*
     cudaFuncSetAttribute(oil_gemm_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     configured = true;
   }
-  const int total = n_tiles * split_k;
-  const int grid = total < num_sms ? total : num_sms;
-  cudaStream_t st = (cudaStream_t)stream;
+  // at least two batches per CTA (one per expanding group): shorter ranges cost more in prologue and reductions
+  // than they win in parallelism
+  const long long total = (long long)n_tiles * nb;
+  int grid = (int)((total + 1) / 2);
+  if (grid > num_sms) grid = num_sms;
+  p.dp_rounds = n_tiles / grid;  // whole tiles while they fill rounds of the grid, the rest is the stream-K tail
   if (bits == 2) oil_gemm_kernel<2><<<grid, THREADS, smem, st>>>(ti, tx, p);
   else if (bits == 4) oil_gemm_kernel<4><<<grid, THREADS, smem, st>>>(ti, tx, p);
   else oil_gemm_kernel<8><<<grid, THREADS, smem, st>>>(ti, tx, p);
@@ -388,14 +632,57 @@ extern "C" int inv_oil_gemm(const void* x, int ldx, const void* idx, const void*
   return e == cudaSuccess ? 0 : -(int)e;
 }
 
+// acc (fp32 [M, ldo]) must be zero on entry or hold a partial sum to add to. M <= 256, K % 64 == 0.
+extern "C" int inv_oil_gemm(const void* x, int ldx, const void* idx, const void* scales, const float* codebook, int bits, float* acc, int ldo,
+                            int M, int N, int K, int split_k, int* status, void* stream, int multimem) {
+  (void)split_k;  // the split is stream-K: equal (tile, batch) ranges per CTA
+  if ((bits != 2 && bits != 4 && bits != 8) || M < 1 || M > 256 || (K % 64) || (ldx % 8) || N < 1) return -ERR_BAD_ARG;
+  for (int m0 = 0; m0 < M; m0 += og::MAXM) {
+    const int m = M - m0 < og::MAXM ? M - m0 : og::MAXM;
+    const int rc = oil_gemm_launch((const __nv_bfloat16*)x + (size_t)m0 * ldx, ldx, idx, scales, codebook, bits, acc + (size_t)m0 * ldo, ldo, m, N, K,
+                                   status, (cudaStream_t)stream, multimem);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
 extern "C" int inv_oil_gemm_finish(float* acc, const void* bias, const void* residual, void* out, long M, int N, int ld_acc, int ld_out,
                                    int ld_res, int clear, void* stream) {
   if (M <= 0) return 0;
-  int gx = (N + 255) / 256;
+  const bool vec = (N % 4 == 0) && (ld_acc % 4 == 0) && (ld_out % 4 == 0) && (ld_res % 4 == 0) && ((uintptr_t)acc % 16 == 0) &&
+                   ((uintptr_t)out % 8 == 0) && ((uintptr_t)bias % 8 == 0) && ((uintptr_t)residual % 8 == 0);
+  const int per_block = vec ? 1024 : 256;
+  int gx = (N + per_block - 1) / per_block;
   if (gx > 32) gx = 32;
   dim3 grid(gx, (unsigned)M);
   oil_gemm_finish_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(acc, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)residual,
-                                                                  (__nv_bfloat16*)out, M, N, ld_acc, ld_out, ld_res, clear);
+                                                                  (__nv_bfloat16*)out, M, N, ld_acc, ld_out, ld_res, clear, vec ? 1 : 0);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+// out[M, F] = silu(acc[:, :F] + bias[:F]) * (acc[:, F:] + bias[F:]); acc [M, 2F] is cleared.
+extern "C" int inv_oil_gemm_finish_swiglu(float* acc, const void* bias, void* out, long M, int F, int ld_acc, int ld_out, void* stream) {
+  if (M <= 0) return 0;
+  if ((F % 4) || (ld_acc % 4) || (ld_out % 4) || ((uintptr_t)acc % 16) || ((uintptr_t)out % 8)) return -ERR_BAD_ARG;
+  int gx = (F + 1023) / 1024;
+  if (gx > 32) gx = 32;
+  dim3 grid(gx, (unsigned)M);
+  oil_gemm_finish_swiglu_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(acc, (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, F, ld_acc, ld_out);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+// x_out[M, N] = acc + bias + residual (bf16), h_out[M, N] = rms_norm(x_out) * norm_w; acc is cleared.
+extern "C" int inv_oil_gemm_finish_norm(float* acc, const void* bias, const void* residual, void* x_out, const void* norm_w, float eps, void* h_out,
+                                        long M, int N, int ld_acc, int ld_x, int ld_res, int ld_h, void* stream) {
+  if (M <= 0) return 0;
+  if ((N % 4) || N > 16384 || (ld_acc % 4) || (ld_x % 4) || (ld_res % 4) || (ld_h % 4) || ((uintptr_t)acc % 16) || ((uintptr_t)x_out % 8) ||
+      ((uintptr_t)h_out % 8) || ((uintptr_t)bias % 8) || ((uintptr_t)residual % 8) || ((uintptr_t)norm_w % 8))
+    return -ERR_BAD_ARG;
+  oil_gemm_finish_norm_kernel<<<(unsigned)M, 256, 0, (cudaStream_t)stream>>>(acc, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)residual,
+                                                                              (__nv_bfloat16*)x_out, (const __nv_bfloat16*)norm_w, eps,
+                                                                              (__nv_bfloat16*)h_out, N, ld_acc, ld_x, ld_res, ld_h);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }

@@ -414,6 +414,226 @@ __global__ void __launch_bounds__(128) paged_decode_oil4_kernel(const __nv_bfloa
   }
 }
 
+// OIL4 decode attention on the tensor cores (warp-level mma.sync m16n8k16, fp16 inputs, fp32 accumulation).
+// A GQA group has at most 8 query heads per KV head, far below the 64-row minimum of tcgen05.mma, and the kernel
+// is bound by index bytes and table lookups, not by tensor throughput, so the warp-level MMA is the right size:
+// one warp owns one 16-token page at a time and never touches shared memory except for the lookup table.
+//   scores  S[head, token]  = Q[head, d] . K[token, d]^T   A = Q (rows >= G are zero), B = K: lane (token = lane/4,
+//           quarter = lane%4) expands the 16 index bytes of its token's d-quarter; since the contraction runs over
+//           d, the d order inside the MMA is permuted so that every lane feeds its own bytes in order
+//   softmax on the accumulator fragment (lane holds 4 tokens of head lane/4), running max / sum per head
+//   values  O^T[d, head]    = V^T[d, token] . P^T[token, head]   B = P^T is the score fragment as it stands, A = V^T:
+//           lane (d-chunk = lane/4) expands 8 bytes of four tokens and pairs values of neighbouring tokens with
+//           byte permutes; the output d order is permuted the same way and undone when the result is written
+// K, V and their scales for the next page are loaded before the current page is processed.
+__device__ __forceinline__ void mma_16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
+
+template <int D>
+__global__ void __launch_bounds__(128) paged_decode_oil4_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q, const int* __restrict__ page_table,
+                                                                    int max_pages, const int* __restrict__ seq_lens, int H, int Hkv,
+                                                                    const uint8_t* __restrict__ k_pool, const uint8_t* __restrict__ v_pool,
+                                                                    const __half* __restrict__ k_scale, const __half* __restrict__ v_scale,
+                                                                    float scale, float* __restrict__ part, int splits) {
+  constexpr int MAXG = 8;
+  constexpr int KCH = D / 4;        // d-values of a K row per lane (one quarter of the row)
+  constexpr int KW = KCH / 8;       // ... as 32-bit words of indices (4 for D = 128)
+  constexpr int KSTEPS = KCH / 4;   // MMA k-steps: 4 d-values per lane and step
+  constexpr int VCH = D / 8;        // d-values of a V row per lane (one eighth of the row)
+  constexpr int VW = VCH / 8;       // ... as 32-bit words (2 for D = 128)
+  constexpr int VMMA = VCH / 2;     // PV MMAs per page: 2 d-values per lane and MMA
+  __shared__ __align__(16) uint32_t lut[256 * 32];  // byte -> half2(level[low nibble], level[high nibble]); entry e of lane l at [e * 32 + l]
+  __shared__ float sm_m[4][MAXG], sm_l[4][MAXG];
+  float (*sm_o)[MAXG][D] = reinterpret_cast<float (*)[MAXG][D]>(lut);  // the per-warp outputs reuse the table once the loop is over
+  for (int i4 = threadIdx.x; i4 < 256 * 8; i4 += blockDim.x) {
+    const int e = i4 >> 3;
+    const uint32_t v = h2_as_u32(__floats2half2_rn(c_kv_levels[e & 15], c_kv_levels[e >> 4]));
+    *reinterpret_cast<uint4*>(&lut[i4 * 4]) = make_uint4(v, v, v, v);
+  }
+  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int G = H / Hkv;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int len = seq_lens[b];
+  const int npages = (len + PAGE - 1) / PAGE;
+  const int per = (npages + splits - 1) / splits;
+  const int p0 = split * per, p1 = min(npages, p0 + per);
+  const float c = scale * 1.4426950408889634f;
+  // Q fragment: row gid = query head, this lane's d-quarter; rows 8..15 of the MMA are zero
+  uint32_t qa[KSTEPS][2];
+  {
+    const __nv_bfloat16* qrow = q + (long)b * ld_q + (hk * G + min(gid, G - 1)) * D + tig * KCH;
+#pragma unroll
+    for (int st = 0; st < KSTEPS; ++st) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(qrow + st * 4);
+      const float f0 = __uint_as_float(raw.x << 16) * c, f1 = __uint_as_float(raw.x & 0xffff0000u) * c;
+      const float f2 = __uint_as_float(raw.y << 16) * c, f3 = __uint_as_float(raw.y & 0xffff0000u) * c;
+      qa[st][0] = gid < G ? h2_as_u32(__floats2half2_rn(f0, f1)) : 0u;
+      qa[st][1] = gid < G ? h2_as_u32(__floats2half2_rn(f2, f3)) : 0u;
+    }
+  }
+  __syncthreads();
+  float m_run = -INFINITY, l_run = 0.f;  // of head gid; l is this lane's share (its 4 tokens per page)
+  float o[VMMA][4];
+#pragma unroll
+  for (int i = 0; i < VMMA; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  uint32_t kraw[2][KW], vraw[4][VW];
+  __half ksc[2], vsc[4];
+  auto fetch = [&](int pg) {
+    const int page = page_table[(long)b * max_pages + pg];
+    const long row0 = ((long)page * Hkv + hk) * PAGE;
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {  // K: tokens gid and gid + 8, bytes of d-quarter tig
+      const long row = row0 + gid + 8 * t;
+      const uint8_t* kp = k_pool + row * (D / 2) + tig * (KCH / 2);
+      if (KW == 4) {
+        const uint4 v4 = *reinterpret_cast<const uint4*>(kp);
+        kraw[t][0] = v4.x; kraw[t][1] = v4.y; kraw[t][2 % KW] = v4.z; kraw[t][3 % KW] = v4.w;
+      } else {
+        const uint2 v2 = *reinterpret_cast<const uint2*>(kp);
+        kraw[t][0] = v2.x; kraw[t][1] = v2.y;
+      }
+      ksc[t] = k_scale[row * (D / 32) + (tig * KCH) / 32];
+    }
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {  // V: tokens 2 tig, 2 tig + 1, 2 tig + 8, 2 tig + 9, bytes of d-chunk gid
+      const long row = row0 + 2 * tig + (t & 1) + 8 * (t >> 1);
+      const uint8_t* vp = v_pool + row * (D / 2) + gid * (VCH / 2);
+      if (VW == 2) {
+        const uint2 v2 = *reinterpret_cast<const uint2*>(vp);
+        vraw[t][0] = v2.x; vraw[t][1 % VW] = v2.y;
+      } else {
+        vraw[t][0] = *reinterpret_cast<const uint32_t*>(vp);
+      }
+      vsc[t] = v_scale[row * (D / 32) + (gid * VCH) / 32];
+    }
+  };
+  int pg = p0 + warp;
+  if (pg < p1) fetch(pg);
+  for (; pg < p1; pg += 4) {
+    // ---- this page's registers; then start the next page's loads ----
+    uint32_t kr[2][KW], vr[4][VW];
+    __half2 ks2[2], vs2[4];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+#pragma unroll
+      for (int w = 0; w < KW; ++w) kr[t][w] = kraw[t][w];
+      ks2[t] = __half2half2(ksc[t]);
+    }
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+#pragma unroll
+      for (int w = 0; w < VW; ++w) vr[t][w] = vraw[t][w];
+      const int tok = pg * PAGE + 2 * tig + (t & 1) + 8 * (t >> 1);
+      vs2[t] = tok < len ? __half2half2(vsc[t]) : __float2half2_rn(0.f);  // rows past the end may hold anything
+    }
+    if (pg + 4 < p1) fetch(pg + 4);
+    // ---- scores: two n-tiles of 8 tokens ----
+    float s[2][4];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
+#pragma unroll
+      for (int st = 0; st < KSTEPS; ++st) {
+        // bytes 2 st and 2 st + 1 of the lane's chunk: d-values 4 st .. 4 st + 3
+        const uint32_t two = kr[t][st >> 1] >> (16 * (st & 1));
+        const __half2 k01 = __hmul2(u32_as_h2(lut[((two & 255) << 5) + lane]), ks2[t]);
+        const __half2 k23 = __hmul2(u32_as_h2(lut[(((two >> 8) & 255) << 5) + lane]), ks2[t]);
+        const uint32_t a[4] = {qa[st][0], 0u, qa[st][1], 0u};
+        mma_16816(s[t], a, h2_as_u32(k01), h2_as_u32(k23));
+      }
+    }
+    // lane: head gid, tokens {2 tig, 2 tig + 1} (+ 8 for the second tile) in s[t][0], s[t][1]
+    float sv[4];
+#pragma unroll
+    for (int t = 0; t < 2; ++t)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int tok = pg * PAGE + 8 * t + 2 * tig + e;
+        sv[t * 2 + e] = tok < len ? s[t][e] : -INFINITY;
+      }
+    float mx = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);  // finite: a page in range has at least its first token valid
+    const float alpha = exp2f(m_run - m_new);  // 0 on the first page (m_run = -inf)
+    float pe[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pe[i] = exp2f(sv[i] - m_new);
+    l_run = l_run * alpha + (pe[0] + pe[1]) + (pe[2] + pe[3]);
+    m_run = m_new;
+    const uint32_t pb0 = h2_as_u32(__floats2half2_rn(pe[0], pe[1])), pb1 = h2_as_u32(__floats2half2_rn(pe[2], pe[3]));
+    // ---- rescale O^T: this lane's columns are heads 2 tig and 2 tig + 1, whose factors live in lanes 8 tig, 8 tig + 4 ----
+    const float al0 = __shfl_sync(0xffffffffu, alpha, 8 * tig), al1 = __shfl_sync(0xffffffffu, alpha, 8 * tig + 4);
+    if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+      for (int i = 0; i < VMMA; ++i) {
+        o[i][0] *= al0; o[i][1] *= al1; o[i][2] *= al0; o[i][3] *= al1;
+      }
+    }
+    // ---- values: MMA i covers d = gid * VCH + 2 i (row gid) and + 1 (row gid + 8) ----
+#pragma unroll
+    for (int i = 0; i < VMMA; ++i) {
+      __half2 x[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const uint32_t byte = (vr[t][i >> 2] >> (8 * (i & 3))) & 255;
+        x[t] = __hmul2(u32_as_h2(lut[(byte << 5) + lane]), vs2[t]);  // (V[token t][d], V[token t][d + 1])
+      }
+      uint32_t a[4];
+      a[0] = __byte_perm(h2_as_u32(x[0]), h2_as_u32(x[1]), 0x5410);  // row d,     tokens 2 tig, 2 tig + 1
+      a[1] = __byte_perm(h2_as_u32(x[0]), h2_as_u32(x[1]), 0x7632);  // row d + 1, same tokens
+      a[2] = __byte_perm(h2_as_u32(x[2]), h2_as_u32(x[3]), 0x5410);  // row d,     tokens + 8
+      a[3] = __byte_perm(h2_as_u32(x[2]), h2_as_u32(x[3]), 0x7632);
+      mma_16816(o[i], a, pb0, pb1);
+    }
+  }
+  // ---- fold the lanes' shares of l, then the 4 warps ----
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  if (tig == 0 && gid < G) {
+    sm_m[warp][gid] = m_run;
+    sm_l[warp][gid] = l_run;
+  }
+  __syncthreads();  // every warp is done with the table
+#pragma unroll
+  for (int i = 0; i < VMMA; ++i) {
+    const int d0 = gid * VCH + 2 * i;
+    if (2 * tig < G) {
+      sm_o[warp][2 * tig][d0] = o[i][0];
+      sm_o[warp][2 * tig][d0 + 1] = o[i][2];
+    }
+    if (2 * tig + 1 < G) {
+      sm_o[warp][2 * tig + 1][d0] = o[i][1];
+      sm_o[warp][2 * tig + 1][d0 + 1] = o[i][3];
+    }
+  }
+  __syncthreads();
+  float* out = part + (((long)b * Hkv + hk) * splits + split) * (long)G * (D + 2);
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+    const int g = i / D, e = i % D;
+    float mm = -INFINITY;
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_m[w][g]);
+    float acc = 0.f, ll = 0.f;
+    for (int w = 0; w < 4; ++w) {
+      const float f = sm_m[w][g] == -INFINITY ? 0.f : exp2f(sm_m[w][g] - mm);
+      acc += sm_o[w][g][e] * f;
+      ll += sm_l[w][g] * f;
+    }
+    out[g * (D + 2) + 2 + e] = acc;
+    if (e == 0) {
+      out[g * (D + 2)] = mm;
+      out[g * (D + 2) + 1] = ll;
+    }
+  }
+}
+
 // out[b, h*D + e] = sum_s o_s * 2^(m_s - m) / sum_s l_s * 2^(m_s - m)
 __global__ void attn_combine_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int ld_o, int B, int H, int Hkv, int D,
                                     int splits) {
@@ -477,7 +697,7 @@ extern "C" int inv_paged_decode(const void* q, int ld_q, const int* page_table, 
                                                    (const __half*)v_scale, scale, scratch, splits)
   if (oil4) {
 #define INV_PD4(DD)                                                                                                                        \
-  paged_decode_oil4_kernel<DD><<<grid, 128, 0, st>>>((const __nv_bfloat16*)q, ld_q, page_table, max_pages, seq_lens, H, Hkv,               \
+  paged_decode_oil4_mma_kernel<DD><<<grid, 128, 0, st>>>((const __nv_bfloat16*)q, ld_q, page_table, max_pages, seq_lens, H, Hkv,               \
                                                      (const uint8_t*)k_pool, (const uint8_t*)v_pool, (const __half*)k_scale,               \
                                                      (const __half*)v_scale, scale, scratch, splits)
     if (D == 64) INV_PD4(64); else INV_PD4(128);

@@ -24,6 +24,9 @@ _native.register_cuda_sigs({
                      _native.i32, _native.i32, _native.vp, _native.vp, _native.i32],
     "inv_oil_gemm_finish": [_native.vp, _native.vp, _native.vp, _native.vp, _native.i64, _native.i32, _native.i32, _native.i32, _native.i32,
                             _native.i32, _native.vp],
+    "inv_oil_gemm_finish_swiglu": [_native.vp, _native.vp, _native.vp, _native.i64, _native.i32, _native.i32, _native.i32, _native.vp],
+    "inv_oil_gemm_finish_norm": [_native.vp, _native.vp, _native.vp, _native.vp, _native.vp, _native.f32, _native.vp, _native.i64, _native.i32,
+                                 _native.i32, _native.i32, _native.i32, _native.i32, _native.vp],
 })
 
 
@@ -87,6 +90,21 @@ def quantize_weight(w: torch.Tensor, fmt: str = "oil4", codebook: Optional[torch
 _acc = {}
 
 
+def _acc_for(x: torch.Tensor, qw: QuantWeight, M: int) -> torch.Tensor:
+    key = (x.device.index, qw.N)
+    acc = _acc.get(key)
+    if acc is None or acc.shape[0] < min(M, 256):
+        acc = torch.zeros((256, qw.N), dtype=torch.float32, device=x.device)  # kept zero between calls by the finish kernels
+        _acc[key] = acc
+    return acc
+
+
+def _gemm_into_acc(xs: torch.Tensor, qw: QuantWeight, acc: torch.Tensor):
+    status = rt.status_tensor(xs.device).data_ptr()
+    rt.check(rt.lib().inv_oil_gemm(xs.data_ptr(), xs.stride(0), qw.idx.data_ptr(), qw.scales.data_ptr(), qw.codebook.data_ptr(), qw.bits,
+                                   acc.data_ptr(), acc.stride(0), xs.shape[0], qw.N, qw.K, 0, status, rt.stream_ptr(), 0), "inv_oil_gemm")
+
+
 def oil_linear(x: torch.Tensor, qw: QuantWeight, residual: Optional[torch.Tensor] = None, split_k: int = 0) -> torch.Tensor:
     """x [..., K] bf16 -> [..., N] bf16."""
     shp = x.shape
@@ -100,19 +118,60 @@ def oil_linear(x: torch.Tensor, qw: QuantWeight, residual: Optional[torch.Tensor
         x2 = x2.contiguous()
     M = x2.shape[0]
     out = torch.empty((M, qw.N), dtype=torch.bfloat16, device=x.device)
-    key = (x.device.index, qw.N)
-    acc = _acc.get(key)
-    if acc is None or acc.shape[0] < min(M, 256):
-        acc = torch.zeros((256, qw.N), dtype=torch.float32, device=x.device)  # kept zero between calls by the finish kernel
-        _acc[key] = acc
+    acc = _acc_for(x, qw, M)
     res2 = None if residual is None else residual.reshape(-1, qw.N)
-    status = rt.status_tensor(x.device).data_ptr()
     for m0 in range(0, M, 256):
         m1 = min(M, m0 + 256)
-        xs = x2[m0:m1]
-        rt.check(rt.lib().inv_oil_gemm(xs.data_ptr(), xs.stride(0), qw.idx.data_ptr(), qw.scales.data_ptr(), qw.codebook.data_ptr(), qw.bits,
-                                       acc.data_ptr(), acc.stride(0), m1 - m0, qw.N, qw.K, split_k, status, rt.stream_ptr(), 0), "inv_oil_gemm")
+        _gemm_into_acc(x2[m0:m1], qw, acc)
         rs = None if res2 is None else res2[m0:m1]
         rt.check(rt.lib().inv_oil_gemm_finish(acc.data_ptr(), rt.ptr(qw.bias), rt.ptr(rs), out[m0:m1].data_ptr(), m1 - m0, qw.N, acc.stride(0),
                                               out.stride(0), 0 if rs is None else rs.stride(0), 1, rt.stream_ptr()), "inv_oil_gemm_finish")
     return out.view(*shp[:-1], qw.N)
+
+
+def oil_linear_swiglu(x: torch.Tensor, qw: QuantWeight) -> torch.Tensor:
+    """silu(g) * u with [g | u] = x W^T (+ b): the gate / up projection, its finish and the activation in two kernels
+    (the GEMM, and one pass over the fp32 accumulator). x [..., K] -> [..., N / 2]."""
+    shp = x.shape
+    x2 = x.reshape(-1, qw.K)
+    Fh = qw.N // 2
+    if not x2.is_cuda or Fh % 4:
+        from .functional import swiglu
+        return swiglu(oil_linear(x, qw))
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    M = x2.shape[0]
+    out = torch.empty((M, Fh), dtype=torch.bfloat16, device=x.device)
+    acc = _acc_for(x, qw, M)
+    for m0 in range(0, M, 256):
+        m1 = min(M, m0 + 256)
+        _gemm_into_acc(x2[m0:m1], qw, acc)
+        rt.check(rt.lib().inv_oil_gemm_finish_swiglu(acc.data_ptr(), rt.ptr(qw.bias), out[m0:m1].data_ptr(), m1 - m0, Fh, acc.stride(0),
+                                                     out.stride(0), rt.stream_ptr()), "inv_oil_gemm_finish_swiglu")
+    return out.view(*shp[:-1], Fh)
+
+
+def finish_norm(acc: torch.Tensor, M: int, N: int, bias, residual, norm_w: torch.Tensor, eps: float):
+    """(x, h) from an fp32 accumulator [>= M, N]: x = bf16(acc + bias + residual), h = rms_norm(x) * norm_w. Clears acc."""
+    x_out = torch.empty((M, N), dtype=torch.bfloat16, device=acc.device)
+    h_out = torch.empty((M, N), dtype=torch.bfloat16, device=acc.device)
+    rt.check(rt.lib().inv_oil_gemm_finish_norm(acc.data_ptr(), rt.ptr(bias), rt.ptr(residual), x_out.data_ptr(), norm_w.data_ptr(), float(eps),
+                                               h_out.data_ptr(), M, N, acc.stride(0) if acc.dim() == 2 else N, N,
+                                               0 if residual is None else residual.stride(0), N, rt.stream_ptr()), "inv_oil_gemm_finish_norm")
+    return x_out, h_out
+
+
+def oil_linear_norm(x: torch.Tensor, qw: QuantWeight, residual: torch.Tensor, norm_w: torch.Tensor, eps: float):
+    """(y, rms_norm(y) * norm_w) with y = x W^T (+ b) + residual: a block's closing projection fused with the next
+    block's RMSNorm. x [M, K], residual [M, N] -> two [M, N] bf16 tensors."""
+    x2 = x.reshape(-1, qw.K)
+    M = x2.shape[0]
+    if not x2.is_cuda or qw.N % 4 or qw.N > 16384 or M > 256:
+        from .functional import rms_norm
+        y = oil_linear(x2, qw, residual)
+        return y, rms_norm(y, norm_w, eps)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    acc = _acc_for(x, qw, M)
+    _gemm_into_acc(x2, qw, acc)
+    return finish_norm(acc, M, qw.N, qw.bias, residual.reshape(M, qw.N), norm_w, eps)

@@ -26,7 +26,7 @@ from .. import ops
 from ..inference.kv_cache import PagedKVCache, PAGE
 from ..models.config import TransformerConfig
 from ..ops import runtime as rt
-from ..ops.oil_linear import QuantWeight, oil_linear, quantize_weight
+from ..ops.oil_linear import QuantWeight, finish_norm, oil_linear, oil_linear_norm, oil_linear_swiglu, quantize_weight
 
 
 class TPContext:
@@ -57,12 +57,15 @@ class TPContext:
 
 
 def tp_reduce_linear(x: torch.Tensor, qw: QuantWeight, ctx: Optional[TPContext], residual=None, n_total: Optional[int] = None,
-                     n_offset: int = 0, out_fp32: bool = False) -> torch.Tensor:
+                     n_offset: int = 0, out_fp32: bool = False, norm=None):
     """y[M, n_total] = sum over ranks of x_local @ W_local^T, every rank receiving the full result.
 
     Row-parallel layers pass n_offset = 0 and n_total = qw.N (true reduction); the vocabulary-parallel
-    head passes its column offset, so that the "reduction" is an all-gather into disjoint columns."""
+    head passes its column offset, so that the "reduction" is an all-gather into disjoint columns.
+    With ``norm = (weight, eps)`` the finish pass also applies the next RMSNorm and the call returns (y, normed y)."""
     if ctx is None or ctx.world == 1:
+        if norm is not None:
+            return oil_linear_norm(x, qw, residual, norm[0], norm[1])
         y = oil_linear(x, qw, residual)
         return y.float() if out_fp32 else y
     x2 = x.reshape(-1, qw.K)
@@ -88,8 +91,10 @@ def tp_reduce_linear(x: torch.Tensor, qw: QuantWeight, ctx: Optional[TPContext],
         y = acc[: M * n_total].view(M, n_total).clone()
         acc[: M * n_total].zero_()
         return y
-    out = torch.empty((M, n_total), dtype=torch.bfloat16, device=x.device)
     res2 = None if residual is None else residual.reshape(M, n_total)
+    if norm is not None:
+        return finish_norm(acc[: M * n_total].view(M, n_total), M, n_total, qw.bias, res2, norm[0], norm[1])
+    out = torch.empty((M, n_total), dtype=torch.bfloat16, device=x.device)
     rt.check(lib.inv_oil_gemm_finish(acc.data_ptr(), rt.ptr(qw.bias), rt.ptr(res2), out.data_ptr(), M, n_total, n_total, n_total,
                                      0 if res2 is None else res2.stride(0), 1, st), "inv_oil_gemm_finish")
     return out
@@ -184,8 +189,8 @@ class TPDecoder:
         c.commit(list(range(B)), [S] * B)
         return self._logits(x[:, -1].contiguous())
 
-    def _logits(self, last: torch.Tensor) -> torch.Tensor:
-        h = ops.rms_norm(last, self.norm_w, self.cfg.norm_eps)
+    def _logits(self, last: torch.Tensor, normed: bool = False) -> torch.Tensor:
+        h = last if normed else ops.rms_norm(last, self.norm_w, self.cfg.norm_eps)
         Vs = self.cfg.padded_vocab // self.world
         lg = tp_reduce_linear(h, self.head, self.ctx, n_total=self.cfg.padded_vocab, n_offset=self.rank * Vs, out_fp32=True)
         if self.ctx is not None:
@@ -207,8 +212,8 @@ class TPDecoder:
         x = self.emb[tokens]
         scale = D ** -0.5
         lib, st = rt.lib(), rt.stream_ptr()
+        h = ops.rms_norm(x, self.layers[0]["n1"], cfg.norm_eps)
         for li, l in enumerate(self.layers):
-            h = ops.rms_norm(x, l["n1"], cfg.norm_eps)
             qkv = oil_linear(h, l["qkv"]).view(B, 1, -1)
             qkv = ops.rope_qk(qkv, self.rope[0], self.rope[1], H, Hkv, D, pos)
             k, v = qkv[..., H * D:(H + Hkv) * D], qkv[..., (H + Hkv) * D:]
@@ -221,11 +226,12 @@ class TPDecoder:
                                           c.k_pool[li].data_ptr(), c.v_pool[li].data_ptr(), rt.ptr(c.k_scale[li]), rt.ptr(c.v_scale[li]),
                                           int(c.fmt == "oil4"), float(scale), a.data_ptr(), a.stride(0), self._scratch.data_ptr(),
                                           self._splits, st), "inv_paged_decode")
-            x = tp_reduce_linear(a, l["o"], self.ctx, residual=x)
-            h = ops.rms_norm(x, l["n2"], cfg.norm_eps)
-            act = ops.swiglu(oil_linear(h, l["gu"]))
-            x = tp_reduce_linear(act, l["down"], self.ctx, residual=x)
-        return self._logits(x)
+            # every projection's finish pass carries what follows it: the residual add and the next RMSNorm, or SwiGLU
+            x, h = tp_reduce_linear(a, l["o"], self.ctx, residual=x, norm=(l["n2"], cfg.norm_eps))
+            act = oil_linear_swiglu(h, l["gu"])
+            nxt = self.layers[li + 1]["n1"] if li + 1 < len(self.layers) else self.norm_w
+            x, h = tp_reduce_linear(act, l["down"], self.ctx, residual=x, norm=(nxt, cfg.norm_eps))
+        return self._logits(h, normed=True)
 
     @torch.no_grad()
     def generate(self, ids: torch.Tensor, max_new_tokens: int, use_graph: bool = True):
