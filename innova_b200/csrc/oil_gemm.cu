@@ -39,8 +39,8 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_
 namespace og {
 constexpr int BN = 128;     // weight rows per tile (MMA M)
 constexpr int BK = 64;      // k-block: one A stage, one activation tile
-constexpr int MAX_A_STAGES = 8; // dequantised A stages in tensor memory (32 columns each), also the depth of the activation ring
 constexpr int STG_PITCH = 132;  // floats per token row of the epilogue staging tile (128 weight rows + 4: conflict-free both ways)
+constexpr int STG_TOK = 16;     // tokens per staging pass
 constexpr int MAX_IDX_STAGES = 6;
 constexpr int THREADS = 320;
 constexpr int MAXM = 128;   // tokens per launch (MMA N); the host entry point splits larger M
@@ -55,7 +55,6 @@ struct OilGemmParams {
   float* out;  // [M, N] fp32
   int ldo;
   int idx_stages;  // depth of the raw index ring: whatever shared memory is left, at most MAX_IDX_STAGES
-  int a_stages;    // A stages in tensor memory = activation tiles in shared memory: 8, or 4 when M > 64
   int dp_rounds;   // whole tiles per CTA before the stream-K tail (tile = round * gridDim.x + blockIdx.x)
   int* status;
   int multimem;  // out is an NVLS multicast address: every partial sum is added into all ranks' copies
@@ -207,18 +206,17 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
   const int IDX_STAGES = p.idx_stages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const int A_STAGES = p.a_stages;
-  uint8_t* sX = smem;                                  // A_STAGES x X_TILE (a multiple of 2 KB)
-  uint8_t* sIdx = sX + A_STAGES * X_TILE;              // IDX_STAGES x IDX_TILE (swizzled by TMA: 1 KB aligned)
+  uint8_t* sX = smem;                                  // 2 slots x KBB activation tiles (X_TILE is a multiple of 2 KB)
+  uint8_t* sIdx = sX + 2 * KBB * X_TILE;               // IDX_STAGES x IDX_TILE (swizzled by TMA: 1 KB aligned)
   uint32_t* lut = reinterpret_cast<uint32_t*>(sIdx + IDX_STAGES * IDX_TILE);  // 256 entries x 32 bank copies
-  float* stage = reinterpret_cast<float*>(lut + 256 * 32);  // epilogue staging: per group 32 tokens x STG_PITCH
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stage + 2 * 32 * STG_PITCH);
+  float* stage = reinterpret_cast<float*>(lut + 256 * 32);  // epilogue staging: per group STG_TOK tokens x STG_PITCH
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stage + 2 * STG_TOK * STG_PITCH);
   uint64_t* idx_full = bars;
   uint64_t* idx_empty = idx_full + MAX_IDX_STAGES;
-  uint64_t* a_full = idx_empty + MAX_IDX_STAGES;
-  uint64_t* a_empty = a_full + MAX_A_STAGES;
-  uint64_t* x_full = a_empty + MAX_A_STAGES;
-  uint64_t* acc_full = x_full + MAX_A_STAGES;
+  uint64_t* a_full = idx_empty + MAX_IDX_STAGES;  // [2]: slot g holds the batch expanded by group g (KBB k-blocks, 32 TMEM columns each)
+  uint64_t* a_empty = a_full + 2;
+  uint64_t* x_full = a_empty + 2;                 // [2]: the activation tiles of the same batch
+  uint64_t* acc_full = x_full + 2;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -238,12 +236,10 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
       mbar_init(&idx_full[s], 1);
       mbar_init(&idx_empty[s], 4);  // the four warps of the group that expanded the tile
     }
-    for (int s = 0; s < A_STAGES; ++s) {
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&a_full[s], 4);
       mbar_init(&a_empty[s], 1);
       mbar_init(&x_full[s], 1);
-    }
-    for (int s = 0; s < 2; ++s) {
       mbar_init(&acc_full[s], 1);
       mbar_init(&acc_empty[s], 4);
     }
@@ -273,47 +269,50 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
         if (++si == IDX_STAGES) { si = 0; ph ^= 1; }
       }
     } else if (lane == 1) {
-      int it = 0;
-      bool ok = true;
-      for (OgCursor c(n_tiles, nb, p.dp_rounds); ok && c.valid; c.advance()) {
+      int lb = 0;
+      for (OgCursor c(n_tiles, nb, p.dp_rounds); c.valid; c.advance(), ++lb) {
         const int kb0 = c.bb * KBB, nkb = min(KBB, kb_total - kb0);
-        for (int kk = 0; kk < nkb; ++kk, ++it) {
-          const int sx = it % A_STAGES;
-          // the x stage is released together with the A stage (same MMA commit)
-          if (!mbar_wait(&a_empty[sx], ((it / A_STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
-          mbar_expect_tx(&x_full[sx], X_TILE);
-          tma_load_2d(sX + sx * X_TILE, &tmap_x, &x_full[sx], (kb0 + kk) * BK, 0);
-        }
+        const int slot = lb & 1;
+        // the activation slot is released together with the A slot (same MMA commit)
+        if (!mbar_wait(&a_empty[slot], ((lb >> 1) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_EMPTY)) break;
+        mbar_expect_tx(&x_full[slot], nkb * X_TILE);
+        for (int kk = 0; kk < nkb; ++kk) tma_load_2d(sX + (slot * KBB + kk) * X_TILE, &tmap_x, &x_full[slot], (kb0 + kk) * BK, 0);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc_bf16(128, p.Mpad, 0, 0);
-      int it = 0, seg = 0;
-      bool ok = true;
-      for (OgCursor c(n_tiles, nb, p.dp_rounds); ok && c.valid; c.advance()) {
-        const int kb0 = c.bb * KBB, nkb = min(KBB, kb_total - kb0);
-        bool first = c.seg_first();
+      // One thread runs at a few cycles per dependent instruction, so this loop is kept lean: one pair of waits and
+      // one commit per batch, descriptors advanced by additions.
+      const uint64_t xdesc0 = make_smem_desc(smem_u32(sX), 16, 1024, 2);
+      const uint32_t x_step = (uint32_t)(X_TILE >> 4);
+      int lb = 0, seg = 0;
+      for (OgCursor c(n_tiles, nb, p.dp_rounds); c.valid; c.advance(), ++lb) {
+        const int nkb = min(KBB, kb_total - c.bb * KBB);
+        const int slot = lb & 1;
+        const uint32_t ph = (lb >> 1) & 1;
+        const bool first = c.seg_first();
         if (first) {
           if (!mbar_wait(&acc_empty[seg & 1], ((seg >> 1) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) break;
-          tc_fence_after();
         }
+        if (!mbar_wait(&a_full[slot], ph, abort_flag, p.status, ERR_WAIT_FULL)) break;
+        if (!mbar_wait(&x_full[slot], ph, abort_flag, p.status, ERR_WAIT_FULL)) break;
+        tc_fence_after();
         const uint32_t acc = tmem_base + (seg & 1) * ACC_COLS;
-        for (int kk = 0; kk < nkb; ++kk, ++it) {
-          const int s = it % A_STAGES;
-          const uint32_t ph = (it / A_STAGES) & 1;
-          if (!mbar_wait(&a_full[s], ph, abort_flag, p.status, ERR_WAIT_FULL)) { ok = false; break; }
-          if (!mbar_wait(&x_full[s], ph, abort_flag, p.status, ERR_WAIT_FULL)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t x_base = smem_u32(sX + s * X_TILE);
+        const uint32_t a_col = tmem_base + A_COL0 + slot * (KBB * 32);
+        const uint64_t xd = xdesc0 + (uint64_t)(slot * KBB) * x_step;
+        umma_bf16_tmem_a(acc, a_col, xd, idesc, first ? 0u : 1u);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)  // 16 k = 8 packed columns of the A stage
-            umma_bf16_tmem_a(acc, tmem_base + A_COL0 + s * 32 + k * 8, make_smem_desc(x_base + k * 32, 16, 1024, 2), idesc,
-                             (!first || k > 0) ? 1u : 0u);
-          umma_commit(&a_empty[s]);
-          first = false;
+        for (int k = 1; k < BK / 16; ++k) umma_bf16_tmem_a(acc, a_col + k * 8, xd + k * 2, idesc, 1u);
+#pragma unroll
+        for (int kk = 1; kk < KBB; ++kk) {
+          if (kk < nkb) {
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k)  // 16 k = 8 packed columns of the A slot, 32 bytes of the swizzled activation row
+              umma_bf16_tmem_a(acc, a_col + kk * 32 + k * 8, xd + (uint64_t)kk * x_step + k * 2, idesc, 1u);
+          }
         }
-        if (!ok) break;
+        umma_commit(&a_empty[slot]);
         if (c.seg_last()) {
           umma_commit(&acc_full[seg & 1]);
           ++seg;
@@ -352,13 +351,13 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
     OgCursor pc(n_tiles, nb, p.dp_rounds);  // runs one own batch ahead of the main cursor
     if (grp == 1 && pc.valid) pc.advance();
     if (pc.valid) fetch_scales(pc.tile, pc.bb);
-    float* stg = stage + grp * (32 * STG_PITCH);
+    float* stg = stage + grp * (STG_TOK * STG_PITCH);
     const int gt = threadIdx.x - 64 - grp * 128;  // thread index inside the group
     const bool vec_ok = ((p.ldo & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
-    int it = 0, seg = 0, lb = 0;
+    int seg = 0, lb = 0;
     bool ok = true;
     for (OgCursor c(n_tiles, nb, p.dp_rounds); ok && c.valid; c.advance(), ++lb) {
-      const int kb0 = c.bb * KBB, nkb = min(KBB, kb_total - kb0);
+      const int nkb = min(KBB, kb_total - c.bb * KBB);
       const bool seg_end = c.seg_last();
       if ((lb & 1) == grp) {
         unsigned short sc[2 * KBB];
@@ -378,27 +377,22 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&idx_empty[si]);  // the tile lives in registers now
+        // group g owns A slot g: free once the MMAs of this group's previous batch have completed
+        if (!mbar_wait_warp(&a_empty[grp], ((lb >> 1) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+        tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < KBB; ++kk) {
           if (kk < nkb) {
-            const int s = (it + kk) % A_STAGES;
-            if (!mbar_wait_warp(&a_empty[s], (((it + kk) / A_STAGES) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
-            tc_fence_after();
             uint32_t o[32];
             const __nv_bfloat16_raw r0{sc[2 * kk]}, r1{sc[2 * kk + 1]};
             expand_row<BITS>(raw + kk * KB_CHUNKS, __nv_bfloat16(r0), __nv_bfloat16(r1), lut, cb, lane, o);
-            tmem_st_32x32(t_lane + A_COL0 + s * 32, o);
+            tmem_st_32x32(t_lane + A_COL0 + (grp * KBB + kk) * 32, o);
           }
         }
-        if (!ok) break;
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) {  // one arrival per warp and stage
-#pragma unroll
-          for (int kk = 0; kk < KBB; ++kk)
-            if (kk < nkb) mbar_arrive(&a_full[(it + kk) % A_STAGES]);
-        }
+        if (lane == 0) mbar_arrive(&a_full[grp]);  // one arrival per warp
         if (seg_end) {
           // ---- segment end: accumulator [weight row (lane), token (column)] -> out[token][tile * 128 + row] ----
           // The tile is transposed through shared memory 32 tokens at a time, so that a thread ends up with four
@@ -407,16 +401,15 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
           if (!mbar_wait_warp(&acc_full[seg & 1], (seg >> 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint32_t t_acc = t_lane + (seg & 1) * ACC_COLS;
-          for (int mh = 0; mh < p.Mpad; mh += 32) {
-            uint32_t v[32];
+          for (int mh = 0; mh < p.Mpad; mh += STG_TOK) {
+            uint32_t v[16];
             tmem_ld_32x16(t_acc + mh, v);
-            if (mh + 16 < p.Mpad) tmem_ld_32x16(t_acc + mh + 16, v + 16);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) stg[j * STG_PITCH + r] = __uint_as_float(v[j]);
+            for (int j = 0; j < 16; ++j) stg[j * STG_PITCH + r] = __uint_as_float(v[j]);
             asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
+            for (int k = 0; k < 4; ++k) {
               const int e = k * 128 + gt, m = e >> 5, n4 = (e & 31) * 4;
               const int gm = mh + m, n = c.tile * BN + n4;
               if (gm < p.M && n < p.N) {
@@ -447,7 +440,6 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
           if (lane == 0) mbar_arrive(&acc_empty[seg & 1]);
         }
       }
-      it += nkb;
       if (seg_end) ++seg;
     }
   }
@@ -605,8 +597,7 @@ static int oil_gemm_launch(const void* x, int ldx, const void* idx, const void* 
   if ((rc = make_tmap_bytes(&ti, idx, (uint64_t)row_bytes, (uint64_t)N, rowb, BN))) return rc;
   if ((rc = make_tmap_2d_bf16(&tx, x, (uint64_t)K, (uint64_t)M, (uint64_t)ldx, BK, (uint32_t)p.Mpad))) return rc;
   const int idx_tile = BN * rowb;
-  p.a_stages = p.Mpad <= 64 ? MAX_A_STAGES : 4;
-  const int fixed = 1024 + p.a_stages * p.Mpad * BK * 2 + 256 * 32 * 4 + 2 * 32 * STG_PITCH * 4 + (2 * MAX_IDX_STAGES + 3 * MAX_A_STAGES + 4) * 8 + 16 + 1024 + 64;
+  const int fixed = 1024 + 2 * kbb * p.Mpad * BK * 2 + 256 * 32 * 4 + 2 * STG_TOK * STG_PITCH * 4 + (2 * MAX_IDX_STAGES + 10) * 8 + 16 + 1024 + 64;
   int stages = (227 * 1024 - fixed) / idx_tile;
   if (stages > MAX_IDX_STAGES) stages = MAX_IDX_STAGES;
   if (stages < 2) return -ERR_BAD_ARG;
