@@ -42,9 +42,9 @@ constexpr int BK = 64;      // k-block: one A stage, one activation tile
 constexpr int STG_PITCH = 132;  // floats per token row of the epilogue staging tile (128 weight rows + 4: conflict-free both ways)
 constexpr int STG_TOK = 16;     // tokens per staging pass
 constexpr int MAX_IDX_STAGES = 6;
-constexpr int THREADS = 320;
+constexpr int THREADS = 352;  // warp 0 TMA, warps 1 and 10 MMA issuers, warps 2-9 expand
 constexpr int MAXM = 128;   // tokens per launch (MMA N); the host entry point splits larger M
-constexpr int ACC_COLS = 128, A_COL0 = 256;  // TMEM: two accumulators [0,128) [128,256), A ring [256,512)
+constexpr int A_COL0 = 256;  // TMEM: accumulators in [0,256) (per buffer and issuer), A slots in [256,512)
 }  // namespace og
 
 struct OilGemmParams {
@@ -216,8 +216,8 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
   uint64_t* a_full = idx_empty + MAX_IDX_STAGES;  // [2]: slot g holds the batch expanded by group g (KBB k-blocks, 32 TMEM columns each)
   uint64_t* a_empty = a_full + 2;
   uint64_t* x_full = a_empty + 2;                 // [2]: the activation tiles of the same batch
-  uint64_t* acc_full = x_full + 2;
-  uint64_t* acc_empty = acc_full + 2;
+  uint64_t* acc_full = x_full + 2;   // [buffer][owner group]: a barrier is always waited on by the same group, use after use
+  uint64_t* acc_empty = acc_full + 4;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* cb = reinterpret_cast<float*>(tmem_slot + 2);  // codebook copy, 256 entries
@@ -240,7 +240,8 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
       mbar_init(&a_full[s], 4);
       mbar_init(&a_empty[s], 1);
       mbar_init(&x_full[s], 1);
-      mbar_init(&acc_full[s], 1);
+      mbar_init(&acc_full[2 * s], 2);  // one commit per MMA issuer
+      mbar_init(&acc_full[2 * s + 1], 2);
       mbar_init(&acc_empty[s], 4);
     }
     *abort_flag = 0;
@@ -279,47 +280,55 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
         for (int kk = 0; kk < nkb; ++kk) tma_load_2d(sX + (slot * KBB + kk) * X_TILE, &tmap_x, &x_full[slot], (kb0 + kk) * BK, 0);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 10) {
+    // Two MMA issuers, one per expanding group (a thread issues one tcgen05.mma per ~100 cycles whatever its size, so
+    // with 64 tokens per instruction a single issuer would be the bottleneck). Issuer g multiplies the batches of
+    // group g into its own accumulator; the epilogue adds the two. A thread runs at a few cycles per dependent
+    // instruction, so the loop is kept lean: one pair of waits and one commit per batch, descriptors advanced by
+    // additions.
     if (lane == 0) {
+      const int g = warp == 1 ? 0 : 1;
       const uint32_t idesc = make_idesc_bf16(128, p.Mpad, 0, 0);
-      // One thread runs at a few cycles per dependent instruction, so this loop is kept lean: one pair of waits and
-      // one commit per batch, descriptors advanced by additions.
-      const uint64_t xdesc0 = make_smem_desc(smem_u32(sX), 16, 1024, 2);
+      const uint64_t xdesc0 = make_smem_desc(smem_u32(sX), 16, 1024, 2) + (uint64_t)(g * KBB) * (uint32_t)(X_TILE >> 4);
       const uint32_t x_step = (uint32_t)(X_TILE >> 4);
-      int lb = 0, seg = 0;
+      const uint32_t a_col = tmem_base + A_COL0 + g * (KBB * 32);
+      const int nbuf = p.Mpad <= 64 ? 2 : 1, accw = p.Mpad <= 64 ? 64 : 128;
+      int lb = 0, seg = 0, seg_lb0 = 0;
       for (OgCursor c(n_tiles, nb, p.dp_rounds); c.valid; c.advance(), ++lb) {
-        const int nkb = min(KBB, kb_total - c.bb * KBB);
-        const int slot = lb & 1;
-        const uint32_t ph = (lb >> 1) & 1;
-        const bool first = c.seg_first();
-        if (first) {
-          if (!mbar_wait(&acc_empty[seg & 1], ((seg >> 1) & 1) ^ 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) break;
+        const int buf = nbuf == 2 ? (seg & 1) : 0, use = nbuf == 2 ? (seg >> 1) : seg;
+        if (c.seg_first()) {
+          seg_lb0 = lb;
+          // both issuers wait here, owner of a batch in this segment or not: nobody may commit for this use of the
+          // buffer before the previous use has been read out
+          if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) break;
         }
-        if (!mbar_wait(&a_full[slot], ph, abort_flag, p.status, ERR_WAIT_FULL)) break;
-        if (!mbar_wait(&x_full[slot], ph, abort_flag, p.status, ERR_WAIT_FULL)) break;
-        tc_fence_after();
-        const uint32_t acc = tmem_base + (seg & 1) * ACC_COLS;
-        const uint32_t a_col = tmem_base + A_COL0 + slot * (KBB * 32);
-        const uint64_t xd = xdesc0 + (uint64_t)(slot * KBB) * x_step;
-        umma_bf16_tmem_a(acc, a_col, xd, idesc, first ? 0u : 1u);
+        if ((lb & 1) == g) {
+          const int nkb = min(KBB, kb_total - c.bb * KBB);
+          const uint32_t ph = (lb >> 1) & 1;
+          if (!mbar_wait(&a_full[g], ph, abort_flag, p.status, ERR_WAIT_FULL)) break;
+          if (!mbar_wait(&x_full[g], ph, abort_flag, p.status, ERR_WAIT_FULL)) break;
+          tc_fence_after();
+          const uint32_t acc = tmem_base + (buf * 2 + g) * accw;
+          umma_bf16_tmem_a(acc, a_col, xdesc0, idesc, (lb - seg_lb0) < 2 ? 0u : 1u);  // this issuer's first batch of the segment
 #pragma unroll
-        for (int k = 1; k < BK / 16; ++k) umma_bf16_tmem_a(acc, a_col + k * 8, xd + k * 2, idesc, 1u);
+          for (int k = 1; k < BK / 16; ++k) umma_bf16_tmem_a(acc, a_col + k * 8, xdesc0 + k * 2, idesc, 1u);
 #pragma unroll
-        for (int kk = 1; kk < KBB; ++kk) {
-          if (kk < nkb) {
+          for (int kk = 1; kk < KBB; ++kk) {
+            if (kk < nkb) {
 #pragma unroll
-            for (int k = 0; k < BK / 16; ++k)  // 16 k = 8 packed columns of the A slot, 32 bytes of the swizzled activation row
-              umma_bf16_tmem_a(acc, a_col + kk * 32 + k * 8, xd + (uint64_t)kk * x_step + k * 2, idesc, 1u);
+              for (int k = 0; k < BK / 16; ++k)  // 16 k = 8 packed columns of the A slot, 32 bytes of the swizzled activation row
+                umma_bf16_tmem_a(acc, a_col + kk * 32 + k * 8, xdesc0 + (uint64_t)kk * x_step + k * 2, idesc, 1u);
+            }
           }
+          umma_commit(&a_empty[g]);
         }
-        umma_commit(&a_empty[slot]);
         if (c.seg_last()) {
-          umma_commit(&acc_full[seg & 1]);
+          umma_commit(&acc_full[buf * 2 + (lb & 1)]);  // the group that owns the last batch reads the segment out
           ++seg;
         }
       }
     }
-  } else {
+  } else if (warp >= 2 && warp < 10) {
     // lookup table: OIL4 -> bf16 pair (codebook[low nibble], codebook[high nibble]) per byte; OIL8 -> one bf16
     // entry e for lane l lives at lut[e * 32 + l]: every lane reads its own bank, whatever the indices are
     if (BITS != 2) {
@@ -354,7 +363,9 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
     float* stg = stage + grp * (STG_TOK * STG_PITCH);
     const int gt = threadIdx.x - 64 - grp * 128;  // thread index inside the group
     const bool vec_ok = ((p.ldo & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    const int nbuf = p.Mpad <= 64 ? 2 : 1, accw = p.Mpad <= 64 ? 64 : 128;
     int seg = 0, lb = 0;
+    uint32_t full_par = 0;  // bit b: parity of this group's next wait on acc_full[b * 2 + grp]
     bool ok = true;
     for (OgCursor c(n_tiles, nb, p.dp_rounds); ok && c.valid; c.advance(), ++lb) {
       const int nkb = min(KBB, kb_total - c.bb * KBB);
@@ -398,15 +409,20 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
           // The tile is transposed through shared memory 32 tokens at a time, so that a thread ends up with four
           // consecutive weight rows of one token: one 16-byte store (whole tile) or vector reduction per thread.
           const bool full = c.seg_full() && !p.multimem;
-          if (!mbar_wait_warp(&acc_full[seg & 1], (seg >> 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+          const int buf = nbuf == 2 ? (seg & 1) : 0, use = nbuf == 2 ? (seg >> 1) : seg;
+          (void)use;
+          if (!mbar_wait_warp(&acc_full[buf * 2 + grp], (full_par >> buf) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+          full_par ^= 1u << buf;
           tc_fence_after();
-          const uint32_t t_acc = t_lane + (seg & 1) * ACC_COLS;
+          const uint32_t t_acc = t_lane + (buf * 2 + grp) * accw, t_other = t_lane + (buf * 2 + (grp ^ 1)) * accw;
+          const bool both = c.bb1 - c.bb0 >= 2;  // the other issuer contributed to this segment too
           for (int mh = 0; mh < p.Mpad; mh += STG_TOK) {
-            uint32_t v[16];
+            uint32_t v[16], v2[16];
             tmem_ld_32x16(t_acc + mh, v);
+            if (both) tmem_ld_32x16(t_other + mh, v2);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) stg[j * STG_PITCH + r] = __uint_as_float(v[j]);
+            for (int j = 0; j < 16; ++j) stg[j * STG_PITCH + r] = __uint_as_float(v[j]) + (both ? __uint_as_float(v2[j]) : 0.f);
             asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
@@ -437,7 +453,7 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
           }
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&acc_empty[seg & 1]);
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
       }
       if (seg_end) ++seg;
@@ -597,9 +613,10 @@ static int oil_gemm_launch(const void* x, int ldx, const void* idx, const void* 
   if ((rc = make_tmap_bytes(&ti, idx, (uint64_t)row_bytes, (uint64_t)N, rowb, BN))) return rc;
   if ((rc = make_tmap_2d_bf16(&tx, x, (uint64_t)K, (uint64_t)M, (uint64_t)ldx, BK, (uint32_t)p.Mpad))) return rc;
   const int idx_tile = BN * rowb;
-  const int fixed = 1024 + 2 * kbb * p.Mpad * BK * 2 + 256 * 32 * 4 + 2 * STG_TOK * STG_PITCH * 4 + (2 * MAX_IDX_STAGES + 10) * 8 + 16 + 1024 + 64;
+  const int fixed = 1024 + 2 * kbb * p.Mpad * BK * 2 + 256 * 32 * 4 + 2 * STG_TOK * STG_PITCH * 4 + (2 * MAX_IDX_STAGES + 12) * 8 + 16 + 1024 + 64;
   int stages = (227 * 1024 - fixed) / idx_tile;
   if (stages > MAX_IDX_STAGES) stages = MAX_IDX_STAGES;
+  stages &= ~1;  // even: a ring stage is then always read by the same expanding group, which sees every phase of its barrier
   if (stages < 2) return -ERR_BAD_ARG;
   p.idx_stages = stages;
   const int smem = fixed + stages * idx_tile;

@@ -79,7 +79,7 @@ def test_quant_weight_cpu_linear():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("fmt", ["oil4", "oil8"])
-@pytest.mark.parametrize("M,N,K", [(64, 768, 4096), (1, 256, 128), (200, 1000, 1344), (300, 128, 64), (64, 384, 2752), (128, 2048, 512)])
+@pytest.mark.parametrize("M,N,K", [(64, 768, 4096), (1, 256, 128), (200, 1000, 1344), (300, 128, 64), (64, 384, 2752), (128, 2048, 512), (128, 256, 128), (100, 640, 192)])
 def test_gpu_oil_gemm_matches_dequantised_matmul(fmt, M, N, K):
     from innova_b200.ops import runtime as rt
     from innova_b200.ops.oil_linear import quantize_weight, oil_linear
