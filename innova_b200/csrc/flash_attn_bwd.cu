@@ -22,7 +22,7 @@ namespace inv {
 
 int make_tmap_tokens_bf16(CUtensorMap* out, const void* ptr, int cols, int S, int B, int ld, int box_rows);
 
-constexpr int FB_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 softmax
+constexpr int FB_THREADS = 384;  // warp 0 TMA, warps 1, 10, 11 MMA issuers, warps 2-9 softmax
 
 struct FlashBwdParams {
   const float* lse;    // [B, H, S], log2 domain: log2(sum exp(scores))
@@ -97,12 +97,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     mbar_init(kv_full, 1);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&q_full[s], 1);
-      mbar_init(&q_empty[s], 1);
+      mbar_init(&q_empty[s], 2);  // the two issuers that read Q and dO
     }
-    mbar_init(s_full, 1);
+    mbar_init(s_full, 2);      // S^T and dP^T have one issuer each
     mbar_init(s_empty, 8);
     mbar_init(pds_full, 8);
-    mbar_init(mma2_done, 1);
+    mbar_init(mma2_done, 3);   // dV, dK and dQ have one issuer each
     mbar_init(dq_empty, 8);
     *abort_flag = 0;
     fence_barrier_init();
@@ -142,70 +142,76 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp >= 10) {
+    // Three MMA issuers in three warps. A thread issues one tcgen05.mma per ~100 cycles whatever its size, and a
+    // query block needs 32 (D = 64) or 64 of them: one issuer would spend more time issuing than the tensor pipe
+    // spends computing. Every accumulator has exactly one issuer, so the order of its updates is program order:
+    //   role 0 (warp 1):  S^T = K Q^T    and  dV += P^T dO
+    //   role 1 (warp 10): dP^T = V dO^T  and  dK += dS^T Q
+    //   role 2 (warp 11): dQ_blk = dS K
     if (lane == 0) {
+      const int role = warp == 1 ? 0 : warp - 9;
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);   // K-major x K-major
       const uint32_t idesc_kv = make_idesc_bf16(128, D, 0, 1);    // K-major A, MN-major B
       const uint32_t idesc_dq = make_idesc_bf16(128, D, 1, 1);    // MN-major A and B
       const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV);
       const uint32_t pt_base = smem_u32(sPt), dst_base = smem_u32(sdSt);
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, ERR_WAIT_FULL);
-      auto issue_s = [&](int it) -> bool {
+      auto issue_s = [&](int it) -> bool {  // roles 0 and 1
         const int st = it % STAGES;
         if (!mbar_wait(&q_full[st], (it / STAGES) & 1, abort_flag, p.status, ERR_WAIT_FULL)) return false;
         if (it > 0 && !mbar_wait(s_empty, (it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) return false;
-        if (!OVERLAP && it > 0 && !mbar_wait(dq_empty, (it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) return false;
+        if (!OVERLAP && role == 0 && it > 0 && !mbar_wait(dq_empty, (it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) return false;
         tc_fence_after();
-        const uint32_t q_base = smem_u32(sQ + st * L::TILE), do_base = smem_u32(sdO + st * L::TILE);
+        const uint32_t a_base = role == 0 ? k_base : v_base;
+        const uint32_t b_base = smem_u32((role == 0 ? sQ : sdO) + st * L::TILE);
+        const uint32_t d_col = tmem_base + (role == 0 ? ST_COL : DPT_COL);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
-          umma_bf16(tmem_base + ST_COL, make_smem_desc(k_base + off, 16, 1024, 2), make_smem_desc(q_base + off, 16, 1024, 2), idesc_s, ks > 0);
-        }
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks / 4) * 16384 + (ks % 4) * 32;
-          umma_bf16(tmem_base + DPT_COL, make_smem_desc(v_base + off, 16, 1024, 2), make_smem_desc(do_base + off, 16, 1024, 2), idesc_s, ks > 0);
+          umma_bf16(d_col, make_smem_desc(a_base + off, 16, 1024, 2), make_smem_desc(b_base + off, 16, 1024, 2), idesc_s, ks > 0);
         }
         umma_commit(s_full);
         return true;
       };
-      if (ok && OVERLAP) ok = issue_s(0);
+      if (ok && OVERLAP && role < 2) ok = issue_s(0);
       for (int it = 0; ok && it < n_it; ++it) {
-        if (OVERLAP) {
-          if (it + 1 < n_it && !issue_s(it + 1)) break;
-        } else {
-          if (!issue_s(it)) break;
+        if (role < 2) {
+          if (OVERLAP) {
+            if (it + 1 < n_it && !issue_s(it + 1)) break;
+          } else {
+            if (!issue_s(it)) break;
+          }
         }
         const int st = it % STAGES;
         if (!mbar_wait(pds_full, it & 1, abort_flag, p.status, ERR_WAIT_MISC)) break;
-        if (OVERLAP && it > 0 && !mbar_wait(dq_empty, (it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) break;
+        if (OVERLAP && role == 2 && it > 0 && !mbar_wait(dq_empty, (it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
-        const uint32_t q_base = smem_u32(sQ + st * L::TILE), do_base = smem_u32(sdO + st * L::TILE);
-        // dV += P^T dO ; dK += dS^T Q   (A: [keys x queries] K-major, B: [queries x d] MN-major)
+        if (role < 2) {
+          // dV += P^T dO ; dK += dS^T Q   (A: [keys x queries] K-major, B: [queries x d] MN-major)
+          const uint32_t a_base = role == 0 ? pt_base : dst_base;
+          const uint32_t b_base = smem_u32((role == 0 ? sdO : sQ) + st * L::TILE);
+          const uint32_t d_col = tmem_base + (role == 0 ? DV_COL : DK_COL);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t a_off = (ks / 4) * 16384 + (ks % 4) * 32;
-          umma_bf16(tmem_base + DV_COL, make_smem_desc(pt_base + a_off, 16, 1024, 2), make_smem_desc(do_base + ks * 2048, 16384, 1024, 2),
-                    idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
-        }
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t a_off = (ks / 4) * 16384 + (ks % 4) * 32;
+            umma_bf16(d_col, make_smem_desc(a_base + a_off, 16, 1024, 2), make_smem_desc(b_base + ks * 2048, 16384, 1024, 2), idesc_kv,
+                      (it > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit(mma2_done);
+          umma_commit(&q_empty[st]);  // both roles read Q and dO of this stage
+        } else {
+          // dQ_blk = dS K   (A: dS^T tile read MN-major, B: K tile read MN-major; reduction over keys)
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t a_off = (ks / 4) * 16384 + (ks % 4) * 32;
-          umma_bf16(tmem_base + DK_COL, make_smem_desc(dst_base + a_off, 16, 1024, 2), make_smem_desc(q_base + ks * 2048, 16384, 1024, 2),
-                    idesc_kv, (it > 0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < 8; ++ks) {
+            umma_bf16(tmem_base + DQ_COL, make_smem_desc(dst_base + ks * 2048, 16384, 1024, 2), make_smem_desc(k_base + ks * 2048, 16384, 1024, 2),
+                      idesc_dq, ks > 0);
+          }
+          umma_commit(mma2_done);
         }
-        // dQ_blk = dS K   (A: dS^T tile read MN-major, B: K tile read MN-major; reduction over keys)
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          umma_bf16(tmem_base + DQ_COL, make_smem_desc(dst_base + ks * 2048, 16384, 1024, 2), make_smem_desc(k_base + ks * 2048, 16384, 1024, 2),
-                    idesc_dq, ks > 0);
-        }
-        umma_commit(mma2_done);
-        umma_commit(&q_empty[st]);
       }
     }
-  } else {
+  } else if (warp >= 2 && warp < 10) {
     // ---------------- softmax warps ----------------
     const int q = warp & 3;            // TMEM lane quarter
     const int hf = (warp - 2) >> 2;    // which half of the columns

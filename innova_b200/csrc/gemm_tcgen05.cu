@@ -258,7 +258,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       const uint32_t a_kstep = A_MN ? 2048u : 32u;
       const uint32_t b_kstep = B_MN ? 2048u : 32u;
-      int it = 0, tile_i = 0;
+      // One thread executes a dependent instruction every few cycles, so everything that can be is hoisted out of the
+      // k loop: descriptors advance by additions, the ring position is a counter.
+      const uint64_t da0 = make_smem_desc(smem_u32(sA), a_lbo, a_sbo, 2), db0 = make_smem_desc(smem_u32(sB), b_lbo, b_sbo, 2);
+      const uint32_t a_k = a_kstep >> 4, b_k = b_kstep >> 4;
+      int s = 0, tile_i = 0;
+      uint32_t ph = 0;
       for (int w = bid; w < total_work; w += gdim) {
         WorkUnit u = decode_work(w, p, m_tiles, n_tiles, kb_total, kb_per_split);
         if (u.skip) continue;
@@ -268,20 +273,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         bool ok = true;
-        for (int kb = u.kb_begin; kb < u.kb_end; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
+        for (int kb = u.kb_begin; kb < u.kb_end; ++kb) {
           if (!mbar_wait(&full_bar[s], ph, abort_flag, p.status, ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_base = smem_u32(sA + s * A_STAGE_BYTES);
-          const uint32_t b_base = smem_u32(sB + s * B_STAGE_BYTES);
+          const uint64_t da = da0 + (uint64_t)(s * (A_STAGE_BYTES >> 4)), db = db0 + (uint64_t)(s * (B_STAGE_BYTES >> 4));
+          umma_bf16(d_tmem, da, db, idesc, kb > u.kb_begin ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = make_smem_desc(a_base + k * a_kstep, a_lbo, a_sbo, 2);
-            const uint64_t db = make_smem_desc(b_base + k * b_kstep, b_lbo, b_sbo, 2);
-            umma_bf16(d_tmem, da, db, idesc, (kb > u.kb_begin || k > 0) ? 1u : 0u);
-          }
+          for (int k = 1; k < BK / UMMA_K; ++k) umma_bf16(d_tmem, da + k * a_k, db + k * b_k, idesc, 1u);
           umma_commit(&empty_bar[s]);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
         umma_commit(&tmem_full[acc]);

@@ -192,7 +192,13 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       const uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1u : 0u, B_MN ? 1u : 0u);
       const uint32_t a_lbo = A_MN ? 8192u : 16u, b_lbo = B_MN ? 8192u : 16u, sbo = 1024u;
       const uint32_t a_kstep = A_MN ? 2048u : 32u, b_kstep = B_MN ? 2048u : 32u;
-      int it = 0, tile_i = 0;
+      // One thread executes a dependent instruction every few cycles, so everything that can be is hoisted out of the
+      // k loop: descriptors and barrier addresses advance by additions, the ring position is a counter.
+      const uint64_t da0 = make_smem_desc(smem_u32(sA), a_lbo, sbo, 2), db0 = make_smem_desc(smem_u32(sB), b_lbo, sbo, 2);
+      const uint32_t a_k = a_kstep >> 4, b_k = b_kstep >> 4;
+      const uint32_t e0 = mapa_shared(smem_u32(&empty_bar[0]), 0), e1 = mapa_shared(smem_u32(&empty_bar[0]), 1);
+      int s = 0, tile_i = 0;
+      uint32_t ph = 0;
       bool ok = true;
       for (int w = pair; ok && w < total_work; w += npairs, ++tile_i) {
         const WorkUnit2 u = decode_work2(w, m_tiles, n_tiles, kb_total, kb_per_split);
@@ -201,23 +207,17 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = u.kb_begin; kb < u.kb_end; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
+        for (int kb = u.kb_begin; kb < u.kb_end; ++kb) {
           if (!mbar_wait(&full_bar[s], ph, abort_flag, p.status, ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_base = smem_u32(sA + s * A_STAGE);
-          const uint32_t b_base = smem_u32(sB + s * B_STAGE);
+          const uint64_t da = da0 + (uint64_t)(s * (A_STAGE >> 4)), db = db0 + (uint64_t)(s * (B_STAGE >> 4));
+          umma_bf16_pair(d_tmem, da, db, idesc, kb > u.kb_begin ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = make_smem_desc(a_base + k * a_kstep, a_lbo, sbo, 2);
-            const uint64_t db = make_smem_desc(b_base + k * b_kstep, b_lbo, sbo, 2);
-            if (!(p.swap_lbo_sbo & 8)) umma_bf16_pair(d_tmem, da, db, idesc, (kb > u.kb_begin || k > 0) ? 1u : 0u);
-          }
+          for (int k = 1; k < BK / UMMA_K; ++k) umma_bf16_pair(d_tmem, da + k * a_k, db + k * b_k, idesc, 1u);
           // free this stage in both CTAs
-          const uint32_t e_local = smem_u32(&empty_bar[s]);
-          umma_commit_pair(mapa_shared(e_local, 0));
-          umma_commit_pair(mapa_shared(e_local, 1));
+          umma_commit_pair(e0 + s * 8);
+          umma_commit_pair(e1 + s * 8);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
         const uint32_t f_local = smem_u32(&tmem_full[acc]);
