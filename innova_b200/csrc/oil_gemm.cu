@@ -57,7 +57,8 @@ struct OilGemmParams {
   int idx_stages;  // depth of the raw index ring: whatever shared memory is left, at most MAX_IDX_STAGES
   int dp_rounds;   // whole tiles per CTA before the stream-K tail (tile = round * gridDim.x + blockIdx.x)
   int* status;
-  int multimem;  // out is an NVLS multicast address: every partial sum is added into all ranks' copies
+  int multimem;  // 1: out is an NVLS multicast address, every partial sum is added into all ranks' copies; 2: out may hold
+                 // other ranks' partial sums (a peer's buffer): always add, never store
 };
 
 typedef CUresult (*EncodeTiledFnO)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -408,7 +409,7 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
           // ---- segment end: accumulator [weight row (lane), token (column)] -> out[token][tile * 128 + row] ----
           // The tile is transposed through shared memory 32 tokens at a time, so that a thread ends up with four
           // consecutive weight rows of one token: one 16-byte store (whole tile) or vector reduction per thread.
-          const bool full = c.seg_full() && !p.multimem;
+          const bool full = c.seg_full() && p.multimem == 0;
           const int buf = nbuf == 2 ? (seg & 1) : 0, use = nbuf == 2 ? (seg >> 1) : seg;
           (void)use;
           if (!mbar_wait_warp(&acc_full[buf * 2 + grp], (full_par >> buf) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
@@ -432,8 +433,10 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
                 const float4 val = *reinterpret_cast<const float4*>(stg + m * STG_PITCH + n4);
                 float* o = p.out + (size_t)gm * p.ldo + n;
                 if (vec_ok && n + 3 < p.N) {
-                  if (p.multimem)
+                  if (p.multimem == 1)
                     asm volatile("multimem.red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(val.x), "f"(val.y), "f"(val.z), "f"(val.w) : "memory");
+                  else if (p.multimem == 2)
+                    asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(val.x), "f"(val.y), "f"(val.z), "f"(val.w) : "memory");
                   else if (full)
                     *reinterpret_cast<float4*>(o) = val;
                   else
@@ -443,7 +446,7 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
 #pragma unroll
                   for (int z = 0; z < 4; ++z)
                     if (n + z < p.N) {
-                      if (p.multimem) asm volatile("multimem.red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(o + z), "f"(vv[z]) : "memory");
+                      if (p.multimem == 1) asm volatile("multimem.red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(o + z), "f"(vv[z]) : "memory");
                       else atomicAdd(o + z, vv[z]);
                     }
                 }

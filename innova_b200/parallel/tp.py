@@ -84,7 +84,7 @@ def tp_reduce_linear(x: torch.Tensor, qw: QuantWeight, ctx: Optional[TPContext],
         for k in range(ctx.world):
             peer = buf.peer_ptrs[(ctx.rank + k) % ctx.world]
             rt.check(lib.inv_oil_gemm(x2.data_ptr(), x2.stride(0), qw.idx.data_ptr(), qw.scales.data_ptr(), qw.codebook.data_ptr(), qw.bits,
-                                      peer + n_offset * 4, n_total, M, qw.N, qw.K, 0, status, st, 0), "inv_oil_gemm")
+                                      peer + n_offset * 4, n_total, M, qw.N, qw.K, 0, status, st, 2), "inv_oil_gemm")
     ctx.barrier()
     acc = buf.tensor
     if out_fp32:

@@ -96,3 +96,44 @@ def test_gpu_oil_gemm_matches_dequantised_matmul(fmt, M, N, K):
     assert float((y.float() - ref).norm() / ref.norm()) < 1e-2
     y2 = oil_linear(x, qw, residual=res)  # the accumulator was left clean
     assert torch.equal(y, y2) or float((y2.float() - ref).norm() / ref.norm()) < 1e-2
+
+
+def test_fused_finish_fallbacks_cpu():
+    from innova_b200 import ops
+    from innova_b200.ops.oil_linear import oil_linear, oil_linear_norm, oil_linear_swiglu, quantize_weight
+    torch.manual_seed(5)
+    w = torch.randn(64, 128) * 0.05
+    x = torch.randn(3, 128)
+    qw = quantize_weight(w, "oil4")
+    assert torch.allclose(oil_linear_swiglu(x, qw), ops.swiglu(oil_linear(x, qw)))
+    res = torch.randn(3, 64)
+    nw = torch.rand(64) + 0.5
+    y, h = oil_linear_norm(x, qw, res, nw, 1e-5)
+    assert torch.allclose(y, oil_linear(x, qw, res))
+    assert torch.allclose(h, ops.rms_norm(y, nw, 1e-5))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [1, 64, 200])
+def test_gpu_fused_finish_matches_unfused(M):
+    from innova_b200 import ops
+    from innova_b200.ops import runtime as rt
+    from innova_b200.ops.oil_linear import oil_linear, oil_linear_norm, oil_linear_swiglu, quantize_weight
+    torch.manual_seed(6)
+    dev = torch.device("cuda", 0)
+    K, N = 512, 768
+    x = torch.randn(M, K, device=dev).bfloat16()
+    qw = quantize_weight(torch.randn(N, K, device=dev) * 0.05, "oil4", bias=torch.randn(N, device=dev).bfloat16() * 0.1)
+    a = oil_linear_swiglu(x, qw)
+    b = ops.swiglu(oil_linear(x, qw))
+    assert float((a.float() - b.float()).abs().max()) <= 2e-2 * float(b.float().abs().max())
+    res = torch.randn(M, N, device=dev).bfloat16()
+    nw = (torch.rand(N, device=dev) + 0.5).bfloat16()
+    y, h = oil_linear_norm(x, qw, res, nw, 1e-5)
+    y_ref = oil_linear(x, qw, res)
+    h_ref = ops.rms_norm(y_ref, nw, 1e-5)
+    rt.check_status()
+    assert float((y.float() - y_ref.float()).abs().max()) <= 2e-2 * float(y_ref.float().abs().max())
+    assert float((h.float() - h_ref.float()).abs().max()) <= 3e-2 * float(h_ref.float().abs().max())
+    # the accumulator is left clean by every finish variant
+    assert torch.equal(oil_linear(x, qw, res), y_ref) or float((oil_linear(x, qw, res).float() - y_ref.float()).abs().max()) < 1e-1
