@@ -174,4 +174,107 @@ __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// ----- fused all-gather: flags, bounded tile wait, copier CTAs (shared by the one- and two-CTA kernels) -----
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded wait for a gathered tile; afterwards the async proxy (TMA) may read what the copier's ordinary stores wrote.
+__device__ __forceinline__ bool ag_wait_tile(const GemmParams& p, int tile, volatile int* abort_flag) {
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  while (ld_acquire_gpu_u32(p.ag_flags + tile) != p.ag_epoch) {
+    if ((++spins & 0xffu) == 0) {  // the global timer is slow to read: look at it only now and then
+      if (*abort_flag) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > INV_WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        if (p.status) atomicExch(p.status, ERR_WAIT_PEER);
+        return false;
+      }
+    }
+  }
+  asm volatile("fence.proxy.async;" ::: "memory");
+  return true;
+}
+// Copier CTAs: remote shards, nearest peer first, one tile (`tile_rows` rows of K elements) per step. One thread drives the
+// copy engine: bulk asynchronous copies peer memory -> shared memory -> local memory through a ring of 32 KB slots, four
+// loads in flight ahead of the stores (about 160 KB per CTA: NVLink round trips are microseconds long, so a CTA moving
+// registers' worth of data at a time would reach a few GB/s only). No cluster multicast.
+static __device__ __noinline__ void ag_copier(const GemmParams& p, int tile_rows, uint8_t* ring, uint64_t* bars, volatile int* abort_flag) {
+  constexpr int SLOTS = 6, AHEAD = 4, CH = 32768;
+  if (threadIdx.x != 0) return;
+  for (int s = 0; s < SLOTS; ++s) mbar_init(&bars[s], 1);
+  *abort_flag = 0;
+  fence_barrier_init();
+  const int per = p.ag_shard_rows / tile_rows;
+  const int remote_tiles = (p.ag_world - 1) * per;
+  const size_t row_bytes = (size_t)p.K * 2, ld_bytes = (size_t)p.ag_ld * 2;
+  const bool flat = row_bytes == ld_bytes;  // the tile is one contiguous range: copy it in 32 KB pieces, else row by row
+  const size_t tile_bytes = (size_t)tile_rows * row_bytes;
+  const int pieces_per_row = (int)((row_bytes + CH - 1) / CH);
+  const int nch = flat ? (int)((tile_bytes + CH - 1) / CH) : tile_rows * pieces_per_row;
+  uint32_t gi = 0;  // loads issued so far: slot = gi % SLOTS, use = gi / SLOTS
+  uint32_t gw = 0;  // loads waited for so far
+  for (int c = blockIdx.x; c < remote_tiles; c += p.ag_copy_ctas) {
+    const int r = (p.ag_rank + 1 + c / per) % p.ag_world;
+    const int tile = r * per + c % per;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(p.ag_src[r]) + (size_t)tile * tile_rows * ld_bytes;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(p.ag_dst) + (size_t)tile * tile_rows * ld_bytes;
+    auto piece = [&](int i, size_t& off, uint32_t& bytes) {
+      if (flat) {
+        off = (size_t)i * CH;
+        bytes = (uint32_t)(tile_bytes - off < (size_t)CH ? tile_bytes - off : (size_t)CH);
+      } else {
+        const int row = i / pieces_per_row, pc = i % pieces_per_row;
+        const size_t col = (size_t)pc * CH;
+        off = (size_t)row * ld_bytes + col;
+        bytes = (uint32_t)(row_bytes - col < (size_t)CH ? row_bytes - col : (size_t)CH);
+      }
+    };
+    bool ok = true;
+    for (int i = 0; ok && i < nch + AHEAD; ++i) {
+      if (i < nch) {
+        // the slot's previous store must have read its data: at most SLOTS - AHEAD - 1 newer stores may still be pending
+        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        size_t off;
+        uint32_t bytes;
+        piece(i, off, bytes);
+        const uint32_t slot = gi % SLOTS;
+        mbar_expect_tx(&bars[slot], bytes);
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(ring + slot * CH)),
+                     "l"(src + off), "r"(bytes), "r"(smem_u32(&bars[slot]))
+                     : "memory");
+        ++gi;
+      }
+      if (i >= AHEAD) {
+        size_t off;
+        uint32_t bytes;
+        piece(i - AHEAD, off, bytes);
+        const uint32_t slot = gw % SLOTS;
+        if (!mbar_wait(&bars[slot], (gw / SLOTS) & 1, abort_flag, p.status, ERR_WAIT_PEER)) { ok = false; break; }
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst + off), "r"(smem_u32(ring + slot * CH)), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        ++gw;
+      }
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // also on the way out after a failed wait: no store of ours stays in flight
+    if (!ok) {  // give the loads still in flight a bounded time to land before the shared memory goes away
+      const uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+      return;
+    }
+    __threadfence();
+    asm volatile("fence.proxy.async;" ::: "memory");
+    st_release_gpu_u32(p.ag_flags + tile, p.ag_epoch);
+  }
+}
+
+
 }  // namespace inv

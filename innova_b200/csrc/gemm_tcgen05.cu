@@ -91,108 +91,6 @@ __device__ __forceinline__ WorkUnit decode_work(int w, const GemmParams& p, int 
   return u;
 }
 
-__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_gpu_u32(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-// Bounded wait for a gathered tile; afterwards the async proxy (TMA) may read what the copier's ordinary stores wrote.
-__device__ __forceinline__ bool ag_wait_tile(const GemmParams& p, int tile, volatile int* abort_flag) {
-  uint64_t t0 = 0;
-  uint32_t spins = 0;
-  while (ld_acquire_gpu_u32(p.ag_flags + tile) != p.ag_epoch) {
-    if ((++spins & 0xffu) == 0) {  // the global timer is slow to read: look at it only now and then
-      if (*abort_flag) return false;
-      const uint64_t now = globaltimer_ns();
-      if (t0 == 0) {
-        t0 = now;
-      } else if (now - t0 > INV_WAIT_LIMIT_NS) {
-        *abort_flag = 1;
-        if (p.status) atomicExch(p.status, ERR_WAIT_PEER);
-        return false;
-      }
-    }
-  }
-  asm volatile("fence.proxy.async;" ::: "memory");
-  return true;
-}
-// Copier CTAs: remote shards, nearest peer first, one tile (BM or BN rows of K elements) per step. One thread drives the
-// copy engine: bulk asynchronous copies peer memory -> shared memory -> local memory through a ring of 32 KB slots, four
-// loads in flight ahead of the stores (about 160 KB per CTA: NVLink round trips are microseconds long, so a CTA moving
-// registers' worth of data at a time would reach a few GB/s only). No cluster multicast.
-__device__ void ag_copier(const GemmParams& p, uint8_t* ring, uint64_t* bars, volatile int* abort_flag) {
-  constexpr int SLOTS = 6, AHEAD = 4, CH = 32768;
-  if (threadIdx.x != 0) return;
-  for (int s = 0; s < SLOTS; ++s) mbar_init(&bars[s], 1);
-  *abort_flag = 0;
-  fence_barrier_init();
-  const int tile_rows = p.ag_operand == 1 ? BN : BM;
-  const int per = p.ag_shard_rows / tile_rows;
-  const int remote_tiles = (p.ag_world - 1) * per;
-  const size_t row_bytes = (size_t)p.K * 2, ld_bytes = (size_t)p.ag_ld * 2;
-  const bool flat = row_bytes == ld_bytes;  // the tile is one contiguous range: copy it in 32 KB pieces, else row by row
-  const size_t tile_bytes = (size_t)tile_rows * row_bytes;
-  const int pieces_per_row = (int)((row_bytes + CH - 1) / CH);
-  const int nch = flat ? (int)((tile_bytes + CH - 1) / CH) : tile_rows * pieces_per_row;
-  uint32_t gi = 0;  // loads issued so far: slot = gi % SLOTS, use = gi / SLOTS
-  uint32_t gw = 0;  // loads waited for so far
-  for (int c = blockIdx.x; c < remote_tiles; c += p.ag_copy_ctas) {
-    const int r = (p.ag_rank + 1 + c / per) % p.ag_world;
-    const int tile = r * per + c % per;
-    const uint8_t* src = reinterpret_cast<const uint8_t*>(p.ag_src[r]) + (size_t)tile * tile_rows * ld_bytes;
-    uint8_t* dst = reinterpret_cast<uint8_t*>(p.ag_dst) + (size_t)tile * tile_rows * ld_bytes;
-    auto piece = [&](int i, size_t& off, uint32_t& bytes) {
-      if (flat) {
-        off = (size_t)i * CH;
-        bytes = (uint32_t)(tile_bytes - off < (size_t)CH ? tile_bytes - off : (size_t)CH);
-      } else {
-        const int row = i / pieces_per_row, pc = i % pieces_per_row;
-        const size_t col = (size_t)pc * CH;
-        off = (size_t)row * ld_bytes + col;
-        bytes = (uint32_t)(row_bytes - col < (size_t)CH ? row_bytes - col : (size_t)CH);
-      }
-    };
-    bool ok = true;
-    for (int i = 0; ok && i < nch + AHEAD; ++i) {
-      if (i < nch) {
-        // the slot's previous store must have read its data: at most SLOTS - AHEAD - 1 newer stores may still be pending
-        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-        size_t off;
-        uint32_t bytes;
-        piece(i, off, bytes);
-        const uint32_t slot = gi % SLOTS;
-        mbar_expect_tx(&bars[slot], bytes);
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(ring + slot * CH)),
-                     "l"(src + off), "r"(bytes), "r"(smem_u32(&bars[slot]))
-                     : "memory");
-        ++gi;
-      }
-      if (i >= AHEAD) {
-        size_t off;
-        uint32_t bytes;
-        piece(i - AHEAD, off, bytes);
-        const uint32_t slot = gw % SLOTS;
-        if (!mbar_wait(&bars[slot], (gw / SLOTS) & 1, abort_flag, p.status, ERR_WAIT_PEER)) { ok = false; break; }
-        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst + off), "r"(smem_u32(ring + slot * CH)), "r"(bytes) : "memory");
-        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        ++gw;
-      }
-    }
-    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // also on the way out after a failed wait: no store of ours stays in flight
-    if (!ok) {  // give the loads still in flight a bounded time to land before the shared memory goes away
-      const uint64_t t0 = globaltimer_ns();
-      while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
-      return;
-    }
-    __threadfence();
-    asm volatile("fence.proxy.async;" ::: "memory");
-    st_release_gpu_u32(p.ag_flags + tile, p.ag_epoch);
-  }
-}
-
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
@@ -212,7 +110,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   // with a fused all-gather the first CTAs of the grid only copy; they own no barriers and no TMEM
   const int n_copy = p.ag_world > 1 ? p.ag_copy_ctas : 0;
   if ((int)blockIdx.x < n_copy) {
-    ag_copier(p, smem, full_bar, abort_flag);
+    ag_copier(p, p.ag_operand == 1 ? BN : BM, smem, full_bar, abort_flag);
     return;
   }
   const int bid = blockIdx.x - n_copy, gdim = gridDim.x - n_copy;
@@ -560,10 +458,15 @@ extern "C" int inv_gemm_ag_bf16(const uint64_t* peer_bufs, int W, int rank, int 
   p.ag_dst = local; p.ag_flags = flags; p.ag_epoch = epoch;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
   const long total = (long)m_tiles * n_tiles;
+  // a copier CTA keeps ~130 KB in flight, i.e. ~40 GB/s over a microseconds-long round trip: enough CTAs to fill the links
   if (W == 1) copy_ctas = 0;
-  else if (copy_ctas < 1) copy_ctas = 8;
+  else if (copy_ctas < 1) copy_ctas = W >= 8 ? 20 : (W >= 4 ? 12 : 8);
   if (copy_ctas > g_num_sms / 4) copy_ctas = g_num_sms / 4;
   p.ag_copy_ctas = copy_ctas;
+  // 256x256 tiles on CTA pairs when the shards are whole 256-row tiles (the faster kernel)
+  if (shard_rows % 256 == 0 && M >= 512 && N >= 256 && K % 64 == 0)
+    return gemm_2cta_dispatch(A, B, p, operand ? ld_other : ld_gathered, operand ? ld_gathered : ld_other, 0, 0, g_num_sms,
+                              reinterpret_cast<cudaStream_t>(stream));
   long gemm_ctas = total < g_num_sms - copy_ctas ? total : g_num_sms - copy_ctas;
   // the whole grid must be resident at once (the GEMM CTAs wait for the copier CTAs): one CTA per SM
   return launch_gemm<false, false>(ta, tb, p, (int)gemm_ctas + copy_ctas, reinterpret_cast<cudaStream_t>(stream));
@@ -645,4 +548,65 @@ extern "C" int inv_gemm_grouped(const void* A, const void* B, void* C, int M, in
   if (!a_mn && b_mn) return launch_gemm<false, true>(ta, tb, p, grid, st);
   if (a_mn && !b_mn) return launch_gemm<true, false>(ta, tb, p, grid, st);
   return launch_gemm<false, false>(ta, tb, p, grid, st);
+}
+
+// GEMM fused with a reduce-scatter, push form: every rank computes the full [M, N] partial product of its K-slice in
+// bf16 and its epilogue stores the tile rows owned by rank r straight into this rank's slot of r's receive buffer
+// (peer_slots[r], [M / W, ldc] bf16, plain 16-byte stores: posted writes over NVLink, no atomics), visiting the
+// owners starting after the local rank so that the local rows, which cross no link, come last. The owner then adds
+// its W slots (inv_sum_slots_bf16) once every rank has passed a barrier. The transfer overlaps the math tile by tile;
+// the bytes on the links are the bf16 partial sums, as in a library reduce-scatter.
+extern "C" int inv_gemm_rs_push_bf16(const void* A, int lda, const void* B, int ldb, const uint64_t* peer_slots, int W, int rank, int ldc, int M,
+                                     int N, int K, int* status, void* stream) {
+  if (W < 1 || W > 8 || rank < 0 || rank >= W || M % W || (M / W) % BM) return -ERR_BAD_ARG;
+  if ((lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8)) return -ERR_BAD_ARG;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  GemmParams p;
+  fill_plain(p, M, N, K, reinterpret_cast<void*>(peer_slots[rank]), ldc, 0, nullptr, nullptr, 0, nullptr, EPI_NONE, 1.0f, status);
+  CUtensorMap ta, tb;
+  int rc;
+  if ((rc = make_tmap_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM))) return rc;
+  if ((rc = make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, BN))) return rc;
+  p.rs_world = W; p.rs_rank = rank; p.rs_shard_rows = M / W;
+  for (int r = 0; r < W; ++r) p.rs_dst[r] = reinterpret_cast<float*>(peer_slots[r]);  // typed by c_f32 in the epilogue
+  if ((M / W) % 256 == 0 && N >= 256 && K % 64 == 0)
+    return gemm_2cta_dispatch(A, B, p, lda, ldb, 0, 0, g_num_sms, reinterpret_cast<cudaStream_t>(stream));
+  const long total = (long)((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  return launch_gemm<false, false>(ta, tb, p, (int)(total < g_num_sms ? total : g_num_sms), reinterpret_cast<cudaStream_t>(stream));
+}
+
+namespace inv {
+// out[i] = bf16(sum_w slots[w * stride + i]), eight elements per thread.
+__global__ void sum_slots_bf16_kernel(const __nv_bfloat16* __restrict__ slots, long stride, int W, __nv_bfloat16* __restrict__ out, long n8) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int w = 0; w < W; ++w) {
+      const uint4 v = *reinterpret_cast<const uint4*>(slots + w * stride + i * 8);
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += __uint_as_float(u[j] << 16);
+        acc[2 * j + 1] += __uint_as_float(u[j] & 0xffff0000u);
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]); o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + i * 8) = o;
+  }
+}
+}  // namespace inv
+
+extern "C" int inv_sum_slots_bf16(const void* slots, long stride_elems, int W, void* out, long n, void* stream) {
+  if (n % 8 || stride_elems % 8) return -ERR_BAD_ARG;
+  const long n8 = n / 8;
+  long grid = (n8 + 255) / 256;
+  if (grid > 148 * 8) grid = 148 * 8;
+  inv::sum_slots_bf16_kernel<<<(int)grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)slots, stride_elems, W, (__nv_bfloat16*)out, n8);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
 }

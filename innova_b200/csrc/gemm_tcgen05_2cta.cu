@@ -79,15 +79,40 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
+// Output maps of the reduce-scatter form: one per owner rank, over this rank's slot in that owner's receive buffer.
+struct RsMaps {
+  CUtensorMap m[8];
+};
+
 struct WorkUnit2 {
   int m0, n0, kb_begin, kb_end;
+  int ag_tile;  // 256-row tile of the gathered operand this unit reads, -1 when it is local or nothing is gathered
 };
-__device__ __forceinline__ WorkUnit2 decode_work2(int w, int m_tiles, int n_tiles, int kb_total, int kb_per_split) {
+__device__ __forceinline__ WorkUnit2 decode_work2(int w, const GemmParams& p, int m_tiles, int n_tiles, int kb_total, int kb_per_split) {
   WorkUnit2 u;
-  const int n_blk = w % n_tiles;
-  const int rest = w / n_tiles;
-  const int m_blk = rest % m_tiles;
-  const int ks = rest / m_tiles;
+  u.ag_tile = -1;
+  int n_blk, m_blk, ks;
+  if (p.ag_world > 1 && p.ag_operand == 1) {  // B is gathered: all m-tiles of an n-tile before the next n-tile, local shard first
+    m_blk = w % m_tiles;
+    const int rest = w / m_tiles;
+    n_blk = rest % n_tiles;
+    ks = rest / n_tiles;
+    const int per = p.ag_shard_rows / g2::BN;
+    n_blk = (n_blk + p.ag_rank * per) % n_tiles;
+    if (n_blk / per != p.ag_rank) u.ag_tile = n_blk;
+  } else {
+    n_blk = w % n_tiles;
+    const int rest = w / n_tiles;
+    m_blk = rest % m_tiles;
+    ks = rest / m_tiles;
+    if (p.ag_world > 1) {  // A is gathered: local rows first, then the peers' in the order the copiers fetch them
+      const int per = p.ag_shard_rows / g2::BM;
+      m_blk = (m_blk + p.ag_rank * per) % m_tiles;
+      if (m_blk / per != p.ag_rank) u.ag_tile = m_blk;
+    } else if (p.rs_world > 1) {  // reduce-scatter: the next rank's rows first, the local rows last
+      m_blk = (m_blk + (p.rs_rank + 1) * (p.rs_shard_rows / g2::BM)) % m_tiles;
+    }
+  }
   u.m0 = m_blk * g2::BM;
   u.n0 = n_blk * g2::BN;
   u.kb_begin = ks * kb_per_split;
@@ -98,7 +123,8 @@ __device__ __forceinline__ WorkUnit2 decode_work2(int w, int m_tiles, int n_tile
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(g2::THREADS, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                      const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_aux, const GemmParams p) {
+                      const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_aux, const __grid_constant__ RsMaps rs_maps,
+                      const GemmParams p) {
   using namespace g2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -115,7 +141,13 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta = cluster_ctarank();
   const bool leader = cta == 0;
-  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  // with a fused all-gather the first clusters of the grid only copy; they own no barriers and no tensor memory
+  const int n_copy = p.ag_world > 1 ? p.ag_copy_ctas : 0;
+  if ((int)blockIdx.x < n_copy) {
+    ag_copier(p, 256, smem, full_bar, abort_flag);
+    return;
+  }
+  const int pair = ((int)blockIdx.x - n_copy) >> 1, npairs = ((int)gridDim.x - n_copy) >> 1;
 
   const int m_tiles = (p.M + BM - 1) / BM;
   const int n_tiles = (p.N + BN - 1) / BN;
@@ -155,9 +187,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       int it = 0;
       bool ok = true;
       for (int w = pair; ok && w < total_work; w += npairs) {
-        const WorkUnit2 u = decode_work2(w, m_tiles, n_tiles, kb_total, kb_per_split);
+        const WorkUnit2 u = decode_work2(w, p, m_tiles, n_tiles, kb_total, kb_per_split);
         const int my_m0 = u.m0 + (int)cta * 128;
         const int my_n0 = u.n0 + (int)cta * 128;
+        if (u.ag_tile >= 0 && !ag_wait_tile(p, u.ag_tile, abort_flag)) break;
         for (int kb = u.kb_begin; kb < u.kb_end; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -201,7 +234,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       uint32_t ph = 0;
       bool ok = true;
       for (int w = pair; ok && w < total_work; w += npairs, ++tile_i) {
-        const WorkUnit2 u = decode_work2(w, m_tiles, n_tiles, kb_total, kb_per_split);
+        const WorkUnit2 u = decode_work2(w, p, m_tiles, n_tiles, kb_total, kb_per_split);
         const int acc = tile_i & 1;
         const uint32_t acc_ph = (tile_i >> 1) & 1;
         if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1, abort_flag, p.status, ERR_WAIT_TMEM_EMPTY)) break;
@@ -235,15 +268,25 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     uint8_t* my_stage = sStage + (warp - 2) * 8192;
     int tile_i = 0;
     for (int w = pair; w < total_work; w += npairs, ++tile_i) {
-      const WorkUnit2 u = decode_work2(w, m_tiles, n_tiles, kb_total, kb_per_split);
+      const WorkUnit2 u = decode_work2(w, p, m_tiles, n_tiles, kb_total, kb_per_split);
       const int acc = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
       if (!mbar_wait_warp(&tmem_full[acc], acc_ph, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
-      const int row = u.m0 + (int)cta * 128 + q * 32 + lane;
+      int row = u.m0 + (int)cta * 128 + q * 32 + lane;
       const bool row_ok = row < p.M;
+      GemmParams pe = p;
+      const CUtensorMap* c_map = &tmap_c;
+      int row_shift = 0;
+      if (p.rs_world > 1) {  // this tile's rows belong to one owner: store into its buffer (TMA stores reach peer memory) at the shard-relative row
+        const int owner = u.m0 / p.rs_shard_rows;
+        pe.C = p.rs_dst[owner];
+        c_map = &rs_maps.m[owner];
+        row_shift = owner * p.rs_shard_rows;
+        row -= row_shift;
+      }
       const uint32_t t_row = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
-      const int row0 = u.m0 + (int)cta * 128 + q * 32;
+      const int row0_abs = u.m0 + (int)cta * 128 + q * 32;
 #pragma unroll 1
       for (int c = half * 4; c < half * 4 + 4; c += 2) {
         const int col0 = u.n0 + c * 32;
@@ -264,13 +307,13 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&tmap_c, my_stage, col0, row0);
-            if (staged_aux) tma_store_2d(&tmap_aux, my_stage + 4096, col0, row0);
+            tma_store_2d(c_map, my_stage, col0, row0_abs - row_shift);
+            if (staged_aux) tma_store_2d(&tmap_aux, my_stage + 4096, col0, row0_abs);
             tma_store_commit();
           }
         } else {
-          gemm_epilogue_chunk(p, row, row_ok, col0, r0);
-          if (col0 + 32 < p.N) gemm_epilogue_chunk(p, row, row_ok, col0 + 32, r1);
+          gemm_epilogue_chunk(pe, row, row_ok, col0, r0);
+          if (col0 + 32 < p.N) gemm_epilogue_chunk(pe, row, row_ok, col0 + 32, r1);
         }
       }
       tc_fence_before();
@@ -296,7 +339,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 }
 
 template <bool A_MN, bool B_MN>
-static int launch_gemm_2cta(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tx,
+static int launch_gemm_2cta(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tx, const RsMaps& rs,
                             const GemmParams& p, int grid, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
@@ -304,7 +347,7 @@ static int launch_gemm_2cta(const CUtensorMap& ta, const CUtensorMap& tb, const 
     if (e != cudaSuccess) return -(int)e;
     configured = true;
   }
-  gemm_bf16_2cta_kernel<A_MN, B_MN><<<grid, g2::THREADS, g2::SMEM_BYTES, stream>>>(ta, tb, tc, tx, p);
+  gemm_bf16_2cta_kernel<A_MN, B_MN><<<grid, g2::THREADS, g2::SMEM_BYTES, stream>>>(ta, tb, tc, tx, rs, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }
@@ -341,13 +384,21 @@ int gemm_2cta_dispatch(const void* A, const void* B, const GemmParams& p0, int l
   }
   p.split_k = split_k;
   const long total = (long)((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * split_k;
-  const int max_pairs = num_sms / 2;
+  const int n_copy = p.ag_world > 1 ? (p.ag_copy_ctas & ~1) : 0;  // whole clusters; the whole grid must be resident at once
+  p.ag_copy_ctas = n_copy;
+  const int max_pairs = (num_sms - n_copy) / 2;
   const int pairs = (int)(total < max_pairs ? total : max_pairs);
-  const int grid = pairs * 2;
-  if (a_mn && b_mn) return launch_gemm_2cta<true, true>(ta, tb, tc, tx, p, grid, stream);
-  if (a_mn && !b_mn) return launch_gemm_2cta<true, false>(ta, tb, tc, tx, p, grid, stream);
-  if (!a_mn && b_mn) return launch_gemm_2cta<false, true>(ta, tb, tc, tx, p, grid, stream);
-  return launch_gemm_2cta<false, false>(ta, tb, tc, tx, p, grid, stream);
+  const int grid = pairs * 2 + n_copy;
+  RsMaps rs;
+  for (int r = 0; r < 8; ++r) rs.m[r] = tc;
+  if (p.rs_world > 1 && !p.c_f32) {
+    for (int r = 0; r < p.rs_world; ++r)
+      if ((rc = make_tmap_2d_bf16(&rs.m[r], p.rs_dst[r], (uint64_t)p.N, (uint64_t)p.rs_shard_rows, (uint64_t)p.ldc, 64, 32))) return rc;
+  }
+  if (a_mn && b_mn) return launch_gemm_2cta<true, true>(ta, tb, tc, tx, rs, p, grid, stream);
+  if (a_mn && !b_mn) return launch_gemm_2cta<true, false>(ta, tb, tc, tx, rs, p, grid, stream);
+  if (!a_mn && b_mn) return launch_gemm_2cta<false, true>(ta, tb, tc, tx, rs, p, grid, stream);
+  return launch_gemm_2cta<false, false>(ta, tb, tc, tx, rs, p, grid, stream);
 }
 
 }  // namespace inv

@@ -57,6 +57,8 @@ struct OilGemmParams {
   int idx_stages;  // depth of the raw index ring: whatever shared memory is left, at most MAX_IDX_STAGES
   int dp_rounds;   // whole tiles per CTA before the stream-K tail (tile = round * gridDim.x + blockIdx.x)
   int* status;
+  float* peers[8];  // mode 2: the same partial sums are added into each of these buffers (every rank's copy of the accumulator)
+  int n_peers;
   int multimem;  // 1: out is an NVLS multicast address, every partial sum is added into all ranks' copies; 2: out may hold
                  // other ranks' partial sums (a peer's buffer): always add, never store
 };
@@ -435,8 +437,11 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
                 if (vec_ok && n + 3 < p.N) {
                   if (p.multimem == 1)
                     asm volatile("multimem.red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(val.x), "f"(val.y), "f"(val.z), "f"(val.w) : "memory");
-                  else if (p.multimem == 2)
-                    asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(val.x), "f"(val.y), "f"(val.z), "f"(val.w) : "memory");
+                  else if (p.multimem == 2) {
+                    const size_t off = (size_t)gm * p.ldo + n;
+                    for (int k = 0; k < p.n_peers; ++k)
+                      asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p.peers[k] + off), "f"(val.x), "f"(val.y), "f"(val.z), "f"(val.w) : "memory");
+                  }
                   else if (full)
                     *reinterpret_cast<float4*>(o) = val;
                   else
@@ -447,7 +452,9 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
                   for (int z = 0; z < 4; ++z)
                     if (n + z < p.N) {
                       if (p.multimem == 1) asm volatile("multimem.red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(o + z), "f"(vv[z]) : "memory");
-                      else atomicAdd(o + z, vv[z]);
+                      else if (p.multimem == 2) {
+                        for (int k = 0; k < p.n_peers; ++k) atomicAdd(p.peers[k] + (size_t)gm * p.ldo + n + z, vv[z]);
+                      } else atomicAdd(o + z, vv[z]);
                     }
                 }
               }
@@ -593,7 +600,8 @@ __global__ void __launch_bounds__(256) oil_gemm_finish_norm_kernel(float* __rest
 using namespace inv;
 
 static int oil_gemm_launch(const void* x, int ldx, const void* idx, const void* scales, const float* codebook, int bits, float* acc, int ldo,
-                           int M, int N, int K, int* status, cudaStream_t st, int multimem) {
+                           int M, int N, int K, int* status, cudaStream_t st, int multimem, const uint64_t* peers = nullptr, int n_peers = 0,
+                           size_t peer_off = 0) {
   using namespace og;
   static int num_sms = 0;
   if (num_sms == 0) {
@@ -608,6 +616,12 @@ static int oil_gemm_launch(const void* x, int ldx, const void* idx, const void* 
   p.scales = (const __nv_bfloat16*)scales;
   p.codebook = codebook;
   p.out = acc; p.ldo = ldo; p.status = status; p.multimem = multimem;
+  p.n_peers = 0;
+  for (int k = 0; k < 8; ++k) p.peers[k] = nullptr;
+  if (multimem == 2) {
+    if (peers == nullptr) { p.peers[0] = acc; p.n_peers = 1; }
+    else { p.n_peers = n_peers; for (int k = 0; k < n_peers; ++k) p.peers[k] = reinterpret_cast<float*>(peers[k]) + peer_off; }
+  }
   const int kbb = bits == 8 ? 2 : 4;
   const int n_tiles = (N + BN - 1) / BN, kb_total = K / BK, nb = (kb_total + kbb - 1) / kbb;
   CUtensorMap ti, tx;
@@ -652,6 +666,21 @@ extern "C" int inv_oil_gemm(const void* x, int ldx, const void* idx, const void*
     const int m = M - m0 < og::MAXM ? M - m0 : og::MAXM;
     const int rc = oil_gemm_launch((const __nv_bfloat16*)x + (size_t)m0 * ldx, ldx, idx, scales, codebook, bits, acc + (size_t)m0 * ldo, ldo, m, N, K,
                                    status, (cudaStream_t)stream, multimem);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+// The same GEMM with the partial sums added into n_peers buffers (each rank's copy of a replicated accumulator, given
+// as addresses that already include the column offset): one launch, the weights are read once.
+extern "C" int inv_oil_gemm_peers(const void* x, int ldx, const void* idx, const void* scales, const float* codebook, int bits,
+                                  const uint64_t* peers, int n_peers, int ldo, int M, int N, int K, int* status, void* stream) {
+  if ((bits != 2 && bits != 4 && bits != 8) || M < 1 || M > 256 || (K % 64) || (ldx % 8) || N < 1 || n_peers < 1 || n_peers > 8) return -ERR_BAD_ARG;
+  for (int m0 = 0; m0 < M; m0 += og::MAXM) {
+    const int m = M - m0 < og::MAXM ? M - m0 : og::MAXM;
+    const int rc = oil_gemm_launch((const __nv_bfloat16*)x + (size_t)m0 * ldx, ldx, idx, scales, codebook, bits,
+                                   reinterpret_cast<float*>(peers[0]) + (size_t)m0 * ldo, ldo, m, N, K, status, (cudaStream_t)stream, 2, peers, n_peers,
+                                   (size_t)m0 * ldo);
     if (rc) return rc;
   }
   return 0;

@@ -435,7 +435,7 @@ __device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *reinterpret_c
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
 
 template <int D>
-__global__ void __launch_bounds__(128) paged_decode_oil4_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q, const int* __restrict__ page_table,
+__global__ void __launch_bounds__(128, 4) paged_decode_oil4_mma_kernel(const __nv_bfloat16* __restrict__ q, int ld_q, const int* __restrict__ page_table,
                                                                     int max_pages, const int* __restrict__ seq_lens, int H, int Hkv,
                                                                     const uint8_t* __restrict__ k_pool, const uint8_t* __restrict__ v_pool,
                                                                     const __half* __restrict__ k_scale, const __half* __restrict__ v_scale,

@@ -29,6 +29,8 @@ vp, i32, i64, f32 = _native.vp, _native.i32, _native.i64, _native.f32
 _native.register_cuda_sigs({
     "inv_gemm_ag_bf16": [vp, i32, i32, i32, i32, i32, vp, i32, vp, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, vp, C.c_uint32, i32, vp, vp],
     "inv_gemm_rs_bf16": [vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp],
+    "inv_gemm_rs_push_bf16": [vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, i32, vp, vp],
+    "inv_sum_slots_bf16": [vp, i64, i32, vp, i64, vp],
 })
 
 
@@ -39,7 +41,7 @@ def _ws(group):
 class FusedGemmComm:
     """Buffers are sized on first use per (rows, cols) and reused; one instance per process group."""
 
-    def __init__(self, group=None, device=None, copy_ctas: int = 8):
+    def __init__(self, group=None, device=None, copy_ctas: int = 0):
         self.group = group
         self.world, self.rank = _ws(group)
         self.device = torch.device(device) if device is not None else (
@@ -48,6 +50,7 @@ class FusedGemmComm:
         self.copy_ctas = copy_ctas
         self._gather = {}   # (rows_total, cols) -> SymmBuffer bf16
         self._rs = {}       # (shard_rows, cols) -> SymmBuffer fp32
+        self._recv = {}     # (shard_rows, cols) -> [two SymmBuffers of W bf16 slots, next index]
         self._flags = None
         self._sync = None
         self._epoch = 0
@@ -141,6 +144,26 @@ class FusedGemmComm:
                 dist.all_reduce(y, group=self.group)
             return y[r * S:(r + 1) * S].to(out_dtype)
         from ..ops import runtime as rt
+        from .symm import SymmBuffer, ptr_array
+        if out_dtype == torch.bfloat16 and N % 8 == 0:
+            # push form: the epilogue stores every tile into this rank's slot at the tile's owner; two receive buffers
+            # alternate, so one barrier per call is enough (a rank reaches the call after next only through the next
+            # call's barrier, which the slowest reader of this call's slots has to join first)
+            key = (S, N)
+            if key not in self._recv:
+                self._recv[key] = [[SymmBuffer(W * S * N, torch.bfloat16, self.group, self.device) for _ in range(2)], 0]
+            bufs, turn = self._recv[key]
+            self._recv[key][1] = turn ^ 1
+            buf = bufs[turn]
+            x, w = x.contiguous(), w.contiguous()
+            slots = ptr_array([p + r * S * N * 2 for p in buf.peer_ptrs])
+            rc = rt.lib().inv_gemm_rs_push_bf16(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), slots, W, r, N, M, N, x.shape[1],
+                                                rt.status_tensor(self.device).data_ptr(), rt.stream_ptr())
+            rt.check(rc, "inv_gemm_rs_push_bf16")
+            self._barrier()                  # every rank's partial rows have landed in this rank's slots
+            out = torch.empty((S, N), dtype=torch.bfloat16, device=self.device)
+            rt.check(rt.lib().inv_sum_slots_bf16(buf.tensor.data_ptr(), S * N, W, out.data_ptr(), S * N, rt.stream_ptr()), "inv_sum_slots_bf16")
+            return out
         buf = self._rs_buf(S, N)
         acc = buf.tensor.view(S, N)
         self._barrier()                      # nobody still reads the previous result

@@ -81,10 +81,11 @@ def tp_reduce_linear(x: torch.Tensor, qw: QuantWeight, ctx: Optional[TPContext],
         rt.check(lib.inv_oil_gemm(x2.data_ptr(), x2.stride(0), qw.idx.data_ptr(), qw.scales.data_ptr(), qw.codebook.data_ptr(), qw.bits,
                                   buf.multicast_ptr + n_offset * 4, n_total, M, qw.N, qw.K, 0, status, st, 1), "inv_oil_gemm")
     else:
-        for k in range(ctx.world):
-            peer = buf.peer_ptrs[(ctx.rank + k) % ctx.world]
-            rt.check(lib.inv_oil_gemm(x2.data_ptr(), x2.stride(0), qw.idx.data_ptr(), qw.scales.data_ptr(), qw.codebook.data_ptr(), qw.bits,
-                                      peer + n_offset * 4, n_total, M, qw.N, qw.K, 0, status, st, 2), "inv_oil_gemm")
+        # no multicast object on this machine: one launch whose epilogue adds every tile into each rank's copy
+        from .symm import ptr_array
+        peers = ptr_array([buf.peer_ptrs[(ctx.rank + k) % ctx.world] + n_offset * 4 for k in range(ctx.world)])
+        rt.check(lib.inv_oil_gemm_peers(x2.data_ptr(), x2.stride(0), qw.idx.data_ptr(), qw.scales.data_ptr(), qw.codebook.data_ptr(), qw.bits,
+                                        peers, ctx.world, n_total, M, qw.N, qw.K, status, st), "inv_oil_gemm_peers")
     ctx.barrier()
     acc = buf.tensor
     if out_fp32:

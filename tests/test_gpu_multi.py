@@ -208,6 +208,14 @@ def _fused_worker(rank, world, port, out):
         y4 = comm.gemm_reduce_scatter(xr, wr)
     Sr = x_all.shape[0] // world
     res["rs"] = float((y4.float().cpu() - ref[rank * Sr:(rank + 1) * Sr]).abs().max() / ref.abs().max())
+    # shards that are not whole 256-row tiles take the one-CTA kernel
+    S2 = 384
+    x2_all = (torch.randn(world * S2, K, generator=g) * 0.5).bfloat16()
+    ref_s = x2_all.float() @ w.float().t()
+    y5 = comm.all_gather_gemm(x2_all[rank * S2:(rank + 1) * S2].to(dev), w.to(dev))
+    res["ag_small"] = float((y5.float().cpu() - ref_s).abs().max() / ref_s.abs().max())
+    y6 = comm.gemm_reduce_scatter(x2_all[:, rank * Kl:(rank + 1) * Kl].contiguous().to(dev), wr)
+    res["rs_small"] = float((y6.float().cpu() - ref_s[rank * S2:(rank + 1) * S2]).abs().max() / ref_s.abs().max())
     rt.check_status()
     torch.save(res, out + f".{rank}")
     dist.barrier()
@@ -221,7 +229,7 @@ def test_fused_gemm_collectives(tmp_path):
     mp.spawn(_fused_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     for rank in range(world):
         r = torch.load(out + f".{rank}")
-        for k in ("ag", "ag_gelu", "agw", "rs"):
+        for k in ("ag", "ag_gelu", "agw", "rs", "ag_small", "rs_small"):
             assert r[k] < 1.5e-2, (rank, k, r[k])
 
 
