@@ -4,7 +4,7 @@
 
 Cases (one JSON line each, printed by rank 0; every time is device-timed with CUDA events and the maximum over ranks):
   ag_gemm    all-gather of the sequence-sharded activations fused into the GEMM      vs NCCL all_gather + the same GEMM
-  gemm_rs    GEMM whose epilogue reduce-scatters into the owner's buffer            vs GEMM + NCCL reduce_scatter
+  gemm_rs    GEMM whose epilogue pushes every tile to its owner, owner adds W slots  vs GEMM + NCCL reduce_scatter
   tp_decode  row-parallel OIL4 linear, partial sums reduced in the switch             vs the same GEMM + NCCL all_reduce
   fsdp_step  gradient reduce-scatter + clip + AdamW + parameter all-gather, 2 kernels vs NCCL reduce_scatter + AdamW + all_gather
 Roofline of a fused kernel = the slower of FLOPs / measured GEMM peak and bytes that must cross NVLink / 770 GB/s per
@@ -110,7 +110,7 @@ def main():
             fused = lambda: fc.gemm_reduce_scatter(xr, wr)
             fu, bu = timed(fused, a.iters), timed(base, a.iters)
             flops = 2.0 * T * E * F
-            link_bytes = (world - 1) * S * E * 4          # fp32 partial sums this GPU sends to the owners
+            link_bytes = (world - 1) * S * E * 2          # bf16 partial tiles this GPU pushes to the owners
             roof = max(flops / (tf * 1e12), link_bytes / (LINK_GBS * 1e9)) * 1e6
             report("gemm_rs", fu, bu, roof, {"M": T, "N": E, "K": F, "gemm_only_us": round(flops / (tf * 1e12) * 1e6, 1)})
 
