@@ -1,0 +1,127 @@
+import torch
+
+from innova_b200.training.continual import (CompressedReplayBuffer, ContinualConfig, ContinualTrainer, DeltaAdapterConfig, DeltaAdapterHost,
+                                             ECCState, ForgettingBenchmark, MTPHeadConfig, MTPHeadTrainer, forgetting_bound)
+
+
+class _TinyLM(torch.nn.Module):
+    def __init__(self, vocab=32, d=24):
+        super().__init__()
+        torch.manual_seed(0)
+        self.emb = torch.nn.Embedding(vocab, d)
+        self.mix = torch.nn.Linear(d, d)
+        self.head = torch.nn.Linear(d, vocab)
+
+    def forward(self, ids):
+        h = self.emb(ids)
+        h = h + torch.tanh(self.mix(torch.cumsum(h, dim=1) / (1 + torch.arange(ids.shape[1]).view(1, -1, 1))))
+        return self.head(h)
+
+
+def _task(seed, vocab=32, n=16, s=12):
+    g = torch.Generator().manual_seed(seed)
+    start = torch.randint(0, vocab, (n, 1), generator=g)
+    step = 1 + seed % 5
+    ids = (start + step * torch.arange(s + 1).view(1, -1)) % vocab
+    return ids[:, :-1], ids[:, 1:]
+
+
+def test_replay_buffer_compresses_and_samples_by_importance():
+    buf = CompressedReplayBuffer(capacity=8)
+    torch.manual_seed(1)
+    for i in range(12):
+        buf.insert(torch.randn(64), torch.randn(64), task_id=i % 2, fisher_importance=100.0 if i == 3 else 1.0)
+    assert len(buf) == 8 and buf.compression_ratio() > 3.0
+    x = torch.randn(64)
+    b2 = CompressedReplayBuffer(4)
+    b2.insert(x, torch.arange(5), 0)
+    ins, tgs, w = b2.sample_batch(1)
+    assert (ins[0] - x).norm() / x.norm() < 0.2 and torch.equal(tgs[0], torch.arange(5))
+    b2.update_importance(0.5)
+    assert abs(b2.entries[0].fisher - 0.5) < 1e-6
+
+
+def test_ecc_and_forgetting_metrics():
+    p = torch.nn.Parameter(torch.ones(4))
+    ecc = ECCState([p])
+    p.grad = torch.tensor([1.0, 0.0, 2.0, 0.0])
+    ecc.update_fisher(alpha=1.0)
+    ecc.update_anchor()
+    with torch.no_grad():
+        p.add_(torch.tensor([1.0, 1.0, 1.0, 1.0]))
+    assert abs(float(ecc.regularize(2.0)) - (1.0 + 4.0)) < 1e-5
+    fb = ForgettingBenchmark()
+    a, b = fb.register_task(None, None), fb.register_task(None, None)
+    fb.record_zero_shot(b, 3.0)
+    fb.record_baseline(a, 1.0), fb.record_baseline(b, 1.5)
+    fb.record_current(a, 1.6), fb.record_current(b, 1.5)
+    m = fb.compute()
+    assert abs(m.avg_forgetting - 0.3) < 1e-6 and abs(m.max_forgetting - 0.6) < 1e-6
+    assert abs(m.backward_transfer + 0.6) < 1e-6 and abs(m.forward_transfer - 1.5) < 1e-6
+    assert forgetting_bound(1.0, 10, [0.5, 0.5], 0.1, 4.0) > forgetting_bound(1.0, 10, [0.5] * 2 + [0.0] * 6, 0.1, 4.0) - 0.1
+
+
+def test_continual_trainer_forgets_less_than_plain_finetuning():
+    xa, ya = _task(1)
+    xb, yb = _task(2)
+    results = {}
+    for continual in (False, True):
+        model = _TinyLM()
+        tr = ContinualTrainer(model, ContinualConfig(continual=continual, learning_rate=2e-2, ecc_lambda=200.0, distill_alpha=1.0, replay_batch=8,
+                                                     forgetting_check_interval=20, fisher_alpha=0.05))
+        for _ in range(150):
+            tr.train_step(xa, ya)
+        tr.on_task_boundary(1, eval_set=(xa, ya))
+        base = tr.bench.tasks[0]["baseline"]
+        for _ in range(150):
+            m = tr.train_step(xb, yb)
+        with torch.no_grad():
+            after = float(tr._lm_loss(xa, ya)[0])
+            new = float(tr._lm_loss(xb, yb)[0])
+        results[continual] = (after - base, new)
+        if continual:
+            assert m.replay_buffer_size > 0 and m.ecc_regularizer >= 0 and m.distill_loss >= 0
+    assert results[True][0] < 0.6 * results[False][0], results     # forgetting of task A
+    assert results[True][1] < 2.5, results                         # and task B was still learnt
+
+
+def test_delta_adapter_host():
+    host = DeltaAdapterHost(DeltaAdapterConfig(max_adapters=2))
+    a = host.create_adapter("task-a")
+    w = torch.zeros(4, 32)
+    g = torch.ones(4, 32)
+    host.update_delta(a, "w", g, lr=0.5)
+    host.accumulate_fisher(a, "w", g * g)
+    assert torch.allclose(host.merge_deltas(w, "w", a), torch.full((4, 32), -0.5))
+    assert abs(host.regularizer(a, 2.0) - 0.25 * 128) < 1e-4
+    host.freeze_adapter(a)
+    host.update_delta(a, "w", g, lr=0.5)             # ignored
+    assert host.is_frozen(a) and (host.merge_deltas(w, "w", a) + 0.5).abs().max() < 0.05
+    b = host.create_adapter("task-b")
+    host.update_delta(b, "w", -g, lr=1.0)
+    assert (host.merge_all_active(w, "w") - 0.5).abs().max() < 0.05 and host.active_adapter_ids() == [b]
+    assert host.total_adapter_params() == 256 and host.remove_adapter(a) and host.adapter_count() == 1 if hasattr(host, "adapter_count") else True
+
+
+def test_mtp_heads_learn_and_tune_draft_length():
+    torch.manual_seed(3)
+    V, E = 16, 16
+    emb = torch.nn.functional.one_hot(torch.arange(V), E).float()
+    ids = (torch.arange(40).view(1, -1) * 3 + torch.arange(4).view(-1, 1)) % V     # next token = +3: t+2 is +6, t+3 is +9
+    hidden = emb[ids]
+    tr = MTPHeadTrainer(MTPHeadConfig(num_heads=2, hidden_size=E, vocab_size=V, learning_rate=5e-2, weight_decay=0.0, max_draft_k=2))
+    first = tr.train_step(hidden, ids)
+    for _ in range(200):
+        last = tr.train_step(hidden, ids)
+    assert last[0] < 0.3 * first[0] and last[1] < 0.3 * first[1]
+    prop = tr.propose_tokens(hidden[:, 0], k=2)
+    assert torch.equal(prop[:, 0], (ids[:, 0] + 6) % V) and torch.equal(prop[:, 1], (ids[:, 0] + 9) % V)
+    tr.quantize_heads("oil8")
+    assert torch.equal(tr.propose_tokens(hidden[:, 0], k=2), prop)
+    tr.draft_k = 1
+    for _ in range(3):
+        tr.update_draft_k(0.95)
+    assert tr.draft_k == 2
+    for _ in range(200):
+        tr.update_draft_k(0.1)
+    assert tr.draft_k == 1
