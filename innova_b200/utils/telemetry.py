@@ -65,6 +65,40 @@ class SopsCounters:
 GLOBAL_SOPS = SopsCounters()
 
 
+class CycleCounter:
+    """Time-stamp-counter sections (the reference brackets its hot loops with rdtsc, include/oil/sops.h:26-80):
+    ``with counter.section("name"):`` accumulates cycles and calls; ``report()`` converts to seconds with the
+    measured counter rate. Host-side only: device work is timed with CUDA events (``KernelTimer``)."""
+
+    def __init__(self):
+        import ctypes
+        from .. import _native
+        lib = _native.host()
+        lib.sops_rdtsc.restype, lib.sops_rdtsc.argtypes = ctypes.c_uint64, []
+        lib.sops_tsc_hz.restype, lib.sops_tsc_hz.argtypes = ctypes.c_double, []
+        self._rdtsc, self.hz = lib.sops_rdtsc, float(lib.sops_tsc_hz())
+        self.cycles, self.calls = {}, {}
+
+    def now(self) -> int:
+        return int(self._rdtsc())
+
+    def section(self, name: str):
+        counter = self
+
+        class _Section:
+            def __enter__(self):
+                self.t0 = counter.now()
+
+            def __exit__(self, *exc):
+                counter.cycles[name] = counter.cycles.get(name, 0) + counter.now() - self.t0
+                counter.calls[name] = counter.calls.get(name, 0) + 1
+
+        return _Section()
+
+    def report(self) -> dict:
+        return {n: {"cycles": c, "calls": self.calls[n], "seconds": c / self.hz} for n, c in self.cycles.items()}
+
+
 class SopsScheduler:
     """Priority task queue: higher priority first, FIFO among equals."""
 

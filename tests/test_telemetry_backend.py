@@ -49,3 +49,14 @@ def test_backend_probe_and_selection():
     assert B.select_optimal_backend(gpu) == "distributed"
     r = B.benchmark_operation(lambda: torch.randn(32, 32) @ torch.randn(32, 32), iters=3, warmup=1)
     assert r["min_ms"] <= r["median_ms"]
+
+
+def test_cycle_counter_sections():
+    import time
+    from innova_b200.utils.telemetry import CycleCounter
+    c = CycleCounter()
+    for _ in range(2):
+        with c.section("nap"):
+            time.sleep(0.02)
+    r = c.report()["nap"]
+    assert r["calls"] == 2 and 0.03 < r["seconds"] < 0.5 and c.hz > 1e6
