@@ -273,17 +273,14 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       const uint32_t acc_ph = (tile_i >> 1) & 1;
       if (!mbar_wait_warp(&tmem_full[acc], acc_ph, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
-      int row = u.m0 + (int)cta * 128 + q * 32 + lane;
+      const int row = u.m0 + (int)cta * 128 + q * 32 + lane;
       const bool row_ok = row < p.M;
-      GemmParams pe = p;
       const CUtensorMap* c_map = &tmap_c;
       int row_shift = 0;
-      if (p.rs_world > 1) {  // this tile's rows belong to one owner: store into its buffer (TMA stores reach peer memory) at the shard-relative row
+      if (p.rs_world > 1) {  // this tile's rows belong to one owner: the staged tile is TMA-stored into its buffer (peer memory) at the shard-relative row
         const int owner = u.m0 / p.rs_shard_rows;
-        pe.C = p.rs_dst[owner];
         c_map = &rs_maps.m[owner];
         row_shift = owner * p.rs_shard_rows;
-        row -= row_shift;
       }
       const uint32_t t_row = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
       const int row0_abs = u.m0 + (int)cta * 128 + q * 32;
@@ -312,8 +309,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             tma_store_commit();
           }
         } else {
-          gemm_epilogue_chunk(pe, row, row_ok, col0, r0);
-          if (col0 + 32 < p.N) gemm_epilogue_chunk(pe, row, row_ok, col0 + 32, r1);
+          gemm_epilogue_chunk(p, row, row_ok, col0, r0);
+          if (col0 + 32 < p.N) gemm_epilogue_chunk(p, row, row_ok, col0 + 32, r1);
         }
       }
       tc_fence_before();

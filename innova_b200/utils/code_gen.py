@@ -370,7 +370,7 @@ class CodeGenerator:
             call = lambda: fn(ctypes.c_void_p(ids.data_ptr()), ctypes.c_void_p(table.data_ptr()), ctypes.c_void_p(out.data_ptr()), ctypes.c_int(256), None)
             ref = self._reference(s, (ids, table))
         elif s.kind == "quantize_dequantize":
-            n = s.N or 1 << 16
+            n = max(s.block, (s.N or 1 << 16) // s.block * s.block)      # whole blocks, so that the check below can view them
             x = torch.randn(n, device=dev, generator=g)
             out = torch.empty_like(x)
             call = lambda: fn(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()), ctypes.c_long(n), None)
