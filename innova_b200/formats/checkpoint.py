@@ -135,3 +135,112 @@ def load_sharded(engine, directory: str):
         engine.exp_avg_sq[:n].copy_(full["v"][lo:lo + n])
         engine.flat_param[: min(total, engine.total)].copy_(full["master"][: min(total, engine.total)].to(engine.flat_param.dtype))
     engine.step_count = man["step"]
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# The dense trainer's second checkpoint format (engines/trainer/dense/checkpoint.cpp:53-172), byte for byte:
+#   u32 magic 0x4B504843, u32 version 2, u32 step, f32 learning rate,
+#   u32 n, n x tensor "param_i", u32 n, n x (tensor "m_i", tensor "v_i")
+#   tensor = u32 name length, name, u32 payload size, payload = i32 rank, rank x i64 dims, u8 dtype, data
+#   dtype codes: 0 int64, 1 uint8, 2 packed 4-bit, 3 fp16, 4 fp32.
+# ----------------------------------------------------------------------------------------------------------------
+CKPT2_MAGIC, CKPT2_VERSION = 0x4B504843, 2
+_CKPT2_DTYPES = {0: torch.int64, 1: torch.uint8, 3: torch.float16, 4: torch.float32}
+
+
+def _ckpt2_write_tensor(f, name: str, t: torch.Tensor):
+    import struct
+    t = t.detach().cpu().contiguous()
+    if t.dtype not in (torch.int64, torch.uint8, torch.float16):
+        t = t.float()
+    code = {torch.int64: 0, torch.uint8: 1, torch.float16: 3, torch.float32: 4}[t.dtype]
+    payload = struct.pack("<i", t.dim()) + b"".join(struct.pack("<q", d) for d in t.shape) + struct.pack("<B", code) + t.numpy().tobytes()
+    if len(payload) > 0xFFFFFFFF:
+        raise ValueError("tensor too large for this checkpoint format (> 4 GB)")
+    nb = name.encode()
+    f.write(struct.pack("<I", len(nb)) + nb + struct.pack("<I", len(payload)) + payload)
+
+
+def _ckpt2_read_tensor(f):
+    import struct
+    import numpy as np
+    (nl,) = struct.unpack("<I", f.read(4))
+    name = f.read(nl).decode()
+    (size,) = struct.unpack("<I", f.read(4))
+    buf = f.read(size)
+    if len(buf) != size:
+        raise IOError("corrupt checkpoint: tensor data")
+    (rank,) = struct.unpack_from("<i", buf, 0)
+    if not 0 <= rank <= 8:
+        raise IOError("corrupt checkpoint: rank")
+    dims = struct.unpack_from(f"<{rank}q", buf, 4) if rank else ()
+    code = buf[4 + 8 * rank]
+    if code not in _CKPT2_DTYPES:
+        raise IOError(f"checkpoint tensor {name}: unsupported dtype code {code}")
+    dt = _CKPT2_DTYPES[code]
+    np_dt = {torch.int64: "<i8", torch.uint8: "u1", torch.float16: "<f2", torch.float32: "<f4"}[dt]
+    data = np.frombuffer(buf, dtype=np_dt, offset=5 + 8 * rank).copy()
+    return name, torch.from_numpy(data).view(*dims) if rank else torch.from_numpy(data).reshape(())
+
+
+def save_checkpoint_v2(path: str, params, step: int, lr: float, exp_avg=None, exp_avg_sq=None):
+    """``params`` / ``exp_avg`` / ``exp_avg_sq``: sequences of tensors in parameter order (missing moments are zeros)."""
+    import struct
+    params = list(params)
+    if step > 0xFFFFFFFF:
+        raise ValueError("checkpoint: step exceeds the 32-bit field")
+    with open(path, "wb") as f:
+        f.write(struct.pack("<IIIfI", CKPT2_MAGIC, CKPT2_VERSION, int(step), float(lr), len(params)))
+        for i, p in enumerate(params):
+            _ckpt2_write_tensor(f, f"param_{i}", p)
+        f.write(struct.pack("<I", len(params)))
+        for i, p in enumerate(params):
+            _ckpt2_write_tensor(f, f"m_{i}", exp_avg[i] if exp_avg is not None else torch.zeros_like(p, dtype=torch.float32))
+            _ckpt2_write_tensor(f, f"v_{i}", exp_avg_sq[i] if exp_avg_sq is not None else torch.zeros_like(p, dtype=torch.float32))
+
+
+def load_checkpoint_v2(path: str):
+    """-> dict(step, lr, params [tensors], exp_avg [tensors], exp_avg_sq [tensors])."""
+    import struct
+    with open(path, "rb") as f:
+        magic, version, step, lr, n = struct.unpack("<IIIfI", f.read(20))
+        if magic != CKPT2_MAGIC:
+            raise IOError("not a dense-trainer checkpoint (magic)")
+        if version != CKPT2_VERSION:
+            raise IOError(f"unsupported checkpoint version {version}")
+        params = []
+        for i in range(n):
+            name, t = _ckpt2_read_tensor(f)
+            if name != f"param_{i}":
+                raise IOError(f"corrupt checkpoint: expected param_{i}, found {name}")
+            params.append(t)
+        (n_opt,) = struct.unpack("<I", f.read(4))
+        m, v = [], []
+        for i in range(n_opt):
+            m.append(_ckpt2_read_tensor(f)[1])
+            v.append(_ckpt2_read_tensor(f)[1])
+    return {"step": step, "lr": lr, "params": params, "exp_avg": m, "exp_avg_sq": v}
+
+
+def save_trainer_v2(trainer, path: str):
+    """A ``Trainer`` with an unsharded flat engine written in the v2 layout: master weights and AdamW moments per
+    parameter tensor, in the engine's parameter order."""
+    eng = trainer.engine
+    if getattr(eng, "shard_lo", 0) != 0 or getattr(eng, "shard_hi", eng.total) != eng.total:
+        raise ValueError("the v2 checkpoint holds whole tensors: gather the sharded state first (save_sharded keeps shards)")
+    cut = lambda flat: [flat[o:o + k].view(p.shape) for _, p, o, k in eng.entries]
+    save_checkpoint_v2(path, cut(eng.master), eng.step_count, eng.lr, cut(eng.exp_avg), cut(eng.exp_avg_sq))
+
+
+def load_trainer_v2(trainer, path: str):
+    eng = trainer.engine
+    ck = load_checkpoint_v2(path)
+    if len(ck["params"]) != len(eng.entries):
+        raise IOError("checkpoint and model disagree on the number of parameters")
+    for (_, p, o, k), w, m, v in zip(eng.entries, ck["params"], ck["exp_avg"], ck["exp_avg_sq"]):
+        eng.master[o:o + k].copy_(w.reshape(-1))
+        eng.flat_param[o:o + k].copy_(w.reshape(-1))
+        eng.exp_avg[o:o + k].copy_(m.reshape(-1))
+        eng.exp_avg_sq[o:o + k].copy_(v.reshape(-1))
+    eng.step_count, eng.lr = ck["step"], ck["lr"]
+    return ck["step"]

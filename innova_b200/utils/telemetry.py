@@ -65,6 +65,25 @@ class SopsCounters:
 GLOBAL_SOPS = SopsCounters()
 
 
+class nvtx_range:
+    """``with nvtx_range("forward"):`` marks a range for timeline profilers (no-op without CUDA)."""
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        import torch
+        self._on = torch.cuda.is_available()
+        if self._on:
+            torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        if self._on:
+            import torch
+            torch.cuda.nvtx.range_pop()
+
+
 class CycleCounter:
     """Time-stamp-counter sections (the reference brackets its hot loops with rdtsc, include/oil/sops.h:26-80):
     ``with counter.section("name"):`` accumulates cycles and calls; ``report()`` converts to seconds with the
