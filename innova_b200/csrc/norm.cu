@@ -28,6 +28,15 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float* f) {
     f[2 * j + 1] = t.y;
   }
 }
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 t = __bfloat1622float2(h[j]);
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
 __device__ __forceinline__ void store8(__nv_bfloat16* p, const float* f) {
   uint4 o;
   o.x = pack_bf16x2(f[0], f[1]);
@@ -217,23 +226,44 @@ __global__ void __launch_bounds__(256) norm_bwd_small_kernel(const __nv_bfloat16
       if (c >= D) g[k][j] = 0.f;
     }
   }
-  for (int row = gw; row < T; row += nw) {
+  // The next row's x and dy are in flight (packed, 2 * NCH registers of 16 bytes) while this row is reduced and
+  // written: one row per warp at a time would expose a full memory round trip per row.
+  uint4 nx[NCH], nd[NCH];
+  float nmean = 0.f, nrstd = 0.f;
+  auto prefetch = [&](int row) {
     const __nv_bfloat16* xr = x + (size_t)row * D;
     const __nv_bfloat16* dyr = dy + (size_t)row * D;
-    const float mean = RMS ? 0.f : mean_in[row];
-    const float rstd = rstd_in[row];
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < D) {
+        nx[k] = *reinterpret_cast<const uint4*>(xr + c);
+        nd[k] = *reinterpret_cast<const uint4*>(dyr + c);
+      }
+    }
+    nmean = RMS ? 0.f : mean_in[row];
+    nrstd = rstd_in[row];
+  };
+  if (gw < T) prefetch(gw);
+  for (int row = gw; row < T; row += nw) {
+    const float mean = nmean;
+    const float rstd = nrstd;
     float xh[NCH][8], d[NCH][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
       const int c = k * 256 + lane * 8;
       if (c < D) {
-        load8(xr + c, xh[k]);
-        load8(dyr + c, d[k]);
+        unpack8(nx[k], xh[k]);
+        unpack8(nd[k], d[k]);
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) xh[k][j] = mean, d[k][j] = 0.f;
       }
+    }
+    if (row + nw < T) prefetch(row + nw);
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         xh[k][j] = (xh[k][j] - mean) * rstd;
