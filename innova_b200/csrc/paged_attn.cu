@@ -439,7 +439,8 @@ __global__ void __launch_bounds__(128, 4) paged_decode_oil4_mma_kernel(const __n
                                                                     int max_pages, const int* __restrict__ seq_lens, int H, int Hkv,
                                                                     const uint8_t* __restrict__ k_pool, const uint8_t* __restrict__ v_pool,
                                                                     const __half* __restrict__ k_scale, const __half* __restrict__ v_scale,
-                                                                    float scale, float* __restrict__ part, int splits) {
+                                                                    float scale, float* __restrict__ part, int splits,
+                                                                    __nv_bfloat16* __restrict__ out_direct, int ld_o) {
   constexpr int MAXG = 8;
   constexpr int KCH = D / 4;        // d-values of a K row per lane (one quarter of the row)
   constexpr int KW = KCH / 8;       // ... as 32-bit words of indices (4 for D = 128)
@@ -626,6 +627,10 @@ __global__ void __launch_bounds__(128, 4) paged_decode_oil4_mma_kernel(const __n
       acc += sm_o[w][g][e] * f;
       ll += sm_l[w][g] * f;
     }
+    if (out_direct != nullptr) {  // a single split: the result is final, no combine pass
+      out_direct[(long)b * ld_o + (hk * G + g) * D + e] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+      continue;
+    }
     out[g * (D + 2) + 2 + e] = acc;
     if (e == 0) {
       out[g * (D + 2)] = mm;
@@ -681,6 +686,102 @@ extern "C" int inv_kv_append(const void* k_new, const void* v_new, int ld_k, int
   return e == cudaSuccess ? 0 : -(int)e;
 }
 
+namespace inv {
+// Decode-step finish of the QKV projection: one pass over the fp32 accumulator [B, (H + 2 Hkv) D] that adds the bias,
+// rounds to bf16 (as the stand-alone finish pass does), rotates the query and key heads (half-split RoPE at the token's
+// position), writes the queries as bf16 and appends the key / value heads to the paged cache (OIL4: block-32 abs-max
+// scale + nearest of the 16 levels; or bf16), and clears the accumulator. Replaces three launches per layer.
+// One warp per (token, head slot); lane l owns elements l + 32 j, so a rotation pair (e, e + D/2) sits in one thread.
+template <bool OIL4, int D>
+__global__ void __launch_bounds__(256) decode_qkv_finish_kernel(float* __restrict__ acc, int ld_acc, const __nv_bfloat16* __restrict__ bias,
+                                                                const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                                const int* __restrict__ pos, const int* __restrict__ page_table, int max_pages,
+                                                                int B, int H, int Hkv, __nv_bfloat16* __restrict__ q_out, int ld_q,
+                                                                uint8_t* __restrict__ k_pool, uint8_t* __restrict__ v_pool,
+                                                                __half* __restrict__ k_scale, __half* __restrict__ v_scale) {
+  constexpr int NJ = D / 32, HALFJ = NJ / 2;
+  const int lane = threadIdx.x & 31;
+  const long warp_id = blockIdx.x * (long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int slots = H + 2 * Hkv;
+  if (warp_id >= (long)B * slots) return;
+  const int slot = (int)(warp_id % slots), b = (int)(warp_id / slots);
+  float* arow = acc + (size_t)b * ld_acc + slot * D;
+  float v[NJ];
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    const int e = lane + 32 * j;
+    float x = arow[e];
+    arow[e] = 0.f;
+    if (bias) x += __bfloat162float(bias[slot * D + e]);
+    v[j] = __bfloat162float(__float2bfloat16_rn(x));
+  }
+  const int p = pos[b];
+  if (slot < H + Hkv) {  // query and key heads rotate
+#pragma unroll
+    for (int j = 0; j < HALFJ; ++j) {
+      const int i = lane + 32 * j;
+      const float c = cos_t[(size_t)p * (D / 2) + i], sn = sin_t[(size_t)p * (D / 2) + i];
+      const float x1 = v[j], x2 = v[j + HALFJ];
+      v[j] = __bfloat162float(__float2bfloat16_rn(x1 * c - x2 * sn));
+      v[j + HALFJ] = __bfloat162float(__float2bfloat16_rn(x1 * sn + x2 * c));
+    }
+  }
+  if (slot < H) {
+    __nv_bfloat16* qo = q_out + (size_t)b * ld_q + slot * D;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) qo[lane + 32 * j] = __float2bfloat16_rn(v[j]);
+    return;
+  }
+  const int which = slot >= H + Hkv;  // 0 = key, 1 = value
+  const int hk = slot - H - which * Hkv;
+  const int page = page_table[(long)b * max_pages + p / PAGE];
+  const long row = ((long)page * Hkv + hk) * PAGE + p % PAGE;
+  uint8_t* pool = which ? v_pool : k_pool;
+  if (!OIL4) {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(pool) + row * D;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) dst[lane + 32 * j] = __float2bfloat16_rn(v[j]);
+    return;
+  }
+  __half* sc = (which ? v_scale : k_scale) + row * (D / 32);
+  uint8_t* dst = pool + row * (D / 2);
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    float amax = fabsf(v[j]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = amax < 1e-10f ? 1.f : amax;
+    const int code = nearest_level16(v[j] / scale);
+    const int hi = __shfl_down_sync(0xffffffffu, code, 1);
+    if ((lane & 1) == 0) dst[j * 16 + (lane >> 1)] = (uint8_t)(code | (hi << 4));
+    if (lane == 0) sc[j] = __float2half_rn(scale);
+  }
+}
+
+}  // namespace inv
+using namespace inv;
+extern "C" int inv_decode_qkv_finish(float* acc, int ld_acc, const void* bias, const float* cos_t, const float* sin_t, const int* pos,
+                                     const int* page_table, int max_pages, int B, int H, int Hkv, int D, void* q_out, int ld_q, void* k_pool,
+                                     void* v_pool, void* k_scale, void* v_scale, int oil4, void* stream) {
+  if (D != 64 && D != 128) return -ERR_BAD_ARG;
+  if (B <= 0) return 0;
+  const long warps = (long)B * (H + 2 * Hkv);
+  const int grid = (int)((warps + 7) / 8);
+  cudaStream_t st = (cudaStream_t)stream;
+#define INV_DQF(O, DD)                                                                                                                      \
+  decode_qkv_finish_kernel<O, DD><<<grid, 256, 0, st>>>(acc, ld_acc, (const __nv_bfloat16*)bias, cos_t, sin_t, pos, page_table, max_pages, B, \
+                                                        H, Hkv, (__nv_bfloat16*)q_out, ld_q, (uint8_t*)k_pool, (uint8_t*)v_pool,             \
+                                                        (__half*)k_scale, (__half*)v_scale)
+  if (oil4) {
+    if (D == 64) INV_DQF(true, 64); else INV_DQF(true, 128);
+  } else {
+    if (D == 64) INV_DQF(false, 64); else INV_DQF(false, 128);
+  }
+#undef INV_DQF
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
 // Scratch floats needed by inv_paged_decode.
 extern "C" long inv_paged_decode_scratch_floats(int B, int H, int D, int splits) { return (long)B * H * splits * (D + 2); }
 
@@ -699,9 +800,14 @@ extern "C" int inv_paged_decode(const void* q, int ld_q, const int* page_table, 
 #define INV_PD4(DD)                                                                                                                        \
   paged_decode_oil4_mma_kernel<DD><<<grid, 128, 0, st>>>((const __nv_bfloat16*)q, ld_q, page_table, max_pages, seq_lens, H, Hkv,               \
                                                      (const uint8_t*)k_pool, (const uint8_t*)v_pool, (const __half*)k_scale,               \
-                                                     (const __half*)v_scale, scale, scratch, splits)
+                                                     (const __half*)v_scale, scale, scratch, splits,                                        \
+                                                     splits == 1 ? (__nv_bfloat16*)out : nullptr, ld_o)
     if (D == 64) INV_PD4(64); else INV_PD4(128);
 #undef INV_PD4
+    if (splits == 1) {  // the kernel wrote the final output
+      cudaError_t e1 = cudaGetLastError();
+      return e1 == cudaSuccess ? 0 : -(int)e1;
+    }
   } else {
     if (D == 64) INV_PD(false, 64); else INV_PD(false, 128);
   }

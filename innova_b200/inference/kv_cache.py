@@ -17,6 +17,8 @@ from .. import _native
 from ..ops import runtime as rt
 
 _native.register_cuda_sigs({
+    "inv_decode_qkv_finish": [_native.vp, _native.i32, _native.vp, _native.vp, _native.vp, _native.vp, _native.vp, _native.i32, _native.i32, _native.i32,
+                              _native.i32, _native.i32, _native.vp, _native.i32, _native.vp, _native.vp, _native.vp, _native.vp, _native.i32, _native.vp],
     "inv_kv_append": [_native.vp, _native.vp, _native.i32, _native.i32, _native.vp, _native.i32, _native.vp, _native.i32, _native.i32, _native.i32,
                       _native.i32, _native.vp, _native.vp, _native.vp, _native.vp, _native.i32, _native.vp],
     "inv_paged_decode": [_native.vp, _native.i32, _native.vp, _native.i32, _native.vp, _native.i32, _native.i32, _native.i32, _native.i32,

@@ -26,7 +26,7 @@ from .. import ops
 from ..inference.kv_cache import PagedKVCache, PAGE
 from ..models.config import TransformerConfig
 from ..ops import runtime as rt
-from ..ops.oil_linear import QuantWeight, finish_norm, oil_linear, oil_linear_norm, oil_linear_swiglu, quantize_weight
+from ..ops.oil_linear import QuantWeight, _acc_for, _gemm_into_acc, finish_norm, oil_linear, oil_linear_norm, oil_linear_swiglu, quantize_weight
 
 
 class TPContext:
@@ -215,14 +215,17 @@ class TPDecoder:
         lib, st = rt.lib(), rt.stream_ptr()
         h = ops.rms_norm(x, self.layers[0]["n1"], cfg.norm_eps)
         for li, l in enumerate(self.layers):
-            qkv = oil_linear(h, l["qkv"]).view(B, 1, -1)
-            qkv = ops.rope_qk(qkv, self.rope[0], self.rope[1], H, Hkv, D, pos)
-            k, v = qkv[..., H * D:(H + Hkv) * D], qkv[..., (H + Hkv) * D:]
-            rt.check(lib.inv_kv_append(k.data_ptr(), v.data_ptr(), k.stride(1), v.stride(1), c.page_table.data_ptr(), c.max_pages, pos.data_ptr(),
-                                       B, 1, Hkv, D, c.k_pool[li].data_ptr(), c.v_pool[li].data_ptr(), rt.ptr(c.k_scale[li]),
-                                       rt.ptr(c.v_scale[li]), int(c.fmt == "oil4"), st), "inv_kv_append")
+            # QKV projection: the GEMM leaves fp32 sums, one finish kernel adds the bias, applies RoPE, writes the queries
+            # and appends the new keys / values to the paged cache (quantised)
+            qw = l["qkv"]
+            acc = _acc_for(h, qw, B)
+            _gemm_into_acc(h.reshape(B, -1), qw, acc)
+            q2 = torch.empty(B, H * D, dtype=torch.bfloat16, device=self.dev)
+            rt.check(lib.inv_decode_qkv_finish(acc.data_ptr(), acc.stride(0), rt.ptr(qw.bias), self.rope[0].data_ptr(), self.rope[1].data_ptr(),
+                                               pos.data_ptr(), c.page_table.data_ptr(), c.max_pages, B, H, Hkv, D, q2.data_ptr(), q2.stride(0),
+                                               c.k_pool[li].data_ptr(), c.v_pool[li].data_ptr(), rt.ptr(c.k_scale[li]), rt.ptr(c.v_scale[li]),
+                                               int(c.fmt == "oil4"), st), "inv_decode_qkv_finish")
             a = torch.empty(B, H * D, dtype=torch.bfloat16, device=self.dev)
-            q2 = qkv.view(B, -1)
             rt.check(lib.inv_paged_decode(q2.data_ptr(), q2.stride(0), c.page_table.data_ptr(), c.max_pages, c.seq_lens.data_ptr(), B, H, Hkv, D,
                                           c.k_pool[li].data_ptr(), c.v_pool[li].data_ptr(), rt.ptr(c.k_scale[li]), rt.ptr(c.v_scale[li]),
                                           int(c.fmt == "oil4"), float(scale), a.data_ptr(), a.stride(0), self._scratch.data_ptr(),
