@@ -260,6 +260,7 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == 0) {
     // lane 0 streams index tiles, lane 1 streams activation tiles; each runs ahead on its own ring
@@ -273,6 +274,11 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
         if (++si == IDX_STAGES) { si = 0; ph ^= 1; }
       }
     } else if (lane == 1) {
+      // Programmatic dependent launch: this grid may start while the kernel that produces the activations is still
+      // running. Everything that touches only the (static) weights runs ahead: index tiles are fetched and expanded
+      // into tensor memory; the activation loads, and with them the MMAs and the epilogue, wait here for the
+      // previous grid to complete.
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       int lb = 0;
       for (OgCursor c(n_tiles, nb, p.dp_rounds); c.valid; c.advance(), ++lb) {
         const int kb0 = c.bb * KBB, nkb = min(KBB, kb_total - kb0);
@@ -485,6 +491,7 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
 // out_bf16[m, n] = bf16(acc[m, n] + bias[n] (+ residual[m, n])); clears acc for the next use. Four columns per thread.
 __global__ void oil_gemm_finish_kernel(float* __restrict__ acc, const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ residual,
                                        __nv_bfloat16* __restrict__ out, long M, int N, int ld_acc, int ld_out, int ld_res, int clear, int vec) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the next GEMM may start fetching and expanding its weights
   const long m = blockIdx.y;
   if (vec) {
     for (int n = (blockIdx.x * blockDim.x + threadIdx.x) * 4; n < N; n += gridDim.x * blockDim.x * 4) {
@@ -517,6 +524,7 @@ __global__ void oil_gemm_finish_kernel(float* __restrict__ acc, const __nv_bfloa
 // The gate / up projection's finish and the SwiGLU in one pass. F % 4 == 0.
 __global__ void oil_gemm_finish_swiglu_kernel(float* __restrict__ acc, const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int F,
                                               int ld_acc, int ld_out) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const long m = blockIdx.y;
   for (int f = (blockIdx.x * blockDim.x + threadIdx.x) * 4; f < F; f += gridDim.x * blockDim.x * 4) {
     float4 g = *reinterpret_cast<float4*>(acc + m * ld_acc + f);
@@ -545,6 +553,7 @@ __global__ void __launch_bounds__(256) oil_gemm_finish_norm_kernel(float* __rest
                                                                    const __nv_bfloat16* __restrict__ w, float eps, __nv_bfloat16* __restrict__ h_out,
                                                                    int N, int ld_acc, int ld_x, int ld_res, int ld_h) {
   constexpr int MAXV = 16;  // float4 groups per thread: 256 * 16 * 4 = 16384 columns
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const long m = blockIdx.x;
   __shared__ float red[8];
   float4 xs[MAXV];
@@ -650,10 +659,20 @@ static int oil_gemm_launch(const void* x, int ldx, const void* idx, const void* 
   int grid = (int)((total + 1) / 2);
   if (grid > num_sms) grid = num_sms;
   p.dp_rounds = n_tiles / grid;  // whole tiles while they fill rounds of the grid, the rest is the stream-K tail
-  if (bits == 2) oil_gemm_kernel<2><<<grid, THREADS, smem, st>>>(ti, tx, p);
-  else if (bits == 4) oil_gemm_kernel<4><<<grid, THREADS, smem, st>>>(ti, tx, p);
-  else oil_gemm_kernel<8><<<grid, THREADS, smem, st>>>(ti, tx, p);
-  cudaError_t e = cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e;
+  if (bits == 2) e = cudaLaunchKernelEx(&cfg, oil_gemm_kernel<2>, ti, tx, p);
+  else if (bits == 4) e = cudaLaunchKernelEx(&cfg, oil_gemm_kernel<4>, ti, tx, p);
+  else e = cudaLaunchKernelEx(&cfg, oil_gemm_kernel<8>, ti, tx, p);
   return e == cudaSuccess ? 0 : -(int)e;
 }
 

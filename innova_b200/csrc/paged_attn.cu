@@ -448,6 +448,7 @@ __global__ void __launch_bounds__(128, 4) paged_decode_oil4_mma_kernel(const __n
   constexpr int VCH = D / 8;        // d-values of a V row per lane (one eighth of the row)
   constexpr int VW = VCH / 8;       // ... as 32-bit words (2 for D = 128)
   constexpr int VMMA = VCH / 2;     // PV MMAs per page: 2 d-values per lane and MMA
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the output projection may start on its weights
   __shared__ __align__(16) uint32_t lut[256 * 32];  // byte -> half2(level[low nibble], level[high nibble]); entry e of lane l at [e * 32 + l]
   __shared__ float sm_m[4][MAXG], sm_l[4][MAXG];
   float (*sm_o)[MAXG][D] = reinterpret_cast<float (*)[MAXG][D]>(lut);  // the per-warp outputs reuse the table once the loop is over
@@ -700,6 +701,7 @@ __global__ void __launch_bounds__(256) decode_qkv_finish_kernel(float* __restric
                                                                 uint8_t* __restrict__ k_pool, uint8_t* __restrict__ v_pool,
                                                                 __half* __restrict__ k_scale, __half* __restrict__ v_scale) {
   constexpr int NJ = D / 32, HALFJ = NJ / 2;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const long warp_id = blockIdx.x * (long)(blockDim.x >> 5) + (threadIdx.x >> 5);
   const int slots = H + 2 * Hkv;
