@@ -223,6 +223,29 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     uint8_t* pt_row = sPt + hf * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
     uint8_t* dst_row = sdSt + hf * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
     bool ok = true;
+    // dQ block j: TMEM lanes are query rows now; this thread adds D/2 columns of row q0 + r into the fp32 buffer
+    auto dq_readout = [&](int j) {
+      const int hj = hk * G + j / nq_it;
+      const int qrow = (i0 + j % nq_it) * 128 + r;
+#pragma unroll
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int col0 = hf * (D / 2) + cc * 32;
+        uint32_t rr[32];
+        tmem_ld_32x32(t_lane + DQ_COL + col0, rr);
+        tmem_ld_wait();
+        if (qrow < p.S && !(p.causal & 2)) {
+          float* dst = p.dq_acc + ((size_t)b * p.S + qrow) * ((size_t)p.H * D) + hj * D + col0;
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + g * 4), "f"(__uint_as_float(rr[g * 4])),
+                         "f"(__uint_as_float(rr[g * 4 + 1])), "f"(__uint_as_float(rr[g * 4 + 2])), "f"(__uint_as_float(rr[g * 4 + 3]))
+                         : "memory");
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_empty);
+    };
     for (int it = 0; it < n_it; ++it) {
       const int h = hk * G + it / nq_it;
       const int q0 = (i0 + it % nq_it) * 128;
@@ -251,13 +274,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_empty);  // one arrival per warp: arrivals on one mbarrier are serialised
+      uint32_t pk_all[2][16], dk_all[2][16];  // P^T and dS^T of this block as packed bf16 pairs, kept in registers until the
+                                              // shared-memory tiles are free
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int col0 = hf * 64 + cc * 32;
         const uint32_t* s_r = s_all + cc * 32;
         const uint32_t* dp_r = dp_all + cc * 32;
-
-        uint32_t pk[16], dk[16];  // P^T and dS^T of this chunk as packed bf16 pairs
+        uint32_t* pk = pk_all[cc];
+        uint32_t* dk = dk_all[cc];
         if (!need_mask) {
           // interior block: no predicates, statistics fetched as 16-byte broadcast loads; one MUFU op per element,
           // bf16 packing on the integer pipe
@@ -293,38 +318,41 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             dk[i >> 1] = pack_bf16x2_int(de[0], de[1]);
           }
         }
+      }
+      // Software pipeline (when dQ has its own TMEM columns): the arithmetic above ran while the MMAs of the previous
+      // block were still reading its P^T / dS^T tiles; only now wait for them, publish this block's tiles, and read the
+      // previous block's dQ out of TMEM while this block's MMAs run.
+      if (OVERLAP && it > 0) {
+        if (!mbar_wait_warp(mma2_done, (it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+      }
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           const int chunk = (cc * 4 + g) ^ (r & 7);
-          *reinterpret_cast<uint4*>(pt_row + chunk * 16) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
-          *reinterpret_cast<uint4*>(dst_row + chunk * 16) = make_uint4(dk[g * 4], dk[g * 4 + 1], dk[g * 4 + 2], dk[g * 4 + 3]);
+          *reinterpret_cast<uint4*>(pt_row + chunk * 16) = make_uint4(pk_all[cc][g * 4], pk_all[cc][g * 4 + 1], pk_all[cc][g * 4 + 2], pk_all[cc][g * 4 + 3]);
+          *reinterpret_cast<uint4*>(dst_row + chunk * 16) = make_uint4(dk_all[cc][g * 4], dk_all[cc][g * 4 + 1], dk_all[cc][g * 4 + 2], dk_all[cc][g * 4 + 3]);
         }
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
-      // dQ block: TMEM lanes are query rows now; this thread adds D/2 columns of row q0 + r.
-      if (!mbar_wait_warp(mma2_done, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
-      tc_fence_after();
-      const int qrow = q0 + r;
-#pragma unroll
-      for (int cc = 0; cc < D / 64; ++cc) {
-        const int col0 = hf * (D / 2) + cc * 32;
-        uint32_t rr[32];
-        tmem_ld_32x32(t_lane + DQ_COL + col0, rr);
-        tmem_ld_wait();
-        if (qrow < p.S && !(p.causal & 2)) {
-          float* dst = p.dq_acc + ((size_t)b * p.S + qrow) * ((size_t)p.H * D) + h * D + col0;
-#pragma unroll
-          for (int g = 0; g < 8; ++g)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + g * 4), "f"(__uint_as_float(rr[g * 4])),
-                         "f"(__uint_as_float(rr[g * 4 + 1])), "f"(__uint_as_float(rr[g * 4 + 2])), "f"(__uint_as_float(rr[g * 4 + 3]))
-                         : "memory");
-        }
+      if (OVERLAP) {
+        if (it > 0) dq_readout(it - 1);
+      } else {
+        if (!mbar_wait_warp(mma2_done, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        dq_readout(it);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(dq_empty);
+    }
+    if (OVERLAP && ok && n_it > 0) {
+      if (mbar_wait_warp(mma2_done, (n_it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) {
+        tc_fence_after();
+        dq_readout(n_it - 1);
+      } else {
+        ok = false;
+      }
     }
     // dK, dV: the last mma2_done covers every accumulation. TMEM lanes are key rows.
     if (ok && n_it > 0) {
