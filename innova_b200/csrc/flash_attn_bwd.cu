@@ -284,8 +284,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         uint32_t* pk = pk_all[cc];
         uint32_t* dk = dk_all[cc];
         if (!need_mask) {
-          // interior block: no predicates, statistics fetched as 16-byte broadcast loads; one MUFU op per element,
-          // bf16 packing on the integer pipe
+          // interior block: no predicates, statistics fetched as 16-byte broadcast loads; one MUFU op and half a
+          // conversion per element
           const float4* l4 = reinterpret_cast<const float4*>(stat + col0);
           const float4* d4 = reinterpret_cast<const float4*>(stat + 128 + col0);
 #pragma unroll
@@ -294,10 +294,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             const int i = i4 * 4;
             const float e0 = exp2f(fmaf(__uint_as_float(s_r[i]), c, -l.x)), e1 = exp2f(fmaf(__uint_as_float(s_r[i + 1]), c, -l.y));
             const float e2 = exp2f(fmaf(__uint_as_float(s_r[i + 2]), c, -l.z)), e3 = exp2f(fmaf(__uint_as_float(s_r[i + 3]), c, -l.w));
-            pk[i4 * 2] = pack_bf16x2_int(e0, e1);
-            pk[i4 * 2 + 1] = pack_bf16x2_int(e2, e3);
-            dk[i4 * 2] = pack_bf16x2_int(e0 * (__uint_as_float(dp_r[i]) - dl.x), e1 * (__uint_as_float(dp_r[i + 1]) - dl.y));
-            dk[i4 * 2 + 1] = pack_bf16x2_int(e2 * (__uint_as_float(dp_r[i + 2]) - dl.z), e3 * (__uint_as_float(dp_r[i + 3]) - dl.w));
+            pk[i4 * 2] = cvt_bf16x2(e0, e1);
+            pk[i4 * 2 + 1] = cvt_bf16x2(e2, e3);
+            dk[i4 * 2] = cvt_bf16x2(e0 * (__uint_as_float(dp_r[i]) - dl.x), e1 * (__uint_as_float(dp_r[i + 1]) - dl.y));
+            dk[i4 * 2 + 1] = cvt_bf16x2(e2 * (__uint_as_float(dp_r[i + 2]) - dl.z), e3 * (__uint_as_float(dp_r[i + 3]) - dl.w));
           }
         } else {
 #pragma unroll
