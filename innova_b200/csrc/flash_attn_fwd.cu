@@ -738,8 +738,8 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       m_used = m_new;
       const bool any_rescale = __any_sync(0xffffffffu, j > 0 && raise);
       const float mc = m_used * c;
-      // exponentials into registers (packed bf16 pairs overwrite the scores) and their sum. One MUFU op per
-      // element and nothing else on that unit: the bf16 packing is done with integer instructions.
+      // exponentials into registers (packed bf16 pairs overwrite the scores) and their sum: one MUFU op per element and
+      // one hardware conversion per pair
       float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
       for (int i = 0; i < 128; i += 2) {
@@ -747,7 +747,7 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         const float e1 = exp2f(fmaf(__uint_as_float(sr[i + 1]), c, -mc));
         rs0 += e0;
         rs1 += e1;
-        sr[i >> 1] = pack_bf16x2_int(e0, e1);  // slot i/2 <= i: never read again as a score
+        sr[i >> 1] = cvt_bf16x2(e0, e1);  // slot i/2 <= i: never read again as a score
       }
       l = l * alpha + (rs0 + rs1);
       if (j > 0) {
