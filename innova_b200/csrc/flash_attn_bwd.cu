@@ -9,7 +9,7 @@
 // accumulates dK and dV in TMEM. Per query block, five MMAs:
 //   S^T  = K Q^T            dP^T = V dO^T            (both 128 keys x 128 queries, fp32 in TMEM)
 //   dV  += P^T dO           dK  += dS^T Q            dQ_blk = dS K
-// 8 softmax warps (thread <-> key row, two halves of the query columns) turn S^T, dP^T into
+// 16 softmax warps (thread <-> key row, four quarters of the query columns) turn S^T, dP^T into
 // P^T = exp(S^T*scale - lse) and dS^T = P^T * (dP^T - D) as bf16 tiles in swizzled shared memory.
 // The same dS^T tile serves as a K-major A operand (dK) and as an MN-major A operand (dQ), and the
 // Q / dO / K tiles serve as K-major B operands (S^T, dP^T) and MN-major B operands (dK, dV, dQ), so
@@ -22,7 +22,8 @@ namespace inv {
 
 int make_tmap_tokens_bf16(CUtensorMap* out, const void* ptr, int cols, int S, int B, int ld, int box_rows);
 
-constexpr int FB_THREADS = 384;  // warp 0 TMA, warps 1, 10, 11 MMA issuers, warps 2-9 softmax
+constexpr int FB_THREADS = 640;  // warp 0 TMA, warps 1, 18, 19 MMA issuers, warps 2-17 softmax (four per scheduler: the
+                                 // dependent FMA -> MUFU -> FMUL -> convert chains of two warps per scheduler left it mostly idle)
 
 struct FlashBwdParams {
   const float* lse;    // [B, H, S], log2 domain: log2(sum exp(scores))
@@ -100,10 +101,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       mbar_init(&q_empty[s], 2);  // the two issuers that read Q and dO
     }
     mbar_init(s_full, 2);      // S^T and dP^T have one issuer each
-    mbar_init(s_empty, 8);
-    mbar_init(pds_full, 8);
+    mbar_init(s_empty, 16);
+    mbar_init(pds_full, 16);
     mbar_init(mma2_done, 3);   // dV, dK and dQ have one issuer each
-    mbar_init(dq_empty, 8);
+    mbar_init(dq_empty, 16);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_q);
@@ -142,15 +143,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
       }
     }
-  } else if (warp == 1 || warp >= 10) {
+  } else if (warp == 1 || warp >= 18) {
     // Three MMA issuers in three warps. A thread issues one tcgen05.mma per ~100 cycles whatever its size, and a
     // query block needs 32 (D = 64) or 64 of them: one issuer would spend more time issuing than the tensor pipe
     // spends computing. Every accumulator has exactly one issuer, so the order of its updates is program order:
     //   role 0 (warp 1):  S^T = K Q^T    and  dV += P^T dO
-    //   role 1 (warp 10): dP^T = V dO^T  and  dK += dS^T Q
-    //   role 2 (warp 11): dQ_blk = dS K
+    //   role 1 (warp 18): dP^T = V dO^T  and  dK += dS^T Q
+    //   role 2 (warp 19): dQ_blk = dS K
     if (lane == 0) {
-      const int role = warp == 1 ? 0 : warp - 9;
+      const int role = warp == 1 ? 0 : warp - 17;
       const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);   // K-major x K-major
       const uint32_t idesc_kv = make_idesc_bf16(128, D, 0, 1);    // K-major A, MN-major B
       const uint32_t idesc_dq = make_idesc_bf16(128, D, 1, 1);    // MN-major A and B
@@ -211,10 +212,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
       }
     }
-  } else if (warp >= 2 && warp < 10) {
+  } else if (warp >= 2 && warp < 18) {
     // ---------------- softmax warps ----------------
     const int q = warp & 3;            // TMEM lane quarter
-    const int hf = (warp - 2) >> 2;    // which half of the columns
+    const int cq = (warp - 2) >> 2;    // which quarter of the 128 query columns (32 per thread)
+    const int hf = cq >> 1;            // the 64-column half (shared-memory tile) it falls in
+    constexpr int DC = D / 4;          // dQ / dK / dV columns per thread
     const int r = q * 32 + lane;       // row inside a tile
     const int key = k0 + r;
     const uint32_t t_lane = tmem_base + (uint32_t(q * 32) << 16);
@@ -227,16 +230,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     auto dq_readout = [&](int j) {
       const int hj = hk * G + j / nq_it;
       const int qrow = (i0 + j % nq_it) * 128 + r;
-#pragma unroll
-      for (int cc = 0; cc < D / 64; ++cc) {
-        const int col0 = hf * (D / 2) + cc * 32;
-        uint32_t rr[32];
-        tmem_ld_32x32(t_lane + DQ_COL + col0, rr);
+      {
+        const int col0 = cq * DC;
+        uint32_t rr[DC];
+        if (DC == 16) tmem_ld_32x16(t_lane + DQ_COL + col0, rr);
+        else tmem_ld_32x32(t_lane + DQ_COL + col0, rr);
         tmem_ld_wait();
         if (qrow < p.S && !(p.causal & 2)) {
           float* dst = p.dq_acc + ((size_t)b * p.S + qrow) * ((size_t)p.H * D) + hj * D + col0;
 #pragma unroll
-          for (int g = 0; g < 8; ++g)
+          for (int g = 0; g < DC / 4; ++g)
             asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + g * 4), "f"(__uint_as_float(rr[g * 4])),
                          "f"(__uint_as_float(rr[g * 4 + 1])), "f"(__uint_as_float(rr[g * 4 + 2])), "f"(__uint_as_float(rr[g * 4 + 3]))
                          : "memory");
@@ -255,34 +258,29 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // for the MMAs so that its latency is hidden): the inner loop then reads them as broadcast 16-byte loads
       float* stat = sStat + (it & 1) * 256;
       {
-        const int st = threadIdx.x - 64;  // 0..255 over the softmax warps
+        const int st = threadIdx.x - 64;  // 0..511 over the softmax warps: the first 256 fetch
         const int qi = min(q0 + (st & 127), p.S - 1);
-        stat[st] = (st < 128) ? __ldg(lse_row + qi) : __ldg(dl_row + qi);
+        if (st < 256) stat[st] = (st < 128) ? __ldg(lse_row + qi) : __ldg(dl_row + qi);
       }
       if (!mbar_wait_warp(s_full, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      asm volatile("bar.sync 1, 256;" ::: "memory");  // the statistics of this block are in place (softmax warps only)
+      asm volatile("bar.sync 1, 512;" ::: "memory");  // the statistics of this block are in place (softmax warps only)
       const bool need_mask = ((p.causal & 1) && q0 < k0 + 127) || (q0 + 128 > p.S) || (k0 + 128 > p.S);
       // both 32-column chunks of S^T and dP^T come in with four back-to-back TMEM loads and one wait; the columns
       // are handed back to the tensor core before the arithmetic starts, so the next block's first MMAs overlap it
-      uint32_t s_all[64], dp_all[64];
-      tmem_ld_32x32(t_lane + ST_COL + hf * 64, s_all);
-      tmem_ld_32x32(t_lane + DPT_COL + hf * 64, dp_all);
-      tmem_ld_32x32(t_lane + ST_COL + hf * 64 + 32, s_all + 32);
-      tmem_ld_32x32(t_lane + DPT_COL + hf * 64 + 32, dp_all + 32);
+      uint32_t s_all[32], dp_all[32];
+      tmem_ld_32x32(t_lane + ST_COL + cq * 32, s_all);
+      tmem_ld_32x32(t_lane + DPT_COL + cq * 32, dp_all);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_empty);  // one arrival per warp: arrivals on one mbarrier are serialised
-      uint32_t pk_all[2][16], dk_all[2][16];  // P^T and dS^T of this block as packed bf16 pairs, kept in registers until the
-                                              // shared-memory tiles are free
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int col0 = hf * 64 + cc * 32;
-        const uint32_t* s_r = s_all + cc * 32;
-        const uint32_t* dp_r = dp_all + cc * 32;
-        uint32_t* pk = pk_all[cc];
-        uint32_t* dk = dk_all[cc];
+      uint32_t pk[16], dk[16];  // P^T and dS^T of this thread's 32 columns as packed bf16 pairs, kept in registers until the
+                                // shared-memory tiles are free
+      {
+        const int col0 = cq * 32;
+        const uint32_t* s_r = s_all;
+        const uint32_t* dp_r = dp_all;
         if (!need_mask) {
           // interior block: no predicates, statistics fetched as 16-byte broadcast loads; one MUFU op and half a
           // conversion per element
@@ -327,13 +325,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tc_fence_after();
       }
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int chunk = (cc * 4 + g) ^ (r & 7);
-          *reinterpret_cast<uint4*>(pt_row + chunk * 16) = make_uint4(pk_all[cc][g * 4], pk_all[cc][g * 4 + 1], pk_all[cc][g * 4 + 2], pk_all[cc][g * 4 + 3]);
-          *reinterpret_cast<uint4*>(dst_row + chunk * 16) = make_uint4(dk_all[cc][g * 4], dk_all[cc][g * 4 + 1], dk_all[cc][g * 4 + 2], dk_all[cc][g * 4 + 3]);
-        }
+      for (int g = 0; g < 4; ++g) {
+        const int chunk = ((cq & 1) * 4 + g) ^ (r & 7);
+        *reinterpret_cast<uint4*>(pt_row + chunk * 16) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
+        *reinterpret_cast<uint4*>(dst_row + chunk * 16) = make_uint4(dk[g * 4], dk[g * 4 + 1], dk[g * 4 + 2], dk[g * 4 + 3]);
       }
       fence_proxy_async_smem();
       __syncwarp();
@@ -363,16 +358,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         __nv_bfloat16* outp = which == 0 ? p.dv : p.dk;
         const int ld = which == 0 ? p.ld_dv : p.ld_dk;
         const float sc = which == 0 ? 1.f : p.scale;
-#pragma unroll
-        for (int cc = 0; cc < D / 64; ++cc) {
-          const int col0 = hf * (D / 2) + cc * 32;
-          uint32_t rr[32];
-          tmem_ld_32x32(t_lane + colbase + col0, rr);
+        {
+          const int col0 = cq * DC;
+          uint32_t rr[DC];
+          if (DC == 16) tmem_ld_32x16(t_lane + colbase + col0, rr);
+          else tmem_ld_32x32(t_lane + colbase + col0, rr);
           tmem_ld_wait();
           if (key < p.S) {
             __nv_bfloat16* dst = outp + ((size_t)b * p.S + key) * ld + hk * D + col0;
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
+            for (int g = 0; g < DC / 8; ++g) {
               uint4 o;
               o.x = pack_bf16x2(__uint_as_float(rr[g * 8 + 0]) * sc, __uint_as_float(rr[g * 8 + 1]) * sc);
               o.y = pack_bf16x2(__uint_as_float(rr[g * 8 + 2]) * sc, __uint_as_float(rr[g * 8 + 3]) * sc);
