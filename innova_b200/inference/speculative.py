@@ -194,3 +194,108 @@ class SpeculativeDecoder:
 
     def theorem13(self, cost_ratio: float) -> Theorem13Result:
         return Theorem13Result.compute(self.stats.acceptance_rate, cost_ratio)
+
+
+@dataclass
+class RejectionStatsV2:
+    total_draft_tokens: int = 0
+    accepted_draft_tokens: int = 0
+    target_calls: int = 0
+    tokens_saved: int = 0            # tokens produced beyond one per target call
+    wall_time_sec: float = 0.0
+
+    @property
+    def acceptance_rate(self) -> float:
+        return self.accepted_draft_tokens / self.total_draft_tokens if self.total_draft_tokens else 0.0
+
+    @property
+    def tokens_saved_per_call(self) -> float:
+        return self.tokens_saved / self.target_calls if self.target_calls else 0.0
+
+
+class SpeculativeDecoderV2:
+    """Greedy speculative decoding over a tree of drafts (include/oil/inference_opt.h:248-298, ``SpeculativeDecoderV2``).
+
+    Each round the draft model proposes ``n_tree_candidates`` branches: its top-n tokens after the pending token, each
+    continued greedily for ``gamma`` - 1 tokens. The target scores all branches in ONE batched forward (one cache row per
+    branch; every row holds the same committed prefix) and the branch with the longest prefix of argmax matches wins, so
+    a miss on the draft's first choice still yields accepted tokens when a sibling matches. Both models keep their KV
+    caches between rounds: rows are rewound to the committed prefix and the tokens accepted in the last round are fed
+    again together with the next drafts (a few extra columns in a memory-bound forward) instead of copying KV pages
+    between rows. The output equals the target's own greedy decoding. With ``use_tree_attention`` off (or one candidate)
+    it verifies a single chain. Both generators need ``max_batch`` >= ``n_tree_candidates``."""
+
+    def __init__(self, draft: Generator, target: Generator, gamma: int = 5, n_tree_candidates: int = 4):
+        self.draft, self.target = draft, target
+        self.gamma, self.n_tree = int(gamma), int(n_tree_candidates)
+        self.use_tree_attn = True
+        self.stats = RejectionStatsV2()
+        assert min(draft.cache.max_batch, target.cache.max_batch) >= 1
+
+    def set_use_tree_attention(self, use: bool):
+        self.use_tree_attn = use
+
+    def use_tree_attention(self) -> bool:
+        return self.use_tree_attn
+
+    def reset_stats(self):
+        self.stats = RejectionStatsV2()
+
+    @torch.no_grad()
+    def generate(self, prompt, max_tokens: int = 64, eos_id: Optional[int] = None) -> List[int]:
+        import time
+        t0 = time.perf_counter()
+        tgt, drf = self.target, self.draft
+        n = min(self.n_tree, tgt.cache.max_batch, drf.cache.max_batch) if self.use_tree_attn else 1
+        rows = list(range(n))
+        for g in (tgt, drf):
+            for b in range(g.cache.max_batch):
+                g.cache.free(b)
+        ids = torch.as_tensor(prompt, dtype=torch.long).view(1, -1)
+        L = ids.shape[1]
+        logits = tgt._forward(ids.repeat(n, 1).to(tgt.device), [0] * n)
+        drf._forward(ids.repeat(n, 1).to(drf.device), [0] * n)
+        pending = int(logits[0].argmax())
+        out = [pending]
+        carry: List[int] = []               # accepted tokens whose KV is not yet in every row (both models)
+        while len(out) < max_tokens and (eos_id is None or out[-1] != eos_id):
+            G = max(1, min(self.gamma, max_tokens - len(out), tgt.max_seq - L - len(carry) - 2))
+            # ---- draft tree: n heads, greedy chains
+            feed = torch.tensor([carry + [pending]] * n, device=drf.device)
+            dl = drf._forward(feed, [L] * n)
+            heads = dl[0].float().topk(n).indices
+            branches = heads.view(n, 1)
+            d_len = L + feed.shape[1]
+            for _ in range(G - 1):
+                dl = drf._forward(branches[:, -1:].contiguous(), [d_len] * n)
+                d_len += 1
+                branches = torch.cat([branches, dl.argmax(-1, keepdim=True)], 1)
+            # ---- one target forward over all branches
+            base = len(carry) + 1
+            t_in = torch.cat([feed.to(tgt.device), branches.to(tgt.device)], 1)
+            tl = tgt._forward(t_in, [L] * n, all_logits=True)
+            pred = tl[:, base - 1:].argmax(-1)                         # [n, G + 1]: target's choice after pending, after each draft
+            match = (pred[:, :G] == branches.to(tgt.device)).long().cumprod(1).sum(1)
+            best = int(match.argmax())
+            k = int(match[best])
+            accepted = branches[best, :k].tolist()
+            nxt = int(pred[best, k])
+            # ---- commit what every row has in common, rewind the rest
+            L += base
+            for g in (tgt, drf):
+                for b in rows:
+                    g.cache.truncate(b, L)
+            carry = accepted
+            out.extend(accepted)
+            out.append(nxt)
+            pending = nxt
+            s = self.stats
+            s.total_draft_tokens += G
+            s.accepted_draft_tokens += k
+            s.target_calls += 1
+            s.tokens_saved += k
+            if eos_id is not None and eos_id in out[-(k + 1):]:
+                out = out[: len(out) - (k + 1) + out[-(k + 1):].index(eos_id) + 1]
+                break
+        self.stats.wall_time_sec += time.perf_counter() - t0
+        return out[:max_tokens]

@@ -124,3 +124,28 @@ def test_tensor_ops_cpu():
     y = T.batch_norm(x, torch.ones(6), torch.zeros(6))
     assert torch.allclose(y.mean(0), torch.zeros(6, 5), atol=1e-5)
     assert torch.allclose(T.gemv(x[0], x[0, 0]), x[0] @ x[0, 0])
+
+
+def test_speculative_decoder_v2_tree_equals_greedy_and_beats_a_single_chain():
+    from innova_b200.inference.generator import Generator
+    from innova_b200.inference.speculative import SpeculativeDecoderV2
+    from innova_b200.models import DenseModel, PRESETS
+    cfg = PRESETS["tiny"]()
+    target = DenseModel(cfg, dtype=torch.float32, device="cpu", seed=5)
+    draft = DenseModel(cfg, dtype=torch.float32, device="cpu", seed=6)
+    prompt = [1, 5, 9, 2, 7]
+    ref = Generator(target, kv_format="bf16").generate_tokens([prompt], 20)[0]
+    mk = lambda m: Generator(m, kv_format="bf16", max_batch=4)
+    tree = SpeculativeDecoderV2(mk(draft), mk(target), gamma=3, n_tree_candidates=4)
+    assert tree.generate(prompt, 20) == ref
+    chain = SpeculativeDecoderV2(mk(draft), mk(target), gamma=3, n_tree_candidates=4)
+    chain.set_use_tree_attention(False)
+    assert chain.generate(prompt, 20) == ref and not chain.use_tree_attention()
+    # siblings can only add matches: the tree needs no more target calls than the chain
+    assert tree.stats.target_calls <= chain.stats.target_calls and tree.stats.accepted_draft_tokens >= chain.stats.accepted_draft_tokens
+    own = SpeculativeDecoderV2(mk(target), mk(target), gamma=4, n_tree_candidates=2)
+    assert own.generate(prompt, 20) == ref and own.stats.acceptance_rate == 1.0
+    assert own.stats.tokens_saved_per_call > 2 and own.stats.wall_time_sec > 0
+    own.reset_stats()
+    assert own.stats.target_calls == 0
+    assert tree.generate(prompt, 20, eos_id=ref[6])[-1] == ref[6]
