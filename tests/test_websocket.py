@@ -1,0 +1,60 @@
+"""WebSocket framing, handshake, streaming and broadcast over loopback sockets (CPU)."""
+import json
+import time
+
+from innova_b200.serving.websocket import (OP_CLOSE, OP_PING, OP_PONG, OP_TEXT, ErrorCode, Result, WebSocketClient, WebSocketHandler,
+                                           compute_accept_key, create_frame, parse_frame)
+
+
+def test_accept_key_and_frames():
+    assert compute_accept_key("dGhlIHNhbXBsZSBub25jZQ==") == "s3pPLMBiTxaQ9kYGzzhZRbK+xOo="      # the example of RFC 6455
+    for n in (0, 5, 125, 126, 300, 70000):
+        data = bytes(i & 0xFF for i in range(n))
+        for mask in (None, b"\x01\x02\x03\x04"):
+            fr = create_frame(data, 0x2, mask)
+            payload, op, fin, used = parse_frame(fr + b"extra")
+            assert payload == data and op == 0x2 and fin and used == len(fr)
+            assert parse_frame(fr[:-1]) is None if n else True
+    assert create_frame("Hello")[:2] == b"\x81\x05" and parse_frame(b"\x81") is None
+
+
+def test_stream_ping_broadcast_close():
+    ws = WebSocketHandler(port=0)
+    ws.set_generate_callback(lambda prompt, n, stream: (f"{prompt}-{i} " for i in range(n)))
+    ws.start()
+    try:
+        assert ws.is_running() and ws.port > 0
+        a, b = WebSocketClient("127.0.0.1", ws.port), WebSocketClient("127.0.0.1", ws.port)
+        deadline = time.time() + 5
+        while ws.client_count() < 2 and time.time() < deadline:
+            time.sleep(0.01)
+        assert ws.client_count() == 2
+        a.send(json.dumps({"prompt": "tok", "max_tokens": 3}))
+        got = [a.recv() for _ in range(4)]
+        assert [p.decode() for _, p in got[:3]] == ["tok-0 ", "tok-1 ", "tok-2 "] and json.loads(got[3][1]) == {"done": True}
+        a.send("not json")
+        assert "error" in json.loads(a.recv()[1])
+        a.send(b"abc", OP_PING)
+        assert a.recv() == (OP_PONG, b"abc")
+        assert ws.broadcast("hello all") == 2
+        assert a.recv() == (OP_TEXT, b"hello all") and b.recv() == (OP_TEXT, b"hello all")
+        b.close()
+        deadline = time.time() + 5
+        while ws.client_count() > 1 and time.time() < deadline:
+            time.sleep(0.01)
+        assert ws.client_count() == 1 and ws.broadcast("x") == 1
+        big = "y" * 70000
+        a.send(json.dumps({"prompt": big, "max_tokens": 1}))
+        assert a.recv() == (OP_TEXT, b"x")
+        assert a.recv()[1].decode() == big + "-0 "
+    finally:
+        ws.stop()
+    assert not ws.is_running()
+
+
+def test_result_codes(tmp_path):
+    r, v = Result.wrap(open, str(tmp_path / "missing"))
+    assert r.code == ErrorCode.FILE_NOT_FOUND and not r.ok() and v is None
+    r, v = Result.wrap(int, "12")
+    assert r.ok() and v == 12
+    assert Result.wrap(int, "x")[0].code == ErrorCode.INVALID_ARGUMENT
