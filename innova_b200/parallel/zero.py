@@ -178,6 +178,108 @@ class ActivationCheckpointing:
 GradientCheckpointManager = ActivationCheckpointing
 
 
+class CheckpointMode:
+    NONE, FULL, PARTIAL, BALANCED = range(4)
+
+
+class MemoryBudget:
+    def __init__(self, total_bytes: int = 0, activation_bytes: int = 0, param_bytes: int = 0, grad_bytes: int = 0, opt_state_bytes: int = 0):
+        self.total_bytes, self.activation_bytes, self.param_bytes = total_bytes, activation_bytes, param_bytes
+        self.grad_bytes, self.opt_state_bytes = grad_bytes, opt_state_bytes
+
+    def usage_ratio(self) -> float:
+        return (self.activation_bytes + self.param_bytes + self.grad_bytes + self.opt_state_bytes) / max(1, self.total_bytes)
+
+    def activation_room(self) -> int:
+        """Bytes left for activations once parameters, gradients and optimizer states are placed (0 = unlimited budget)."""
+        return max(0, self.total_bytes - self.param_bytes - self.grad_bytes - self.opt_state_bytes) if self.total_bytes else 0
+
+
+class RegionInfo:
+    def __init__(self, name: str, forward_activations_bytes: int = 0, recompute_cost_flops: int = 0, mode: int = CheckpointMode.FULL):
+        self.name, self.forward_activations_bytes, self.recompute_cost_flops = name, forward_activations_bytes, recompute_cost_flops
+        self.mode, self.is_checkpointed = mode, mode != CheckpointMode.NONE
+
+
+class ActivationCheckpoint:
+    """Budget planner for activation recomputation (include/oil/zero_optimizer.h:337-410, src/zero_optimizer_mem.cpp:580-702).
+    Regions (usually one per transformer block) are declared with the bytes their forward pass would keep and the FLOPs a
+    recomputation costs. ``auto_place_checkpoints`` picks the regions to recompute so that the kept activations fit the
+    budget at the least extra compute: regions are taken in order of bytes saved per recomputed FLOP until the rest fits.
+    FULL keeps only a region's input, PARTIAL keeps ``partial_keep`` of its activations (e.g. the attention output and
+    the row statistics) and recomputes the remainder."""
+    partial_keep = 0.25
+
+    def __init__(self, budget: Optional[MemoryBudget] = None, input_bytes_per_region: int = 0):
+        self.budget = budget or MemoryBudget()
+        self.input_bytes = input_bytes_per_region
+        self.reset()
+
+    def reset(self):
+        self.regions: List[RegionInfo] = []
+        self._open: List[RegionInfo] = []
+        self.total_saved = self.total_recomputed = 0
+
+    def set_budget(self, budget: MemoryBudget):
+        self.budget = budget
+
+    def begin_region(self, name: str, mode: int = CheckpointMode.FULL, forward_activations_bytes: int = 0, recompute_cost_flops: int = 0):
+        self._open.append(RegionInfo(name, forward_activations_bytes, recompute_cost_flops, mode))
+
+    def end_region(self):
+        r = self._open.pop()
+        self.regions.append(r)
+        if r.is_checkpointed:
+            self.total_saved += self.estimated_savings(r)
+            self.total_recomputed += r.recompute_cost_flops
+
+    def in_checkpoint_region(self) -> bool:
+        return bool(self._open) and self._open[-1].is_checkpointed
+
+    @staticmethod
+    def estimate_layer_activations(B: int, N: int, H: int, D: int, ffn_mult: float = 4.0, elem: int = 2) -> int:
+        """Bytes one pre-norm block keeps for its backward pass with flash attention (no N x N matrix): two norm inputs,
+        QKV, the attention output, the two FFN inputs and the gated hidden state, plus the fp32 row statistics."""
+        E = H * D
+        return int(B * N * (E * (2 + 3 + 1 + 1) + 3 * ffn_mult * E) * elem + B * H * N * 4 * 2)
+
+    def estimated_savings(self, r: RegionInfo) -> int:
+        if r.mode == CheckpointMode.NONE:
+            return 0
+        kept = self.partial_keep * r.forward_activations_bytes if r.mode == CheckpointMode.PARTIAL else 0
+        return max(0, int(r.forward_activations_bytes - kept - self.input_bytes))
+
+    def estimated_savings_all(self) -> int:
+        return sum(self.estimated_savings(r) for r in self.regions if r.is_checkpointed)
+
+    def compute_overhead(self) -> float:
+        """Recomputed FLOPs over the forward FLOPs of all regions (0.33 of a step's total when everything is recomputed)."""
+        tot = sum(r.recompute_cost_flops for r in self.regions)
+        return sum(r.recompute_cost_flops for r in self.regions if r.is_checkpointed) / tot if tot else 0.0
+
+    def should_checkpoint(self, r: RegionInfo) -> bool:
+        room = self.budget.activation_room()
+        return bool(room) and sum(x.forward_activations_bytes for x in self.regions) > room and r.forward_activations_bytes > self.input_bytes
+
+    def auto_place_checkpoints(self) -> List[str]:
+        room = self.budget.activation_room()
+        for r in self.regions:
+            r.is_checkpointed, r.mode = False, CheckpointMode.NONE
+        need = sum(r.forward_activations_bytes for r in self.regions) - room if room else 0
+        chosen: List[str] = []
+        full = lambda r: max(0, r.forward_activations_bytes - self.input_bytes)
+        for r in sorted(self.regions, key=lambda r: -full(r) / max(1, r.recompute_cost_flops)):
+            if need <= 0:
+                break
+            r.is_checkpointed, r.mode = True, CheckpointMode.FULL
+            need -= full(r)
+            chosen.append(r.name)
+        self.total_saved = self.estimated_savings_all()
+        self.total_recomputed = sum(r.recompute_cost_flops for r in self.regions if r.is_checkpointed)
+        self.budget.activation_bytes = sum(r.forward_activations_bytes for r in self.regions) - self.total_saved
+        return chosen
+
+
 # ---------------------------------------------------------------------------------------------- CPU offload
 class CPUOffloadEngine:
     """Pinned host pool with asynchronous copies on a side stream: ``offload`` starts a device->host copy and

@@ -105,3 +105,24 @@ def test_dense_bf16_goes_through_the_flash_kernel_and_matches_the_tiled_path():
     win = MemoryEfficientAttention(MEAConfig(use_block_sparse=True, block_sparse_window=96))(Q, K, V)
     i, j = torch.arange(N, device="cuda")[:, None], torch.arange(N, device="cuda")[None, :]
     assert (win.float() - dense(Q.float(), K.float(), V.float(), (j <= i) & (i - j < 96))).abs().max() < 3e-2
+
+
+def test_activation_checkpoint_budget_planner():
+    from innova_b200.parallel.zero import ActivationCheckpoint, CheckpointMode, MemoryBudget
+    per = ActivationCheckpoint.estimate_layer_activations(B=2, N=4096, H=40, D=128, ffn_mult=2.7)
+    assert 1.0e9 < per < 1.6e9                                    # ~1.3 GB per 13B-shaped block at 8192 tokens
+    inp = 2 * 4096 * 5120 * 2
+    plan = ActivationCheckpoint(MemoryBudget(total_bytes=40 * per // 2 + 10 ** 9, param_bytes=10 ** 9), input_bytes_per_region=inp)
+    for i in range(40):
+        plan.begin_region(f"block{i}", CheckpointMode.NONE, per, recompute_cost_flops=(2 if i % 2 else 1) * 10 ** 12)
+        assert not plan.in_checkpoint_region()
+        plan.end_region()
+    assert plan.compute_overhead() == 0.0 and plan.should_checkpoint(plan.regions[0])
+    chosen = plan.auto_place_checkpoints()
+    kept = 40 * per - plan.estimated_savings_all()
+    assert kept <= plan.budget.activation_room() and plan.budget.usage_ratio() <= 1.0
+    assert 20 <= len(chosen) <= 22 and all(int(n[5:]) % 2 == 0 for n in chosen[:20])      # the cheap-to-recompute blocks go first
+    assert 0.0 < plan.compute_overhead() < 0.5
+    roomy = ActivationCheckpoint(MemoryBudget(total_bytes=0))
+    roomy.begin_region("a", CheckpointMode.PARTIAL, 1000, 10); roomy.end_region()
+    assert roomy.estimated_savings_all() == 750 and roomy.auto_place_checkpoints() == []
