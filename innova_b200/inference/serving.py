@@ -373,6 +373,81 @@ def attention_reference(q, k, v, n_kv_heads: Optional[int] = None, window: int =
     return torch.einsum("hqk,hkd->hqd", torch.softmax(s, -1), v2.float())
 
 
+def flash_decoding(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, n_splits: int = 4, lengths: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode attention of one new token per sequence with the keys cut into ``n_splits`` ranges that are reduced
+    independently and merged by their log-sum-exp (include/oil/inference_opt.h ``flash_decoding``): q [B, H, D],
+    k / v [B, Hkv, S, D], optional valid ``lengths`` [B]. This is the host-side statement of what the paged decode kernel
+    does with its split grid (``csrc/paged_attn.cu``); a long context keeps all SMs busy at batch 1."""
+    B, H, D = q.shape
+    Hkv, S = k.shape[1], k.shape[2]
+    g = H // Hkv
+    k2, v2 = k.repeat_interleave(g, 1).float(), v.repeat_interleave(g, 1).float()
+    s = torch.einsum("bhd,bhsd->bhs", q.float(), k2) * D ** -0.5
+    if lengths is not None:
+        s = s.masked_fill(torch.arange(S, device=q.device).view(1, 1, S) >= lengths.view(B, 1, 1), float("-inf"))
+    bounds = [S * i // n_splits for i in range(n_splits + 1)]
+    parts, lses = [], []
+    for lo, hi in zip(bounds[:-1], bounds[1:]):
+        if hi == lo:
+            continue
+        seg = s[..., lo:hi]
+        m = seg.amax(-1, keepdim=True)
+        safe = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+        p = torch.exp(seg - safe)
+        l = p.sum(-1, keepdim=True)
+        parts.append(torch.einsum("bhs,bhsd->bhd", p, v2[:, :, lo:hi]) / l.clamp_min(1e-30))
+        lses.append((safe + torch.log(l.clamp_min(1e-30))).masked_fill(l == 0, float("-inf")))
+    w = torch.softmax(torch.cat(lses, -1), -1)                       # [B, H, splits]
+    return torch.einsum("bhn,nbhd->bhd", w, torch.stack(parts)).to(q.dtype)
+
+
+class GroupedQueryAttention:
+    """``n_kv_heads`` key/value heads shared by groups of query heads (include/oil/inference_opt.h:321-339)."""
+
+    def __init__(self, n_heads: int, n_kv_heads: int, head_dim: int, window: int = 0, alibi: bool = False):
+        assert n_heads % n_kv_heads == 0
+        self.n_heads, self.n_kv_heads, self.head_dim, self.window, self.alibi = n_heads, n_kv_heads, head_dim, window, alibi
+
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        """q [H, Sq, D], k / v [Hkv, Sk, D] (causal; the queries are the last Sq positions)."""
+        return attention_reference(q, k, v, self.n_kv_heads, self.window, self.alibi)
+
+    __call__ = forward
+
+    def kv_bytes_per_token(self, elem: int = 2) -> int:
+        return 2 * self.n_kv_heads * self.head_dim * elem
+
+
+class MultiQueryAttention(GroupedQueryAttention):
+    """One key/value head for all query heads (include/oil/inference_opt.h:303-319)."""
+
+    def __init__(self, n_heads: int, head_dim: int):
+        super().__init__(n_heads, 1, head_dim)
+
+
+class SlidingWindowAttention(GroupedQueryAttention):
+    """Each query sees the last ``window`` keys only (include/oil/inference_opt.h:341-356); the cache may drop the rest."""
+
+    def __init__(self, n_heads: int, head_dim: int, window: int, n_kv_heads: Optional[int] = None):
+        super().__init__(n_heads, n_kv_heads or n_heads, head_dim, window=window)
+
+    def trim_cache(self, k: torch.Tensor, v: torch.Tensor):
+        return k[:, -self.window:], v[:, -self.window:]
+
+
+class ALiBi(GroupedQueryAttention):
+    """Linear distance bias per head instead of position embeddings (include/oil/inference_opt.h:358-372)."""
+
+    def __init__(self, n_heads: int, head_dim: int, n_kv_heads: Optional[int] = None):
+        super().__init__(n_heads, n_kv_heads or n_heads, head_dim, alibi=True)
+
+    def slopes(self) -> torch.Tensor:
+        return alibi_slopes(self.n_heads)
+
+    def bias(self, q_len: int, k_len: int) -> torch.Tensor:
+        return alibi_bias(self.n_heads, q_len, k_len)
+
+
 # ---------------------------------------------------------------------------------------------- quantised inference
 class INT8Inference:
     """Per-row absmax int8 weights, dequantised on the fly."""

@@ -126,3 +126,25 @@ def test_activation_checkpoint_budget_planner():
     roomy = ActivationCheckpoint(MemoryBudget(total_bytes=0))
     roomy.begin_region("a", CheckpointMode.PARTIAL, 1000, 10); roomy.end_region()
     assert roomy.estimated_savings_all() == 750 and roomy.auto_place_checkpoints() == []
+
+
+def test_flash_decoding_and_attention_variant_classes():
+    from innova_b200.inference.serving import (ALiBi, GroupedQueryAttention, MultiQueryAttention, SlidingWindowAttention, attention_reference,
+                                               flash_decoding)
+    torch.manual_seed(0)
+    B, H, Hkv, S, D = 3, 8, 2, 77, 16
+    q, k, v = torch.randn(B, H, D), torch.randn(B, Hkv, S, D), torch.randn(B, Hkv, S, D)
+    lens = torch.tensor([77, 40, 5])
+    ref = torch.stack([attention_reference(q[b][:, None], k[b][:, :lens[b]], v[b][:, :lens[b]])[:, 0] for b in range(B)])
+    for n in (1, 4, 16):
+        assert torch.allclose(flash_decoding(q, k, v, n, lens), ref, atol=1e-5)
+    qs, ks, vs = torch.randn(H, 10, D), torch.randn(Hkv, 30, D), torch.randn(Hkv, 30, D)
+    assert torch.allclose(GroupedQueryAttention(H, Hkv, D)(qs, ks, vs), attention_reference(qs, ks, vs))
+    mqa = MultiQueryAttention(H, D)
+    assert mqa(qs, ks[:1], vs[:1]).shape == (H, 10, D) and mqa.kv_bytes_per_token() == 2 * D * 2
+    sw = SlidingWindowAttention(H, D, window=6, n_kv_heads=Hkv)
+    kt, vt = sw.trim_cache(ks, vs)
+    assert kt.shape[1] == 6 and torch.allclose(sw(qs[:, -1:], ks, vs), sw(qs[:, -1:], kt, vt), atol=1e-6)   # older keys do not matter
+    al = ALiBi(H, D, Hkv)
+    assert al.slopes().shape == (H,) and al.bias(10, 30).shape == (H, 10, 30)
+    assert not torch.allclose(al(qs, ks, vs), attention_reference(qs, ks, vs))
