@@ -348,3 +348,103 @@ class ExpertParallelEngine:
         FlatParamEngineStep = type(self.exp).step
         FlatParamEngineStep(self.rep, gs, total)        # skip the DDP engine's own sync: already done above
         self.exp.step(gs, total)
+
+
+# ---------------------------------------------------------------------------------------------- micro-batch pipeline
+class PipelineStage:
+    def __init__(self, stage_id: int, fn):
+        self.stage_id, self.fn = stage_id, fn
+        self.forward_done = self.backward_done = 0
+        self.busy_steps = 0
+
+
+class PipelineScheduler:
+    """Software pipeline over the stages of an expert-parallel layer (include/oil/expert_parallel.h:193-228; the usual
+    stages are route + dispatch, expert FFN, combine): micro-batch m runs stage s at step m + s, so the token exchange of
+    one micro-batch overlaps the expert GEMMs of the previous one. On a GPU every stage owns a CUDA stream and the
+    hand-over between stages is an event, so the overlap is real; on the CPU the same order runs sequentially.
+    ``schedule_forward`` / ``schedule_backward`` queue work, ``execute_pipeline`` drains it and returns the outputs in
+    micro-batch order; ``timeline`` records (step, stage, micro-batch, direction) for inspection."""
+
+    def __init__(self, stage_fns, micro_batch_size: int = 0, backward_fns=None, device=None):
+        self.stages = [PipelineStage(i, f) for i, f in enumerate(stage_fns)]
+        self.backward_fns = list(backward_fns) if backward_fns is not None else None
+        self.num_stages, self.micro_batch_size = len(self.stages), micro_batch_size
+        self.device = torch.device(device) if device is not None else None
+        self.cuda = self.device is not None and self.device.type == "cuda"
+        self.streams = [torch.cuda.Stream(self.device) for _ in self.stages] if self.cuda else None
+        self.reset()
+
+    def reset(self):
+        self._fwd, self._bwd = [], []
+        self.timeline = []
+        self.current_step = self.total_steps = 0
+        for s in self.stages:
+            s.forward_done = s.backward_done = s.busy_steps = 0
+
+    def schedule_forward(self, x, stage_id: int = 0):
+        assert stage_id == 0, "forward work enters at the first stage"
+        self._fwd.append(x)
+
+    def schedule_backward(self, grad_output, stage_id: Optional[int] = None):
+        assert self.backward_fns is not None
+        self._bwd.append(grad_output)
+
+    def split(self, x: torch.Tensor):
+        """Queues ``x`` in micro-batches of ``micro_batch_size`` rows."""
+        for part in x.split(self.micro_batch_size or x.shape[0], 0):
+            self.schedule_forward(part)
+
+    def get_stage(self, stage_id: int) -> PipelineStage:
+        return self.stages[stage_id]
+
+    def all_stages_done(self) -> bool:
+        return not self._fwd and not self._bwd and self.current_step >= self.total_steps
+
+    def _drain(self, items, fns, direction):
+        S, M = len(fns), len(items)
+        vals = list(items)
+        events = [None] * M
+        self.total_steps += M + S - 1 if M else 0
+        for step in range(M + S - 1 if M else 0):
+            for s in range(S):
+                m = step - s
+                if not 0 <= m < M:
+                    continue
+                st = self.stages[s if direction == "fwd" else S - 1 - s]
+                if self.cuda:
+                    stream = self.streams[st.stage_id]
+                    if events[m] is not None:
+                        stream.wait_event(events[m])
+                    else:
+                        stream.wait_stream(torch.cuda.current_stream(self.device))
+                    with torch.cuda.stream(stream):
+                        vals[m] = fns[s](vals[m])
+                        events[m] = torch.cuda.Event()
+                        events[m].record(stream)
+                else:
+                    vals[m] = fns[s](vals[m])
+                st.busy_steps += 1
+                if direction == "fwd":
+                    st.forward_done += 1
+                else:
+                    st.backward_done += 1
+                self.timeline.append((self.current_step, st.stage_id, m, direction))
+            self.current_step += 1
+        if self.cuda:
+            for e in events:
+                if e is not None:
+                    torch.cuda.current_stream(self.device).wait_event(e)
+        return vals
+
+    def execute_pipeline(self):
+        """-> (forward outputs, backward outputs), each in the order the work was queued."""
+        f, self._fwd = self._fwd, []
+        outs = self._drain(f, [s.fn for s in self.stages], "fwd")
+        b, self._bwd = self._bwd, []
+        grads = self._drain(b, list(reversed(self.backward_fns)), "bwd") if self.backward_fns is not None and b else []
+        return outs, grads
+
+    def utilisation(self) -> float:
+        """Busy stage-steps over stage-steps: M / (M + S - 1) per drained direction (the pipeline bubble)."""
+        return sum(s.busy_steps for s in self.stages) / max(1, self.total_steps * self.num_stages)

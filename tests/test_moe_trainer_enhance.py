@@ -149,3 +149,26 @@ def test_pruner_dropout_merger_capacity_pool():
     assert pool.remove_expert(2) and pool.count() == 2 and torch.allclose(pool(x), y2, atol=1e-6) and not pool.remove_expert(7)
     pool(x).sum().backward()
     assert pool.router.grad is not None
+
+
+def test_ep_pipeline_scheduler_order_and_results():
+    from innova_b200.parallel.expert_parallel import PipelineScheduler
+    fns = [lambda x: x + 1, lambda x: x * 2, lambda x: x - 3]
+    bfn = [lambda g: g * 1.0, lambda g: g * 2.0, lambda g: g * 1.0]       # derivatives of the three stages
+    ps = PipelineScheduler(fns, micro_batch_size=2, backward_fns=bfn)
+    x = torch.arange(8.0).view(8, 1)
+    ps.split(x)
+    for _ in range(4):
+        ps.schedule_backward(torch.ones(2, 1))
+    assert not ps.all_stages_done()
+    outs, grads = ps.execute_pipeline()
+    assert torch.equal(torch.cat(outs), (x + 1) * 2 - 3) and all(torch.equal(g, torch.full((2, 1), 2.0)) for g in grads)
+    fwd = [t for t in ps.timeline if t[3] == "fwd"]
+    # micro-batch m reaches stage s at step m + s; within a step later stages (older micro-batches) are not starved
+    assert all(step == m + s for step, s, m, _ in fwd) and len(fwd) == 12
+    assert {(s, m) for step, s, m, _ in fwd if step == 2} == {(0, 2), (1, 1), (2, 0)}
+    bwd = [t for t in ps.timeline if t[3] == "bwd"]
+    assert bwd[0][1] == 2 and ps.get_stage(1).forward_done == 4 and ps.get_stage(1).backward_done == 4
+    assert ps.all_stages_done() and abs(ps.utilisation() - 4 / 6) < 1e-9
+    ps.reset()
+    assert ps.timeline == [] and ps.execute_pipeline() == ([], [])
