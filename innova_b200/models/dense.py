@@ -167,7 +167,8 @@ class DenseModel(nn.Module):
         w = _ste(self.lm_head.weight, self.cfg)
         if labels is None:
             return ops.linear(h, w)[..., : self.cfg.vocab_size]
-        return ops.lm_head_cross_entropy(h, w, labels, vocab=self.cfg.vocab_size, grad_scale=grad_scale)
+        return ops.lm_head_cross_entropy(h, w, labels, vocab=self.cfg.vocab_size, grad_scale=grad_scale,
+                                         smoothing=getattr(self, "label_smoothing", 0.0) if self.training else 0.0)
 
     def num_params(self):
         return sum(p.numel() for p in self.parameters())

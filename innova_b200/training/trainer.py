@@ -89,6 +89,8 @@ class Trainer:
         self.global_step = 0
         self._micro = 0
         self.device = next(model.parameters()).device
+        if c.label_smoothing > 0:
+            model.label_smoothing = c.label_smoothing      # read by the model's fused LM-head loss in training mode
 
     def add_callback(self, fn):
         self.callbacks.append(fn)

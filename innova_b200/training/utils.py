@@ -479,3 +479,24 @@ class ScalarLogWriter:
 
     def close(self):
         self.f.close()
+
+
+# ---------------------------------------------------------------------------------------------- R-Drop
+def r_drop_loss(logits_a: torch.Tensor, logits_b: torch.Tensor, labels: torch.Tensor, alpha: float = 1.0, label_smoothing: float = 0.0,
+                ignore_index: int = -100) -> torch.Tensor:
+    """Regularised-dropout objective of the reference trainer (src/trainer_core.cpp:519-544): the mean cross entropy of two
+    stochastic forward passes over the same batch plus ``alpha`` times their symmetric KL divergence."""
+    import torch.nn.functional as F
+    V = logits_a.shape[-1]
+    a, b, t = logits_a.reshape(-1, V).float(), logits_b.reshape(-1, V).float(), labels.reshape(-1)
+    ce = 0.5 * (F.cross_entropy(a, t, ignore_index=ignore_index, label_smoothing=label_smoothing)
+                + F.cross_entropy(b, t, ignore_index=ignore_index, label_smoothing=label_smoothing))
+    keep = t != ignore_index
+    la, lb = F.log_softmax(a[keep], -1), F.log_softmax(b[keep], -1)
+    kl = 0.5 * ((la.exp() * (la - lb)).sum(-1) + (lb.exp() * (lb - la)).sum(-1)).mean() if keep.any() else a.new_zeros(())
+    return ce + alpha * kl
+
+
+def r_drop_step(model, ids: torch.Tensor, labels: torch.Tensor, alpha: float = 1.0, label_smoothing: float = 0.0) -> torch.Tensor:
+    """Two forward passes of ``model(ids)`` (logits) in training mode, combined by ``r_drop_loss``."""
+    return r_drop_loss(model(ids), model(ids), labels, alpha, label_smoothing)
