@@ -193,3 +193,16 @@ def dump(argv=None):
 
 if __name__ == "__main__":
     sys.exit(dump())
+
+
+def import_main(argv=None):
+    """oil-import: the funnel of the adapters edition (safetensors / GGUF / raw fp32-fp16-bf16-fp8 -> mixed-format .oil with
+    norms and biases kept in OIL32 and embeddings never below 4 bits); same flags as oil-convert."""
+    from .convert import main
+    return main(argv)
+
+
+def ptq(argv=None):
+    """oil-ptq: post-training quantisation of an existing .oil to one wire format (per-layer overrides); flags of oil-quantize."""
+    from .quantize import main
+    return main(argv)

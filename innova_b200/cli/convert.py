@@ -120,6 +120,20 @@ def read_safetensors(path):
     return out
 
 
+def read_raw(path, dtype="fp32") -> torch.Tensor:
+    """A flat file of little-endian fp32 / fp16 / bf16 / fp8-e4m3 values -> fp32 tensor."""
+    if dtype == "fp32":
+        return torch.from_numpy(np.fromfile(path, dtype="<f4"))
+    if dtype == "fp16":
+        return torch.from_numpy(np.fromfile(path, dtype="<f2").astype(np.float32))
+    raw = np.fromfile(path, dtype=np.uint8)
+    if dtype == "bf16":
+        return torch.from_numpy(raw[: raw.size // 2 * 2].copy()).view(torch.bfloat16).float()
+    if dtype == "fp8":
+        return torch.from_numpy(raw.copy()).view(torch.float8_e4m3fn).float()
+    raise ValueError(dtype)
+
+
 def plan_for(name, t, target_bpw, to_format, per_layer, verbose=False):
     from ..formats import oil, registry
     for key, f in per_layer.items():
@@ -148,6 +162,8 @@ def main(argv=None):
     ap.add_argument("--to", default="", help="encode every matrix in this wire format instead of planning by bpw")
     ap.add_argument("--per-layer", default="", help="name=FORMAT,... overrides by substring")
     ap.add_argument("--num-bits", type=int, default=0, help="shorthand for --to OIL<bits>")
+    ap.add_argument("--raw-dtype", default="fp32", choices=["fp32", "fp16", "bf16", "fp8"], help="element type of a raw input file (fp8 = e4m3)")
+    ap.add_argument("--dedup", action="store_true", help="store tensors with identical content once (tied embeddings / LM head)")
     ap.add_argument("--verbose", action="store_true")
     a = ap.parse_args(argv)
     from ..formats import export, oil
@@ -163,12 +179,12 @@ def main(argv=None):
             config = r.config
             tensors = {n: r.read_tensor(n) for n in r.tensor_names()}
     else:
-        tensors = {"weights": torch.from_numpy(np.fromfile(a.input, dtype="<f4"))}
+        tensors = {"weights": read_raw(a.input, a.raw_dtype)}
     to = a.to or (f"OIL{a.num_bits}" if a.num_bits else "")
     per_layer = dict(kv.split("=") for kv in a.per_layer.split(",") if "=" in kv)
     w = oil.OILWriter(a.output, version=1, config=config)
     for name, t in tensors.items():
-        w.add_tensor(name, t, plan_for(name, t, a.bpw, to, per_layer, a.verbose))
+        (w.add_tensor_dedup if a.dedup else w.add_tensor)(name, t, plan_for(name, t, a.bpw, to, per_layer, a.verbose))
     payload = w.payload_bytes()
     w.close(write_index=True)
     total = sum(t.numel() for t in tensors.values())

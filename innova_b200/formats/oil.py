@@ -7,6 +7,7 @@ src/oil_format.cpp:196-482,540-622; codec src/block_codec.cpp:368-720; ids inclu
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Dict, Iterable, List, Optional, Sequence, Union
 
 import numpy as np
@@ -140,6 +141,23 @@ class OILWriter:
             raise ValueError(f"add_tensor({name}) failed: {rc}")
         self.names.append(name)
 
+    def add_tensor_dedup(self, name: str, data, fmt: Union[int, str, Sequence] = "OIL32", block: int = DEFAULT_BLOCK) -> str:
+        """Content-addressed variant (the reference's ``OILWriter::write_dedup`` keys blobs by the hex SHA-256 of their
+        bytes, src/oil_format.cpp:240-260): a tensor whose fp32 content and format equal an earlier one (tied embedding and
+        LM head, shared experts) is not stored again. Returns the name that holds the data; aliases go to a JSON sidecar
+        ``<path>.alias.json`` on ``close`` and ``OILReader`` resolves them."""
+        a = _f32(data)
+        key = sha256(a.tobytes()).hex() + "|" + (str(fmt) if isinstance(fmt, (int, str)) else ",".join(map(str, fmt))) + f"|{block}"
+        if not hasattr(self, "_digests"):
+            self._digests, self.aliases = {}, {}
+        first = self._digests.get(key)
+        if first is not None:
+            self.aliases[name] = first
+            return first
+        self.add_tensor(name, a, fmt, block)
+        self._digests[key] = name
+        return name
+
     def payload_bytes(self) -> int:
         return int(lib().oilw_payload_bytes(self._h))
 
@@ -152,6 +170,10 @@ class OILWriter:
             raise IOError(f"writing {self.path} failed: {rc}")
         if write_index:
             write_idx(self.path + "idx" if self.path.endswith(".oil") else self.path + ".oilidx", self.names)
+        if getattr(self, "aliases", None):
+            import json
+            with open(self.path + ".alias.json", "w") as f:
+                json.dump(self.aliases, f)
 
     def __enter__(self):
         return self
@@ -177,6 +199,13 @@ class OILReader:
         self.tensors: Dict[str, int] = {}
         for i in range(L.oilr_num_tensors(self._h)):
             self.tensors[L.oilr_tensor_name(self._h, i).decode()] = i
+        self.aliases: Dict[str, str] = {}
+        if os.path.exists(self.path + ".alias.json"):          # names stored once by ``OILWriter.add_tensor_dedup``
+            import json
+            with open(self.path + ".alias.json") as f:
+                self.aliases = {a: t for a, t in json.load(f).items() if t in self.tensors}
+            for a, t in self.aliases.items():
+                self.tensors[a] = self.tensors[t]
 
     def tensor_names(self) -> List[str]:
         return list(self.tensors)

@@ -96,3 +96,40 @@ def test_adapters_edition_tools(tiny):
     chat_out = io.StringIO()
     assert T.chat([adapted, "--max-tokens", "4", "--greedy", "--device", "cpu"], stdin=io.StringIO("the quick\n/reset\nbrown\n/quit\n"), stdout=chat_out) == 0
     assert len(chat_out.getvalue().splitlines()) >= 2
+
+
+def test_import_raw_dtypes_dedup_and_ptq(tmp_path, capsys):
+    import json
+    import numpy as np
+    import torch
+    from innova_b200.cli import adapters_tools
+    from innova_b200.cli.convert import read_raw
+    from innova_b200.formats import oil
+    w = torch.randn(8192)
+    for dt, tol in (("fp16", 1e-3), ("bf16", 1e-2), ("fp8", 0.07)):
+        p = str(tmp_path / f"w.{dt}")
+        t = {"fp16": w.half(), "bf16": w.bfloat16(), "fp8": w.to(torch.float8_e4m3fn)}[dt]
+        t.view(torch.uint8).numpy().tofile(p)
+        back = read_raw(p, dt)
+        assert back.shape == w.shape and float((back - w).abs().max() / w.abs().max()) < tol
+    src = str(tmp_path / "w.fp16")
+    out = str(tmp_path / "m.oil")
+    assert adapters_tools.import_main(["--input", src, "--output", out, "--raw-dtype", "fp16", "--to", "OIL8"]) == 0
+    info = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert info["weights"] == 8192 and info["bpw"] < 10
+    # identical tensors are stored once and read back under both names
+    p2 = str(tmp_path / "tied.oil")
+    wr = oil.OILWriter(p2)
+    assert wr.add_tensor_dedup("tok_embeddings.weight", w, "OIL8") == "tok_embeddings.weight"
+    one = wr.payload_bytes()
+    assert wr.add_tensor_dedup("lm_head.weight", w.clone(), "OIL8") == "tok_embeddings.weight" and wr.payload_bytes() == one
+    assert wr.add_tensor_dedup("other", w + 1, "OIL8") == "other" and wr.payload_bytes() > one
+    assert wr.add_tensor_dedup("same_data_other_format", w, "OIL4") == "same_data_other_format"
+    wr.close()
+    with oil.OILReader(p2) as r:
+        assert r.aliases == {"lm_head.weight": "tok_embeddings.weight"}
+        assert torch.equal(r.read_tensor("lm_head.weight"), r.read_tensor("tok_embeddings.weight")) and "lm_head.weight" in r.tensor_names()
+    q = str(tmp_path / "q.oil")
+    assert adapters_tools.ptq(["--input", out, "--output", q, "--format", "OIL4"]) == 0
+    with oil.OILReader(q) as r:
+        assert r.numel("weights") == 8192
