@@ -9,7 +9,7 @@ gradient. CUDA tensors run ``csrc/quant.cu``; CPU tensors run the same arithmeti
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -209,3 +209,52 @@ def pack_nibbles(idx: torch.Tensor) -> torch.Tensor:
 def snr_db(w: torch.Tensor, q: torch.Tensor) -> float:
     err = (w.float() - q.float()).pow(2).sum().clamp(min=1e-30)
     return float(10 * torch.log10(w.float().pow(2).sum() / err))
+
+
+class STEQuantizer:
+    """The reference's ``STEQuantizer`` object (src/ste_quantizer.cpp:19-66,145-238): ``forward(w, fmt)`` is
+    quantise -> dequantise with an identity gradient; OIL8 / OIL4 use one codebook per format for the whole process,
+    trained (Lloyd) on the first tensor that is passed and reused afterwards; the ternary format thresholds at half the
+    block's maximum; ``forward_mixed`` gives every block of ``block`` weights its own format and, for the codebook formats,
+    a codebook fitted to that block alone. ``use_ste = False`` returns the weights untouched (``TrainConfig::use_ste``)."""
+    _static: dict = {}
+
+    def __init__(self, block: int = BLOCK, use_ste: bool = True, train_iters: int = 20):
+        self.block, self.use_ste, self.train_iters = block, use_ste, train_iters
+
+    @classmethod
+    def reset_static_codebooks(cls):
+        cls._static.clear()
+
+    def codebook(self, w: torch.Tensor, fmt: str) -> Optional[torch.Tensor]:
+        if fmt not in ("oil8", "oil4"):
+            return None
+        key = (fmt, str(w.device))
+        if key not in self._static:
+            self._static[key] = train_codebook(w.detach().float(), fmt, self.block, self.train_iters)
+        return self._static[key]
+
+    def forward(self, w: torch.Tensor, fmt: str = "oil8") -> torch.Tensor:
+        if not self.use_ste:
+            return w
+        return ste_fake_quant(w, fmt, self.block, self.codebook(w, fmt))
+
+    __call__ = forward
+
+    def forward_mixed(self, w: torch.Tensor, formats: Sequence[str], block: int = 256) -> torch.Tensor:
+        """``formats[b]`` in {"oil8", "oil4", "spark", "oil1", "fp32"} for block b of ``block`` consecutive weights."""
+        if not self.use_ste:
+            return w
+        flat = w.reshape(-1)
+        nb = (flat.numel() + block - 1) // block
+        assert len(formats) == nb, f"{nb} blocks need {nb} formats"
+        parts = []
+        for b, fmt in enumerate(formats):
+            seg = flat[b * block:(b + 1) * block]
+            if fmt in ("fp32", "oil32", "OIL32"):
+                parts.append(seg)
+                continue
+            sub = min(self.block, seg.numel())
+            cb = train_codebook(seg.detach().float(), fmt, sub, self.train_iters) if fmt in ("oil8", "oil4") else None
+            parts.append(ste_fake_quant(seg, fmt, sub, cb))
+        return torch.cat(parts).view(w.shape)

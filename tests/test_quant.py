@@ -137,3 +137,29 @@ def test_gpu_fused_finish_matches_unfused(M):
     assert float((h.float() - h_ref.float()).abs().max()) <= 3e-2 * float(h_ref.float().abs().max())
     # the accumulator is left clean by every finish variant
     assert torch.equal(oil_linear(x, qw, res), y_ref) or float((oil_linear(x, qw, res).float() - y_ref.float()).abs().max()) < 1e-1
+
+
+def test_ste_quantizer_static_codebook_and_mixed_blocks():
+    from innova_b200.ops.quant import STEQuantizer, default_codebook
+    STEQuantizer.reset_static_codebooks()
+    torch.manual_seed(0)
+    q = STEQuantizer()
+    w1 = torch.randn(4096) * 0.02
+    y1 = q(w1, "oil4")
+    cb = q.codebook(w1, "oil4")
+    assert cb.numel() == 16 and not torch.allclose(cb, default_codebook("oil4"))          # trained on the first tensor
+    w2 = torch.rand(4096)                                                                   # another distribution: same codebook
+    q(w2, "oil4")
+    assert q.codebook(w2, "oil4") is cb
+    # the trained codebook fits the first tensor better than the uniform grid the training started from
+    from innova_b200.ops.quant import ste_fake_quant
+    assert (y1 - w1).square().mean() < (ste_fake_quant(w1, "oil4", codebook=torch.linspace(-1.0, 1.0, 16)) - w1).square().mean()
+    w = (torch.randn(1024) * 0.1).requires_grad_(True)
+    fm = ["oil8", "oil4", "spark", "fp32"]
+    y = q.forward_mixed(w, fm, block=256)
+    err = [(y[i * 256:(i + 1) * 256] - w[i * 256:(i + 1) * 256]).detach().square().mean().item() for i in range(4)]
+    assert err[3] == 0.0 and err[0] < err[1] < err[2]
+    y.sum().backward()
+    assert torch.equal(w.grad, torch.ones_like(w))                                          # identity gradient through every format
+    assert STEQuantizer(use_ste=False)(w, "oil4") is w
+    STEQuantizer.reset_static_codebooks()
