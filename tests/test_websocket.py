@@ -58,3 +58,26 @@ def test_result_codes(tmp_path):
     r, v = Result.wrap(int, "12")
     assert r.ok() and v == 12
     assert Result.wrap(int, "x")[0].code == ErrorCode.INVALID_ARGUMENT
+
+
+def test_c_api_shaped_calls(tmp_path):
+    import ctypes as C
+    import torch
+    from innova_b200.formats import export
+    from innova_b200.models import DenseModel, PRESETS
+    from innova_b200.serving import capi
+    assert capi.oil_model_load(str(tmp_path / "missing.oil")) == 0 and "missing.oil" in capi.oil_last_error()
+    assert capi.oil_generate(12345, "x", 4) is None and "invalid handle" in capi.oil_last_error()
+    p = str(tmp_path / "m.oil")
+    export.save_model(DenseModel(PRESETS["tiny"](), dtype=torch.float32, device="cpu", seed=1), p)
+    h = capi.oil_model_load(p, device="cpu")
+    assert h > 0 and capi.oil_last_error() == ""
+    out = capi.oil_generate(h, "ab", 5)
+    assert isinstance(out, str) and capi.oil_generate(h, "ab", 5) == out           # greedy by default: repeatable
+    fns = capi.export_c_callbacks()
+    ptr = fns["oil_generate"](h, b"ab", 5)
+    assert C.string_at(ptr).decode("utf-8", "replace") == out
+    capi.oil_free_string(out)
+    capi.oil_model_free(h)
+    assert capi.oil_generate(h, "ab", 5) is None
+    assert b"invalid handle" in C.string_at(fns["oil_last_error"]())
