@@ -14,7 +14,7 @@ from innova_b200.formats import oil
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REF_SO = os.path.join(ROOT, "baseline", "_ref", "libref_oil.so")
-REF_SRC = "/root/reference"
+REF_SRC = os.environ.get("INNOVA_REFERENCE_SRC", os.path.join(os.path.dirname(ROOT), "reference"))   # a checkout beside this repository
 
 
 def _ref():
