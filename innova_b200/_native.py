@@ -7,6 +7,7 @@ GPU run can never fall back silently to PyTorch ops.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import threading
 from pathlib import Path
 
@@ -79,7 +80,8 @@ def host():
     if _host is None:
         with _lock:
             if _host is None:
-                path = lib_dir() / "libinnova_host.so"
+                override = os.environ.get("INNOVA_HOST_LIB")       # e.g. the sanitizer build (build.build_host_sanitized)
+                path = Path(override) if override else lib_dir() / "libinnova_host.so"
                 if not path.exists():
                     from . import build
                     build.build_host()

@@ -110,6 +110,28 @@ def build_host(force: bool = False) -> Path:
     return out
 
 
+def build_host_sanitized() -> Path:
+    """``libinnova_host_asan.so``: the host runtime with AddressSanitizer and UndefinedBehaviorSanitizer (the reference's
+    ``OIL_SANITIZE`` build, cmake/compiler.cmake:11-14). Load it in a process started with ``LD_PRELOAD=$(gcc
+    -print-file-name=libasan.so)`` and ``INNOVA_HOST_LIB`` pointing at it; any heap error or undefined operation in the
+    codecs, the container, the page tables or the arena aborts that process with a report."""
+    out = LIB / "libinnova_host_asan.so"
+    srcs = host_sources()
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if cxx is None:
+        raise RuntimeError("no C++ compiler found")
+    LIB.mkdir(exist_ok=True)
+    if _newer(srcs + list((CSRC / "host").glob("*.h")), out):
+        _run([cxx, "-O1", "-g", "-std=c++17", "-fPIC", "-pthread", "-fno-omit-frame-pointer", "-fsanitize=address,undefined",
+              "-fno-sanitize-recover=undefined", "-I", str(CSRC / "host"), "-shared", "-o", str(out), *map(str, srcs)])
+    return out
+
+
+def asan_runtime() -> str:
+    cc = shutil.which("gcc") or shutil.which("cc")
+    return subprocess.run([cc, "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip() if cc else ""
+
+
 def build_all(force: bool = False, verbose: bool = False):
     LIB.mkdir(exist_ok=True)
     return build_cuda(force, verbose), build_host(force)

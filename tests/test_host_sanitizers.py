@@ -1,0 +1,47 @@
+"""The C++ host runtime under AddressSanitizer + UndefinedBehaviorSanitizer: codecs, container, arena and page tables are
+driven in a child process that loads the instrumented library; any report makes the child exit non-zero."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+from innova_b200 import build
+
+CHILD = r"""
+import numpy as np, torch, tempfile, os, threading
+from innova_b200.formats import oil
+from innova_b200.utils.memory import MemoryPool, StackAllocator
+rng = np.random.default_rng(0)
+for fmt in oil.FORMATS:
+    for n in (1, 31, 256, 257):
+        oil.roundtrip(fmt, rng.standard_normal(n).astype(np.float32), 256)
+d = tempfile.mkdtemp()
+p = os.path.join(d, "t.oil")
+w = oil.OILWriter(p)
+w.add_tensor("a", rng.standard_normal(1000).astype(np.float32), "OIL8")
+w.add_tensor("b", rng.standard_normal(513).astype(np.float32), "OIL4")
+w.close(write_index=True)
+with oil.OILReader(p) as r:
+    assert r.read_tensor("a").numel() == 1000 and r.read_tensor("b").numel() == 513
+pool = StackAllocator(1 << 16)
+def work():
+    for _ in range(200):
+        pool.allocate_bytes(100)
+ts = [threading.Thread(target=work) for _ in range(4)]
+[t.start() for t in ts]; [t.join() for t in ts]
+pool.reset(); pool.push(); pool.allocate((8,), torch.float32); pool.pop(); pool.reset()
+print("sanitized run ok")
+"""
+
+
+def test_host_runtime_is_clean_under_asan_ubsan():
+    rt = build.asan_runtime()
+    if not rt or not os.path.exists(rt):
+        pytest.skip("no AddressSanitizer runtime for this compiler")
+    lib = build.build_host_sanitized()
+    env = dict(os.environ, LD_PRELOAD=rt, INNOVA_HOST_LIB=str(lib), ASAN_OPTIONS="detect_leaks=0:abort_on_error=1", UBSAN_OPTIONS="halt_on_error=1",
+               PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    r = subprocess.run([sys.executable, "-c", CHILD], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "sanitized run ok" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
+    assert "runtime error" not in r.stderr and "AddressSanitizer" not in r.stderr
