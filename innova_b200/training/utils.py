@@ -500,3 +500,183 @@ def r_drop_loss(logits_a: torch.Tensor, logits_b: torch.Tensor, labels: torch.Te
 def r_drop_step(model, ids: torch.Tensor, labels: torch.Tensor, alpha: float = 1.0, label_smoothing: float = 0.0) -> torch.Tensor:
     """Two forward passes of ``model(ids)`` (logits) in training mode, combined by ``r_drop_loss``."""
     return r_drop_loss(model(ids), model(ids), labels, alpha, label_smoothing)
+
+
+# ---------------------------------------------------------------------------------------------- TensorBoard / W&B-style writers
+def _crc32c_table():
+    tab = []
+    for i in range(256):
+        c = i
+        for _ in range(8):
+            c = (c >> 1) ^ 0x82F63B78 if c & 1 else c >> 1
+        tab.append(c)
+    return tab
+
+
+_CRC_TAB = _crc32c_table()
+
+
+def crc32c(data: bytes) -> int:
+    c = 0xFFFFFFFF
+    for b in data:
+        c = _CRC_TAB[(c ^ b) & 0xFF] ^ (c >> 8)
+    return c ^ 0xFFFFFFFF
+
+
+def _masked_crc(data: bytes) -> int:
+    c = crc32c(data)
+    return (((c >> 15) | (c << 17)) + 0xA282EAD8) & 0xFFFFFFFF
+
+
+def _varint(v: int) -> bytes:
+    out = bytearray()
+    while v > 0x7F:
+        out.append((v & 0x7F) | 0x80)
+        v >>= 7
+    out.append(v)
+    return bytes(out)
+
+
+def _field(num: int, wire: int) -> bytes:
+    return _varint((num << 3) | wire)
+
+
+class EventWriter:
+    """Scalar summaries in TensorBoard's event-file format without a protobuf dependency (the reference's ``EventWriter``,
+    include/oil/log_writer.h:10-23, src/log_writer.cpp:42-140): each record is ``Event{wall_time=1 (double), step=2 (varint),
+    summary=5{value=1{tag=1, simple_value=2 (float)}}}`` framed as length, masked CRC-32C of the length, payload, masked
+    CRC-32C of the payload."""
+
+    def __init__(self, logdir: str):
+        import os
+        import struct
+        import threading
+        import time
+        self._struct, self._time = struct, time
+        os.makedirs(logdir, exist_ok=True)
+        self.path = os.path.join(logdir, f"events.out.tfevents.{int(time.time())}.localhost")
+        self._f = open(self.path, "wb")
+        self._lock = threading.Lock()
+        self._record(self._struct.pack("<Bd", 0x09, time.time()) + _field(3, 2) + _varint(len(b"brain.Event:2")) + b"brain.Event:2")
+
+    def _record(self, payload: bytes):
+        head = self._struct.pack("<Q", len(payload))
+        self._f.write(head + self._struct.pack("<I", _masked_crc(head)) + payload + self._struct.pack("<I", _masked_crc(payload)))
+
+    def write_scalar(self, tag: str, value: float, step: int):
+        t = tag.encode("utf-8")
+        val = _field(1, 2) + _varint(len(t)) + t + _field(2, 5) + self._struct.pack("<f", float(value))
+        summary = _field(1, 2) + _varint(len(val)) + val
+        ev = self._struct.pack("<Bd", 0x09, self._time.time()) + _field(2, 0) + _varint(int(step)) + _field(5, 2) + _varint(len(summary)) + summary
+        with self._lock:
+            self._record(ev)
+
+    def write_scalars(self, metrics, step: int):
+        """Every numeric field of a metrics object (``TrainMetrics``, ``MoEMetrics``, a dict)."""
+        items = metrics.items() if isinstance(metrics, dict) else vars(metrics).items()
+        for k, v in items:
+            if isinstance(v, (int, float)) and not isinstance(v, bool) and v == v:
+                self.write_scalar(k, float(v), step)
+
+    def flush(self):
+        with self._lock:
+            self._f.flush()
+
+    def close(self):
+        self.flush()
+        self._f.close()
+
+    @staticmethod
+    def read(path: str):
+        """-> [(step, tag, value)] of the scalar records (checks both checksums)."""
+        import struct
+        out, data, off = [], open(path, "rb").read(), 0
+
+        def varint(buf, i):
+            v = s = 0
+            while True:
+                b = buf[i]
+                i += 1
+                v |= (b & 0x7F) << s
+                s += 7
+                if not b & 0x80:
+                    return v, i
+        while off < len(data):
+            head = data[off:off + 8]
+            (n,) = struct.unpack("<Q", head)
+            assert struct.unpack("<I", data[off + 8:off + 12])[0] == _masked_crc(head), "length checksum"
+            payload = data[off + 12:off + 12 + n]
+            assert struct.unpack("<I", data[off + 12 + n:off + 16 + n])[0] == _masked_crc(payload), "payload checksum"
+            off += 16 + n
+            i, step, summary = 0, 0, None
+            while i < len(payload):
+                key, i = varint(payload, i)
+                num, wire = key >> 3, key & 7
+                if wire == 1:
+                    i += 8
+                elif wire == 0:
+                    v, i = varint(payload, i)
+                    step = v if num == 2 else step
+                elif wire == 2:
+                    ln, i = varint(payload, i)
+                    if num == 5:
+                        summary = payload[i:i + ln]
+                    i += ln
+                elif wire == 5:
+                    i += 4
+            if summary is None:
+                continue
+            _, j = varint(summary, 0)
+            ln, j = varint(summary, j)
+            val = summary[j:j + ln]
+            _, k = varint(val, 0)
+            tl, k = varint(val, k)
+            tag = val[k:k + tl].decode()
+            k += tl + 1
+            out.append((step, tag, struct.unpack("<f", val[k:k + 4])[0]))
+        return out
+
+
+class WandBLogger:
+    """Offline run directory in the spirit of the reference's ``WandBLogger`` (include/oil/log_writer.h:25-36): one JSON line
+    per ``log`` call in ``<project>/<run>/metrics.json`` plus ``config.json`` and a ``summary.json`` with the last value of
+    every key."""
+
+    def __init__(self, project: str, run_name: str = "", config: Optional[dict] = None, root: str = "."):
+        import json
+        import os
+        import threading
+        import time
+        self._json = json
+        self.run_name = run_name or time.strftime("run-%Y%m%d-%H%M%S")
+        self.dir = os.path.join(root, project, self.run_name)
+        os.makedirs(self.dir, exist_ok=True)
+        self._f = open(os.path.join(self.dir, "metrics.json"), "a")
+        self._lock = threading.Lock()
+        self.summary: dict = {}
+        if config is not None:
+            with open(os.path.join(self.dir, "config.json"), "w") as f:
+                json.dump(config, f)
+
+    def log(self, key: str, value: float, step: int):
+        with self._lock:
+            self._f.write(self._json.dumps({"step": int(step), key: float(value)}) + "\n")
+            self.summary[key] = float(value)
+
+    def log_metrics(self, metrics, step: int):
+        items = metrics.items() if isinstance(metrics, dict) else vars(metrics).items()
+        row = {k: float(v) for k, v in items if isinstance(v, (int, float)) and not isinstance(v, bool) and v == v}
+        with self._lock:
+            self._f.write(self._json.dumps({"step": int(step), **row}) + "\n")
+            self.summary.update(row)
+
+    def flush(self):
+        import os
+        with self._lock:
+            self._f.flush()
+            with open(os.path.join(self.dir, "summary.json"), "w") as f:
+                self._json.dump(self.summary, f)
+
+    def close(self):
+        self.flush()
+        self._f.close()

@@ -93,3 +93,32 @@ def test_label_smoothing_in_the_fused_lm_head_loss_gpu():
     assert abs(float(loss) - float(ref)) < 2e-2
     gx = x.grad if x.grad is not None else x.main_grad
     assert (gx.float() - xr.grad).norm() / xr.grad.norm() < 3e-2
+
+
+def test_event_writer_and_offline_run_logger(tmp_path):
+    import json
+    from innova_b200.training.trainer import TrainMetrics
+    from innova_b200.training.utils import EventWriter, WandBLogger, crc32c
+    assert crc32c(b"123456789") == 0xE3069283                       # the check value of CRC-32C
+    w = EventWriter(str(tmp_path / "tb"))
+    w.write_scalar("loss", 2.5, 1)
+    w.write_scalar("loss", 1.25, 300)
+    w.write_scalars(TrainMetrics(step=300, loss=1.25, lr=3e-4), 300)
+    w.close()
+    rec = EventWriter.read(w.path)
+    assert rec[0] == (1, "loss", 2.5) and rec[1] == (300, "loss", 1.25)
+    assert ("lr" in [t for _, t, _ in rec]) and all(s == 300 for s, _, _ in rec[1:])
+    try:
+        from tensorboard.backend.event_processing.event_file_loader import EventFileLoader      # the real reader, when installed
+        tags = [v.tag for e in EventFileLoader(w.path).Load() for v in e.summary.value]
+        assert tags[:2] == ["loss", "loss"]
+    except ImportError:
+        pass
+    lg = WandBLogger("proj", "r1", config={"lr": 1e-3}, root=str(tmp_path))
+    lg.log("loss", 3.0, 1)
+    lg.log_metrics({"loss": 2.0, "ppl": 7.4, "note": "text is skipped"}, 2)
+    lg.close()
+    rows = [json.loads(l) for l in open(tmp_path / "proj" / "r1" / "metrics.json")]
+    assert rows == [{"step": 1, "loss": 3.0}, {"step": 2, "loss": 2.0, "ppl": 7.4}]
+    assert json.load(open(tmp_path / "proj" / "r1" / "summary.json")) == {"loss": 2.0, "ppl": 7.4}
+    assert json.load(open(tmp_path / "proj" / "r1" / "config.json")) == {"lr": 1e-3}
