@@ -23,6 +23,8 @@ import math
 from dataclasses import dataclass
 from typing import Dict, List, Optional
 
+import os
+
 import torch
 import torch.nn.functional as F
 
@@ -66,6 +68,9 @@ class HybridEngine:
         self.ok = False
         self.logits: Optional[torch.Tensor] = None
         self._rng = torch.Generator().manual_seed(0x9E3779B9)
+        # debugging switches of the reference engine (src/adapters/tools/qwen35_engine.cpp:91-92): drop one kind of mixer
+        self.skip_full = os.environ.get("OIL_SKIP_FULL") is not None
+        self.skip_gla = os.environ.get("OIL_SKIP_GLA") is not None
         self.reset()
 
     # ------------------------------------------------------------------ weights
@@ -231,7 +236,8 @@ class HybridEngine:
         for L in range(c.layers):
             b = f"{p}layers.{L}."
             h = _rms(x, self.w[b + "input_layernorm.weight"], c.eps)
-            x = x + (self._full(L, h) if c.is_full(L) else self._gla(L, h))
+            if not (self.skip_full if c.is_full(L) else self.skip_gla):
+                x = x + (self._full(L, h) if c.is_full(L) else self._gla(L, h))
             h = _rms(x, self.w[b + "post_attention_layernorm.weight"], c.eps)
             x = x + self._lin(F.silu(self._lin(h, b + "mlp.gate_proj.weight")) * self._lin(h, b + "mlp.up_proj.weight"), b + "mlp.down_proj.weight")
         self.pos += ids.shape[0]

@@ -60,3 +60,16 @@ def test_save_load_roundtrip(tmp_path):
     assert e2.load(path) and torch.allclose(e2.prefill([7, 7, 1, 30]), ref, atol=1e-5)
     e3 = HybridEngine(HybridConfig(vocab_size=96, hidden=64, layers=8))           # more layers than the file has
     assert not e3.load(path)
+
+
+def test_skip_switches_from_the_environment(monkeypatch):
+    ids = [5, 17, 3, 90]
+    base = HybridEngine(CFG).init_random(1).prefill(ids).clone()
+    monkeypatch.setenv("OIL_SKIP_FULL", "1")
+    e = HybridEngine(CFG).init_random(1)
+    assert e.skip_full and not e.skip_gla
+    no_full = e.prefill(ids).clone()
+    monkeypatch.delenv("OIL_SKIP_FULL")
+    monkeypatch.setenv("OIL_SKIP_GLA", "1")
+    no_gla = HybridEngine(CFG).init_random(1).prefill(ids).clone()
+    assert not torch.allclose(base, no_full) and not torch.allclose(base, no_gla) and not torch.allclose(no_full, no_gla)
