@@ -99,3 +99,50 @@ class PeerFlags:
         self.epoch_barrier = getattr(self, "epoch_barrier", 0) + 1
         self.signal(s, self.epoch_barrier)
         self.wait(s, self.epoch_barrier)
+
+
+class CanaryGuard:
+    """Guard regions around a payload inside one flat allocation: ``guard_bytes`` of a fixed pattern before and after the
+    payload. Peer-memory kernels address a rank's buffer by raw pointer plus offset, so an indexing error on another GPU
+    shows up here as a damaged guard instead of silently corrupting a neighbouring tensor. ``payload`` is what the kernels
+    get; ``check()`` after a fused collective compares both guards with the pattern (one small device reduction) and
+    reports which side was hit and the first damaged byte. Works on any flat uint8 tensor, host or device, e.g.
+    ``CanaryGuard(SymmBuffer(CanaryGuard.total_bytes(n), torch.uint8).tensor, n)``."""
+    PATTERN = 0xA5
+
+    def __init__(self, storage: torch.Tensor, payload_bytes: int, guard_bytes: int = 256):
+        assert storage.dtype == torch.uint8 and storage.dim() == 1 and storage.numel() >= payload_bytes + 2 * guard_bytes
+        self.storage, self.guard_bytes, self.payload_bytes = storage, guard_bytes, payload_bytes
+        self.front = storage[:guard_bytes]
+        self.payload = storage[guard_bytes:guard_bytes + payload_bytes]
+        self.back = storage[guard_bytes + payload_bytes:guard_bytes + payload_bytes + guard_bytes]
+        self.arm()
+
+    @staticmethod
+    def total_bytes(payload_bytes: int, guard_bytes: int = 256) -> int:
+        return payload_bytes + 2 * guard_bytes
+
+    @property
+    def payload_offset(self) -> int:
+        """Byte offset of the payload inside the allocation (add it to every peer pointer)."""
+        return self.guard_bytes
+
+    def view(self, dtype: torch.dtype, *shape) -> torch.Tensor:
+        return self.payload.view(dtype).view(*shape)
+
+    def arm(self):
+        self.front.fill_(self.PATTERN)
+        self.back.fill_(self.PATTERN)
+
+    def damage(self):
+        """-> None when both guards are intact, else (side, offset of the first damaged byte inside that guard)."""
+        for side, g in (("front", self.front), ("back", self.back)):
+            bad = g != self.PATTERN
+            if bool(bad.any()):
+                return side, int(bad.nonzero()[0, 0])
+        return None
+
+    def check(self, what: str = "buffer"):
+        d = self.damage()
+        if d is not None:
+            raise RuntimeError(f"{what}: write outside the payload, {d[0]} guard damaged at byte {d[1]}")

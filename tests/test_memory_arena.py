@@ -92,3 +92,20 @@ def test_device_pool_feeds_kernels():
         assert x.is_cuda and x.data_ptr() % 256 == 0
         assert (y.float() - x.float() @ w.float().t()).abs().max() < 0.5
     assert pool.bytes_used == 0 and pool.peak_usage >= (256 + 384) * 512 * 2
+
+
+def test_canary_guard_detects_out_of_range_writes():
+    from innova_b200.parallel.symm import CanaryGuard
+    n = 1000 * 4
+    g = CanaryGuard(torch.zeros(CanaryGuard.total_bytes(n), dtype=torch.uint8), n)
+    x = g.view(torch.float32, 10, 100)
+    x.fill_(3.0)
+    assert g.damage() is None and g.payload_offset == 256
+    g.check("staging")
+    g.storage[256 + n + 5] = 0                      # one byte past the payload
+    assert g.damage() == ("back", 5)
+    with pytest.raises(RuntimeError, match="back guard damaged at byte 5"):
+        g.check("staging")
+    g.arm()
+    g.storage[255] = 1
+    assert g.damage() == ("front", 255) and float(x.sum()) == 3000.0
