@@ -21,7 +21,7 @@ from .config import TransformerConfig
 def _ste(w, cfg):
     if cfg.ste_format:
         from ..ops.quant import ste_fake_quant
-        return ste_fake_quant(w, cfg.ste_format, cfg.ste_block)
+        return ste_fake_quant(w, cfg.ste_format, cfg.ste_block, getattr(cfg, "ste_codebook", None))   # None: the format's default levels
     return w
 
 

@@ -37,6 +37,8 @@ class TrainConfig:
     label_smoothing: float = 0.0
     ema_decay: float = 0.0               # 0 = off
     grad_noise_std: float = 0.0
+    codebook_ema_interval: int = 0       # > 0: refresh the STE codebook by EMA every so many steps (the reference uses 100)
+    codebook_ema_decay: float = 0.99
     use_loss_scaling: bool = False       # bf16/fp32 need none; kept for parity with the reference
     initial_loss_scale: float = 128.0
     reference_adamw: bool = False
@@ -128,7 +130,29 @@ class Trainer:
         if self.ema is not None:
             self.ema.mul_(c.ema_decay).add_(self.engine.flat_param.float(), alpha=1 - c.ema_decay)
         self.global_step += 1
+        if c.codebook_ema_interval and self.global_step % c.codebook_ema_interval == 0:
+            self.update_ste_codebook()
         return total / A
+
+    @torch.no_grad()
+    def update_ste_codebook(self, max_samples: int = 1 << 20):
+        """Moves the shared OIL8 / OIL4 codebook of the straight-through quantiser towards the current weight distribution
+        (src/trainer_core.cpp:408-474: codebook EMA every 100 steps). The statistics come from an evenly strided sample of
+        the matrices in the flat parameter buffer."""
+        mcfg = getattr(self.model, "cfg", None)
+        fmt = getattr(mcfg, "ste_format", None)
+        if fmt not in ("oil8", "oil4"):
+            return None
+        from ..ops.quant import default_codebook, ema_update_codebook
+        flat = self.engine.flat_param
+        blk = mcfg.ste_block
+        n_blocks = flat.numel() // blk
+        stride = max(1, n_blocks // max(1, max_samples // blk))
+        sample = flat[: n_blocks * blk].view(n_blocks, blk)[::stride].reshape(-1).float()
+        cb = getattr(mcfg, "ste_codebook", None)
+        cb = default_codebook(fmt, flat.device).clone() if cb is None else cb
+        mcfg.ste_codebook = ema_update_codebook(cb, sample, self.cfg.codebook_ema_decay, blk).to(flat.device).contiguous()
+        return mcfg.ste_codebook
 
     def _takes_grad_scale(self):
         if not hasattr(self, "_tgs"):

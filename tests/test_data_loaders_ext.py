@@ -122,3 +122,25 @@ def test_event_writer_and_offline_run_logger(tmp_path):
     assert rows == [{"step": 1, "loss": 3.0}, {"step": 2, "loss": 2.0, "ppl": 7.4}]
     assert json.load(open(tmp_path / "proj" / "r1" / "summary.json")) == {"loss": 2.0, "ppl": 7.4}
     assert json.load(open(tmp_path / "proj" / "r1" / "config.json")) == {"lr": 1e-3}
+
+
+def test_codebook_ema_during_training():
+    from innova_b200.models import DenseModel, PRESETS
+    from innova_b200.ops.quant import default_codebook
+    from innova_b200.training.trainer import TrainConfig, Trainer
+    torch.manual_seed(0)
+    cfg = PRESETS["tiny"]()
+    cfg.ste_format = "oil4"
+    model = DenseModel(cfg, dtype=torch.float32, device="cpu", seed=3)
+    tr = Trainer(model, TrainConfig(lr=1e-3, codebook_ema_interval=2, codebook_ema_decay=0.5))
+    ids = torch.randint(0, cfg.vocab_size, (2, 16))
+    labels = torch.roll(ids, -1, 1)
+    tr.train_step(ids, labels)
+    assert getattr(cfg, "ste_codebook", None) is None
+    tr.train_step(ids, labels)
+    cb = cfg.ste_codebook
+    assert cb.shape == (16,) and bool((cb[1:] >= cb[:-1]).all()) and not torch.allclose(cb, default_codebook("oil4"))
+    l = float(tr.train_step(ids, labels))                       # the model now quantises with the refreshed levels
+    assert l == l
+    tr.train_step(ids, labels)
+    assert not torch.equal(cfg.ste_codebook, cb)
