@@ -6,6 +6,7 @@
 
 #include "oil/block_codec.h"
 #include "oil/oil_format.h"
+#include "oil/random.h"
 
 extern "C" {
 int ref_encode_block(int fmt, const float* w, int n, uint8_t* idx_out, uint64_t* idx_len, uint8_t* cb_out, uint64_t* cb_len) {
@@ -53,5 +54,13 @@ int ref_write_single(const char* path, const char* name, const float* w, long n,
   for (auto& b : blocks) wr.write_block(b);
   wr.close();
   return 0;
+}
+// The reference's random stream: n raw words, then n uniforms, n normals and n integers in [lo, hi] from fresh generators.
+void ref_rng_stream(uint64_t seed, int n, uint64_t* words, float* uniforms, float* normals, int lo, int hi, int* ints) {
+  oil::RNG a(seed), b(seed), c(seed), d(seed);
+  for (int i = 0; i < n; i++) words[i] = a.next_u64();
+  for (int i = 0; i < n; i++) uniforms[i] = b.uniform();
+  for (int i = 0; i < n; i++) normals[i] = c.normal();
+  for (int i = 0; i < n; i++) ints[i] = d.uniform_int(lo, hi);
 }
 }

@@ -125,3 +125,34 @@ def test_concurrency_helpers():
     with m.exclusive():
         order.append("exclusive")
     assert order == ["two readers", "writer", "exclusive"]
+
+
+def test_rng_matches_the_reference_sources():
+    """The same seed gives the same words, uniforms, normals and bounded integers as the reference's own generator (its
+    sources are compiled, unmodified, into a test-only oracle library when a checkout is available)."""
+    import ctypes as C
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref_src = os.environ.get("INNOVA_REFERENCE_SRC", os.path.join(os.path.dirname(root), "reference"))
+    if not os.path.isdir(ref_src):
+        pytest.skip("no reference checkout")
+    so = os.path.join(root, "baseline", "_ref", "libref_rng.so")
+    shim = os.path.join(root, "baseline", "ref_shim.cpp")
+    if not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(shim):
+        os.makedirs(os.path.dirname(so), exist_ok=True)
+        srcs = [os.path.join(ref_src, "src", f) for f in ("block_codec.cpp", "oil_format.cpp", "tensor.cpp", "memory.cpp", "codebook.cpp", "random.cpp")]
+        subprocess.run(["g++", "-O2", "-std=c++20", "-fPIC", "-shared", "-I" + os.path.join(ref_src, "include"), "-o", so, shim] + srcs,
+                       check=False, capture_output=True)
+    if not os.path.exists(so):
+        pytest.skip("reference oracle library not built")
+    lib = C.CDLL(so)
+    n = 64
+    words, uni, nor, ints = (C.c_uint64 * n)(), (C.c_float * n)(), (C.c_float * n)(), (C.c_int * n)()
+    lib.ref_rng_stream.argtypes = [C.c_uint64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    for seed in (1, 42, 2 ** 63 + 5):
+        lib.ref_rng_stream(seed, n, words, uni, nor, -3, 11, ints)
+        a, b, c, d = RNG(seed), RNG(seed), RNG(seed), RNG(seed)
+        assert [a.next_u64() for _ in range(n)] == list(words)
+        assert np.allclose([b.uniform() for _ in range(n)], list(uni), rtol=0, atol=1e-7)
+        assert np.allclose([c.normal() for _ in range(n)], list(nor), rtol=1e-5, atol=1e-6)
+        assert [d.uniform_int(-3, 11) for _ in range(n)] == list(ints)
