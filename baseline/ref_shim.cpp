@@ -7,6 +7,7 @@
 #include "oil/block_codec.h"
 #include "oil/oil_format.h"
 #include "oil/random.h"
+#include "oil/tensor.h"
 
 extern "C" {
 int ref_encode_block(int fmt, const float* w, int n, uint8_t* idx_out, uint64_t* idx_len, uint8_t* cb_out, uint64_t* cb_len) {
@@ -62,5 +63,16 @@ void ref_rng_stream(uint64_t seed, int n, uint64_t* words, float* uniforms, floa
   for (int i = 0; i < n; i++) uniforms[i] = b.uniform();
   for (int i = 0; i < n; i++) normals[i] = c.normal();
   for (int i = 0; i < n; i++) ints[i] = d.uniform_int(lo, hi);
+}
+// Serialises a tensor of the given dims / dtype code / raw bytes with the reference's Tensor::serialize; returns the size.
+long ref_serialize_tensor(const int64_t* dims, int rank, int dtype, const uint8_t* raw, long raw_bytes, uint8_t* out, long cap) {
+  oil::Shape sh;
+  sh.rank = rank;
+  for (int i = 0; i < rank; i++) sh.dims[i] = dims[i];
+  oil::Tensor t(sh, (oil::DType)dtype);
+  if ((long)t.size_bytes() != raw_bytes) return -1;
+  std::memcpy(t.data(), raw, (size_t)raw_bytes);
+  if ((long)t.serialized_size() > cap) return -2;
+  return (long)t.serialize(out);
 }
 }

@@ -156,3 +156,15 @@ def test_rng_matches_the_reference_sources():
         assert np.allclose([b.uniform() for _ in range(n)], list(uni), rtol=0, atol=1e-7)
         assert np.allclose([c.normal() for _ in range(n)], list(nor), rtol=1e-5, atol=1e-6)
         assert [d.uniform_int(-3, 11) for _ in range(n)] == list(ints)
+    # the tensor wire layout against Tensor::serialize of the same sources
+    lib.ref_serialize_tensor.restype = C.c_long
+    lib.ref_serialize_tensor.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_long, C.c_void_p, C.c_long]
+    for t, code in ((torch.arange(24, dtype=torch.float32).view(2, 3, 4), 4), (torch.tensor([[1, -2], [3, 4]], dtype=torch.int64), 0),
+                    (torch.arange(7, dtype=torch.uint8), 1), (torch.tensor([0.5, -1.5, 2.0], dtype=torch.float16), 3)):
+        raw = t.numpy().tobytes()
+        dims = (C.c_int64 * 8)(*t.shape)
+        out = (C.c_uint8 * (len(raw) + 128))()
+        n = lib.ref_serialize_tensor(dims, t.dim(), code, raw, len(raw), out, len(raw) + 128)
+        assert n > 0 and bytes(out[:n]) == serialize_tensor(t)
+        back, _ = deserialize_tensor(bytes(out[:n]))
+        assert torch.equal(back, t)
