@@ -32,6 +32,7 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=2, help="sequences per tensor-parallel group and micro-step")
     ap.add_argument("--global-batch", type=int, default=128, help="sequences per optimizer step over all groups")
     ap.add_argument("--ste-format", default="oil8")
+    ap.add_argument("--cache-ste", action="store_true", help="quantise the weights once per optimizer step instead of once per micro-step")
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=1)
     a = ap.parse_args()
@@ -59,7 +60,7 @@ def main():
     cfg = TransformerConfig(vocab_size=a.vocab, hidden_size=a.hidden, num_layers=a.layers, num_heads=a.heads, head_dim=a.hidden // a.heads,
                             ffn_hidden_size=a.ffn, max_seq_len=a.seq, activation="silu", norm="rmsnorm", positions="rope", bias=False,
                             ste_format=a.ste_format or None, gradient_checkpointing=True)
-    model = TPDenseModel(cfg, tp_group, dtype=torch.bfloat16, device=dev, seed=1).train()
+    model = TPDenseModel(cfg, tp_group, dtype=torch.bfloat16, device=dev, seed=1, cache_ste=a.cache_ste).train()
     eng = ShardedFlatEngine(model, lr=1e-4, weight_decay=0.1, max_grad_norm=0.0, group=dp_group)
     accum = max(1, a.global_batch // (dp * a.micro_batch))
     group_id = rank // tp            # both ranks of a pair read the same micro-batches
@@ -80,6 +81,7 @@ def main():
                 p.grad = None
         model.sync_replicated_grads()
         eng.step()
+        model.invalidate_ste_cache()
         return loss
 
     for i in range(a.warmup):
@@ -105,7 +107,7 @@ def main():
                           "ms_per_step": float(ms), "steps": a.steps, "warmup": a.warmup, "dtype": "bf16", "data": "synthetic Zipf(1.1)",
                           "config": {"model": f"dense {a.layers}L d{a.hidden} {a.heads}h ffn{a.ffn} vocab{a.vocab}", "global_batch_sequences":
                                      dp * accum * a.micro_batch, "seq_len": a.seq, "parallelism": f"fsdp{dp} x tp{tp}", "grad_accum": accum,
-                                     "ste_format": a.ste_format, "gradient_checkpointing": True},
+                                     "ste_format": a.ste_format, "gradient_checkpointing": True, "cache_ste": a.cache_ste},
                           "params_total": rep + (params - rep) * tp, "gpu_launches": rt.launch_count() - n0, "loss": float(loss),
                           "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)}))
     dist.barrier()

@@ -30,11 +30,34 @@ from ..parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear, 
 from .config import TransformerConfig
 
 
-def _w(layer, ste_format, block):
-    if ste_format:
+class _CachedSte(torch.autograd.Function):
+    """Straight-through fake quantisation whose forward value is computed once per optimizer step: the weights only change
+    at the step, so the micro-steps of one step (and the recomputation under checkpointing) reuse the quantised copy."""
+
+    @staticmethod
+    def forward(ctx, w, holder, fmt, block):
+        q = holder.get("q")
+        if q is None:
+            from ..ops.quant import ste_fake_quant
+            q = holder["q"] = ste_fake_quant(w.detach(), fmt, block).detach()
+        return q.view_as(q)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None, None, None
+
+
+def _w(layer, ste_format, block, cache=None):
+    if not ste_format:
+        return layer.weight
+    if cache is None:
         from ..ops.quant import ste_fake_quant
         return ste_fake_quant(layer.weight, ste_format, block)
-    return layer.weight
+    out = _CachedSte.apply(layer.weight, cache.setdefault(id(layer), {}), ste_format, block)
+    mg = getattr(layer.weight, "main_grad", None)
+    if mg is not None:
+        out.main_grad = mg            # fused weight-gradient kernels accumulate into the parameter's fp32 buffer
+    return out
 
 
 class TPBlock(nn.Module):
@@ -43,6 +66,7 @@ class TPBlock(nn.Module):
         W = comm.world
         assert cfg.num_heads % W == 0 and cfg.kv_heads % W == 0 and cfg.ffn_hidden_size % W == 0
         self.cfg, self.comm = cfg, comm
+        self.ste_cache = None          # set by the model when quantised weights are cached per optimizer step
         self.H, self.Hkv, self.D = cfg.num_heads // W, cfg.kv_heads // W, cfg.head_dim
         E, F = cfg.hidden_size, cfg.ffn_hidden_size
         self.n1 = nn.Parameter(torch.ones(E, dtype=dtype, device=device))
@@ -58,20 +82,21 @@ class TPBlock(nn.Module):
         cfg, c = self.cfg, self.comm
         fmt, blk = cfg.ste_format, cfg.ste_block
         h = ops.rms_norm(x, self.n1, cfg.norm_eps)
-        qkv = _ColumnParallelFn.apply(h, _w(self.qkv, fmt, blk), None, c, False).view(batch, seq, -1)
+        qkv = _ColumnParallelFn.apply(h, _w(self.qkv, fmt, blk, self.ste_cache), None, c, False).view(batch, seq, -1)
         qkv = ops.rope_qk(qkv, cos, sin, self.H, self.Hkv, self.D)
         a = ops.flash_attention(qkv, self.H, self.Hkv, self.D, causal=True).reshape(batch * seq, -1)
-        x = x + _RowParallelFn.apply(a, _w(self.o, fmt, blk), c)
+        x = x + _RowParallelFn.apply(a, _w(self.o, fmt, blk, self.ste_cache), c)
         h = ops.rms_norm(x, self.n2, cfg.norm_eps)
-        act = ops.swiglu(_ColumnParallelFn.apply(h, _w(self.gu, fmt, blk), None, c, False))
-        return x + _RowParallelFn.apply(act, _w(self.down, fmt, blk), c)
+        act = ops.swiglu(_ColumnParallelFn.apply(h, _w(self.gu, fmt, blk, self.ste_cache), None, c, False))
+        return x + _RowParallelFn.apply(act, _w(self.down, fmt, blk, self.ste_cache), c)
 
 
 class TPDenseModel(nn.Module):
     """``forward(ids, labels)`` -> this rank's share of the micro-batch loss (already divided by the tensor-parallel
     world size: summing the ranks' values gives the mean loss over all tokens)."""
 
-    def __init__(self, cfg: TransformerConfig, tp_group=None, dtype=torch.bfloat16, device="cuda", seed: int = 0, comm: Optional[FusedGemmComm] = None):
+    def __init__(self, cfg: TransformerConfig, tp_group=None, dtype=torch.bfloat16, device="cuda", seed: int = 0, comm: Optional[FusedGemmComm] = None,
+                 cache_ste: bool = False):
         super().__init__()
         self.cfg = cfg
         self.tp_group = tp_group
@@ -86,9 +111,18 @@ class TPDenseModel(nn.Module):
         self.norm = nn.Parameter(torch.ones(E, dtype=dtype, device=dev))
         torch.manual_seed(seed * 1000 + 17 + self.tp_rank)
         self.blocks = nn.ModuleList(TPBlock(cfg, self.comm, dtype, dev) for _ in range(cfg.num_layers))
+        self._ste_cache = {} if (cache_ste and cfg.ste_format) else None
+        for b in self.blocks:
+            b.ste_cache = self._ste_cache
         cos, sin = ops.rope_tables(cfg.max_seq_len, cfg.head_dim, cfg.rope_theta, dev)
         self.register_buffer("cos", cos, persistent=False)
         self.register_buffer("sin", sin, persistent=False)
+
+    def invalidate_ste_cache(self):
+        """Call after every optimizer step when ``cache_ste`` is on: the next forward pass quantises the new weights."""
+        if self._ste_cache is not None:
+            for h in self._ste_cache.values():
+                h.clear()
 
     def replicated_parameters(self) -> List[nn.Parameter]:
         out = [self.emb, self.head, self.norm]

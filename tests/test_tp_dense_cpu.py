@@ -73,3 +73,32 @@ def test_tp_dense_matches_single_rank(tmp_path):
         assert abs(r["loss"] - r["ref"]) < 1e-4, r
         for k in ("emb", "n1", "o", "gu"):
             assert r[k] < 1e-4 * max(1.0, r["scale"]), (rank, k, r)
+
+
+def test_cached_ste_weights_match_per_microstep_quantisation():
+    import torch
+    from innova_b200.models import TransformerConfig
+    from innova_b200.models.tp_dense import TPDenseModel
+    cfg = TransformerConfig(vocab_size=64, hidden_size=32, num_layers=2, num_heads=2, head_dim=16, ffn_hidden_size=64, max_seq_len=16,
+                            vocab_pad_to=1, activation="silu", norm="rmsnorm", positions="rope", bias=False, ste_format="oil8",
+                            gradient_checkpointing=True)
+    a = TPDenseModel(cfg, None, dtype=torch.float32, device="cpu", seed=3).train()
+    b = TPDenseModel(cfg, None, dtype=torch.float32, device="cpu", seed=3, cache_ste=True).train()
+    b.load_state_dict(a.state_dict())
+    torch.manual_seed(0)
+    for _ in range(2):                                           # two micro-steps of one optimizer step
+        ids = torch.randint(0, 64, (2, 16))
+        la, lb = a(ids, torch.roll(ids, -1, 1)), b(ids, torch.roll(ids, -1, 1))
+        la.backward(); lb.backward()
+        assert torch.allclose(la, lb, atol=1e-6)
+    for (n, p), q in zip(a.named_parameters(), b.parameters()):
+        assert torch.allclose(p.grad, q.grad, atol=1e-5), n
+    assert len(b._ste_cache) == 8 and all("q" in h for h in b._ste_cache.values())
+    with torch.no_grad():                                        # an optimizer step
+        for p, q in zip(a.parameters(), b.parameters()):
+            p.add_(0.05 * torch.randn_like(p)); q.copy_(p)
+    ids = torch.randint(0, 64, (2, 16))
+    stale = float(b(ids, torch.roll(ids, -1, 1)).detach())
+    b.invalidate_ste_cache()
+    fresh, want = float(b(ids, torch.roll(ids, -1, 1)).detach()), float(a(ids, torch.roll(ids, -1, 1)).detach())
+    assert abs(fresh - want) < 1e-6 and abs(stale - want) > 1e-7
