@@ -35,7 +35,17 @@ def build_server(model_path: str, port: int = 8080, host: str = "127.0.0.1", dev
     srv.set_load_model_callback(load)
     if rate_limit > 0:
         srv.set_rate_limit(rate_limit, int(max(1, rate_limit)))
+    srv.generate_for_websocket = generate
     return srv
+
+
+def build_websocket(srv, port: int = 8081, host: str = "127.0.0.1"):
+    """Token streaming over WebSocket next to the HTTP server (the reference's ``WebSocketHandler`` on port 8081): a client
+    sends ``{"prompt": ..., "max_tokens": ...}`` and receives the pieces as text frames, then ``{"done": true}``."""
+    from ..serving.websocket import WebSocketHandler
+    ws = WebSocketHandler(port, host)
+    ws.set_generate_callback(srv.generate_for_websocket)
+    return ws
 
 
 def main(argv=None):
@@ -45,15 +55,23 @@ def main(argv=None):
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--rate-limit", type=float, default=0.0)
     ap.add_argument("--device", default=None)
+    ap.add_argument("--ws-port", type=int, default=0, help="also stream tokens over WebSocket on this port (0 = off; the reference uses 8081)")
     a = ap.parse_args(argv)
     srv = build_server(a.model, a.port, a.host, a.device, a.rate_limit)
     srv.start()
     print(f"serving {a.model} on http://{a.host}:{srv.port}", flush=True)
+    ws = None
+    if a.ws_port:
+        ws = build_websocket(srv, a.ws_port, a.host)
+        ws.start()
+        print(f"token streaming on ws://{a.host}:{ws.port}", flush=True)
     try:
         while srv.is_running():
             time.sleep(0.5)
     except KeyboardInterrupt:
         srv.stop()
+    if ws is not None:
+        ws.stop()
     return 0
 
 

@@ -65,6 +65,24 @@ def test_serve_answers_over_http(tiny):
         req = urllib.request.Request(f"http://127.0.0.1:{srv.port}/v1/embeddings", data=json.dumps({"input": "fox"}).encode(), method="POST")
         with urllib.request.urlopen(req, timeout=60) as r:
             assert len(json.loads(r.read())["data"][0]["embedding"]) == 64
+        # the same model streams tokens over WebSocket
+        from innova_b200.cli.serve import build_websocket
+        from innova_b200.serving.websocket import WebSocketClient
+        ws = build_websocket(srv, port=0)
+        ws.start()
+        try:
+            c = WebSocketClient("127.0.0.1", ws.port, timeout=60)
+            c.send(json.dumps({"prompt": "the quick", "max_tokens": 4}))
+            pieces = []
+            while True:
+                _, payload = c.recv()
+                if payload.startswith(b"{") and json.loads(payload).get("done"):
+                    break
+                pieces.append(payload.decode("utf-8", "replace"))
+            assert 1 <= len(pieces) <= 4
+            c.close()
+        finally:
+            ws.stop()
     finally:
         srv.stop()
 
