@@ -85,6 +85,7 @@ def parse():
     ap.add_argument("--batch-per-gpu", type=int, default=64)
     ap.add_argument("--seq-len", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=12, help="for debugging only; the reported config is 12")
+    ap.add_argument("--engine", default="fsdp3", choices=["fsdp3", "zero2"], help="data-parallel engine at N > 1")
     return ap.parse_args()
 
 
@@ -155,10 +156,18 @@ def run_ours(args):
     tcfg = TrainConfig(lr=3e-4, weight_decay=0.1, max_grad_norm=1.0)
     engine = None
     parallelism = "single"
-    if world > 1:
+    memory = None
+    if world > 1 and args.engine == "fsdp3":
+        # stage 3: parameters, gradients and optimizer state sharded; gathers and reduce-scatters ride in the GEMMs
+        from innova_b200.parallel.fsdp3 import FSDP3Engine
+        engine = FSDP3Engine(model, lr=tcfg.lr, weight_decay=tcfg.weight_decay, max_grad_norm=tcfg.max_grad_norm).install()
+        parallelism = f"fsdp{world} (stage 3: sharded params, grads, optimizer state)"
+        memory = engine.memory_report()
+    elif world > 1:
+        # replicated bf16 parameters and fp32 gradients, sharded fp32 master weights and Adam state
         from innova_b200.parallel.fsdp import ShardedFlatEngine
         engine = ShardedFlatEngine(model, lr=tcfg.lr, weight_decay=tcfg.weight_decay, max_grad_norm=tcfg.max_grad_norm)
-        parallelism = f"fsdp{world}"
+        parallelism = f"zero2 x{world} (replicated params and grads, sharded optimizer state)"
     trainer = Trainer(model, tcfg, engine=engine)
 
     n_batches = args.warmup + args.steps
@@ -247,6 +256,7 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": 2 * B * S * 8,
                     "d2h_bytes_per_step": 4},
             "gpu_launches": launches,
+            "resident_bytes_per_rank": memory,
             "loss_first": float(losses[0]), "loss_last": e2e_losses[-1] if e2e_losses else float(losses[-1]),
         }
         print(json.dumps(out))

@@ -7,6 +7,9 @@ Cases (one JSON line each, printed by rank 0; every time is device-timed with CU
   gemm_rs    GEMM whose epilogue pushes every tile to its owner, owner adds W slots  vs GEMM + NCCL reduce_scatter
   tp_decode  row-parallel OIL4 linear, partial sums reduced in the switch             vs the same GEMM + NCCL all_reduce
   fsdp_step  gradient reduce-scatter + clip + AdamW + parameter all-gather, 2 kernels vs NCCL reduce_scatter + AdamW + all_gather
+  fsdp3_jobs the stage-3 engine's side jobs: parameter all-gather and gradient reduce-scatter of one transformer block
+             and of the embedding unit, alone on many CTAs (vs NCCL all_gather / reduce_scatter) and carried by the helper
+             CTAs of a GEMM (GEMM + job against the GEMM alone: what the overlap costs)
 Roofline of a fused kernel = the slower of FLOPs / measured GEMM peak and bytes that must cross NVLink / 770 GB/s per
 direction per GPU (the measured peer-copy rate); the tensor-parallel decode GEMM is bounded by its weight bytes / HBM.
 """
@@ -113,6 +116,63 @@ def main():
             link_bytes = (world - 1) * S * E * 2          # bf16 partial tiles this GPU pushes to the owners
             roof = max(flops / (tf * 1e12), link_bytes / (LINK_GBS * 1e9)) * 1e6
             report("gemm_rs", fu, bu, roof, {"M": T, "N": E, "K": F, "gemm_only_us": round(flops / (tf * 1e12) * 1e6, 1)})
+
+    if want("fsdp3_jobs") and world > 1:
+        from innova_b200.models import DenseModel, gpt2_small
+        from innova_b200.parallel.fsdp3 import FSDP3Engine, JOB_GATHER, JOB_REDUCE
+        model = DenseModel(gpt2_small(num_layers=2), dtype=torch.bfloat16, device=dev)
+        eng = FSDP3Engine(model)
+        xg = (torch.randn(65536, 768, device=dev, generator=g) * 0.5).bfloat16()
+        wg = (torch.randn(2304, 768, device=dev, generator=g) * 0.02).bfloat16()
+        yg = torch.empty(65536, 2304, dtype=torch.bfloat16, device=dev)
+        gemm_flops = 2.0 * 65536 * 2304 * 768
+        gemm_alone = timed(lambda: ops.gemm(xg, wg, out=yg), a.iters)
+        for l, label in ((1, "block"), (0, "embeddings")):
+            u = eng.units[l]
+            for kind, name in ((JOB_GATHER, "gather"), (JOB_REDUCE, "reduce")):
+                per_rank = u.n * (2 if kind == JOB_GATHER else 4)
+                item = lambda: [kind, l, 0, per_rank] + ([0] if kind == JOB_REDUCE else [])
+                q = eng._gathers if kind == JOB_GATHER else eng._reduces
+
+                def solo():
+                    q.append(item())
+                    eng._flush(q)
+                    eng._pieces = 0
+
+                if kind == JOB_GATHER:
+                    full = torch.empty(u.size, dtype=torch.bfloat16, device=dev)
+                    mine = eng.shard16[u.soff:u.soff + u.n]
+                    base = lambda: dist.all_gather_into_tensor(full, mine)
+                else:
+                    full32 = eng.gslots[l % 3][:u.size]
+                    mine32 = torch.empty(u.n, dtype=torch.float32, device=dev)
+
+                    def base():
+                        dist.reduce_scatter_tensor(mine32, full32)
+                        mine32.mul_(1.0 / world)
+                fu, bu = timed(solo, a.iters), timed(base, a.iters)
+                link_bytes = (world - 1) * per_rank
+                roof = link_bytes / (LINK_GBS * 1e9) * 1e6
+                extra = {"unit": label, "bytes_per_rank": per_rank, "ctas": eng.solo_ctas}
+                report(f"fsdp3_{name}_alone", fu, bu, roof, extra)
+                if l == 1:
+                    # the same collective cut into the pieces the engine would give GEMMs of this size, each carried by one GEMM
+                    def ride():
+                        q.append(item())
+                        n = 0
+                        while q:
+                            ops.gemm(xg, wg, out=yg)
+                            n += 1
+                        eng._pieces = 0
+                        return n
+                    n_gemms = ride()
+                    ru = timed(ride, a.iters)
+                    roof2 = max(n_gemms * gemm_flops / (tf * 1e12), link_bytes / (LINK_GBS * 1e9)) * 1e6
+                    report(f"fsdp3_{name}_in_gemm", ru, n_gemms * gemm_alone + bu, roof2,
+                           {"unit": label, "gemms": n_gemms, "gemm_alone_us": round(gemm_alone, 1), "helper_ctas": eng.helper_ctas,
+                            "overhead_vs_gemm_alone": round(ru / (n_gemms * gemm_alone) - 1.0, 4)})
+        rt.check_status()
+        del eng, model
 
     if want("tp_decode") and world > 1:
         from innova_b200.ops.oil_linear import oil_linear, quantize_weight

@@ -22,6 +22,7 @@ f32 = C.c_float
 
 _CUDA_SIGS = {
     "inv_gemm_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, i32, f32, vp, vp, i32],
+    "inv_gemm_bf16_job": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, vp, i32, i32, f32, vp, vp, vp],
     "inv_norm_fwd": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, i32, vp],
     "inv_norm_bwd_grid": [i32],
     "inv_norm_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],

@@ -101,33 +101,41 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(__nv_bfloat16
     if (lse_out) lse_out[row] = lse;
   }
   if (!write_grad) return;
-  __syncthreads();  // x[label] has been read before anyone overwrites it
-  const float inv_s = 1.f / s;
+  // Second pass: p = exp2(x * log2(e) - (m * log2(e) + log2(s))) with the packed bf16x2 exponential: two results per
+  // MUFU instruction, and the result is stored as bf16 anyway. (With one fp32 exponential per element in each pass the
+  // kernel was bound by the special-function unit, not by memory.) The label's column is rewritten in fp32 afterwards.
   const float g = valid ? gscale : 0.f;
-  const float sm_uniform = smoothing / V;
+  const float kL2E = 1.4426950408889634f;
+  const float c = -(m * kL2E + __log2f(s));
+  const uint32_t g2 = pack_bf16x2(g, g);
+  const uint32_t ug2 = pack_bf16x2(-g * smoothing / V, -g * smoothing / V);
+  const float xl = valid ? __bfloat162float(x[label]) : 0.f;
+  __syncthreads();  // x[label] has been read by every thread before anyone overwrites it
   for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
     uint4 v = *reinterpret_cast<const uint4*>(x + i * 8);
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-    float f[8];
+    uint32_t o[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      float2 t = __bfloat1622float2(h[j]);
-      f[2 * j] = t.x;
-      f[2 * j + 1] = t.y;
+      const float2 t = __bfloat1622float2(h[j]);
+      const uint32_t e = ex2_bf16x2(pack_bf16x2_int(fmaf(t.x, kL2E, c), fmaf(t.y, kL2E, c)));
+      asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(o[j]) : "r"(e), "r"(g2), "r"(ug2));
     }
+    if (i * 8 + 8 > V) {  // the vector that straddles the end of the vocabulary, and the padding behind it
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int col = i * 8 + j;
-      float p = __expf(f[j] - m) * inv_s;
-      float d = p - sm_uniform - (col == label ? (1.f - smoothing) : 0.f);
-      f[j] = col < V ? d * g : 0.f;
+      for (int j = 0; j < 4; ++j) {
+        if (i * 8 + 2 * j >= V) o[j] = 0u;
+        else if (i * 8 + 2 * j + 1 >= V) o[j] &= 0x0000ffffu;
+      }
     }
-    uint4 o;
-    o.x = pack_bf16x2(f[0], f[1]);
-    o.y = pack_bf16x2(f[2], f[3]);
-    o.z = pack_bf16x2(f[4], f[5]);
-    o.w = pack_bf16x2(f[6], f[7]);
-    *reinterpret_cast<uint4*>(x + i * 8) = o;
+    *reinterpret_cast<uint4*>(x + i * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  if (valid) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const float pl = __expf(xl - m) / s;
+      x[label] = __float2bfloat16((pl - smoothing / V - (1.f - smoothing)) * g);
+    }
   }
 }
 

@@ -2,6 +2,7 @@
 #pragma once
 #include "sm100_common.cuh"
 #include "inv_api.h"
+#include "side_job.cuh"
 
 namespace inv {
 
@@ -18,7 +19,6 @@ struct GemmParams {
   int epilogue;
   float alpha;
   int* status;
-  int swap_lbo_sbo;  // debug aid for MN-major descriptors
   // Grouped (mixture-of-experts) operation, single-CTA kernel only. Rows of A are grouped in
   // segments that start on multiples of 128 rows (csrc/moe.cu).
   //   1: C[rows of group e] = A[rows of group e] * B_e^T. tile_expert[m_tile] gives e (-1: unused tile);
@@ -50,6 +50,9 @@ struct GemmParams {
   // after this rank so the ranks never all write to the same destination.
   int rs_world = 0, rs_rank = 0, rs_shard_rows = 0;
   float* rs_dst[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  // A collective of the sharded data-parallel engine carried by the first side.n_ctas CTAs of the grid (side_job.cuh);
+  // CTA-pair kernel only, not together with a fused all-gather.
+  SideJob side = {};
 };
 
 // 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows of `ld` elements; 128B swizzle.
@@ -61,8 +64,12 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_
 // bf16 results go either straight to global memory (stg_c == nullptr) or into this thread's 128-byte
 // row of a 32-row x 64-column staging box in shared memory (128B swizzle), from which the warp
 // issues one TMA store; `sub` says which 32-column half of the box these columns are.
+// `stg_in` (optional): this thread's 128-byte row of a box of the same shape and swizzle that a TMA load filled with
+// the epilogue's second operand (residual / pre-activation); it may be the same box as `stg_c` (each thread reads its
+// own 16-byte slots before it overwrites them).
 __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& p, int row, bool row_ok, int col0, const uint32_t* r,
-                                                    uint8_t* stg_c = nullptr, uint8_t* stg_aux = nullptr, int sub = 0, int lane = 0) {
+                                                    uint8_t* stg_c = nullptr, uint8_t* stg_aux = nullptr, int sub = 0, int lane = 0,
+                                                    const uint8_t* stg_in = nullptr) {
     float v[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
@@ -105,7 +112,8 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& p, int row
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           if (col0 + g * 8 < p.N) {
-            uint4 av = *reinterpret_cast<const uint4*>(ap + g * 8);
+            const uint4 av = stg_in ? *reinterpret_cast<const uint4*>(stg_in + (((sub * 4 + g) ^ (lane & 7)) << 4))
+                                    : *reinterpret_cast<const uint4*>(ap + g * 8);
             const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {

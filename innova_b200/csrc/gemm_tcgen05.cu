@@ -185,10 +185,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // 64-element groups along MN are one box (8192 B) apart, 8-row groups along K 1024 B apart.
       uint32_t a_lbo = A_MN ? 8192u : 16u, a_sbo = 1024u;
       uint32_t b_lbo = B_MN ? 8192u : 16u, b_sbo = 1024u;
-      if (p.swap_lbo_sbo) {
-        if (A_MN) { uint32_t t = a_lbo; a_lbo = a_sbo; a_sbo = t; }
-        if (B_MN) { uint32_t t = b_lbo; b_lbo = b_sbo; b_sbo = t; }
-      }
       const uint32_t a_kstep = A_MN ? 2048u : 32u;
       const uint32_t b_kstep = B_MN ? 2048u : 32u;
       // One thread executes a dependent instruction every few cycles, so everything that can be is hoisted out of the
@@ -336,9 +332,9 @@ int gemm_2cta_dispatch(const void* A, const void* B, const GemmParams& p0, int l
 
 using namespace inv;
 
-extern "C" int inv_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int a_mn,
-                             int b_mn, int epilogue, const void* bias, const void* aux_in, int ld_aux, void* aux_out, int c_f32,
-                             int split_k, float alpha, int* status, void* stream, int debug_flags) {
+static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int a_mn,
+                         int b_mn, int epilogue, const void* bias, const void* aux_in, int ld_aux, void* aux_out, int c_f32,
+                         int split_k, float alpha, int* status, void* stream, int kernel_select, const SideJob* job) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   // TMA needs 16-byte aligned bases and row pitches; the vector epilogue needs N % 8 == 0.
   if ((lda % 8) || (ldb % 8) || (ldc % (c_f32 ? 4 : 8)) || (N % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
@@ -352,7 +348,8 @@ extern "C" int inv_gemm_bf16(const void* A, const void* B, void* C, int M, int N
     cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
     if (g_num_sms <= 0) g_num_sms = 148;
   }
-  if (!(debug_flags & 2) && M > 128 && N > 128) {
+  if (job != nullptr && !(kernel_select != 1 && M > 128 && N > 128)) return -ERR_BAD_ARG;  // only the CTA-pair kernel carries side jobs
+  if (kernel_select != 1 && M > 128 && N > 128) {
     // large problems: 256x256 tiles on CTA pairs (gemm_tcgen05_2cta.cu)
     GemmParams q;
     q.M = M; q.N = N; q.K = K; q.split_k = split_k;
@@ -364,9 +361,9 @@ extern "C" int inv_gemm_bf16(const void* A, const void* B, void* C, int M, int N
     q.epilogue = epilogue;
     q.alpha = alpha;
     q.status = status;
-    q.swap_lbo_sbo = debug_flags;
     q.group_mode = 0; q.num_groups = 1; q.tile_expert = nullptr; q.group_offsets = nullptr; q.group_rows_b = 0;
     q.group_stride_bias = 0; q.group_stride_c = 0;
+    if (job != nullptr) q.side = *job;
     return gemm_2cta_dispatch(A, B, q, lda, ldb, a_mn, b_mn, g_num_sms, reinterpret_cast<cudaStream_t>(stream));
   }
   CUtensorMap ta, tb;
@@ -396,7 +393,6 @@ extern "C" int inv_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   p.epilogue = epilogue;
   p.alpha = alpha;
   p.status = status;
-  p.swap_lbo_sbo = debug_flags & 1;
   p.group_mode = 0; p.num_groups = 1; p.tile_expert = nullptr; p.group_offsets = nullptr; p.group_rows_b = 0;
   p.group_stride_bias = 0; p.group_stride_c = 0;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
@@ -410,6 +406,22 @@ extern "C" int inv_gemm_bf16(const void* A, const void* B, void* C, int M, int N
 }
 
 
+extern "C" int inv_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int a_mn,
+                             int b_mn, int epilogue, const void* bias, const void* aux_in, int ld_aux, void* aux_out, int c_f32,
+                             int split_k, float alpha, int* status, void* stream, int kernel_select) {
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, epilogue, bias, aux_in, ld_aux, aux_out, c_f32, split_k, alpha, status,
+                        stream, kernel_select, nullptr);
+}
+
+// The same GEMM with a side job (side_job.cuh) run by the first job->n_ctas CTAs of its grid. Only problems that take
+// the CTA-pair kernel (M > 128 and N > 128) can carry one; others are refused.
+extern "C" int inv_gemm_bf16_job(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int a_mn,
+                                 int b_mn, int epilogue, const void* bias, const void* aux_in, int ld_aux, void* aux_out, int c_f32,
+                                 int split_k, float alpha, int* status, void* stream, const void* job) {
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, epilogue, bias, aux_in, ld_aux, aux_out, c_f32, split_k, alpha, status,
+                        stream, 0, reinterpret_cast<const SideJob*>(job));
+}
+
 static void fill_plain(GemmParams& p, int M, int N, int K, void* C, int ldc, int c_f32, const void* bias, const void* aux_in, int ld_aux,
                        void* aux_out, int epilogue, float alpha, int* status) {
   p.M = M; p.N = N; p.K = K; p.split_k = 1;
@@ -418,7 +430,7 @@ static void fill_plain(GemmParams& p, int M, int N, int K, void* C, int ldc, int
   p.aux_in = reinterpret_cast<const __nv_bfloat16*>(aux_in);
   p.ld_aux = ld_aux;
   p.aux_out = reinterpret_cast<__nv_bfloat16*>(aux_out);
-  p.epilogue = epilogue; p.alpha = alpha; p.status = status; p.swap_lbo_sbo = 0;
+  p.epilogue = epilogue; p.alpha = alpha; p.status = status;
   p.group_mode = 0; p.num_groups = 1; p.tile_expert = nullptr; p.group_offsets = nullptr; p.group_rows_b = 0;
   p.group_stride_bias = 0; p.group_stride_c = 0;
 }
@@ -537,7 +549,7 @@ extern "C" int inv_gemm_grouped(const void* A, const void* B, void* C, int M, in
   p.epilogue = epilogue;
   p.alpha = 1.0f;
   p.status = status;
-  p.swap_lbo_sbo = 0;
+ 
   p.group_mode = group_mode; p.num_groups = num_groups; p.tile_expert = tile_expert; p.group_offsets = group_offsets;
   p.group_rows_b = group_rows_b; p.group_stride_bias = group_stride_bias; p.group_stride_c = group_stride_c;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;

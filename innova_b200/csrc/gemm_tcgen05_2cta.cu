@@ -25,7 +25,7 @@ constexpr int A_STAGE = 128 * BK * 2;  // this CTA's 128 rows of A
 constexpr int B_STAGE = 128 * BK * 2;  // this CTA's 128 columns of B
 constexpr int THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
 constexpr int STAGING = 8 * 8192;     // per epilogue warp: a 32x64 bf16 box for C and one for the pre-activation
-constexpr int SMEM_BYTES = STAGES * (A_STAGE + B_STAGE) + STAGING + 1024 + 256;
+constexpr int SMEM_BYTES = STAGES * (A_STAGE + B_STAGE) + STAGING + 1024 + 384;  // + alignment slack + barriers
 constexpr int TMEM_COLS = 512;
 }  // namespace g2
 
@@ -135,16 +135,18 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   uint64_t* empty_bar = full_bar + STAGES;                                                 // one set per CTA
   uint64_t* tmem_full = empty_bar + STAGES;                                                // one set per CTA
   uint64_t* tmem_empty = tmem_full + 2;                                                    // used in the leader
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* aux_bar = tmem_empty + 2;  // two per epilogue warp: "second operand box has landed" (TMA loads of the residual / pre-activation)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_bar + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta = cluster_ctarank();
   const bool leader = cta == 0;
   // with a fused all-gather the first clusters of the grid only copy; they own no barriers and no tensor memory
-  const int n_copy = p.ag_world > 1 ? p.ag_copy_ctas : 0;
+  const int n_copy = p.ag_world > 1 ? p.ag_copy_ctas : (p.side.kind != JOB_NONE ? p.side.n_ctas : 0);
   if ((int)blockIdx.x < n_copy) {
-    ag_copier(p, 256, smem, full_bar, abort_flag);
+    if (p.ag_world > 1) ag_copier(p, 256, smem, full_bar, abort_flag);
+    else run_side_job(p.side, (int)blockIdx.x, smem);
     return;
   }
   const int pair = ((int)blockIdx.x - n_copy) >> 1, npairs = ((int)gridDim.x - n_copy) >> 1;
@@ -164,6 +166,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       mbar_init(&tmem_full[a], 1);
       mbar_init(&tmem_empty[a], 16);  // 8 epilogue warps in each CTA
     }
+    for (int i = 0; i < 16; ++i) mbar_init(&aux_bar[i], 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
@@ -265,15 +268,43 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const int half = (warp - 2) >> 2;
     const bool staged = !p.c_f32;
     const bool staged_aux = staged && p.epilogue == EPI_GELU && p.aux_out != nullptr;
+    // Second operand of the epilogue (residual to add, pre-activation of the GELU backward) through TMA: the warp's two
+    // 4 KB boxes alternate; box i is loaded while box i-1 is computed, the result overwrites the operand in place and
+    // leaves through a TMA store. Per-thread global loads of a row-strided operand serialise on memory latency
+    // (sixteen dependent round trips per tile) and made these epilogues three times as long as the main loop.
+    const bool aux_tma = staged && (p.epilogue == EPI_DGELU || p.epilogue == EPI_ADD);
     uint8_t* my_stage = sStage + (warp - 2) * 8192;
+    uint64_t* my_aux_bar = aux_bar + (warp - 2) * 2;
+    const int row_in_tile = (int)cta * 128 + q * 32;
+    // (w, j): j-th 64-column box of this warp in work unit w; false when the unit or the box does not exist
+    auto box_of = [&](int w, int j, int& col0, int& row0) -> bool {
+      if (w >= total_work) return false;
+      const WorkUnit2 u = decode_work2(w, p, m_tiles, n_tiles, kb_total, kb_per_split);
+      col0 = u.n0 + (half * 4 + 2 * j) * 32;
+      row0 = u.m0 + row_in_tile;
+      return col0 < p.N;
+    };
+    uint32_t boxes_done = 0;       // boxes this warp has computed: box i uses buffer i & 1, phase (i >> 1) & 1 of its barrier
+    int nw = pair, nj = 0;          // next box to prefetch
+    auto prefetch_next = [&](uint32_t box_index) {   // lane 0 only
+      int col0, row0;
+      while (nw < total_work && !box_of(nw, nj, col0, row0)) { nw += npairs; nj = 0; }   // a missing box 0 or 1 ends the unit for this warp
+      if (nw >= total_work) return;
+      const uint32_t b = box_index & 1;
+      mbar_expect_tx(&my_aux_bar[b], 4096);
+      tma_load_2d(my_stage + b * 4096, &tmap_aux, &my_aux_bar[b], col0, row0);
+      if (nj == 0) nj = 1; else { nj = 0; nw += npairs; }
+    };
+    if (aux_tma && lane == 0) prefetch_next(0);
     int tile_i = 0;
-    for (int w = pair; w < total_work; w += npairs, ++tile_i) {
+    bool ok = true;
+    for (int w = pair; ok && w < total_work; w += npairs, ++tile_i) {
       const WorkUnit2 u = decode_work2(w, p, m_tiles, n_tiles, kb_total, kb_per_split);
       const int acc = tile_i & 1;
       const uint32_t acc_ph = (tile_i >> 1) & 1;
       if (!mbar_wait_warp(&tmem_full[acc], acc_ph, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
-      const int row = u.m0 + (int)cta * 128 + q * 32 + lane;
+      const int row = u.m0 + row_in_tile + lane;
       const bool row_ok = row < p.M;
       const CUtensorMap* c_map = &tmap_c;
       int row_shift = 0;
@@ -283,7 +314,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         row_shift = owner * p.rs_shard_rows;
       }
       const uint32_t t_row = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
-      const int row0_abs = u.m0 + (int)cta * 128 + q * 32;
+      const int row0_abs = u.m0 + row_in_tile;
 #pragma unroll 1
       for (int c = half * 4; c < half * 4 + 4; c += 2) {
         const int col0 = u.n0 + c * 32;
@@ -292,8 +323,24 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         tmem_ld_32x32(t_row + c * 32, r0);
         tmem_ld_32x32(t_row + c * 32 + 32, r1);
         tmem_ld_wait();
-        if (p.swap_lbo_sbo & 4) continue;
-        if (staged) {
+        if (aux_tma) {
+          const uint32_t b = boxes_done & 1;
+          if (lane == 0) {
+            tma_store_wait_read();          // the other buffer's store (box i-1) has left shared memory
+            prefetch_next(boxes_done + 1);  // ... so box i+1 may land there while box i is computed
+          }
+          if (!mbar_wait_warp(&my_aux_bar[b], (boxes_done >> 1) & 1, abort_flag, p.status, ERR_WAIT_MISC)) { ok = false; break; }
+          uint8_t* sc = my_stage + b * 4096 + lane * 128;
+          gemm_epilogue_chunk(p, row, row_ok, col0, r0, sc, nullptr, 0, lane, sc);
+          if (col0 + 32 < p.N) gemm_epilogue_chunk(p, row, row_ok, col0 + 32, r1, sc, nullptr, 1, lane, sc);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(c_map, my_stage + b * 4096, col0, row0_abs - row_shift);
+            tma_store_commit();
+          }
+          ++boxes_done;
+        } else if (staged) {
           // bf16 output: registers -> swizzled 32x64 box in shared memory -> one TMA store per box
           if (lane == 0) tma_store_wait_read();  // the previous box of this warp has left shared memory
           __syncwarp();
@@ -313,6 +360,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           if (col0 + 32 < p.N) gemm_epilogue_chunk(p, row, row_ok, col0 + 32, r1);
         }
       }
+      if (!ok) break;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(mapa_shared(smem_u32(&tmem_empty[acc]), 0));
@@ -370,6 +418,9 @@ int gemm_2cta_dispatch(const void* A, const void* B, const GemmParams& p0, int l
     if (p.epilogue == EPI_GELU && p.aux_out != nullptr &&
         (rc = make_tmap_2d_bf16(&tx, p.aux_out, (uint64_t)p.N, (uint64_t)p.M, (uint64_t)p.ld_aux, 64, 32)))
       return rc;
+    if ((p.epilogue == EPI_DGELU || p.epilogue == EPI_ADD) &&   // the epilogue's second operand arrives through TMA loads
+        (rc = make_tmap_2d_bf16(&tx, p.aux_in, (uint64_t)p.N, (uint64_t)p.M, (uint64_t)p.ld_aux, 64, 32)))
+      return rc;
   }
   const int kb_total = (p.K + BK - 1) / BK;
   int split_k = p.split_k < 1 ? 1 : p.split_k;
@@ -381,8 +432,17 @@ int gemm_2cta_dispatch(const void* A, const void* B, const GemmParams& p0, int l
   }
   p.split_k = split_k;
   const long total = (long)((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * split_k;
-  const int n_copy = p.ag_world > 1 ? (p.ag_copy_ctas & ~1) : 0;  // whole clusters; the whole grid must be resident at once
-  p.ag_copy_ctas = n_copy;
+  // helper CTAs come in whole clusters; the whole grid must be resident at once
+  int n_copy = 0;
+  if (p.ag_world > 1) {
+    n_copy = p.ag_copy_ctas & ~1;
+    p.side.kind = JOB_NONE;
+  } else if (p.side.kind != JOB_NONE) {
+    n_copy = p.side.n_ctas & ~1;
+    if (n_copy < 2) n_copy = 2;
+    p.side.n_ctas = n_copy;
+  }
+  p.ag_copy_ctas = p.ag_world > 1 ? n_copy : 0;
   const int max_pairs = (num_sms - n_copy) / 2;
   const int pairs = (int)(total < max_pairs ? total : max_pairs);
   const int grid = pairs * 2 + n_copy;

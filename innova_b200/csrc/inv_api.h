@@ -21,7 +21,7 @@ enum {
 // = 1: operand stored [K, rows] row-major. lda/ldb/ldc/ld_aux in elements.
 int inv_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int a_mn, int b_mn,
                   int epilogue, const void* bias, const void* aux_in, int ld_aux, void* aux_out, int c_f32, int split_k,
-                  float alpha, int* status, void* stream, int debug_flags);
+                  float alpha, int* status, void* stream, int kernel_select);
 
 #ifdef __cplusplus
 }

@@ -228,7 +228,7 @@ __global__ void __launch_bounds__(256) norm_bwd_small_kernel(const __nv_bfloat16
   }
   // The next row's x and dy are in flight (packed, 2 * NCH registers of 16 bytes) while this row is reduced and
   // written: one row per warp at a time would expose a full memory round trip per row.
-  uint4 nx[NCH], nd[NCH];
+  uint4 nx[NCH], nd[NCH], nr[NCH];   // nr: the gradient arriving on the residual stream, when there is one
   float nmean = 0.f, nrstd = 0.f;
   auto prefetch = [&](int row) {
     const __nv_bfloat16* xr = x + (size_t)row * D;
@@ -239,6 +239,7 @@ __global__ void __launch_bounds__(256) norm_bwd_small_kernel(const __nv_bfloat16
       if (c < D) {
         nx[k] = *reinterpret_cast<const uint4*>(xr + c);
         nd[k] = *reinterpret_cast<const uint4*>(dyr + c);
+        if (dres) nr[k] = *reinterpret_cast<const uint4*>(dres + (size_t)row * D + c);
       }
     }
     nmean = RMS ? 0.f : mean_in[row];
@@ -249,6 +250,7 @@ __global__ void __launch_bounds__(256) norm_bwd_small_kernel(const __nv_bfloat16
     const float mean = nmean;
     const float rstd = nrstd;
     float xh[NCH][8], d[NCH][8];
+    uint4 rr[NCH];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
@@ -256,6 +258,7 @@ __global__ void __launch_bounds__(256) norm_bwd_small_kernel(const __nv_bfloat16
       if (c < D) {
         unpack8(nx[k], xh[k]);
         unpack8(nd[k], d[k]);
+        if (dres) rr[k] = nr[k];
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) xh[k][j] = mean, d[k][j] = 0.f;
@@ -288,7 +291,7 @@ __global__ void __launch_bounds__(256) norm_bwd_small_kernel(const __nv_bfloat16
       if (c < D) {
         if (dres) {
           float r[8];
-          load8(dres + (size_t)row * D + c, r);
+          unpack8(rr[k], r);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] += r[j];
         }

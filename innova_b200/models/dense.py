@@ -37,6 +37,10 @@ class Norm(nn.Module):
             return ops.layer_norm(x, self.weight, self.bias, self.eps)
         return ops.rms_norm(x, self.weight, self.eps)
 
+    def with_residual(self, x):
+        """(norm(x), x) with the two gradients summed inside the norm's backward kernel."""
+        return ops.norm_residual(x, self.weight, self.bias, self.eps, rms=self.kind != "layernorm")
+
 
 class Attention(nn.Module):
     def __init__(self, cfg: TransformerConfig, dtype):
@@ -107,8 +111,10 @@ class TransformerBlock(nn.Module):
             # GPT-NeoX form: x + attn(norm1(x)) + ffn(norm2(x))
             a = self.attention(self.attention_norm(x), x, rope, positions)
             return self.ffn(self.ffn_norm(x), a)
-        x = self.attention(self.attention_norm(x), x, rope, positions)
-        return self.ffn(self.ffn_norm(x), x)
+        h, x = self.attention_norm.with_residual(x)
+        x = self.attention(h, x, rope, positions)
+        h, x = self.ffn_norm.with_residual(x)
+        return self.ffn(h, x)
 
 
 class DenseModel(nn.Module):

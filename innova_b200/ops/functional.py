@@ -47,26 +47,59 @@ class _NormFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x2, gamma, beta, mean, rstd = ctx.saved_tensors
-        T, D = x2.shape
-        dy2 = dy.reshape(T, D)
-        if not dy2.is_contiguous():
-            dy2 = dy2.contiguous()
-        dx = torch.empty_like(x2)
-        grid = rt.lib().inv_norm_bwd_grid(T)
-        scr = rt.scratch("norm_bwd", grid * 2 * D * 4, x2.device)
-        mg_g = getattr(gamma, "main_grad", None)
-        mg_b = getattr(beta, "main_grad", None) if beta is not None else None
-        dg = mg_g if mg_g is not None else torch.zeros(D, dtype=torch.float32, device=x2.device)
-        db = None
-        if beta is not None:
-            db = mg_b if mg_b is not None else torch.zeros(D, dtype=torch.float32, device=x2.device)
-        rt.check(rt.lib().inv_norm_bwd(dy2.data_ptr(), x2.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), 0,
-                                       dx.data_ptr(), dg.data_ptr(), rt.ptr(db), scr.data_ptr(), T, D, int(ctx.rms),
-                                       rt.stream_ptr()), "inv_norm_bwd")
-        g_out = None if mg_g is not None else dg.to(gamma.dtype)
-        b_out = None if (beta is None or mg_b is not None) else db.to(beta.dtype)
-        return dx.view(ctx.xshape), g_out, b_out, None, None
+        return _norm_backward(ctx, dy, None)
+
+
+def _norm_backward(ctx, dy, dres):
+    """dx = norm'(dy) (+ dres, the gradient that arrives on the residual stream, added in the same kernel)."""
+    x2, gamma, beta, mean, rstd = ctx.saved_tensors
+    T, D = x2.shape
+    if dy is None:   # the normalised branch was not used
+        return (dres.reshape(ctx.xshape) if dres is not None else None), None, None, None, None
+    dy2 = dy.reshape(T, D)
+    if not dy2.is_contiguous():
+        dy2 = dy2.contiguous()
+    dr2 = None
+    if dres is not None:
+        dr2 = dres.reshape(T, D)
+        if not dr2.is_contiguous():
+            dr2 = dr2.contiguous()
+    dx = torch.empty_like(x2)
+    grid = rt.lib().inv_norm_bwd_grid(T)
+    scr = rt.scratch("norm_bwd", grid * 2 * D * 4, x2.device)
+    mg_g = getattr(gamma, "main_grad", None)
+    mg_b = getattr(beta, "main_grad", None) if beta is not None else None
+    dg = mg_g if mg_g is not None else torch.zeros(D, dtype=torch.float32, device=x2.device)
+    db = None
+    if beta is not None:
+        db = mg_b if mg_b is not None else torch.zeros(D, dtype=torch.float32, device=x2.device)
+    rt.check(rt.lib().inv_norm_bwd(dy2.data_ptr(), x2.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), rt.ptr(dr2),
+                                   dx.data_ptr(), dg.data_ptr(), rt.ptr(db), scr.data_ptr(), T, D, int(ctx.rms),
+                                   rt.stream_ptr()), "inv_norm_bwd")
+    g_out = None if mg_g is not None else dg.to(gamma.dtype)
+    b_out = None if (beta is None or mg_b is not None) else db.to(beta.dtype)
+    return dx.view(ctx.xshape), g_out, b_out, None, None
+
+
+class _NormResFn(torch.autograd.Function):
+    """(norm(x), x): the second output is the residual stream handed on unchanged, so that the gradient coming back on
+    it is added inside the norm's backward kernel instead of by a separate pass over the activations."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps, rms):
+        y = _NormFn.forward(ctx, x, gamma, beta, eps, rms)
+        return y, x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, dres):
+        return _norm_backward(ctx, dy, dres)
+
+
+def norm_residual(x, gamma, beta, eps=1e-5, rms=False):
+    """Returns (norm(x), x) for a pre-norm residual block: feed the second value to the block's residual add."""
+    if not x.is_cuda:
+        return (rms_norm(x, gamma, eps) if rms else layer_norm(x, gamma, beta, eps)), x
+    return _NormResFn.apply(x, gamma, None if rms else beta, eps, rms)
 
 
 def layer_norm(x, gamma, beta, eps=1e-5):
@@ -330,7 +363,7 @@ class _LMHeadCEFn(torch.autograd.Function):
         return dxo, dw, None, None, None, None, None
 
 
-def lm_head_cross_entropy(x, weight, labels, vocab=None, chunk=8192, smoothing=0.0, grad_scale=1.0):
+def lm_head_cross_entropy(x, weight, labels, vocab=None, chunk=16384, smoothing=0.0, grad_scale=1.0):
     """Fused LM head + mean cross entropy. ``weight`` is [V_padded, D]; columns >= vocab are ignored."""
     vocab = weight.shape[0] if vocab is None else vocab
     if not x.is_cuda:

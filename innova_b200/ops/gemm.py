@@ -18,7 +18,19 @@ from . import runtime as rt
 EPI_NONE, EPI_GELU, EPI_DGELU, EPI_ADD, EPI_ATOMIC = 0, 1, 2, 3, 4
 NUM_SMS = 148
 import os
-_debug_flags = int(os.environ.get("INV_GEMM_DEBUG", "0"))
+# 0: tile shape chosen by problem size (256x256 CTA pairs for large problems); 1: always the single-CTA 128x256 kernel
+_kernel_select = int(os.environ.get("INV_GEMM_KERNEL", "0"))
+
+
+# Side jobs (csrc/side_job.cuh): a sharded data-parallel engine registers a provider; every GEMM that takes the CTA-pair
+# kernel and is at least `_side_job_min_flops` large asks it for a collective to carry in helper CTAs of its grid.
+_side_job_provider = None
+_side_job_min_flops = 0.0
+
+
+def set_side_job_provider(fn, min_flops: float = 0.0):
+    global _side_job_provider, _side_job_min_flops
+    _side_job_provider, _side_job_min_flops = fn, min_flops
 
 
 def _split_k_for(M, N, K):
@@ -66,10 +78,21 @@ def gemm(a, b, out=None, *, a_mn=False, b_mn=False, M=None, N=None, K=None, epil
         ld_aux = aux_in.stride(0)
     elif aux_out is not None:
         ld_aux = aux_out.stride(0)
+    job = None
+    if _side_job_provider is not None and M > 128 and N > 128 and _kernel_select != 1 and 2.0 * M * N * K >= _side_job_min_flops:
+        job = _side_job_provider(2.0 * M * N * K)
+    if job is not None:
+        import ctypes
+        rc = rt.lib().inv_gemm_bf16_job(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn),
+            epilogue, rt.ptr(bias), rt.ptr(aux_in), ld_aux, rt.ptr(aux_out), int(c_f32), split_k, float(alpha),
+            rt.status_tensor(a.device).data_ptr(), rt.stream_ptr(), ctypes.addressof(job))
+        rt.check(rc, "inv_gemm_bf16_job")
+        return out
     rc = rt.lib().inv_gemm_bf16(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn),
         epilogue, rt.ptr(bias), rt.ptr(aux_in), ld_aux, rt.ptr(aux_out), int(c_f32), split_k, float(alpha),
-        rt.status_tensor(a.device).data_ptr(), rt.stream_ptr(), _debug_flags)
+        rt.status_tensor(a.device).data_ptr(), rt.stream_ptr(), _kernel_select)
     rt.check(rc, "inv_gemm_bf16")
     return out
 

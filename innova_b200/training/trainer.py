@@ -163,6 +163,8 @@ class Trainer:
     def _collect_autograd_grads(self):
         """Gradients that autograd produced in ``.grad`` (CPU path, or ops without a fused
         accumulate) are folded into the fp32 flat gradient."""
+        if getattr(self.engine, "collects_grads", False):
+            return
         for _, p, _, _ in self.engine.entries:
             if p.grad is not None:
                 p.main_grad.add_(p.grad.float())

@@ -78,6 +78,30 @@ def test_gemm_epilogues():
     assert _rel_err(acc, ref + 1.0) < 1e-2
 
 
+@pytest.mark.parametrize("M,N,K", [(20000, 776, 192), (2 * 74 * 256 + 300, 520, 128), (1000, 136, 64)])
+def test_gemm_second_operand_epilogues_tails(M, N, K):
+    """Residual-add and GELU-backward epilogues on the CTA-pair kernel: more tiles than CTA pairs (the operand boxes are
+    fetched one ahead, across tiles), ragged last row and column tiles, a strided second operand, output aliasing it."""
+    from innova_b200 import ops
+    torch.manual_seed(5)
+    dev = _dev()
+    A = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
+    B = (torch.randn(N, K, device=dev) * 0.1).bfloat16()
+    big = torch.randn(M, N + 24, device=dev).bfloat16()
+    aux = big[:, 8:8 + N]                      # row pitch N + 24, 16-byte aligned start
+    ref = A.float() @ B.float().t()
+    out = ops.gemm(A, B, epilogue=ops.EPI_ADD, aux_in=aux)
+    assert _rel_err(out, ref + aux.float()) < 1e-2
+    x = aux.float().requires_grad_(True)
+    F.gelu(x, approximate="tanh").sum().backward()
+    out = ops.gemm(A, B, epilogue=ops.EPI_DGELU, aux_in=aux)
+    assert _rel_err(out, ref * x.grad) < 2e-2
+    res = aux.contiguous()
+    want = ref + res.float()
+    ops.gemm(A, B, out=res, epilogue=ops.EPI_ADD, aux_in=res)
+    assert _rel_err(res, want) < 1e-2
+
+
 def test_gemm_wgrad_shape():
     """dW[N,K] += dY[T,N]^T X[T,K] with a long reduction and split-K chosen by the wrapper."""
     from innova_b200 import ops
