@@ -4,7 +4,8 @@
 oil_inference, oil_tokenizer and oil_trainer exactly as its CMakeLists.txt lists them (CMakeLists.txt:41-153), with the one
 translation unit of oil_trainer that cannot compile on Linux left out (src/hf_streamer.cpp includes <windows.h> and WinHTTP
 unconditionally; nothing else in the trainer refers to it). ``ref_train_bench`` links ``baseline/ref_train_bench.cpp``
-against it. Flags are the reference's own GCC Release flags with AVX2 (cmake/compiler.cmake:30-47) minus ``-march=native``,
+against it, ``ref_quant_oracle`` links ``baseline/ref_quant_oracle.cpp`` (codebook wire form and the whole-tensor
+codebook checkpoint, for the format tests). Flags are the reference's own GCC Release flags with AVX2 (cmake/compiler.cmake:30-47) minus ``-march=native``,
 so that a binary built on one machine runs on another x86-64 host with AVX2.
 
     python baseline/build_ref.py [--reference /path/to/InNova]
@@ -59,7 +60,9 @@ def build(ref: Path | None = None, force: bool = False) -> Path:
     ref = ref or reference_root()
     exe = OUT / "ref_train_bench"
     driver = HERE / "ref_train_bench.cpp"
-    if exe.exists() and not force and exe.stat().st_mtime > driver.stat().st_mtime:
+    oracle = HERE / "ref_quant_oracle.cpp"
+    if exe.exists() and (OUT / "ref_quant_oracle").exists() and not force and exe.stat().st_mtime > driver.stat().st_mtime and \
+            (OUT / "ref_quant_oracle").stat().st_mtime > oracle.stat().st_mtime:
         return exe
     if not (ref / "CMakeLists.txt").exists():
         raise RuntimeError("reference sources not found at %s" % ref)
@@ -86,9 +89,10 @@ def build(ref: Path | None = None, force: bool = False) -> Path:
     if lib.exists():
         lib.unlink()
     subprocess.run(["ar", "rcs", str(lib), *map(str, objs)], check=True)
-    r = subprocess.run([cxx, *FLAGS, *inc, str(driver), str(lib), "-o", str(exe)], capture_output=True, text=True)
-    if r.returncode != 0:
-        raise RuntimeError("ref_train_bench failed to link:\n%s" % r.stderr[-3000:])
+    for src, out in ((driver, exe), (HERE / "ref_quant_oracle.cpp", OUT / "ref_quant_oracle")):
+        r = subprocess.run([cxx, *FLAGS, *inc, str(src), str(lib), "-o", str(out)], capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("%s failed to link:\n%s" % (src.name, r.stderr[-3000:]))
     return exe
 
 

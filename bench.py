@@ -86,6 +86,8 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=12, help="for debugging only; the reported config is 12")
     ap.add_argument("--engine", default="fsdp3", choices=["fsdp3", "zero2"], help="data-parallel engine at N > 1")
+    ap.add_argument("--decode-new", type=int, default=64, help="generated tokens of the decode section (0: skip it)")
+    ap.add_argument("--decode-layers", type=int, default=32, help="for debugging only; the reported decode config is 32")
     return ap.parse_args()
 
 
@@ -131,6 +133,53 @@ class ClockSampler(threading.Thread):
     def summary(self):
         s = sorted(self.samples)
         return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def run_decode(args, rank, world, dev):
+    """The other half of the metric: greedy decode of a Llama-7B-shaped decoder with OIL4 weights and a paged OIL4 KV
+    cache, tensor parallel over the N GPUs, batch 64, 512-token Zipf(1.1) prompts. Device-timed (CUDA events, max over
+    ranks); the end-to-end figure covers prompt ids from pinned host memory to generated tokens back in pinned host memory,
+    prefill and CUDA-graph capture included."""
+    import torch
+    import torch.distributed as dist
+    from innova_b200.models import llama_7b
+    from innova_b200.ops import runtime as rt
+    from innova_b200.parallel.tp import TPDecoder
+    from innova_b200.utils.data import zipf_tokens
+    B, P, NEW = 64, 512, args.decode_new
+    cfg = llama_7b(num_layers=args.decode_layers)
+    dec = TPDecoder(cfg, fmt="oil4", max_batch=B, max_seq=P + NEW + 16, kv_format="oil4", device=dev)
+    host_ids = zipf_tokens(B * P, cfg.vocab_size, 1.1, seed=7).view(B, P).pin_memory()
+    host_out = torch.zeros(B, NEW, dtype=torch.int64).pin_memory()
+    c0 = rt.launch_count()
+    toks, t_prefill, t_decode = dec.generate(host_ids.to(dev), NEW)          # device-timed inside
+    # end to end: host ids in, host tokens out, everything in between
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    ids = host_ids.to(dev, non_blocking=True)
+    toks2, _, _ = dec.generate(ids, NEW)
+    host_out.copy_(toks2, non_blocking=True)
+    e1.record()
+    torch.cuda.synchronize()
+    rt.check_status()
+    t = torch.tensor([t_prefill, t_decode, e0.elapsed_time(e1) / 1e3], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    steps = NEW - 1
+    out = {"metric": "decode_tokens_per_sec", "value": B * steps / float(t[1]), "unit": "tokens/s", "ms_per_step": float(t[1]) / steps * 1e3,
+           "prefill_tokens_per_sec": B * P / float(t[0]),
+           "config": {"model": "llama-7b-shaped (32L d4096 32q/8kv heads swiglu 11008 vocab 32000)" if args.decode_layers == 32
+                      else f"DEBUG {args.decode_layers} layers", "weights": "oil4 (codebook indices, block 32)",
+                      "kv_cache": "oil4 paged(16)", "batch": B, "prompt": P, "new_tokens": NEW, "parallelism": f"tp{world}", "sampling": "greedy",
+                      "cuda_graph": True},
+           "e2e": {"value": B * NEW / float(t[2]), "unit": "tokens/s", "seconds": float(t[2]), "h2d_bytes": B * P * 8, "d2h_bytes": B * NEW * 8,
+                   "includes": "prompt copy, prefill, graph capture, decode, token copy"},
+           "gpu_launches": rt.launch_count() - c0, "weight_bytes_per_gpu": dec.weight_bytes(), "first_tokens": toks[0, :8].tolist()}
+    del dec
+    return out
 
 
 def run_ours(args):
@@ -240,6 +289,17 @@ def run_ours(args):
     ms_e2e, _, _ = timed(e2e_region)
     rt.check_status()
 
+    decode = None
+    if args.decode_new > 0:
+        # training state is no longer needed: release it before the 7B decoder is built
+        trainer = engine = model = dev_batches = None
+        from innova_b200.ops.gemm import set_side_job_provider
+        set_side_job_provider(None)
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        decode = run_decode(args, rank, world, dev)
+
     tokens_per_step = B * S * world
     value = tokens_per_step * args.steps / (ms / 1e3)
     e2e_value = tokens_per_step * args.steps / (ms_e2e / 1e3)
@@ -257,6 +317,7 @@ def run_ours(args):
                     "d2h_bytes_per_step": 4},
             "gpu_launches": launches,
             "resident_bytes_per_rank": memory,
+            "decode": decode,
             "loss_first": float(losses[0]), "loss_last": e2e_losses[-1] if e2e_losses else float(losses[-1]),
         }
         print(json.dumps(out))

@@ -10,26 +10,39 @@ import time
 def build_server(model_path: str, port: int = 8080, host: str = "127.0.0.1", device=None, rate_limit: float = 0.0, max_new_tokens: int = 256):
     from ..inference.serving import EmbeddingEndpoint, InferenceEngine
     from ..serving.http_server import HTTPServer
-    state = {"engine": InferenceEngine(model_path, device=device)}
+    import threading
+    # One engine = one generator = one paged KV cache whose rows a generation frees and rewrites at its start. HTTP
+    # request threads and WebSocket client threads all end up here, so a generation (the whole stream, not only its
+    # start), an embedding and a model swap each hold this lock from beginning to end.
+    state = {"engine": InferenceEngine(model_path, device=device), "lock": threading.Lock()}
     srv = HTTPServer(port, host)
     srv.set_model_name(model_path.rsplit("/", 1)[-1])
 
+    def _locked_stream(prompt, n):
+        with state["lock"]:
+            yield from state["engine"].stream(prompt, n)
+
     def generate(prompt, n, stream):
-        eng = state["engine"]
         n = min(n, max_new_tokens)
-        return eng.stream(prompt, n) if stream else eng.generate(prompt, n)
+        if stream:
+            return _locked_stream(prompt, n)      # the lock is taken when the first piece is asked for, released with the last
+        with state["lock"]:
+            return state["engine"].generate(prompt, n)
 
     def embed(text):
-        eng = state["engine"]
-        return EmbeddingEndpoint(eng.model, eng.tok).embed(text).tolist()
+        with state["lock"]:
+            eng = state["engine"]
+            return EmbeddingEndpoint(eng.model, eng.tok).embed(text).tolist()
 
     def load(path):
         try:
-            state["engine"] = InferenceEngine(path, device=device)
-            srv.set_model_name(path.rsplit("/", 1)[-1])
-            return True
+            new = InferenceEngine(path, device=device)       # built outside the lock: running generations are not held up
         except Exception:
             return False
+        with state["lock"]:
+            state["engine"] = new
+            srv.set_model_name(path.rsplit("/", 1)[-1])
+        return True
     srv.set_generate_callback(generate)
     srv.set_embeddings_callback(embed)
     srv.set_load_model_callback(load)

@@ -38,7 +38,7 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
 }
 
 // Waits until flags[r] >= epoch for every r < W. Returns false (and records the error) on timeout.
-__device__ bool wait_all_flags(const uint32_t* flags, int W, uint32_t epoch, int* status) {
+__device__ bool wait_all_flags(const uint32_t* flags, int W, uint32_t epoch, int* status, uint64_t limit_ns = PEER_WAIT_NS) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
@@ -51,7 +51,7 @@ __device__ bool wait_all_flags(const uint32_t* flags, int W, uint32_t epoch, int
         const uint64_t now = globaltimer_ns();
         if (t0 == 0) {
           t0 = now;
-        } else if (now - t0 > PEER_WAIT_NS) {
+        } else if (now - t0 > limit_ns) {
           s_ok = 0;
           if (status) atomicCAS(status, 0, ERR_WAIT_PEER);
           break;
@@ -68,7 +68,9 @@ __global__ void signal_peers_kernel(PeerPtrs peer_flags, int W, int rank, uint32
   __threadfence_system();
   if (threadIdx.x < W) st_release_sys(reinterpret_cast<uint32_t*>(peer_flags.p[threadIdx.x]) + rank, epoch);
 }
-__global__ void wait_flags_kernel(const uint32_t* flags, int W, uint32_t epoch, int* status) { wait_all_flags(flags, W, epoch, status); }
+__global__ void wait_flags_kernel(const uint32_t* flags, int W, uint32_t epoch, int* status, uint64_t limit_ns) {
+  wait_all_flags(flags, W, epoch, status, limit_ns);
+}
 
 // Barrier over peer memory whose epoch lives on the device, so that it can sit inside a captured CUDA
 // graph and advance on every replay: bump this rank's counter, publish it to every peer, wait until
@@ -302,7 +304,14 @@ extern "C" int inv_signal_peers(const uint64_t* peer_flags, int W, int rank, uin
 }
 extern "C" int inv_wait_flags(const void* flags, int W, uint32_t epoch, int* status, void* stream) {
   if (W < 1 || W > MAX_RANKS) return -ERR_BAD_ARG;
-  wait_flags_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((const uint32_t*)flags, W, epoch, status);
+  wait_flags_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((const uint32_t*)flags, W, epoch, status, PEER_WAIT_NS);
+  RET_LAUNCH();
+}
+// The same wait with the caller's time limit (nanoseconds of the global timer): after it the kernel writes ERR_WAIT_PEER to
+// *status and returns normally, so the context stays usable. Used to exercise the error path without hanging anything.
+extern "C" int inv_wait_flags_limit(const void* flags, int W, uint32_t epoch, long limit_ns, int* status, void* stream) {
+  if (W < 1 || W > MAX_RANKS || limit_ns < 0) return -ERR_BAD_ARG;
+  wait_flags_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((const uint32_t*)flags, W, epoch, status, (uint64_t)limit_ns);
   RET_LAUNCH();
 }
 

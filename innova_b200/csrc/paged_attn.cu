@@ -229,191 +229,6 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const __nv_bfloat16* 
   }
 }
 
-// OIL4 decode attention, second version. The first one issued one 2-byte global load per value token inside a
-// loop with a run-time trip count, so every page paid sixteen dependent memory latencies. Here a warp
-//   * fetches a page's K and V indices with 16-byte loads (lane = token x half row) one page ahead of use,
-//   * scores the 16 tokens against the G query heads of its KV head,
-//   * expands V once into a per-warp bf16 tile in shared memory (row pitch 272 B: conflict-free for the
-//     16-byte stores and the 8-byte reads) and accumulates P.V from there with the loop fully unrolled.
-template <int D>
-__global__ void __launch_bounds__(128) paged_decode_oil4_kernel(const __nv_bfloat16* __restrict__ q, int ld_q, const int* __restrict__ page_table,
-                                                                int max_pages, const int* __restrict__ seq_lens, int H, int Hkv,
-                                                                const uint8_t* __restrict__ k_pool, const uint8_t* __restrict__ v_pool,
-                                                                const __half* __restrict__ k_scale, const __half* __restrict__ v_scale,
-                                                                float scale, float* __restrict__ part, int splits) {
-  constexpr int MAXG = 8;
-  constexpr int EPL = D / 32;      // output elements per lane
-  constexpr int HALF = D / 2;      // elements per lane in the score phase (two lanes per token)
-  constexpr int NB = HALF / 32;    // 32-element scale blocks per lane
-  constexpr int VP = D + 8;        // bf16 elements per row of the V tile (272 B for D = 128)
-  __shared__ float sq[MAXG][D];
-  __shared__ float sm_m[4][MAXG], sm_l[4][MAXG];
-  constexpr int TILE_BYTES = (4 * PAGE * VP * 2 > 4 * MAXG * D * 4) ? 4 * PAGE * VP * 2 : 4 * MAXG * D * 4;
-  __shared__ __align__(16) unsigned char tile_raw[TILE_BYTES];  // V tiles during the loop, the per-warp outputs afterwards
-  __shared__ float lv[16 * 32];
-  __nv_bfloat16* sv = reinterpret_cast<__nv_bfloat16*>(tile_raw);
-  float (*sm_o)[MAXG][D] = reinterpret_cast<float (*)[MAXG][D]>(tile_raw);
-  for (int i = threadIdx.x; i < 16 * 32; i += blockDim.x) lv[i] = c_kv_levels[i >> 5];
-  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
-  const int G = H / Hkv;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int len = seq_lens[b];
-  const int npages = (len + PAGE - 1) / PAGE;
-  const int per = (npages + splits - 1) / splits;
-  const int p0 = split * per, p1 = min(npages, p0 + per);
-  const float c = scale * 1.4426950408889634f;
-  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
-    const int g = i / D, e = i % D;
-    sq[g][e] = __bfloat162float(q[(long)b * ld_q + (hk * G + g) * D + e]) * c;
-  }
-  __syncthreads();
-  float m[MAXG], l[MAXG], o[MAXG][EPL];
-#pragma unroll
-  for (int g = 0; g < MAXG; ++g) {
-    m[g] = -INFINITY;
-    l[g] = 0.f;
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) o[g][e] = 0.f;
-  }
-  const int t = lane & 15, hf = lane >> 4;
-  __nv_bfloat16* my_v = sv + (size_t)warp * PAGE * VP;
-  uint4 kraw[NB], vraw[NB];
-  __half ksc[NB], vsc[NB];
-  auto fetch = [&](int pg) {
-    const int page = page_table[(long)b * max_pages + pg];
-    const long row = ((long)page * Hkv + hk) * PAGE + t;
-    const uint8_t* kp = k_pool + row * (D / 2) + hf * (HALF / 2);
-    const uint8_t* vp = v_pool + row * (D / 2) + hf * (HALF / 2);
-#pragma unroll
-    for (int j = 0; j < NB; ++j) {
-      kraw[j] = *reinterpret_cast<const uint4*>(kp + j * 16);
-      vraw[j] = *reinterpret_cast<const uint4*>(vp + j * 16);
-      ksc[j] = k_scale[row * (D / 32) + hf * NB + j];
-      vsc[j] = v_scale[row * (D / 32) + hf * NB + j];
-    }
-  };
-  int pg = p0 + warp;
-  if (pg < p1) fetch(pg);
-  for (; pg < p1; pg += 4) {
-    // ---- expand this page's registers, then start the next page's loads ----
-    float kf[HALF];
-#pragma unroll
-    for (int j = 0; j < NB; ++j) {
-      const float s = __half2float(ksc[j]);
-      const uint32_t wds[4] = {kraw[j].x, kraw[j].y, kraw[j].z, kraw[j].w};
-#pragma unroll
-      for (int w = 0; w < 4; ++w)
-#pragma unroll
-        for (int n = 0; n < 8; ++n) kf[j * 32 + w * 8 + n] = lv[(((wds[w] >> (4 * n)) & 15) << 5) + lane] * s;
-    }
-    __syncwarp();  // the previous page's V tile has been consumed by every lane
-#pragma unroll
-    for (int j = 0; j < NB; ++j) {
-      const float s = __half2float(vsc[j]);
-      const uint32_t wds[4] = {vraw[j].x, vraw[j].y, vraw[j].z, vraw[j].w};
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        float v8[8];
-#pragma unroll
-        for (int n = 0; n < 8; ++n) v8[n] = lv[(((wds[w] >> (4 * n)) & 15) << 5) + lane] * s;
-        uint4 pk;
-        pk.x = pack_bf16x2(v8[0], v8[1]);
-        pk.y = pack_bf16x2(v8[2], v8[3]);
-        pk.z = pack_bf16x2(v8[4], v8[5]);
-        pk.w = pack_bf16x2(v8[6], v8[7]);
-        *reinterpret_cast<uint4*>(my_v + t * VP + hf * HALF + j * 32 + w * 8) = pk;
-      }
-    }
-    const bool valid = pg * PAGE + t < len;
-    if (pg + 4 < p1) fetch(pg + 4);
-    // ---- scores ----
-    float pr[MAXG], alpha[MAXG];
-#pragma unroll
-    for (int g = 0; g < MAXG; ++g) {
-      if (g < G) {
-        float s0 = 0.f, s1 = 0.f;
-        const float* qg = &sq[g][hf * HALF];
-#pragma unroll
-        for (int e = 0; e < HALF; e += 2) {
-          s0 += kf[e] * qg[e];
-          s1 += kf[e + 1] * qg[e + 1];
-        }
-        float s = s0 + s1;
-        s += __shfl_xor_sync(0xffffffffu, s, 16);
-        s = valid ? s : -INFINITY;
-        float mx = s;
-#pragma unroll
-        for (int off = 8; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-        const float m_new = fmaxf(m[g], mx);
-        alpha[g] = m[g] == -INFINITY ? 0.f : exp2f(m[g] - m_new);
-        pr[g] = (s == -INFINITY) ? 0.f : exp2f(s - m_new);
-        float ps = pr[g];
-#pragma unroll
-        for (int off = 8; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
-        l[g] = l[g] * alpha[g] + ps;
-        m[g] = m_new;
-      }
-    }
-#pragma unroll
-    for (int g = 0; g < MAXG; ++g)
-      if (g < G)
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) o[g][e] *= alpha[g];
-    __syncwarp();  // the V tile is complete
-    // ---- values: lane owns output elements [lane*EPL, lane*EPL+EPL); tokens past the end carry p = 0 ----
-#pragma unroll
-    for (int tt = 0; tt < PAGE; ++tt) {
-      float vf[EPL];
-      if (EPL == 4) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(my_v + tt * VP + lane * 4);
-        vf[0] = __uint_as_float(raw.x << 16);
-        vf[1] = __uint_as_float(raw.x & 0xffff0000u);
-        vf[2 % EPL] = __uint_as_float(raw.y << 16);
-        vf[3 % EPL] = __uint_as_float(raw.y & 0xffff0000u);
-      } else {
-        const uint32_t raw = *reinterpret_cast<const uint32_t*>(my_v + tt * VP + lane * 2);
-        vf[0] = __uint_as_float(raw << 16);
-        vf[1 % EPL] = __uint_as_float(raw & 0xffff0000u);
-      }
-#pragma unroll
-      for (int g = 0; g < MAXG; ++g)
-        if (g < G) {
-          const float pt = __shfl_sync(0xffffffffu, pr[g], tt);
-#pragma unroll
-          for (int e = 0; e < EPL; ++e) o[g][e] += pt * vf[e];
-        }
-    }
-  }
-  // ---- fold the 4 warps (the V tiles are dead: their memory holds the per-warp outputs now) ----
-  __syncthreads();
-  for (int g = 0; g < G; ++g) {
-    if (lane == 0) {
-      sm_m[warp][g] = m[g];
-      sm_l[warp][g] = l[g];
-    }
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) sm_o[warp][g][lane * EPL + e] = o[g][e];
-  }
-  __syncthreads();
-  float* out = part + (((long)b * Hkv + hk) * splits + split) * (long)G * (D + 2);
-  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
-    const int g = i / D, e = i % D;
-    float mm = -INFINITY;
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_m[w][g]);
-    float acc = 0.f, ll = 0.f;
-    for (int w = 0; w < 4; ++w) {
-      const float f = sm_m[w][g] == -INFINITY ? 0.f : exp2f(sm_m[w][g] - mm);
-      acc += sm_o[w][g][e] * f;
-      ll += sm_l[w][g] * f;
-    }
-    out[g * (D + 2) + 2 + e] = acc;
-    if (e == 0) {
-      out[g * (D + 2)] = mm;
-      out[g * (D + 2) + 1] = ll;
-    }
-  }
-}
-
 // OIL4 decode attention on the tensor cores (warp-level mma.sync m16n8k16, fp16 inputs, fp32 accumulation).
 // A GQA group has at most 8 query heads per KV head, far below the 64-row minimum of tcgen05.mma, and the kernel
 // is bound by index bytes and table lookups, not by tensor throughput, so the warp-level MMA is the right size:

@@ -216,6 +216,15 @@ class OILReader:
     def read_tensor(self, name: str) -> torch.Tensor:
         """Flat fp32 tensor (the container stores no shapes)."""
         i = self.tensors[name]
+        start, nb = self.block_range(name)
+        if nb:
+            info = self.block_info(start)
+            if info["format"] in (2, 3, 4) and info["idx_bytes"] == info["num_weights"] and info["cb_bytes"] in (1028, 36):
+                # a whole-tensor codebook block of DenseModel::save_quantized (one byte per index, serialized codebook)
+                from .codebook import read_legacy_tensor
+                t = read_legacy_tensor(self, name)
+                if t is not None:
+                    return t
         out = np.empty(self.numel(name), dtype=np.float32)
         lib().oilr_read_tensor(self._h, i, out.ctypes.data)
         return torch.from_numpy(out)

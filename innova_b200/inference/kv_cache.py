@@ -106,12 +106,23 @@ class PagedKVCache:
         """k, v: [B, S_new, Hkv*D] views (token-major, unit inner stride) for the listed sequences."""
         B, S_new = k.shape[0], k.shape[1]
         if k.is_cuda:
-            assert batch_ids == list(range(B)), "device path appends the leading sequences in order"
+            # the kernel walks consecutive cache rows from the row its page-table pointer starts at: one launch per run of
+            # consecutive rows (a running batch is one run; a request admitted into row r is a run of one)
+            assert k.stride(0) == S_new * k.stride(1) and v.stride(0) == S_new * v.stride(1)
             st = torch.tensor(start, dtype=torch.int32, device=self.device)
-            rc = rt.lib().inv_kv_append(k.data_ptr(), v.data_ptr(), k.stride(1), v.stride(1), self.page_table.data_ptr(), self.max_pages,
-                                        st.data_ptr(), B, S_new, self.Hkv, self.D, self.k_pool[layer].data_ptr(), self.v_pool[layer].data_ptr(),
-                                        rt.ptr(self.k_scale[layer]), rt.ptr(self.v_scale[layer]), int(self.fmt == "oil4"), rt.stream_ptr())
-            rt.check(rc, "inv_kv_append")
+            i0 = 0
+            while i0 < B:
+                i1 = i0 + 1
+                while i1 < B and batch_ids[i1] == batch_ids[i1 - 1] + 1:
+                    i1 += 1
+                row0 = batch_ids[i0]
+                rc = rt.lib().inv_kv_append(k.data_ptr() + i0 * k.stride(0) * k.element_size(), v.data_ptr() + i0 * v.stride(0) * v.element_size(),
+                                            k.stride(1), v.stride(1), self.page_table.data_ptr() + row0 * self.max_pages * 4, self.max_pages,
+                                            st.data_ptr() + i0 * 4, i1 - i0, S_new, self.Hkv, self.D, self.k_pool[layer].data_ptr(),
+                                            self.v_pool[layer].data_ptr(), rt.ptr(self.k_scale[layer]), rt.ptr(self.v_scale[layer]),
+                                            int(self.fmt == "oil4"), rt.stream_ptr())
+                rt.check(rc, "inv_kv_append")
+                i0 = i1
             return
         for i, b in enumerate(batch_ids):
             for s in range(S_new):

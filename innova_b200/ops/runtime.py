@@ -19,8 +19,14 @@ def stream_ptr() -> int:
 
 def status_tensor(device=None) -> torch.Tensor:
     """One int32 word per device into which kernels write a code when a bounded wait runs out."""
-    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if device is None:
+        dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+    else:
+        dev = torch.device(device)
+    if dev.type == "cpu":       # host-only runs keep a word too, so that the code that reads it is the same (and testable)
+        key = "cpu"
+    else:
+        key = dev.index if dev.index is not None else torch.cuda.current_device()
     t = _status.get(key)
     if t is None:
         t = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -28,11 +34,26 @@ def status_tensor(device=None) -> torch.Tensor:
     return t
 
 
+_on_error = []
+
+
+def on_status_error(fn):
+    """Registers ``fn(code)`` to run before ``check_status`` raises: engines reset the device counters that a kernel which
+    gave up on a wait left half-updated, so that the step after the error starts clean."""
+    _on_error.append(fn)
+    return fn
+
+
 def check_status(device=None):
     """Synchronises and raises if any kernel reported a wait that ran out."""
     code = int(status_tensor(device).item())
     if code != 0:
         status_tensor(device).zero_()
+        for fn in list(_on_error):
+            try:
+                fn(code)
+            except Exception:
+                pass
         raise RuntimeError(f"innova_b200 kernel reported error {code} ({ERR_NAMES.get(code, '?')})")
 
 

@@ -50,9 +50,17 @@ class ShardedFlatEngine(FlatParamEngine):
             self.ticket = torch.zeros(1, dtype=torch.int32, device=self.device)
             self._grad_peers = self._symm["grad"].peers()
             self._param_peers = self._symm["param"].peers()
+            from ..ops import runtime as rt
+            rt.on_status_error(self._reset_after_error)
         if self.device.type == "cuda":
             torch.cuda.synchronize()
         dist.barrier(group=self.group)
+
+    def _reset_after_error(self, code):
+        """A reduce or update kernel that gave up on a peer returned before its last block cleared the partial norm and
+        the arrival counter: clear them, or the next step would clip with a stale norm."""
+        self.sumsq_local.zero_()
+        self.ticket.zero_()
 
     def _alloc(self, n, dtype, kind):
         if self.backend != "p2p":

@@ -187,8 +187,15 @@ class FSDP3Engine:
         if self.backend == "p2p":
             from ..ops.gemm import set_side_job_provider
             set_side_job_provider(self._next_job)
+            ops.runtime.on_status_error(self._reset_after_error)
             torch.cuda.synchronize()
         dist.barrier(group=self.group)
+
+    def _reset_after_error(self, code):
+        """After a kernel gave up on a wait: arrival counters and partial sums may be half-updated."""
+        self.ticket.zero_()
+        self.sumsq_parts.zero_()
+        self._pieces = 0
 
     # ------------------------------------------------------------------------------------------ layout helpers
     def memory_report(self) -> dict:

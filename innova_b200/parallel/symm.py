@@ -19,6 +19,7 @@ from .. import _native
 _native.register_cuda_sigs({
     "inv_signal_peers": [_native.vp, _native.i32, _native.i32, C.c_uint32, _native.vp],
     "inv_wait_flags": [_native.vp, _native.i32, C.c_uint32, _native.vp, _native.vp],
+    "inv_wait_flags_limit": [_native.vp, _native.i32, C.c_uint32, _native.i64, _native.vp, _native.vp],
     "inv_fsdp_reduce": [_native.vp, _native.i32, _native.i32, _native.i64, _native.i64, _native.vp, _native.vp, _native.vp, _native.vp,
                         _native.vp, _native.vp, C.c_uint32, _native.vp, _native.vp],
     "inv_fsdp_adamw_push": [_native.vp] * 5 + [_native.i32, _native.i32, _native.i64, _native.i64, _native.i64] + [_native.vp] * 4 +

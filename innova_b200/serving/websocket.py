@@ -90,6 +90,19 @@ def create_frame(data: Union[str, bytes], opcode: int = OP_TEXT, mask: Optional[
     return bytes(head) + payload
 
 
+def declared_length(buf: bytes):
+    """Payload length that the frame header at the start of ``buf`` announces, or None while the header is incomplete.
+    Lets a receiver refuse an oversized frame before buffering it."""
+    if len(buf) < 2:
+        return None
+    n = buf[1] & 0x7F
+    if n == 126:
+        return struct.unpack(">H", buf[2:4])[0] if len(buf) >= 4 else None
+    if n == 127:
+        return struct.unpack(">Q", buf[2:10])[0] if len(buf) >= 10 else None
+    return n
+
+
 def parse_frame(buf: bytes):
     """-> (payload, opcode, fin, bytes consumed) or None when ``buf`` does not hold a whole frame yet."""
     if len(buf) < 2:
@@ -119,12 +132,13 @@ def parse_frame(buf: bytes):
 
 
 class WebSocketHandler:
-    def __init__(self, port: int = 8081, host: str = "127.0.0.1", max_message: int = 1 << 20):
-        self.port, self.host, self.max_message = port, host, max_message
+    def __init__(self, port: int = 8081, host: str = "127.0.0.1", max_message: int = 1 << 20, send_timeout: float = 30.0):
+        self.port, self.host, self.max_message, self.send_timeout = port, host, max_message, send_timeout
         self.generate_cb: Optional[Callable[[str, int, bool], Union[str, Iterable[str]]]] = None
         self.on_message: Optional[Callable[[str], None]] = None
         self._sock: Optional[socket.socket] = None
         self._clients: List[socket.socket] = []
+        self._send_locks = {}                 # one per client: broadcast() and a client's own stream share its socket
         self._lock = threading.Lock()
         self._threads: List[threading.Thread] = []
         self._running = False
@@ -168,6 +182,22 @@ class WebSocketHandler:
             t.join(timeout=1.0)
         self._threads = []
 
+    def _send(self, conn: socket.socket, frame: bytes):
+        """One whole frame at a time per client, whichever thread sends it; blocking with a generous limit (the 0.2 s
+        receive poll would drop a client that reads slowly)."""
+        with self._lock:
+            lk = self._send_locks.setdefault(conn, threading.Lock())
+        with lk:
+            old = conn.gettimeout()
+            conn.settimeout(self.send_timeout)
+            try:
+                conn.sendall(frame)
+            finally:
+                try:
+                    conn.settimeout(old)
+                except OSError:
+                    pass
+
     def broadcast(self, token: str) -> int:
         """Sends a text frame to every client; returns how many received it. Clients whose socket fails are dropped."""
         frame = create_frame(token, OP_TEXT)
@@ -176,7 +206,7 @@ class WebSocketHandler:
         sent = 0
         for c in clients:
             try:
-                c.sendall(frame)
+                self._send(c, frame)
                 sent += 1
             except OSError:
                 self._remove(c)
@@ -195,14 +225,18 @@ class WebSocketHandler:
             t.start()
             self._threads.append(t)
 
-    def _handshake(self, conn: socket.socket) -> bool:
+    def _handshake(self, conn: socket.socket):
+        """-> bytes that followed the request head (the client's first frames may share its packet), or None on failure."""
         conn.settimeout(5.0)
         data = b""
         while b"\r\n\r\n" not in data and len(data) < 16384:
             chunk = conn.recv(4096)
             if not chunk:
-                return False
+                return None
             data += chunk
+        if b"\r\n\r\n" not in data:
+            return None
+        data, rest = data.split(b"\r\n\r\n", 1)
         headers = {}
         for line in data.decode("latin1").split("\r\n")[1:]:
             if ":" in line:
@@ -211,14 +245,15 @@ class WebSocketHandler:
         key = headers.get("sec-websocket-key")
         if not key or "websocket" not in headers.get("upgrade", "").lower():
             conn.sendall(b"HTTP/1.1 400 Bad Request\r\nContent-Length: 0\r\nConnection: close\r\n\r\n")
-            return False
+            return None
         conn.sendall(("HTTP/1.1 101 Switching Protocols\r\nUpgrade: websocket\r\nConnection: Upgrade\r\n"
                       f"Sec-WebSocket-Accept: {compute_accept_key(key)}\r\n\r\n").encode())
-        return True
+        return rest
 
     def _client_loop(self, conn: socket.socket):
         try:
-            if not self._handshake(conn):
+            rest = self._handshake(conn)
+            if rest is None:
                 self._close(conn)
                 return
         except OSError:
@@ -227,31 +262,36 @@ class WebSocketHandler:
         with self._lock:
             self._clients.append(conn)
         conn.settimeout(0.2)
-        buf, message = b"", b""
+        buf, message = rest, b""
         try:
             while self._running:
-                try:
-                    chunk = conn.recv(65536)
-                except socket.timeout:
-                    continue
-                if not chunk:
-                    break
-                buf += chunk
+                if not buf or parse_frame(buf) is None:
+                    try:
+                        chunk = conn.recv(65536)
+                    except socket.timeout:
+                        continue
+                    if not chunk:
+                        break
+                    buf += chunk
                 while True:
+                    n = declared_length(buf)
+                    if n is not None and n + len(message) > self.max_message:      # refuse before buffering the payload
+                        self._send(conn, create_frame(struct.pack(">H", 1009), OP_CLOSE))
+                        raise ConnectionAbortedError
                     fr = parse_frame(buf)
                     if fr is None:
                         break
                     payload, op, fin, used = fr
                     buf = buf[used:]
                     if op == OP_CLOSE:
-                        conn.sendall(create_frame(payload[:2], OP_CLOSE))
+                        self._send(conn, create_frame(payload[:2], OP_CLOSE))
                         raise ConnectionAbortedError
                     if op == OP_PING:
-                        conn.sendall(create_frame(payload, OP_PONG))
+                        self._send(conn, create_frame(payload, OP_PONG))
                     elif op in (OP_TEXT, OP_BINARY, OP_CONT):
                         message += payload
                         if len(message) > self.max_message:
-                            conn.sendall(create_frame(struct.pack(">H", 1009), OP_CLOSE))
+                            self._send(conn, create_frame(struct.pack(">H", 1009), OP_CLOSE))
                             raise ConnectionAbortedError
                         if fin:
                             self._on_text(conn, message.decode("utf-8", "replace"))
@@ -269,17 +309,18 @@ class WebSocketHandler:
             req = json.loads(text)
             prompt, max_tokens = str(req["prompt"]), int(req.get("max_tokens", 64))
         except (ValueError, KeyError, TypeError):
-            conn.sendall(create_frame(json.dumps({"error": "expected {\"prompt\": ..., \"max_tokens\": ...}"})))
+            self._send(conn, create_frame(json.dumps({"error": "expected {\"prompt\": ..., \"max_tokens\": ...}"})))
             return
         out = self.generate_cb(prompt, max_tokens, True)
         for piece in ([out] if isinstance(out, str) else out):
-            conn.sendall(create_frame(piece))
-        conn.sendall(create_frame(json.dumps({"done": True})))
+            self._send(conn, create_frame(piece))
+        self._send(conn, create_frame(json.dumps({"done": True})))
 
     def _remove(self, conn: socket.socket):
         with self._lock:
             if conn in self._clients:
                 self._clients.remove(conn)
+            self._send_locks.pop(conn, None)
         self._close(conn)
 
     @staticmethod

@@ -199,6 +199,7 @@ class Trainer:
                 step = self.global_step
                 if step % c.log_interval == 0 or step == 1:
                     lv = float(loss)
+                    self.check_device_status()          # the loss read above has synchronised already
                     dt = time.time() - t0
                     m = TrainMetrics(step=step, epoch=epoch, loss=lv, perplexity=math.exp(min(lv, 30.0)), lr=self.engine.current_lr(),
                                      tokens_per_sec=tokens / max(dt, 1e-9), val_loss=m.val_loss)
@@ -213,9 +214,17 @@ class Trainer:
         return m
 
     # ------------------------------------------------------------------ checkpoint
+    def check_device_status(self):
+        """Raises if a kernel gave up on a bounded wait (a peer that never signalled, a pipeline stage that never filled)
+        since the last check: without this a step would go on with unreduced gradients or stale parameters. Called where
+        the host synchronises anyway: when a loss is read for logging, before a checkpoint is written."""
+        from ..ops import runtime as rt
+        rt.check_status(self.device)
+
     def save_checkpoint(self, path: str):
         """``<path>`` = weights as a .oil container, ``<path>.opt`` = optimizer state
         (the reference's pair of files, src/trainer_core.cpp:315-347)."""
+        self.check_device_status()
         from ..formats.checkpoint import save_training_checkpoint
         save_training_checkpoint(self, path)
 

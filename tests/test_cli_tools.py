@@ -87,6 +87,34 @@ def test_serve_answers_over_http(tiny):
         srv.stop()
 
 
+def test_serve_concurrent_requests_equal_sequential(tiny):
+    """HTTP and WebSocket threads share one engine and one paged KV cache: overlapping requests (plain and streamed)
+    must produce what the same requests produce one after the other."""
+    import threading
+    d, model, corpus = tiny
+    from innova_b200.cli.serve import build_server
+    srv = build_server(model, port=0, device="cpu")
+    gen = srv.generate_for_websocket
+    prompts = ["the quick", "lazy dog", "brown fox jumps", "over the", "dog. the", "quick brown"]
+    want = [gen(p, 8, False) if i % 2 == 0 else "".join(gen(p, 8, True)) for i, p in enumerate(prompts)]
+    got = [None] * len(prompts)
+    errs = []
+
+    def work(i):
+        try:
+            for _ in range(2):
+                got[i] = gen(prompts[i], 8, False) if i % 2 == 0 else "".join(gen(prompts[i], 8, True))
+        except Exception as e:  # noqa: BLE001
+            errs.append(e)
+    ts = [threading.Thread(target=work, args=(i,)) for i in range(len(prompts))]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join(120)
+    assert not errs, errs
+    assert got == want
+
+
 def test_adapters_edition_tools(tiny):
     import io
     from innova_b200.cli import adapters_tools as T

@@ -126,6 +126,9 @@ def _tp_worker(rank, world, port, out, variant=0):
     from innova_b200.parallel.tp import TPDecoder
     cfg = TransformerConfig(vocab_size=1024, hidden_size=512, num_layers=2, num_heads=8, head_dim=64, ffn_hidden_size=1408, num_kv_heads=4,
                             max_seq_len=256)
+    if variant == 2:   # enough heads for 8 ranks (one KV head per rank there), FFN shards that need padding at 8
+        cfg = TransformerConfig(vocab_size=2048, hidden_size=1024, num_layers=2, num_heads=16, head_dim=64, ffn_hidden_size=2752, num_kv_heads=8,
+                                max_seq_len=256)
     if variant == 1:   # one KV head per rank, a vocabulary shard that is not a whole number of 128-row tiles, padded FFN shard
         cfg = TransformerConfig(vocab_size=1152, hidden_size=512, num_layers=2, num_heads=8, head_dim=64, ffn_hidden_size=2752, num_kv_heads=2,
                                 max_seq_len=256)
@@ -162,6 +165,20 @@ def test_tensor_parallel_decode_matches_single_gpu(tmp_path, variant):
     assert rel(a0, b0) < 2e-2, ("prefill", rel(a0, b0), mm)
     assert rel(a1, b1) < 2e-2, ("decode", rel(a1, b1), mm)
     assert (ta[:, 0] == tb[:, 0]).float().mean() >= 0.5  # greedy continuations diverge after the first near-tie
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_tensor_parallel_decode_matches_single_gpu_wide(tmp_path, world):
+    """Prefill and decode logits of the tensor-parallel decoder at 4 and 8 ranks against the one-GPU decoder."""
+    _need_gpus(world)
+    out = str(tmp_path / "tp.pt")
+    mp.spawn(_tp_worker, args=(world, _free_port(), out, 2), nprocs=world, join=True)
+    res = torch.load(out)
+    (a0, a1, ta, mm), (b0, b1, tb, _) = res["tp"], res["one"]
+    rel = lambda x, y: float((x - y).norm() / y.norm())
+    assert rel(a0, b0) < 2e-2, ("prefill", rel(a0, b0), mm)
+    assert rel(a1, b1) < 2e-2, ("decode", rel(a1, b1), mm)
+    assert (ta[:, 0] == tb[:, 0]).float().mean() >= 0.5
 
 
 def _coll_worker(rank, world, port, out):
@@ -205,9 +222,9 @@ def _coll_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_native_collectives_match_nccl(tmp_path):
-    _need_gpus(2)
-    world = 2
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_native_collectives_match_nccl(tmp_path, world):
+    _need_gpus(world)
     out = str(tmp_path / "coll")
     mp.spawn(_coll_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     for rank in range(world):
@@ -272,9 +289,9 @@ def _fused_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_fused_gemm_collectives(tmp_path):
-    _need_gpus(2)
-    world = 2
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_gemm_collectives(tmp_path, world):
+    _need_gpus(world)
     out = str(tmp_path / "fused")
     mp.spawn(_fused_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     for rank in range(world):
@@ -316,10 +333,10 @@ def _ep_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_expert_parallel_dispatch_combine(tmp_path):
-    _need_gpus(2)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_dispatch_combine(tmp_path, world):
+    _need_gpus(world)
     from innova_b200.ops.moe import moe_ffn_reference
-    world = 2
     out = str(tmp_path / "ep")
     mp.spawn(_ep_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     g = torch.Generator().manual_seed(11)

@@ -81,3 +81,43 @@ def test_c_api_shaped_calls(tmp_path):
     capi.oil_model_free(h)
     assert capi.oil_generate(h, "ab", 5) is None
     assert b"invalid handle" in C.string_at(fns["oil_last_error"]())
+
+
+def test_oversized_frame_is_refused_from_its_header_and_early_frames_survive_the_handshake():
+    import socket
+    import struct
+    import time
+    from innova_b200.serving.websocket import OP_CLOSE, OP_TEXT, WebSocketHandler, compute_accept_key, create_frame, parse_frame
+    got = []
+    ws = WebSocketHandler(0, max_message=1024)
+    ws.on_message = got.append
+    ws.start()
+    try:
+        # request head and the first frame in one packet: the frame must not be lost
+        s = socket.create_connection(("127.0.0.1", ws.port), timeout=5)
+        key = "dGhlIHNhbXBsZSBub25jZQ=="
+        s.sendall((f"GET / HTTP/1.1\r\nHost: x\r\nUpgrade: websocket\r\nConnection: Upgrade\r\nSec-WebSocket-Key: {key}\r\n"
+                   "Sec-WebSocket-Version: 13\r\n\r\n").encode() + create_frame("early", OP_TEXT, mask=b"abcd"))
+        data = b""
+        while b"\r\n\r\n" not in data:
+            data += s.recv(4096)
+        assert compute_accept_key(key).encode() in data
+        for _ in range(100):
+            if got:
+                break
+            time.sleep(0.02)
+        assert got == ["early"]
+        # a header that announces 2^40 bytes: closed with 1009 although no payload byte was sent
+        s.sendall(bytes([0x81, 0x80 | 127]) + struct.pack(">Q", 1 << 40) + b"abcd")
+        buf = data.split(b"\r\n\r\n", 1)[1]
+        fr = None
+        while fr is None:
+            chunk = s.recv(4096)
+            if not chunk:
+                break
+            buf += chunk
+            fr = parse_frame(buf)
+        assert fr is not None and fr[1] == OP_CLOSE and struct.unpack(">H", fr[0][:2])[0] == 1009
+        s.close()
+    finally:
+        ws.stop()

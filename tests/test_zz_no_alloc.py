@@ -66,6 +66,17 @@ def test_noalloc_matches_regular_entry_point_twice(rms):
         assert rc == 0
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        # The caching allocator's counter cannot see a cudaMalloc made inside the library, the driver's free-byte count
+        # can. The call above has loaded every kernel this shape uses (module loading is lazy and may take memory once),
+        # so a repeat of the same call must leave the device's free memory exactly where it was.
+        free_before = torch.cuda.mem_get_info(dev)[0]
+        dg.zero_()
+        db.zero_()
+        rc = noalloc(dy.data_ptr(), x.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), None, dx.data_ptr(), dg.data_ptr(),
+                     db.data_ptr(), T, D, rms, stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info(dev)[0] == free_before
         tol = 2e-2
         assert float((dx.float() - dx_ref.float()).norm() / (dx_ref.float().norm() + 1e-12)) < tol
         assert float((dg - dg_ref).norm() / (dg_ref.norm() + 1e-12)) < tol
