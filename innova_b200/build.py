@@ -132,9 +132,32 @@ def asan_runtime() -> str:
     return subprocess.run([cc, "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip() if cc else ""
 
 
+def build_capi(force: bool = False) -> Path | None:
+    """``liboil_capi.so``: the C entry points ``oil_model_load`` ... ``oil_last_error`` (csrc/capi/oil_capi.h) over the
+    Python engine. Needs the Python development headers and shared library; returns None when they are missing."""
+    import sysconfig
+    out = LIB / "liboil_capi.so"
+    src = CSRC / "capi" / "oil_capi.cpp"
+    inc = sysconfig.get_config_var("INCLUDEPY")
+    libdir = sysconfig.get_config_var("LIBDIR")
+    ver = sysconfig.get_config_var("LDVERSION")
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if cxx is None or not inc or not os.path.exists(os.path.join(inc, "Python.h")) or not sysconfig.get_config_var("Py_ENABLE_SHARED"):
+        return out if out.exists() else None
+    if force or _newer([src, CSRC / "capi" / "oil_capi.h"], out):
+        LIB.mkdir(exist_ok=True)
+        _run([cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-I", inc, "-I", str(CSRC / "capi"), str(src), "-o", str(out),
+              "-L", str(libdir), f"-lpython{ver}", "-ldl", f"-Wl,-rpath,{libdir}"])
+    return out
+
+
 def build_all(force: bool = False, verbose: bool = False):
     LIB.mkdir(exist_ok=True)
-    return build_cuda(force, verbose), build_host(force)
+    paths = [build_cuda(force, verbose), build_host(force)]
+    capi = build_capi(force)
+    if capi is not None:
+        paths.append(capi)
+    return tuple(paths)
 
 
 if __name__ == "__main__":
