@@ -35,6 +35,7 @@ struct FlashBwdParams {
   int B, S, H, Hkv;
   float scale;
   int causal;
+  int window;  // > 0 (causal only): a query sees the `window` most recent keys, its own position included
   int* status;
 };
 
@@ -90,8 +91,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int G = p.H / p.Hkv;
   const int k0 = j * 128;
   const int nqb = (p.S + 127) / 128;
-  const int i0 = (p.causal & 1) ? j : 0;
-  const int nq_it = nqb - i0;
+  const int i0 = p.causal ? j : 0;
+  // with a sliding window the last query that sees key k0 + 127 is row k0 + 126 + window
+  const int i_end = (p.causal && p.window > 0) ? min(nqb, (k0 + 126 + p.window) / 128 + 1) : nqb;
+  const int nq_it = i_end - i0;
   const int n_it = G * nq_it;
 
   if (threadIdx.x == 0) {
@@ -236,7 +239,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (DC == 16) tmem_ld_32x16(t_lane + DQ_COL + col0, rr);
         else tmem_ld_32x32(t_lane + DQ_COL + col0, rr);
         tmem_ld_wait();
-        if (qrow < p.S && !(p.causal & 2)) {
+        if (qrow < p.S) {
           float* dst = p.dq_acc + ((size_t)b * p.S + qrow) * ((size_t)p.H * D) + hj * D + col0;
 #pragma unroll
           for (int g = 0; g < DC / 4; ++g)
@@ -265,7 +268,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (!mbar_wait_warp(s_full, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       asm volatile("bar.sync 1, 512;" ::: "memory");  // the statistics of this block are in place (softmax warps only)
-      const bool need_mask = ((p.causal & 1) && q0 < k0 + 127) || (q0 + 128 > p.S) || (k0 + 128 > p.S);
+      const bool windowed = p.causal && p.window > 0;
+      const bool need_mask = (p.causal && q0 < k0 + 127) || (q0 + 128 > p.S) || (k0 + 128 > p.S) || (windowed && q0 + 127 - k0 >= p.window);
       // both 32-column chunks of S^T and dP^T come in with four back-to-back TMEM loads and one wait; the columns
       // are handed back to the tensor core before the arithmetic starts, so the next block's first MMAs overlap it
       uint32_t s_all[32], dp_all[32];
@@ -308,7 +312,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
               const float lse = __ldg(lse_row + qc);
               const float dl = __ldg(dl_row + qc);
               float e = exp2f(__uint_as_float(s_r[i + u]) * c - lse);
-              if (((p.causal & 1) && key > qi) || qi >= p.S || key >= p.S) e = 0.f;
+              if ((p.causal && key > qi) || qi >= p.S || key >= p.S || (windowed && qi - key >= p.window)) e = 0.f;
               pe[u] = e;
               de[u] = e * (__uint_as_float(dp_r[i + u]) - dl);
             }
@@ -456,10 +460,12 @@ extern "C" long inv_flash_attn_bwd_scratch_bytes(int B, int S, int H, int head_d
 // q,k,v,o,do: token-major bf16. dq,dk,dv: token-major bf16 outputs (may point into one dqkv buffer).
 extern "C" int inv_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, void* dq,
                                   void* dk, void* dv, void* scratch, int B, int S, int H, int Hkv, int head_dim, int ld_q, int ld_k, int ld_v,
-                                  int ld_o, int ld_do, int ld_dq, int ld_dk, int ld_dv, float scale, int causal, int* status, void* stream) {
+                                  int ld_o, int ld_do, int ld_dq, int ld_dk, int ld_dv, float scale, int causal, int window, int* status,
+                                  void* stream) {
   if ((head_dim != 64 && head_dim != 128) || H % Hkv || (ld_q % 8) || (ld_k % 8) || (ld_v % 8) || (ld_o % 8) || (ld_do % 8) ||
       (ld_dq % 8) || (ld_dk % 8) || (ld_dv % 8))
     return -ERR_BAD_ARG;
+  if (window < 0 || (window > 0 && !causal)) return -ERR_BAD_ARG;
   if (B <= 0 || S <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   float* delta = reinterpret_cast<float*>(scratch);
@@ -482,7 +488,7 @@ extern "C" int inv_flash_attn_bwd(const void* q, const void* k, const void* v, c
   FlashBwdParams p;
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
   p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv; p.ld_dk = ld_dk; p.ld_dv = ld_dv;
-  p.B = B; p.S = S; p.H = H; p.Hkv = Hkv; p.scale = scale; p.causal = causal; p.status = status;
+  p.B = B; p.S = S; p.H = H; p.Hkv = Hkv; p.scale = scale; p.causal = causal ? 1 : 0; p.window = window >= S ? 0 : window; p.status = status;
   dim3 grid((S + 127) / 128, Hkv, B);
   static bool configured = false;
   if (!configured) {

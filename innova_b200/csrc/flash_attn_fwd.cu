@@ -31,6 +31,7 @@ struct FlashFwdParams {
   int B, S, H, Hkv;
   float scale;
   int causal;
+  int window;  // > 0 (causal only): a query sees the `window` most recent keys, its own position included
   int* status;
 };
 
@@ -87,7 +88,9 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const int hk = h / (p.H / p.Hkv);
   const int q0 = q_blk * FA_BM;
   const int nkb_all = (p.S + FA_BN - 1) / FA_BN;
-  const int nkb = p.causal ? min(nkb_all, q_blk + 1) : nkb_all;
+  // key blocks visited: [jlo, jlo + nkb). A sliding window skips the blocks that lie wholly before the first query's window.
+  const int jlo = (p.causal && p.window > 0) ? max(0, q0 - p.window + 1) / FA_BN : 0;
+  const int nkb = (p.causal ? min(nkb_all, q_blk + 1) : nkb_all) - jlo;
   constexpr uint32_t TMEM_COLS = ND == 1 ? 256 : 512;
   constexpr uint32_t O_COL = 128, P_COL = 128 + D;
 
@@ -126,7 +129,7 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         const uint32_t ph = (n / SLOTS) & 1;
         if (!mbar_wait(&kv_empty[slot], ph ^ 1, abort_flag, p.status, ERR_WAIT_EMPTY)) break;
         mbar_expect_tx(&kv_full[slot], L::TILE);
-        const int j = n >> 1;
+        const int j = jlo + (n >> 1);
         const CUtensorMap* tm = (n & 1) ? &tmap_v : &tmap_k;
 #pragma unroll
         for (int a = 0; a < ND; ++a) tma_load_3d(sKV + slot * L::TILE + a * 16384, tm, &kv_full[slot], hk * D + a * 64, j * FA_BN, b);
@@ -183,9 +186,11 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     for (int j = 0; j < nkb; ++j) {
       if (!mbar_wait_warp(s_full, j & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      const int k0 = j * FA_BN;
-      const bool need_mask = (p.causal && k0 + FA_BN - 1 > q0) || (k0 + FA_BN > p.S);
+      const int k0 = (jlo + j) * FA_BN;
+      const bool windowed = p.causal && p.window > 0;
+      const bool need_mask = (p.causal && k0 + FA_BN - 1 > q0) || (k0 + FA_BN > p.S) || (windowed && k0 <= q0 + FA_BM - 1 - p.window);
       const int kmax = p.causal ? min(row, p.S - 1) : p.S - 1;
+      const int kmin = windowed ? row - p.window + 1 : 0;
       uint32_t sr[128];
       tmem_ld_32x32(t_lane, sr);
       tmem_ld_32x32(t_lane + 32, sr + 32);
@@ -198,7 +203,7 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 128; ++i)
-          if (k0 + i > kmax) sr[i] = 0xff800000u;  // -inf
+          if (k0 + i > kmax || k0 + i < kmin) sr[i] = 0xff800000u;  // -inf
       }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
@@ -214,7 +219,7 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       const float alpha = (j == 0 || !raise) ? 1.0f : exp2f((m_used - m_new) * c);
       m_used = m_new;
       const bool any_rescale = __any_sync(0xffffffffu, j > 0 && raise);
-      const float mc = m_used * c;
+      const float mc = m_used == -INFINITY ? 0.f : m_used * c;  // a row that has seen no key yet (window edge): every exponential is 0
       // exponentials into registers (packed bf16 pairs overwrite the scores) and their sum: one MUFU op per element and
       // one hardware conversion per pair
       float rs0 = 0.f, rs1 = 0.f;
@@ -325,8 +330,10 @@ using namespace inv;
 // q/k/v: token-major bf16 [B*S, ld*]; q has H heads, k and v have Hkv heads of `head_dim` columns.
 // out: [B*S, ld_o] bf16; lse: [B, H, S] fp32 (may be null).
 extern "C" int inv_flash_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int H, int Hkv,
-                                  int head_dim, int ld_q, int ld_k, int ld_v, int ld_o, float scale, int causal, int* status, void* stream) {
+                                  int head_dim, int ld_q, int ld_k, int ld_v, int ld_o, float scale, int causal, int window, int* status,
+                                  void* stream) {
   if ((head_dim != 64 && head_dim != 128) || H % Hkv || (ld_q % 8) || (ld_k % 8) || (ld_v % 8) || (ld_o % 8)) return -ERR_BAD_ARG;
+  if (window < 0 || (window > 0 && !causal)) return -ERR_BAD_ARG;  // the sliding window is defined for causal attention
   if (B <= 0 || S <= 0) return 0;
   CUtensorMap tq, tk, tv;
   int rc;
@@ -335,7 +342,7 @@ extern "C" int inv_flash_attn_fwd(const void* q, const void* k, const void* v, v
   if ((rc = make_tmap_tokens_bf16(&tv, v, Hkv * head_dim, S, B, ld_v, FA_BN))) return rc;
   FlashFwdParams p;
   p.out = (__nv_bfloat16*)out; p.ld_o = ld_o; p.lse = lse;
-  p.B = B; p.S = S; p.H = H; p.Hkv = Hkv; p.scale = scale; p.causal = causal; p.status = status;
+  p.B = B; p.S = S; p.H = H; p.Hkv = Hkv; p.scale = scale; p.causal = causal; p.window = 0; p.status = status;
   dim3 grid((S + FA_BM - 1) / FA_BM, H, B);
   cudaStream_t st = (cudaStream_t)stream;
   static bool configured = false;
@@ -344,7 +351,8 @@ extern "C" int inv_flash_attn_fwd(const void* q, const void* k, const void* v, v
     cudaFuncSetAttribute(flash_fwd3_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd3Smem<2>::TOTAL);
     configured = true;
   }
-  p.causal = causal & 1;
+  p.causal = causal ? 1 : 0;
+  p.window = window >= S ? 0 : window;
   if (head_dim == 64) flash_fwd3_kernel<1><<<grid, FA_THREADS, Fwd3Smem<1>::TOTAL, st>>>(tq, tk, tv, p);
   else flash_fwd3_kernel<2><<<grid, FA_THREADS, Fwd3Smem<2>::TOTAL, st>>>(tq, tk, tv, p);
   cudaError_t e = cudaGetLastError();

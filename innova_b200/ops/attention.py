@@ -17,14 +17,9 @@ from . import runtime as rt
 from .. import _native
 
 _native.register_cuda_sigs({
-    "inv_flash_attn_fwd": [_native.vp] * 5 + [_native.i32] * 9 + [_native.f32, _native.i32, _native.vp, _native.vp],
-    "inv_flash_attn_bwd": [_native.vp] * 10 + [_native.i32] * 13 + [_native.f32, _native.i32, _native.vp, _native.vp],
+    "inv_flash_attn_fwd": [_native.vp] * 5 + [_native.i32] * 9 + [_native.f32, _native.i32, _native.i32, _native.vp, _native.vp],
+    "inv_flash_attn_bwd": [_native.vp] * 10 + [_native.i32] * 13 + [_native.f32, _native.i32, _native.i32, _native.vp, _native.vp],
 })
-
-
-import os
-_BWD_DEBUG = int(os.environ.get('INV_ATTN_DEBUG', '0'))
-_FWD_DEBUG = int(os.environ.get('INV_ATTN_FWD_DEBUG', '0'))   # 8: first-generation forward kernel
 
 
 def _scratch_bytes(B, S, H, D):
@@ -34,24 +29,24 @@ def _scratch_bytes(B, S, H, D):
 
 class _FlashAttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, qkv, H, Hkv, D, causal, scale):
+    def forward(ctx, qkv, H, Hkv, D, causal, scale, window=0):
         B, S, ld = qkv.shape
         assert ld == (H + 2 * Hkv) * D and qkv.is_contiguous() and qkv.dtype == torch.bfloat16
         out = torch.empty((B, S, H * D), dtype=torch.bfloat16, device=qkv.device)
         lse = torch.empty((B, H, S), dtype=torch.float32, device=qkv.device)
         base = qkv.data_ptr()
         rc = rt.lib().inv_flash_attn_fwd(base, base + H * D * 2, base + (H + Hkv) * D * 2, out.data_ptr(), lse.data_ptr(), B, S, H, Hkv, D,
-                                         ld, ld, ld, H * D, float(scale), int(causal) | _FWD_DEBUG, rt.status_tensor(qkv.device).data_ptr(),
+                                         ld, ld, ld, H * D, float(scale), int(causal), int(window), rt.status_tensor(qkv.device).data_ptr(),
                                          rt.stream_ptr())
         rt.check(rc, "inv_flash_attn_fwd")
         ctx.save_for_backward(qkv, out, lse)
-        ctx.cfg = (H, Hkv, D, causal, scale)
+        ctx.cfg = (H, Hkv, D, causal, scale, window)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         qkv, out, lse = ctx.saved_tensors
-        H, Hkv, D, causal, scale = ctx.cfg
+        H, Hkv, D, causal, scale, window = ctx.cfg
         B, S, ld = qkv.shape
         dout = dout.contiguous()
         dqkv = torch.empty_like(qkv)
@@ -59,14 +54,15 @@ class _FlashAttnFn(torch.autograd.Function):
         base, dbase = qkv.data_ptr(), dqkv.data_ptr()
         rc = rt.lib().inv_flash_attn_bwd(base, base + H * D * 2, base + (H + Hkv) * D * 2, out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
                                          dbase, dbase + H * D * 2, dbase + (H + Hkv) * D * 2, scr.data_ptr(), B, S, H, Hkv, D, ld, ld, ld,
-                                         H * D, H * D, ld, ld, ld, float(scale), int(causal) | _BWD_DEBUG, rt.status_tensor(qkv.device).data_ptr(),
+                                         H * D, H * D, ld, ld, ld, float(scale), int(causal), int(window), rt.status_tensor(qkv.device).data_ptr(),
                                          rt.stream_ptr())
         rt.check(rc, "inv_flash_attn_bwd")
-        return dqkv, None, None, None, None, None
+        return dqkv, None, None, None, None, None, None
 
 
-def attention_reference(qkv, H, Hkv, D, causal=True, scale=None):
-    """Plain PyTorch attention on the same fused layout (CPU path and test oracle)."""
+def attention_reference(qkv, H, Hkv, D, causal=True, scale=None, window=0):
+    """Plain PyTorch attention on the same fused layout (CPU path and test oracle). ``window`` > 0 (causal only): a query
+    sees its ``window`` most recent positions, its own included."""
     B, S, _ = qkv.shape
     q, k, v = qkv.split([H * D, Hkv * D, Hkv * D], dim=-1)
     q = q.view(B, S, H, D).transpose(1, 2)
@@ -75,12 +71,21 @@ def attention_reference(qkv, H, Hkv, D, causal=True, scale=None):
     if Hkv != H:
         k = k.repeat_interleave(H // Hkv, dim=1)
         v = v.repeat_interleave(H // Hkv, dim=1)
-    o = F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale)
+    if window and window < S:
+        assert causal, "the sliding window is defined for causal attention"
+        pos = torch.arange(S, device=qkv.device)
+        keep = (pos[None, :] <= pos[:, None]) & (pos[:, None] - pos[None, :] < window)
+        o = F.scaled_dot_product_attention(q, k, v, attn_mask=keep, scale=scale)
+    else:
+        o = F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale)
     return o.transpose(1, 2).reshape(B, S, H * D)
 
 
-def flash_attention(qkv, n_heads, n_kv_heads, head_dim, causal=True, scale=None):
+def flash_attention(qkv, n_heads, n_kv_heads, head_dim, causal=True, scale=None, window=0):
+    """``window`` > 0 (causal only): sliding-window attention, a query sees its ``window`` most recent positions. The
+    tcgen05 kernels skip the key blocks (forward) and query blocks (backward) that lie wholly outside the window, so time
+    is O(S * window)."""
     scale = 1.0 / math.sqrt(head_dim) if scale is None else scale
     if not qkv.is_cuda:
-        return attention_reference(qkv, n_heads, n_kv_heads, head_dim, causal, scale)
-    return _FlashAttnFn.apply(qkv, n_heads, n_kv_heads, head_dim, causal, scale)
+        return attention_reference(qkv, n_heads, n_kv_heads, head_dim, causal, scale, window)
+    return _FlashAttnFn.apply(qkv, n_heads, n_kv_heads, head_dim, causal, scale, window)

@@ -8,7 +8,8 @@ backward pass, the statistics of the last online softmax, and estimates of the m
 Paths:
   * dense causal / full attention of bf16 CUDA tensors without an explicit mask goes to the tcgen05 flash-attention
     kernels of this package (``ops.flash_attention``), which keep only the row statistics;
-  * everything else (windows, block lists, masks, fp32, CPU) runs the tiled algorithm below: per query block, the keys
+  * a causal local window without global blocks (bf16, CUDA) is the same kernels' sliding-window mode: O(N * window);
+  * everything else (global blocks, explicit block lists, masks, fp32, CPU) runs the tiled algorithm below: per query block, the keys
     it can see are visited block by block with a running maximum and sum, so memory is O(N * block) and, with a window,
     time is O(N * window). The tile products are batched matrix multiplications of the tensor library.
 """
@@ -131,20 +132,24 @@ class MemoryEfficientAttention:
     def forward(self, Q, K, V, mask: Optional[torch.Tensor] = None):
         c = self.cfg
         assert Q.shape[2] <= c.max_context_tokens and K.shape[2] <= c.max_context_tokens, "context longer than max_context_tokens"
-        if c.use_block_sparse:
-            idx = self.window_block_indices(Q.shape[2], K.shape[2])
-            return self._run(Q, K, V, mask, idx, c.block_sparse_window)
-        dense_kernel = (Q.is_cuda and Q.dtype == torch.bfloat16 and mask is None and c.dropout_p == 0 and Q.shape[2] == K.shape[2]
-                        and Q.shape[-1] in (64, 128) and Q.shape[2] % 128 == 0)
-        if dense_kernel:
+        kernel_ok = (Q.is_cuda and Q.dtype == torch.bfloat16 and mask is None and c.dropout_p == 0 and Q.shape[2] == K.shape[2]
+                     and Q.shape[-1] in (64, 128) and Q.shape[2] % 128 == 0)
+        # the causal local window (no global blocks) is a mode of the tcgen05 flash kernels: key blocks before the window
+        # are never loaded, forward or backward
+        window = c.block_sparse_window if (c.use_block_sparse and c.causal and c.global_blocks == 0) else 0
+        if kernel_ok and (not c.use_block_sparse or window):
             from .attention import flash_attention
             B, H, N, D = Q.shape
             Hkv = K.shape[1]
             qkv = torch.cat([Q.transpose(1, 2).reshape(B, N, H * D), K.transpose(1, 2).reshape(B, N, Hkv * D),
                              V.transpose(1, 2).reshape(B, N, Hkv * D)], -1)
-            o = flash_attention(qkv, H, Hkv, D, causal=c.causal, scale=c.softmax_scale or None)
-            self.last_stats = SoftmaxStats(0.0, 0.0, ((N + 127) // 128) ** 2)
+            o = flash_attention(qkv, H, Hkv, D, causal=c.causal, scale=c.softmax_scale or None, window=window)
+            nb = (N + 127) // 128
+            self.last_stats = SoftmaxStats(0.0, 0.0, nb * min(nb, (window + 126) // 128 + 1) if window else nb * nb)
             return o.view(B, N, H, D).transpose(1, 2)
+        if c.use_block_sparse:
+            idx = self.window_block_indices(Q.shape[2], K.shape[2])
+            return self._run(Q, K, V, mask, idx, c.block_sparse_window)
         return self._run(Q, K, V, mask, None, None)
 
     __call__ = forward

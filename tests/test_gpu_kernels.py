@@ -328,6 +328,37 @@ def test_flash_attention(D, B, S, H, Hkv, causal):
 
 
 # ------------------------------------------------------------------------------------------ model
+@pytest.mark.parametrize("D,B,S,H,Hkv,window", [(64, 2, 1024, 4, 4, 256), (64, 1, 640, 4, 2, 100), (128, 1, 768, 4, 2, 300), (64, 1, 512, 2, 2, 33),
+                                                 (64, 1, 384, 2, 1, 128)])
+def test_sliding_window_attention(D, B, S, H, Hkv, window):
+    """Causal local window in the tcgen05 flash kernels (forward and backward) against fp32 attention with the same mask:
+    windows that end inside a key block, windows shorter than a block (rows that see nothing of their first block), GQA."""
+    from innova_b200 import ops
+    torch.manual_seed(11)
+    dev = _dev()
+    qkv = (torch.randn(B, S, (H + 2 * Hkv) * D, device=dev) * 0.5).bfloat16().requires_grad_(True)
+    out = ops.flash_attention(qkv, H, Hkv, D, causal=True, window=window)
+    ref_in = qkv.detach().float().requires_grad_(True)
+    ref = ops.attention_reference(ref_in, H, Hkv, D, True, None, window)
+    assert _rel_err(out, ref) < 2e-2
+    w = torch.randn_like(ref)
+    (out.float() * w).sum().backward()
+    (ref * w).sum().backward()
+    assert _rel_err(qkv.grad, ref_in.grad) < 3e-2
+    from innova_b200.ops import runtime as rt
+    rt.check_status()
+    # memory-efficient attention routes the same pattern to these kernels
+    from innova_b200.ops.mea import MEAConfig, MemoryEfficientAttention
+    if S % 128 == 0:
+        q, k, v = qkv.detach().split([H * D, Hkv * D, Hkv * D], -1)
+        Q = q.view(B, S, H, D).transpose(1, 2).contiguous()
+        K = k.view(B, S, Hkv, D).transpose(1, 2).contiguous()
+        V = v.view(B, S, Hkv, D).transpose(1, 2).contiguous()
+        mea = MemoryEfficientAttention(MEAConfig(use_block_sparse=True, block_sparse_window=window, causal=True))
+        o2 = mea(Q, K, V).transpose(1, 2).reshape(B, S, H * D)
+        assert _rel_err(o2, ref) < 2e-2
+
+
 def test_dense_model_matches_cpu_reference():
     from innova_b200.models import DenseModel, gpt2_small
     torch.manual_seed(13)
