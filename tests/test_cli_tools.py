@@ -115,6 +115,32 @@ def test_serve_concurrent_requests_equal_sequential(tiny):
     assert got == want
 
 
+def test_oil_server_token_api(tiny):
+    d, model, corpus = tiny
+    from innova_b200.cli.server import OilServer
+    srv = OilServer(model, device="cpu", max_tokens=16).start(0)
+    try:
+        def call(path, obj=None):
+            req = urllib.request.Request(f"http://127.0.0.1:{srv.port}{path}", data=None if obj is None else json.dumps(obj).encode(),
+                                         method="GET" if obj is None else "POST")
+            with urllib.request.urlopen(req, timeout=60) as r:
+                return r.read()
+        assert json.loads(call("/health"))["status"] == "ok"
+        toks = json.loads(call("/api/tokenize", {"content": "the quick"}))["tokens"]
+        assert len(toks) >= 2 and json.loads(call("/api/detokenize", {"tokens": toks}))["content"] == "the quick"
+        g = json.loads(call("/api/generate", {"prompt": "the quick", "max_tokens": 6, "temperature": 0.0}))
+        assert g["usage"]["prompt_tokens"] == len(toks) and 0 <= g["usage"]["completion_tokens"] <= 6 and isinstance(g["choices"][0]["text"], str)
+        sse = call("/api/generate", {"prompt": "the quick", "max_tokens": 6, "temperature": 0.0, "stream": True}).decode()
+        events = [json.loads(l[6:]) for l in sse.splitlines() if l.startswith("data: ")]
+        assert events[-1]["done"] is True and events[-1]["count"] == len(events) - 1
+        assert "".join(e["token"] for e in events[:-1]) == g["choices"][0]["text"]
+        st, obj, _ = srv.handle("POST", "/api/generate", b"{not json")
+        assert st == 400 and "invalid JSON" in obj["error"]
+        assert srv.handle("POST", "/api/nothing", b"{}")[0] == 404
+    finally:
+        srv.stop()
+
+
 def test_adapters_edition_tools(tiny):
     import io
     from innova_b200.cli import adapters_tools as T
