@@ -43,7 +43,7 @@ class EPContext:
     """Symmetric staging buffers shared by all expert-parallel layers of a process group."""
 
     def __init__(self, group, num_experts: int, hidden: int, max_tokens: int, top_k: int, device, capacity_factor: Optional[float] = None):
-        from .symm import PeerFlags, SymmBuffer
+        from .symm import GuardedSymmBuffer, PeerFlags, SymmBuffer
         self.group = group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         assert num_experts % self.world == 0
@@ -51,8 +51,9 @@ class EPContext:
         cf = float(self.world) if capacity_factor is None else capacity_factor       # world = dropless
         self.cap = (int(cf * max_tokens * top_k) + self.epr * ALIGN + ALIGN - 1) // ALIGN * ALIGN
         self.max_tokens = max_tokens
-        self.stage_in = SymmBuffer(self.cap * hidden, torch.bfloat16, group, device)
-        self.stage_out = SymmBuffer(self.cap * hidden, torch.bfloat16, group, device)
+        # peers store dispatched rows into stage_in and pull results from stage_out: both sit between canary regions
+        self.stage_in = GuardedSymmBuffer(self.cap * hidden, torch.bfloat16, group, device)
+        self.stage_out = GuardedSymmBuffer(self.cap * hidden, torch.bfloat16, group, device)
         self.table = SymmBuffer(self.world * num_experts, torch.int32, group, device)
         self.flags = PeerFlags(4, group)
         self.device = device

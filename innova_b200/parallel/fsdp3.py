@@ -137,10 +137,11 @@ class FSDP3Engine:
         # ---- storage ----
         dev = self.device
         if self.backend == "p2p":
-            from .symm import PeerFlags, SymmBuffer
-            self._shard_buf = SymmBuffer(self.shard_elems, self.dtype, self.group, dev)
+            from .symm import GuardedSymmBuffer, PeerFlags
+            # what peers read (parameter shards, gradient buffers) sits between canary regions: ``check_guards``
+            self._shard_buf = GuardedSymmBuffer(self.shard_elems, self.dtype, self.group, dev)
             self.shard16 = self._shard_buf.tensor
-            self._gslot_buf = SymmBuffer(3 * self.max_unit, torch.float32, self.group, dev)
+            self._gslot_buf = GuardedSymmBuffer(3 * self.max_unit, torch.float32, self.group, dev)
             gs = self._gslot_buf.tensor
             self.flags = PeerFlags(n_sets=8, group=self.group)
             assert C.sizeof(SideJob) == ops.runtime.lib().inv_side_job_struct_bytes(), "SideJob layout differs from the native struct"
@@ -148,9 +149,16 @@ class FSDP3Engine:
             self.shard16 = torch.zeros(self.shard_elems, dtype=self.dtype, device=dev)
             gs = torch.zeros(3 * self.max_unit, dtype=torch.float32, device=dev)
         self.gslots = [gs[i * self.max_unit:(i + 1) * self.max_unit] for i in range(3)]
-        ps = torch.zeros(2 * self.max_unit, dtype=self.dtype, device=dev)
+        # what the side jobs write locally (gathered parameters, reduced gradient shard) is guarded the same way
+        from .symm import CanaryGuard
+        es = torch.empty((), dtype=self.dtype).element_size()
+        self._ps_guard = CanaryGuard(torch.zeros(CanaryGuard.total_bytes(2 * self.max_unit * es), dtype=torch.uint8, device=dev),
+                                     2 * self.max_unit * es)
+        ps = self._ps_guard.payload.view(self.dtype)
         self.pslots = [ps[i * self.max_unit:(i + 1) * self.max_unit] for i in range(2)]
-        self.gshard = torch.zeros(self.shard_elems, dtype=torch.float32, device=dev)
+        self._gs_guard = CanaryGuard(torch.zeros(CanaryGuard.total_bytes(self.shard_elems * 4), dtype=torch.uint8, device=dev),
+                                     self.shard_elems * 4)
+        self.gshard = self._gs_guard.payload.view(torch.float32)
         self.exp_avg = torch.zeros(self.shard_elems, dtype=torch.float32, device=dev)
         self.exp_avg_sq = torch.zeros(self.shard_elems, dtype=torch.float32, device=dev)
         # ---- shard the initial weights (rank 0's), then point every parameter into its rotating buffers ----
@@ -190,6 +198,15 @@ class FSDP3Engine:
             ops.runtime.on_status_error(self._reset_after_error)
             torch.cuda.synchronize()
         dist.barrier(group=self.group)
+
+    def check_guards(self):
+        """Raises if a side job (of any rank) wrote outside the gathered-parameter buffers, the gradient shard, the
+        parameter shards or the gradient unit buffers."""
+        self._ps_guard.check("gathered parameter buffers")
+        self._gs_guard.check("gradient shard")
+        if self.backend == "p2p":
+            self._shard_buf.check("parameter shards")
+            self._gslot_buf.check("gradient unit buffers")
 
     def _reset_after_error(self, code):
         """After a kernel gave up on a wait: arrival counters and partial sums may be half-updated."""

@@ -55,6 +55,17 @@ class FusedGemmComm:
         self._sync = None
         self._epoch = 0
 
+    def check_guards(self):
+        """Every staging buffer of this object sits between canary regions; raises if a fused kernel of any rank wrote
+        outside a payload (call after the collectives have completed, e.g. behind a synchronize)."""
+        for key, b in self._gather.items():
+            b.check(f"all-gather staging {key}")
+        for key, b in self._rs.items():
+            b.check(f"reduce-scatter accumulator {key}")
+        for key, (bufs, _) in self._recv.items():
+            for i, b in enumerate(bufs):
+                b.check(f"reduce-scatter receive slots {key}[{i}]")
+
     # ---------------------------------------------------------------- plumbing
     def _barrier(self):
         if self._sync is None:
@@ -63,17 +74,17 @@ class FusedGemmComm:
         self._sync.barrier(1)
 
     def _gather_buf(self, rows_total, cols):
-        from .symm import SymmBuffer
+        from .symm import GuardedSymmBuffer
         key = (rows_total, cols)
         if key not in self._gather:
-            self._gather[key] = SymmBuffer(rows_total * cols, torch.bfloat16, self.group, self.device)
+            self._gather[key] = GuardedSymmBuffer(rows_total * cols, torch.bfloat16, self.group, self.device)
         return self._gather[key]
 
     def _rs_buf(self, shard_rows, cols):
-        from .symm import SymmBuffer
+        from .symm import GuardedSymmBuffer
         key = (shard_rows, cols)
         if key not in self._rs:
-            self._rs[key] = SymmBuffer(shard_rows * cols, torch.float32, self.group, self.device)
+            self._rs[key] = GuardedSymmBuffer(shard_rows * cols, torch.float32, self.group, self.device)
         return self._rs[key]
 
     def _next_epoch(self, tiles):
@@ -144,14 +155,14 @@ class FusedGemmComm:
                 dist.all_reduce(y, group=self.group)
             return y[r * S:(r + 1) * S].to(out_dtype)
         from ..ops import runtime as rt
-        from .symm import SymmBuffer, ptr_array
+        from .symm import GuardedSymmBuffer, ptr_array
         if out_dtype == torch.bfloat16 and N % 8 == 0:
             # push form: the epilogue stores every tile into this rank's slot at the tile's owner; two receive buffers
             # alternate, so one barrier per call is enough (a rank reaches the call after next only through the next
             # call's barrier, which the slowest reader of this call's slots has to join first)
             key = (S, N)
             if key not in self._recv:
-                self._recv[key] = [[SymmBuffer(W * S * N, torch.bfloat16, self.group, self.device) for _ in range(2)], 0]
+                self._recv[key] = [[GuardedSymmBuffer(W * S * N, torch.bfloat16, self.group, self.device) for _ in range(2)], 0]
             bufs, turn = self._recv[key]
             self._recv[key][1] = turn ^ 1
             buf = bufs[turn]

@@ -147,3 +147,27 @@ class CanaryGuard:
         d = self.damage()
         if d is not None:
             raise RuntimeError(f"{what}: write outside the payload, {d[0]} guard damaged at byte {d[1]}")
+
+
+class GuardedSymmBuffer:
+    """A ``SymmBuffer`` whose payload sits between two canary regions on every rank. Same surface as ``SymmBuffer``
+    (``tensor``, ``peer_ptrs``, ``peers()``, ``rank``, ``world``); the peer pointers already point at the payload.
+    ``check()`` after a fused collective raises if any kernel, local or on a peer, wrote outside this rank's payload."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, group=None, device=None, guard_bytes: int = 256):
+        es = torch.empty((), dtype=dtype).element_size()
+        nbytes = numel * es
+        self.raw = SymmBuffer(CanaryGuard.total_bytes(nbytes, guard_bytes), torch.uint8, group, device)
+        self.guard = CanaryGuard(self.raw.tensor, nbytes, guard_bytes)
+        self.tensor = self.guard.payload.view(dtype)
+        self.rank, self.world, self.group = self.raw.rank, self.raw.world, self.raw.group
+        self.peer_ptrs = [p + guard_bytes for p in self.raw.peer_ptrs]
+        self.multicast_ptr = self.raw.multicast_ptr + guard_bytes if self.raw.multicast_ptr else 0
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)          # every rank's guards are armed before anyone may write
+
+    def peers(self, byte_offset: int = 0):
+        return ptr_array([p + byte_offset for p in self.peer_ptrs])
+
+    def check(self, what: str = "symmetric buffer"):
+        self.guard.check(what)

@@ -90,6 +90,7 @@ def _fsdp3_worker(rank, world, port, out):
             labels = torch.roll(ids, -1, dims=1)
             losses.append(float(tr.train_step(ids, labels)))
         rt.check_status()
+        eng.check_guards()
         full = eng.gather_full("master")
         results[name] = ({k: v.cpu() for k, v in full.items()}, losses, eng.memory_report())
     if rank == 0:
@@ -284,6 +285,7 @@ def _fused_worker(rank, world, port, out):
     y6 = comm.gemm_reduce_scatter(x2_all[:, rank * Kl:(rank + 1) * Kl].contiguous().to(dev), wr)
     res["rs_small"] = float((y6.float().cpu() - ref_s[rank * S2:(rank + 1) * S2]).abs().max() / ref_s.abs().max())
     rt.check_status()
+    comm.check_guards()          # no fused kernel of any rank wrote outside a staging payload
     torch.save(res, out + f".{rank}")
     dist.barrier()
     dist.destroy_process_group()
@@ -326,6 +328,8 @@ def _ep_worker(rank, world, port, out):
         y, aux, counts = m(x, res)
         (y.float() * torch.linspace(-1, 1, D, device=dev)).sum().backward()
     rt.check_status()
+    m.ep.stage_in.check("expert-parallel dispatch staging")
+    m.ep.stage_out.check("expert-parallel result staging")
     outs = {"y": y.float().cpu(), "dx": x.grad.float().cpu(), "gw_gu": m.w_gu.grad.float().cpu(), "gw_down": m.w_down.grad.float().cpu(),
             "gr": m.router.grad.float().cpu(), "counts": counts.cpu()}
     torch.save(outs, out + f".{rank}")
