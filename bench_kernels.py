@@ -2,8 +2,8 @@
 tools/bench.cpp:51-155): device-timed with CUDA events after warm-up, L2 flushed between
 iterations, reported against the measured peaks in MEASURED_PEAKS.json when present.
 
-    python bench_kernels.py --kernel gemm --m 32768 --n 3072 --k 768 [--layout nt|nn|tn|tt] [--iters 20]
-    python bench_kernels.py --kernel attn --batch 16 --seq 1024 --heads 12 --head-dim 64 [--backward]
+    python bench_kernels.py --kernel gemm --m 32768 --n 3072 --k 768 [--layout nt|nn|tn|tt] [--epilogue add|dgelu|gelu] [--iters 20]
+    python bench_kernels.py --kernel attn --batch 16 --seq 1024 --heads 12 --head-dim 64 [--backward] [--window 256]
     python bench_kernels.py --kernel norm|ce|adamw ...
     python bench_kernels.py --kernel all
 """
@@ -57,11 +57,16 @@ def bench_gemm(a):
     B = torch.randn((K, N) if b_mn else (N, K), device="cuda").bfloat16()
     out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
     t = Timer(not a.no_flush)
-    ms = t(lambda: ops.gemm(A, B, out=out, a_mn=a_mn, b_mn=b_mn), a.iters)
+    kw = {}
+    if a.epilogue in ("add", "dgelu"):      # second operand of the epilogue: residual / pre-activation, TMA-loaded box by box
+        kw = dict(epilogue=ops.EPI_ADD if a.epilogue == "add" else ops.EPI_DGELU, aux_in=torch.randn(M, N, device="cuda").bfloat16())
+    elif a.epilogue == "gelu":
+        kw = dict(epilogue=ops.EPI_GELU, aux_out=torch.empty(M, N, device="cuda", dtype=torch.bfloat16))
+    ms = t(lambda: ops.gemm(A, B, out=out, a_mn=a_mn, b_mn=b_mn, **kw), a.iters)
     ref = t(lambda: torch.matmul(A.t() if a_mn else A, B if b_mn else B.t(), out=out), a.iters) if a.compare else None
     hbm, tf, kind = peaks()
     fl = 2.0 * M * N * K
-    res = {"kernel": "gemm_bf16", "M": M, "N": N, "K": K, "layout": a.layout, "ms": ms, "tflops": fl / ms / 1e9,
+    res = {"kernel": "gemm_bf16", "M": M, "N": N, "K": K, "layout": a.layout, "epilogue": a.epilogue, "ms": ms, "tflops": fl / ms / 1e9,
            "frac_of_%s_bf16_peak" % kind: fl / ms / 1e9 / tf}
     if ref:
         res["cublas_ms"] = ref
@@ -76,21 +81,24 @@ def bench_attn(a):
     qkv = (torch.randn(B, S, (H + 2 * Hkv) * D, device="cuda") * 0.5).bfloat16().requires_grad_(a.backward)
     t = Timer(not a.no_flush)
     fl_f = 4.0 * B * H * S * S * D * (0.5 if a.causal else 1.0)
+    w = a.window if (a.causal and 0 < a.window < S) else 0
+    if w:       # visible (query, key) pairs of a causal window: w per row, fewer for the first w rows
+        fl_f = 4.0 * B * H * D * (S * w - w * (w - 1) / 2.0)
     if a.backward:
-        out = ops.flash_attention(qkv, H, Hkv, D, causal=a.causal)
+        out = ops.flash_attention(qkv, H, Hkv, D, causal=a.causal, window=w)
         go = torch.randn_like(out)
 
         def fb():
-            o = ops.flash_attention(qkv, H, Hkv, D, causal=a.causal)
+            o = ops.flash_attention(qkv, H, Hkv, D, causal=a.causal, window=w)
             o.backward(go)
         ms = t(fb, a.iters)
         fl = 3.5 * fl_f
     else:
         with torch.no_grad():
-            ms = t(lambda: ops.flash_attention(qkv, H, Hkv, D, causal=a.causal), a.iters)
+            ms = t(lambda: ops.flash_attention(qkv, H, Hkv, D, causal=a.causal, window=w), a.iters)
         fl = fl_f
     hbm, tf, kind = peaks()
-    return {"kernel": "flash_attn_" + ("fwd_bwd" if a.backward else "fwd"), "B": B, "S": S, "H": H, "Hkv": Hkv, "D": D, "causal": a.causal,
+    return {"kernel": "flash_attn_" + ("fwd_bwd" if a.backward else "fwd"), "B": B, "S": S, "H": H, "Hkv": Hkv, "D": D, "causal": a.causal, "window": w,
             "ms": ms, "tflops": fl / ms / 1e9, "frac_of_%s_bf16_peak" % kind: fl / ms / 1e9 / tf}
 
 
@@ -213,6 +221,8 @@ def main():
     ap.add_argument("--kv-heads", type=int, default=0)
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--causal", type=int, default=1)
+    ap.add_argument("--window", type=int, default=0, help="attn: causal sliding window (0 = full causal)")
+    ap.add_argument("--epilogue", default="none", choices=["none", "add", "dgelu", "gelu"], help="gemm: fused epilogue")
     ap.add_argument("--backward", action="store_true")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--compare", action="store_true", help="also time the library GEMM")

@@ -127,8 +127,9 @@ def _tp_worker(rank, world, port, out, variant=0):
     from innova_b200.parallel.tp import TPDecoder
     cfg = TransformerConfig(vocab_size=1024, hidden_size=512, num_layers=2, num_heads=8, head_dim=64, ffn_hidden_size=1408, num_kv_heads=4,
                             max_seq_len=256)
-    if variant == 2:   # enough heads for 8 ranks (one KV head per rank there), FFN shards that need padding at 8
-        cfg = TransformerConfig(vocab_size=2048, hidden_size=1024, num_layers=2, num_heads=16, head_dim=64, ffn_hidden_size=2752, num_kv_heads=8,
+    if variant == 2:   # enough heads for 8 ranks (one KV head per rank there). FFN 11008: a shard is 1376 columns at 8 ranks (whole
+        # 32-weight quantisation blocks, so that sharded and whole weights quantise alike; padded to the 64-wide k-block), 2752 at 4
+        cfg = TransformerConfig(vocab_size=2048, hidden_size=1024, num_layers=2, num_heads=16, head_dim=64, ffn_hidden_size=11008, num_kv_heads=8,
                                 max_seq_len=256)
     if variant == 1:   # one KV head per rank, a vocabulary shard that is not a whole number of 128-row tiles, padded FFN shard
         cfg = TransformerConfig(vocab_size=1152, hidden_size=512, num_layers=2, num_heads=8, head_dim=64, ffn_hidden_size=2752, num_kv_heads=2,
