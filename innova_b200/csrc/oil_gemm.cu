@@ -60,7 +60,10 @@ struct OilGemmParams {
   float* peers[8];  // mode 2: the same partial sums are added into each of these buffers (every rank's copy of the accumulator)
   int n_peers;
   int multimem;  // 1: out is an NVLS multicast address, every partial sum is added into all ranks' copies; 2: out may hold
-                 // other ranks' partial sums (a peer's buffer): always add, never store
+                 // other ranks' partial sums (a peer's buffer): always add, never store; 3: reduce-scatter: column n is
+                 // added into peers[n / owner_cols] only (the rank that owns that column range), so every partial sum
+                 // crosses NVLink once instead of once per rank
+  int owner_cols;
 };
 
 typedef CUresult (*EncodeTiledFnO)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -447,6 +450,9 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
                     const size_t off = (size_t)gm * p.ldo + n;
                     for (int k = 0; k < p.n_peers; ++k)
                       asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p.peers[k] + off), "f"(val.x), "f"(val.y), "f"(val.z), "f"(val.w) : "memory");
+                  } else if (p.multimem == 3) {  // owner_cols % 4 == 0: the four columns have one owner
+                    asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p.peers[n / p.owner_cols] + (size_t)gm * p.ldo + n),
+                                 "f"(val.x), "f"(val.y), "f"(val.z), "f"(val.w) : "memory");
                   }
                   else if (full)
                     *reinterpret_cast<float4*>(o) = val;
@@ -460,6 +466,8 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
                       if (p.multimem == 1) asm volatile("multimem.red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(o + z), "f"(vv[z]) : "memory");
                       else if (p.multimem == 2) {
                         for (int k = 0; k < p.n_peers; ++k) atomicAdd(p.peers[k] + (size_t)gm * p.ldo + n + z, vv[z]);
+                      } else if (p.multimem == 3) {
+                        atomicAdd_system(p.peers[(n + z) / p.owner_cols] + (size_t)gm * p.ldo + n + z, vv[z]);
                       } else atomicAdd(o + z, vv[z]);
                     }
                 }
@@ -610,7 +618,7 @@ using namespace inv;
 
 static int oil_gemm_launch(const void* x, int ldx, const void* idx, const void* scales, const float* codebook, int bits, float* acc, int ldo,
                            int M, int N, int K, int* status, cudaStream_t st, int multimem, const uint64_t* peers = nullptr, int n_peers = 0,
-                           size_t peer_off = 0) {
+                           size_t peer_off = 0, int owner_cols = 0) {
   using namespace og;
   static int num_sms = 0;
   if (num_sms == 0) {
@@ -626,7 +634,12 @@ static int oil_gemm_launch(const void* x, int ldx, const void* idx, const void* 
   p.codebook = codebook;
   p.out = acc; p.ldo = ldo; p.status = status; p.multimem = multimem;
   p.n_peers = 0;
+  p.owner_cols = owner_cols;
   for (int k = 0; k < 8; ++k) p.peers[k] = nullptr;
+  if (multimem == 3) {
+    p.n_peers = n_peers;
+    for (int k = 0; k < n_peers; ++k) p.peers[k] = reinterpret_cast<float*>(peers[k]) + peer_off;
+  }
   if (multimem == 2) {
     if (peers == nullptr) { p.peers[0] = acc; p.n_peers = 1; }
     else { p.n_peers = n_peers; for (int k = 0; k < n_peers; ++k) p.peers[k] = reinterpret_cast<float*>(peers[k]) + peer_off; }
@@ -703,6 +716,122 @@ extern "C" int inv_oil_gemm_peers(const void* x, int ldx, const void* idx, const
     if (rc) return rc;
   }
   return 0;
+}
+
+// Reduce-scatter form for tensor-parallel row-parallel layers: peers[r] is rank r's accumulator ([M, ldo] fp32, zero on
+// entry); column n of every rank's partial product is added into peers[n / owner_cols] only. After a barrier rank r holds
+// the complete sums of columns [r * owner_cols, (r + 1) * owner_cols).
+extern "C" int inv_oil_gemm_rs(const void* x, int ldx, const void* idx, const void* scales, const float* codebook, int bits,
+                               const uint64_t* peers, int W, int owner_cols, int ldo, int M, int N, int K, int* status, void* stream) {
+  if ((bits != 2 && bits != 4 && bits != 8) || M < 1 || M > 256 || (K % 64) || (ldx % 8) || N < 1 || W < 1 || W > 8 || owner_cols < 4 ||
+      (owner_cols % 4) || owner_cols * W < N)
+    return -ERR_BAD_ARG;
+  for (int m0 = 0; m0 < M; m0 += og::MAXM) {
+    const int m = M - m0 < og::MAXM ? M - m0 : og::MAXM;
+    const int rc = oil_gemm_launch((const __nv_bfloat16*)x + (size_t)m0 * ldx, ldx, idx, scales, codebook, bits,
+                                   reinterpret_cast<float*>(peers[0]) + (size_t)m0 * ldo, ldo, m, N, K, status, (cudaStream_t)stream, 3, peers, W,
+                                   (size_t)m0 * ldo, owner_cols);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+namespace inv {
+struct SlicePeers {
+  __nv_bfloat16* x[8];   // every rank's copy of the [M, N] residual stream
+  float* sumsq[8];       // every rank's [W, M] partial sums of squares
+};
+// Second half of the tensor-parallel all-reduce. This rank owns columns [c0, c0 + cols) of the reduced accumulator: add
+// bias and residual there, round to bf16, write the slice into EVERY rank's copy of the residual stream together with the
+// slice's sum of squares per row, clear the accumulator slice. One CTA per row.
+__global__ void __launch_bounds__(256) tp_slice_finish_push_kernel(float* __restrict__ acc, int ld_acc, const __nv_bfloat16* __restrict__ bias,
+                                                                   const __nv_bfloat16* __restrict__ residual, int ld_res, SlicePeers peers,
+                                                                   int ld_x, int W, int rank, int c0, int cols, int M) {
+  const int m = blockIdx.x;
+  float ss = 0.f;
+  for (int c = threadIdx.x * 4; c < cols; c += blockDim.x * 4) {
+    const int n = c0 + c;
+    float4 v = *reinterpret_cast<float4*>(acc + (size_t)m * ld_acc + n);
+    *reinterpret_cast<float4*>(acc + (size_t)m * ld_acc + n) = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (bias) {
+      const uint2 b = *reinterpret_cast<const uint2*>(bias + n);
+      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+      const float2 f0 = __bfloat1622float2(b2[0]), f1 = __bfloat1622float2(b2[1]);
+      v.x += f0.x; v.y += f0.y; v.z += f1.x; v.w += f1.y;
+    }
+    if (residual) {
+      const uint2 r = *reinterpret_cast<const uint2*>(residual + (size_t)m * ld_res + n);
+      const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&r);
+      const float2 f0 = __bfloat1622float2(r2[0]), f1 = __bfloat1622float2(r2[1]);
+      v.x += f0.x; v.y += f0.y; v.z += f1.x; v.w += f1.y;
+    }
+    uint2 o;
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+    // the norm is taken of the rounded values, as the one-GPU finish pass does
+    const __nv_bfloat162* q2 = reinterpret_cast<const __nv_bfloat162*>(&o);
+    const float2 g0 = __bfloat1622float2(q2[0]), g1 = __bfloat1622float2(q2[1]);
+    ss += g0.x * g0.x + g0.y * g0.y + g1.x * g1.x + g1.y * g1.y;
+    for (int k = 0; k < W; ++k) {
+      const int r = (rank + k) % W;
+      *reinterpret_cast<uint2*>(peers.x[r] + (size_t)m * ld_x + n) = o;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  __shared__ float red[8];
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += red[w];
+    for (int k = 0; k < W; ++k) peers.sumsq[(rank + k) % W][rank * M + m] = t;
+  }
+}
+// h[m, :] = x[m, :] * rsqrt(sum_r sumsq[r][m] / N + eps) * w   (rows of the gathered residual stream)
+__global__ void __launch_bounds__(256) tp_norm_apply_kernel(const __nv_bfloat16* __restrict__ x, int ld_x, const float* __restrict__ sumsq, int W,
+                                                            int M, const __nv_bfloat16* __restrict__ w, float eps, __nv_bfloat16* __restrict__ h,
+                                                            int ld_h, int N) {
+  const int m = blockIdx.x;
+  float t = 0.f;
+  for (int r = 0; r < W; ++r) t += sumsq[r * M + m];
+  const float rs = rsqrtf(t / (float)N + eps);
+  for (int c = threadIdx.x * 4; c < N; c += blockDim.x * 4) {
+    const uint2 xv = *reinterpret_cast<const uint2*>(x + (size_t)m * ld_x + c);
+    const uint2 wv = *reinterpret_cast<const uint2*>(w + c);
+    const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+    const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+    const float2 a0 = __bfloat1622float2(x2[0]), a1 = __bfloat1622float2(x2[1]);
+    const float2 g0 = __bfloat1622float2(w2[0]), g1 = __bfloat1622float2(w2[1]);
+    uint2 o;
+    o.x = pack_bf16x2(a0.x * rs * g0.x, a0.y * rs * g0.y);
+    o.y = pack_bf16x2(a1.x * rs * g1.x, a1.y * rs * g1.y);
+    *reinterpret_cast<uint2*>(h + (size_t)m * ld_h + c) = o;
+  }
+}
+}  // namespace inv
+
+extern "C" int inv_tp_slice_finish_push(float* acc, int ld_acc, const void* bias, const void* residual, int ld_res, const uint64_t* peer_x,
+                                        const uint64_t* peer_sumsq, int ld_x, int W, int rank, int c0, int cols, int M, void* stream) {
+  if (W < 1 || W > 8 || rank < 0 || rank >= W || (cols % 4) || (c0 % 4) || (ld_acc % 4) || (ld_res % 4) || (ld_x % 4) || M < 1) return -ERR_BAD_ARG;
+  SlicePeers sp;
+  for (int r = 0; r < 8; ++r) {
+    sp.x[r] = reinterpret_cast<__nv_bfloat16*>(peer_x[r < W ? r : 0]);
+    sp.sumsq[r] = reinterpret_cast<float*>(peer_sumsq[r < W ? r : 0]);
+  }
+  tp_slice_finish_push_kernel<<<(unsigned)M, 256, 0, (cudaStream_t)stream>>>(acc, ld_acc, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)residual,
+                                                                             ld_res, sp, ld_x, W, rank, c0, cols, M);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+extern "C" int inv_tp_norm_apply(const void* x, int ld_x, const float* sumsq, int W, int M, const void* w, float eps, void* h, int ld_h, int N,
+                                 void* stream) {
+  if ((N % 4) || (ld_x % 4) || (ld_h % 4) || M < 1) return -ERR_BAD_ARG;
+  tp_norm_apply_kernel<<<(unsigned)M, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ld_x, sumsq, W, M, (const __nv_bfloat16*)w, eps,
+                                                                      (__nv_bfloat16*)h, ld_h, N);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
 }
 
 extern "C" int inv_oil_gemm_finish(float* acc, const void* bias, const void* residual, void* out, long M, int N, int ld_acc, int ld_out,

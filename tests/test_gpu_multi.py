@@ -140,6 +140,8 @@ def _tp_worker(rank, world, port, out, variant=0):
         if single and rank != 0:
             continue
         dec = TPDecoder(cfg, max_batch=4, max_seq=128, seed=3, device=dev, single=single)
+        if dec.ctx is not None and variant == 1:
+            dec.ctx.rs_min_world = 2      # the reduce-scatter form of the all-reduce also at two ranks
         dec._splits = 1
         dec._scratch = torch.empty(4 * dec.H * (dec.D + 2), dtype=torch.float32, device=dev)
         l0 = dec.prefill(ids)
