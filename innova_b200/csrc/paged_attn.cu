@@ -75,6 +75,19 @@ __global__ void __launch_bounds__(256) kv_append_kernel(const __nv_bfloat16* __r
   }
 }
 
+// Rows of a token tree. Without it, query row b is the newest token of sequence b and sees seq_lens[b] cached tokens.
+// With it, query row b belongs to sequence row_seq[b] (several rows may share one), sees every cached token below
+// tail_start[b], and of the at most 64 tokens from tail_start[b] on only those whose bit is set in tail_mask[b]
+// (its ancestors in the tree and itself). All three pointers are null or all are set.
+struct TreeRows {
+  const int* row_seq;
+  const int* tail_start;
+  const unsigned long long* tail_mask;
+};
+__device__ __forceinline__ bool token_visible(int tok, int len, int tail0, unsigned long long tail_bits) {
+  return tok < len && (tok < tail0 || ((tail_bits >> ((tok - tail0) & 63)) & 1ull));
+}
+
 // Decode attention: one query token per sequence. grid = (splits, Hkv, B), 128 threads.
 // Writes partial (m, l, o[G][D]) per (b, hk, split) to scratch; attn_combine_kernel finishes.
 template <bool OIL4, int D>
@@ -82,7 +95,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const __nv_bfloat16* 
                                                            int max_pages, const int* __restrict__ seq_lens, int H, int Hkv,
                                                            const uint8_t* __restrict__ k_pool, const uint8_t* __restrict__ v_pool,
                                                            const __half* __restrict__ k_scale, const __half* __restrict__ v_scale, float scale,
-                                                           float* __restrict__ part, int splits) {
+                                                           float* __restrict__ part, int splits, TreeRows tree) {
   constexpr int MAXG = 8;
   constexpr int EPL = D / 32;  // output elements per lane
   constexpr int HALF = D / 2;  // elements per lane in the QK phase (two lanes per token)
@@ -96,7 +109,10 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const __nv_bfloat16* 
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int G = H / Hkv;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int len = seq_lens[b];
+  const int seq = tree.row_seq ? tree.row_seq[b] : b;
+  const int len = seq_lens[seq];
+  const int tail0 = tree.tail_start ? tree.tail_start[b] : len;
+  const unsigned long long tail_bits = tree.tail_mask ? tree.tail_mask[b] : 0ull;
   const int npages = (len + PAGE - 1) / PAGE;
   const int per = (npages + splits - 1) / splits;
   const int p0 = split * per, p1 = min(npages, p0 + per);
@@ -116,7 +132,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const __nv_bfloat16* 
   }
   const int t = lane & 15, hf = lane >> 4;
   for (int pg = p0 + warp; pg < p1; pg += 4) {
-    const int page = page_table[(long)b * max_pages + pg];
+    const int page = page_table[(long)seq * max_pages + pg];
     const long row0 = ((long)page * Hkv + hk) * PAGE;
     // ---- scores: lane = (token t, half hf) ----
     float kf[HALF];
@@ -147,7 +163,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const __nv_bfloat16* 
         }
       }
     }
-    const bool valid = pg * PAGE + t < len;
+    const bool valid = token_visible(pg * PAGE + t, len, tail0, tail_bits);
     float pr[MAXG], alpha[MAXG];
 #pragma unroll
     for (int g = 0; g < MAXG; ++g) {
@@ -255,7 +271,7 @@ __global__ void __launch_bounds__(128, 4) paged_decode_oil4_mma_kernel(const __n
                                                                     const uint8_t* __restrict__ k_pool, const uint8_t* __restrict__ v_pool,
                                                                     const __half* __restrict__ k_scale, const __half* __restrict__ v_scale,
                                                                     float scale, float* __restrict__ part, int splits,
-                                                                    __nv_bfloat16* __restrict__ out_direct, int ld_o) {
+                                                                    __nv_bfloat16* __restrict__ out_direct, int ld_o, TreeRows tree) {
   constexpr int MAXG = 8;
   constexpr int KCH = D / 4;        // d-values of a K row per lane (one quarter of the row)
   constexpr int KW = KCH / 8;       // ... as 32-bit words of indices (4 for D = 128)
@@ -276,7 +292,10 @@ __global__ void __launch_bounds__(128, 4) paged_decode_oil4_mma_kernel(const __n
   const int G = H / Hkv;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gid = lane >> 2, tig = lane & 3;
-  const int len = seq_lens[b];
+  const int seq = tree.row_seq ? tree.row_seq[b] : b;
+  const int len = seq_lens[seq];
+  const int tail0 = tree.tail_start ? tree.tail_start[b] : len;
+  const unsigned long long tail_bits = tree.tail_mask ? tree.tail_mask[b] : 0ull;
   const int npages = (len + PAGE - 1) / PAGE;
   const int per = (npages + splits - 1) / splits;
   const int p0 = split * per, p1 = min(npages, p0 + per);
@@ -303,7 +322,7 @@ __global__ void __launch_bounds__(128, 4) paged_decode_oil4_mma_kernel(const __n
   uint32_t kraw[2][KW], vraw[4][VW];
   __half ksc[2], vsc[4];
   auto fetch = [&](int pg) {
-    const int page = page_table[(long)b * max_pages + pg];
+    const int page = page_table[(long)seq * max_pages + pg];
     const long row0 = ((long)page * Hkv + hk) * PAGE;
 #pragma unroll
     for (int t = 0; t < 2; ++t) {  // K: tokens gid and gid + 8, bytes of d-quarter tig
@@ -373,16 +392,18 @@ __global__ void __launch_bounds__(128, 4) paged_decode_oil4_mma_kernel(const __n
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int tok = pg * PAGE + 8 * t + 2 * tig + e;
-        sv[t * 2 + e] = tok < len ? s[t][e] : -INFINITY;
+        sv[t * 2 + e] = token_visible(tok, len, tail0, tail_bits) ? s[t][e] : -INFINITY;
       }
     float mx = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-    const float m_new = fmaxf(m_run, mx);  // finite: a page in range has at least its first token valid
-    const float alpha = exp2f(m_run - m_new);  // 0 on the first page (m_run = -inf)
+    const float m_new = fmaxf(m_run, mx);
+    // -inf only while a tree row has met nothing but other branches' tokens: keep the exponent arguments defined
+    const float m_ref = m_new == -INFINITY ? 0.f : m_new;
+    const float alpha = exp2f(m_run - m_ref);  // 0 on the first page (m_run = -inf)
     float pe[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) pe[i] = exp2f(sv[i] - m_new);
+    for (int i = 0; i < 4; ++i) pe[i] = exp2f(sv[i] - m_ref);
     l_run = l_run * alpha + (pe[0] + pe[1]) + (pe[2] + pe[3]);
     m_run = m_new;
     const uint32_t pb0 = h2_as_u32(__floats2half2_rn(pe[0], pe[1])), pb1 = h2_as_u32(__floats2half2_rn(pe[2], pe[3]));
@@ -602,9 +623,9 @@ extern "C" int inv_decode_qkv_finish(float* acc, int ld_acc, const void* bias, c
 // Scratch floats needed by inv_paged_decode.
 extern "C" long inv_paged_decode_scratch_floats(int B, int H, int D, int splits) { return (long)B * H * splits * (D + 2); }
 
-extern "C" int inv_paged_decode(const void* q, int ld_q, const int* page_table, int max_pages, const int* seq_lens, int B, int H, int Hkv, int D,
-                                const void* k_pool, const void* v_pool, const void* k_scale, const void* v_scale, int oil4, float scale,
-                                void* out, int ld_o, float* scratch, int splits, void* stream) {
+static int paged_decode_impl(const void* q, int ld_q, const int* page_table, int max_pages, const int* seq_lens, int B, int H, int Hkv, int D,
+                             const void* k_pool, const void* v_pool, const void* k_scale, const void* v_scale, int oil4, float scale,
+                             void* out, int ld_o, float* scratch, int splits, TreeRows tree, void* stream) {
   if ((D != 64 && D != 128) || H % Hkv || H / Hkv > 8 || splits < 1) return -ERR_BAD_ARG;
   if (B <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
@@ -612,13 +633,13 @@ extern "C" int inv_paged_decode(const void* q, int ld_q, const int* page_table, 
 #define INV_PD(O, DD)                                                                                                                      \
   paged_decode_kernel<O, DD><<<grid, 128, 0, st>>>((const __nv_bfloat16*)q, ld_q, page_table, max_pages, seq_lens, H, Hkv,                 \
                                                    (const uint8_t*)k_pool, (const uint8_t*)v_pool, (const __half*)k_scale,                 \
-                                                   (const __half*)v_scale, scale, scratch, splits)
+                                                   (const __half*)v_scale, scale, scratch, splits, tree)
   if (oil4) {
 #define INV_PD4(DD)                                                                                                                        \
   paged_decode_oil4_mma_kernel<DD><<<grid, 128, 0, st>>>((const __nv_bfloat16*)q, ld_q, page_table, max_pages, seq_lens, H, Hkv,               \
                                                      (const uint8_t*)k_pool, (const uint8_t*)v_pool, (const __half*)k_scale,               \
                                                      (const __half*)v_scale, scale, scratch, splits,                                        \
-                                                     splits == 1 ? (__nv_bfloat16*)out : nullptr, ld_o)
+                                                     splits == 1 ? (__nv_bfloat16*)out : nullptr, ld_o, tree)
     if (D == 64) INV_PD4(64); else INV_PD4(128);
 #undef INV_PD4
     if (splits == 1) {  // the kernel wrote the final output
@@ -635,4 +656,24 @@ extern "C" int inv_paged_decode(const void* q, int ld_q, const int* page_table, 
   attn_combine_kernel<<<(int)g, 256, 0, st>>>(scratch, (__nv_bfloat16*)out, ld_o, B, H, Hkv, D, splits);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
+}
+
+extern "C" int inv_paged_decode(const void* q, int ld_q, const int* page_table, int max_pages, const int* seq_lens, int B, int H, int Hkv, int D,
+                                const void* k_pool, const void* v_pool, const void* k_scale, const void* v_scale, int oil4, float scale,
+                                void* out, int ld_o, float* scratch, int splits, void* stream) {
+  return paged_decode_impl(q, ld_q, page_table, max_pages, seq_lens, B, H, Hkv, D, k_pool, v_pool, k_scale, v_scale, oil4, scale, out, ld_o,
+                           scratch, splits, TreeRows{nullptr, nullptr, nullptr}, stream);
+}
+
+// Attention of T query rows over shared sequences with a per-row visibility mask over the newest (at most 64) tokens:
+// the verification pass of tree-structured speculative decoding in one launch (include/oil/inference_opt.h:262-298).
+// Row t attends sequence row_seq[t]: every cached token below tail_start[t], and token tail_start[t] + i iff bit i of
+// tail_mask[t] is set. seq_lens[row_seq[t]] - tail_start[t] must not exceed 64.
+extern "C" int inv_paged_decode_tree(const void* q, int ld_q, const int* page_table, int max_pages, const int* seq_lens, const int* row_seq,
+                                     const int* tail_start, const unsigned long long* tail_mask, int T, int H, int Hkv, int D,
+                                     const void* k_pool, const void* v_pool, const void* k_scale, const void* v_scale, int oil4, float scale,
+                                     void* out, int ld_o, float* scratch, int splits, void* stream) {
+  if (row_seq == nullptr || tail_start == nullptr || tail_mask == nullptr) return -ERR_BAD_ARG;
+  return paged_decode_impl(q, ld_q, page_table, max_pages, seq_lens, T, H, Hkv, D, k_pool, v_pool, k_scale, v_scale, oil4, scale, out, ld_o,
+                           scratch, splits, TreeRows{row_seq, tail_start, tail_mask}, stream);
 }

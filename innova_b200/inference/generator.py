@@ -80,13 +80,20 @@ class Generator:
             else:
                 if li == 0:
                     cache.commit(batch_ids, [start[b] + S for b in range(B)])
-                outs = []
-                for s in range(S):  # S == 1 in the decode loop; > 1 when verifying drafted tokens
-                    if S > 1:
+                    if 1 < S <= 64:   # a chain of drafted tokens: token s sees the cache below start and tokens 0..s of the chain
+                        chain = (torch.tensor(batch_ids, dtype=torch.int32).repeat_interleave(S).to(self.device),
+                                 torch.tensor(start, dtype=torch.int32).repeat_interleave(S).to(self.device),
+                                 torch.tensor([(2 << s) - 1 for s in range(S)] * B, dtype=torch.int64).to(self.device))
+                if S == 1:
+                    a = cache.decode_attention(li, qkv[:, 0], H, scale).unsqueeze(1).to(x.dtype)
+                elif S <= 64:     # all B * S rows in one launch
+                    a = cache.tree_attention(li, qkv.reshape(B * S, -1), H, scale, *chain).view(B, S, -1).to(x.dtype)
+                else:
+                    outs = []
+                    for s in range(S):
                         cache.commit(batch_ids, [start[b] + s + 1 for b in range(B)])
-                    outs.append(cache.decode_attention(li, qkv[:, s], H, scale))
-                a = torch.stack(outs, dim=1).to(x.dtype)
-                if S > 1:
+                        outs.append(cache.decode_attention(li, qkv[:, s], H, scale))
+                    a = torch.stack(outs, dim=1).to(x.dtype)
                     cache.commit(batch_ids, [start[b] + S for b in range(B)])
             att = self.linear(a, blk.attention.o_proj)
             if cfg.use_parallel_residual:
@@ -99,6 +106,54 @@ class Generator:
         assert prefill or slots is None, "decoding runs on cache rows 0..B-1"
         last = m.norm(x if all_logits else x[:, -1])
         logits = ops.linear(last, m.lm_head.weight)
+        return logits[..., : cfg.vocab_size]
+
+    @torch.no_grad()
+    def _forward_tree(self, tokens: List[int], parents: List[int], start: int, row: int = 0) -> torch.Tensor:
+        """One forward over a TREE of new tokens of cache row ``row``, which holds ``start`` committed tokens.
+
+        ``parents[i]`` is the index (< i) of token i's parent among ``tokens``, or -1 when it follows the committed
+        prefix directly. Token i is rotated for position start + depth(i), stored in cache slot start + i, and attends the
+        prefix plus its ancestors and itself: one masked attention launch per layer for the whole tree
+        (include/oil/inference_opt.h:262-298). Returns logits [len(tokens), vocab]. The caller truncates the row to the
+        part it keeps."""
+        m, cfg, cache = self.model, self.cfg, self.cache
+        T = len(tokens)
+        assert 1 <= T <= 64 and all(-1 <= p < i for i, p in enumerate(parents))
+        H, Hkv, D = cfg.num_heads, cfg.kv_heads, cfg.head_dim
+        depth, mask = [], []
+        for i, p in enumerate(parents):
+            depth.append(0 if p < 0 else depth[p] + 1)
+            mask.append((1 << i) | (0 if p < 0 else mask[p]))
+        dev = self.device
+        ids = torch.tensor(tokens, device=dev).view(1, T)
+        pos = torch.tensor([start + d for d in depth], device=dev).view(1, T)
+        row_seq = torch.full((T,), row, dtype=torch.int32, device=dev)
+        tail_start = torch.full((T,), start, dtype=torch.int32, device=dev)
+        tail_mask = torch.tensor(mask, dtype=torch.int64, device=dev)
+        cache.reserve(row, start + T)
+        x = m.tok_embeddings.weight[ids.clamp(0, cfg.padded_vocab - 1)]
+        if m.pos_embeddings is not None:
+            x = x + m.pos_embeddings.weight[pos.clamp(max=cfg.max_seq_len - 1)]
+        rope = m.rope(dev)
+        pos32 = pos.reshape(-1).to(torch.int32).contiguous()
+        scale = D ** -0.5
+        for li, blk in enumerate(m.layers):
+            h = blk.attention_norm(x)
+            qkv = self.linear(h, blk.attention.qkv_proj)
+            if rope is not None:
+                qkv = ops.rope_qk(qkv, rope[0], rope[1], H, Hkv, D, pos32)
+            cache.append(li, qkv[..., H * D:(H + Hkv) * D], qkv[..., (H + Hkv) * D:], [row], [start])
+            if li == 0:
+                cache.commit([row], [start + T])
+            a = cache.tree_attention(li, qkv.view(T, -1), H, scale, row_seq, tail_start, tail_mask).view(1, T, -1).to(x.dtype)
+            att = self.linear(a, blk.attention.o_proj)
+            if cfg.use_parallel_residual:
+                x = x + att + self._ffn(blk, blk.ffn_norm(x))
+            else:
+                x = x + att
+                x = x + self._ffn(blk, blk.ffn_norm(x))
+        logits = ops.linear(m.norm(x[0]), m.lm_head.weight)
         return logits[..., : cfg.vocab_size]
 
     def _ffn(self, blk, h):

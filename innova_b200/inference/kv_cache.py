@@ -24,6 +24,9 @@ _native.register_cuda_sigs({
     "inv_paged_decode": [_native.vp, _native.i32, _native.vp, _native.i32, _native.vp, _native.i32, _native.i32, _native.i32, _native.i32,
                          _native.vp, _native.vp, _native.vp, _native.vp, _native.i32, _native.f32, _native.vp, _native.i32, _native.vp,
                          _native.i32, _native.vp],
+    "inv_paged_decode_tree": [_native.vp, _native.i32, _native.vp, _native.i32, _native.vp, _native.vp, _native.vp, _native.vp, _native.i32,
+                              _native.i32, _native.i32, _native.i32, _native.vp, _native.vp, _native.vp, _native.vp, _native.i32, _native.f32,
+                              _native.vp, _native.i32, _native.vp, _native.i32, _native.vp],
 })
 
 PAGE = 16
@@ -186,3 +189,46 @@ class PagedKVCache:
             p = torch.softmax(s, dim=-1)
             res.append(torch.einsum("hgt,thd->hgd", p, v).reshape(H * D))
         return torch.stack(res).to(q.dtype)
+
+    def tree_attention(self, layer: int, q: torch.Tensor, num_heads: int, scale: float, row_seq: torch.Tensor, tail_start: torch.Tensor,
+                       tail_mask: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Attention of T query rows in ONE launch, several rows per sequence, each with its own view of the newest tokens.
+
+        q: [T, >= H*D]; row t belongs to cache row ``row_seq[t]`` (int32), sees every cached token below ``tail_start[t]``
+        (int32) and token ``tail_start[t] + i`` iff bit i of ``tail_mask[t]`` (int64) is set. The tokens of the tree are
+        already appended and committed, at most 64 past each row's ``tail_start``. A chain of S drafted tokens is the mask
+        ``(1 << (s + 1)) - 1``; a tree row sets the bits of its ancestors and its own (include/oil/inference_opt.h:262-298)."""
+        T = q.shape[0]
+        H, D = num_heads, self.D
+        if q.is_cuda:
+            out = out if out is not None else torch.empty(T, H * D, dtype=torch.bfloat16, device=q.device)
+            max_len = max(self._host_lens) if self._host_lens else 0
+            splits = max(1, min(8, (max_len // PAGE) // 8, (148 * 2) // max(1, T * self.Hkv)))
+            scr = rt.scratch("paged_decode", T * H * splits * (D + 2) * 4, q.device)
+            rc = rt.lib().inv_paged_decode_tree(q.data_ptr(), q.stride(0), self.page_table.data_ptr(), self.max_pages, self.seq_lens.data_ptr(),
+                                                row_seq.data_ptr(), tail_start.data_ptr(), tail_mask.data_ptr(), T, H, self.Hkv, D,
+                                                self.k_pool[layer].data_ptr(), self.v_pool[layer].data_ptr(), rt.ptr(self.k_scale[layer]),
+                                                rt.ptr(self.v_scale[layer]), int(self.fmt == "oil4"), float(scale), out.data_ptr(),
+                                                out.stride(0), scr.data_ptr(), splits, rt.stream_ptr())
+            rt.check(rc, "inv_paged_decode_tree")
+            return out
+        res = []
+        G = H // self.Hkv
+        seqs, starts, masks = row_seq.tolist(), tail_start.tolist(), tail_mask.tolist()
+        kv = {}
+        for t in range(T):
+            b = seqs[t]
+            if b not in kv:
+                kv[b] = self.gather(layer, b)
+            k, v = kv[b]
+            n = k.shape[0]
+            idx = torch.arange(n)
+            bits = torch.tensor([(masks[t] >> i) & 1 for i in range(64)], dtype=torch.bool)
+            vis = (idx < starts[t]) | bits[(idx - starts[t]).clamp(0, 63)]
+            qt = q[t, : H * D].float().view(self.Hkv, G, D)
+            s = torch.einsum("hgd,thd->hgt", qt, k) * scale
+            s = s.masked_fill(~vis.view(1, 1, n), float("-inf"))
+            p = torch.softmax(s, dim=-1)
+            res.append(torch.einsum("hgt,thd->hgd", p, v).reshape(H * D))
+        return torch.stack(res).to(q.dtype)
+

@@ -217,13 +217,16 @@ class SpeculativeDecoderV2:
     """Greedy speculative decoding over a tree of drafts (include/oil/inference_opt.h:248-298, ``SpeculativeDecoderV2``).
 
     Each round the draft model proposes ``n_tree_candidates`` branches: its top-n tokens after the pending token, each
-    continued greedily for ``gamma`` - 1 tokens. The target scores all branches in ONE batched forward (one cache row per
-    branch; every row holds the same committed prefix) and the branch with the longest prefix of argmax matches wins, so
-    a miss on the draft's first choice still yields accepted tokens when a sibling matches. Both models keep their KV
-    caches between rounds: rows are rewound to the committed prefix and the tokens accepted in the last round are fed
-    again together with the next drafts (a few extra columns in a memory-bound forward) instead of copying KV pages
-    between rows. The output equals the target's own greedy decoding. With ``use_tree_attention`` off (or one candidate)
-    it verifies a single chain. Both generators need ``max_batch`` >= ``n_tree_candidates``."""
+    continued greedily for ``gamma`` - 1 tokens. The target scores the whole tree in ONE forward over ONE cache row: the
+    tree's tokens are appended behind the committed prefix and every token attends the prefix plus its own ancestors
+    through the per-row mask of the paged attention kernel (``Generator._forward_tree``: one attention launch per layer,
+    the prefix KV is stored and read once, not once per branch). The branch with the longest prefix of argmax matches
+    wins, so a miss on the draft's first choice still yields accepted tokens when a sibling matches. Both models keep
+    their KV caches between rounds: rows are rewound to the committed prefix and the tokens accepted in the last round
+    are fed again together with the next drafts (a few extra columns in a memory-bound forward) instead of moving KV
+    rows inside the pool. The output equals the target's own greedy decoding. With ``use_tree_attention`` off (or one
+    candidate) it verifies a single chain. The draft generator needs ``max_batch`` >= ``n_tree_candidates`` (it extends
+    the branches as a batch); the target needs one row."""
 
     def __init__(self, draft: Generator, target: Generator, gamma: int = 5, n_tree_candidates: int = 4):
         self.draft, self.target = draft, target
@@ -246,20 +249,20 @@ class SpeculativeDecoderV2:
         import time
         t0 = time.perf_counter()
         tgt, drf = self.target, self.draft
-        n = min(self.n_tree, tgt.cache.max_batch, drf.cache.max_batch) if self.use_tree_attn else 1
+        n = min(self.n_tree, drf.cache.max_batch) if self.use_tree_attn else 1
         rows = list(range(n))
         for g in (tgt, drf):
             for b in range(g.cache.max_batch):
                 g.cache.free(b)
         ids = torch.as_tensor(prompt, dtype=torch.long).view(1, -1)
         L = ids.shape[1]
-        logits = tgt._forward(ids.repeat(n, 1).to(tgt.device), [0] * n)
+        logits = tgt._forward(ids.to(tgt.device), [0])
         drf._forward(ids.repeat(n, 1).to(drf.device), [0] * n)
         pending = int(logits[0].argmax())
         out = [pending]
         carry: List[int] = []               # accepted tokens whose KV is not yet in every row (both models)
         while len(out) < max_tokens and (eos_id is None or out[-1] != eos_id):
-            G = max(1, min(self.gamma, max_tokens - len(out), tgt.max_seq - L - len(carry) - 2))
+            G = max(1, min(self.gamma, max_tokens - len(out), (tgt.max_seq - L - len(carry) - 2) // n, (63 - len(carry)) // n))
             # ---- draft tree: n heads, greedy chains
             feed = torch.tensor([carry + [pending]] * n, device=drf.device)
             dl = drf._forward(feed, [L] * n)
@@ -270,11 +273,14 @@ class SpeculativeDecoderV2:
                 dl = drf._forward(branches[:, -1:].contiguous(), [d_len] * n)
                 d_len += 1
                 branches = torch.cat([branches, dl.argmax(-1, keepdim=True)], 1)
-            # ---- one target forward over all branches
+            # ---- one target forward over the tree: the chain carry + pending, then n branches hanging off pending
             base = len(carry) + 1
-            t_in = torch.cat([feed.to(tgt.device), branches.to(tgt.device)], 1)
-            tl = tgt._forward(t_in, [L] * n, all_logits=True)
-            pred = tl[:, base - 1:].argmax(-1)                         # [n, G + 1]: target's choice after pending, after each draft
+            br = branches.tolist()
+            tokens = carry + [pending] + [t for row in br for t in row]
+            parents = list(range(-1, base - 1)) + [base - 1 if i == 0 else base + j * G + i - 1 for j in range(n) for i in range(G)]
+            tl = tgt._forward_tree(tokens, parents, L).argmax(-1)      # [base + n * G]: the target's choice after each tree token
+            node = torch.arange(n * G, device=tl.device).view(n, G) + base
+            pred = torch.cat([tl[base - 1].expand(n, 1), tl[node]], 1)  # [n, G + 1]: after pending, after each draft
             match = (pred[:, :G] == branches.to(tgt.device)).long().cumprod(1).sum(1)
             best = int(match.argmax())
             k = int(match[best])
@@ -282,9 +288,9 @@ class SpeculativeDecoderV2:
             nxt = int(pred[best, k])
             # ---- commit what every row has in common, rewind the rest
             L += base
-            for g in (tgt, drf):
-                for b in rows:
-                    g.cache.truncate(b, L)
+            tgt.cache.truncate(0, L)
+            for b in rows:
+                drf.cache.truncate(b, L)
             carry = accepted
             out.extend(accepted)
             out.append(nxt)

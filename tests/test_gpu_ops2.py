@@ -252,3 +252,64 @@ def test_continuous_batching_on_gpu_equals_sequential_greedy(kv):
     assert agree >= len(ref) - 1, (out, ref)
     assert all(len(out[i]) == len(ref[i]) for i in ref)
     assert len(cb.gen.cache._free) == cb.gen.cache.num_pages
+
+
+@pytest.mark.parametrize("fmt,D,H,Hkv", [("oil4", 128, 8, 2), ("oil4", 64, 4, 4), ("bf16", 64, 8, 2)])
+def test_tree_attention_one_launch_matches_fp32(fmt, D, H, Hkv):
+    """Rows of a token tree over shared cache rows: the masked paged-attention launch against fp32 softmax attention over
+    the dequantised cache with the same visibility."""
+    from innova_b200.inference.kv_cache import PagedKVCache
+    torch.manual_seed(7)
+    lens = [150, 37]                                   # committed prefix per cache row; several pages, ragged
+    tails = [23, 40]                                   # tree tokens appended behind it (<= 64)
+    cache = PagedKVCache(1, Hkv, D, 2, 256, DEV, fmt)
+    for b, (n, t) in enumerate(zip(lens, tails)):
+        cache.reserve(b, n + t)
+    for b, (n, t) in enumerate(zip(lens, tails)):
+        kv = torch.randn(2, 1, n + t, Hkv * D, device=DEV, dtype=torch.bfloat16)
+        cache.append(0, kv[0], kv[1], [b], [0])
+    cache.commit([0, 1], [n + t for n, t in zip(lens, tails)])
+    gen = torch.Generator().manual_seed(1)
+    row_seq, tail_start, masks = [], [], []
+    for b, (n, t) in enumerate(zip(lens, tails)):
+        for i in range(t):                             # random ancestor sets that always include the token itself
+            m = int(torch.randint(0, 2 ** 31, (1,), generator=gen)) | (int(torch.randint(0, 2 ** 31, (1,), generator=gen)) << 31)
+            masks.append((m & ((1 << i) - 1)) | (1 << i))
+            row_seq.append(b)
+            tail_start.append(n)
+    masks[3] = 1 << 3                                   # a row that sees nothing of the tail but itself
+    masks[-1] = (1 << tails[1]) - 1                     # a row that sees the whole tail
+    T = len(masks)
+    q = torch.randn(T, H * D, device=DEV, dtype=torch.bfloat16)
+    rs = torch.tensor(row_seq, dtype=torch.int32, device=DEV)
+    ts = torch.tensor(tail_start, dtype=torch.int32, device=DEV)
+    tm = torch.tensor(masks, dtype=torch.int64, device=DEV)
+    out = cache.tree_attention(0, q, H, D ** -0.5, rs, ts, tm).float().cpu()
+    G = H // Hkv
+    for t in range(T):
+        k, v = cache.gather(0, row_seq[t])
+        n = k.shape[0]
+        idx = torch.arange(n, device=DEV)
+        vis = (idx < tail_start[t]) | torch.tensor([i >= tail_start[t] and bool((masks[t] >> (i - tail_start[t])) & 1) for i in range(n)],
+                                                    device=DEV)
+        s = torch.einsum("hgd,thd->hgt", q[t].float().view(Hkv, G, D), k) * D ** -0.5
+        p = torch.softmax(s.masked_fill(~vis.view(1, 1, n), float("-inf")), -1)
+        ref = torch.einsum("hgt,thd->hgd", p, v).reshape(H * D).cpu()
+        assert torch.allclose(out[t], ref, atol=3e-2, rtol=3e-2), (t, float((out[t] - ref).abs().max()))
+
+
+def test_speculative_tree_decoder_gpu_equals_greedy():
+    from innova_b200.inference.generator import Generator
+    from innova_b200.inference.speculative import SpeculativeDecoderV2
+    from innova_b200.models import DenseModel, PRESETS
+    cfg = PRESETS["tiny"]()
+    target = DenseModel(cfg, dtype=torch.bfloat16, device=DEV, seed=5)
+    prompt = [1, 5, 9, 2, 7, 3, 3, 8]
+    ref = Generator(target, kv_format="bf16").generate_tokens([prompt], 24)[0]
+    # the target as its own draft: every branch head is one of its top tokens, so every round accepts the whole chain
+    dec = SpeculativeDecoderV2(Generator(target, kv_format="bf16", max_batch=3), Generator(target, kv_format="bf16"), gamma=4,
+                               n_tree_candidates=3)
+    got = dec.generate(prompt, 24)
+    # bf16 logits of the batched draft rows and of the tree rows may break a near tie differently: the prefix must agree
+    agree = next((i for i, (a, b) in enumerate(zip(got, ref)) if a != b), len(ref))
+    assert agree >= 12 and dec.stats.target_calls < 24

@@ -149,3 +149,35 @@ def test_speculative_decoder_v2_tree_equals_greedy_and_beats_a_single_chain():
     own.reset_stats()
     assert own.stats.target_calls == 0
     assert tree.generate(prompt, 20, eos_id=ref[6])[-1] == ref[6]
+
+
+def test_tree_forward_equals_one_chain_forward_per_branch():
+    """A tree of drafts in one forward over one cache row gives, at every node, the logits that a plain forward over the
+    node's own root-to-node chain gives."""
+    from innova_b200.inference.generator import Generator
+    from innova_b200.models import DenseModel, PRESETS
+    cfg = PRESETS["tiny"]()
+    model = DenseModel(cfg, dtype=torch.float32, device="cpu", seed=11)
+    prompt = [3, 8, 1, 6, 2, 9, 4]
+    # tokens: a root chain of 2, then two branches of 3 hanging off token 1, one of which forks again
+    tokens = [5, 7, 11, 12, 13, 21, 22, 23, 31]
+    parents = [-1, 0, 1, 2, 3, 1, 5, 6, 5]
+    g = Generator(model, kv_format="bf16", max_batch=1)
+    g._forward(torch.tensor([prompt]), [0])
+    tree_logits = g._forward_tree(tokens, parents, len(prompt))
+    assert g.cache.lengths()[0] == len(prompt) + len(tokens)
+    for node in (4, 7, 8):
+        chain, i = [], node
+        while i >= 0:
+            chain.append(tokens[i])
+            i = parents[i]
+        chain.reverse()
+        h = Generator(model, kv_format="bf16", max_batch=1)
+        h._forward(torch.tensor([prompt]), [0])
+        ref = h._forward(torch.tensor([chain]), [len(prompt)], all_logits=True)[0, -1]
+        assert torch.allclose(tree_logits[node], ref, atol=1e-4, rtol=1e-4), node
+    # a chain through the batched path (S > 1) uses the same masked attention
+    h = Generator(model, kv_format="bf16", max_batch=2)
+    h._forward(torch.tensor([prompt, prompt]), [0, 0])
+    both = h._forward(torch.tensor([[5, 7, 11], [5, 7, 21]]), [len(prompt)] * 2, all_logits=True)
+    assert torch.allclose(both[0, 2], tree_logits[2], atol=1e-4, rtol=1e-4) and torch.allclose(both[1, 2], tree_logits[5], atol=1e-4, rtol=1e-4)
