@@ -31,6 +31,40 @@ def work():
 ts = [threading.Thread(target=work) for _ in range(4)]
 [t.start() for t in ts]; [t.join() for t in ts]
 pool.reset(); pool.push(); pool.allocate((8,), torch.float32); pool.pop(); pool.reset()
+# native importers: valid files, then a few hundred damaged copies (every outcome but a sanitizer report is fine)
+import json, struct
+from innova_b200.formats.importers import TensorFile
+def st_file():
+    a = rng.standard_normal(64).astype("<f4").tobytes()
+    hdr = json.dumps({"w": {"dtype": "F32", "shape": [8, 8], "data_offsets": [0, 256]}, "__metadata__": {"k": "v"}}).encode()
+    return struct.pack("<Q", len(hdr)) + hdr + a
+def gguf_file():
+    s = lambda x: struct.pack("<Q", len(x)) + x
+    out = b"GGUF" + struct.pack("<IQQ", 3, 2, 1) + s(b"general.alignment") + struct.pack("<II", 4, 32)
+    out += s(b"q") + struct.pack("<IQIQ", 1, 256, 12, 0) + s(b"f") + struct.pack("<IQQIQ", 2, 4, 2, 0, 160)
+    out += b"\0" * (-len(out) % 32)
+    return out + bytes(rng.integers(0, 256, 144, dtype=np.uint8)) + b"\0" * 16 + rng.standard_normal(8).astype("<f4").tobytes()
+for make in (st_file, gguf_file):
+    good = make()
+    q = os.path.join(d, "imp.bin")
+    open(q, "wb").write(good)
+    with TensorFile(q) as f:
+        for name in f.names:
+            f.read(name)
+    for trial in range(300):
+        bad = bytearray(good)
+        if trial % 3 == 0:
+            bad = bad[: int(rng.integers(1, len(bad)))]
+        else:
+            for _ in range(int(rng.integers(1, 4))):
+                bad[int(rng.integers(0, min(len(bad), 200)))] = int(rng.integers(0, 256))
+        open(q, "wb").write(bytes(bad))
+        try:
+            with TensorFile(q) as f:
+                for name in f.names:
+                    f.read(name)
+        except (ValueError, RuntimeError, MemoryError):
+            pass
 print("sanitized run ok")
 """
 
