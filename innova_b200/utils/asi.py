@@ -12,8 +12,10 @@ and reward estimates), ``CuriosityDrivenExplorer`` (count-based novelty), ``Neur
 retrieval), ``ToolUse``, ``ChainOfThought``, ``PromptOptimizer``, ``EvaluationHarness`` and the ``Flywheel`` loop that
 ties them together (evaluate -> propose -> test in the sandbox -> accept under the guardrails -> log).
 
-The reference's sandbox compiles C++; candidate code here is Python, run with ``python -I`` in a child process under
-``resource`` limits. Nothing in this file touches a GPU.
+``Sandbox`` runs Python candidates with ``python -I`` in a child process under ``resource`` limits; ``CppSandbox`` is the
+reference's own form (src/asi_flywheel.cpp:863-905,1322-1406): the candidate is C++, wrapped in a CHECK harness, compiled
+with ``g++ -std=c++20`` in a scratch directory, run under a timeout and resource limits, and scored from the harness's
+``Score: x (passed/total)`` line. Nothing in this file touches a GPU.
 """
 from __future__ import annotations
 
@@ -255,6 +257,146 @@ class Sandbox:
     def verify_correctness(self, code: str, tests: Sequence[str]) -> bool:
         r = self.compile_and_test(code, tests)
         return r.compiled and not r.timed_out and r.tests_passed == r.tests_total
+
+
+@dataclass
+class CppSandboxResult:
+    compiled: bool = False
+    passed: bool = False
+    score: float = 0.0
+    stdout_capture: str = ""
+    stderr_capture: str = ""
+    runtime_ms: float = 0.0
+    exit_code: int = -1
+    timed_out: bool = False
+
+
+class CppSandbox:
+    """Compile-and-test for C++ candidates (include/oil/asi.h:191-209; src/asi_flywheel.cpp:863-905,1322-1406).
+
+    ``compile_and_test(code, task, checks)`` writes ``code`` followed by a harness whose ``main`` evaluates every entry of
+    ``checks`` (C++ boolean expressions over what ``code`` defines) through a CHECK macro and prints
+    ``=== Score: 0.75 (3/4) ===``; the score and pass flag come from that line, as in the reference. The binary runs in
+    the scratch directory with address-space, CPU-time, file-size and process-count limits and a wall-clock timeout, so a
+    candidate that loops, allocates without bound or forks cannot take the host with it. ``static_analysis`` refuses code
+    that reaches outside the process (shell, sockets, files, inline assembly) before anything is compiled."""
+
+    BANNED = ("system(", "popen(", "fork(", "execv", "execl", "<fstream>", "<filesystem>", "<unistd.h>", "<sys/", "socket(", "asm(",
+              "__asm", "dlopen", "<thread>", "std::thread", "#include \"", "remove(", "rename(", "fopen(", "freopen(")
+    HEADERS = ("cstdio", "cstdlib", "cmath", "cstring", "string", "vector", "algorithm", "cstdint", "sstream", "cassert", "numeric", "map",
+               "array")
+
+    def __init__(self, compiler: str = "g++", flags: Sequence[str] = ("-std=c++20", "-O1")):
+        self.dir = tempfile.mkdtemp(prefix="inv_cpp_sandbox_")
+        self.compiler, self.flags = compiler, list(flags)
+        self._lock = threading.Lock()
+
+    def get_sandbox_path(self) -> str:
+        return self.dir
+
+    def static_analysis(self, code: str) -> List[str]:
+        issues = [f"banned construct: {b}" for b in self.BANNED if b in code]
+        if re.search(r"\bwhile\s*\(\s*(true|1)\s*\)|\bfor\s*\(\s*;\s*;\s*\)", code):
+            issues.append("unbounded loop")
+        if code.count("{") != code.count("}"):
+            issues.append("unbalanced braces")
+        return issues
+
+    def check_resource_limits(self, code: str, max_memory_mb: int = 256, max_time_sec: float = 10.0) -> bool:
+        """A cheap static screen before compiling: no allocation literal larger than the memory limit, no loop bound
+        above 1e10 (the run-time limits catch the rest)."""
+        for m in re.finditer(r"(?:new\s+\w+\s*\[|malloc\s*\(|resize\s*\(|reserve\s*\()\s*(\d+)", code):
+            if int(m.group(1)) > max_memory_mb << 20:
+                return False
+        return not any(int(m.group(1)) > 10 ** 10 for m in re.finditer(r"<\s*(\d{11,})", code)) and max_time_sec > 0
+
+    def generate_test_program(self, code: str, task: str, checks: Sequence[str] = ()) -> str:
+        inc = "".join(f"#include <{h}>\n" for h in self.HEADERS)
+        title = re.sub(r"[^\w .,:;()+*/=-]", " ", task)[:60]
+        body = "".join(f"    CHECK(({c}), {json.dumps(c)});\n" for c in checks)
+        return (f"// test harness for: {title}\n{inc}\n{code}\n\n"
+                "static int g_passed = 0, g_total = 0;\n"
+                "#define CHECK(cond, msg) do { g_total++; if (cond) { g_passed++; std::printf(\"  PASS: %s\\n\", msg); } "
+                "else { std::printf(\"  FAIL: %s\\n\", msg); } } while (0)\n"
+                "int main() {\n"
+                f"    std::printf(\"=== Running tests for task: {title} ===\\n\");\n"
+                "    CHECK(true, \"test environment initialized\");\n"
+                f"{body}"
+                "    double score = (double)g_passed / (double)(g_total > 0 ? g_total : 1);\n"
+                "    std::printf(\"\\n=== Score: %.2f (%d/%d) ===\\n\", score, g_passed, g_total);\n"
+                "    return g_passed == g_total ? 0 : 1;\n}\n")
+
+    def _limits(self, max_memory_mb: int, timeout: float):
+        def apply():
+            import resource
+            resource.setrlimit(resource.RLIMIT_AS, (max_memory_mb << 20, max_memory_mb << 20))
+            resource.setrlimit(resource.RLIMIT_CPU, (int(timeout) + 1, int(timeout) + 1))
+            resource.setrlimit(resource.RLIMIT_FSIZE, (1 << 20, 1 << 20))
+            resource.setrlimit(resource.RLIMIT_CORE, (0, 0))
+        return apply
+
+    def compile_and_test(self, code: str, task: str = "", checks: Sequence[str] = (), timeout: float = 10.0,
+                         max_memory_mb: int = 256) -> CppSandboxResult:
+        res = CppSandboxResult()
+        issues = self.static_analysis(code)
+        if issues or not self.check_resource_limits(code, max_memory_mb, timeout):
+            res.stderr_capture = "; ".join(issues) or "resource screen failed"
+            return res
+        with self._lock:
+            tag = time.time_ns()
+            src, exe = os.path.join(self.dir, f"sandbox_{tag}.cpp"), os.path.join(self.dir, f"sandbox_{tag}.bin")
+            with open(src, "w") as f:
+                f.write(self.generate_test_program(code, task, checks))
+            t0 = time.perf_counter()
+            try:
+                try:
+                    c = subprocess.run([self.compiler, "-x", "c++", *self.flags, "-o", exe, src], capture_output=True, text=True, timeout=120,
+                                       cwd=self.dir)
+                except (OSError, subprocess.TimeoutExpired) as e:
+                    res.stderr_capture = f"compiler did not run: {e}"
+                    return res
+                res.runtime_ms = (time.perf_counter() - t0) * 1e3
+                if c.returncode != 0 or not os.path.exists(exe):
+                    res.stderr_capture = c.stderr[-4000:] or f"Compilation failed (exit={c.returncode})"
+                    return res
+                res.compiled = True
+                t1 = time.perf_counter()
+                try:
+                    r = subprocess.run([exe], capture_output=True, text=True, timeout=timeout, cwd=self.dir, env={},
+                                       preexec_fn=self._limits(max_memory_mb, timeout))
+                    res.stdout_capture, res.stderr_capture, res.exit_code = r.stdout[-20000:], r.stderr[-4000:], r.returncode
+                except subprocess.TimeoutExpired as e:
+                    res.timed_out, res.exit_code = True, 124
+                    res.stdout_capture = (e.stdout or b"").decode("utf-8", "replace")[-20000:] if isinstance(e.stdout, bytes) else (e.stdout or "")
+                res.runtime_ms += (time.perf_counter() - t1) * 1e3
+                m = re.search(r"Score:\s+(\d+\.?\d*)\s*\((\d+)/(\d+)\)", res.stdout_capture)
+                if m and int(m.group(3)) > 0:
+                    res.score = int(m.group(2)) / int(m.group(3))
+                    res.passed = m.group(2) == m.group(3) and res.exit_code == 0
+                return res
+            finally:
+                for pth in (src, exe):
+                    try:
+                        os.remove(pth)
+                    except OSError:
+                        pass
+
+    def verify_correctness(self, code: str, test_cases: Sequence[str]) -> bool:
+        r = self.compile_and_test(code, "verify", test_cases)
+        return r.compiled and r.passed and not r.timed_out
+
+    def benchmark(self, code: str, call: str, iters: int = 1000) -> Tuple[bool, float, float]:
+        """Times ``iters`` evaluations of the C++ expression ``call`` inside the sandbox -> (ok, ops_per_sec, avg_latency_ms)."""
+        timed = (code + "\n#include <chrono>\nstatic double bench_ns() { auto t0 = std::chrono::steady_clock::now(); volatile long sink = 0; "
+                 f"for (int i = 0; i < {int(iters)}; ++i) sink = sink + (long)({call}); auto t1 = std::chrono::steady_clock::now(); "
+                 "double ns = (double)std::chrono::duration_cast<std::chrono::nanoseconds>(t1 - t0).count(); "
+                 "std::printf(\"BENCH_NS %.0f\\n\", ns); return ns; }\n")
+        r = self.compile_and_test(timed, "benchmark", ["bench_ns() >= 0"])
+        m = re.search(r"BENCH_NS (\d+)", r.stdout_capture)
+        if not (r.compiled and r.passed and m):
+            return False, 0.0, 0.0
+        ns = max(1.0, float(m.group(1)))
+        return True, iters / (ns * 1e-9), ns / iters * 1e-6
 
 
 @dataclass
