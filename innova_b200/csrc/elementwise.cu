@@ -112,9 +112,11 @@ __global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* __rest
 
 // mode 0: y = gelu(x); 1: dx = dy * gelu'(x); 2: y = silu(g) * u (x = [g | u] halves of a 2F row);
 // 3: SwiGLU backward: d[g|u] from dy, g, u.
+// rows_dev != nullptr: only the first min(rows, *rows_dev) rows are processed (a row count that lives on the device).
 __global__ void act_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ out, long rows,
-                           int F, int mode) {
+                           int F, int mode, const int* __restrict__ rows_dev) {
   const int vec = F / 8;
+  if (rows_dev != nullptr) rows = min(rows, (long)*rows_dev);
   const long total = rows * vec;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
     const long r = i / vec;
@@ -246,7 +248,17 @@ extern "C" int inv_act(const void* x, const void* dy, void* out, long rows, int 
   if (F % 8) return -ERR_BAD_ARG;
   if (rows <= 0) return 0;
   act_kernel<<<grid_for(rows * F / 8, 256), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,
-                                                                          (__nv_bfloat16*)out, rows, F, mode);
+                                                                          (__nv_bfloat16*)out, rows, F, mode, nullptr);
+  CHECK_LAUNCH();
+}
+// The same over the first min(max_rows, *rows_dev) rows: buffers sized for a capacity, filled to a count known on the device.
+extern "C" int inv_act_rows(const void* x, const void* dy, void* out, long max_rows, const int* rows_dev, int F, int mode, void* stream) {
+  if (F % 8 || rows_dev == nullptr) return -ERR_BAD_ARG;
+  if (max_rows <= 0) return 0;
+  long blocks = (max_rows * (F / 8) + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  act_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (__nv_bfloat16*)out, max_rows, F,
+                                                            mode, rows_dev);
   CHECK_LAUNCH();
 }
 extern "C" int inv_rope(void* buf, const int* pos, const float* cos_t, const float* sin_t, int T, int S, int ld, int col0, int nheads, int hd,

@@ -4,10 +4,10 @@
 // [T, D] output per layer; src/moe_model.cpp:484-641) and ExpertDispatcher::plan_all_to_all / dispatch_tokens /
 // gather_results (src/expert_parallel.cpp:408-478) with a dropless all-to-all that moves each routed token once:
 //
-//   counts   every rank publishes its per-expert token counts into all peers' [W, E] table
-//   plan     each rank derives, from that table alone, (a) where in the owner's receive buffer its tokens of
-//            expert e start (owner segments are 128-row aligned per expert, source ranks in rank order inside a
-//            segment) and (b) its own receive layout (segment starts, expert of every 128-row tile)
+//   plan     one launch: every rank publishes its per-expert token counts into all peers' [W, E] table, the ranks meet
+//            at a flag barrier, and each rank derives from its table alone (a) where in the owner's receive buffer its
+//            tokens of expert e start (owner segments are 128-row aligned per expert, source ranks in rank order inside
+//            a segment) and (b) its own receive layout (segment starts, real ends, expert of every 128-row tile)
 //   dispatch one warp per (token, choice) stores the token's row straight into the owner GPU's receive buffer
 //   combine  one warp per token loads its k expert outputs from the owners' output buffers, weights and sums
 //
@@ -25,18 +25,11 @@ struct Peers {
   void* p[MAX_W];
 };
 
-__global__ void ep_push_counts_kernel(Peers tables, const int* __restrict__ counts, int W, int rank, int E) {
-  for (int i = threadIdx.x; i < E * W; i += blockDim.x) {
-    const int r = i / E, e = i % E;
-    reinterpret_cast<int*>(tables.p[r])[rank * E + e] = counts[e];
-  }
-}
-
-// table[W][E] -> send_base[E], local_offsets[epr + 1], tile_expert[max_tiles] (local expert id, -1 unused),
-// cursor[E] = 0, recv_rows[0] = rows used on this rank.
-__global__ void ep_plan_kernel(const int* __restrict__ table, int W, int rank, int E, int epr, int cap_rows, int* __restrict__ send_base,
-                               int* __restrict__ local_offsets, int* __restrict__ tile_expert, int* __restrict__ cursor, int max_tiles,
-                               int* __restrict__ recv_rows) {
+// table[W][E] -> send_base[E], local_offsets[epr + 1], real_end[epr] (one past the last real row of each local
+// segment), tile_expert[max_tiles] (local expert id, -1 unused), cursor[E] = 0, recv_rows[0] = rows used on this rank.
+__device__ void ep_plan_body(const int* __restrict__ table, int W, int rank, int E, int epr, int cap_rows, int* __restrict__ send_base,
+                             int* __restrict__ local_offsets, int* __restrict__ real_end, int* __restrict__ tile_expert, int* __restrict__ cursor,
+                             int max_tiles, int* __restrict__ recv_rows) {
   __shared__ int seg_start[MAX_E];   // start of expert e's segment inside its owner's buffer
   __shared__ int s_local[MAX_E + 1];
   if (threadIdx.x == 0) {
@@ -47,7 +40,10 @@ __global__ void ep_plan_kernel(const int* __restrict__ table, int W, int rank, i
         seg_start[e] = run;
         int tot = 0;
         for (int s = 0; s < W; ++s) tot += table[s * E + e];
-        if (o == rank) s_local[le] = run;
+        if (o == rank) {
+          s_local[le] = run;
+          if (real_end != nullptr) real_end[le] = min(run + tot, cap_rows);
+        }
         run += (tot + ALIGN - 1) / ALIGN * ALIGN;
       }
       if (o == rank) s_local[epr] = run;
@@ -61,7 +57,7 @@ __global__ void ep_plan_kernel(const int* __restrict__ table, int W, int rank, i
     cursor[e] = 0;
   }
   for (int le = threadIdx.x; le <= epr; le += blockDim.x) local_offsets[le] = min(s_local[le], cap_rows);
-  if (threadIdx.x == 0) recv_rows[0] = s_local[epr];
+  if (threadIdx.x == 0) recv_rows[0] = min(s_local[epr], cap_rows);
   for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) {
     const int row = t * ALIGN;
     int ex = -1;
@@ -69,6 +65,54 @@ __global__ void ep_plan_kernel(const int* __restrict__ table, int W, int rank, i
       if (row >= s_local[le] && row < s_local[le + 1]) ex = le;
     tile_expert[t] = ex;
   }
+}
+
+// Counts exchange, the barrier behind it and the plan in ONE launch: publish this rank's counts into every peer's table,
+// raise this rank's word of every peer's flag set to the next epoch (the epoch counter lives on the device), wait (at most
+// a second; the status word records a give-up) until every peer's word has reached it, then plan from the local table.
+__global__ void __launch_bounds__(256) ep_exchange_plan_kernel(Peers tables, Peers flags, uint32_t* __restrict__ local_flags,
+                                                               uint32_t* __restrict__ counter, const int* __restrict__ counts, int W, int rank,
+                                                               int E, int epr, int cap_rows, int* __restrict__ send_base,
+                                                               int* __restrict__ local_offsets, int* __restrict__ real_end,
+                                                               int* __restrict__ tile_expert, int* __restrict__ cursor, int max_tiles,
+                                                               int* __restrict__ recv_rows, int* __restrict__ status) {
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+  for (int i = threadIdx.x; i < E * W; i += blockDim.x) {
+    const int r = i / E, e = i % E;
+    reinterpret_cast<int*>(tables.p[r])[rank * E + e] = counts[e];
+  }
+  if (threadIdx.x == 0) {
+    s_epoch = atomicAdd(counter, 1u) + 1u;
+    s_ok = 1;
+  }
+  __threadfence_system();
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  if (threadIdx.x < W) {
+    uint32_t* f = reinterpret_cast<uint32_t*>(flags.p[threadIdx.x]) + rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
+    uint64_t t0 = 0;
+    uint32_t spins = 0, v;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local_flags + threadIdx.x) : "memory");
+      if ((int32_t)(v - epoch) >= 0) break;
+      if ((++spins & 0xffu) == 0) {
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > 1000000000ull) {
+          s_ok = 0;
+          if (status) atomicCAS(status, 0, (int)inv::ERR_WAIT_PEER);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (!s_ok) return;   // a peer never arrived: leave the plan untouched, the host reads the status word
+  ep_plan_body(reinterpret_cast<const int*>(tables.p[rank]), W, rank, E, epr, cap_rows, send_base, local_offsets, real_end, tile_expert, cursor,
+               max_tiles, recv_rows);
 }
 
 // assign = 1: claim a row (send_base[e] + cursor[e]++) and remember it in slot; assign = 0: reuse slot.
@@ -156,6 +200,24 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(Peers ybuf, const int* 
   }
 }
 
+// Zero the padding rows of this rank's receive segments (rows between an expert's last real row and the next 128-row
+// boundary): the only rows of the receive buffer that the expert GEMMs read and that no peer writes.
+__global__ void __launch_bounds__(256) ep_zero_pad_kernel(__nv_bfloat16* __restrict__ stage, const int* __restrict__ local_offsets,
+                                                          const int* __restrict__ real_end, int D) {
+  const int le = blockIdx.y;
+  const int lo = real_end[le], hi = local_offsets[le + 1];
+  const long vec = D / 8;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < (long)(hi - lo) * vec; i += (long)gridDim.x * blockDim.x)
+    reinterpret_cast<uint4*>(stage + (size_t)lo * D)[i] = make_uint4(0, 0, 0, 0);
+}
+
+// dst[r] = src[r] for r < min(max_rows, *rows_dev); rows of row_bytes (a multiple of 16).
+__global__ void __launch_bounds__(256) copy_rows_dev_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, long vec_per_row, long max_rows,
+                                                            const int* __restrict__ rows_dev) {
+  const long total = min(max_rows, (long)*rows_dev) * vec_per_row;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
 static int fill(Peers& pp, const uint64_t* host_ptrs, int W) {
   if (W < 1 || W > MAX_W) return -1;
   for (int i = 0; i < MAX_W; ++i) pp.p[i] = i < W ? reinterpret_cast<void*>(host_ptrs[i]) : nullptr;
@@ -172,19 +234,6 @@ using namespace inv::ep;
     return e == cudaSuccess ? 0 : -(int)e;  \
   } while (0)
 
-extern "C" int inv_ep_push_counts(const uint64_t* peer_tables, const int* counts, int W, int rank, int E, void* stream) {
-  Peers t;
-  if (fill(t, peer_tables, W) || E < 1 || E > MAX_E) return -inv::ERR_BAD_ARG;
-  ep_push_counts_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(t, counts, W, rank, E);
-  EP_RET();
-}
-extern "C" int inv_ep_plan(const int* table, int W, int rank, int E, int experts_per_rank, int cap_rows, int* send_base, int* local_offsets,
-                           int* tile_expert, int* cursor, int max_tiles, int* recv_rows, void* stream) {
-  if (W < 1 || W > MAX_W || E < 1 || E > MAX_E || experts_per_rank * W != E) return -inv::ERR_BAD_ARG;
-  ep_plan_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(table, W, rank, E, experts_per_rank, cap_rows, send_base, local_offsets, tile_expert, cursor,
-                                                      max_tiles, recv_rows);
-  EP_RET();
-}
 extern "C" int inv_ep_dispatch(const void* x, const int* topk_idx, const int* send_base, int* cursor, int* slot, const float* scale_w,
                                const uint64_t* peer_recv, int W, int T, int K, int D, int experts_per_rank, int cap_rows, int assign, void* stream) {
   Peers r;
@@ -202,5 +251,26 @@ extern "C" int inv_ep_combine(const uint64_t* peer_y, int W, const int* topk_idx
   if (T <= 0) return 0;
   ep_combine_kernel<<<(T + 7) / 8, 256, 0, (cudaStream_t)stream>>>(y, topk_idx, slot, weights, (const __nv_bfloat16*)residual, (__nv_bfloat16*)out,
                                                                   (__nv_bfloat16*)y_copy, T, K, D, experts_per_rank);
+  EP_RET();
+}
+extern "C" int inv_ep_zero_pad(void* stage, const int* local_offsets, const int* real_end, int experts_per_rank, int D, void* stream) {
+  if (experts_per_rank < 1 || experts_per_rank > MAX_E || D % 8) return -inv::ERR_BAD_ARG;
+  ep_zero_pad_kernel<<<dim3(8, experts_per_rank), 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)stage, local_offsets, real_end, D);
+  EP_RET();
+}
+extern "C" int inv_ep_exchange_plan(const uint64_t* peer_tables, const uint64_t* peer_flags, void* local_flags, void* counter, const int* counts,
+                                    int W, int rank, int E, int experts_per_rank, int cap_rows, int* send_base, int* local_offsets, int* real_end,
+                                    int* tile_expert, int* cursor, int max_tiles, int* recv_rows, int* status, void* stream) {
+  Peers t, f;
+  if (fill(t, peer_tables, W) || fill(f, peer_flags, W) || E < 1 || E > MAX_E || experts_per_rank * W != E) return -inv::ERR_BAD_ARG;
+  ep_exchange_plan_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(t, f, (uint32_t*)local_flags, (uint32_t*)counter, counts, W, rank, E,
+                                                               experts_per_rank, cap_rows, send_base, local_offsets, real_end, tile_expert, cursor,
+                                                               max_tiles, recv_rows, status);
+  EP_RET();
+}
+extern "C" int inv_copy_rows_dev(void* dst, const void* src, long row_bytes, long max_rows, const int* rows_dev, void* stream) {
+  if (row_bytes % 16 || rows_dev == nullptr) return -inv::ERR_BAD_ARG;
+  if (max_rows <= 0) return 0;
+  copy_rows_dev_kernel<<<148 * 8, 256, 0, (cudaStream_t)stream>>>((uint4*)dst, (const uint4*)src, row_bytes / 16, max_rows, rows_dev);
   EP_RET();
 }

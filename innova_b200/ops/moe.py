@@ -43,6 +43,12 @@ def _grouped(a, b, out, *, mode, E, tile_expert, offsets, rows_b, a_mn=False, b_
     return out
 
 
+def wgrad_split_k(groups: int, m: int, n: int) -> int:
+    """Split the contraction of a grouped weight-gradient GEMM only while whole 128 x 256 output tiles would leave SMs idle:
+    every split is one more atomic read-modify-write pass over the fp32 gradient."""
+    return 1 if groups * ((m + 127) // 128) * ((n + 255) // 256) >= 2 * 148 else 4
+
+
 def _main_grad_or_new(w):
     mg = getattr(w, "main_grad", None)
     if mg is not None:
@@ -122,7 +128,7 @@ class _MoEFn(torch.autograd.Function):
         _grouped(dy_perm, w_down.view(E * D, Fh), dact, mode=1, E=E, tile_expert=tile_expert, offsets=offsets, rows_b=D, b_mn=True, M=R, N=Fh, K=D)
         gd, own_d = _main_grad_or_new(w_down)
         _grouped(dy_perm, act, gd.view(E, D, Fh), mode=2, E=E, tile_expert=None, offsets=offsets, rows_b=0, a_mn=True, b_mn=True, M=D, N=Fh, K=R,
-                 split_k=4, stride_c=D * Fh)
+                 split_k=wgrad_split_k(E, D, Fh), stride_c=D * Fh)
         # SwiGLU
         dgu = torch.empty_like(gu)
         rt.check(lib.inv_act(gu.data_ptr(), dact.data_ptr(), dgu.data_ptr(), R, Fh, 3, st), "inv_act")
@@ -132,7 +138,7 @@ class _MoEFn(torch.autograd.Function):
                  K=2 * Fh)
         ggu, own_gu = _main_grad_or_new(w_gu)
         _grouped(dgu, x_perm, ggu.view(E, 2 * Fh, D), mode=2, E=E, tile_expert=None, offsets=offsets, rows_b=0, a_mn=True, b_mn=True, M=2 * Fh, N=D,
-                 K=R, split_k=4, stride_c=2 * Fh * D)
+                 K=R, split_k=wgrad_split_k(E, 2 * Fh, D), stride_c=2 * Fh * D)
         # gather token gradients back (plain sum over the k copies)
         dx = torch.empty((T, D), dtype=torch.bfloat16, device=dev)
         rt.check(lib.inv_moe_combine(dx_perm.data_ptr(), slot.data_ptr(), 0, 0, dx.data_ptr(), 0, 0, T, K, D, st), "inv_moe_combine")

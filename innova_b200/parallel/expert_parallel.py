@@ -30,10 +30,12 @@ from ..ops import moe as moe_ops
 
 vp, i32 = _native.vp, _native.i32
 _native.register_cuda_sigs({
-    "inv_ep_push_counts": [vp, vp, i32, i32, i32, vp],
-    "inv_ep_plan": [vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, i32, vp, vp],
     "inv_ep_dispatch": [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp],
     "inv_ep_combine": [vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp],
+    "inv_ep_exchange_plan": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, i32, vp, vp, vp],
+    "inv_ep_zero_pad": [vp, vp, vp, i32, i32, vp],
+    "inv_copy_rows_dev": [vp, vp, _native.i64, _native.i64, vp, vp],
+    "inv_act_rows": [vp, vp, vp, _native.i64, vp, i32, i32, vp],
 })
 
 ALIGN = 128
@@ -56,10 +58,15 @@ class EPContext:
         self.stage_out = GuardedSymmBuffer(self.cap * hidden, torch.bfloat16, group, device)
         self.table = SymmBuffer(self.world * num_experts, torch.int32, group, device)
         self.flags = PeerFlags(4, group)
+        self.counters = torch.zeros(4, dtype=torch.int32, device=device)     # device-side epochs of flag sets 0 (barrier) and 1 (counts)
         self.device = device
 
     def barrier(self):
-        self.flags.barrier(0)
+        """All ranks meet on the current stream: one launch, the epoch lives on the device."""
+        from ..ops import runtime as rt
+        f = self.flags
+        rt.check(rt.lib().inv_device_barrier(f.set_ptrs(0), f.set_ptr_local(0), self.counters.data_ptr(), self.world, self.rank,
+                                             rt.status_tensor(self.device).data_ptr(), rt.stream_ptr()), "inv_device_barrier")
 
 
 class _EPMoEFn(torch.autograd.Function):
@@ -88,26 +95,33 @@ class _EPMoEFn(torch.autograd.Function):
                                     top_k, st), "inv_moe_router")
         stage_in = ep.stage_in.tensor.view(cap, D)
         stage_out = ep.stage_out.tensor.view(cap, D)
-        stage_in.zero_()                       # padding rows of the segments must be zero for the weight gradients
-        rt.check(lib.inv_ep_push_counts(ep.table.peers(), counts.data_ptr(), W, ep.rank, E, st), "inv_ep_push_counts")
-        ep.barrier()
         max_tiles = cap // ALIGN
-        send_base = torch.empty(E, dtype=torch.int32, device=dev)
-        offsets = torch.empty(epr + 1, dtype=torch.int32, device=dev)
-        tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
-        cursor = torch.empty(E, dtype=torch.int32, device=dev)
-        recv_rows = torch.empty(1, dtype=torch.int32, device=dev)
-        rt.check(lib.inv_ep_plan(ep.table.tensor.data_ptr(), W, ep.rank, E, epr, cap, send_base.data_ptr(), offsets.data_ptr(),
-                                 tile_expert.data_ptr(), cursor.data_ptr(), max_tiles, recv_rows.data_ptr(), st), "inv_ep_plan")
+        # one int32 block for the plan: send_base[E] | cursor[E] | offsets[epr + 1] | real_end[epr] | recv_rows[1] | tile_expert[max_tiles]
+        plan = torch.empty(2 * E + 2 * epr + 2 + max_tiles, dtype=torch.int32, device=dev)
+        send_base, cursor = plan[:E], plan[E:2 * E]
+        offsets = plan[2 * E:2 * E + epr + 1]
+        real_end = plan[2 * E + epr + 1:2 * E + 2 * epr + 1]
+        recv_rows = plan[2 * E + 2 * epr + 1:2 * E + 2 * epr + 2]
+        tile_expert = plan[2 * E + 2 * epr + 2:]
+        # counts to every peer + the barrier behind them + the plan, one launch. This barrier is also what lets the staging
+        # buffers be reused: a rank passes it only after every peer has finished the previous layer's reads of them.
+        fl = ep.flags
+        rt.check(lib.inv_ep_exchange_plan(ep.table.peers(), fl.set_ptrs(1), fl.set_ptr_local(1), ep.counters.data_ptr() + 4, counts.data_ptr(), W,
+                                          ep.rank, E, epr, cap, send_base.data_ptr(), offsets.data_ptr(), real_end.data_ptr(),
+                                          tile_expert.data_ptr(), cursor.data_ptr(), max_tiles, recv_rows.data_ptr(),
+                                          rt.status_tensor(dev).data_ptr(), st), "inv_ep_exchange_plan")
+        # padding rows of the segments must be zero for the weight gradients; every other row the GEMMs read is written by a peer
+        rt.check(lib.inv_ep_zero_pad(stage_in.data_ptr(), offsets.data_ptr(), real_end.data_ptr(), epr, D, st), "inv_ep_zero_pad")
         slot = torch.empty((T, top_k), dtype=torch.int32, device=dev)
         rt.check(lib.inv_ep_dispatch(x2.data_ptr(), idx.data_ptr(), send_base.data_ptr(), cursor.data_ptr(), slot.data_ptr(), 0,
                                      ep.stage_in.peers(), W, T, top_k, D, epr, cap, 1, st), "inv_ep_dispatch")
         ep.barrier()                           # every rank's rows have landed
-        x_perm = stage_in.clone()
+        x_perm = torch.empty((cap, D), dtype=torch.bfloat16, device=dev)       # kept for the weight gradients; rows in use only
+        rt.check(lib.inv_copy_rows_dev(x_perm.data_ptr(), stage_in.data_ptr(), D * 2, cap, recv_rows.data_ptr(), st), "inv_copy_rows_dev")
         gu = torch.empty((cap, F2), dtype=torch.bfloat16, device=dev)
         moe_ops._grouped(x_perm, w_gu.view(epr * F2, D), gu, mode=1, E=epr, tile_expert=tile_expert, offsets=offsets, rows_b=F2, M=cap, N=F2, K=D)
         act = torch.empty((cap, Fh), dtype=torch.bfloat16, device=dev)
-        rt.check(lib.inv_act(gu.data_ptr(), 0, act.data_ptr(), cap, Fh, 2, st), "inv_act")
+        rt.check(lib.inv_act_rows(gu.data_ptr(), 0, act.data_ptr(), cap, recv_rows.data_ptr(), Fh, 2, st), "inv_act_rows")
         moe_ops._grouped(act, w_down.view(epr * D, Fh), stage_out, mode=1, E=epr, tile_expert=tile_expert, offsets=offsets, rows_b=D, M=cap, N=D,
                          K=Fh)
         ep.barrier()                           # every owner's outputs are complete
@@ -116,12 +130,12 @@ class _EPMoEFn(torch.autograd.Function):
         res2 = None if residual is None else residual.reshape(T, D).contiguous()
         rt.check(lib.inv_ep_combine(ep.stage_out.peers(), W, idx.data_ptr(), slot.data_ptr(), wts.data_ptr(), rt.ptr(res2), out.data_ptr(),
                                     y_local.data_ptr(), T, top_k, D, epr, st), "inv_ep_combine")
-        ep.barrier()                           # staging buffers may be reused
+        # no barrier here: the next use of the staging buffers starts with one (the counts exchange, or the backward pass's first)
         f_e = counts.float() / float(T * top_k)
         p_e = stats[:E] / float(T)
         aux = lb_coef * E * (f_e * p_e).sum() + z_coef * stats[2 * E] / float(T)
         ctx.save_for_backward(x2, router_w, w_gu, w_down, logits, probs, idx, wts, slot, offsets, tile_expert, x_perm, gu, act, y_local, f_e,
-                              send_base)
+                              send_base, real_end, recv_rows)
         ctx.cfg = (shp, T, E, Fh, D, top_k, lb_coef, z_coef, residual is not None)
         ctx.ep = ep
         return out.view(shp), aux, counts
@@ -131,7 +145,7 @@ class _EPMoEFn(torch.autograd.Function):
         from ..ops import runtime as rt
         from ..ops.gemm import EPI_ATOMIC, gemm
         (x2, router_w, w_gu, w_down, logits, probs, idx, wts, slot, offsets, tile_expert, x_perm, gu, act, y_local, f_e,
-         send_base) = ctx.saved_tensors
+         send_base, real_end, recv_rows) = ctx.saved_tensors
         shp, T, E, Fh, D, K, lb_coef, z_coef, has_res = ctx.cfg
         ep: EPContext = ctx.ep
         epr, W, cap = ep.epr, ep.world, ep.cap
@@ -144,8 +158,8 @@ class _EPMoEFn(torch.autograd.Function):
         rt.check(lib.inv_moe_combine(y_local.data_ptr(), ar.data_ptr(), 0, 0, 0, g.data_ptr(), dw.data_ptr(), T, K, D, st), "inv_moe_combine")
         stage_in = ep.stage_in.tensor.view(cap, D)
         stage_out = ep.stage_out.tensor.view(cap, D)
-        stage_in.zero_()
-        ep.barrier()
+        rt.check(lib.inv_ep_zero_pad(stage_in.data_ptr(), offsets.data_ptr(), real_end.data_ptr(), epr, D, st), "inv_ep_zero_pad")
+        ep.barrier()                           # every peer is done with the previous contents of the staging buffers
         rt.check(lib.inv_ep_dispatch(g.data_ptr(), idx.data_ptr(), send_base.data_ptr(), 0, slot.data_ptr(), wts.data_ptr(), ep.stage_in.peers(), W,
                                      T, K, D, epr, cap, 0, st), "inv_ep_dispatch")
         ep.barrier()
@@ -154,20 +168,20 @@ class _EPMoEFn(torch.autograd.Function):
         moe_ops._grouped(dy_perm, w_down.view(epr * D, Fh), dact, mode=1, E=epr, tile_expert=tile_expert, offsets=offsets, rows_b=D, b_mn=True,
                          M=cap, N=Fh, K=D)
         gd, own_d = moe_ops._main_grad_or_new(w_down)
+        sk = lambda m, n: moe_ops.wgrad_split_k(epr, m, n)
         moe_ops._grouped(dy_perm, act, gd.view(epr, D, Fh), mode=2, E=epr, tile_expert=None, offsets=offsets, rows_b=0, a_mn=True, b_mn=True, M=D,
-                         N=Fh, K=cap, split_k=4, stride_c=D * Fh)
+                         N=Fh, K=cap, split_k=sk(D, Fh), stride_c=D * Fh)
         dgu = torch.empty_like(gu)
-        rt.check(lib.inv_act(gu.data_ptr(), dact.data_ptr(), dgu.data_ptr(), cap, Fh, 3, st), "inv_act")
+        rt.check(lib.inv_act_rows(gu.data_ptr(), dact.data_ptr(), dgu.data_ptr(), cap, recv_rows.data_ptr(), Fh, 3, st), "inv_act_rows")
         moe_ops._grouped(dgu, w_gu.view(epr * 2 * Fh, D), stage_out, mode=1, E=epr, tile_expert=tile_expert, offsets=offsets, rows_b=2 * Fh,
                          b_mn=True, M=cap, N=D, K=2 * Fh)
         ggu, own_gu = moe_ops._main_grad_or_new(w_gu)
         moe_ops._grouped(dgu, x_perm, ggu.view(epr, 2 * Fh, D), mode=2, E=epr, tile_expert=None, offsets=offsets, rows_b=0, a_mn=True, b_mn=True,
-                         M=2 * Fh, N=D, K=cap, split_k=4, stride_c=2 * Fh * D)
+                         M=2 * Fh, N=D, K=cap, split_k=sk(2 * Fh, D), stride_c=2 * Fh * D)
         ep.barrier()
         dx = torch.empty((T, D), dtype=torch.bfloat16, device=dev)
         rt.check(lib.inv_ep_combine(ep.stage_out.peers(), W, idx.data_ptr(), slot.data_ptr(), 0, 0, dx.data_ptr(), 0, T, K, D, epr, st),
                  "inv_ep_combine")
-        ep.barrier()
         dprobs = torch.zeros((T, E), dtype=torch.float32, device=dev)
         dprobs.scatter_add_(1, idx.long(), dw)
         da = daux if daux is not None else torch.zeros((), device=dev)
