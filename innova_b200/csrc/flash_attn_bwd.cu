@@ -21,6 +21,18 @@
 namespace inv {
 
 int make_tmap_tokens_bf16(CUtensorMap* out, const void* ptr, int cols, int S, int B, int ld, int box_rows);
+int make_tmap_tokens_f32(CUtensorMap* out, const void* ptr, int cols, int S, int B);
+
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }  // sources read
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }        // copies complete
+// Adds a [1 x 128 rows x 32 floats] shared-memory box (128-byte swizzle) into the fp32 tensor behind the map. Rows past
+// the end of a sequence are clipped by the copy engine.
+__device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2) {
+  asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
 
 constexpr int FB_THREADS = 640;  // warp 0 TMA, warps 1, 18, 19 MMA issuers, warps 2-17 softmax (four per scheduler: the
                                  // dependent FMA -> MUFU -> FMUL -> convert chains of two warps per scheduler left it mostly idle)
@@ -49,16 +61,29 @@ struct BwdSmem {
   static constexpr int DO_OFF = Q_OFF + STAGES * TILE;
   static constexpr int PT_OFF = DO_OFF + STAGES * TILE;
   static constexpr int DST_OFF = PT_OFF + 32768;
-  static constexpr int STAT_OFF = DST_OFF + 32768;     // lse and delta of the current query block, two stages
+  static constexpr int DQS_OFF = DST_OFF + 32768;      // D = 64: the fp32 dQ block (two 128 x 32 boxes) on its way to the reduce copy
+  static constexpr int STAT_OFF = DQS_OFF + (ND == 1 ? 32768 : 0);  // lse and delta of the current query block, two stages
   static constexpr int BAR_OFF = STAT_OFF + 2 * 2 * 128 * 4;
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
+// Build with -DFB_TRACE to record the SM clock at the phases of CTA (0, 0, 0) of the most recent launch
+// (inv_fb_trace_read): 0 entry, 1 set-up done, 2 K/V landed (issuer), 3 exit, 4 dK/dV written, 8 + 3 it: S^T ready for
+// query block it, 9 + 3 it: P^T / dS^T published, 10 + 3 it: dQ of block it - 1 read out.
+#ifdef FB_TRACE
+__device__ long long fb_trace_buf[64];
+#define FB_STAMP(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (i) < 64) fb_trace_buf[i] = clock64(); } while (0)
+#else
+#define FB_STAMP(i) do {} while (0)
+#endif
+
 template <int ND>
 __global__ void __launch_bounds__(FB_THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do, const FlashBwdParams p) {
+                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                 const __grid_constant__ CUtensorMap tmap_dq, const FlashBwdParams p) {
   constexpr int D = 64 * ND;
+  constexpr bool DQ_TMA = (ND == 1);  // dQ blocks leave through shared memory and one reduce copy per 32 columns, not per-thread reductions
   using L = BwdSmem<ND>;
   constexpr int STAGES = L::STAGES;
   constexpr bool OVERLAP = (ND == 1);  // D = 128 has no spare TMEM: dQ reuses the S^T columns
@@ -73,6 +98,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   uint8_t* sdO = smem + L::DO_OFF;
   uint8_t* sPt = smem + L::PT_OFF;
   uint8_t* sdSt = smem + L::DST_OFF;
+  uint8_t* sDq = smem + L::DQS_OFF;
   float* sStat = reinterpret_cast<float*>(smem + L::STAT_OFF);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* kv_full = bars;        // 1
@@ -96,6 +122,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int i_end = (p.causal && p.window > 0) ? min(nqb, (k0 + 126 + p.window) / 128 + 1) : nqb;
   const int nq_it = i_end - i0;
   const int n_it = G * nq_it;
+  if (threadIdx.x == 0) FB_STAMP(0);
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -114,6 +141,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
     tma_prefetch_desc(&tmap_do);
+    if (DQ_TMA) tma_prefetch_desc(&tmap_dq);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -123,6 +151,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) FB_STAMP(1);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -161,6 +190,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV);
       const uint32_t pt_base = smem_u32(sPt), dst_base = smem_u32(sdSt);
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.status, ERR_WAIT_FULL);
+      if (role == 0) FB_STAMP(2);
       auto issue_s = [&](int it) -> bool {  // roles 0 and 1
         const int st = it % STAGES;
         if (!mbar_wait(&q_full[st], (it / STAGES) & 1, abort_flag, p.status, ERR_WAIT_FULL)) return false;
@@ -233,6 +263,31 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     auto dq_readout = [&](int j) {
       const int hj = hk * G + j / nq_it;
       const int qrow = (i0 + j % nq_it) * 128 + r;
+      if (DQ_TMA) {
+        // 16 columns of this thread's query row -> four 16-byte chunks of the swizzled box; thread 64 made sure before the
+        // barrier at the top of the iteration that the previous block's copy has read the staging tile
+        uint32_t rr[16];
+        tmem_ld_32x16(t_lane + DQ_COL + cq * 16, rr);
+        tmem_ld_wait();
+        uint8_t* row = sDq + (cq >> 1) * 16384 + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = ((cq & 1) * 4 + g) ^ (r & 7);
+          *reinterpret_cast<uint4*>(row + chunk * 16) = make_uint4(rr[g * 4], rr[g * 4 + 1], rr[g * 4 + 2], rr[g * 4 + 3]);
+        }
+        tc_fence_before();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dq_empty);
+        asm volatile("bar.sync 2, 512;" ::: "memory");  // the whole block is staged
+        if (threadIdx.x == 64) {
+          const int q0j = (i0 + j % nq_it) * 128;
+          tma_reduce_add_3d(&tmap_dq, sDq, hj * D, q0j, b);
+          tma_reduce_add_3d(&tmap_dq, sDq + 16384, hj * D + 32, q0j, b);
+          bulk_commit();
+        }
+        return;
+      }
       {
         const int col0 = cq * DC;
         uint32_t rr[DC];
@@ -267,6 +322,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
       if (!mbar_wait_warp(s_full, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
+      if (DQ_TMA && threadIdx.x == 64) bulk_wait_read();  // the dQ staging tile may be written again after the barrier below
+      if (threadIdx.x == 64) FB_STAMP(8 + 3 * it);
       asm volatile("bar.sync 1, 512;" ::: "memory");  // the statistics of this block are in place (softmax warps only)
       const bool windowed = p.causal && p.window > 0;
       const bool need_mask = (p.causal && q0 < k0 + 127) || (q0 + 128 > p.S) || (k0 + 128 > p.S) || (windowed && q0 + 127 - k0 >= p.window);
@@ -308,9 +365,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
               const int qi = q0 + col0 + i + u;
-              const int qc = min(qi, p.S - 1);
-              const float lse = __ldg(lse_row + qc);
-              const float dl = __ldg(dl_row + qc);
+              const float lse = stat[col0 + i + u];          // staged above for row min(qi, S - 1)
+              const float dl = stat[128 + col0 + i + u];
               float e = exp2f(__uint_as_float(s_r[i + u]) * c - lse);
               if ((p.causal && key > qi) || qi >= p.S || key >= p.S || (windowed && qi - key >= p.window)) e = 0.f;
               pe[u] = e;
@@ -337,8 +393,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
+      if (threadIdx.x == 64) FB_STAMP(9 + 3 * it);
       if (OVERLAP) {
         if (it > 0) dq_readout(it - 1);
+        if (threadIdx.x == 64) FB_STAMP(10 + 3 * it);
       } else {
         if (!mbar_wait_warp(mma2_done, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
@@ -348,6 +406,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     if (OVERLAP && ok && n_it > 0) {
       if (mbar_wait_warp(mma2_done, (n_it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) {
         tc_fence_after();
+        if (DQ_TMA) {  // the copy of the block before this one must have read the staging tile
+          if (threadIdx.x == 64) bulk_wait_read();
+          asm volatile("bar.sync 1, 512;" ::: "memory");
+        }
         dq_readout(n_it - 1);
       } else {
         ok = false;
@@ -383,10 +445,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
       }
       tc_fence_before();
+      if (threadIdx.x == 64) FB_STAMP(4);
     }
+    if (DQ_TMA && threadIdx.x == 64) bulk_wait_all();  // the reduce copies must have landed before the grid ends
   }
 
   __syncthreads();
+  if (threadIdx.x == 0) FB_STAMP(3);
   if (*abort_flag) {
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
@@ -479,12 +544,13 @@ extern "C" int inv_flash_attn_bwd(const void* q, const void* k, const void* v, c
     attn_delta_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, B, S, H,
                                                                         head_dim, ld_o, ld_do);
   }
-  CUtensorMap tq, tk, tv, tdo;
+  CUtensorMap tq, tk, tv, tdo, tdq;
   int rc;
   if ((rc = make_tmap_tokens_bf16(&tq, q, H * head_dim, S, B, ld_q, 128))) return rc;
   if ((rc = make_tmap_tokens_bf16(&tk, k, Hkv * head_dim, S, B, ld_k, 128))) return rc;
   if ((rc = make_tmap_tokens_bf16(&tv, v, Hkv * head_dim, S, B, ld_v, 128))) return rc;
   if ((rc = make_tmap_tokens_bf16(&tdo, d_o, H * head_dim, S, B, ld_do, 128))) return rc;
+  if ((rc = make_tmap_tokens_f32(&tdq, dq_acc, H * head_dim, S, B))) return rc;
   FlashBwdParams p;
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
   p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv; p.ld_dk = ld_dk; p.ld_dv = ld_dv;
@@ -496,8 +562,8 @@ extern "C" int inv_flash_attn_bwd(const void* q, const void* k, const void* v, c
     cudaFuncSetAttribute(flash_bwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<2>::TOTAL);
     configured = true;
   }
-  if (head_dim == 64) flash_bwd_kernel<1><<<grid, FB_THREADS, BwdSmem<1>::TOTAL, st>>>(tq, tk, tv, tdo, p);
-  else flash_bwd_kernel<2><<<grid, FB_THREADS, BwdSmem<2>::TOTAL, st>>>(tq, tk, tv, tdo, p);
+  if (head_dim == 64) flash_bwd_kernel<1><<<grid, FB_THREADS, BwdSmem<1>::TOTAL, st>>>(tq, tk, tv, tdo, tdq, p);
+  else flash_bwd_kernel<2><<<grid, FB_THREADS, BwdSmem<2>::TOTAL, st>>>(tq, tk, tv, tdo, tdq, p);
   {
     const long n = T * H * head_dim / 8;
     long g = (n + 255) / 256;
@@ -507,3 +573,9 @@ extern "C" int inv_flash_attn_bwd(const void* q, const void* k, const void* v, c
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }
+
+#ifdef FB_TRACE
+extern "C" int inv_fb_trace_read(long long* host64) {
+  return (int)cudaMemcpyFromSymbol(host64, inv::fb_trace_buf, sizeof(long long) * 64);
+}
+#endif

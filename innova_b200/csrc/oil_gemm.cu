@@ -198,6 +198,19 @@ struct OgCursor {
   __device__ __forceinline__ bool seg_full() const { return bb0 == 0 && bb1 == nb; }
 };
 
+// Build with -DOG_TRACE to record, for CTA 0 of the most recent launch, the SM clock at the phases of the kernel
+// (inv_og_trace_read copies the stamps out): 0 entry, 1 set-up done, 2 first index TMA issued, 3 previous grid complete,
+// 4 lookup table built, 5 first index tile landed, 6 first MMA inputs ready, 7 last MMA committed, 8 first epilogue
+// starts, 9 last epilogue done, 10 exit.
+#ifdef OG_TRACE
+__device__ long long og_trace_buf[16];
+#define OG_STAMP(i) do { if (blockIdx.x == 0) og_trace_buf[i] = clock64(); } while (0)
+#define OG_STAMP_ONCE(i, flag) do { if (blockIdx.x == 0 && !(flag)) { og_trace_buf[i] = clock64(); flag = true; } } while (0)
+#else
+#define OG_STAMP(i) do {} while (0)
+#define OG_STAMP_ONCE(i, flag) do {} while (0)
+#endif
+
 template <int BITS>
 __global__ void __launch_bounds__(og::THREADS, 1)
 oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_constant__ CUtensorMap tmap_x, const OilGemmParams p) {
@@ -236,7 +249,10 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
   // another round of the grid (a CTA walks down K inside a tile and adds the finished segment into the fp32 output
   // with reductions). Every role below walks the same OgCursor.
 
+  if (threadIdx.x == 0) OG_STAMP(0);
   if (threadIdx.x < (BITS == 8 ? 256 : (1 << BITS))) cb[threadIdx.x] = p.codebook[threadIdx.x];
+  OgCursor idx_cur(n_tiles, nb, p.dp_rounds);  // thread 0's walk over the index tiles (it issues their loads)
+  int idx_issued = 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < IDX_STAGES; ++s) {
       mbar_init(&idx_full[s], 1);
@@ -252,8 +268,14 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
     }
     *abort_flag = 0;
     fence_barrier_init();
-    tma_prefetch_desc(&tmap_idx);
     tma_prefetch_desc(&tmap_x);
+    // the first round of the index ring goes out now: the weights are static, every slot is free, and the loads'
+    // latency then overlaps the tensor-memory allocation, the lookup-table build and the CTA-wide sync below
+    for (; idx_cur.valid && idx_issued < IDX_STAGES; idx_cur.advance(), ++idx_issued) {
+      mbar_expect_tx(&idx_full[idx_issued], IDX_TILE);
+      tma_load_2d(sIdx + idx_issued * IDX_TILE, &tmap_idx, &idx_full[idx_issued], idx_cur.bb * ROWB, idx_cur.tile * BN);
+    }
+    OG_STAMP(2);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -264,13 +286,16 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (threadIdx.x == 0) OG_STAMP(1);
+  [[maybe_unused]] bool og_once = false, og_once2 = false;
 
   if (warp == 0) {
     // lane 0 streams index tiles, lane 1 streams activation tiles; each runs ahead on its own ring
     if (lane == 0) {
-      int si = 0;
-      uint32_t ph = 1;
-      for (OgCursor c(n_tiles, nb, p.dp_rounds); c.valid; c.advance()) {
+      // continues behind the loads issued before the sync
+      int si = idx_issued == IDX_STAGES ? 0 : idx_issued;
+      uint32_t ph = idx_issued == IDX_STAGES ? 0 : 1;
+      for (OgCursor& c = idx_cur; c.valid; c.advance()) {
         if (!mbar_wait(&idx_empty[si], ph, abort_flag, p.status, ERR_WAIT_EMPTY)) break;
         mbar_expect_tx(&idx_full[si], IDX_TILE);  // bytes past the end of K are filled with zeros and counted
         tma_load_2d(sIdx + si * IDX_TILE, &tmap_idx, &idx_full[si], c.bb * ROWB, c.tile * BN);
@@ -282,6 +307,7 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
       // into tensor memory; the activation loads, and with them the MMAs and the epilogue, wait here for the
       // previous grid to complete.
       asm volatile("griddepcontrol.wait;" ::: "memory");
+      OG_STAMP(3);
       int lb = 0;
       for (OgCursor c(n_tiles, nb, p.dp_rounds); c.valid; c.advance(), ++lb) {
         const int kb0 = c.bb * KBB, nkb = min(KBB, kb_total - kb0);
@@ -320,6 +346,7 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
           if (!mbar_wait(&a_full[g], ph, abort_flag, p.status, ERR_WAIT_FULL)) break;
           if (!mbar_wait(&x_full[g], ph, abort_flag, p.status, ERR_WAIT_FULL)) break;
           tc_fence_after();
+          if (g == 0) OG_STAMP_ONCE(6, og_once);
           const uint32_t acc = tmem_base + (buf * 2 + g) * accw;
           umma_bf16_tmem_a(acc, a_col, xdesc0, idesc, (lb - seg_lb0) < 2 ? 0u : 1u);  // this issuer's first batch of the segment
 #pragma unroll
@@ -339,28 +366,16 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
           ++seg;
         }
       }
+      if (g == 0) OG_STAMP(7);
     }
   } else if (warp >= 2 && warp < 10) {
     // lookup table: OIL4 -> bf16 pair (codebook[low nibble], codebook[high nibble]) per byte; OIL8 -> one bf16
     // entry e for lane l lives at lut[e * 32 + l]: every lane reads its own bank, whatever the indices are
-    if (BITS != 2) {
-      for (int i = threadIdx.x - 64; i < 256 * 32; i += 256) {
-        const int e = i >> 5;
-        lut[i] = (BITS == 4) ? pack_bf16x2(cb[e & 15], cb[e >> 4]) : pack_bf16x2(cb[e], 0.f);
-      }
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-    }
-    // ---------------- dequantise + epilogue ----------------
-    // Two groups of four warps take alternate batches, so that one group's waits and barrier traffic overlap the
-    // other group's table lookups. A thread owns weight row r of the tile: it reads the row's index bytes of the
-    // whole batch, expands one k-block at a time into 32 registers of packed bf16 and stores them into its lane
-    // of the A stage in tensor memory (the MMA reads A from there: no shared-memory round trip).
     const int q = warp & 3;
     const int grp = (warp - 2) >> 2;
     const int r = q * 32 + lane;        // weight row inside the tile = TMEM lane
     const int nsb = p.K / 32;           // scale blocks per weight row
     const unsigned short* scales = reinterpret_cast<const unsigned short*>(p.scales);
-    const uint32_t t_lane = tmem_base + (uint32_t(q * 32) << 16);
     // block scales of a batch are fetched one own batch (two batches) ahead of their use
     unsigned short sc_next[2 * KBB];
     auto fetch_scales = [&](int t, int bbx) {
@@ -371,9 +386,24 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
     };
     OgCursor pc(n_tiles, nb, p.dp_rounds);  // runs one own batch ahead of the main cursor
     if (grp == 1 && pc.valid) pc.advance();
-    if (pc.valid) fetch_scales(pc.tile, pc.bb);
+    if (pc.valid) fetch_scales(pc.tile, pc.bb);  // in flight while the table is built
+    if (BITS != 2) {
+      // eight lanes write the 32 bank copies of one entry as 16-byte stores: a warp covers four entries (512 contiguous bytes)
+      for (int e = (warp - 2) * 4 + (lane >> 3); e < 256; e += 32) {
+        const uint32_t v = (BITS == 4) ? pack_bf16x2(cb[e & 15], cb[e >> 4]) : pack_bf16x2(cb[e], 0.f);
+        *reinterpret_cast<uint4*>(lut + e * 32 + (lane & 7) * 4) = make_uint4(v, v, v, v);
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+    }
+    if (threadIdx.x == 64) OG_STAMP(4);
+    // ---------------- dequantise + epilogue ----------------
+    // Two groups of four warps take alternate batches, so that one group's waits and barrier traffic overlap the
+    // other group's table lookups. A thread owns weight row r of the tile: it reads the row's index bytes of the
+    // whole batch, expands one k-block at a time into 32 registers of packed bf16 and stores them into its lane
+    // of the A stage in tensor memory (the MMA reads A from there: no shared-memory round trip).
+    const uint32_t t_lane = tmem_base + (uint32_t(q * 32) << 16);
     float* stg = stage + grp * (STG_TOK * STG_PITCH);
-    const int gt = threadIdx.x - 64 - grp * 128;  // thread index inside the group
+    [[maybe_unused]] const int gt = threadIdx.x - 64 - grp * 128;  // thread index inside the group
     const bool vec_ok = ((p.ldo & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
     const int nbuf = p.Mpad <= 64 ? 2 : 1, accw = p.Mpad <= 64 ? 64 : 128;
     int seg = 0, lb = 0;
@@ -391,6 +421,7 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
         if (pc.valid) fetch_scales(pc.tile, pc.bb);
         const int si = lb % IDX_STAGES;
         if (!mbar_wait_warp(&idx_full[si], (lb / IDX_STAGES) & 1, abort_flag, p.status, ERR_WAIT_FULL)) { ok = false; break; }
+        if (threadIdx.x == 64) OG_STAMP_ONCE(5, og_once);
         uint4 raw[ROW_CHUNKS];
         {
           const uint8_t* src = sIdx + si * IDX_TILE + r * ROWB;
@@ -426,6 +457,7 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
           if (!mbar_wait_warp(&acc_full[buf * 2 + grp], (full_par >> buf) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
           full_par ^= 1u << buf;
           tc_fence_after();
+          if (gt == 0) OG_STAMP_ONCE(8, og_once2);
           const uint32_t t_acc = t_lane + (buf * 2 + grp) * accw, t_other = t_lane + (buf * 2 + (grp ^ 1)) * accw;
           const bool both = c.bb1 - c.bb0 >= 2;  // the other issuer contributed to this segment too
           for (int mh = 0; mh < p.Mpad; mh += STG_TOK) {
@@ -435,10 +467,10 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 16; ++j) stg[j * STG_PITCH + r] = __uint_as_float(v[j]) + (both ? __uint_as_float(v2[j]) : 0.f);
-            asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+            __syncwarp();  // a warp reads back only the 32 weight rows it wrote: no barrier across the group
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-              const int e = k * 128 + gt, m = e >> 5, n4 = (e & 31) * 4;
+              const int e = k * 32 + lane, m = e >> 3, n4 = q * 32 + (e & 7) * 4;
               const int gm = mh + m, n = c.tile * BN + n4;
               if (gm < p.M && n < p.N) {
                 const float4 val = *reinterpret_cast<const float4*>(stg + m * STG_PITCH + n4);
@@ -473,11 +505,12 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
                 }
               }
             }
-            asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory");
+            __syncwarp();
           }
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          if (gt == 0) OG_STAMP(9);
         }
       }
       if (seg_end) ++seg;
@@ -485,6 +518,7 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
   }
 
   __syncthreads();
+  if (threadIdx.x == 0) OG_STAMP(10);
   if (*abort_flag) {
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
@@ -874,3 +908,9 @@ extern "C" int inv_oil_gemm_finish_norm(float* acc, const void* bias, const void
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }
+
+#ifdef OG_TRACE
+extern "C" int inv_og_trace_read(long long* host16) {
+  return (int)cudaMemcpyFromSymbol(host16, og_trace_buf, sizeof(long long) * 16);
+}
+#endif
