@@ -18,6 +18,8 @@
 #include "sm100_common.cuh"
 #include "inv_api.h"
 
+#include <type_traits>
+
 namespace inv {
 
 int make_tmap_tokens_bf16(CUtensorMap* out, const void* ptr, int cols, int S, int B, int ld, int box_rows);
@@ -69,7 +71,8 @@ struct BwdSmem {
 
 // Build with -DFB_TRACE to record the SM clock at the phases of CTA (0, 0, 0) of the most recent launch
 // (inv_fb_trace_read): 0 entry, 1 set-up done, 2 K/V landed (issuer), 3 exit, 4 dK/dV written, 8 + 3 it: S^T ready for
-// query block it, 9 + 3 it: P^T / dS^T published, 10 + 3 it: dQ of block it - 1 read out.
+// query block it, 9 + 3 it: P^T / dS^T published, 10 + 3 it: dQ of block it - 1 read out, 32 + 3 it: S^T / dP^T in registers,
+// 33 + 3 it: exponentials done, 34 + 3 it: the previous block's MMAs have released the P^T / dS^T tiles.
 #ifdef FB_TRACE
 __device__ long long fb_trace_buf[64];
 #define FB_STAMP(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (i) < 64) fb_trace_buf[i] = clock64(); } while (0)
@@ -264,10 +267,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       const int hj = hk * G + j / nq_it;
       const int qrow = (i0 + j % nq_it) * 128 + r;
       if (DQ_TMA) {
-        // 16 columns of this thread's query row -> four 16-byte chunks of the swizzled box; thread 64 made sure before the
-        // barrier at the top of the iteration that the previous block's copy has read the staging tile
+        // 16 columns of this thread's query row -> four 16-byte chunks of the swizzled box
         uint32_t rr[16];
         tmem_ld_32x16(t_lane + DQ_COL + cq * 16, rr);
+        if (threadIdx.x == 64) bulk_wait_read();        // the previous block's copies have read the staging tile
+        asm volatile("bar.sync 2, 512;" ::: "memory");
         tmem_ld_wait();
         uint8_t* row = sDq + (cq >> 1) * 16384 + r * 128;
 #pragma unroll
@@ -307,83 +311,92 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_empty);
     };
-    for (int it = 0; it < n_it; ++it) {
+    // The row statistics (lse, delta) of a query block go through shared memory: one global load per thread (the first
+    // 256 softmax threads) and block, read back in the inner loop as broadcast 16-byte loads. The load for block it + 1 is
+    // issued while block it is being computed and its value is parked in a register, so that no warp waits on it.
+    const int st_tid = threadIdx.x - 64;  // 0..511 over the softmax warps
+    auto stat_load = [&](int it) -> float {
       const int h = hk * G + it / nq_it;
+      const int qi = min((i0 + it % nq_it) * 128 + (st_tid & 127), p.S - 1);
+      const float* row = (st_tid < 128 ? p.lse : p.delta) + ((size_t)b * p.H + h) * p.S;
+      return __ldg(row + qi);
+    };
+    if (n_it > 0 && st_tid < 256) sStat[st_tid] = stat_load(0);
+    for (int it = 0; it < n_it; ++it) {
       const int q0 = (i0 + it % nq_it) * 128;
-      const float* lse_row = p.lse + ((size_t)b * p.H + h) * p.S;
-      const float* dl_row = p.delta + ((size_t)b * p.H + h) * p.S;
-      // the block's row statistics go to shared memory first (one global load per thread, issued before the wait
-      // for the MMAs so that its latency is hidden): the inner loop then reads them as broadcast 16-byte loads
       float* stat = sStat + (it & 1) * 256;
-      {
-        const int st = threadIdx.x - 64;  // 0..511 over the softmax warps: the first 256 fetch
-        const int qi = min(q0 + (st & 127), p.S - 1);
-        if (st < 256) stat[st] = (st < 128) ? __ldg(lse_row + qi) : __ldg(dl_row + qi);
-      }
       if (!mbar_wait_warp(s_full, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
-      if (DQ_TMA && threadIdx.x == 64) bulk_wait_read();  // the dQ staging tile may be written again after the barrier below
       if (threadIdx.x == 64) FB_STAMP(8 + 3 * it);
       asm volatile("bar.sync 1, 512;" ::: "memory");  // the statistics of this block are in place (softmax warps only)
       const bool windowed = p.causal && p.window > 0;
       const bool need_mask = (p.causal && q0 < k0 + 127) || (q0 + 128 > p.S) || (k0 + 128 > p.S) || (windowed && q0 + 127 - k0 >= p.window);
-      // both 32-column chunks of S^T and dP^T come in with four back-to-back TMEM loads and one wait; the columns
-      // are handed back to the tensor core before the arithmetic starts, so the next block's first MMAs overlap it
-      uint32_t s_all[32], dp_all[32];
-      tmem_ld_32x32(t_lane + ST_COL + cq * 32, s_all);
-      tmem_ld_32x32(t_lane + DPT_COL + cq * 32, dp_all);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty);  // one arrival per warp: arrivals on one mbarrier are serialised
+      // The thread's 32 columns of S^T and dP^T come in as two halves of 16 (the register file holds 96 registers per
+      // thread at this block size: both halves at once spill). The TMEM columns go back to the tensor core after the
+      // second load. A column i of the thread is live iff lim_lo <= i < lim_hi (causal diagonal, sequence end, window).
       uint32_t pk[16], dk[16];  // P^T and dS^T of this thread's 32 columns as packed bf16 pairs, kept in registers until the
                                 // shared-memory tiles are free
-      {
-        const int col0 = cq * 32;
-        const uint32_t* s_r = s_all;
-        const uint32_t* dp_r = dp_all;
-        if (!need_mask) {
-          // interior block: no predicates, statistics fetched as 16-byte broadcast loads; one MUFU op and half a
-          // conversion per element
-          const float4* l4 = reinterpret_cast<const float4*>(stat + col0);
-          const float4* d4 = reinterpret_cast<const float4*>(stat + 128 + col0);
+      float stat_next = 0.f;
+      const int col0 = cq * 32;
+      int lim_lo = 0, lim_hi = 32;
+      if (need_mask) {
+        if (p.causal) lim_lo = key - q0 - col0;
+        lim_hi = min(32, p.S - q0 - col0);
+        if (windowed) lim_hi = min(lim_hi, key + p.window - q0 - col0);
+        if (key >= p.S) lim_hi = 0;
+      }
+      auto softmax_block = [&](auto masked_tag) {
+      constexpr bool MASKED = decltype(masked_tag)::value;
 #pragma unroll
-          for (int i4 = 0; i4 < 8; ++i4) {
-            const float4 l = l4[i4], dl = d4[i4];
-            const int i = i4 * 4;
-            const float e0 = exp2f(fmaf(__uint_as_float(s_r[i]), c, -l.x)), e1 = exp2f(fmaf(__uint_as_float(s_r[i + 1]), c, -l.y));
-            const float e2 = exp2f(fmaf(__uint_as_float(s_r[i + 2]), c, -l.z)), e3 = exp2f(fmaf(__uint_as_float(s_r[i + 3]), c, -l.w));
-            pk[i4 * 2] = cvt_bf16x2(e0, e1);
-            pk[i4 * 2 + 1] = cvt_bf16x2(e2, e3);
-            dk[i4 * 2] = cvt_bf16x2(e0 * (__uint_as_float(dp_r[i]) - dl.x), e1 * (__uint_as_float(dp_r[i + 1]) - dl.y));
-            dk[i4 * 2 + 1] = cvt_bf16x2(e2 * (__uint_as_float(dp_r[i + 2]) - dl.z), e3 * (__uint_as_float(dp_r[i + 3]) - dl.w));
+      for (int half = 0; half < 2; ++half) {
+        uint32_t s_r[16], dp_r[16];
+        tmem_ld_32x16(t_lane + ST_COL + col0 + half * 16, s_r);
+        tmem_ld_32x16(t_lane + DPT_COL + col0 + half * 16, dp_r);
+        tmem_ld_wait();
+        if (half == 1) {
+          if (threadIdx.x == 64) FB_STAMP(32 + 3 * it);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_empty);  // one arrival per warp: arrivals on one mbarrier are serialised
+          if (it + 1 < n_it && st_tid < 256) stat_next = stat_load(it + 1);
+        }
+        // statistics as 16-byte broadcast loads; one MUFU op and half a conversion per element
+        const float4* l4 = reinterpret_cast<const float4*>(stat + col0 + half * 16);
+        const float4* d4 = reinterpret_cast<const float4*>(stat + 128 + col0 + half * 16);
+#pragma unroll
+        for (int i4 = 0; i4 < 4; ++i4) {
+          const float4 l = l4[i4], dl = d4[i4];
+          const int i = i4 * 4;
+          float e0 = exp2f(fmaf(__uint_as_float(s_r[i]), c, -l.x)), e1 = exp2f(fmaf(__uint_as_float(s_r[i + 1]), c, -l.y));
+          float e2 = exp2f(fmaf(__uint_as_float(s_r[i + 2]), c, -l.z)), e3 = exp2f(fmaf(__uint_as_float(s_r[i + 3]), c, -l.w));
+          if (MASKED) {
+            const int ci = half * 16 + i;
+            e0 = (ci >= lim_lo && ci < lim_hi) ? e0 : 0.f;
+            e1 = (ci + 1 >= lim_lo && ci + 1 < lim_hi) ? e1 : 0.f;
+            e2 = (ci + 2 >= lim_lo && ci + 2 < lim_hi) ? e2 : 0.f;
+            e3 = (ci + 3 >= lim_lo && ci + 3 < lim_hi) ? e3 : 0.f;
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float pe[2], de[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int qi = q0 + col0 + i + u;
-              const float lse = stat[col0 + i + u];          // staged above for row min(qi, S - 1)
-              const float dl = stat[128 + col0 + i + u];
-              float e = exp2f(__uint_as_float(s_r[i + u]) * c - lse);
-              if ((p.causal && key > qi) || qi >= p.S || key >= p.S || (windowed && qi - key >= p.window)) e = 0.f;
-              pe[u] = e;
-              de[u] = e * (__uint_as_float(dp_r[i + u]) - dl);
-            }
-            pk[i >> 1] = pack_bf16x2_int(pe[0], pe[1]);
-            dk[i >> 1] = pack_bf16x2_int(de[0], de[1]);
-          }
+          const int o = half * 8 + i4 * 2;
+          pk[o] = cvt_bf16x2(e0, e1);
+          pk[o + 1] = cvt_bf16x2(e2, e3);
+          dk[o] = cvt_bf16x2(e0 * (__uint_as_float(dp_r[i]) - dl.x), e1 * (__uint_as_float(dp_r[i + 1]) - dl.y));
+          dk[o + 1] = cvt_bf16x2(e2 * (__uint_as_float(dp_r[i + 2]) - dl.z), e3 * (__uint_as_float(dp_r[i + 3]) - dl.w));
         }
       }
+      };
+      if (need_mask) softmax_block(std::true_type{});   // two copies of the loop: interior blocks carry no selects
+      else softmax_block(std::false_type{});
+      // the other statistics buffer was last read in block it - 1, which every warp left before this block's barrier
+      if (it + 1 < n_it && st_tid < 256) sStat[((it + 1) & 1) * 256 + st_tid] = stat_next;
       // Software pipeline (when dQ has its own TMEM columns): the arithmetic above ran while the MMAs of the previous
       // block were still reading its P^T / dS^T tiles; only now wait for them, publish this block's tiles, and read the
       // previous block's dQ out of TMEM while this block's MMAs run.
+      if (threadIdx.x == 64) FB_STAMP(33 + 3 * it);
       if (OVERLAP && it > 0) {
         if (!mbar_wait_warp(mma2_done, (it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
       }
+      if (threadIdx.x == 64) FB_STAMP(34 + 3 * it);
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         const int chunk = ((cq & 1) * 4 + g) ^ (r & 7);
@@ -406,10 +419,6 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     if (OVERLAP && ok && n_it > 0) {
       if (mbar_wait_warp(mma2_done, (n_it - 1) & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) {
         tc_fence_after();
-        if (DQ_TMA) {  // the copy of the block before this one must have read the staging tile
-          if (threadIdx.x == 64) bulk_wait_read();
-          asm volatile("bar.sync 1, 512;" ::: "memory");
-        }
         dq_readout(n_it - 1);
       } else {
         ok = false;
