@@ -26,6 +26,7 @@ _CUDA_SIGS = {
     "inv_norm_fwd": [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, i32, vp],
     "inv_norm_bwd_grid": [i32],
     "inv_norm_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
+    "inv_norm_bwd_colsum": [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp],
     "inv_embedding_fwd": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
     "inv_embedding_bwd": [vp, vp, vp, vp, i32, i32, i32, i32, vp],
     "inv_colsum": [vp, vp, i32, i32, i32, vp],

@@ -203,18 +203,24 @@ __global__ void __launch_bounds__(256) norm_bwd_kernel(const __nv_bfloat16* __re
 }
 
 
-// Rows of at most 1024 elements: the row (x and dy) and this thread's share of the gamma/beta
-// gradient stay in registers; no shared-memory atomics. NCH = ceil(D / 256) chunks of 8 per lane.
-template <bool RMS, int NCH>
-__global__ void __launch_bounds__(256) norm_bwd_small_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
-                                                             const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
-                                                             const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
-                                                             __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int T, int D) {
+// ----------------------------------------------------------------------------------------------
+// Backward for D <= 1024, the bandwidth-bound form. A warp owns a row; the x and dy of the next TWO rows of the warp are
+// in flight as packed registers while the current row is reduced and written (one row ahead left the memory system
+// under-subscribed: 8 warps per SM with 4.6 KB each). The row is unpacked twice (sums, then dx) instead of being held in
+// fp32. CS adds a third column sum next to dgamma / dbeta: the column sums of the dx that is written, which is the bias
+// gradient of the linear layer that feeds the residual stream at this point.
+// ----------------------------------------------------------------------------------------------
+template <bool RMS, int NCH, bool CS>
+__global__ void __launch_bounds__(256, 1) norm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                                                               const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                                                               const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres,
+                                                               __nv_bfloat16* __restrict__ dx, float* __restrict__ partial,
+                                                               float* __restrict__ partial_cs, int T, int D) {
   __shared__ float red[8][256];  // one 256-column slab at a time
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gw = blockIdx.x * 8 + warp;
   const int nw = gridDim.x * 8;
-  float g[NCH][8], dg[NCH][8], db[NCH][8];
+  float g[NCH][8], dg[NCH][8], db[NCH][8], dc[CS ? NCH : 1][8];
 #pragma unroll
   for (int k = 0; k < NCH; ++k) {
     const int c = k * 256 + lane * 8;
@@ -223,56 +229,53 @@ __global__ void __launch_bounds__(256) norm_bwd_small_kernel(const __nv_bfloat16
     for (int j = 0; j < 8; ++j) {
       dg[k][j] = 0.f;
       db[k][j] = 0.f;
+      if (CS) dc[k][j] = 0.f;
       if (c >= D) g[k][j] = 0.f;
     }
   }
-  // The next row's x and dy are in flight (packed, 2 * NCH registers of 16 bytes) while this row is reduced and
-  // written: one row per warp at a time would expose a full memory round trip per row.
-  uint4 nx[NCH], nd[NCH], nr[NCH];   // nr: the gradient arriving on the residual stream, when there is one
-  float nmean = 0.f, nrstd = 0.f;
-  auto prefetch = [&](int row) {
+  struct Row {
+    uint4 x[NCH], d[NCH];
+    float mean, rstd;
+  };
+  auto fetch = [&](int row, Row& R) {
+    if (row >= T) return;
     const __nv_bfloat16* xr = x + (size_t)row * D;
     const __nv_bfloat16* dyr = dy + (size_t)row * D;
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
       const int c = k * 256 + lane * 8;
       if (c < D) {
-        nx[k] = *reinterpret_cast<const uint4*>(xr + c);
-        nd[k] = *reinterpret_cast<const uint4*>(dyr + c);
-        if (dres) nr[k] = *reinterpret_cast<const uint4*>(dres + (size_t)row * D + c);
+        R.x[k] = *reinterpret_cast<const uint4*>(xr + c);
+        R.d[k] = *reinterpret_cast<const uint4*>(dyr + c);
       }
     }
-    nmean = RMS ? 0.f : mean_in[row];
-    nrstd = rstd_in[row];
+    R.mean = RMS ? 0.f : mean_in[row];
+    R.rstd = rstd_in[row];
   };
-  if (gw < T) prefetch(gw);
-  for (int row = gw; row < T; row += nw) {
-    const float mean = nmean;
-    const float rstd = nrstd;
-    float xh[NCH][8], d[NCH][8];
+  auto process = [&](int row, const Row& R) {
     uint4 rr[NCH];
+    if (dres) {
+#pragma unroll
+      for (int k = 0; k < NCH; ++k) {
+        const int c = k * 256 + lane * 8;
+        if (c < D) rr[k] = *reinterpret_cast<const uint4*>(dres + (size_t)row * D + c);
+      }
+    }
+    const float mean = R.mean, rstd = R.rstd;
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
       const int c = k * 256 + lane * 8;
       if (c < D) {
-        unpack8(nx[k], xh[k]);
-        unpack8(nd[k], d[k]);
-        if (dres) rr[k] = nr[k];
-      } else {
+        float xv[8], dv[8];
+        unpack8(R.x[k], xv);
+        unpack8(R.d[k], dv);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) xh[k][j] = mean, d[k][j] = 0.f;
-      }
-    }
-    if (row + nw < T) prefetch(row + nw);
-#pragma unroll
-    for (int k = 0; k < NCH; ++k) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        xh[k][j] = (xh[k][j] - mean) * rstd;
-        const float gg = d[k][j] * g[k][j];
-        s1 += gg;
-        s2 += gg * xh[k][j];
+        for (int j = 0; j < 8; ++j) {
+          const float gg = dv[j] * g[k][j];
+          s1 += gg;
+          s2 += gg * ((xv[j] - mean) * rstd);
+        }
       }
     }
     s1 = RMS ? 0.f : warp_sum(s1) / D;
@@ -281,41 +284,77 @@ __global__ void __launch_bounds__(256) norm_bwd_small_kernel(const __nv_bfloat16
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
       const int c = k * 256 + lane * 8;
-      float o[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        o[j] = rstd * (d[k][j] * g[k][j] - s1 - xh[k][j] * s2);
-        dg[k][j] += d[k][j] * xh[k][j];
-        db[k][j] += d[k][j];
-      }
       if (c < D) {
+        float xv[8], dv[8], o[8];
+        unpack8(R.x[k], xv);
+        unpack8(R.d[k], dv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xh = (xv[j] - mean) * rstd;
+          o[j] = rstd * (dv[j] * g[k][j] - s1 - xh * s2);
+          dg[k][j] += dv[j] * xh;
+          db[k][j] += dv[j];
+        }
         if (dres) {
           float r[8];
           unpack8(rr[k], r);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] += r[j];
         }
+        if (CS) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) dc[k][j] += o[j];
+        }
         store8(dxr + c, o);
       }
     }
+  };
+  if constexpr (NCH <= 3) {  // two rows ahead
+    Row r0, r1, r2;
+    fetch(gw, r0);
+    fetch(gw + nw, r1);
+    for (int row = gw; row < T; row += 3 * nw) {
+      fetch(row + 2 * nw, r2);
+      process(row, r0);
+      if (row + nw < T) {
+        fetch(row + 3 * nw, r0);
+        process(row + nw, r1);
+      }
+      if (row + 2 * nw < T) {
+        fetch(row + 4 * nw, r1);
+        process(row + 2 * nw, r2);
+      }
+    }
+  } else {  // 769 .. 1024 columns: the register file holds one row ahead
+    Row r0, r1;
+    fetch(gw, r0);
+    for (int row = gw; row < T; row += 2 * nw) {
+      fetch(row + nw, r1);
+      process(row, r0);
+      if (row + nw < T) {
+        fetch(row + 2 * nw, r0);
+        process(row + nw, r1);
+      }
+    }
   }
-  // fold the 8 warps of the CTA, one 256-column slab at a time, and write this CTA's partial row
+  // fold the 8 warps of the CTA, one 256-column slab at a time, and write this CTA's partial rows
   float* out = partial + (size_t)blockIdx.x * 2 * D;
 #pragma unroll
-  for (int which = 0; which < 2; ++which) {
-    if (RMS && which == 1) break;
+  for (int which = 0; which < (CS ? 3 : 2); ++which) {
+    if (RMS && which == 1) continue;
 #pragma unroll
     for (int k = 0; k < NCH; ++k) {
       __syncthreads();
 #pragma unroll
-      for (int j = 0; j < 8; ++j) red[warp][lane * 8 + j] = which == 0 ? dg[k][j] : db[k][j];
+      for (int j = 0; j < 8; ++j) red[warp][lane * 8 + j] = which == 0 ? dg[k][j] : which == 1 ? db[k][j] : dc[CS ? k : 0][j];
       __syncthreads();
       const int c = k * 256 + threadIdx.x;
       if (c < D) {
         float s = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; ++w) s += red[w][threadIdx.x];
-        out[which * D + c] = s;
+        if (which < 2) out[which * D + c] = s;
+        else partial_cs[(size_t)blockIdx.x * D + c] = s;
       }
     }
   }
@@ -324,15 +363,35 @@ __global__ void __launch_bounds__(256) norm_bwd_small_kernel(const __nv_bfloat16
   }
 }
 
-// dgamma[D] += sum_b partial[b][0][:], dbeta[D] += sum_b partial[b][1][:]
-__global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dgamma, float* __restrict__ dbeta,
-                                       int nblocks, int D) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * D) return;
+// dgamma[D] += sum_b partial[b][0][:], dbeta[D] += sum_b partial[b][1][:], colsum[D] = sum_b partial_cs[b][:].
+// grid (ceil(D / 32), 3): a CTA owns 32 columns of one of the three sums; its 8 warps take the partial rows round robin
+// (coalesced 128-byte reads) and meet in shared memory.
+__global__ void __launch_bounds__(256) norm_bwd_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ partial_cs,
+                                                              float* __restrict__ dgamma, float* __restrict__ dbeta,
+                                                              float* __restrict__ colsum, int nblocks, int D) {
+  __shared__ float red[8][32];
+  const int which = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
+  float* dst = which == 0 ? dgamma : which == 1 ? dbeta : colsum;
+  if (dst == nullptr) return;
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += partial[(size_t)b * 2 * D + c];
-  if (c < D) dgamma[c] += s;
-  else if (dbeta) dbeta[c - D] += s;
+  if (c < D) {
+    if (which < 2) {
+      for (int b = warp; b < nblocks; b += 8) s += partial[(size_t)b * 2 * D + which * D + c];
+    } else {
+      for (int b = warp; b < nblocks; b += 8) s += partial_cs[(size_t)b * D + c];
+    }
+  }
+  red[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && c < D) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w][lane];
+    if (which < 2) dst[c] += t;
+    else dst[c] = t;
+  }
 }
 
 }  // namespace inv
@@ -358,18 +417,16 @@ extern "C" int inv_norm_fwd(const void* x, const void* res, const void* gamma, c
   return e == cudaSuccess ? 0 : -(int)e;
 }
 
-// Number of CTAs the backward launches for T rows; scratch must hold grid*2*D floats.
+// Number of CTAs the backward launches for T rows; scratch must hold grid * 3 * D floats (2 * D per CTA for dgamma and
+// dbeta, then D per CTA for the optional column sums of dx).
 extern "C" int inv_norm_bwd_grid(int T) {
   int g = (T + 7) / 8;
-  return g < 296 ? (g < 1 ? 1 : g) : 296;
+  return g < 148 ? (g < 1 ? 1 : g) : 148;
 }
 
-extern "C" int inv_norm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, const void* dres,
-                            void* dx, float* dgamma, float* dbeta, float* scratch, int T, int D, int rms, void* stream) {
-  if (D % 8 || D > 12288) return -ERR_BAD_ARG;
-  if (T <= 0) return 0;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int grid = inv_norm_bwd_grid(T);
+// colsum (nullable, D <= 1024 only): fp32 [D], overwritten with the column sums of dx as written (dres included).
+static int norm_bwd_launch(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, const void* dres, void* dx,
+                           float* dgamma, float* dbeta, float* colsum, float* scratch, int grid, int T, int D, int rms, cudaStream_t st) {
   const size_t smem = (size_t)2 * ((D + 255) & ~255) * sizeof(float);
   static bool configured = false;
   if (!configured) {
@@ -383,22 +440,45 @@ extern "C" int inv_norm_bwd(const void* dy, const void* x, const void* gamma, co
   auto DR = reinterpret_cast<const __nv_bfloat16*>(dres);
   auto DX = reinterpret_cast<__nv_bfloat16*>(dx);
   const int nch = (D + 255) / 256;
-#define INV_NB_SMALL(R, N) norm_bwd_small_kernel<R, N><<<grid, 256, 0, st>>>(DY, X, G, mean, rstd, DR, DX, scratch, T, D)
+  float* scratch_cs = scratch + (size_t)grid * 2 * D;
+  if (colsum != nullptr && nch > 4) return -ERR_BAD_ARG;
+#define INV_NB_ROWS(R, N)                                                                                                             \
+  do {                                                                                                                                \
+    if (colsum) norm_bwd_rows_kernel<R, N, true><<<grid, 256, 0, st>>>(DY, X, G, mean, rstd, DR, DX, scratch, scratch_cs, T, D);      \
+    else norm_bwd_rows_kernel<R, N, false><<<grid, 256, 0, st>>>(DY, X, G, mean, rstd, DR, DX, scratch, scratch_cs, T, D);            \
+  } while (0)
   if (nch <= 4) {  // register path
     if (rms) {
-      if (nch == 1) INV_NB_SMALL(true, 1); else if (nch == 2) INV_NB_SMALL(true, 2); else if (nch == 3) INV_NB_SMALL(true, 3); else INV_NB_SMALL(true, 4);
+      if (nch == 1) INV_NB_ROWS(true, 1); else if (nch == 2) INV_NB_ROWS(true, 2); else if (nch == 3) INV_NB_ROWS(true, 3); else INV_NB_ROWS(true, 4);
     } else {
-      if (nch == 1) INV_NB_SMALL(false, 1); else if (nch == 2) INV_NB_SMALL(false, 2); else if (nch == 3) INV_NB_SMALL(false, 3); else INV_NB_SMALL(false, 4);
+      if (nch == 1) INV_NB_ROWS(false, 1); else if (nch == 2) INV_NB_ROWS(false, 2); else if (nch == 3) INV_NB_ROWS(false, 3); else INV_NB_ROWS(false, 4);
     }
   } else if (rms) {
     norm_bwd_kernel<true><<<grid, 256, smem, st>>>(DY, X, G, mean, rstd, DR, DX, scratch, T, D);
   } else {
     norm_bwd_kernel<false><<<grid, 256, smem, st>>>(DY, X, G, mean, rstd, DR, DX, scratch, T, D);
   }
-#undef INV_NB_SMALL
-  norm_bwd_reduce_kernel<<<(2 * D + 255) / 256, 256, 0, st>>>(scratch, dgamma, rms ? nullptr : dbeta, grid, D);
+#undef INV_NB_ROWS
+  norm_bwd_reduce_kernel<<<dim3((D + 31) / 32, colsum ? 3 : 2), 256, 0, st>>>(scratch, scratch_cs, dgamma, rms ? nullptr : dbeta, colsum, grid, D);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
+}
+
+extern "C" int inv_norm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, const void* dres,
+                            void* dx, float* dgamma, float* dbeta, float* scratch, int T, int D, int rms, void* stream) {
+  if (D % 8 || D > 12288) return -ERR_BAD_ARG;
+  if (T <= 0) return 0;
+  return norm_bwd_launch(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, nullptr, scratch, inv_norm_bwd_grid(T), T, D, rms,
+                         reinterpret_cast<cudaStream_t>(stream));
+}
+
+// The same with the column sums of dx (fp32 [D], overwritten) as a by-product: D <= 1024.
+extern "C" int inv_norm_bwd_colsum(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd, const void* dres,
+                                   void* dx, float* dgamma, float* dbeta, float* colsum, float* scratch, int T, int D, int rms, void* stream) {
+  if (D % 8 || D > 1024 || colsum == nullptr) return -ERR_BAD_ARG;
+  if (T <= 0) return 0;
+  return norm_bwd_launch(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, colsum, scratch, inv_norm_bwd_grid(T), T, D, rms,
+                         reinterpret_cast<cudaStream_t>(stream));
 }
 
 // ----------------------------------------------------------------------------------------------
@@ -456,7 +536,7 @@ extern "C" int inv_norm_bwd_noalloc(const void* dy, const void* x, const void* g
   auto DX = reinterpret_cast<__nv_bfloat16*>(dx);
   if (rms) norm_bwd_kernel<true><<<grid, 256, smem, st>>>(DY, X, G, mean, rstd, DR, DX, partials, T, D);
   else norm_bwd_kernel<false><<<grid, 256, smem, st>>>(DY, X, G, mean, rstd, DR, DX, partials, T, D);
-  norm_bwd_reduce_kernel<<<(2 * D + 255) / 256, 256, 0, st>>>(partials, dgamma, rms ? nullptr : dbeta, grid, D);
+  norm_bwd_reduce_kernel<<<dim3((D + 31) / 32, 2), 256, 0, st>>>(partials, nullptr, dgamma, rms ? nullptr : dbeta, nullptr, grid, D);
   err = cudaGetLastError();
   return err == cudaSuccess ? 0 : -(int)err;
 }

@@ -66,16 +66,25 @@ def _norm_backward(ctx, dy, dres):
             dr2 = dr2.contiguous()
     dx = torch.empty_like(x2)
     grid = rt.lib().inv_norm_bwd_grid(T)
-    scr = rt.scratch("norm_bwd", grid * 2 * D * 4, x2.device)
+    scr = rt.scratch("norm_bwd", grid * 3 * D * 4, x2.device)
     mg_g = getattr(gamma, "main_grad", None)
     mg_b = getattr(beta, "main_grad", None) if beta is not None else None
     dg = mg_g if mg_g is not None else torch.zeros(D, dtype=torch.float32, device=x2.device)
     db = None
     if beta is not None:
         db = mg_b if mg_b is not None else torch.zeros(D, dtype=torch.float32, device=x2.device)
-    rt.check(rt.lib().inv_norm_bwd(dy2.data_ptr(), x2.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), rt.ptr(dr2),
-                                   dx.data_ptr(), dg.data_ptr(), rt.ptr(db), scr.data_ptr(), T, D, int(ctx.rms),
-                                   rt.stream_ptr()), "inv_norm_bwd")
+    if D <= 1024:
+        # the column sums of dx come out of the same kernel: they are the bias gradient of the linear layer whose output
+        # gradient dx is, and that layer's backward picks them up instead of making its own pass over dx
+        cs = torch.empty(D, dtype=torch.float32, device=x2.device)
+        rt.check(rt.lib().inv_norm_bwd_colsum(dy2.data_ptr(), x2.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), rt.ptr(dr2),
+                                              dx.data_ptr(), dg.data_ptr(), rt.ptr(db), cs.data_ptr(), scr.data_ptr(), T, D, int(ctx.rms),
+                                              rt.stream_ptr()), "inv_norm_bwd_colsum")
+        rt.offer_colsum(dx, cs)
+    else:
+        rt.check(rt.lib().inv_norm_bwd(dy2.data_ptr(), x2.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(), rt.ptr(dr2),
+                                       dx.data_ptr(), dg.data_ptr(), rt.ptr(db), scr.data_ptr(), T, D, int(ctx.rms),
+                                       rt.stream_ptr()), "inv_norm_bwd")
     g_out = None if mg_g is not None else dg.to(gamma.dtype)
     b_out = None if (beta is None or mg_b is not None) else db.to(beta.dtype)
     return dx.view(ctx.xshape), g_out, b_out, None, None

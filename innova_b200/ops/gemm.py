@@ -109,9 +109,15 @@ def _accumulate_wgrad(weight, dy2, x2):
     return g.to(weight.dtype)
 
 
-def _accumulate_bgrad(bias, dy2):
+def _accumulate_bgrad(bias, dy2, colsum=None):
+    """``colsum``: fp32 column sums of ``dy2`` when its producer already computed them (``rt.take_colsum``)."""
     mg = getattr(bias, "main_grad", None)
     T, N = dy2.shape
+    if colsum is not None:
+        if mg is not None:
+            mg.add_(colsum)
+            return None
+        return colsum.to(bias.dtype)
     if mg is not None:
         rt.check(rt.lib().inv_colsum(dy2.data_ptr(), mg.data_ptr(), T, N, dy2.stride(0), rt.stream_ptr()), "inv_colsum")
         return None
@@ -156,17 +162,19 @@ class _LinearFn(torch.autograd.Function):
         dy2 = dy.reshape(-1, N)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
+        cs = rt.take_colsum(dy2)             # left by the norm backward that produced dy, if any
         dres = dy if ctx.mode == "add" else None
         if ctx.mode == "gelu":
             # dpre = dy * gelu'(pre), then the usual dgrad / wgrad on dpre
             dpre = torch.empty_like(dy2)
             rt.check(rt.lib().inv_act(pre.data_ptr(), dy2.data_ptr(), dpre.data_ptr(), dy2.shape[0], N, 1, rt.stream_ptr()), "inv_act")
             dy2 = dpre
+            cs = None
         dx = None
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, weight, b_mn=True).view(ctx.xshape)
         dw = _accumulate_wgrad(weight, dy2, x2) if ctx.needs_input_grad[1] else None
-        db = _accumulate_bgrad(bias, dy2) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
+        db = _accumulate_bgrad(bias, dy2, cs) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
         return dx, dw, db, dres, None
 
 
@@ -218,9 +226,10 @@ class _MlpGeluFn(torch.autograd.Function):
         dy2 = dy.reshape(-1, N)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
+        cs = rt.take_colsum(dy2)
         dpre = gemm(dy2, w2, b_mn=True, epilogue=EPI_DGELU, aux_in=pre)
         dw2 = _accumulate_wgrad(w2, dy2, act)
-        db2 = _accumulate_bgrad(b2, dy2) if b2 is not None else None
+        db2 = _accumulate_bgrad(b2, dy2, cs) if b2 is not None else None
         dx = gemm(dpre, w1, b_mn=True).view(ctx.xshape)
         dw1 = _accumulate_wgrad(w1, dpre, x2)
         db1 = _accumulate_bgrad(b1, dpre) if b1 is not None else None

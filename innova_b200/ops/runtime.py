@@ -90,3 +90,26 @@ def check(rc: int, what: str):
 def launch_count() -> int:
     """Number of native kernel-launching calls made so far (each launches at least one kernel)."""
     return _launches
+
+
+# ---------------------------------------------------------------------------------------------- column sums handed downstream
+# The norm backward kernel produces the column sums of the gradient it writes at no extra cost. That gradient is the
+# output gradient of the linear layer that feeds the residual stream at that point, and its column sums are that layer's
+# bias gradient. One slot: the most recent offer, which only the very next linear backward may take (any linear backward
+# clears it), and only for the very same tensor (address, shape and version counter).
+_pending_colsum = None
+
+
+def offer_colsum(t2d: torch.Tensor, colsum: torch.Tensor):
+    global _pending_colsum
+    _pending_colsum = (t2d.data_ptr(), tuple(t2d.shape), t2d._version, colsum)
+
+
+def take_colsum(dy2: torch.Tensor):
+    """-> fp32 [N] column sums of ``dy2`` if the producer of ``dy2`` left them, else None. Clears the slot either way."""
+    global _pending_colsum
+    p, _pending_colsum = _pending_colsum, None
+    if p is not None and p[0] == dy2.data_ptr() and p[1] == tuple(dy2.shape) and p[2] == dy2._version:
+        return p[3]
+    return None
+
