@@ -82,9 +82,62 @@ __global__ void embedding_bwd_kernel(const int64_t* __restrict__ ids, const __nv
   }
 }
 
-// out[n] += sum_t x[t,n]   (bias gradient). grid = (ceil(N/64), row_chunks), block = 256.
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = __bfloat1622float2(h[j]);
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
+
+// out[n] += sum_t x[t,n]   (bias gradient). grid = (ceil(N/256), row_chunks), block = 256: a lane owns 8 columns (one 16-byte
+// load per row), a warp 256 columns, the 8 warps of a CTA take rows round robin with four rows in flight each; the CTA's
+// 256 partial sums meet in shared memory and leave as one atomic per column.
 __global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int T, int N, int ld,
                                                       int rows_per_block) {
+  __shared__ float red[8][256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + lane * 8;
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(T, r0 + rows_per_block);
+  float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (col < N) {  // N % 8 == 0: a lane's 8 columns are inside or outside together
+    const __nv_bfloat16* base = x + col;
+    int r = r0 + warp;
+    for (; r + 24 < r1; r += 32) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const uint4*>(base + (size_t)(r + 8 * u) * ld);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float f[8];
+        unpack8(v[u], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] += f[j];
+      }
+    }
+    for (; r < r1; r += 8) {
+      float f[8];
+      unpack8(*reinterpret_cast<const uint4*>(base + (size_t)r * ld), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] += f[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[warp][lane * 8 + j] = a[j];
+  __syncthreads();
+  float s = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) s += red[w][threadIdx.x];
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c < N) atomicAdd(out + c, s);
+}
+
+// The same for rows that are not 16-byte friendly (N or ld not a multiple of 8): two columns per lane.
+__global__ void __launch_bounds__(256) colsum2_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int T, int N, int ld,
+                                                       int rows_per_block) {
   __shared__ float red[8][64];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int col = blockIdx.x * 64 + lane * 2;
@@ -237,11 +290,20 @@ extern "C" int inv_embedding_bwd(const int64_t* ids, const void* dy, float* dwte
 extern "C" int inv_colsum(const void* x, float* out, int T, int N, int ld, void* stream) {
   if (N % 2 || ld % 2) return -ERR_BAD_ARG;
   if (T <= 0) return 0;
+  if (N % 8 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    const int gx = (N + 255) / 256;
+    int chunks = (148 * 4 + gx - 1) / gx;          // four CTAs per SM over the whole grid
+    const int max_chunks = (T + 63) / 64;          // at least 64 rows (8 per warp) per CTA
+    if (chunks > max_chunks) chunks = max_chunks;
+    const int rows_per_block = (T + chunks - 1) / chunks;
+    colsum_kernel<<<dim3(gx, chunks), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, out, T, N, ld, rows_per_block);
+    CHECK_LAUNCH();
+  }
   int chunks = (T + 2047) / 2048;
   if (chunks > 64) chunks = 64;
   const int rows_per_block = (T + chunks - 1) / chunks;
   dim3 grid((N + 63) / 64, chunks);
-  colsum_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, out, T, N, ld, rows_per_block);
+  colsum2_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, out, T, N, ld, rows_per_block);
   CHECK_LAUNCH();
 }
 extern "C" int inv_act(const void* x, const void* dy, void* out, long rows, int F, int mode, void* stream) {

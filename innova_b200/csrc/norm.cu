@@ -127,6 +127,109 @@ __global__ void __launch_bounds__(256) norm_fwd_kernel(const __nv_bfloat16* __re
   }
 }
 
+// Forward for D <= 1024: the row is read once into packed registers (the next row of the warp is in flight meanwhile),
+// mean and variance are two passes over registers, not over memory. Persistent grid: a warp walks rows gw, gw + nw, ...
+template <bool RMS, int NCH>
+__global__ void __launch_bounds__(256) norm_fwd_rows_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                                                            const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
+                                                            __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ xsum,
+                                                            float* __restrict__ mean_out, float* __restrict__ rstd_out, int T, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int gw = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int nw = gridDim.x * 8;
+  uint4 gp[NCH], bp[NCH];
+#pragma unroll
+  for (int k = 0; k < NCH; ++k) {
+    const int c = k * 256 + lane * 8;
+    gp[k] = bp[k] = make_uint4(0, 0, 0, 0);
+    if (c < D) {
+      gp[k] = *reinterpret_cast<const uint4*>(gamma + c);
+      if (!RMS && beta) bp[k] = *reinterpret_cast<const uint4*>(beta + c);
+    }
+  }
+  uint4 nx[NCH], nr[NCH];
+  auto fetch = [&](int row) {
+    if (row >= T) return;
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < D) {
+        nx[k] = *reinterpret_cast<const uint4*>(x + (size_t)row * D + c);
+        if (res) nr[k] = *reinterpret_cast<const uint4*>(res + (size_t)row * D + c);
+      }
+    }
+  };
+  fetch(gw);
+  for (int row = gw; row < T; row += nw) {
+    float v[NCH][8];
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < D) {
+        unpack8(nx[k], v[k]);
+        if (res) {
+          float r[8];
+          unpack8(nr[k], r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[k][j] += r[j];
+          // the residual stream is stored rounded, and the statistics use the rounded sum so that backward sees the same row
+          uint4 packed;
+          packed.x = pack_bf16x2(v[k][0], v[k][1]);
+          packed.y = pack_bf16x2(v[k][2], v[k][3]);
+          packed.z = pack_bf16x2(v[k][4], v[k][5]);
+          packed.w = pack_bf16x2(v[k][6], v[k][7]);
+          *reinterpret_cast<uint4*>(xsum + (size_t)row * D + c) = packed;
+          unpack8(packed, v[k]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s += RMS ? v[k][j] * v[k][j] : v[k][j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[k][j] = 0.f;
+      }
+    }
+    fetch(row + nw);
+    s = warp_sum(s);
+    float mean = 0.f, rstd;
+    if (RMS) {
+      rstd = rsqrtf(s / D + eps);
+    } else {
+      mean = s / D;
+      float q = 0.f;
+#pragma unroll
+      for (int k = 0; k < NCH; ++k) {
+        const int c = k * 256 + lane * 8;
+        if (c < D) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float d = v[k][j] - mean;
+            q += d * d;
+          }
+        }
+      }
+      q = warp_sum(q);
+      rstd = rsqrtf(q / D + eps);
+    }
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const int c = k * 256 + lane * 8;
+      if (c < D) {
+        float g[8], b[8], o[8];
+        unpack8(gp[k], g);
+        unpack8(bp[k], b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (v[k][j] - mean) * rstd * g[j] + b[j];
+        store8(y + (size_t)row * D + c, o);
+      }
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------------------------
 // Backward. dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) for LayerNorm (g = dy * gamma),
 // dx = rstd * (g - xhat * mean(g * xhat)) for RMSNorm. If `dres` is given it is added to dx
@@ -411,7 +514,18 @@ extern "C" int inv_norm_fwd(const void* x, const void* res, const void* gamma, c
   auto B = reinterpret_cast<const __nv_bfloat16*>(beta);
   auto Y = reinterpret_cast<__nv_bfloat16*>(y);
   auto XS = reinterpret_cast<__nv_bfloat16*>(xsum);
-  if (rms) norm_fwd_kernel<true><<<grid, block, 0, st>>>(X, R, G, B, Y, XS, mean, rstd, T, D, eps);
+  const int nch = (D + 255) / 256;
+  if (nch <= 4) {  // register path, persistent grid
+    int g = (T + 7) / 8;
+    if (g > 148 * 2) g = 148 * 2;  // two CTAs per SM at 124 registers: one resident wave
+#define INV_NF_ROWS(R_, N_) norm_fwd_rows_kernel<R_, N_><<<g, 256, 0, st>>>(X, R, G, B, Y, XS, mean, rstd, T, D, eps)
+    if (rms) {
+      if (nch == 1) INV_NF_ROWS(true, 1); else if (nch == 2) INV_NF_ROWS(true, 2); else if (nch == 3) INV_NF_ROWS(true, 3); else INV_NF_ROWS(true, 4);
+    } else {
+      if (nch == 1) INV_NF_ROWS(false, 1); else if (nch == 2) INV_NF_ROWS(false, 2); else if (nch == 3) INV_NF_ROWS(false, 3); else INV_NF_ROWS(false, 4);
+    }
+#undef INV_NF_ROWS
+  } else if (rms) norm_fwd_kernel<true><<<grid, block, 0, st>>>(X, R, G, B, Y, XS, mean, rstd, T, D, eps);
   else norm_fwd_kernel<false><<<grid, block, 0, st>>>(X, R, G, B, Y, XS, mean, rstd, T, D, eps);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
