@@ -251,8 +251,6 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
 
   if (threadIdx.x == 0) OG_STAMP(0);
   if (threadIdx.x < (BITS == 8 ? 256 : (1 << BITS))) cb[threadIdx.x] = p.codebook[threadIdx.x];
-  OgCursor idx_cur(n_tiles, nb, p.dp_rounds);  // thread 0's walk over the index tiles (it issues their loads)
-  int idx_issued = 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < IDX_STAGES; ++s) {
       mbar_init(&idx_full[s], 1);
@@ -268,14 +266,8 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
     }
     *abort_flag = 0;
     fence_barrier_init();
+    tma_prefetch_desc(&tmap_idx);
     tma_prefetch_desc(&tmap_x);
-    // the first round of the index ring goes out now: the weights are static, every slot is free, and the loads'
-    // latency then overlaps the tensor-memory allocation, the lookup-table build and the CTA-wide sync below
-    for (; idx_cur.valid && idx_issued < IDX_STAGES; idx_cur.advance(), ++idx_issued) {
-      mbar_expect_tx(&idx_full[idx_issued], IDX_TILE);
-      tma_load_2d(sIdx + idx_issued * IDX_TILE, &tmap_idx, &idx_full[idx_issued], idx_cur.bb * ROWB, idx_cur.tile * BN);
-    }
-    OG_STAMP(2);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -292,13 +284,13 @@ oil_gemm_kernel(const __grid_constant__ CUtensorMap tmap_idx, const __grid_const
   if (warp == 0) {
     // lane 0 streams index tiles, lane 1 streams activation tiles; each runs ahead on its own ring
     if (lane == 0) {
-      // continues behind the loads issued before the sync
-      int si = idx_issued == IDX_STAGES ? 0 : idx_issued;
-      uint32_t ph = idx_issued == IDX_STAGES ? 0 : 1;
-      for (OgCursor& c = idx_cur; c.valid; c.advance()) {
+      int si = 0;
+      uint32_t ph = 1;
+      for (OgCursor c(n_tiles, nb, p.dp_rounds); c.valid; c.advance()) {
         if (!mbar_wait(&idx_empty[si], ph, abort_flag, p.status, ERR_WAIT_EMPTY)) break;
         mbar_expect_tx(&idx_full[si], IDX_TILE);  // bytes past the end of K are filled with zeros and counted
         tma_load_2d(sIdx + si * IDX_TILE, &tmap_idx, &idx_full[si], c.bb * ROWB, c.tile * BN);
+        OG_STAMP_ONCE(2, og_once);
         if (++si == IDX_STAGES) { si = 0; ph ^= 1; }
       }
     } else if (lane == 1) {
