@@ -28,8 +28,8 @@ int make_tmap_tokens_f32(CUtensorMap* out, const void* ptr, int cols, int S, int
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }  // sources read
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }        // copies complete
-// Adds a [1 x 128 rows x 32 floats] shared-memory box (128-byte swizzle) into the fp32 tensor behind the map. Rows past
-// the end of a sequence are clipped by the copy engine.
+// Adds a shared-memory box (shape and swizzle are the tensor map's: 32 rows x 16 floats, 64-byte swizzle) into the fp32
+// tensor behind the map. Rows past the end of a sequence are clipped by the copy engine.
 __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* m, const void* smem_src, int c0, int c1, int c2) {
   asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(reinterpret_cast<uint64_t>(m)),
                "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
@@ -63,9 +63,9 @@ struct BwdSmem {
   static constexpr int DO_OFF = Q_OFF + STAGES * TILE;
   static constexpr int PT_OFF = DO_OFF + STAGES * TILE;
   static constexpr int DST_OFF = PT_OFF + 32768;
-  static constexpr int DQS_OFF = DST_OFF + 32768;      // D = 64: the fp32 dQ block (two 128 x 32 boxes) on its way to the reduce copy
+  static constexpr int DQS_OFF = DST_OFF + 32768;      // D = 64: the fp32 dQ block on its way to the reduce copies, one 32 x 16 box per softmax warp
   static constexpr int STAT_OFF = DQS_OFF + (ND == 1 ? 32768 : 0);  // lse and delta of the current query block, two stages
-  static constexpr int BAR_OFF = STAT_OFF + 2 * 2 * 128 * 4;
+  static constexpr int BAR_OFF = STAT_OFF + 16 * 2 * 64 * 4;   // per softmax warp: two stages of 32 lse + 32 delta
   static constexpr int TOTAL = BAR_OFF + 256 + 1024;
 };
 
@@ -267,27 +267,27 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       const int hj = hk * G + j / nq_it;
       const int qrow = (i0 + j % nq_it) * 128 + r;
       if (DQ_TMA) {
-        // 16 columns of this thread's query row -> four 16-byte chunks of the swizzled box
+        // Every warp drains its own 32 rows x 16 columns: TMEM -> a private 2 KB box in shared memory (64-byte rows,
+        // 64-byte swizzle: chunk ^ ((row >> 1) & 3)) -> one reduce copy issued by the warp's first lane. No barrier
+        // across warps: a warp only waits for its own previous copy to have read its box.
         uint32_t rr[16];
         tmem_ld_32x16(t_lane + DQ_COL + cq * 16, rr);
-        if (threadIdx.x == 64) bulk_wait_read();        // the previous block's copies have read the staging tile
-        asm volatile("bar.sync 2, 512;" ::: "memory");
+        if (lane == 0) bulk_wait_read();
+        __syncwarp();
         tmem_ld_wait();
-        uint8_t* row = sDq + (cq >> 1) * 16384 + r * 128;
+        uint8_t* box = sDq + (warp - 2) * 2048;
+        uint8_t* row = box + lane * 64;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const int chunk = ((cq & 1) * 4 + g) ^ (r & 7);
+          const int chunk = g ^ ((lane >> 1) & 3);
           *reinterpret_cast<uint4*>(row + chunk * 16) = make_uint4(rr[g * 4], rr[g * 4 + 1], rr[g * 4 + 2], rr[g * 4 + 3]);
         }
         tc_fence_before();
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(dq_empty);
-        asm volatile("bar.sync 2, 512;" ::: "memory");  // the whole block is staged
-        if (threadIdx.x == 64) {
-          const int q0j = (i0 + j % nq_it) * 128;
-          tma_reduce_add_3d(&tmap_dq, sDq, hj * D, q0j, b);
-          tma_reduce_add_3d(&tmap_dq, sDq + 16384, hj * D + 32, q0j, b);
+        if (lane == 0) {
+          mbar_arrive(dq_empty);
+          tma_reduce_add_3d(&tmap_dq, box, hj * D + cq * 16, (i0 + j % nq_it) * 128 + q * 32, b);
           bulk_commit();
         }
         return;
@@ -311,24 +311,32 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_empty);
     };
-    // The row statistics (lse, delta) of a query block go through shared memory: one global load per thread (the first
-    // 256 softmax threads) and block, read back in the inner loop as broadcast 16-byte loads. The load for block it + 1 is
-    // issued while block it is being computed and its value is parked in a register, so that no warp waits on it.
-    const int st_tid = threadIdx.x - 64;  // 0..511 over the softmax warps
-    auto stat_load = [&](int it) -> float {
+    // The row statistics (lse, delta) of a query block go through shared memory, a private region per warp: lane i
+    // fetches lse and delta of column cq * 32 + i (two global loads per thread and block; the four warps of a column
+    // quarter fetch the same values), the inner loop reads them back as broadcast 16-byte loads. The loads for block
+    // it + 1 are issued while block it is being computed and parked in registers, so that no warp waits on them, and
+    // no barrier across warps is involved.
+    float* wstat = sStat + (warp - 2) * 128;  // [stage][lse 32 | delta 32]
+    auto stat_load = [&](int it, float& l, float& d) {
       const int h = hk * G + it / nq_it;
-      const int qi = min((i0 + it % nq_it) * 128 + (st_tid & 127), p.S - 1);
-      const float* row = (st_tid < 128 ? p.lse : p.delta) + ((size_t)b * p.H + h) * p.S;
-      return __ldg(row + qi);
+      const int qi = min((i0 + it % nq_it) * 128 + cq * 32 + lane, p.S - 1);
+      const size_t o = ((size_t)b * p.H + h) * p.S + qi;
+      l = __ldg(p.lse + o);
+      d = __ldg(p.delta + o);
     };
-    if (n_it > 0 && st_tid < 256) sStat[st_tid] = stat_load(0);
+    if (n_it > 0) {
+      float l, d;
+      stat_load(0, l, d);
+      wstat[lane] = l;
+      wstat[32 + lane] = d;
+    }
     for (int it = 0; it < n_it; ++it) {
       const int q0 = (i0 + it % nq_it) * 128;
-      float* stat = sStat + (it & 1) * 256;
+      const float* stat = wstat + (it & 1) * 64;
       if (!mbar_wait_warp(s_full, it & 1, abort_flag, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       if (threadIdx.x == 64) FB_STAMP(8 + 3 * it);
-      asm volatile("bar.sync 1, 512;" ::: "memory");  // the statistics of this block are in place (softmax warps only)
+      __syncwarp();  // the statistics of this block are in place (written by this warp)
       const bool windowed = p.causal && p.window > 0;
       const bool need_mask = (p.causal && q0 < k0 + 127) || (q0 + 128 > p.S) || (k0 + 128 > p.S) || (windowed && q0 + 127 - k0 >= p.window);
       // The thread's 32 columns of S^T and dP^T come in as two halves of 16 (the register file holds 96 registers per
@@ -336,7 +344,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       // second load. A column i of the thread is live iff lim_lo <= i < lim_hi (causal diagonal, sequence end, window).
       uint32_t pk[16], dk[16];  // P^T and dS^T of this thread's 32 columns as packed bf16 pairs, kept in registers until the
                                 // shared-memory tiles are free
-      float stat_next = 0.f;
+      float stat_next_l = 0.f, stat_next_d = 0.f;
       const int col0 = cq * 32;
       int lim_lo = 0, lim_hi = 32;
       if (need_mask) {
@@ -358,11 +366,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(s_empty);  // one arrival per warp: arrivals on one mbarrier are serialised
-          if (it + 1 < n_it && st_tid < 256) stat_next = stat_load(it + 1);
+          if (it + 1 < n_it) stat_load(it + 1, stat_next_l, stat_next_d);
         }
         // statistics as 16-byte broadcast loads; one MUFU op and half a conversion per element
-        const float4* l4 = reinterpret_cast<const float4*>(stat + col0 + half * 16);
-        const float4* d4 = reinterpret_cast<const float4*>(stat + 128 + col0 + half * 16);
+        const float4* l4 = reinterpret_cast<const float4*>(stat + half * 16);
+        const float4* d4 = reinterpret_cast<const float4*>(stat + 32 + half * 16);
 #pragma unroll
         for (int i4 = 0; i4 < 4; ++i4) {
           const float4 l = l4[i4], dl = d4[i4];
@@ -386,8 +394,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       };
       if (need_mask) softmax_block(std::true_type{});   // two copies of the loop: interior blocks carry no selects
       else softmax_block(std::false_type{});
-      // the other statistics buffer was last read in block it - 1, which every warp left before this block's barrier
-      if (it + 1 < n_it && st_tid < 256) sStat[((it + 1) & 1) * 256 + st_tid] = stat_next;
+      // the warp's other statistics stage was last read in block it - 1
+      if (it + 1 < n_it) {
+        wstat[((it + 1) & 1) * 64 + lane] = stat_next_l;
+        wstat[((it + 1) & 1) * 64 + 32 + lane] = stat_next_d;
+      }
       // Software pipeline (when dQ has its own TMEM columns): the arithmetic above ran while the MMAs of the previous
       // block were still reading its P^T / dS^T tiles; only now wait for them, publish this block's tiles, and read the
       // previous block's dQ out of TMEM while this block's MMAs run.
@@ -456,7 +467,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       tc_fence_before();
       if (threadIdx.x == 64) FB_STAMP(4);
     }
-    if (DQ_TMA && threadIdx.x == 64) bulk_wait_all();  // the reduce copies must have landed before the grid ends
+    if (DQ_TMA && lane == 0) bulk_wait_all();  // this warp's reduce copies must have landed before the grid ends
   }
 
   __syncthreads();

@@ -323,16 +323,16 @@ int make_tmap_tokens_bf16(CUtensorMap* out, const void* ptr, int cols, int S, in
   return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
 }
 
-// fp32 [B, S, cols] (dense rows): boxes of 128 rows x 32 floats, 128-byte swizzle.
+// fp32 [B, S, cols] (dense rows): boxes of 32 rows x 16 floats, 64-byte swizzle.
 int make_tmap_tokens_f32(CUtensorMap* out, const void* ptr, int cols, int S, int B) {
   EncodeTiledFn enc = fa_encode_fn();
   if (!enc) return -1;
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)S, (cuuint64_t)B};
   cuuint64_t strides[2] = {(cuuint64_t)cols * 4, (cuuint64_t)S * cols * 4};
-  cuuint32_t box[3] = {32, 128, 1};
+  cuuint32_t box[3] = {16, 32, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
 }
 
