@@ -106,7 +106,11 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& p, int row
           }
         }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+        for (int i = 0; i < 32; i += 2) {
+          const float2 y = gelu_tanh_pair(v[i], v[i + 1]);
+          v[i] = y.x;
+          v[i + 1] = y.y;
+        }
       } else if (p.epilogue == EPI_DGELU || p.epilogue == EPI_ADD) {
         const __nv_bfloat16* ap = p.aux_in + (size_t)row * p.ld_aux + col0;
 #pragma unroll
@@ -119,8 +123,9 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& p, int row
             for (int j = 0; j < 4; ++j) {
               float2 f = __bfloat1622float2(a2[j]);
               if (p.epilogue == EPI_DGELU) {
-                v[g * 8 + 2 * j] *= gelu_tanh_grad(f.x);
-                v[g * 8 + 2 * j + 1] *= gelu_tanh_grad(f.y);
+                const float2 d = gelu_tanh_grad_pair(f.x, f.y);
+                v[g * 8 + 2 * j] *= d.x;
+                v[g * 8 + 2 * j + 1] *= d.y;
               } else {
                 v[g * 8 + 2 * j] += f.x;
                 v[g * 8 + 2 * j + 1] += f.y;

@@ -296,6 +296,36 @@ __device__ __forceinline__ float gelu_tanh_grad(float x) {
   float du = k0 * (1.0f + 3.0f * k1 * x2);
   return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
 }
+// The same two functions over a pair of values in packed fp16 arithmetic (one tanh.approx.f16x2 per pair, about half the
+// instructions of the fp32 forms): for the GEMM epilogues, where the activation math competes with the accumulator
+// read-out for issue slots. fp16 keeps 11 significant bits, more than the bf16 the results are rounded to; the argument
+// of the cubic is clamped to +-16 (tanh has saturated long before), so no intermediate overflows.
+__device__ __forceinline__ __half2 gelu_h2_tanh(__half2 xc, __half2& a) {
+  const __half2 k0 = __float2half2_rn(0.7978845608028654f), k01 = __float2half2_rn(0.7978845608028654f * 0.044715f);
+  a = __hmul2(xc, xc);
+  const __half2 u = __hmul2(xc, __hfma2(a, k01, k0));
+  uint32_t t;
+  asm("tanh.approx.f16x2 %0, %1;" : "=r"(t) : "r"(*reinterpret_cast<const uint32_t*>(&u)));
+  return *reinterpret_cast<__half2*>(&t);
+}
+__device__ __forceinline__ __half2 clamp16_h2(__half2 x) {
+  return __hmax2(__hmin2(x, __float2half2_rn(16.f)), __float2half2_rn(-16.f));
+}
+__device__ __forceinline__ float2 gelu_tanh_pair(float x0, float x1) {
+  const __half2 x = __floats2half2_rn(x0, x1), half = __float2half2_rn(0.5f);
+  __half2 a;
+  const __half2 t = gelu_h2_tanh(clamp16_h2(x), a);
+  return __half22float2(__hmul2(x, __hfma2(t, half, half)));
+}
+__device__ __forceinline__ float2 gelu_tanh_grad_pair(float x0, float x1) {
+  const __half2 x = clamp16_h2(__floats2half2_rn(x0, x1)), half = __float2half2_rn(0.5f), one = __float2half2_rn(1.f);
+  const __half2 k0 = __float2half2_rn(0.7978845608028654f), k03 = __float2half2_rn(3.f * 0.7978845608028654f * 0.044715f);
+  __half2 a;
+  const __half2 t = gelu_h2_tanh(x, a);
+  const __half2 w = __hfma2(__hneg2(t), t, one);                       // 1 - t^2
+  const __half2 z = __hmul2(__hmul2(x, half), w);                      // 0.5 x (1 - t^2)
+  return __half22float2(__hfma2(z, __hfma2(a, k03, k0), __hfma2(t, half, half)));
+}
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 __device__ __forceinline__ float silu_grad_f(float x) {
   float s = 1.0f / (1.0f + __expf(-x));
