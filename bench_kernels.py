@@ -2,7 +2,7 @@
 tools/bench.cpp:51-155): device-timed with CUDA events after warm-up, L2 flushed between
 iterations, reported against the measured peaks in MEASURED_PEAKS.json when present.
 
-    python bench_kernels.py --kernel gemm --m 32768 --n 3072 --k 768 [--layout nt|nn|tn|tt] [--epilogue add|dgelu|gelu] [--iters 20]
+    python bench_kernels.py --kernel gemm --m 32768 --n 3072 --k 768 [--layout nt|nn|tn|tt] [--epilogue add|dgelu|gelu|gelu_dg|mul] [--iters 20]
     python bench_kernels.py --kernel attn --batch 16 --seq 1024 --heads 12 --head-dim 64 [--backward] [--window 256]
     python bench_kernels.py --kernel norm|ce|adamw ...
     python bench_kernels.py --kernel all
@@ -58,10 +58,11 @@ def bench_gemm(a):
     out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
     t = Timer(not a.no_flush)
     kw = {}
-    if a.epilogue in ("add", "dgelu"):      # second operand of the epilogue: residual / pre-activation, TMA-loaded box by box
-        kw = dict(epilogue=ops.EPI_ADD if a.epilogue == "add" else ops.EPI_DGELU, aux_in=torch.randn(M, N, device="cuda").bfloat16())
-    elif a.epilogue == "gelu":
-        kw = dict(epilogue=ops.EPI_GELU, aux_out=torch.empty(M, N, device="cuda", dtype=torch.bfloat16))
+    if a.epilogue in ("add", "dgelu", "mul"):      # second operand of the epilogue: residual / pre-activation, TMA-loaded box by box
+        kw = dict(epilogue={"add": ops.EPI_ADD, "dgelu": ops.EPI_DGELU, "mul": ops.EPI_MUL}[a.epilogue],
+                  aux_in=torch.randn(M, N, device="cuda").bfloat16())
+    elif a.epilogue in ("gelu", "gelu_dg"):
+        kw = dict(epilogue=ops.EPI_GELU if a.epilogue == "gelu" else ops.EPI_GELU_DG, aux_out=torch.empty(M, N, device="cuda", dtype=torch.bfloat16))
     ms = t(lambda: ops.gemm(A, B, out=out, a_mn=a_mn, b_mn=b_mn, **kw), a.iters)
     ref = t(lambda: torch.matmul(A.t() if a_mn else A, B if b_mn else B.t(), out=out), a.iters) if a.compare else None
     hbm, tf, kind = peaks()
@@ -222,7 +223,7 @@ def main():
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--causal", type=int, default=1)
     ap.add_argument("--window", type=int, default=0, help="attn: causal sliding window (0 = full causal)")
-    ap.add_argument("--epilogue", default="none", choices=["none", "add", "dgelu", "gelu"], help="gemm: fused epilogue")
+    ap.add_argument("--epilogue", default="none", choices=["none", "add", "dgelu", "gelu", "gelu_dg", "mul"], help="gemm: fused epilogue")
     ap.add_argument("--backward", action="store_true")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--compare", action="store_true", help="also time the library GEMM")

@@ -89,7 +89,30 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& p, int row
       }
     }
     if (row_ok) {
-      if (p.epilogue == EPI_GELU) {
+      if (p.epilogue == EPI_GELU_DG) {
+        // both the activation and its derivative from one tanh per pair; the derivative is what the backward pass needs
+        float dgv[32];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float2 d = gelu_tanh_grad_pair(v[i], v[i + 1]);
+          const float2 y = gelu_tanh_pair(v[i], v[i + 1]);   // the common subexpressions (clamp, cubic, tanh) are merged by the compiler
+          dgv[i] = d.x; dgv[i + 1] = d.y;
+          v[i] = y.x; v[i + 1] = y.y;
+        }
+        __nv_bfloat16* ap = p.aux_out + (size_t)row * p.ld_aux + col0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (col0 + g * 8 < p.N) {
+            uint4 o;
+            o.x = pack_bf16x2(dgv[g * 8 + 0], dgv[g * 8 + 1]);
+            o.y = pack_bf16x2(dgv[g * 8 + 2], dgv[g * 8 + 3]);
+            o.z = pack_bf16x2(dgv[g * 8 + 4], dgv[g * 8 + 5]);
+            o.w = pack_bf16x2(dgv[g * 8 + 6], dgv[g * 8 + 7]);
+            if (stg_aux) *reinterpret_cast<uint4*>(stg_aux + (((sub * 4 + g) ^ (lane & 7)) << 4)) = o;
+            else *reinterpret_cast<uint4*>(ap + g * 8) = o;
+          }
+        }
+      } else if (p.epilogue == EPI_GELU) {
         if (p.aux_out != nullptr) {
           __nv_bfloat16* ap = p.aux_out + (size_t)row * p.ld_aux + col0;
 #pragma unroll
@@ -111,7 +134,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& p, int row
           v[i] = y.x;
           v[i + 1] = y.y;
         }
-      } else if (p.epilogue == EPI_DGELU || p.epilogue == EPI_ADD) {
+      } else if (INV_EPI_READS_AUX(p.epilogue)) {
         const __nv_bfloat16* ap = p.aux_in + (size_t)row * p.ld_aux + col0;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -126,6 +149,9 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& p, int row
                 const float2 d = gelu_tanh_grad_pair(f.x, f.y);
                 v[g * 8 + 2 * j] *= d.x;
                 v[g * 8 + 2 * j + 1] *= d.y;
+              } else if (p.epilogue == EPI_MUL) {
+                v[g * 8 + 2 * j] *= f.x;
+                v[g * 8 + 2 * j + 1] *= f.y;
               } else {
                 v[g * 8 + 2 * j] += f.x;
                 v[g * 8 + 2 * j + 1] += f.y;

@@ -341,7 +341,8 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
       (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(C) & 15))
     return -ERR_BAD_ARG;
   if (epilogue == EPI_ATOMIC && !c_f32) return -ERR_BAD_ARG;
-  if ((epilogue == EPI_DGELU || epilogue == EPI_ADD) && (aux_in == nullptr || (ld_aux % 8))) return -ERR_BAD_ARG;
+  if (INV_EPI_READS_AUX(epilogue) && (aux_in == nullptr || (ld_aux % 8))) return -ERR_BAD_ARG;
+  if (epilogue == EPI_GELU_DG && (aux_out == nullptr || (ld_aux % 8))) return -ERR_BAD_ARG;
   if (g_num_sms == 0) {
     int dev = 0;
     cudaGetDevice(&dev);

@@ -267,12 +267,12 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
     const bool staged = !p.c_f32;
-    const bool staged_aux = staged && p.epilogue == EPI_GELU && p.aux_out != nullptr;
+    const bool staged_aux = staged && INV_EPI_WRITES_AUX(p.epilogue) && p.aux_out != nullptr;
     // Second operand of the epilogue (residual to add, pre-activation of the GELU backward) through TMA: the warp's two
     // 4 KB boxes alternate; box i is loaded while box i-1 is computed, the result overwrites the operand in place and
     // leaves through a TMA store. Per-thread global loads of a row-strided operand serialise on memory latency
     // (sixteen dependent round trips per tile) and made these epilogues three times as long as the main loop.
-    const bool aux_tma = staged && (p.epilogue == EPI_DGELU || p.epilogue == EPI_ADD);
+    const bool aux_tma = staged && INV_EPI_READS_AUX(p.epilogue);
     uint8_t* my_stage = sStage + (warp - 2) * 8192;
     uint64_t* my_aux_bar = aux_bar + (warp - 2) * 2;
     const int row_in_tile = (int)cta * 128 + q * 32;
@@ -415,10 +415,10 @@ int gemm_2cta_dispatch(const void* A, const void* B, const GemmParams& p0, int l
   if (!p.c_f32) {
     if ((rc = make_tmap_2d_bf16(&tc, p.C, (uint64_t)p.N, (uint64_t)p.M, (uint64_t)p.ldc, 64, 32))) return rc;
     tx = tc;
-    if (p.epilogue == EPI_GELU && p.aux_out != nullptr &&
+    if (INV_EPI_WRITES_AUX(p.epilogue) && p.aux_out != nullptr &&
         (rc = make_tmap_2d_bf16(&tx, p.aux_out, (uint64_t)p.N, (uint64_t)p.M, (uint64_t)p.ld_aux, 64, 32)))
       return rc;
-    if ((p.epilogue == EPI_DGELU || p.epilogue == EPI_ADD) &&   // the epilogue's second operand arrives through TMA loads
+    if (INV_EPI_READS_AUX(p.epilogue) &&   // the epilogue's second operand arrives through TMA loads
         (rc = make_tmap_2d_bf16(&tx, p.aux_in, (uint64_t)p.N, (uint64_t)p.M, (uint64_t)p.ld_aux, 64, 32)))
       return rc;
   }

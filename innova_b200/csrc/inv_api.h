@@ -15,7 +15,12 @@ enum {
   EPI_DGELU = 2,   // C = alpha*acc * gelu'(aux_in)
   EPI_ADD = 3,     // C = alpha*acc + bias + aux_in   (residual add; aux_in may alias C)
   EPI_ATOMIC = 4,  // C(fp32) += alpha*acc            (split-K / gradient accumulation)
+  EPI_GELU_DG = 5, // x = alpha*acc + bias; aux_out = gelu'(x); C = gelu(x)   (the backward then needs one multiply: EPI_MUL)
+  EPI_MUL = 6,     // C = alpha*acc * aux_in
 };
+// epilogues that write a second bf16 output / read a second bf16 operand of C's shape
+#define INV_EPI_WRITES_AUX(e) ((e) == EPI_GELU || (e) == EPI_GELU_DG)
+#define INV_EPI_READS_AUX(e) ((e) == EPI_DGELU || (e) == EPI_ADD || (e) == EPI_MUL)
 
 // C[M,N] = op(A)[M,K] * op(B)[N,K]^T. a_mn/b_mn = 0: operand stored [rows, K] row-major;
 // = 1: operand stored [K, rows] row-major. lda/ldb/ldc/ld_aux in elements.

@@ -15,7 +15,7 @@ import torch.nn.functional as F
 
 from . import runtime as rt
 
-EPI_NONE, EPI_GELU, EPI_DGELU, EPI_ADD, EPI_ATOMIC = 0, 1, 2, 3, 4
+EPI_NONE, EPI_GELU, EPI_DGELU, EPI_ADD, EPI_ATOMIC, EPI_GELU_DG, EPI_MUL = 0, 1, 2, 3, 4, 5, 6
 NUM_SMS = 148
 import os
 # 0: tile shape chosen by problem size (256x256 CTA pairs for large problems); 1: always the single-CTA 128x256 kernel
@@ -195,9 +195,10 @@ def linear(x, weight, bias=None, residual=None, mode="none"):
 
 
 class _MlpGeluFn(torch.autograd.Function):
-    """y = gelu(x W1^T + b1) W2^T + b2 (+ residual) as two GEMMs with fused epilogues. Backward fuses
-    the GELU derivative into the dgrad GEMM of the second layer, so the activation gradient never
-    makes a separate pass over memory."""
+    """y = gelu(x W1^T + b1) W2^T + b2 (+ residual) as two GEMMs with fused epilogues. The first epilogue writes the
+    activation and, as its second output, the GELU DERIVATIVE at the pre-activation (same tanh, a few more packed
+    operations); the backward dgrad GEMM of the second layer multiplies by it in its epilogue, so the activation gradient
+    never makes a separate pass over memory and the backward epilogue carries no transcendental math."""
 
     @staticmethod
     def forward(ctx, x, w1, b1, w2, b2, residual):
@@ -207,8 +208,8 @@ class _MlpGeluFn(torch.autograd.Function):
             x2 = x2.contiguous()
         T = x2.shape[0]
         Fdim, N = w1.shape[0], w2.shape[0]
-        pre = torch.empty((T, Fdim), dtype=torch.bfloat16, device=x.device)
-        act = gemm(x2, w1, epilogue=EPI_GELU, bias=b1, aux_out=pre)
+        pre = torch.empty((T, Fdim), dtype=torch.bfloat16, device=x.device)      # holds gelu'(x W1^T + b1)
+        act = gemm(x2, w1, epilogue=EPI_GELU_DG, bias=b1, aux_out=pre)
         y = torch.empty((*shp[:-1], N), dtype=torch.bfloat16, device=x.device)
         if residual is not None:
             gemm(act, w2, out=y.view(-1, N), epilogue=EPI_ADD, bias=b2, aux_in=residual.reshape(-1, N))
@@ -227,7 +228,7 @@ class _MlpGeluFn(torch.autograd.Function):
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         cs = rt.take_colsum(dy2)
-        dpre = gemm(dy2, w2, b_mn=True, epilogue=EPI_DGELU, aux_in=pre)
+        dpre = gemm(dy2, w2, b_mn=True, epilogue=EPI_MUL, aux_in=pre)
         dw2 = _accumulate_wgrad(w2, dy2, act)
         db2 = _accumulate_bgrad(b2, dy2, cs) if b2 is not None else None
         dx = gemm(dpre, w1, b_mn=True).view(ctx.xshape)

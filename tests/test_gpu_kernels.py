@@ -66,6 +66,20 @@ def test_gemm_epilogues():
     F.gelu(x, approximate="tanh").sum().backward()
     out = ops.gemm(A, B, epilogue=ops.EPI_DGELU, aux_in=aux)
     assert _rel_err(out, ref * x.grad) < 2e-2
+    # gelu with its derivative as the second output, and the multiply that consumes it in the backward pass
+    dg = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    out = ops.gemm(A, B, epilogue=ops.EPI_GELU_DG, bias=bias, aux_out=dg)
+    xb = (ref + bias.float()).requires_grad_(True)
+    F.gelu(xb, approximate="tanh").sum().backward()
+    assert _rel_err(out, F.gelu(xb.detach(), approximate="tanh")) < 1e-2
+    assert _rel_err(dg, xb.grad) < 1e-2
+    wide = (torch.randn(M, N, device=dev) * 40).bfloat16()              # far outside the range where tanh has saturated
+    xw = wide.float().requires_grad_(True)
+    F.gelu(xw, approximate="tanh").sum().backward()
+    out = ops.gemm(A, B, epilogue=ops.EPI_DGELU, aux_in=wide)
+    assert torch.isfinite(out.float()).all() and _rel_err(out, ref * xw.grad) < 2e-2
+    out = ops.gemm(A, B, epilogue=ops.EPI_MUL, aux_in=aux)
+    assert _rel_err(out, ref * aux.float()) < 1e-2
     # residual add (aliasing the output)
     res = aux.clone()
     ops.gemm(A, B, out=res, epilogue=ops.EPI_ADD, bias=bias, aux_in=res)
