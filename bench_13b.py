@@ -67,6 +67,8 @@ def main():
     toks = zipf_tokens((a.warmup + a.steps) * accum * a.micro_batch * (a.seq + 1), cfg.vocab_size, 1.1, seed=100 + group_id).view(-1, a.seq + 1)
     host = toks.pin_memory()
 
+    first = []                          # this rank's share of the loss of the very first micro-batch (before any update)
+
     def step(i):
         loss = torch.zeros((), device=dev)
         for m in range(accum):
@@ -75,6 +77,8 @@ def main():
             l = model(b[:, :-1].contiguous(), b[:, 1:].contiguous())
             (l / accum).backward()
             loss += l.detach() / accum
+            if not first:
+                first.append(l.detach().clone())
         for _, p, _, _ in eng.entries:   # parameters whose gradient came through autograd rather than a fused wgrad
             if p.grad is not None:
                 p.main_grad.add_(p.grad.float())
@@ -98,7 +102,14 @@ def main():
     ms = torch.tensor([e0.elapsed_time(e1) / a.steps], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     dist.all_reduce(loss, group=tp_group)          # the pair's shares add up to the mean loss of its micro-batches
+    dist.all_reduce(first[0], group=tp_group)
     rt.check_status()
+    # sanity of the numerics at this size: random-init weights score every token near the uniform guess. The logits of the
+    # 0.02-std LM head over a normalised d-wide stream have variance 4e-4 d, which adds half of that to ln V.
+    import math
+    first_loss, expect = float(first[0]), math.log(a.vocab) + 2e-4 * a.hidden
+    if not abs(first_loss - expect) < 0.1 * math.log(a.vocab):
+        raise SystemExit(f"loss sanity: first micro-batch loss {first_loss:.3f}, expected about {expect:.3f} (ln V = {math.log(a.vocab):.3f})")
     tokens = dp * accum * a.micro_batch * a.seq
     params = sum(p.numel() for p in model.parameters())
     rep = sum(p.numel() for p in model.replicated_parameters())
@@ -108,8 +119,8 @@ def main():
                           "config": {"model": f"dense {a.layers}L d{a.hidden} {a.heads}h ffn{a.ffn} vocab{a.vocab}", "global_batch_sequences":
                                      dp * accum * a.micro_batch, "seq_len": a.seq, "parallelism": f"fsdp{dp} x tp{tp}", "grad_accum": accum,
                                      "ste_format": a.ste_format, "gradient_checkpointing": True, "cache_ste": a.cache_ste},
-                          "params_total": rep + (params - rep) * tp, "gpu_launches": rt.launch_count() - n0, "loss": float(loss),
-                          "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)}))
+                          "params_total": rep + (params - rep) * tp, "gpu_launches": rt.launch_count() - n0, "first_loss": first_loss, "ln_vocab": math.log(a.vocab),
+                          "loss": float(loss), "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)}))
     dist.barrier()
     dist.destroy_process_group()
 

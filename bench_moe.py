@@ -49,6 +49,8 @@ def main():
     toks = zipf_tokens((a.warmup + a.steps) * accum * a.micro_batch * (a.seq + 1), cfg.vocab_size, 1.1, seed=rank).view(-1, a.seq + 1)
     host = toks.pin_memory()
 
+    first = []                          # loss of the very first micro-batch (before any update), auxiliary losses included
+
     def step(i):
         loss = None
         for m in range(accum):
@@ -57,6 +59,8 @@ def main():
             l = model(b[:, :-1].contiguous(), b[:, 1:].contiguous(), grad_scale=1.0 / accum)
             (l / accum).backward()
             loss = l.detach()
+            if not first:
+                first.append(l.detach().clone())
         for _, p, _, _ in eng.entries:
             if p.grad is not None:
                 p.main_grad.add_(p.grad.float())
@@ -79,6 +83,14 @@ def main():
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     rt.check_status()
+    # sanity of the numerics: random-init weights score every token near the uniform guess. The 0.02-std LM head over a
+    # normalised d-wide stream adds 2e-4 d to ln V, the auxiliary losses (load balance 0.01 and z-loss 0.001 per layer) a
+    # few tenths.
+    import math
+    first_loss = float(first[0])
+    expect = math.log(cfg.vocab_size) + 2e-4 * a.hidden + 0.015 * a.layers
+    if not abs(first_loss - expect) < 0.1 * math.log(cfg.vocab_size):
+        raise SystemExit(f"loss sanity: first micro-batch loss {first_loss:.3f}, expected about {expect:.3f}")
     tokens = world * accum * a.micro_batch * a.seq
     if rank == 0:
         print(json.dumps({"metric": "moe_train_tokens_per_sec", "value": tokens / (float(ms) / 1e3), "unit": "tokens/s", "n_gpus": world,
@@ -86,7 +98,8 @@ def main():
                           "config": {"model": f"moe {a.layers}L d{a.hidden} {a.experts}x top-2 ffn{a.ffn}", "global_batch_sequences":
                                      world * accum * a.micro_batch, "seq_len": a.seq, "parallelism": f"ep{world}+dp{world}", "grad_accum": accum},
                           "params_total": sum(p.numel() for p in model.parameters()) + (world - 1) * sum(p.numel() for p in model.expert_parameters())
-                          if world > 1 else model.num_params(), "gpu_launches": rt.launch_count() - n0, "loss": float(loss)}))
+                          if world > 1 else model.num_params(), "gpu_launches": rt.launch_count() - n0, "first_loss": first_loss,
+                          "ln_vocab": math.log(cfg.vocab_size), "loss": float(loss)}))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
