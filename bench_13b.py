@@ -61,7 +61,8 @@ def main():
                             ffn_hidden_size=a.ffn, max_seq_len=a.seq, activation="silu", norm="rmsnorm", positions="rope", bias=False,
                             ste_format=a.ste_format or None, gradient_checkpointing=True)
     model = TPDenseModel(cfg, tp_group, dtype=torch.bfloat16, device=dev, seed=1, cache_ste=a.cache_ste).train()
-    eng = ShardedFlatEngine(model, lr=1e-4, weight_decay=0.1, max_grad_norm=0.0, group=dp_group)
+    warm = lambda s: 1e-4 * min(1.0, s / 200.0)     # linear warm-up: a first AdamW step at the full rate doubles the loss at this size
+    eng = ShardedFlatEngine(model, lr=1e-4, weight_decay=0.1, max_grad_norm=0.0, group=dp_group, lr_schedule=warm)
     accum = max(1, a.global_batch // (dp * a.micro_batch))
     group_id = rank // tp            # both ranks of a pair read the same micro-batches
     toks = zipf_tokens((a.warmup + a.steps) * accum * a.micro_batch * (a.seq + 1), cfg.vocab_size, 1.1, seed=100 + group_id).view(-1, a.seq + 1)

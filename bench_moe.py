@@ -44,7 +44,9 @@ def main():
                             lb_coef=0.01, z_coef=0.001)
     model = MoEModel(cfg, dtype=torch.bfloat16, device=dev, seed=1, ep_group=dist.group.WORLD if world > 1 else None,
                      ep_max_tokens=a.micro_batch * a.seq, ep_capacity_factor=a.capacity_factor)
-    eng = ExpertParallelEngine(model, lr=1e-4, weight_decay=0.1, max_grad_norm=1.0) if world > 1 else FlatParamEngine(model, lr=1e-4, weight_decay=0.1)
+    warm = lambda s: 1e-4 * min(1.0, s / 200.0)     # linear warm-up of the learning rate
+    eng = (ExpertParallelEngine(model, lr=1e-4, weight_decay=0.1, max_grad_norm=1.0, lr_schedule=warm) if world > 1
+           else FlatParamEngine(model, lr=1e-4, weight_decay=0.1, lr_schedule=warm))
     accum = max(1, a.global_batch // (world * a.micro_batch))
     toks = zipf_tokens((a.warmup + a.steps) * accum * a.micro_batch * (a.seq + 1), cfg.vocab_size, 1.1, seed=rank).view(-1, a.seq + 1)
     host = toks.pin_memory()
