@@ -767,13 +767,82 @@ struct SlicePeers {
   __nv_bfloat16* x[8];   // every rank's copy of the [M, N] residual stream
   float* sumsq[8];       // every rank's [W, M] partial sums of squares
 };
+// A barrier over peer flags at the head of a multi-CTA kernel, so that the barrier costs no launch of its own.
+// `state` = {done, tickets} in this rank's memory: `done` is the epoch of the last completed use and is only written by
+// the last CTA of a launch, so every CTA of the next launch reads the same value and derives the same epoch. CTA 0 raises
+// this rank's word in every peer's flag set (everything this rank issued before the launch is complete: kernel boundary);
+// every CTA waits, for at most a second, until all words of the local set have reached the epoch. `barrier_tail` is called
+// by every CTA when it is done.
+struct HeadBarrier {
+  uint32_t* peer_flags[8];
+  const uint32_t* local_flags;
+  uint32_t* state;
+  int* status;
+};
+__device__ __forceinline__ uint32_t barrier_head(const HeadBarrier& hb, int W, int rank) {
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    uint32_t d;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(d) : "l"(hb.state) : "memory");
+    s_epoch = d + 1;
+    s_ok = 1;
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  if (blockIdx.x == 0 && threadIdx.x < W) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(hb.peer_flags[threadIdx.x] + rank), "r"(epoch) : "memory");
+  }
+  if (threadIdx.x < W) {
+    uint64_t t0 = 0;
+    uint32_t spins = 0, v;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(hb.local_flags + threadIdx.x) : "memory");
+      if ((int32_t)(v - epoch) >= 0) break;
+      if ((++spins & 0xffu) == 0) {
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > 1000000000ull) {
+          s_ok = 0;
+          if (hb.status) atomicCAS(hb.status, 0, (int)ERR_WAIT_PEER);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  return s_ok ? epoch : 0u;   // 0: a peer never arrived; the status word says so and the caller skips its work
+}
+__device__ __forceinline__ void barrier_tail(const HeadBarrier& hb, uint32_t epoch) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(hb.state + 1, 1u) == gridDim.x - 1) {
+      hb.state[1] = 0;
+      // on a give-up the epoch still advances, so that the next use does not wait for this one's flags
+      uint32_t d;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(d) : "l"(hb.state) : "memory");
+      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(hb.state), "r"(epoch ? epoch : d + 1) : "memory");
+    }
+  }
+}
 // Second half of the tensor-parallel all-reduce. This rank owns columns [c0, c0 + cols) of the reduced accumulator: add
 // bias and residual there, round to bf16, write the slice into EVERY rank's copy of the residual stream together with the
 // slice's sum of squares per row, clear the accumulator slice. One CTA per row.
 __global__ void __launch_bounds__(256) tp_slice_finish_push_kernel(float* __restrict__ acc, int ld_acc, const __nv_bfloat16* __restrict__ bias,
                                                                    const __nv_bfloat16* __restrict__ residual, int ld_res, SlicePeers peers,
-                                                                   int ld_x, int W, int rank, int c0, int cols, int M) {
+                                                                   int ld_x, int W, int rank, int c0, int cols, int M, HeadBarrier hb) {
   const int m = blockIdx.x;
+  uint32_t epoch = 1;
+  if (hb.state != nullptr) {  // every rank's GEMM has added its partial sums into this rank's accumulator slice
+    epoch = barrier_head(hb, W, rank);
+    if (epoch == 0) {
+      barrier_tail(hb, 0);
+      return;
+    }
+  }
   float ss = 0.f;
   for (int c = threadIdx.x * 4; c < cols; c += blockDim.x * 4) {
     const int n = c0 + c;
@@ -813,12 +882,21 @@ __global__ void __launch_bounds__(256) tp_slice_finish_push_kernel(float* __rest
     for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += red[w];
     for (int k = 0; k < W; ++k) peers.sumsq[(rank + k) % W][rank * M + m] = t;
   }
+  if (hb.state != nullptr) barrier_tail(hb, epoch);
 }
 // h[m, :] = x[m, :] * rsqrt(sum_r sumsq[r][m] / N + eps) * w   (rows of the gathered residual stream)
 __global__ void __launch_bounds__(256) tp_norm_apply_kernel(const __nv_bfloat16* __restrict__ x, int ld_x, const float* __restrict__ sumsq, int W,
                                                             int M, const __nv_bfloat16* __restrict__ w, float eps, __nv_bfloat16* __restrict__ h,
-                                                            int ld_h, int N) {
+                                                            int ld_h, int N, int rank, HeadBarrier hb) {
   const int m = blockIdx.x;
+  uint32_t epoch = 1;
+  if (hb.state != nullptr) {  // every rank's slice and sums of squares have landed in this rank's copy
+    epoch = barrier_head(hb, W, rank);
+    if (epoch == 0) {
+      barrier_tail(hb, 0);
+      return;
+    }
+  }
   float t = 0.f;
   for (int r = 0; r < W; ++r) t += sumsq[r * M + m];
   const float rs = rsqrtf(t / (float)N + eps);
@@ -834,11 +912,23 @@ __global__ void __launch_bounds__(256) tp_norm_apply_kernel(const __nv_bfloat16*
     o.y = pack_bf16x2(a1.x * rs * g1.x, a1.y * rs * g1.y);
     *reinterpret_cast<uint2*>(h + (size_t)m * ld_h + c) = o;
   }
+  if (hb.state != nullptr) barrier_tail(hb, epoch);
 }
 }  // namespace inv
 
+// peer_flags / local_flags / state (all three, or none): the kernel starts with a barrier over that flag set (see HeadBarrier)
+static HeadBarrier make_head_barrier(const uint64_t* peer_flags, void* local_flags, void* state, int W, int* status) {
+  HeadBarrier hb;
+  for (int r = 0; r < 8; ++r) hb.peer_flags[r] = peer_flags ? reinterpret_cast<uint32_t*>(peer_flags[r < W ? r : 0]) : nullptr;
+  hb.local_flags = reinterpret_cast<const uint32_t*>(local_flags);
+  hb.state = (peer_flags && local_flags) ? reinterpret_cast<uint32_t*>(state) : nullptr;
+  hb.status = status;
+  return hb;
+}
+
 extern "C" int inv_tp_slice_finish_push(float* acc, int ld_acc, const void* bias, const void* residual, int ld_res, const uint64_t* peer_x,
-                                        const uint64_t* peer_sumsq, int ld_x, int W, int rank, int c0, int cols, int M, void* stream) {
+                                        const uint64_t* peer_sumsq, int ld_x, int W, int rank, int c0, int cols, int M,
+                                        const uint64_t* peer_flags, void* local_flags, void* barrier_state, int* status, void* stream) {
   if (W < 1 || W > 8 || rank < 0 || rank >= W || (cols % 4) || (c0 % 4) || (ld_acc % 4) || (ld_res % 4) || (ld_x % 4) || M < 1) return -ERR_BAD_ARG;
   SlicePeers sp;
   for (int r = 0; r < 8; ++r) {
@@ -846,16 +936,18 @@ extern "C" int inv_tp_slice_finish_push(float* acc, int ld_acc, const void* bias
     sp.sumsq[r] = reinterpret_cast<float*>(peer_sumsq[r < W ? r : 0]);
   }
   tp_slice_finish_push_kernel<<<(unsigned)M, 256, 0, (cudaStream_t)stream>>>(acc, ld_acc, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)residual,
-                                                                             ld_res, sp, ld_x, W, rank, c0, cols, M);
+                                                                             ld_res, sp, ld_x, W, rank, c0, cols, M,
+                                                                             make_head_barrier(peer_flags, local_flags, barrier_state, W, status));
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }
 
 extern "C" int inv_tp_norm_apply(const void* x, int ld_x, const float* sumsq, int W, int M, const void* w, float eps, void* h, int ld_h, int N,
-                                 void* stream) {
-  if ((N % 4) || (ld_x % 4) || (ld_h % 4) || M < 1) return -ERR_BAD_ARG;
+                                 int rank, const uint64_t* peer_flags, void* local_flags, void* barrier_state, int* status, void* stream) {
+  if ((N % 4) || (ld_x % 4) || (ld_h % 4) || M < 1 || W < 1 || W > 8) return -ERR_BAD_ARG;
   tp_norm_apply_kernel<<<(unsigned)M, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ld_x, sumsq, W, M, (const __nv_bfloat16*)w, eps,
-                                                                      (__nv_bfloat16*)h, ld_h, N);
+                                                                      (__nv_bfloat16*)h, ld_h, N, rank,
+                                                                      make_head_barrier(peer_flags, local_flags, barrier_state, W, status));
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }

@@ -29,9 +29,9 @@ _native.register_cuda_sigs({
     "inv_oil_gemm_rs": [_native.vp, _native.i32, _native.vp, _native.vp, _native.vp, _native.i32, _native.vp, _native.i32, _native.i32, _native.i32,
                         _native.i32, _native.i32, _native.i32, _native.vp, _native.vp],
     "inv_tp_slice_finish_push": [_native.vp, _native.i32, _native.vp, _native.vp, _native.i32, _native.vp, _native.vp, _native.i32, _native.i32,
-                                 _native.i32, _native.i32, _native.i32, _native.i32, _native.vp],
+                                 _native.i32, _native.i32, _native.i32, _native.i32, _native.vp, _native.vp, _native.vp, _native.vp, _native.vp],
     "inv_tp_norm_apply": [_native.vp, _native.i32, _native.vp, _native.i32, _native.i32, _native.vp, _native.f32, _native.vp, _native.i32, _native.i32,
-                          _native.vp],
+                          _native.i32, _native.vp, _native.vp, _native.vp, _native.vp, _native.vp],
     "inv_oil_gemm_finish_swiglu": [_native.vp, _native.vp, _native.vp, _native.i64, _native.i32, _native.i32, _native.i32, _native.vp],
     "inv_oil_gemm_finish_norm": [_native.vp, _native.vp, _native.vp, _native.vp, _native.vp, _native.f32, _native.vp, _native.i64, _native.i32,
                                  _native.i32, _native.i32, _native.i32, _native.i32, _native.vp],

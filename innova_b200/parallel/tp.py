@@ -39,8 +39,9 @@ class TPContext:
         self.rank = dist.get_rank(self.group)
         self.max_tokens, self.max_n = max_tokens, max_n
         self.bufs = [SymmBuffer(max_tokens * max_n, torch.float32, self.group, device) for _ in range(2)]
-        self.flags = PeerFlags(n_sets=2, group=self.group)
-        self.counter = torch.zeros(2, dtype=torch.int32, device=self.bufs[0].tensor.device)
+        self.flags = PeerFlags(n_sets=4, group=self.group)        # 0: stand-alone barrier; 1, 2: barriers at the head of the two
+        self.counter = torch.zeros(2, dtype=torch.int32, device=self.bufs[0].tensor.device)   # finish kernels of the reduce-scatter form
+        self.head_state = torch.zeros(8, dtype=torch.int32, device=self.bufs[0].tensor.device)  # {done epoch, tickets} per flag set
         self.turn = 0
         self.multimem = all(b.multicast_ptr != 0 for b in self.bufs)
         # reduce-scatter form of the all-reduce (no multicast object): every rank's copy of the residual stream and of the
@@ -100,16 +101,18 @@ def tp_reduce_linear(x: torch.Tensor, qw: QuantWeight, ctx: Optional[TPContext],
         oc = n_total // W
         rt.check(lib.inv_oil_gemm_rs(x2.data_ptr(), x2.stride(0), qw.idx.data_ptr(), qw.scales.data_ptr(), qw.codebook.data_ptr(), qw.bits,
                                      buf.peers(), W, oc, n_total, M, qw.N, qw.K, status, st), "inv_oil_gemm_rs")
-        ctx.barrier()
+        # both barriers sit at the head of the kernel that needs them (flag sets 1 and 2): no launches of their own
         xb, sq = ctx.next_xbuf()
         res2 = residual.reshape(M, n_total)
+        f, hs = ctx.flags, ctx.head_state.data_ptr()
         rt.check(lib.inv_tp_slice_finish_push(buf.tensor.data_ptr(), n_total, rt.ptr(qw.bias), res2.data_ptr(), res2.stride(0), xb.peers(),
-                                              sq.peers(), n_total, W, ctx.rank, ctx.rank * oc, oc, M, st), "inv_tp_slice_finish_push")
-        ctx.barrier()
+                                              sq.peers(), n_total, W, ctx.rank, ctx.rank * oc, oc, M, f.set_ptrs(1), f.set_ptr_local(1),
+                                              hs + 8, status, st), "inv_tp_slice_finish_push")
         x_out = xb.tensor[: M * n_total].view(M, n_total)      # lives until the call after next overwrites this buffer
         h_out = torch.empty((M, n_total), dtype=torch.bfloat16, device=x.device)
         rt.check(lib.inv_tp_norm_apply(x_out.data_ptr(), n_total, sq.tensor.data_ptr(), W, M, norm[0].data_ptr(), float(norm[1]),
-                                       h_out.data_ptr(), n_total, n_total, st), "inv_tp_norm_apply")
+                                       h_out.data_ptr(), n_total, n_total, ctx.rank, f.set_ptrs(2), f.set_ptr_local(2), hs + 16, status, st),
+                 "inv_tp_norm_apply")
         return x_out, h_out
     if ctx.multimem:
         rt.check(lib.inv_oil_gemm(x2.data_ptr(), x2.stride(0), qw.idx.data_ptr(), qw.scales.data_ptr(), qw.codebook.data_ptr(), qw.bits,
