@@ -580,15 +580,85 @@ __global__ void oil_gemm_finish_swiglu_kernel(float* __restrict__ acc, const __n
   }
 }
 
+// A barrier over peer flags at the head of a multi-CTA kernel, so that the barrier costs no launch of its own.
+// `state` = {done, tickets} in this rank's memory: `done` is the epoch of the last completed use and is only written by
+// the last CTA of a launch, so every CTA of the next launch reads the same value and derives the same epoch. CTA 0 raises
+// this rank's word in every peer's flag set (everything this rank issued before the launch is complete: kernel boundary);
+// every CTA waits, for at most a second, until all words of the local set have reached the epoch. `barrier_tail` is called
+// by every CTA when it is done.
+struct HeadBarrier {
+  uint32_t* peer_flags[8];
+  const uint32_t* local_flags;
+  uint32_t* state;
+  int* status;
+};
+__device__ __forceinline__ uint32_t barrier_head(const HeadBarrier& hb, int W, int rank) {
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    uint32_t d;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(d) : "l"(hb.state) : "memory");
+    s_epoch = d + 1;
+    s_ok = 1;
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  if (blockIdx.x == 0 && threadIdx.x < W) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(hb.peer_flags[threadIdx.x] + rank), "r"(epoch) : "memory");
+  }
+  if (threadIdx.x < W) {
+    uint64_t t0 = 0;
+    uint32_t spins = 0, v;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(hb.local_flags + threadIdx.x) : "memory");
+      if ((int32_t)(v - epoch) >= 0) break;
+      if ((++spins & 0xffu) == 0) {
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) {
+          t0 = now;
+        } else if (now - t0 > 1000000000ull) {
+          s_ok = 0;
+          if (hb.status) atomicCAS(hb.status, 0, (int)ERR_WAIT_PEER);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  return s_ok ? epoch : 0u;   // 0: a peer never arrived; the status word says so and the caller skips its work
+}
+__device__ __forceinline__ void barrier_tail(const HeadBarrier& hb, uint32_t epoch) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(hb.state + 1, 1u) == gridDim.x - 1) {
+      hb.state[1] = 0;
+      // on a give-up the epoch still advances, so that the next use does not wait for this one's flags
+      uint32_t d;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(d) : "l"(hb.state) : "memory");
+      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(hb.state), "r"(epoch ? epoch : d + 1) : "memory");
+    }
+  }
+}
 // x[m, :] = bf16(acc[m, :] + bias + residual[m, :]);  h[m, :] = bf16(rms_norm(x[m, :]) * w): the finish of a
 // row-parallel projection with the next block's RMSNorm. One CTA of 256 threads per token; N % 4 == 0, N <= 16384.
 __global__ void __launch_bounds__(256) oil_gemm_finish_norm_kernel(float* __restrict__ acc, const __nv_bfloat16* __restrict__ bias,
                                                                    const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ x_out,
                                                                    const __nv_bfloat16* __restrict__ w, float eps, __nv_bfloat16* __restrict__ h_out,
-                                                                   int N, int ld_acc, int ld_x, int ld_res, int ld_h) {
+                                                                   int N, int ld_acc, int ld_x, int ld_res, int ld_h, int W, int rank,
+                                                                   HeadBarrier hb) {
   constexpr int MAXV = 16;  // float4 groups per thread: 256 * 16 * 4 = 16384 columns
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const long m = blockIdx.x;
+  uint32_t epoch = 1;
+  if (hb.state != nullptr) {  // tensor parallel: every rank's GEMM has added its partial sums into this rank's accumulator
+    epoch = barrier_head(hb, W, rank);
+    if (epoch == 0) {
+      barrier_tail(hb, 0);
+      return;
+    }
+  }
   __shared__ float red[8];
   float4 xs[MAXV];
   float ss = 0.f;
@@ -636,11 +706,23 @@ __global__ void __launch_bounds__(256) oil_gemm_finish_norm_kernel(float* __rest
       *reinterpret_cast<uint2*>(h_out + m * ld_h + n) = make_uint2(pack_bf16x2(r0, r1), pack_bf16x2(r2, r3));
     }
   }
+  if (hb.state != nullptr) barrier_tail(hb, epoch);
 }
 
 }  // namespace inv
 
 using namespace inv;
+
+// peer_flags / local_flags / state (all three, or none): the kernel starts with a barrier over that flag set (see HeadBarrier)
+static HeadBarrier make_head_barrier(const uint64_t* peer_flags, void* local_flags, void* state, int W, int* status) {
+  HeadBarrier hb;
+  for (int r = 0; r < 8; ++r) hb.peer_flags[r] = peer_flags ? reinterpret_cast<uint32_t*>(peer_flags[r < W ? r : 0]) : nullptr;
+  hb.local_flags = reinterpret_cast<const uint32_t*>(local_flags);
+  hb.state = (peer_flags && local_flags) ? reinterpret_cast<uint32_t*>(state) : nullptr;
+  hb.status = status;
+  return hb;
+}
+
 
 static int oil_gemm_launch(const void* x, int ldx, const void* idx, const void* scales, const float* codebook, int bits, float* acc, int ldo,
                            int M, int N, int K, int* status, cudaStream_t st, int multimem, const uint64_t* peers = nullptr, int n_peers = 0,
@@ -767,67 +849,6 @@ struct SlicePeers {
   __nv_bfloat16* x[8];   // every rank's copy of the [M, N] residual stream
   float* sumsq[8];       // every rank's [W, M] partial sums of squares
 };
-// A barrier over peer flags at the head of a multi-CTA kernel, so that the barrier costs no launch of its own.
-// `state` = {done, tickets} in this rank's memory: `done` is the epoch of the last completed use and is only written by
-// the last CTA of a launch, so every CTA of the next launch reads the same value and derives the same epoch. CTA 0 raises
-// this rank's word in every peer's flag set (everything this rank issued before the launch is complete: kernel boundary);
-// every CTA waits, for at most a second, until all words of the local set have reached the epoch. `barrier_tail` is called
-// by every CTA when it is done.
-struct HeadBarrier {
-  uint32_t* peer_flags[8];
-  const uint32_t* local_flags;
-  uint32_t* state;
-  int* status;
-};
-__device__ __forceinline__ uint32_t barrier_head(const HeadBarrier& hb, int W, int rank) {
-  __shared__ uint32_t s_epoch;
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) {
-    uint32_t d;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(d) : "l"(hb.state) : "memory");
-    s_epoch = d + 1;
-    s_ok = 1;
-  }
-  __syncthreads();
-  const uint32_t epoch = s_epoch;
-  if (blockIdx.x == 0 && threadIdx.x < W) {
-    __threadfence_system();
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(hb.peer_flags[threadIdx.x] + rank), "r"(epoch) : "memory");
-  }
-  if (threadIdx.x < W) {
-    uint64_t t0 = 0;
-    uint32_t spins = 0, v;
-    while (true) {
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(hb.local_flags + threadIdx.x) : "memory");
-      if ((int32_t)(v - epoch) >= 0) break;
-      if ((++spins & 0xffu) == 0) {
-        const uint64_t now = globaltimer_ns();
-        if (t0 == 0) {
-          t0 = now;
-        } else if (now - t0 > 1000000000ull) {
-          s_ok = 0;
-          if (hb.status) atomicCAS(hb.status, 0, (int)ERR_WAIT_PEER);
-          break;
-        }
-      }
-    }
-  }
-  __syncthreads();
-  return s_ok ? epoch : 0u;   // 0: a peer never arrived; the status word says so and the caller skips its work
-}
-__device__ __forceinline__ void barrier_tail(const HeadBarrier& hb, uint32_t epoch) {
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    if (atomicAdd(hb.state + 1, 1u) == gridDim.x - 1) {
-      hb.state[1] = 0;
-      // on a give-up the epoch still advances, so that the next use does not wait for this one's flags
-      uint32_t d;
-      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(d) : "l"(hb.state) : "memory");
-      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(hb.state), "r"(epoch ? epoch : d + 1) : "memory");
-    }
-  }
-}
 // Second half of the tensor-parallel all-reduce. This rank owns columns [c0, c0 + cols) of the reduced accumulator: add
 // bias and residual there, round to bf16, write the slice into EVERY rank's copy of the residual stream together with the
 // slice's sum of squares per row, clear the accumulator slice. One CTA per row.
@@ -916,16 +937,6 @@ __global__ void __launch_bounds__(256) tp_norm_apply_kernel(const __nv_bfloat16*
 }
 }  // namespace inv
 
-// peer_flags / local_flags / state (all three, or none): the kernel starts with a barrier over that flag set (see HeadBarrier)
-static HeadBarrier make_head_barrier(const uint64_t* peer_flags, void* local_flags, void* state, int W, int* status) {
-  HeadBarrier hb;
-  for (int r = 0; r < 8; ++r) hb.peer_flags[r] = peer_flags ? reinterpret_cast<uint32_t*>(peer_flags[r < W ? r : 0]) : nullptr;
-  hb.local_flags = reinterpret_cast<const uint32_t*>(local_flags);
-  hb.state = (peer_flags && local_flags) ? reinterpret_cast<uint32_t*>(state) : nullptr;
-  hb.status = status;
-  return hb;
-}
-
 extern "C" int inv_tp_slice_finish_push(float* acc, int ld_acc, const void* bias, const void* residual, int ld_res, const uint64_t* peer_x,
                                         const uint64_t* peer_sumsq, int ld_x, int W, int rank, int c0, int cols, int M,
                                         const uint64_t* peer_flags, void* local_flags, void* barrier_state, int* status, void* stream) {
@@ -988,7 +999,26 @@ extern "C" int inv_oil_gemm_finish_norm(float* acc, const void* bias, const void
     return -ERR_BAD_ARG;
   oil_gemm_finish_norm_kernel<<<(unsigned)M, 256, 0, (cudaStream_t)stream>>>(acc, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)residual,
                                                                               (__nv_bfloat16*)x_out, (const __nv_bfloat16*)norm_w, eps,
-                                                                              (__nv_bfloat16*)h_out, N, ld_acc, ld_x, ld_res, ld_h);
+                                                                              (__nv_bfloat16*)h_out, N, ld_acc, ld_x, ld_res, ld_h, 1, 0,
+                                                                              make_head_barrier(nullptr, nullptr, nullptr, 1, nullptr));
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+// The same as the closing pass of a tensor-parallel all-reduce: the kernel starts with a barrier over the ranks' flag set
+// (every rank's GEMM epilogue has added its partial sums into this rank's accumulator), see HeadBarrier.
+extern "C" int inv_oil_gemm_finish_norm_tp(float* acc, const void* bias, const void* residual, void* x_out, const void* norm_w, float eps,
+                                           void* h_out, long M, int N, int ld_acc, int ld_x, int ld_res, int ld_h, int W, int rank,
+                                           const uint64_t* peer_flags, void* local_flags, void* barrier_state, int* status, void* stream) {
+  if (M <= 0) return 0;
+  if ((N % 4) || N > 16384 || (ld_acc % 4) || (ld_x % 4) || (ld_res % 4) || (ld_h % 4) || ((uintptr_t)acc % 16) || ((uintptr_t)x_out % 8) ||
+      ((uintptr_t)h_out % 8) || ((uintptr_t)bias % 8) || ((uintptr_t)residual % 8) || ((uintptr_t)norm_w % 8) || W < 1 || W > 8 ||
+      peer_flags == nullptr || local_flags == nullptr || barrier_state == nullptr)
+    return -ERR_BAD_ARG;
+  oil_gemm_finish_norm_kernel<<<(unsigned)M, 256, 0, (cudaStream_t)stream>>>(acc, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)residual,
+                                                                              (__nv_bfloat16*)x_out, (const __nv_bfloat16*)norm_w, eps,
+                                                                              (__nv_bfloat16*)h_out, N, ld_acc, ld_x, ld_res, ld_h, W, rank,
+                                                                              make_head_barrier(peer_flags, local_flags, barrier_state, W, status));
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }

@@ -35,6 +35,9 @@ _native.register_cuda_sigs({
     "inv_oil_gemm_finish_swiglu": [_native.vp, _native.vp, _native.vp, _native.i64, _native.i32, _native.i32, _native.i32, _native.vp],
     "inv_oil_gemm_finish_norm": [_native.vp, _native.vp, _native.vp, _native.vp, _native.vp, _native.f32, _native.vp, _native.i64, _native.i32,
                                  _native.i32, _native.i32, _native.i32, _native.i32, _native.vp],
+    "inv_oil_gemm_finish_norm_tp": [_native.vp, _native.vp, _native.vp, _native.vp, _native.vp, _native.f32, _native.vp, _native.i64, _native.i32,
+                                    _native.i32, _native.i32, _native.i32, _native.i32, _native.i32, _native.i32, _native.vp, _native.vp,
+                                    _native.vp, _native.vp, _native.vp],
 })
 
 
@@ -159,10 +162,19 @@ def oil_linear_swiglu(x: torch.Tensor, qw: QuantWeight) -> torch.Tensor:
     return out.view(*shp[:-1], Fh)
 
 
-def finish_norm(acc: torch.Tensor, M: int, N: int, bias, residual, norm_w: torch.Tensor, eps: float):
-    """(x, h) from an fp32 accumulator [>= M, N]: x = bf16(acc + bias + residual), h = rms_norm(x) * norm_w. Clears acc."""
+def finish_norm(acc: torch.Tensor, M: int, N: int, bias, residual, norm_w: torch.Tensor, eps: float, barrier=None):
+    """(x, h) from an fp32 accumulator [>= M, N]: x = bf16(acc + bias + residual), h = rms_norm(x) * norm_w. Clears acc.
+    ``barrier = (world, rank, peer flag pointers, local flag pointer, state pointer)``: the kernel starts with a barrier over
+    the ranks (the closing pass of a tensor-parallel all-reduce), which then needs no launch of its own."""
     x_out = torch.empty((M, N), dtype=torch.bfloat16, device=acc.device)
     h_out = torch.empty((M, N), dtype=torch.bfloat16, device=acc.device)
+    if barrier is not None:
+        W, rank, peer_flags, local_flags, state = barrier
+        rt.check(rt.lib().inv_oil_gemm_finish_norm_tp(acc.data_ptr(), rt.ptr(bias), rt.ptr(residual), x_out.data_ptr(), norm_w.data_ptr(), float(eps),
+                                                      h_out.data_ptr(), M, N, acc.stride(0) if acc.dim() == 2 else N, N,
+                                                      0 if residual is None else residual.stride(0), N, W, rank, peer_flags, local_flags, state,
+                                                      rt.status_tensor(acc.device).data_ptr(), rt.stream_ptr()), "inv_oil_gemm_finish_norm_tp")
+        return x_out, h_out
     rt.check(rt.lib().inv_oil_gemm_finish_norm(acc.data_ptr(), rt.ptr(bias), rt.ptr(residual), x_out.data_ptr(), norm_w.data_ptr(), float(eps),
                                                h_out.data_ptr(), M, N, acc.stride(0) if acc.dim() == 2 else N, N,
                                                0 if residual is None else residual.stride(0), N, rt.stream_ptr()), "inv_oil_gemm_finish_norm")

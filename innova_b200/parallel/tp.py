@@ -123,13 +123,18 @@ def tp_reduce_linear(x: torch.Tensor, qw: QuantWeight, ctx: Optional[TPContext],
         peers = ptr_array([buf.peer_ptrs[(ctx.rank + k) % ctx.world] + n_offset * 4 for k in range(ctx.world)])
         rt.check(lib.inv_oil_gemm_peers(x2.data_ptr(), x2.stride(0), qw.idx.data_ptr(), qw.scales.data_ptr(), qw.codebook.data_ptr(), qw.bits,
                                         peers, ctx.world, n_total, M, qw.N, qw.K, status, st), "inv_oil_gemm_peers")
-    ctx.barrier()
     acc = buf.tensor
+    res2 = None if residual is None else residual.reshape(M, n_total)
+    if norm is not None and not out_fp32 and n_total % 4 == 0 and n_total <= 16384:
+        # the barrier sits at the head of the finish kernel (flag set 3)
+        f = ctx.flags
+        return finish_norm(acc[: M * n_total].view(M, n_total), M, n_total, qw.bias, res2, norm[0], norm[1],
+                           barrier=(W, ctx.rank, f.set_ptrs(3), f.set_ptr_local(3), ctx.head_state.data_ptr() + 24))
+    ctx.barrier()
     if out_fp32:
         y = acc[: M * n_total].view(M, n_total).clone()
         acc[: M * n_total].zero_()
         return y
-    res2 = None if residual is None else residual.reshape(M, n_total)
     if norm is not None:
         return finish_norm(acc[: M * n_total].view(M, n_total), M, n_total, qw.bias, res2, norm[0], norm[1])
     out = torch.empty((M, n_total), dtype=torch.bfloat16, device=x.device)
