@@ -40,3 +40,21 @@ def test_trainer_reads_the_status_word_when_it_logs_and_before_it_saves(tmp_path
     assert not (tmp_path / "m.oil").exists()
     tr.save_checkpoint(str(tmp_path / "m.oil"))
     assert (tmp_path / "m.oil").exists()
+
+
+def test_colsum_slot_is_single_use_and_matches_only_the_same_tensor():
+    """The norm backward's column sums reach only the very next linear backward, and only for the very same gradient tensor."""
+    import torch
+    from innova_b200.ops import runtime as rt
+    dx = torch.randn(6, 4)
+    cs = dx.sum(0)
+    rt.offer_colsum(dx, cs)
+    assert rt.take_colsum(dx.view(6, 4)) is cs          # same storage, shape and version
+    assert rt.take_colsum(dx) is None                   # the slot is cleared by the first taker
+    rt.offer_colsum(dx, cs)
+    assert rt.take_colsum(torch.randn(6, 4)) is None and rt.take_colsum(dx) is None     # a different tensor clears it too
+    rt.offer_colsum(dx, cs)
+    dx.mul_(2.0)                                        # modified in place since the offer: the sums are stale
+    assert rt.take_colsum(dx) is None
+    rt.offer_colsum(dx, cs)
+    assert rt.take_colsum(dx.view(4, 6)) is None        # same memory, other shape
