@@ -590,3 +590,31 @@ class InferenceEngine:
 
     def generate_batch(self, prompts: Sequence[str], max_new_tokens: int = 64, sampling: Optional[SamplingParams] = None) -> List[str]:
         return [self.generate(p, max_new_tokens, sampling) for p in prompts]
+
+
+class SentenceEmbedder(torch.nn.Module):
+    """Mean pooling of token embeddings followed by a linear projection to ``output_size`` and L2 normalisation
+    (include/oil/embeddings.h:6-20). ``forward`` takes [S, hidden] or [B, S, hidden] (optionally with a [B, S] mask)."""
+
+    def __init__(self, hidden_size: int, output_size: int, dtype=torch.float32, device=None, seed: int = 0):
+        super().__init__()
+        g = torch.Generator().manual_seed(seed)
+        w = torch.randn(output_size, hidden_size, generator=g) * hidden_size ** -0.5
+        self.projection = torch.nn.Parameter(w.to(device=device, dtype=dtype))
+        self.hidden_size_, self.output_size_ = hidden_size, output_size
+
+    def hidden_size(self) -> int:
+        return self.hidden_size_
+
+    def output_size(self) -> int:
+        return self.output_size_
+
+    def forward(self, token_embeddings: torch.Tensor, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+        x = token_embeddings if token_embeddings.dim() == 3 else token_embeddings.unsqueeze(0)
+        if mask is not None:
+            m = mask.to(x.dtype).unsqueeze(-1)
+            pooled = (x * m).sum(1) / m.sum(1).clamp_min(1.0)
+        else:
+            pooled = x.mean(1)
+        out = F.normalize(pooled.float() @ self.projection.float().t(), dim=-1).to(x.dtype)
+        return out if token_embeddings.dim() == 3 else out[0]

@@ -680,3 +680,183 @@ class WandBLogger:
     def close(self):
         self.flush()
         self._f.close()
+
+
+# ------------------------------------------------------------------------------------------------ more of training_utils.h
+class MetricTracker:
+    """Exponential running average of a metric and its best raw value (include/oil/training_utils.h:139-153). ``improved`` says
+    whether the running average is now better than the best single value seen (always true for the first update)."""
+
+    def __init__(self, alpha: float = 0.9, minimize: bool = True):
+        self.alpha, self.minimize = alpha, minimize
+        self.reset()
+
+    def reset(self):
+        self.running_avg = 0.0
+        self.best = 1e10 if self.minimize else -1e10
+        self.steps = 0
+
+    def update(self, value: float):
+        self.running_avg = value if self.steps == 0 else self.alpha * self.running_avg + (1.0 - self.alpha) * value
+        if self.steps == 0 or (value < self.best if self.minimize else value > self.best):
+            self.best = value
+        self.steps += 1
+
+    def value(self) -> float:
+        return self.running_avg
+
+    def improved(self) -> bool:
+        if self.steps <= 1:
+            return True
+        return self.running_avg < self.best if self.minimize else self.running_avg > self.best
+
+
+class LearningRateWarmup:
+    """target_lr * step / warmup (LINEAR) or target_lr * (1 - e^(-5 p)) / (1 - e^-5) (EXPONENTIAL) until ``warmup_steps``
+    (src/training_utils.cpp:603-613)."""
+    LINEAR, EXPONENTIAL = 0, 1
+
+    def __init__(self, target_lr: float, warmup_steps: int, mode: int = 0):
+        self.target_lr, self.warmup_steps, self.mode = target_lr, warmup_steps, mode
+
+    def get_lr(self, step: int) -> float:
+        if step >= self.warmup_steps or self.warmup_steps <= 0:
+            return self.target_lr
+        p = step / self.warmup_steps
+        if self.mode == self.LINEAR:
+            return self.target_lr * p
+        return self.target_lr * (1.0 - math.exp(-5.0 * p)) / (1.0 - math.exp(-5.0))
+
+
+class MixedPrecisionManager:
+    """fp32 master copies of low-precision parameters plus dynamic loss scaling (include/oil/training_utils.h:56-99): the
+    optimizer updates the master weights, ``sync_weights_to_model`` rounds them into the model's parameters; gradients are
+    checked for overflow, unscaled, and the scale grows by ``growth_factor`` after ``growth_interval`` clean steps and backs
+    off on overflow. bf16 training on B200 needs no scaling (``enabled=False`` makes every call a pass-through); the class
+    serves fp16 fine-tuning and parity with the reference."""
+
+    def __init__(self, enabled: bool = True, init_loss_scale: float = 65536.0, growth_factor: float = 2.0, backoff_factor: float = 0.5,
+                 growth_interval: int = 2000):
+        self.enabled = enabled
+        self.init_loss_scale, self.growth_factor, self.backoff_factor, self.growth_interval = init_loss_scale, growth_factor, backoff_factor, growth_interval
+        self.master_weights: List[torch.Tensor] = []
+        self.reset()
+
+    def reset(self):
+        self.loss_scale = self.init_loss_scale if self.enabled else 1.0
+        self.good_steps = 0
+
+    @staticmethod
+    def to_fp16(t: torch.Tensor) -> torch.Tensor:
+        return t.to(torch.float16)
+
+    @staticmethod
+    def to_fp32(t: torch.Tensor) -> torch.Tensor:
+        return t.to(torch.float32)
+
+    def is_enabled(self) -> bool:
+        return self.enabled
+
+    def current_loss_scale(self) -> float:
+        return self.loss_scale
+
+    def create_master_weights(self, params):
+        self.master_weights = [p.detach().float().clone() for p in params]
+
+    @torch.no_grad()
+    def sync_weights_to_model(self, params):
+        for p, m in zip(params, self.master_weights):
+            p.copy_(m.to(p.dtype))
+
+    @torch.no_grad()
+    def sync_weights_from_model(self, params):
+        for p, m in zip(params, self.master_weights):
+            m.copy_(p.detach().float())
+
+    def scale_loss(self, loss: torch.Tensor) -> torch.Tensor:
+        return loss * self.loss_scale if self.enabled else loss
+
+    @staticmethod
+    def check_gradients(params) -> bool:
+        """True when every gradient is finite."""
+        return all(p.grad is None or bool(torch.isfinite(p.grad).all()) for p in params)
+
+    @torch.no_grad()
+    def unscale_gradients(self, params):
+        if self.enabled and self.loss_scale != 1.0:
+            for p in params:
+                if p.grad is not None:
+                    p.grad.mul_(1.0 / self.loss_scale)
+
+    @torch.no_grad()
+    def cast_gradients_to_fp32(self, params) -> List[Optional[torch.Tensor]]:
+        return [None if p.grad is None else p.grad.float() for p in params]
+
+    def update_loss_scale(self, has_overflow: bool):
+        if not self.enabled:
+            return
+        if has_overflow:
+            self.loss_scale = max(1.0, self.loss_scale * self.backoff_factor)
+            self.good_steps = 0
+        else:
+            self.good_steps += 1
+            if self.good_steps >= self.growth_interval:
+                self.loss_scale *= self.growth_factor
+                self.good_steps = 0
+
+
+class ModelSnapshot:
+    """Optimizer moments, step and learning rate in the reference's ``<path>.snap`` layout (src/training_utils.cpp:494-570):
+    int32 step, fp32 lr, int32 parameter count, then per parameter: int64 size of m, its fp32 values, int64 size of v, its
+    values. ``opt`` is a ``torch.optim`` optimizer with ``exp_avg`` / ``exp_avg_sq`` state (AdamW and relatives); a file
+    written by the reference loads here and the other way round."""
+
+    def __init__(self, path: str = "snapshot"):
+        self.path = path
+
+    def save(self, opt, step: int, current_lr: float, params):
+        import struct
+        with open(self.path + ".snap", "wb") as f:
+            params = list(params)
+            f.write(struct.pack("<ifi", int(step), float(current_lr), len(params)))
+            for p in params:
+                st = opt.state.get(p, {}) if opt is not None else {}
+                for key in ("exp_avg", "exp_avg_sq"):
+                    t = st.get(key)
+                    if t is None:
+                        f.write(struct.pack("<q", 0))
+                    else:
+                        flat = t.detach().float().reshape(-1).cpu().contiguous()
+                        f.write(struct.pack("<q", flat.numel()))
+                        f.write(flat.numpy().tobytes())
+
+    def load(self, opt, params):
+        """-> (step, lr) or None when there is no readable snapshot; moments whose size fits the parameter are restored."""
+        import struct
+        try:
+            f = open(self.path + ".snap", "rb")
+        except OSError:
+            return None
+        with f:
+            head = f.read(12)
+            if len(head) < 12:
+                return None
+            step, lr, n = struct.unpack("<ifi", head)
+            for p in list(params)[: max(0, n)]:
+                for key in ("exp_avg", "exp_avg_sq"):
+                    raw = f.read(8)
+                    if len(raw) < 8:
+                        return step, lr
+                    (sz,) = struct.unpack("<q", raw)
+                    if sz <= 0:
+                        continue
+                    buf = f.read(4 * sz)
+                    if len(buf) < 4 * sz:
+                        return step, lr
+                    if opt is not None and sz <= p.numel():
+                        t = torch.zeros(p.numel(), dtype=torch.float32)
+                        t[:sz] = torch.frombuffer(bytearray(buf), dtype=torch.float32)
+                        st = opt.state.setdefault(p, {})
+                        st[key] = t.view(p.shape).to(p.device)
+                        st.setdefault("step", torch.tensor(float(step)))
+            return step, lr

@@ -1,0 +1,97 @@
+"""MetricTracker, LearningRateWarmup, MixedPrecisionManager, ModelSnapshot (wire layout) and SentenceEmbedder."""
+import math
+import struct
+
+import torch
+
+from innova_b200.inference.serving import SentenceEmbedder
+from innova_b200.training.utils import LearningRateWarmup, MetricTracker, MixedPrecisionManager, ModelSnapshot
+
+
+def test_metric_tracker_and_warmup():
+    t = MetricTracker(alpha=0.5, minimize=True)
+    assert t.improved() and t.steps == 0
+    t.update(4.0)
+    assert t.value() == 4.0 and t.best == 4.0 and t.improved()
+    t.update(2.0)
+    assert t.value() == 3.0 and t.best == 2.0 and not t.improved()            # the average (3.0) is not yet below the best value
+    t.update(0.5); t.update(0.5); t.update(0.5)
+    assert t.best == 0.5 and t.value() > 0.5 and t.steps == 5
+    hi = MetricTracker(0.0, minimize=False)
+    hi.update(1.0); hi.update(3.0)
+    assert hi.best == 3.0 and hi.value() == 3.0 and not hi.improved()
+    hi.reset()
+    assert hi.steps == 0 and hi.best == -1e10
+    w = LearningRateWarmup(1e-3, 100)
+    assert w.get_lr(0) == 0.0 and abs(w.get_lr(50) - 5e-4) < 1e-12 and w.get_lr(100) == 1e-3 and w.get_lr(1000) == 1e-3
+    e = LearningRateWarmup(1e-3, 100, LearningRateWarmup.EXPONENTIAL)
+    assert abs(e.get_lr(50) - 1e-3 * (1 - math.exp(-2.5)) / (1 - math.exp(-5))) < 1e-12 and e.get_lr(50) > w.get_lr(50)
+    assert LearningRateWarmup(2.0, 0).get_lr(0) == 2.0
+
+
+def test_mixed_precision_manager_scale_cycle():
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(8, 4).half()
+    params = list(lin.parameters())
+    mp = MixedPrecisionManager(init_loss_scale=1024.0, growth_interval=2)
+    mp.create_master_weights(params)
+    assert all(m.dtype == torch.float32 for m in mp.master_weights)
+    x = torch.randn(3, 8).half()
+    loss = lin(x).float().pow(2).mean()
+    mp.scale_loss(loss).backward()
+    g_scaled = params[0].grad.clone()
+    assert mp.check_gradients(params)
+    mp.unscale_gradients(params)
+    assert torch.allclose(params[0].grad.float() * 1024.0, g_scaled.float(), rtol=1e-2, atol=1e-3)
+    with torch.no_grad():
+        for m, g in zip(mp.master_weights, mp.cast_gradients_to_fp32(params)):
+            m.sub_(1e-4 * g)                                           # a step too small for fp16 to hold on its own
+    mp.sync_weights_to_model(params)
+    assert torch.equal(params[0], mp.master_weights[0].half())
+    mp.update_loss_scale(False); mp.update_loss_scale(False)
+    assert mp.current_loss_scale() == 2048.0
+    params[0].grad[0, 0] = float("inf")
+    assert not mp.check_gradients(params)
+    mp.update_loss_scale(True)
+    assert mp.current_loss_scale() == 1024.0 and mp.good_steps == 0
+    off = MixedPrecisionManager(enabled=False)
+    assert off.scale_loss(loss) is loss and off.current_loss_scale() == 1.0 and not off.is_enabled()
+    params[0].data.add_(1.0)
+    mp.sync_weights_from_model(params)
+    assert torch.equal(mp.master_weights[0], params[0].float())
+
+
+def test_model_snapshot_layout_round_trip(tmp_path):
+    torch.manual_seed(1)
+    model = torch.nn.Sequential(torch.nn.Linear(5, 3), torch.nn.Linear(3, 2))
+    params = list(model.parameters())
+    opt = torch.optim.AdamW(params, lr=1e-2)
+    model(torch.randn(4, 5)).sum().backward()
+    opt.step()
+    snap = ModelSnapshot(str(tmp_path / "run"))
+    snap.save(opt, 7, 0.125, params)
+    raw = open(str(tmp_path / "run.snap"), "rb").read()
+    step, lr, n = struct.unpack_from("<ifi", raw, 0)
+    (sz_m,) = struct.unpack_from("<q", raw, 12)
+    assert (step, lr, n, sz_m) == (7, 0.125, 4, 15) and len(raw) == 12 + sum(2 * (8 + 4 * p.numel()) for p in params)
+    first_m = torch.frombuffer(bytearray(raw[20:20 + 60]), dtype=torch.float32)
+    assert torch.equal(first_m, opt.state[params[0]]["exp_avg"].reshape(-1))
+    opt2 = torch.optim.AdamW(params, lr=1e-2)
+    assert snap.load(opt2, params) == (7, 0.125)
+    for p in params:
+        assert torch.equal(opt2.state[p]["exp_avg"], opt.state[p]["exp_avg"]) and torch.equal(opt2.state[p]["exp_avg_sq"], opt.state[p]["exp_avg_sq"])
+    assert ModelSnapshot(str(tmp_path / "none")).load(opt2, params) is None
+    snap.save(None, 3, 0.5, params)                                     # no optimizer: sizes of zero, as the reference writes
+    assert len(open(str(tmp_path / "run.snap"), "rb").read()) == 12 + 4 * 16 and snap.load(opt2, params) == (3, 0.5)
+
+
+def test_sentence_embedder_pools_projects_and_normalises():
+    emb = SentenceEmbedder(16, 6, seed=3)
+    x = torch.randn(2, 5, 16)
+    y = emb(x)
+    assert y.shape == (2, 6) and torch.allclose(y.norm(dim=-1), torch.ones(2), atol=1e-5) and emb.hidden_size() == 16 and emb.output_size() == 6
+    assert torch.allclose(emb(x[0]), y[0], atol=1e-6)
+    mask = torch.tensor([[1, 1, 0, 0, 0], [1, 1, 1, 1, 1]])
+    ym = emb(x, mask)
+    ref = torch.nn.functional.normalize(x[0, :2].mean(0) @ emb.projection.t(), dim=-1)
+    assert torch.allclose(ym[0], ref, atol=1e-5) and torch.allclose(ym[1], y[1], atol=1e-6)
