@@ -82,3 +82,109 @@ def benchmark_operation(fn: Callable[[], object], iters: int = 10, warmup: int =
             times.append(1e3 * (time.perf_counter() - t0))
     s = sorted(times)
     return {"median_ms": s[len(s) // 2], "min_ms": s[0], "mean_ms": sum(s) / len(s)}
+
+
+# ------------------------------------------------------------------------------------------------ multi-GPU manager / tile choice
+@dataclass
+class TunedParams:
+    """Tile shape a GEMM of the given size runs with: CTA tile rows / columns, K step, CTAs per tile, split-K factor."""
+    block_m: int = 128
+    block_n: int = 256
+    block_k: int = 64
+    cta_group: int = 1
+    split_k: int = 1
+
+
+def auto_tune_gemm(M: int, N: int, K: int, num_sms: int = 148) -> TunedParams:
+    """The tile the tcgen05 GEMM dispatch picks (reference: ``auto_tune_gemm`` picks 128x128x32 / 64x64x16 CPU blocks by size,
+    src/gpu_extras.cpp:446-452). Problems larger than one 128-row, 128-column tile run 256x256 tiles on CTA pairs
+    (``cta_group::2``), the rest the single-CTA 128x256 kernel; K advances 64 bf16 elements (one 128-byte swizzle row) per
+    stage. When the tiles do not fill the SMs, K is split so that about two work units exist per scheduling unit."""
+    if M > 128 and N > 128:
+        p, tiles, units = TunedParams(256, 256, 64, 2), -(-M // 256) * -(-N // 256), num_sms // 2
+    else:
+        p, tiles, units = TunedParams(128, 256, 64, 1), -(-M // 128) * -(-N // 256), num_sms
+    kb = max(1, -(-K // p.block_k))
+    p.split_k = 1 if tiles >= units else max(1, min(kb, (2 * units) // max(1, tiles)))
+    return p
+
+
+class MultiGPUManager:
+    """Device enumeration, per-device raw allocations and peer copies (reference: ``gpu::MultiGPUManager``,
+    include/oil/gpu_extras.h:54-69). Allocations are byte tensors owned by the manager and addressed by their data pointer,
+    as the reference hands out ``void*``; ``transfer`` is a device-to-device ``copy_`` on the destination's current stream,
+    which goes over NVLink peer access when both ends are GPUs. Without a GPU the manager exposes one host "device" so that
+    code written against it still runs."""
+
+    @dataclass
+    class DeviceInfo:
+        initialized: bool
+        name: str
+        total_mem: int
+
+    def __init__(self):
+        self.devices: List["MultiGPUManager.DeviceInfo"] = []
+        self._blocks: Dict[int, Dict[int, torch.Tensor]] = {}
+
+    def detect_devices(self) -> int:
+        self.devices = []
+        if torch.cuda.is_available():
+            for i in range(torch.cuda.device_count()):
+                p = torch.cuda.get_device_properties(i)
+                self.devices.append(self.DeviceInfo(False, p.name, p.total_memory))
+        else:
+            total = 0
+            try:
+                total = os.sysconf("SC_PAGE_SIZE") * os.sysconf("SC_PHYS_PAGES")
+            except (ValueError, OSError):
+                pass
+            self.devices.append(self.DeviceInfo(False, "host", total))
+        return len(self.devices)
+
+    def device_count(self) -> int:
+        return len(self.devices)
+
+    def device_name(self, idx: int) -> str:
+        return self.devices[idx].name if 0 <= idx < len(self.devices) else ""
+
+    def _torch_device(self, idx: int) -> torch.device:
+        return torch.device("cuda", idx) if torch.cuda.is_available() else torch.device("cpu")
+
+    def init_device(self, idx: int) -> bool:
+        if not 0 <= idx < len(self.devices):
+            return False
+        if torch.cuda.is_available():
+            torch.zeros(1, device=self._torch_device(idx))          # creates the context
+        self.devices[idx].initialized = True
+        self._blocks.setdefault(idx, {})
+        return True
+
+    def allocate_on(self, idx: int, nbytes: int) -> int:
+        """Returns the address of ``nbytes`` of device memory (0 on failure); the block lives until ``free_on``."""
+        if not (0 <= idx < len(self.devices) and self.devices[idx].initialized) or nbytes <= 0:
+            return 0
+        block = torch.empty(nbytes, dtype=torch.uint8, device=self._torch_device(idx))
+        self._blocks[idx][block.data_ptr()] = block
+        return block.data_ptr()
+
+    def free_on(self, idx: int, ptr: int) -> bool:
+        return self._blocks.get(idx, {}).pop(ptr, None) is not None
+
+    def block(self, idx: int, ptr: int) -> torch.Tensor:
+        return self._blocks[idx][ptr]
+
+    def transfer(self, src_idx: int, dst_idx: int, src: int, dst: int, nbytes: int) -> bool:
+        s, d = self._blocks.get(src_idx, {}).get(src), self._blocks.get(dst_idx, {}).get(dst)
+        if s is None or d is None or nbytes > min(s.numel(), d.numel()):
+            return False
+        d[:nbytes].copy_(s[:nbytes], non_blocking=True)
+        return True
+
+    def synchronize(self) -> None:
+        if torch.cuda.is_available():
+            for i, dev in enumerate(self.devices):
+                if dev.initialized:
+                    torch.cuda.synchronize(i)
+
+    def memory_in_use(self, idx: int) -> int:
+        return sum(b.numel() for b in self._blocks.get(idx, {}).values())

@@ -1,0 +1,31 @@
+"""MultiGPUManager on the host device and the GEMM tile rule."""
+import importlib
+
+import torch
+
+G = importlib.import_module("innova_b200.ops.gemm")
+from innova_b200.utils.backend import MultiGPUManager, auto_tune_gemm
+
+
+def test_manager_allocates_frees_and_copies():
+    m = MultiGPUManager()
+    assert m.device_count() == 0 and m.device_name(0) == "" and not m.init_device(0)
+    n = m.detect_devices()
+    assert n == m.device_count() >= 1 and m.device_name(0) and m.allocate_on(0, 64) == 0          # not initialised yet
+    assert m.init_device(0) and not m.init_device(n) and m.devices[0].initialized
+    a, b = m.allocate_on(0, 256), m.allocate_on(0, 128)
+    assert a and b and a != b and m.memory_in_use(0) == 384 and m.allocate_on(0, 0) == 0
+    m.block(0, a).copy_(torch.arange(256, dtype=torch.uint8))
+    assert m.transfer(0, 0, a, b, 128) and not m.transfer(0, 0, a, b, 200) and not m.transfer(0, 0, a, 12345, 8)
+    m.synchronize()
+    assert torch.equal(m.block(0, b).cpu(), torch.arange(128, dtype=torch.uint8))
+    assert m.free_on(0, a) and not m.free_on(0, a) and m.memory_in_use(0) == 128
+
+
+def test_tile_rule_matches_the_gemm_dispatch():
+    p = auto_tune_gemm(65536, 3072, 768)
+    assert (p.block_m, p.block_n, p.block_k, p.cta_group, p.split_k) == (256, 256, 64, 2, 1)
+    q = auto_tune_gemm(64, 4096, 4096)
+    assert (q.block_m, q.block_n, q.cta_group) == (128, 256, 1) and q.split_k > 1
+    for M, N, K in ((65536, 3072, 768), (64, 4096, 4096), (768, 768, 65536), (256, 256, 512), (128, 128, 64), (8, 50304, 768)):
+        assert auto_tune_gemm(M, N, K, G.NUM_SMS).split_k == G._split_k_for(M, N, K)
