@@ -505,10 +505,66 @@ class Message:
 class MultiAgentCoordinator:
     ROLES = ("planner", "executor", "critic", "verifier")
 
-    def __init__(self):
+    def __init__(self, call_model: Optional[Callable[[str], str]] = None):
+        """``call_model`` (prompt -> text) backs the five-phase ``run_task`` pipeline; without one every phase echoes its
+        prompt with " [no model]" appended, as the reference does without a model (src/asi_extended.cpp:238-244)."""
         self.agents: Dict[str, Tuple[str, Callable[[Any], Any]]] = {}
         self.mailbox: Dict[str, List[Message]] = defaultdict(list)
         self.log: List[Message] = []
+        self._call_model = call_model
+        self.current_round = 0
+        self.converged = False
+        self.agent_history: Dict[str, List[str]] = defaultdict(list)
+
+    # -- analyst -> implementer -> verifier -> (critic -> implementer -> verifier)* -> synthesizer (src/asi_extended.cpp:205-236)
+    def call_model(self, prompt: str) -> str:
+        return self._call_model(prompt) if self._call_model is not None else prompt + " [no model]"
+
+    def _phase(self, agent: str, prompt: str) -> str:
+        out = self.call_model(prompt)
+        self.agent_history[agent].append(out)
+        return out
+
+    def analyst_phase(self, task: str) -> str:
+        return self._phase("analyst", "Analyst: Analyze the task: " + task)
+
+    def implementer_phase(self, analysis: str) -> str:
+        return self._phase("implementer", "Implementer: Implement based on analysis: " + analysis)
+
+    def verifier_phase(self, implementation: str) -> str:
+        return self._phase("verifier", "Verifier: Verify implementation: " + implementation)
+
+    def critic_phase(self, implementation: str, verification: str) -> str:
+        return self._phase("critic", "Critic: Critique impl: " + implementation + " and verification: " + verification)
+
+    def synthesizer_phase(self, inputs: Sequence[str]) -> str:
+        return self._phase("synthesizer", "Synthesizer: Synthesize:\n" + "".join(i + "\n" for i in inputs))
+
+    def run_task(self, task_description: str, max_critic_rounds: int = 3) -> str:
+        """The critic loop ends early when a critique contains ``[APPROVED]``; otherwise the critique is what the implementer
+        works from in the next round."""
+        self.current_round, self.converged = 0, False
+        analysis = self.analyst_phase(task_description)
+        implementation = self.implementer_phase(analysis)
+        verification = self.verifier_phase(implementation)
+        for r in range(max_critic_rounds):
+            self.current_round = r + 1
+            critique = self.critic_phase(implementation, verification)
+            if "[APPROVED]" in critique:
+                self.converged = True
+                break
+            implementation = self.implementer_phase(critique)
+            verification = self.verifier_phase(implementation)
+        return self.synthesizer_phase([analysis, implementation, verification])
+
+    def get_agent_history(self, agent: str) -> List[str]:
+        return list(self.agent_history.get(agent, []))
+
+    def clear_agent_history(self, agent: Optional[str] = None) -> None:
+        if agent is None:
+            self.agent_history.clear()
+        else:
+            self.agent_history.pop(agent, None)
 
     def register(self, name: str, role: str, handler: Callable[[Any], Any]):
         assert role in self.ROLES

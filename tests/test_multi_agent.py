@@ -152,3 +152,24 @@ def test_episode_chatter_is_seeded_and_respects_topology():
     a.execute_plan(a.current_plan)
     a.run_episode(5)
     assert a.get_subtasks()[0].status == "completed"
+
+
+def test_coordinator_five_phase_pipeline():
+    from innova_b200.utils.asi import MultiAgentCoordinator
+    c = MultiAgentCoordinator()
+    out = c.run_task("sort numbers", max_critic_rounds=2)
+    assert out.startswith("Synthesizer: Synthesize:\nAnalyst: Analyze the task: sort numbers [no model]\n") and out.endswith(" [no model]")
+    assert c.current_round == 2 and not c.converged and len(c.get_agent_history("critic")) == 2 and len(c.get_agent_history("implementer")) == 3
+    calls = []
+
+    def model(prompt):
+        calls.append(prompt.split(":", 1)[0])
+        return "looks right [APPROVED]" if prompt.startswith("Critic") and calls.count("Critic") == 2 else f"<{len(calls)}>"
+
+    c2 = MultiAgentCoordinator(call_model=model)
+    assert c2.run_task("x", 5) == f"<{len(calls)}>" and c2.converged and c2.current_round == 2
+    assert calls == ["Analyst", "Implementer", "Verifier", "Critic", "Implementer", "Verifier", "Critic", "Synthesizer"]
+    c2.clear_agent_history("critic")
+    assert c2.get_agent_history("critic") == [] and c2.get_agent_history("analyst") == ["<1>"]
+    c2.clear_agent_history()
+    assert c2.get_agent_history("analyst") == []
