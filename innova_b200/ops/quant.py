@@ -258,3 +258,27 @@ class STEQuantizer:
             cb = train_codebook(seg.detach().float(), fmt, sub, self.train_iters) if fmt in ("oil8", "oil4") else None
             parts.append(ste_fake_quant(seg, fmt, sub, cb))
         return torch.cat(parts).view(w.shape)
+
+
+def calibrate_importance(weights: torch.Tensor, activations: torch.Tensor, block_size: int = BLOCK, fmt: str = "oil8") -> torch.Tensor:
+    """Activation-aware importance of each row block of a weight matrix, used to decide which blocks keep a wider format
+    (reference: ``calibrate_{spark,oil4,oil8}_importance``, src/kernel_production.cpp:366-417).
+
+    ``weights`` is [M, K]; ``activations`` is a calibration statistic broadcastable to it: [K] (per input channel, e.g. the
+    RMS of that channel over a calibration set) or [M, K]. Blocks run along K within a row (the last block of a row may be
+    short) and are returned row-major as [M * ceil(K / block_size)]. The score of a block is the mean over its elements of
+    (w a)^2 for ``spark`` / ``oil8`` and of |w a| for ``oil4``, as in the reference; the whole matrix is reduced in one pass
+    on the tensor's device.
+    """
+    w = weights.float()
+    prod = w * activations.float().expand_as(w)
+    prod = prod.abs() if fmt.lower().startswith("oil4") else prod.square()
+    M, K = prod.shape
+    nb = -(-K // block_size)
+    pad = nb * block_size - K
+    if pad:
+        prod = torch.nn.functional.pad(prod, (0, pad))
+    sums = prod.view(M, nb, block_size).sum(-1)
+    counts = torch.full((nb,), float(block_size), device=w.device)
+    counts[-1] = float(block_size - pad)
+    return (sums / counts).reshape(-1)

@@ -33,6 +33,29 @@ _native.register_cuda_sigs({
 })
 
 
+def shutdown_distributed(barrier: bool = True, grace_s: float = 0.05) -> None:
+    """Orderly end of a rank: a barrier (no rank tears down while a peer is still inside a collective), a garbage
+    collection (completed ``Work`` handles and their tensors are released on this thread, with the interpreter alive), then
+    ``destroy_process_group``.
+
+    With the gloo backend a collective's ``Work`` is owned jointly by the caller and by a backend thread; whichever lets go
+    last frees the tensors it holds, and freeing a tensor that Python has seen needs the interpreter lock. If an engine or a
+    trainer still references the process group, ``destroy_process_group`` cannot join the backend threads, and a rank that
+    returns at once can reach interpreter shutdown while a backend thread is still letting go of the last ``Work``: that
+    thread is then refused the lock and the process aborts ("terminate called without an active exception"). The short
+    grace period after the destroy closes that window; dropping the references to engines first avoids it altogether."""
+    if not (dist.is_available() and dist.is_initialized()):
+        return
+    import gc
+    import time
+    if barrier:
+        dist.barrier()
+    gc.collect()
+    dist.destroy_process_group()
+    if grace_s > 0:
+        time.sleep(grace_s)
+
+
 def _world(group=None):
     return dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
 

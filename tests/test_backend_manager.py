@@ -29,3 +29,16 @@ def test_tile_rule_matches_the_gemm_dispatch():
     assert (q.block_m, q.block_n, q.cta_group) == (128, 256, 1) and q.split_k > 1
     for M, N, K in ((65536, 3072, 768), (64, 4096, 4096), (768, 768, 65536), (256, 256, 512), (128, 128, 64), (8, 50304, 768)):
         assert auto_tune_gemm(M, N, K, G.NUM_SMS).split_k == G._split_k_for(M, N, K)
+
+
+def test_activation_aware_block_importance():
+    from innova_b200.ops.quant import calibrate_importance
+    torch.manual_seed(0)
+    w, a = torch.randn(3, 10), torch.rand(10) + 0.5
+    imp8, imp4 = calibrate_importance(w, a, 4, "oil8"), calibrate_importance(w, a, 4, "oil4")
+    assert imp8.shape == (9,) and imp4.shape == (9,)
+    for m in range(3):
+        for b, (lo, hi) in enumerate(((0, 4), (4, 8), (8, 10))):
+            p = w[m, lo:hi] * a[lo:hi]
+            assert torch.allclose(imp8[m * 3 + b], p.square().mean(), atol=1e-6) and torch.allclose(imp4[m * 3 + b], p.abs().mean(), atol=1e-6)
+    assert torch.allclose(calibrate_importance(w, a.expand(3, 10), 4, "spark"), imp8)

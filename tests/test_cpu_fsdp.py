@@ -7,6 +7,12 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 
+def _shutdown():
+    """Barrier, release finished work on this thread, destroy the group (see ``shutdown_distributed``)."""
+    from innova_b200.parallel.collectives import shutdown_distributed
+    shutdown_distributed()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -41,7 +47,7 @@ def _worker(rank, world, port, out):
     full = eng.gather_master()
     if rank == 0:
         torch.save({"flat": eng.flat_param.clone(), "master": full}, out)
-    dist.destroy_process_group()
+    _shutdown()
 
 
 def test_two_rank_sharded_step_matches_single_engine(tmp_path):

@@ -9,6 +9,12 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 
+def _shutdown():
+    """Barrier, release finished work on this thread, destroy the group (see ``shutdown_distributed``)."""
+    from innova_b200.parallel.collectives import shutdown_distributed
+    shutdown_distributed()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -47,7 +53,8 @@ def _worker(rank, world, port, out, accum):
     full = eng.gather_full("master")
     if rank == 0:
         torch.save({"params": full, "losses": losses}, out)
-    dist.destroy_process_group()
+    del tr, eng, model                   # no reference to the process group outlives the shutdown
+    _shutdown()
 
 
 @pytest.mark.parametrize("world,accum", [(2, 1), (3, 1), (2, 2)])

@@ -9,6 +9,12 @@ import torch.multiprocessing as mp
 from innova_b200.parallel.elastic import CapacityAwareRouter, ClusterConfig, FaultToleranceManager, HeartbeatMonitor, run_elastic
 
 
+def _shutdown():
+    """Barrier, release finished work on this thread, destroy the group (see ``shutdown_distributed``)."""
+    from innova_b200.parallel.collectives import shutdown_distributed
+    shutdown_distributed()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -91,7 +97,7 @@ def _segment(rank, world, port, ckpt, steps, first_step, fail_rank, out):
     if rank == 0:
         torch.save({"done": done, "flat": eng.flat_param.clone(), "failed": mon.failed_ranks()}, out)
     dist.barrier()
-    dist.destroy_process_group()
+    _shutdown()
 
 
 def test_elastic_restart_at_smaller_world_matches_uninterrupted_run(tmp_path):

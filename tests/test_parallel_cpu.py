@@ -8,6 +8,12 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 
+def _shutdown():
+    """Barrier, release finished work on this thread, destroy the group (see ``shutdown_distributed``)."""
+    from innova_b200.parallel.collectives import shutdown_distributed
+    shutdown_distributed()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -42,7 +48,7 @@ def _ddp_worker(rank, world, port, out, compression):
         eng.step()
     if rank == 0:
         torch.save({"flat": eng.flat_param.clone(), "bytes": eng.bytes_sent}, out)
-    dist.destroy_process_group()
+    _shutdown()
 
 
 def _single_reference(world, transform=None):
@@ -123,7 +129,7 @@ def _coll_worker(rank, world, port, out):
     ps.pull("w")
     res["ps_w2"] = params["w"].data.clone()
     torch.save(res, out + f".{rank}")
-    dist.destroy_process_group()
+    _shutdown()
 
 
 def test_collectives_api_on_gloo(tmp_path):
@@ -162,7 +168,7 @@ def _tp_worker(rank, world, port, out):
     hp = HeadPartitioner(8, 2, 4)
     res["kv"] = [list(hp.kv_heads(r)) for r in range(4)]
     torch.save(res, out + f".{rank}")
-    dist.destroy_process_group()
+    _shutdown()
 
 
 def test_tensor_parallel_layers_match_dense(tmp_path):
@@ -199,7 +205,7 @@ def _ep_worker(rank, world, port, out):
     (y * torch.arange(1, D + 1)).sum().backward()
     m.sync_router_grad()
     torch.save({"y": y.detach(), "dx": x.grad, "gw": m.w_gu.grad, "gr": m.router.grad, "counts": counts}, out + f".{rank}")
-    dist.destroy_process_group()
+    _shutdown()
 
 
 def test_expert_parallel_fallback_matches_single_process(tmp_path):
@@ -238,7 +244,7 @@ def _pp_worker(rank, world, port, out, schedule):
     loss = pp.train_step(ids if rank == 0 else None, labels if rank == world - 1 else None)
     grads = {n: p.grad.clone() for n, p in stage.named_parameters() if p.grad is not None}
     torch.save({"loss": loss, "grads": grads}, out + f".{rank}")
-    dist.destroy_process_group()
+    _shutdown()
 
 
 @pytest.mark.parametrize("schedule", ["gpipe", "1f1b"])
@@ -289,7 +295,7 @@ def _z3_worker(rank, world, port, out):
     fs = FullyShardedDataParallel(model, stage=3, min_rows=256)
     rep = fs.memory_report()
     torch.save({"y": y.detach(), "dx": x.grad, "dw": lin.weight.grad, "replaced": fs.replaced, "rep": rep}, out + f".{rank}")
-    dist.destroy_process_group()
+    _shutdown()
 
 
 def test_zero3_sharded_linear_and_wrapper(tmp_path):
@@ -364,7 +370,7 @@ def _epeng_worker(rank, world, port, out):
     before = {n: p.detach().clone() for n, p in m.named_parameters()}
     eng.step()
     torch.save({"grads": grads, "before": before, "after": {n: p.detach().clone() for n, p in m.named_parameters()}}, out + f".{rank}")
-    dist.destroy_process_group()
+    _shutdown()
 
 
 def test_expert_parallel_engine_syncs_only_replicated_and_clips_jointly(tmp_path):

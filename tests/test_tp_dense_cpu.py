@@ -7,6 +7,12 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 
+def _shutdown():
+    """Barrier, release finished work on this thread, destroy the group (see ``shutdown_distributed``)."""
+    from innova_b200.parallel.collectives import shutdown_distributed
+    shutdown_distributed()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -62,7 +68,7 @@ def _worker(rank, world, port, out):
            "scale": float(ref.blocks[1].o.weight.grad.abs().max())}
     torch.save(res, f"{out}.{rank}")
     dist.barrier()
-    dist.destroy_process_group()
+    _shutdown()
 
 
 def test_tp_dense_matches_single_rank(tmp_path):
