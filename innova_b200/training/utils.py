@@ -439,6 +439,148 @@ class NASEngine:
             pop = sorted(pop + [child], key=lambda a: a.score)[:population]
         return pop[0]
 
+    # -- population search, DARTS-style local search and hardware scoring (reference: include/oil/hpo_nas.h:174-226,
+    #    src/hpo_nas.cpp:700-970). Scores are losses here: lower is better, everywhere in this class.
+    WIDTHS = (128, 256, 384, 512, 768, 1024, 1536, 2048, 4096)
+
+    def random_architecture(self) -> Architecture:
+        r = self.rng
+        for _ in range(64):
+            d = r.choice(self.WIDTHS)
+            a = Architecture(d, r.randint(1, 48), r.choice([h for h in (1, 2, 4, 8, 16, 32, 64) if d % h == 0 and d // h >= 32]),
+                             r.choice([2.0, 2.67, 4.0]))
+            if self.feasible(a):
+                return a
+        return Architecture(128, 1, 2, 2.0)
+
+    def initialize_population(self, n: int) -> List[Architecture]:
+        return [self.random_architecture() for _ in range(n)]
+
+    def _copy(self, a: Architecture, **kw) -> Architecture:
+        b = Architecture(a.hidden_size, a.num_layers, a.num_heads, a.ffn_mult)
+        for k, v in kw.items():
+            setattr(b, k, v)
+        while b.hidden_size % b.num_heads and b.num_heads > 1:
+            b.num_heads -= 1
+        return b
+
+    def mutate_add_layer(self, a: Architecture) -> Architecture:
+        return self._copy(a, num_layers=min(96, a.num_layers + 1))
+
+    def mutate_remove_layer(self, a: Architecture) -> Architecture:
+        return self._copy(a, num_layers=max(1, a.num_layers - 1))
+
+    def mutate_change_width(self, a: Architecture) -> Architecture:
+        return self._copy(a, hidden_size=max(64, a.hidden_size + self.rng.choice([-128, -64, 64, 128])))
+
+    def mutate_change_heads(self, a: Architecture) -> Architecture:
+        return self._copy(a, num_heads=self.rng.choice([h for h in (1, 2, 4, 8, 16, 32, 64) if a.hidden_size % h == 0]))
+
+    def mutate_change_ffn(self, a: Architecture) -> Architecture:
+        return self._copy(a, ffn_mult=self.rng.choice([2.0, 2.67, 3.0, 4.0]))
+
+    def crossover(self, a: Architecture, b: Architecture) -> Architecture:
+        """Each field from one parent or the other; the head count is lowered until it divides the width."""
+        pick = lambda x, y: x if self.rng.random() < 0.5 else y
+        return self._copy(Architecture(pick(a.hidden_size, b.hidden_size), pick(a.num_layers, b.num_layers), pick(a.num_heads, b.num_heads),
+                                       pick(a.ffn_mult, b.ffn_mult)))
+
+    def tournament_select(self, pop: Sequence[Architecture], size: int = 3) -> Architecture:
+        return min(self.rng.sample(list(pop), min(size, len(pop))), key=lambda a: a.score)
+
+    def _scored(self, a: Architecture, hardware_aware: bool = False) -> Architecture:
+        a.score = self.evaluate(a)
+        if hardware_aware:
+            a.score = a.score / self.hardware_aware_score(a)      # a loss: an over-budget design is made worse, not better
+        self.history.append(a)
+        return a
+
+    def evolve(self, population: int = 50, generations: int = 20, tournament_size: int = 3, mutation_rate: float = 0.3,
+               crossover_rate: float = 0.7, hardware_aware: bool = False) -> Architecture:
+        """Generational search: the best tenth survives unchanged, the rest are tournament-selected children (crossover with
+        probability ``crossover_rate``, then mutation with probability ``mutation_rate``); infeasible children are redrawn."""
+        pop = [self._scored(a, hardware_aware) for a in self.initialize_population(population)]
+        for _ in range(generations):
+            pop.sort(key=lambda a: a.score)
+            nxt = pop[: max(1, population // 10)]
+            while len(nxt) < population:
+                child = self.tournament_select(pop, tournament_size)
+                if self.rng.random() < crossover_rate:
+                    child = self.crossover(child, self.tournament_select(pop, tournament_size))
+                if self.rng.random() < mutation_rate:
+                    child = self.mutate(child)
+                if child in pop or not self.feasible(child):
+                    child = self.random_architecture()
+                nxt.append(self._scored(self._copy(child), hardware_aware))
+            pop = nxt
+        return min(pop, key=lambda a: a.score)
+
+    def darts_evaluate(self, a: Architecture) -> float:
+        return self.evaluate(a)
+
+    def darts_migrate(self, a: Architecture, alpha: float = 0.1) -> Architecture:
+        """A small continuous step: depth, width (kept a multiple of 64) and feed-forward ratio each scaled by a factor in
+        1 +- alpha/2; an infeasible result leaves the architecture as it is."""
+        f = lambda: 1.0 + alpha * (self.rng.random() - 0.5)
+        d = max(64, min(4096, int(a.hidden_size * f()))) // 64 * 64
+        m = self._copy(a, num_layers=max(1, min(96, int(a.num_layers * f()) or 1)), hidden_size=max(64, d),
+                       ffn_mult=max(2.0, min(16.0, a.ffn_mult * f())))
+        return m if self.feasible(m) else a
+
+    def darts_search(self, n_iterations: int = 50, start: Optional[Architecture] = None) -> Architecture:
+        """Hill climbing with a relaxation step: a discrete mutation is kept when it scores better, then the incumbent drifts
+        by ``darts_migrate`` and is kept there when that is no worse."""
+        best = self._scored(start or self.random_architecture())
+        for _ in range(n_iterations):
+            cand = self.mutate(best)
+            if self.feasible(cand) and self._scored(cand).score < best.score:
+                best = cand
+            moved = self.darts_migrate(best, 0.1)
+            if moved is not best and self._scored(moved).score <= best.score:
+                best = moved
+        return best
+
+    def estimate_decode_latency_ms(self, a: Architecture, bytes_per_weight: float = 2.0, hbm_gbs: float = 7700.0) -> float:
+        """One decode step of one sequence reads every weight once: bytes / HBM bandwidth (the memory roofline of a B200)."""
+        return a.params() * bytes_per_weight / (hbm_gbs * 1e9) * 1e3
+
+    def hardware_aware_score(self, a: Architecture, target_latency_ms: Optional[float] = None) -> float:
+        """1 inside the budgets; each exceeded budget (decode latency, memory, parameter count) multiplies in
+        budget / actual; floored at 0.01."""
+        s = 1.0
+        if target_latency_ms:
+            lat = self.estimate_decode_latency_ms(a)
+            if lat > target_latency_ms:
+                s *= target_latency_ms / lat
+        mem = a.params() * self.hc.bytes_per_param
+        if mem > self.hc.max_memory_bytes:
+            s *= self.hc.max_memory_bytes / mem
+        if a.params() > self.hc.max_params:
+            s *= self.hc.max_params / a.params()
+        return max(0.01, s)
+
+    @staticmethod
+    def oil_format_penalty(a: Architecture) -> float:
+        """Widths and feed-forward sizes that are not whole 64-element blocks waste codec blocks (x0.9 each)."""
+        p = 1.0
+        if a.hidden_size % 64:
+            p *= 0.9
+        if int(a.hidden_size * a.ffn_mult) % 64:
+            p *= 0.9
+        return p
+
+    def record_architecture(self, a: Architecture) -> None:
+        self.history.append(a)
+
+    def get_best_architecture(self) -> Optional[Architecture]:
+        return min(self.history, key=lambda a: a.score) if self.history else None
+
+    def pareto_front(self) -> List[Architecture]:
+        """Evaluated architectures that no other one beats on both score and parameter count."""
+        pts = [a for a in self.history if a.score != float("inf")]
+        return sorted((a for a in pts if not any((b.score <= a.score and b.params() < a.params()) or (b.score < a.score and b.params() <= a.params())
+                                                 for b in pts)), key=lambda a: a.params())
+
 
 # ---------------------------------------------------------------------------------------------- log writers
 class CSVLogWriter:
