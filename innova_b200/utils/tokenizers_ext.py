@@ -383,3 +383,281 @@ class MultiLingualTokenizer:
         t.bpe = BPETokenizer.load(d["bpe"])
         t.lang_tags, t.fallback = d["lang_tags"], d["fallback"]
         return t
+
+
+# ------------------------------------------------------------------------------------------------ unicode helpers
+class UnicodeUtil:
+    """Code-point classification and UTF-8 helpers (reference: ``UnicodeUtil``, include/oil/bpe_tokenizer.h:17-41,
+    src/bpe_tokenizer_unicode.cpp). Classification comes from the Unicode character database through ``unicodedata``
+    rather than hand-kept range tables."""
+
+    _LANG = {"cjk": "zh", "hiragana": "ja", "katakana": "ja", "hangul": "ko", "cyrillic": "ru", "arabic": "ar", "hebrew": "he",
+             "devanagari": "hi", "greek": "el", "thai": "th", "latin": "en"}
+
+    @staticmethod
+    def _cat(cp: int) -> str:
+        return unicodedata.category(chr(cp)) if 0 <= cp <= 0x10FFFF else "Cn"
+
+    @staticmethod
+    def is_cjk(cp: int) -> bool:
+        return (0x4E00 <= cp <= 0x9FFF or 0x3400 <= cp <= 0x4DBF or 0x20000 <= cp <= 0x2A6DF or 0xF900 <= cp <= 0xFAFF
+                or 0x3040 <= cp <= 0x30FF or 0xAC00 <= cp <= 0xD7AF)
+
+    @classmethod
+    def is_whitespace(cls, cp: int) -> bool:
+        return cp in (0x09, 0x0A, 0x0B, 0x0C, 0x0D, 0x85) or cls._cat(cp) == "Zs" or cp in (0x2028, 0x2029)
+
+    @classmethod
+    def is_punctuation(cls, cp: int) -> bool:
+        return cls._cat(cp).startswith("P")
+
+    @classmethod
+    def is_letter(cls, cp: int) -> bool:
+        return cls._cat(cp).startswith("L")
+
+    @classmethod
+    def is_digit(cls, cp: int) -> bool:
+        return cls._cat(cp) == "Nd"
+
+    @classmethod
+    def is_control(cls, cp: int) -> bool:
+        return cls._cat(cp) in ("Cc", "Cf") and not cls.is_whitespace(cp)
+
+    @classmethod
+    def is_math_symbol(cls, cp: int) -> bool:
+        return cls._cat(cp) == "Sm"
+
+    @classmethod
+    def is_currency(cls, cp: int) -> bool:
+        return cls._cat(cp) == "Sc"
+
+    @classmethod
+    def is_combining_mark(cls, cp: int) -> bool:
+        return cls._cat(cp).startswith("M")
+
+    @staticmethod
+    def is_regional_indicator(cp: int) -> bool:
+        return 0x1F1E6 <= cp <= 0x1F1FF
+
+    @staticmethod
+    def is_variation_selector(cp: int) -> bool:
+        return 0xFE00 <= cp <= 0xFE0F or 0xE0100 <= cp <= 0xE01EF
+
+    @staticmethod
+    def is_emoji_modifier(cp: int) -> bool:
+        return 0x1F3FB <= cp <= 0x1F3FF
+
+    @classmethod
+    def is_emoji(cls, cp: int) -> bool:
+        return (0x1F300 <= cp <= 0x1FAFF or 0x2600 <= cp <= 0x27BF or 0x1F000 <= cp <= 0x1F2FF or cls.is_regional_indicator(cp)
+                or cp in (0x00A9, 0x00AE, 0x203C, 0x2049, 0x2122, 0x2139, 0x231A, 0x231B, 0x2B50, 0x2B55, 0x3030, 0x303D))
+
+    @staticmethod
+    def utf8_encode(cp: int) -> bytes:
+        if not 0 <= cp <= 0x10FFFF or 0xD800 <= cp <= 0xDFFF:
+            cp = 0xFFFD
+        return chr(cp).encode("utf-8")
+
+    @staticmethod
+    def utf8_decode(data: bytes, pos: int) -> Tuple[int, int]:
+        """Decodes one code point of ``data`` at ``pos`` -> (code point, next position); malformed or truncated sequences
+        (overlong forms and surrogates included) give U+FFFD and advance one byte."""
+        b0 = data[pos]
+        if b0 < 0x80:
+            return b0, pos + 1
+        n, lo = (2, 0x80) if 0xC2 <= b0 <= 0xDF else (3, 0x800) if 0xE0 <= b0 <= 0xEF else (4, 0x10000) if 0xF0 <= b0 <= 0xF4 else (0, 0)
+        if n == 0 or pos + n > len(data) or any(data[pos + i] & 0xC0 != 0x80 for i in range(1, n)):
+            return 0xFFFD, pos + 1
+        cp = b0 & (0xFF >> (n + 1))
+        for i in range(1, n):
+            cp = (cp << 6) | (data[pos + i] & 0x3F)
+        if cp < lo or cp > 0x10FFFF or 0xD800 <= cp <= 0xDFFF:
+            return 0xFFFD, pos + 1
+        return cp, pos + n
+
+    @classmethod
+    def utf8_to_codepoints(cls, data) -> List[int]:
+        data = data.encode("utf-8") if isinstance(data, str) else bytes(data)
+        out, pos = [], 0
+        while pos < len(data):
+            cp, pos = cls.utf8_decode(data, pos)
+            out.append(cp)
+        return out
+
+    @classmethod
+    def codepoints_to_utf8(cls, cps: Sequence[int]) -> bytes:
+        return b"".join(cls.utf8_encode(c) for c in cps)
+
+    @staticmethod
+    def nfkc_normalize(s: str) -> str:
+        return unicodedata.normalize("NFKC", s)
+
+    @staticmethod
+    def compose_pair(a: int, b: int) -> int:
+        """The single code point that canonically composes ``a`` followed by ``b``, or 0 when there is none."""
+        c = unicodedata.normalize("NFC", chr(a) + chr(b))
+        return ord(c) if len(c) == 1 else 0
+
+    @staticmethod
+    def split_on_whitespace(s: str) -> List[str]:
+        return s.split()
+
+    @classmethod
+    def pretokenize(cls, s: str) -> List[str]:
+        """Runs of letters (with their combining marks), runs of digits, single CJK characters, single punctuation /
+        symbol characters; emoji keep their modifiers, variation selectors and joiners; whitespace separates and is dropped."""
+        out: List[str] = []
+        kind = ""
+        for ch in s:
+            cp = ord(ch)
+            if cls.is_whitespace(cp):
+                kind = ""
+                continue
+            glue = cls.is_combining_mark(cp) or cls.is_variation_selector(cp) or cls.is_emoji_modifier(cp) or cp == 0x200D
+            if glue and out and kind:
+                out[-1] += ch
+                continue
+            if out and kind == "emoji" and out[-1].endswith("‍"):
+                out[-1] += ch
+                continue
+            k = "cjk" if cls.is_cjk(cp) else "letter" if cls.is_letter(cp) else "digit" if cls.is_digit(cp) else \
+                "emoji" if cls.is_emoji(cp) else "other"
+            if k == kind and k in ("letter", "digit"):
+                out[-1] += ch
+            elif k == kind == "emoji" and cls.is_regional_indicator(cp) and len(out[-1]) == 1 and cls.is_regional_indicator(ord(out[-1])):
+                out[-1] += ch                                    # a flag is two regional indicators
+            else:
+                out.append(ch)
+            kind = k
+        return out
+
+    @classmethod
+    def detect_language(cls, segment: str) -> str:
+        """Two-letter tag of the script most letters of the segment belong to ("und" when it has no letters)."""
+        votes = Counter(script_of(ch) for ch in segment if cls.is_letter(ord(ch)))
+        return cls._LANG.get(votes.most_common(1)[0][0], "und") if votes else "und"
+
+    @classmethod
+    def width(cls, cp: int) -> int:
+        """Terminal columns: 0 for control / combining / selectors / joiners, 2 for wide and full-width, else 1."""
+        if cp == 0 or cls._cat(cp) in ("Cc", "Cf", "Mn", "Me") or cls.is_variation_selector(cp):
+            return 0
+        return 2 if unicodedata.east_asian_width(chr(cp)) in ("W", "F") else 1
+
+
+# ------------------------------------------------------------------------------------------------ byte-level BPE with a printable byte alphabet
+def _byte_alphabet() -> List[str]:
+    """Every byte as one printable character: printable Latin-1 bytes stand for themselves, the rest are moved to
+    U+0100 onwards (the byte alphabet GPT-2 style vocabularies are written in)."""
+    keep = list(range(0x21, 0x7F)) + list(range(0xA1, 0xAD)) + list(range(0xAE, 0x100))
+    table, extra = {}, 0
+    for b in range(256):
+        if b in keep:
+            table[b] = chr(b)
+        else:
+            table[b] = chr(256 + extra)
+            extra += 1
+    return [table[b] for b in range(256)]
+
+
+class ByteLevelBPETokenizer:
+    """Trainable byte-level BPE whose tokens are strings over the printable byte alphabet (reference:
+    ``ByteLevelBPETokenizer``, include/oil/bpe_tokenizer.h:124-161, src/bpe_tokenizer_bpe.cpp). Ids 0..4 are ``<unk>``,
+    ``<pad>``, ``<mask>``, ``<s>`` (3) and ``</s>`` (4), then the 256 byte tokens, then the merges in the order they were
+    learnt. Training counts pairs over the distinct pre-tokenised words weighted by frequency; a leading space stays part of
+    the following word, so decoding is the exact inverse of encoding for any byte string."""
+
+    SPECIALS = ("<unk>", "<pad>", "<mask>", "<s>", "</s>")
+    _SPLIT = re.compile(r" ?[^\W\d_]+| ?\d+| ?[^\s\w]+|\s+(?!\S)|\s+", re.UNICODE)
+
+    def __init__(self):
+        self.alphabet = _byte_alphabet()
+        self.byte_of = {c: b for b, c in enumerate(self.alphabet)}
+        self.id_to_token: List[str] = list(self.SPECIALS) + self.alphabet
+        self.token_to_id: Dict[str, int] = {t: i for i, t in enumerate(self.id_to_token)}
+        self.merges: Dict[Tuple[int, int], int] = {}
+        self.unk_id, self.bos_id, self.eos_id = 0, 3, 4
+        self._cache: Dict[str, List[int]] = {}
+
+    def vocab_size(self) -> int:
+        return len(self.id_to_token)
+
+    def byte_encode(self, text: str) -> List[int]:
+        return [self.token_to_id[self.alphabet[b]] for b in text.encode("utf-8")]
+
+    def _add_token(self, token: str) -> int:
+        self.token_to_id[token] = len(self.id_to_token)
+        self.id_to_token.append(token)
+        return self.token_to_id[token]
+
+    def train(self, corpus: Iterable[str], vocab_size: int = 50000, min_frequency: int = 2) -> None:
+        words = Counter(w for line in corpus for w in self._SPLIT.findall(line))
+        seqs = {w: self.byte_encode(w) for w in words}
+        while len(self.id_to_token) < vocab_size:
+            pairs: Counter = Counter()
+            for w, ids in seqs.items():
+                f = words[w]
+                for a, b in zip(ids, ids[1:]):
+                    pairs[(a, b)] += f
+            if not pairs:
+                break
+            (a, b), n = max(pairs.items(), key=lambda kv: (kv[1], -kv[0][0], -kv[0][1]))
+            if n < min_frequency:
+                break
+            new = self._add_token(self.id_to_token[a] + self.id_to_token[b])
+            self.merges[(a, b)] = new
+            for w, ids in seqs.items():
+                if a in ids:
+                    seqs[w] = self._apply(ids, a, b, new)
+        self._cache.clear()
+
+    @staticmethod
+    def _apply(ids: List[int], a: int, b: int, new: int) -> List[int]:
+        out, i = [], 0
+        while i < len(ids):
+            if i + 1 < len(ids) and ids[i] == a and ids[i + 1] == b:
+                out.append(new)
+                i += 2
+            else:
+                out.append(ids[i])
+                i += 1
+        return out
+
+    def bpe_merge_tokens(self, ids: List[int]) -> List[int]:
+        """Applies the learnt merges in training order (lowest merged id first) until none applies."""
+        while len(ids) > 1:
+            best = min(((self.merges.get(p, 1 << 60), p) for p in zip(ids, ids[1:])), key=lambda t: t[0])
+            if best[0] == 1 << 60:
+                break
+            ids = self._apply(ids, best[1][0], best[1][1], best[0])
+        return ids
+
+    def encode(self, text: str, add_special: bool = False) -> List[int]:
+        out: List[int] = [self.bos_id] if add_special else []
+        for w in self._SPLIT.findall(text):
+            if w not in self._cache:
+                self._cache[w] = self.bpe_merge_tokens(self.byte_encode(w))
+            out.extend(self._cache[w])
+        return out + ([self.eos_id] if add_special else [])
+
+    def decode(self, ids: Sequence[int]) -> str:
+        data = bytearray()
+        for i in ids:
+            if len(self.SPECIALS) <= i < len(self.id_to_token):
+                data.extend(self.byte_of[c] for c in self.id_to_token[i])
+        return data.decode("utf-8", "replace")
+
+    def save(self, path: str) -> None:
+        with open(path, "w", encoding="utf-8") as f:
+            json.dump({"type": "byte_level_bpe", "merges": [[a, b] for (a, b) in self.merges]}, f)
+
+    def load(self, path: str) -> None:
+        with open(path, encoding="utf-8") as f:
+            blob = json.load(f)
+        if blob.get("type") != "byte_level_bpe":
+            raise ValueError(f"{path}: not a byte-level BPE file")
+        self.__init__()
+        for a, b in blob["merges"]:
+            if not (0 <= a < len(self.id_to_token) and 0 <= b < len(self.id_to_token)):
+                raise ValueError(f"{path}: merge refers to an unknown token")
+            self.merges[(a, b)] = self._add_token(self.id_to_token[a] + self.id_to_token[b])
