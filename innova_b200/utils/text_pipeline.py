@@ -330,3 +330,226 @@ class MinHashDedup:
 
     def duplicate_rate(self) -> float:
         return self.duplicates_found / self.total_checked if self.total_checked else 0.0
+
+
+# ------------------------------------------------------------------------------------------------ memory-mapped and streaming text loaders
+@dataclass
+class MmapDataLoaderConfig:
+    batch_size: int = 8
+    seq_length: int = 2048
+    shuffle_buffer: int = 100000          # sequences are drawn at random from up to this many buffered tokens' worth
+    mmap_window: int = 1024 * 1024        # bytes of text tokenised per refill
+    dedup_enabled: bool = True
+    ngram_size: int = 4
+    seed: int = 42
+    drop_last: bool = True
+    num_workers: int = 1
+    max_seen_ngrams: int = 4_000_000
+
+
+def _cut_at_boundary(buf, start: int, end: int, limit: int) -> int:
+    """Moves ``end`` back to just after the last whitespace byte of [start, end) when the window does not reach ``limit``
+    (the end of the data), so that neither a word nor a UTF-8 sequence is split; falls back to a character boundary."""
+    if end >= limit:
+        return limit
+    for i in range(end, max(start, end - 4096), -1):
+        if buf[i - 1] in b" \n\t\r":
+            return i
+    while end > start and (buf[end] & 0xC0) == 0x80:
+        end -= 1
+    return end
+
+
+class MmapDataLoader:
+    """Batches straight from a memory-mapped text file (reference: ``MmapDataLoader``, include/oil/mmap_dataloader.h:94-160,
+    src/tensor_view.cpp:100-260): a window of the file is tokenised per refill, n-grams seen before are dropped, and batches
+    of ``batch_size`` x ``seq_length`` ids are cut from the token buffer; ``next_batch_with_labels`` returns the next-token
+    targets too. The file is never read whole.
+
+    The n-gram filter is exact and vectorised: every n-gram of a window gets a 64-bit polynomial hash in one numpy pass, a
+    token is dropped when the n-gram starting at it was seen in an earlier window or earlier in this one, and the bounded set
+    of seen hashes is a sorted array probed with ``searchsorted`` (the reference probes a MinHash filter once per token)."""
+
+    def __init__(self, file_path: str, tokenizer, cfg: Optional[MmapDataLoaderConfig] = None):
+        import mmap
+        self.cfg = cfg or MmapDataLoaderConfig()
+        self.tokenizer = tokenizer
+        self._file = open(file_path, "rb")
+        self._size = self._file.seek(0, 2)
+        self._map = mmap.mmap(self._file.fileno(), 0, access=mmap.ACCESS_READ) if self._size else b""
+        self._rng = np.random.default_rng(self.cfg.seed)
+        self.reset()
+
+    def reset(self) -> None:
+        self._offset, self.total_tokens, self.tokens_dropped = 0, 0, 0
+        self._buffer = np.zeros(0, dtype=np.int64)
+        self._seen = np.zeros(0, dtype=np.uint64)
+        self._pool: List[np.ndarray] = []
+
+    def close(self) -> None:
+        if self._size:
+            self._map.close()
+        self._file.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    # -- refill
+    def tokenize_window(self, start: int, length: int) -> np.ndarray:
+        text = bytes(self._map[start: start + length]).decode("utf-8", "replace")
+        return np.asarray(self.tokenizer.encode(text), dtype=np.int64)
+
+    def _dedup(self, tokens: np.ndarray) -> np.ndarray:
+        n = self.cfg.ngram_size
+        if tokens.size < n:
+            return tokens
+        win = np.lib.stride_tricks.sliding_window_view(tokens.astype(np.uint64), n)
+        h = np.full(win.shape[0], 1469598103934665603, dtype=np.uint64)
+        with np.errstate(over="ignore"):
+            for k in range(n):
+                h = (h ^ win[:, k]) * np.uint64(1099511628211)
+        pos = np.searchsorted(self._seen, h)
+        earlier = (pos < self._seen.size) & (self._seen[np.minimum(pos, max(0, self._seen.size - 1))] == h) if self._seen.size else \
+            np.zeros(h.size, dtype=bool)
+        _, first = np.unique(h, return_index=True)
+        repeat = np.ones(h.size, dtype=bool)
+        repeat[first] = False
+        drop = earlier | repeat
+        merged = np.union1d(self._seen, h)
+        self._seen = merged[-self.cfg.max_seen_ngrams:] if merged.size > self.cfg.max_seen_ngrams else merged
+        keep = np.ones(tokens.size, dtype=bool)
+        keep[: h.size] = ~drop
+        self.tokens_dropped += int(drop.sum())
+        return tokens[keep]
+
+    def refill_buffer(self) -> bool:
+        if self._offset >= self._size:
+            return False
+        end = _cut_at_boundary(self._map, self._offset, min(self._size, self._offset + self.cfg.mmap_window), self._size)
+        if end <= self._offset:
+            end = min(self._size, self._offset + self.cfg.mmap_window)
+        tokens = self.tokenize_window(self._offset, end - self._offset)
+        self._offset = end
+        if self.cfg.dedup_enabled:
+            tokens = self._dedup(tokens)
+        self._buffer = np.concatenate([self._buffer, tokens])
+        self.total_tokens += int(tokens.size)
+        return True
+
+    # -- batches
+    def _need(self, extra: int) -> int:
+        return self.cfg.batch_size * self.cfg.seq_length + extra
+
+    def has_next(self) -> bool:
+        return self._buffer.size >= self._need(1) or self._offset < self._size or len(self._pool) >= self.cfg.batch_size
+
+    def num_batches(self) -> int:
+        """Batches worth of tokens read so far (the file's total is only known once it has been read through)."""
+        return self.total_tokens // (self.cfg.batch_size * self.cfg.seq_length)
+
+    def _take(self, extra: int) -> Optional[np.ndarray]:
+        """``batch_size`` rows of ``seq_length + extra`` tokens as a 2-D array (row r + 1 of an unshuffled batch starts where
+        row r's inputs end). With a shuffle buffer the rows are drawn at random from a pool of up to
+        ``shuffle_buffer // seq_length`` buffered rows, each cut whole from the stream with its own label token."""
+        S, B = self.cfg.seq_length, self.cfg.batch_size
+        if self.cfg.shuffle_buffer > 0:
+            want = max(B, self.cfg.shuffle_buffer // S)
+            while len(self._pool) < want:
+                while self._buffer.size < S + 1 and self.refill_buffer():
+                    pass
+                if self._buffer.size < S + 1:
+                    break
+                self._pool.append(self._buffer[: S + 1].copy())
+                self._buffer = self._buffer[S:]
+            if len(self._pool) < B:
+                if self.cfg.drop_last or not self._pool:
+                    self._pool.clear()
+                    return None
+                rows = self._pool + [np.zeros(S + 1, dtype=np.int64)] * (B - len(self._pool))
+                self._pool = []
+                return np.stack(rows)[:, : S + extra]
+            pick = sorted(self._rng.choice(len(self._pool), B, replace=False).tolist(), reverse=True)
+            rows = [self._pool.pop(i) for i in pick]
+            return np.stack(rows[::-1])[:, : S + extra]
+        need = B * S + extra
+        while self._buffer.size < need and self.refill_buffer():
+            pass
+        if self._buffer.size < need:
+            if self.cfg.drop_last or self._buffer.size <= extra:
+                self._buffer = self._buffer[:0]
+                return None
+            flat = np.zeros(need, dtype=np.int64)
+            flat[: self._buffer.size] = self._buffer
+            self._buffer = self._buffer[:0]
+        else:
+            flat = self._buffer[:need]
+            self._buffer = self._buffer[B * S:]
+        return np.stack([flat[r * S: r * S + S + extra] for r in range(B)])
+
+    def next_batch(self) -> Optional[torch.Tensor]:
+        rows = self._take(0)
+        return None if rows is None else torch.from_numpy(np.ascontiguousarray(rows))
+
+    def next_batch_with_labels(self) -> Optional[Tuple[torch.Tensor, torch.Tensor]]:
+        rows = self._take(1)
+        if rows is None:
+            return None
+        t = torch.from_numpy(np.ascontiguousarray(rows))
+        return t[:, :-1].contiguous(), t[:, 1:].contiguous()
+
+
+class StreamingDataLoader:
+    """Sequential batches from a text file read 1 MiB at a time through a rolling token buffer (reference:
+    ``StreamingDataLoader``, include/oil/trainer.h:193-213): ``next_batch`` returns (ids, labels) or None at the end; the
+    file is tokenised incrementally and never held whole."""
+
+    def __init__(self, tokenizer, data_path: str, batch_size: int, seq_length: int, chunk_bytes: int = 1 << 20):
+        self.tokenizer, self.path = tokenizer, data_path
+        self._batch_size, self._seq_length, self.chunk_bytes = batch_size, seq_length, chunk_bytes
+        self._file = open(data_path, "rb")
+        self.reset()
+
+    def batch_size(self) -> int:
+        return self._batch_size
+
+    def seq_length(self) -> int:
+        return self._seq_length
+
+    def num_batches(self) -> int:
+        return self._served
+
+    def reset(self) -> None:
+        self._file.seek(0)
+        self._buffer: List[int] = []
+        self._carry = b""
+        self._eof, self._served = False, 0
+
+    def close(self) -> None:
+        self._file.close()
+
+    def fill_buffer(self) -> None:
+        data = self._file.read(self.chunk_bytes)
+        if not data:
+            self._eof = True
+            data, self._carry = self._carry, b""
+        else:
+            data = self._carry + data
+            cut = _cut_at_boundary(data + b" ", 0, len(data), len(data) + 1)
+            data, self._carry = data[:cut], data[cut:]
+        if data:
+            self._buffer.extend(self.tokenizer.encode(data.decode("utf-8", "replace")))
+
+    def next_batch(self) -> Optional[Tuple[torch.Tensor, torch.Tensor]]:
+        need = self._batch_size * self._seq_length + 1
+        while len(self._buffer) < need and not self._eof:
+            self.fill_buffer()
+        if len(self._buffer) < need:
+            return None
+        flat = torch.tensor(self._buffer[:need], dtype=torch.long)
+        del self._buffer[: need - 1]
+        self._served += 1
+        B, S = self._batch_size, self._seq_length
+        return flat[:-1].view(B, S), flat[1:].view(B, S)
