@@ -209,3 +209,107 @@ class TensorParallelManager:
                 kind = "replicate"
             out.append((name, kind))
         return out
+
+
+# ------------------------------------------------------------------------------------------------ generic wrapper for arbitrary modules
+class _CopyToTP(torch.autograd.Function):
+    """Identity forward; the backward sums the input gradient over the tensor-parallel ranks."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+class _ReduceFromTP(torch.autograd.Function):
+    """Sum over the ranks forward; identity backward."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        x = x.contiguous()
+        dist.all_reduce(x, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class _GatherFromTP(torch.autograd.Function):
+    """Concatenate the ranks' last-dimension slices forward; keep this rank's slice of the gradient backward."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group, ctx.width = group, x.shape[-1]
+        parts = [torch.empty_like(x) for _ in range(dist.get_world_size(group))]
+        dist.all_gather(parts, x.contiguous(), group=group)
+        return torch.cat(parts, dim=-1)
+
+    @staticmethod
+    def backward(ctx, g):
+        r = dist.get_rank(ctx.group)
+        return g[..., r * ctx.width:(r + 1) * ctx.width].contiguous(), None
+
+
+class _ShardedTorchLinear(nn.Module):
+    def __init__(self, lin: nn.Linear, kind: str, group, world: int, rank: int):
+        super().__init__()
+        self.kind, self.group = kind, group
+        w = lin.weight.data
+        if kind == "column":
+            per = w.shape[0] // world
+            self.weight = nn.Parameter(w[rank * per:(rank + 1) * per].clone())
+            self.bias = None if lin.bias is None else nn.Parameter(lin.bias.data[rank * per:(rank + 1) * per].clone())
+        else:
+            per = w.shape[1] // world
+            self.lo, self.hi = rank * per, (rank + 1) * per
+            self.weight = nn.Parameter(w[:, self.lo:self.hi].clone())
+            self.bias = None if lin.bias is None else nn.Parameter(lin.bias.data.clone())       # added once, after the reduction
+
+    def forward(self, x):
+        if self.kind == "column":
+            y = torch.nn.functional.linear(_CopyToTP.apply(x, self.group), self.weight, self.bias)
+            return _GatherFromTP.apply(y, self.group)
+        y = _ReduceFromTP.apply(torch.nn.functional.linear(x[..., self.lo:self.hi], self.weight), self.group)
+        return y if self.bias is None else y + self.bias
+
+
+class TensorParallelWrapper(nn.Module):
+    """Tensor parallelism for any module built from ``nn.Linear`` layers (reference: ``TensorParallelWrapper``,
+    include/oil/distributed.h:68-79): every linear layer the manager's plan marks "column" keeps its slice of the output rows
+    (outputs are gathered), every "row" layer keeps its slice of the input columns (partial products are summed), everything
+    else stays replicated. Activations between layers are full-width, so the wrapped module's own forward code runs unchanged
+    and gives the single-process result; gradients are exact. This is the general path over ``torch.distributed`` (any
+    backend); the fused all-gather-GEMM / GEMM-reduce-scatter kernels serve ``TPDenseModel`` and ``TPDecoder``."""
+
+    def __init__(self, model: nn.Module, group=None, plan: Optional[List[tuple]] = None):
+        super().__init__()
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        named = [(n, tuple(m.weight.shape)) for n, m in model.named_modules() if isinstance(m, nn.Linear)]
+        plan = plan if plan is not None else TensorParallelManager.plan(None, named)
+        self.plan = dict(plan)
+        for name, kind in plan:
+            if kind == "replicate" or self.world == 1:
+                continue
+            parent, _, leaf = name.rpartition(".")
+            holder = model.get_submodule(parent) if parent else model
+            lin = getattr(holder, leaf)
+            dim = lin.weight.shape[0] if kind == "column" else lin.weight.shape[1]
+            if dim % self.world:
+                self.plan[name] = "replicate"
+                continue
+            setattr(holder, leaf, _ShardedTorchLinear(lin, kind, group, self.world, self.rank))
+        self.model = model
+
+    def forward(self, *args, **kw):
+        return self.model(*args, **kw)
+
+    def local_parameter_count(self) -> int:
+        return sum(p.numel() for p in self.model.parameters())

@@ -19,6 +19,7 @@ Mapping on a B200 node:
 from __future__ import annotations
 
 import threading
+from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional
 
 import torch
@@ -376,3 +377,147 @@ class ZeROOffloadManager:
             self._out = False
         e.step(grad_scale)
         self.offload_state()
+
+
+# ------------------------------------------------------------------------------------------------ shard optimizer and offloaded AdamW
+class ZeROOptimizer:
+    """Optimizer for parameter shards handed in one buffer at a time (reference: ``ZeROOptimizer``, include/oil/fsdp.h:233-268,
+    which keeps one Adafactor state per buffer, keyed by the buffer's address, over a 1 x N view of the shard). The state here
+    is the decoupled-weight-decay Adam moments of the shard, kept on the shard's device and keyed by its data pointer;
+    ``step_mixed`` updates an fp32 master shard and writes the rounded result into the low-precision shard. The caller
+    supplies the step number, so several shards can share one schedule."""
+
+    def __init__(self, lr: float = 1e-3, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8, weight_decay: float = 0.01,
+                 world_size: int = 1, world_rank: int = 0):
+        self.lr, self.beta1, self.beta2, self.eps, self.weight_decay = lr, beta1, beta2, eps, weight_decay
+        self.world_size, self.world_rank = world_size, world_rank
+        self._param_count = 0
+        self._state: Dict[int, tuple] = {}
+
+    def param_count(self) -> int:
+        return self._param_count
+
+    def set_param_count(self, n: int) -> None:
+        self._param_count = int(n)
+
+    def _moments(self, buf: torch.Tensor):
+        key = buf.data_ptr()
+        st = self._state.get(key)
+        if st is None or st[0].numel() != buf.numel():
+            st = (torch.zeros(buf.numel(), dtype=torch.float32, device=buf.device), torch.zeros(buf.numel(), dtype=torch.float32, device=buf.device))
+            self._state[key] = st
+        return st
+
+    @torch.no_grad()
+    def _update(self, master: torch.Tensor, grad: torch.Tensor, step_num: int, key_buf: torch.Tensor) -> None:
+        m, v = self._moments(key_buf)
+        g = grad.reshape(-1).float()
+        m.mul_(self.beta1).add_(g, alpha=1 - self.beta1)
+        v.mul_(self.beta2).addcmul_(g, g, value=1 - self.beta2)
+        t = max(1, int(step_num))
+        step = self.lr / (1 - self.beta1 ** t)
+        denom = (v / (1 - self.beta2 ** t)).sqrt_().add_(self.eps)
+        flat = master.view(-1)
+        flat.mul_(1 - self.lr * self.weight_decay).addcdiv_(m, denom, value=-step)
+
+    def step(self, param_shard: torch.Tensor, grad_shard: torch.Tensor, step_num: int) -> None:
+        if param_shard.dtype == torch.float32:
+            self._update(param_shard, grad_shard, step_num, param_shard)
+        else:                                            # no master given: update in fp32 and round once
+            tmp = param_shard.float()
+            self._update(tmp, grad_shard, step_num, param_shard)
+            param_shard.copy_(tmp)
+
+    def step_mixed(self, param_shard: torch.Tensor, fp32_master: torch.Tensor, grad_shard: torch.Tensor, step_num: int) -> None:
+        self._update(fp32_master, grad_shard, step_num, fp32_master)
+        param_shard.copy_(fp32_master.view_as(param_shard))
+
+    def state_bytes(self) -> int:
+        return sum(2 * m.numel() * 4 for m, _ in self._state.values())
+
+
+@dataclass
+class AdamWConfig:
+    learning_rate: float = 3e-4
+    beta1: float = 0.9
+    beta2: float = 0.999
+    eps: float = 1e-8
+    weight_decay: float = 0.01
+    grad_clip: float = 1.0
+    amsgrad: bool = False
+
+
+class AdamWOptimizer:
+    """AdamW over registered (parameter, gradient) pairs whose moments live in the host offload pool between steps
+    (reference: ``AdamWOptimizer``, include/oil/zero_offload.h:125-180). ``step`` clips the global gradient norm to
+    ``grad_clip``, brings each parameter's moments back (the next parameter's copy is started before the current update, so
+    the transfer overlaps it on a GPU), updates, and sends the moments out again. Returns the gradient norm before clipping."""
+
+    def __init__(self, cfg: Optional[AdamWConfig] = None, pool_bytes: int = 8 << 30, device=None):
+        self.cfg = cfg or AdamWConfig()
+        self.offload = CPUOffloadEngine(pool_bytes, device)
+        self._pairs: List[tuple] = []
+        self._vmax: Dict[int, torch.Tensor] = {}
+        self._step = 0
+
+    def add_parameter(self, param: torch.Tensor, grad: torch.Tensor) -> None:
+        i = len(self._pairs)
+        self._pairs.append((param, grad))
+        dev = param.device
+        self.offload.offload(f"m{i}", torch.zeros(param.numel(), dtype=torch.float32, device=dev))
+        self.offload.offload(f"v{i}", torch.zeros(param.numel(), dtype=torch.float32, device=dev))
+
+    def zero_grad(self) -> None:
+        for _, g in self._pairs:
+            g.zero_()
+
+    @torch.no_grad()
+    def clip_gradients(self, max_norm: float) -> float:
+        if not self._pairs:
+            return 0.0
+        total = float(torch.sqrt(sum(g.float().square().sum() for _, g in self._pairs)))
+        if max_norm > 0 and total > max_norm:
+            for _, g in self._pairs:
+                g.mul_(max_norm / (total + 1e-6))
+        return total
+
+    def state_memory_bytes(self) -> int:
+        return sum(2 * p.numel() * 4 for p, _ in self._pairs) + sum(v.numel() * 4 for v in self._vmax.values())
+
+    def step_count(self) -> int:
+        return self._step
+
+    def learning_rate(self) -> float:
+        return self.cfg.learning_rate
+
+    def zero_manager(self) -> CPUOffloadEngine:
+        return self.offload
+
+    @torch.no_grad()
+    def step(self) -> float:
+        c = self.cfg
+        norm = self.clip_gradients(c.grad_clip)
+        self._step += 1
+        t = self._step
+        if self._pairs:
+            self.offload.prefetch("m0")
+            self.offload.prefetch("v0")
+        for i, (p, g) in enumerate(self._pairs):
+            m, v = self.offload.fetch(f"m{i}"), self.offload.fetch(f"v{i}")
+            if i + 1 < len(self._pairs):
+                self.offload.prefetch(f"m{i + 1}")
+                self.offload.prefetch(f"v{i + 1}")
+            gf = g.reshape(-1).float()
+            m.mul_(c.beta1).add_(gf, alpha=1 - c.beta1)
+            v.mul_(c.beta2).addcmul_(gf, gf, value=1 - c.beta2)
+            second = v
+            if c.amsgrad:
+                vm = self._vmax.setdefault(i, torch.zeros_like(v))
+                torch.maximum(vm, v, out=vm)
+                second = vm
+            denom = (second / (1 - c.beta2 ** t)).sqrt_().add_(c.eps)
+            upd = p.reshape(-1).float().mul_(1 - c.learning_rate * c.weight_decay).addcdiv_(m, denom, value=-c.learning_rate / (1 - c.beta1 ** t))
+            p.copy_(upd.view_as(p))
+            self.offload.offload(f"m{i}", m)
+            self.offload.offload(f"v{i}", v)
+        return norm

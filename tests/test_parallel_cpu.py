@@ -391,3 +391,86 @@ def test_expert_parallel_engine_syncs_only_replicated_and_clips_jointly(tmp_path
         ds = r[k]["after"]["shared.weight"] - r[k]["before"]["shared.weight"]
         assert torch.equal(torch.sign(ds), -torch.sign(rep["shared.weight"]))
     assert 0 < clip <= 1
+
+
+# ------------------------------------------------------------------------------------------------ generic tensor-parallel wrapper, shard optimizers
+class _Mlp(torch.nn.Module):
+    def __init__(self):
+        super().__init__()
+        torch.manual_seed(5)
+        self.up_proj, self.down_proj = torch.nn.Linear(12, 32), torch.nn.Linear(32, 12)
+        self.q_proj, self.other = torch.nn.Linear(12, 12, bias=False), torch.nn.Linear(12, 7)
+
+    def forward(self, x):
+        return self.other(self.down_proj(torch.relu(self.up_proj(self.q_proj(x)))))
+
+
+def _tp_wrapper_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from innova_b200.parallel.tensor_parallel import TensorParallelWrapper
+    m = TensorParallelWrapper(_Mlp())
+    torch.manual_seed(9)
+    x = torch.randn(3, 5, 12, requires_grad=True)
+    y = m(x)
+    y.square().sum().backward()
+    torch.save({"y": y.detach(), "dx": x.grad, "plan": m.plan, "n": m.local_parameter_count(),
+                "g_up": m.model.up_proj.weight.grad, "g_down": m.model.down_proj.weight.grad, "g_other": m.model.other.weight.grad}, out + f".{rank}")
+    _shutdown()
+
+
+def test_generic_tensor_parallel_wrapper_matches_single_process(tmp_path):
+    out = str(tmp_path / "tpw")
+    mp.spawn(_tp_wrapper_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    ref = _Mlp()
+    torch.manual_seed(9)
+    x = torch.randn(3, 5, 12, requires_grad=True)
+    y = ref(x)
+    y.square().sum().backward()
+    r = [torch.load(out + f".{i}") for i in range(2)]
+    assert r[0]["plan"] == {"up_proj": "column", "down_proj": "row", "q_proj": "column", "other": "replicate"}
+    full = sum(p.numel() for p in ref.parameters())
+    assert r[0]["n"] < full and r[0]["n"] == (12 * 32 + 32) // 2 + 32 * 12 // 2 + 12 + 12 * 12 // 2 + 12 * 7 + 7
+    for i in range(2):
+        assert torch.allclose(r[i]["y"], y.detach(), atol=1e-5) and torch.allclose(r[i]["dx"], x.grad, atol=1e-4)
+        assert torch.allclose(r[i]["g_up"], ref.up_proj.weight.grad[i * 16:(i + 1) * 16], atol=1e-4)
+        assert torch.allclose(r[i]["g_down"], ref.down_proj.weight.grad[:, i * 16:(i + 1) * 16], atol=1e-4)
+        assert torch.allclose(r[i]["g_other"], ref.other.weight.grad, atol=1e-4)
+
+
+def test_shard_optimizer_and_offloaded_adamw_match_torch():
+    from innova_b200.parallel.zero import AdamWConfig, AdamWOptimizer, ZeROOptimizer
+    torch.manual_seed(0)
+    w0, grads = torch.randn(50), [torch.randn(50) for _ in range(4)]
+    ref = w0.clone().requires_grad_(True)
+    topt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.1)
+    z = ZeROOptimizer(1e-2, 0.9, 0.99, 1e-8, 0.1, world_size=2, world_rank=1)
+    z.set_param_count(50)
+    shard, master, low = w0.clone(), w0.clone(), w0.clone().bfloat16()
+    for t, g in enumerate(grads, 1):
+        ref.grad = g.clone()
+        topt.step()
+        z.step(shard, g, t)
+        z.step_mixed(low, master, g, t)
+    assert torch.allclose(shard, ref.detach(), atol=1e-6) and torch.allclose(master, ref.detach(), atol=1e-6) and torch.equal(low, master.bfloat16())
+    assert z.param_count() == 50 and z.state_bytes() == 2 * 2 * 50 * 4
+    for ams in (False, True):
+        ps = [torch.randn(6, 5), torch.randn(7)]
+        gs = [torch.zeros_like(p) for p in ps]
+        refs = [p.clone().requires_grad_(True) for p in ps]
+        topt = torch.optim.AdamW(refs, lr=3e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, amsgrad=ams)
+        opt = AdamWOptimizer(AdamWConfig(learning_rate=3e-3, grad_clip=0.5, amsgrad=ams), pool_bytes=1 << 20)
+        for p, g in zip(ps, gs):
+            opt.add_parameter(p, g)
+        for step in range(3):
+            new = [torch.randn_like(p) * (3.0 if step == 1 else 0.05) for p in ps]
+            for g, n, r in zip(gs, new, refs):
+                g.copy_(n)
+                r.grad = n.clone()
+            want = float(torch.nn.utils.clip_grad_norm_(refs, 0.5))
+            topt.step()
+            assert opt.step() == pytest.approx(want, rel=1e-5)
+        assert all(torch.allclose(p, r.detach(), atol=1e-6) for p, r in zip(ps, refs)) and opt.step_count() == 3
+        assert opt.state_memory_bytes() == (2 + ams) * 37 * 4 and opt.zero_manager().used == 2 * 37 * 4 and opt.learning_rate() == 3e-3
+        opt.zero_grad()
+        assert all(float(g.abs().sum()) == 0 for g in gs)
