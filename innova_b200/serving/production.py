@@ -188,6 +188,7 @@ class ModelServer:
                 outs = self.generate_batch([j.prompt for j in jobs], max(j.max_tokens for j in jobs))
             except Exception as e:
                 outs = [e] * len(jobs)
+                self._errors = getattr(self, "_errors", 0) + len(jobs)
             now = time.time()
             self.batches += 1
             for j, o in zip(jobs, outs):
@@ -207,3 +208,87 @@ class ModelServer:
             self._stop = True
             self._cv.notify_all()
         self._thread.join(timeout=2)
+
+    # -- the rest of the reference's server surface (include/oil/production.h:20-142)
+    def is_running(self) -> bool:
+        return self._thread.is_alive() and not self._stop
+
+    def set_batch_size(self, bs: int) -> None:
+        self.max_batch = max(1, int(bs))
+
+    def set_queue_wait_ms(self, ms: float) -> None:
+        self.max_wait_s = max(0.0, ms / 1e3)
+
+    def submit_with_callback(self, prompt, max_tokens: int = 64, priority: int = 0,
+                             callback: Optional[Callable[[Any, Any], None]] = None) -> int:
+        """Queues a request and returns its id; ``callback(prompt, result)`` runs on a watcher thread once the batch that
+        carried it has finished (the worker thread itself never runs user code)."""
+        job = self.submit(prompt, max_tokens, priority)
+        if callback is not None:
+            def watch():
+                job.event.wait()
+                callback(prompt, job.result)
+            threading.Thread(target=watch, daemon=True).start()
+        return job.key[1]
+
+    def metrics(self) -> Dict[str, float]:
+        lat = self.latencies
+        pct = self.latency_percentiles()
+        errors = getattr(self, "_errors", 0)
+        return {"total_requests": len(lat), "total_errors": errors, "batches": self.batches, "queued": len(self._q),
+                "avg_latency_ms": 1e3 * sum(lat) / len(lat) if lat else 0.0, "p50_ms": 1e3 * pct["p50"], "p95_ms": 1e3 * pct["p95"],
+                "p99_ms": 1e3 * pct["p99"], "avg_batch": len(lat) / self.batches if self.batches else 0.0}
+
+    def health_json(self) -> str:
+        return json.dumps({"status": "ok" if self.is_running() else "stopped", "model_loaded": self.generate_batch is not None,
+                           "queued": len(self._q), "max_batch": self.max_batch})
+
+    def metrics_json(self) -> str:
+        return json.dumps(self.metrics())
+
+    def load_model(self, loader: Callable[[], Callable[[List[Any], int], List[Any]]]) -> bool:
+        """Swaps the batch function for the one ``loader`` returns; queued requests are served by the new one. False (and the
+        old model kept) when the loader raises."""
+        try:
+            fn = loader()
+        except Exception:   # noqa: BLE001 - a failed load must not take the server down
+            return False
+        with self._cv:
+            self.generate_batch = fn
+        return True
+
+    def unload_model(self) -> None:
+        def unloaded(prompts, max_tokens):
+            raise RuntimeError("no model loaded")
+        with self._cv:
+            self.generate_batch = unloaded
+
+    def is_model_loaded(self) -> bool:
+        return getattr(self.generate_batch, "__name__", "") != "unloaded"
+
+
+@dataclass
+class BatchConsolidationResult:
+    request_ids: List[int]
+    batched_input: Any          # [B, max_len] token ids, right-padded
+    batched_positions: Any      # [B, max_len] positions (0 where padded)
+    seq_lens: List[int]
+    offsets: List[int]          # start of each request in the concatenation of the unpadded sequences
+
+
+def consolidate_batch(requests: List[tuple], pad_id: int = 0) -> BatchConsolidationResult:
+    """``requests`` is [(request id, token ids)]: one right-padded id matrix with positions, the true lengths, and the offsets
+    the sequences would have if packed back to back (reference: ``ModelServer::consolidate_batch``,
+    include/oil/production.h:58-64,128)."""
+    import torch
+    lens = [len(ids) for _, ids in requests]
+    width = max(lens, default=0)
+    inp = torch.full((len(requests), width), pad_id, dtype=torch.long)
+    pos = torch.zeros(len(requests), width, dtype=torch.long)
+    offsets, run = [], 0
+    for r, (_, ids) in enumerate(requests):
+        inp[r, : len(ids)] = torch.as_tensor(list(ids), dtype=torch.long)
+        pos[r, : len(ids)] = torch.arange(len(ids))
+        offsets.append(run)
+        run += len(ids)
+    return BatchConsolidationResult([rid for rid, _ in requests], inp, pos, lens, offsets)

@@ -113,3 +113,31 @@ def test_model_server_batches_and_orders_by_priority():
     assert ms.generate("solo", timeout=5) == "SOLO"
     assert any(len(b) > 1 for b in seen) and ms.latency_percentiles()["p99"] > 0
     ms.stop()
+
+
+def test_model_server_surface_metrics_callbacks_and_model_swap():
+    import json
+    import threading
+    from innova_b200.serving.production import ModelServer, consolidate_batch
+    srv = ModelServer(lambda prompts, n: [p.upper() for p in prompts], max_batch=4, max_wait_s=0.01)
+    try:
+        assert srv.is_running() and srv.is_model_loaded() and json.loads(srv.health_json())["status"] == "ok"
+        got, done = {}, threading.Event()
+        rid = srv.submit_with_callback("abc", 8, 0, lambda p, r: (got.update({p: r}), done.set()))
+        assert rid >= 1 and done.wait(5) and got == {"abc": "ABC"} and srv.generate("x") == "X"
+        m = json.loads(srv.metrics_json())
+        assert m["total_requests"] == 2 and m["total_errors"] == 0 and m["batches"] >= 1 and m["p99_ms"] >= m["p50_ms"] >= 0
+        srv.set_batch_size(2)
+        srv.set_queue_wait_ms(1)
+        assert srv.max_batch == 2 and srv.max_wait_s == 0.001
+        assert srv.load_model(lambda: (lambda prompts, n: [p[::-1] for p in prompts])) and srv.generate("abc") == "cba"
+        assert not srv.load_model(lambda: 1 / 0) and srv.generate("abc") == "cba"            # a failed load keeps the old model
+        srv.unload_model()
+        assert not srv.is_model_loaded() and isinstance(srv.generate("abc"), RuntimeError) and srv.metrics()["total_errors"] == 1
+    finally:
+        srv.stop()
+    assert not srv.is_running() and json.loads(srv.health_json())["status"] == "stopped"
+    b = consolidate_batch([(7, [5, 6, 7]), (9, [1]), (11, [2, 3])], pad_id=0)
+    assert b.request_ids == [7, 9, 11] and b.seq_lens == [3, 1, 2] and b.offsets == [0, 3, 4]
+    assert b.batched_input.tolist() == [[5, 6, 7], [1, 0, 0], [2, 3, 0]] and b.batched_positions.tolist() == [[0, 1, 2], [0, 0, 0], [0, 1, 0]]
+    assert consolidate_batch([]).batched_input.shape == (0, 0)
