@@ -19,8 +19,11 @@ from typing import List, Optional
 import torch
 
 from .. import _native
+from ..utils.telemetry import sops_global
 from .generator import Generator
 from .sampler import Sampler, SamplingParams
+
+_SOPS = sops_global()
 
 vp, i32, i64, f32 = _native.vp, _native.i32, _native.i64, _native.f32
 _native.register_cuda_sigs({"inv_spec_verify": [vp, vp, vp, vp, i32, i32, i32, i64, i64, f32, i32, vp, vp, vp]})
@@ -185,6 +188,8 @@ class SpeculativeDecoder:
             self.stats.accepted += n
             self.stats.rounds += 1
             self.stats.history.append(n)
+            _SOPS.speculative_propose(G)            # process-wide speculative counters (utils.telemetry.sops_report)
+            _SOPS.speculative_accept(n)
             if self.adaptive:
                 self.adapt_gamma(n / G)
             if eos_id is not None and eos_id in out[-(n + 1):]:

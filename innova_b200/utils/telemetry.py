@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import contextlib
 import heapq
+import threading
 import time
 from collections import defaultdict
 from dataclasses import dataclass, field
@@ -250,3 +251,200 @@ class ServerMetrics:
         for q in (0.5, 0.95, 0.99):
             lines.append(f'{prefix}_latency_seconds{{quantile="{q}"}} {self.percentile(q):.6f}')
         return "\n".join(lines) + "\n"
+
+
+# ------------------------------------------------------------------------------------------------ per-format counters and the global hooks
+class SopsCounter:
+    """Information operations (elements x 32 / bits per weight) and elements between ``start`` and ``stop`` (reference:
+    ``SopsCounter``, include/oil/sops.h:113-186). Time is the wall clock on the host; callers that time device work pass the
+    measured seconds to ``stop``."""
+
+    def __init__(self):
+        self.reset()
+
+    def reset(self) -> None:
+        self.total_info_ops, self.total_elements = 0.0, 0
+        self._t0, self._elapsed = None, 0.0
+
+    def start(self) -> None:
+        self._t0 = time.perf_counter()
+
+    def stop(self, seconds: Optional[float] = None) -> None:
+        if seconds is not None:
+            self._elapsed += seconds
+        elif self._t0 is not None:
+            self._elapsed += time.perf_counter() - self._t0
+        self._t0 = None
+
+    def record(self, fmt, count: int) -> None:
+        """``fmt`` is a format name or registry index; unknown formats are ignored."""
+        try:
+            self.record_iw(info_weight(fmt), count)
+        except Exception:   # noqa: BLE001 - an unknown format index must not break the timed path
+            pass
+
+    def record_iw(self, weight: float, count: int) -> None:
+        self.total_info_ops += count * weight
+        self.total_elements += int(count)
+
+    def elapsed_sec(self) -> float:
+        return self._elapsed
+
+    def raw_ops_per_sec(self) -> float:
+        return self.total_info_ops / self._elapsed if self._elapsed > 0 else 0.0
+
+    def sops(self) -> float:
+        return self.raw_ops_per_sec() / 1e21
+
+    def effective_gflops(self) -> float:
+        return self.raw_ops_per_sec() / 1e9
+
+
+@dataclass
+class StabilityPlasticityParams:
+    forgetting_weight: float
+    current_lr_factor: float
+    stability_lr_factor: float
+    plasticity_lr_factor: float
+    forgetting_threshold: float
+
+
+@dataclass
+class SopsReport:
+    training_sops: float = 0.0
+    inference_sops: float = 0.0
+    quantization_sops: float = 0.0
+    effective_training_gflops: float = 0.0
+    effective_inference_gflops: float = 0.0
+    small_batch_calls: int = 0
+    small_batch_avg_sops: float = 0.0
+    stability_updates: int = 0
+    stability_factor: float = 1.0
+    plasticity_factor: float = 1.0
+    draft_k: int = 1
+    acceptance_rate: float = 0.0
+    speculative_accepted: int = 0
+    speculative_proposed: int = 0
+    speculative_efficiency: float = 0.0
+
+
+class SopsGlobalState:
+    """The process-wide counters the training, inference, quantisation, continual-learning and speculative-decoding code
+    report into (reference: include/oil/sops_integration.h:29-230). One lock guards every update: hooks are called from
+    serving threads as well as from the training loop."""
+
+    def __init__(self):
+        self._lock = threading.Lock()
+        self.enabled = True
+        self.reset()
+
+    def reset(self) -> None:
+        with getattr(self, "_lock", threading.Lock()):
+            self.training, self.inference, self.quantization = SopsCounter(), SopsCounter(), SopsCounter()
+            self.small_batch_calls = self.small_batch_elements = 0
+            self.small_batch_avg_sops = 0.0
+            self.stability_plasticity_updates = 0
+            self.current_stability_factor = self.current_plasticity_factor = 1.0
+            self.current_draft_k, self.current_acceptance_rate = 1, 0.0
+            self.speculative_accepted = self.speculative_proposed = 0
+
+    # -- phase brackets
+    def _stop(self, counter: SopsCounter, fmt, elements: int, seconds: Optional[float]) -> None:
+        if self.enabled:
+            with self._lock:
+                counter.stop(seconds)
+                counter.record(fmt, elements)
+
+    def training_start(self) -> None:
+        if self.enabled:
+            self.training.start()
+
+    def training_stop(self, fmt, elements: int, seconds: Optional[float] = None) -> None:
+        self._stop(self.training, fmt, elements, seconds)
+
+    def training_stop_mixed(self, formats, counts, seconds: Optional[float] = None) -> None:
+        """A step over weights in several formats: one (format, element count) pair per tier."""
+        if self.enabled:
+            with self._lock:
+                self.training.stop(seconds)
+                for f, c in zip(formats, counts):
+                    self.training.record(f, c)
+
+    def inference_start(self) -> None:
+        if self.enabled:
+            self.inference.start()
+
+    def inference_stop(self, fmt, elements: int, seconds: Optional[float] = None) -> None:
+        self._stop(self.inference, fmt, elements, seconds)
+
+    def quantize_start(self) -> None:
+        if self.enabled:
+            self.quantization.start()
+
+    def quantize_stop(self, fmt, elements: int, seconds: Optional[float] = None) -> None:
+        self._stop(self.quantization, fmt, elements, seconds)
+
+    # -- the other hooks
+    def small_batch(self, fmt, elements: int, seconds: float) -> None:
+        """Running mean of the SOPS of small-batch (decode-sized) calls."""
+        if not self.enabled:
+            return
+        s = sops(elements, seconds, fmt) / 1e21
+        with self._lock:
+            self.small_batch_calls += 1
+            self.small_batch_elements += elements
+            self.small_batch_avg_sops += (s - self.small_batch_avg_sops) / self.small_batch_calls
+
+    def stability_plasticity(self, forgetting_weight: float, base_lr: float, stability_factor: float, plasticity_factor: float,
+                             threshold: float) -> StabilityPlasticityParams:
+        """Learning-rate factor of a continual-learning step: above the forgetting threshold the stability factor grows by the
+        excess and the plasticity factor shrinks by half the excess (both kept in [0.1, 5]); the step uses the stability
+        factor when forgetting is above the threshold, the plasticity factor otherwise."""
+        sf, pf = stability_factor, plasticity_factor
+        if forgetting_weight > threshold:
+            sf *= 1.0 + (forgetting_weight - threshold)
+            pf *= 1.0 - 0.5 * (forgetting_weight - threshold)
+        sf, pf = min(5.0, max(0.1, sf)), min(5.0, max(0.1, pf))
+        if self.enabled:
+            with self._lock:
+                self.stability_plasticity_updates += 1
+                self.current_stability_factor, self.current_plasticity_factor = sf, pf
+        return StabilityPlasticityParams(forgetting_weight, base_lr * (sf if forgetting_weight > threshold else pf), sf, pf, threshold)
+
+    def draft_length_tune(self, current_k: int, acceptance_rate: float, min_k: int = 1, max_k: int = 8, target_rate: float = 0.7) -> int:
+        """One more draft token when acceptance is more than 0.05 above the target, one fewer when more than 0.10 below."""
+        k = current_k + (acceptance_rate > target_rate + 0.05) - (acceptance_rate < target_rate - 0.10)
+        k = min(max_k, max(min_k, k))
+        if self.enabled:
+            with self._lock:
+                self.current_acceptance_rate, self.current_draft_k = acceptance_rate, k
+        return k
+
+    def speculative_propose(self, count: int) -> None:
+        if self.enabled:
+            with self._lock:
+                self.speculative_proposed += count
+
+    def speculative_accept(self, count: int) -> None:
+        if self.enabled:
+            with self._lock:
+                self.speculative_accepted += count
+
+    def report(self) -> SopsReport:
+        with self._lock:
+            prop, acc = self.speculative_proposed, self.speculative_accepted
+            return SopsReport(self.training.sops(), self.inference.sops(), self.quantization.sops(), self.training.effective_gflops(),
+                              self.inference.effective_gflops(), self.small_batch_calls, self.small_batch_avg_sops,
+                              self.stability_plasticity_updates, self.current_stability_factor, self.current_plasticity_factor,
+                              self.current_draft_k, self.current_acceptance_rate, acc, prop, acc / prop if prop else 0.0)
+
+
+_SOPS_STATE = SopsGlobalState()
+
+
+def sops_global() -> SopsGlobalState:
+    return _SOPS_STATE
+
+
+def sops_report() -> SopsReport:
+    return _SOPS_STATE.report()
