@@ -287,6 +287,77 @@ class CodeGenerator:
         threads = 128 if (kind in _BODY and N <= 1024) else 256
         return self.generate_optimized_kernel(KernelSpec(kind, M, N, K, vec=vec, threads=threads))
 
+    # -- one generator per operator, as the reference names them (include/oil/code_gen.h:103-121); each returns source text
+    def generate_gemm(self, M: int, N: int, K: int) -> str:
+        return self.specialize_for_shape("gemm", M, N, K).source_code
+
+    def generate_rms_norm(self, dim: int) -> str:
+        return self.specialize_for_shape("rms_norm", 0, dim).source_code
+
+    def generate_layer_norm(self, dim: int) -> str:
+        return self.specialize_for_shape("layer_norm", 0, dim).source_code
+
+    def generate_softmax(self, dim: int) -> str:
+        return self.specialize_for_shape("softmax", 0, dim).source_code
+
+    def generate_relu(self, n: int) -> str:
+        return self.specialize_for_shape("relu", 0, n).source_code
+
+    def generate_silu(self, n: int) -> str:
+        return self.specialize_for_shape("silu", 0, n).source_code
+
+    def generate_gelu(self, n: int) -> str:
+        return self.specialize_for_shape("gelu", 0, n).source_code
+
+    def generate_add(self, n: int) -> str:
+        return self.specialize_for_shape("add", 0, n).source_code
+
+    def generate_mul(self, n: int) -> str:
+        return self.specialize_for_shape("mul", 0, n).source_code
+
+    def generate_residual_add(self, n: int) -> str:
+        return self.specialize_for_shape("residual_add", 0, n).source_code
+
+    def generate_scale(self, n: int, scale_val: float) -> str:
+        vec = 4 if n % 4 == 0 else (2 if n % 2 == 0 else 1)
+        return self.generate_optimized_kernel(KernelSpec("scale", 0, n, 0, vec=vec, scale=scale_val,
+                                                         name=f"gen_scale_n{n}_s{abs(hash(float(scale_val))) % 10 ** 8}")).source_code
+
+    def generate_embedding_lookup(self, vocab_size: int, embed_dim: int) -> str:
+        return self.specialize_for_shape("embedding_lookup", vocab_size, embed_dim).source_code
+
+    def generate_quantize_dequantize(self, n: int, block: int = 32, levels: int = 16) -> str:
+        return self.generate_optimized_kernel(KernelSpec("quantize_dequantize", 0, n, 0, block=block, levels=levels,
+                                                         name=f"gen_qdq_n{n}_b{block}_l{levels}")).source_code
+
+    def generate_format_dispatch(self, op_name: str, formats: Sequence[str]) -> str:
+        """A host function ``<op>_dispatch(format, ...)`` that switches on the weight format id and calls ``<op>_<format>``
+        (declared ``extern "C"``; the caller links the per-format kernels). Unknown ids return -1."""
+        from ..formats import oil
+        decl = "".join(f'extern "C" int {op_name}_{f.lower()}(const void* w, const float* x, float* y, long n, void* stream);\n' for f in formats)
+        cases = "".join(f"    case {oil.format_id(f)}: return {op_name}_{f.lower()}(w, x, y, n, stream);  // {f}\n" for f in formats)
+        return (f"{decl}extern \"C\" int {op_name}_dispatch(int format, const void* w, const float* x, float* y, long n, void* stream) {{\n"
+                f"  switch (format) {{\n{cases}    default: return -1;\n  }}\n}}\n")
+
+    def generate_format_branch(self, op_name: str, fmt: str, dim: int) -> str:
+        from ..formats import oil
+        return f"if (format == {oil.format_id(fmt)}) return {op_name}_{fmt.lower()}(w, x, y, {int(dim)}L, stream);  // {fmt}\n"
+
+    def generate_includes(self, includes: Sequence[str]) -> str:
+        return "".join(f"#include <{h}>\n" for h in includes)
+
+    def generate_loop_header(self, var: str, start: int, end: int, step: str = "1") -> str:
+        inc = f"++{var}" if step == "1" else f"{var} += {step}"
+        return f"for (long {var} = {start}; {var} < {end}; {inc})"
+
+    def generate_if_block(self, condition: str, body: str, indent_level: int = 1) -> str:
+        pad = "  " * indent_level
+        return f"{pad}if ({condition}) {{\n{self.generate_block(body, indent_level + 1)}{pad}}}\n"
+
+    def generate_block(self, body: str, indent_level: int) -> str:
+        pad = "  " * indent_level
+        return "".join(pad + line + "\n" for line in body.strip("\n").split("\n"))
+
     def generate_full_source(self, kernels: Sequence[GeneratedKernel]) -> str:
         return _HEADER + "".join(k.source_code for k in kernels)
 

@@ -53,3 +53,33 @@ def test_gpu_auto_optimize_picks_a_correct_variant(tmp_path):
     cg = CodeGenerator(str(tmp_path))
     best = cg.auto_optimize([KernelSpec("silu", N=1 << 20)])
     assert len(best) == 1 and best[0].validated and best[0].benchmark_ms > 0
+
+
+def test_named_generators_and_format_dispatch(tmp_path):
+    cg = CodeGenerator(str(tmp_path))
+    assert "constexpr int M = 64, N = 96, K = 32" in cg.generate_gemm(64, 96, 32) and "rsqrtf(s2 / N" in cg.generate_rms_norm(768)
+    assert "mean" in cg.generate_layer_norm(512) and "__expf(v[j] - mx)" in cg.generate_softmax(1000)
+    for gen, expr in ((cg.generate_relu, "fmaxf(x, 0.f)"), (cg.generate_silu, "__expf(-x)"), (cg.generate_gelu, "tanhf"), (cg.generate_add, "x + y"),
+                      (cg.generate_mul, "x * y"), (cg.generate_residual_add, "x + y")):
+        assert expr in gen(4096)
+    assert "x * 0.25f" in cg.generate_scale(1000, 0.25) and "x * 3.0f" in cg.generate_scale(1000, 3.0)       # one kernel per scale value
+    assert "32000 - 1" in cg.generate_embedding_lookup(32000, 256) and "(256 - 1)" in cg.generate_quantize_dequantize(4096, 64, 256)
+    src = cg.generate_format_dispatch("gemv", ["OIL4", "OIL8"])
+    assert 'extern "C" int gemv_oil4(' in src and "case 3: return gemv_oil4(w, x, y, n, stream);  // OIL4" in src and "default: return -1;" in src
+    assert cg.generate_format_branch("gemv", "OIL8", 512).startswith("if (format == 4) return gemv_oil8(w, x, y, 512L, stream);")
+    assert cg.generate_includes(["cmath", "vector"]) == "#include <cmath>\n#include <vector>\n"
+    assert cg.generate_loop_header("i", 0, 10) == "for (long i = 0; i < 10; ++i)" and cg.generate_loop_header("i", 0, 10, "4").endswith("i += 4)")
+    assert cg.generate_if_block("x > 0", "y = x;\nz = y;", 1) == "  if (x > 0) {\n    y = x;\n    z = y;\n  }\n"
+
+
+@needs_nvcc
+def test_format_dispatch_source_compiles_as_host_code(tmp_path):
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("no C++ compiler")
+    cg = CodeGenerator(str(tmp_path))
+    src = cg.generate_format_dispatch("gemv", ["OIL1", "OIL4", "OIL8", "OIL32"])
+    path = tmp_path / "dispatch.cpp"
+    path.write_text(src)
+    assert subprocess.run(["g++", "-std=c++17", "-c", "-o", str(tmp_path / "d.o"), str(path)], capture_output=True).returncode == 0
