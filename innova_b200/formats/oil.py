@@ -320,3 +320,66 @@ def read_idx(path: str) -> List[str]:
         out.append(raw[at:end].decode())
         at = end + 1
     return out
+
+
+class OILIdxWriter:
+    """Object form of ``write_idx`` (reference: ``OILIdxWriter``, include/oil/oil_format.h:122-135)."""
+
+    def __init__(self, path: str):
+        self.path, self._open = str(path), True
+
+    def write_idx(self, version: int, tensor_names: Iterable[str]) -> None:
+        if not self._open:
+            raise IOError(f"{self.path}: writer is closed")
+        write_idx(self.path, tensor_names, version)
+
+    def close(self) -> None:
+        self._open = False
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
+class OILIdxReader:
+    """Object form of ``read_idx`` (reference: ``OILIdxReader``, include/oil/oil_format.h:137-159): ``valid()`` is False for a
+    missing or foreign file, ``read_idx()`` returns the names and raises ``CorruptIndexError`` when a stored hash does not
+    match its name."""
+
+    def __init__(self, path: str):
+        import os
+        self.path, self._version, self._num, self._names = str(path), 0, 0, None
+        self._valid = False
+        try:
+            with open(self.path, "rb") as f:
+                head = f.read(24)
+            self._valid = os.path.getsize(self.path) >= 16 and head.startswith(b"InNovaIDX")
+        except OSError:
+            return
+        if self._valid:
+            try:
+                ver = C.c_uint32(0)
+                cap = os.path.getsize(self.path) + 16
+                n = lib().oilidx_read(self.path.encode(), C.byref(ver), C.create_string_buffer(cap), cap)
+                self._version, self._num = int(ver.value), max(0, int(n)) if n > -100 else -int(n) - 100
+                self._valid = n >= 0 or n <= -100
+            except Exception:   # noqa: BLE001
+                self._valid = False
+
+    def valid(self) -> bool:
+        return self._valid
+
+    def version(self) -> int:
+        return self._version
+
+    def num_tensors(self) -> int:
+        if self._names is not None:
+            return len(self._names)
+        return self._num
+
+    def read_idx(self) -> List[str]:
+        if self._names is None:
+            self._names = read_idx(self.path)
+        return list(self._names)

@@ -310,3 +310,144 @@ class SpeculativeDecoderV2:
                 break
         self.stats.wall_time_sec += time.perf_counter() - t0
         return out[:max_tokens]
+
+
+# ------------------------------------------------------------------------------------------------ model-agnostic decoder over two interfaces
+class DraftModel:
+    """Anything that can continue a token context (reference: ``DraftModel``, include/oil/speculative_decoder.h:26-32)."""
+
+    def propose(self, context: List[int], num_tokens: int) -> List[int]:
+        raise NotImplementedError
+
+    def vocab_size(self) -> int:
+        raise NotImplementedError
+
+
+class TargetModel:
+    """Anything that scores the next token of a context (reference: ``TargetModel``, :37-42). ``logits_for_drafts`` scores
+    every draft position at once; the default loops over ``logits``, a model with a real forward pass overrides it with ONE
+    pass over context + drafts (row i of that pass is the distribution after ``context + drafts[:i]``)."""
+
+    def logits(self, context: List[int]) -> List[float]:
+        raise NotImplementedError
+
+    def vocab_size(self) -> int:
+        raise NotImplementedError
+
+    def logits_for_drafts(self, context: List[int], drafts: List[int]) -> List[List[float]]:
+        return [self.logits(context + drafts[:i]) for i in range(len(drafts))]
+
+
+@dataclass
+class KVCheckpoint:
+    positions: List[int] = field(default_factory=list)
+    kv_context_len: int = 0
+    saved_k: list = field(default_factory=list)
+    saved_v: list = field(default_factory=list)
+    valid: bool = False
+
+
+@dataclass
+class SpecStepResult:
+    tokens_accepted: List[int] = field(default_factory=list)
+    tokens_rejected: int = 0
+    total_proposed: int = 0
+    acceptance_rate: float = 0.0
+
+
+@dataclass
+class SpecConfig:
+    draft_k: int = 3
+    min_draft_k: int = 1
+    max_draft_k: int = 8
+    target_acceptance_rate: float = 0.7
+    auto_tune_window: int = 100
+    temperature: float = 1.0
+    top_k: int = 50
+    top_p: float = 0.9
+
+
+class InterfaceSpeculativeDecoder:
+    """Exact-match speculative decoding between any ``DraftModel`` and ``TargetModel`` (reference: ``SpeculativeDecoder``,
+    include/oil/speculative_decoder.h:55-127, src/speculative_decoder.cpp:67-166): a draft token is kept while it equals the
+    token the target would emit (arg-max at temperature 0, else a seeded top-k / top-p draw); the first mismatch is replaced
+    by the target's token and ends the step. The draft length follows the running acceptance rate through the process-wide
+    ``draft_length_tune`` hook. A cache object with ``context_len()`` and ``resize(n)`` is rewound to the kept prefix.
+
+    The target is asked for all draft positions in one ``logits_for_drafts`` call, so a model-backed target runs one forward
+    per step where the reference runs one per draft token."""
+
+    def __init__(self, cfg: Optional[SpecConfig] = None, seed: int = 42):
+        self.cfg = cfg or SpecConfig()
+        self.total_accepted = self.total_proposed = 0
+        self._window: List[float] = []
+        self._gen = torch.Generator().manual_seed(seed)
+
+    def current_draft_k(self) -> int:
+        return self.cfg.draft_k
+
+    def acceptance_rate(self) -> float:
+        return self.total_accepted / self.total_proposed if self.total_proposed else 0.0
+
+    def update_draft_k(self, new_k: int) -> None:
+        self.cfg.draft_k = max(self.cfg.min_draft_k, min(self.cfg.max_draft_k, int(new_k)))
+
+    def sample_token(self, logits) -> int:
+        lg = torch.as_tensor(logits, dtype=torch.float32)
+        if self.cfg.temperature <= 0:
+            return int(lg.argmax())
+        k = min(max(1, self.cfg.top_k), lg.numel())
+        vals, idx = (lg / self.cfg.temperature).topk(k)
+        p = torch.softmax(vals, -1)
+        keep = (p.cumsum(-1) - p) < self.cfg.top_p            # the smallest prefix whose mass reaches top_p
+        p = torch.where(keep, p, torch.zeros_like(p))
+        return int(idx[torch.multinomial(p / p.sum(), 1, generator=self._gen)])
+
+    @staticmethod
+    def checkpoint_kv(cache) -> KVCheckpoint:
+        return KVCheckpoint(kv_context_len=int(cache.context_len()), valid=True) if cache is not None else KVCheckpoint()
+
+    @staticmethod
+    def rewind_kv(cache, ckpt: KVCheckpoint, new_len: int) -> None:
+        if cache is not None and ckpt.valid:
+            cache.resize(new_len)
+
+    def decode_step(self, draft: DraftModel, target: TargetModel, context: List[int], cache=None) -> SpecStepResult:
+        """Extends ``context`` in place by the kept drafts and, after a mismatch, by the target's token."""
+        res = SpecStepResult()
+        ckpt = self.checkpoint_kv(cache)
+        drafts = list(draft.propose(list(context), self.cfg.draft_k))
+        rows = target.logits_for_drafts(list(context), drafts) if drafts else []
+        for tok, row in zip(drafts, rows):
+            want = self.sample_token(row)
+            res.total_proposed += 1
+            if tok == want:
+                context.append(tok)
+                res.tokens_accepted.append(tok)
+            else:
+                context.append(want)
+                res.tokens_rejected += 1
+                break
+        _SOPS.speculative_propose(res.total_proposed)
+        _SOPS.speculative_accept(len(res.tokens_accepted))
+        self.rewind_kv(cache, ckpt, len(context))
+        if res.total_proposed:
+            res.acceptance_rate = len(res.tokens_accepted) / res.total_proposed
+        self.total_accepted += len(res.tokens_accepted)
+        self.total_proposed += res.total_proposed
+        self._window.append(res.acceptance_rate)
+        del self._window[: max(0, len(self._window) - self.cfg.auto_tune_window)]
+        self.cfg.draft_k = _SOPS.draft_length_tune(self.cfg.draft_k, sum(self._window) / len(self._window), self.cfg.min_draft_k,
+                                                   self.cfg.max_draft_k, self.cfg.target_acceptance_rate)
+        return res
+
+    def generate(self, draft: DraftModel, target: TargetModel, prompt: List[int], max_tokens: int, cache=None) -> List[int]:
+        context, out = list(prompt), []
+        while len(out) < max_tokens:
+            step = self.decode_step(draft, target, context, cache)
+            out.extend(step.tokens_accepted)
+            if step.tokens_rejected:
+                out.append(context[-1])
+            if step.total_proposed == 0:
+                break
+        return out[:max_tokens]

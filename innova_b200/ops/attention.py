@@ -89,3 +89,49 @@ def flash_attention(qkv, n_heads, n_kv_heads, head_dim, causal=True, scale=None,
     if not qkv.is_cuda:
         return attention_reference(qkv, n_heads, n_kv_heads, head_dim, causal, scale, window)
     return _FlashAttnFn.apply(qkv, n_heads, n_kv_heads, head_dim, causal, scale, window)
+
+
+# ------------------------------------------------------------------------------------------------ [B, H, S, D] front end
+from dataclasses import dataclass as _dataclass
+
+
+@_dataclass
+class FlashAttentionConfig:
+    block_size: int = 64          # kept for interface parity; the kernels' tile sizes are fixed at build time
+    causal: bool = True
+    softmax_scale: float = 0.0    # 0 -> 1 / sqrt(head_dim)
+    dropout: float = 0.0
+
+
+def flash_attention_forward(Q, K, V, mask=None, dropout_p: float = 0.0, causal: bool = True, scale=None):
+    """Attention on separate ``[B, H, S, D]`` tensors (reference: ``flash_attention_forward``, include/oil/flash_attention.h:7-8).
+    bf16 CUDA inputs with head dimension 64 or 128, no explicit mask and no dropout are repacked into the fused token-major
+    layout and run on the tcgen05 flash kernels (grouped K/V heads included); everything else (an additive or boolean
+    ``mask`` broadcastable to [B, H, S, S_k], dropout, other head sizes, CPU) goes through ``scaled_dot_product_attention``."""
+    B, H, S, D = Q.shape
+    Hkv = K.shape[1]
+    scale = (1.0 / math.sqrt(D)) if not scale else float(scale)
+    fused = (Q.is_cuda and Q.dtype == torch.bfloat16 and mask is None and dropout_p == 0.0 and D in (64, 128) and K.shape[2] == S
+             and H % Hkv == 0)
+    if fused:
+        qkv = torch.cat([Q.transpose(1, 2).reshape(B, S, H * D), K.transpose(1, 2).reshape(B, S, Hkv * D),
+                         V.transpose(1, 2).reshape(B, S, Hkv * D)], dim=-1).contiguous()
+        return flash_attention(qkv, H, Hkv, D, causal, scale).view(B, S, H, D).transpose(1, 2)
+    if Hkv != H:
+        K, V = K.repeat_interleave(H // Hkv, dim=1), V.repeat_interleave(H // Hkv, dim=1)
+    if mask is not None and causal:
+        tri = torch.ones(S, K.shape[2], dtype=torch.bool, device=Q.device).tril(K.shape[2] - S)
+        mask = (mask & tri) if mask.dtype == torch.bool else mask.masked_fill(~tri, float("-inf"))
+    return F.scaled_dot_product_attention(Q, K, V, attn_mask=mask, dropout_p=dropout_p, is_causal=causal and mask is None, scale=scale)
+
+
+class FlashAttention:
+    def __init__(self, cfg: FlashAttentionConfig = None):
+        self.cfg = cfg or FlashAttentionConfig()
+        self.training = False
+
+    def forward(self, Q, K, V, mask=None):
+        c = self.cfg
+        return flash_attention_forward(Q, K, V, mask, c.dropout if self.training else 0.0, c.causal, c.softmax_scale or None)
+
+    __call__ = forward

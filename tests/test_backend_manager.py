@@ -42,3 +42,25 @@ def test_activation_aware_block_importance():
             p = w[m, lo:hi] * a[lo:hi]
             assert torch.allclose(imp8[m * 3 + b], p.square().mean(), atol=1e-6) and torch.allclose(imp4[m * 3 + b], p.abs().mean(), atol=1e-6)
     assert torch.allclose(calibrate_importance(w, a.expand(3, 10), 4, "spark"), imp8)
+
+
+def test_flash_attention_front_end_on_cpu():
+    from innova_b200.ops.attention import FlashAttention, FlashAttentionConfig, flash_attention_forward
+    torch.manual_seed(0)
+    B, H, Hkv, S, D = 2, 4, 2, 6, 8
+    q, k, v = torch.randn(B, H, S, D), torch.randn(B, Hkv, S, D), torch.randn(B, Hkv, S, D)
+    kk, vv = k.repeat_interleave(2, 1), v.repeat_interleave(2, 1)
+    s = (q @ kk.transpose(-1, -2)) / D ** 0.5
+    tri = torch.ones(S, S, dtype=torch.bool).tril()
+    want = torch.softmax(s.masked_fill(~tri, float("-inf")), -1) @ vv
+    assert torch.allclose(flash_attention_forward(q, k, v), want, atol=1e-5)
+    assert torch.allclose(FlashAttention(FlashAttentionConfig(causal=False))(q, k, v), torch.softmax(s, -1) @ vv, atol=1e-5)
+    pad = torch.ones(B, 1, 1, S, dtype=torch.bool)
+    pad[1, ..., 4:] = False
+    got = FlashAttention()(q, k, v, pad)
+    want2 = torch.softmax(s.masked_fill(~(tri & pad), float("-inf")), -1) @ vv
+    assert torch.allclose(got, want2, atol=1e-5)
+    bias = torch.randn(1, H, S, S)
+    got3 = flash_attention_forward(q, k, v, bias, causal=True, scale=0.5)
+    want3 = torch.softmax(((q @ kk.transpose(-1, -2)) * 0.5 + bias).masked_fill(~tri, float("-inf")), -1) @ vv
+    assert torch.allclose(got3, want3, atol=1e-5)

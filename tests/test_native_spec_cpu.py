@@ -181,3 +181,79 @@ def test_tree_forward_equals_one_chain_forward_per_branch():
     h._forward(torch.tensor([prompt, prompt]), [0, 0])
     both = h._forward(torch.tensor([[5, 7, 11], [5, 7, 21]]), [len(prompt)] * 2, all_logits=True)
     assert torch.allclose(both[0, 2], tree_logits[2], atol=1e-4, rtol=1e-4) and torch.allclose(both[1, 2], tree_logits[5], atol=1e-4, rtol=1e-4)
+
+
+def test_interface_speculative_decoder_matches_plain_greedy_decoding():
+    from innova_b200.inference.speculative import DraftModel, InterfaceSpeculativeDecoder, SpecConfig, TargetModel
+
+    V = 11
+
+    def rule(ctx):                                            # the target's deterministic next token
+        return (3 * ctx[-1] + len(ctx)) % V
+
+    class Target(TargetModel):
+        calls = 0
+
+        def logits(self, ctx):
+            Target.calls += 1
+            row = [0.0] * V
+            row[rule(ctx)] = 5.0
+            return row
+
+        def vocab_size(self):
+            return V
+
+    class Draft(DraftModel):
+        def __init__(self, wrong_every):
+            self.wrong_every, self.n = wrong_every, 0
+
+        def propose(self, ctx, k):
+            out, c = [], list(ctx)
+            for _ in range(k):
+                self.n += 1
+                t = rule(c) if self.n % self.wrong_every else (rule(c) + 1) % V
+                out.append(t)
+                c.append(t)
+            return out
+
+        def vocab_size(self):
+            return V
+
+    plain, ctx = [], [1, 2]
+    for _ in range(40):
+        plain.append(rule(ctx + plain))
+    cfg = SpecConfig(draft_k=3, temperature=0.0, target_acceptance_rate=0.7)
+    dec = InterfaceSpeculativeDecoder(cfg)
+    got = dec.generate(Draft(wrong_every=5), Target(), ctx, 40)
+    assert got == plain and 0.6 < dec.acceptance_rate() < 0.95 and dec.total_proposed > 0
+    assert cfg.min_draft_k <= dec.current_draft_k() <= cfg.max_draft_k
+    perfect = InterfaceSpeculativeDecoder(SpecConfig(draft_k=2, temperature=0.0))
+    assert perfect.generate(Draft(wrong_every=10 ** 9), Target(), ctx, 30) == plain[:30] and perfect.acceptance_rate() == 1.0
+    assert perfect.current_draft_k() > 2                       # full acceptance lengthens the draft
+
+    class Cache:
+        def __init__(self):
+            self.n, self.resized = 2, []
+
+        def context_len(self):
+            return self.n
+
+        def resize(self, n):
+            self.resized.append(n)
+            self.n = n
+
+    cache, c2 = Cache(), list(ctx)
+    step = InterfaceSpeculativeDecoder(SpecConfig(draft_k=4, temperature=0.0)).decode_step(Draft(wrong_every=3), Target(), c2, cache)
+    assert step.tokens_accepted == plain[:2] and step.tokens_rejected == 1 and step.total_proposed == 3 and c2 == ctx + plain[:3]
+    assert cache.resized == [len(c2)] and abs(step.acceptance_rate - 2 / 3) < 1e-9
+    dec.update_draft_k(99)
+    assert dec.current_draft_k() == 8
+
+    class NoDraft(Draft):
+        def propose(self, ctx, k):
+            return []
+
+    assert InterfaceSpeculativeDecoder().generate(NoDraft(1), Target(), ctx, 5) == []
+    sampler = InterfaceSpeculativeDecoder(SpecConfig(temperature=1.0, top_k=3, top_p=0.5), seed=1)
+    draws = {sampler.sample_token([0.0, 4.0, 3.9, -2.0, 3.8]) for _ in range(50)}
+    assert draws <= {1, 2} and 1 in draws                     # top_p 0.5 keeps the two most likely of the top three

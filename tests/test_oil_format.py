@@ -205,3 +205,23 @@ def test_sha256_and_index_corruption(tmp_path):
     open(p, "wb").write(raw[:40])
     with pytest.raises(oil.CorruptIndexError):
         oil.read_idx(p)
+
+
+def test_idx_reader_and_writer_objects(tmp_path):
+    p = str(tmp_path / "m.oilidx")
+    with oil.OILIdxWriter(p) as w:
+        w.write_idx(2, ["tok_embeddings.weight", "layers.0.attn.wq", "norm"])
+    with pytest.raises(IOError):
+        w.write_idx(2, ["late"])
+    r = oil.OILIdxReader(p)
+    assert r.valid() and r.version() == 2 and r.num_tensors() == 3 and r.read_idx() == ["tok_embeddings.weight", "layers.0.attn.wq", "norm"]
+    assert not oil.OILIdxReader(str(tmp_path / "missing")).valid()
+    (tmp_path / "junk").write_bytes(b"x" * 64)
+    assert not oil.OILIdxReader(str(tmp_path / "junk")).valid()
+    raw = bytearray(open(p, "rb").read())
+    raw[-1] ^= 0xFF                                   # damage the last stored hash
+    (tmp_path / "bad.oilidx").write_bytes(bytes(raw))
+    bad = oil.OILIdxReader(str(tmp_path / "bad.oilidx"))
+    assert bad.valid()                                # the header is fine; the names do not verify
+    with pytest.raises(oil.CorruptIndexError):
+        bad.read_idx()
