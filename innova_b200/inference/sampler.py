@@ -32,9 +32,37 @@ class SamplingParams:
 
 
 class Sampler:
-    def __init__(self, params: Optional[SamplingParams] = None):
+    def __init__(self, params: Optional[SamplingParams] = None, native_cpu: bool = False):
+        """``native_cpu``: host rows are sampled by the C++ sampler of the host library (same kept-set and inverse-CDF rules
+        as the device kernel, so that a CPU run and a GPU run draw the same tokens from the same logits and seed) instead of
+        the PyTorch path."""
         self.p = params or SamplingParams()
         self.gen = torch.Generator().manual_seed(self.p.seed)
+        self.native_cpu = native_cpu
+
+    _cpu_fn = None
+
+    @classmethod
+    def _native_fn(cls):
+        if cls._cpu_fn is None:
+            import ctypes as C
+            fn = _native.host().inv_cpu_sample
+            fn.restype = C.c_int
+            fn.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_float, C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_void_p]
+            cls._cpu_fn = fn
+        return cls._cpu_fn
+
+    def _sample_native(self, lg: torch.Tensor, history: Optional[torch.Tensor]) -> torch.Tensor:
+        """``lg`` [B, V] fp32 contiguous on the host; ``sample`` has already applied the repetition penalty to it."""
+        p = self.p
+        B, V = lg.shape
+        out = torch.empty(B, dtype=torch.int32)
+        u = torch.rand(B, generator=self.gen) if p.temperature > 0.0 else torch.zeros(B)
+        rc = self._native_fn()(lg.data_ptr(), B, V, V, float(max(p.temperature, 0.0)), int(p.top_k), float(p.top_p), u.data_ptr(), None, 0, 1.0,
+                               out.data_ptr())
+        if rc != 0:
+            raise RuntimeError(f"inv_cpu_sample failed ({rc})")
+        return out.long()
 
     def apply_repetition_penalty(self, logits: torch.Tensor, history: Optional[torch.Tensor], hist_len: Optional[torch.Tensor] = None):
         """logits [B, V] fp32 (modified in place); history [B, T] token ids (negative = unused slot)."""
@@ -66,6 +94,8 @@ class Sampler:
                                      out.data_ptr(), rt.status_tensor(lg.device).data_ptr(), rt.stream_ptr())
             rt.check(rc, "inv_sample")
             return out.long()
+        if self.native_cpu:
+            return self._sample_native(lg, history)
         if greedy:
             return lg.argmax(dim=-1)
         lg = lg / p.temperature

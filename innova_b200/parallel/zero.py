@@ -287,11 +287,17 @@ class CPUOffloadEngine:
     returns a handle, ``prefetch`` starts the copy back, ``fetch`` waits for it. Double buffering falls out of the
     side stream: copies of tensor i+1 overlap compute on tensor i."""
 
-    def __init__(self, pool_bytes: int = 8 << 30, device=None):
+    def __init__(self, pool_bytes: int = 8 << 30, device=None, slab_bytes: int = 0):
+        """``slab_bytes`` > 0: host copies are carved from ONE pinned slab of that size by the native offset allocator
+        (no pinning call per tensor); a tensor that does not fit the slab falls back to its own pinned buffer."""
         self.device = torch.device(device) if device is not None else (
             torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
         self.cuda = self.device.type == "cuda"
         self.pool_bytes, self.used = pool_bytes, 0
+        self.slab = None
+        if slab_bytes > 0:
+            from ..utils.memory import SlabPool
+            self.slab = SlabPool(min(slab_bytes, pool_bytes), "cpu", pin=self.cuda)
         self.stream = torch.cuda.Stream(self.device) if self.cuda else None
         self.store: Dict[str, dict] = {}
         self.lock = threading.Lock()
@@ -303,7 +309,9 @@ class CPUOffloadEngine:
             if self.used + nbytes > self.pool_bytes:
                 raise MemoryError(f"offload pool exhausted ({self.used + nbytes} > {self.pool_bytes})")
             self.used += nbytes
-        host = torch.empty(t.shape, dtype=t.dtype, pin_memory=self.cuda)
+        host = self.slab.allocate(t.shape, t.dtype) if self.slab is not None else None
+        if host is None:
+            host = torch.empty(t.shape, dtype=t.dtype, pin_memory=self.cuda)
         ev = None
         if self.cuda:
             self.stream.wait_stream(torch.cuda.current_stream(self.device))
@@ -345,6 +353,10 @@ class CPUOffloadEngine:
         if release:
             with self.lock:
                 self.used -= t.numel() * t.element_size()
+            if self.slab is not None and self.slab.owns(e["host"]):
+                if self.cuda and e["event"] is not None:
+                    e["event"].synchronize()          # the copy out of the slab block has finished before the block is reused
+                self.slab.free(e["host"])
             del self.store[name]
         return t
 

@@ -34,6 +34,13 @@ def _native():
         for f in ("used", "peak", "capacity", "allocations", "failures"):
             fn = getattr(lib, "inv_arena_" + f)
             fn.restype, fn.argtypes = C.c_uint64, [C.c_void_p]
+        lib.inv_pool_create.restype, lib.inv_pool_create.argtypes = C.c_void_p, [C.c_uint64]
+        lib.inv_pool_destroy.restype, lib.inv_pool_destroy.argtypes = None, [C.c_void_p]
+        lib.inv_pool_alloc.restype, lib.inv_pool_alloc.argtypes = C.c_uint64, [C.c_void_p, C.c_uint64, C.c_uint64]
+        lib.inv_pool_free.restype, lib.inv_pool_free.argtypes = C.c_int64, [C.c_void_p, C.c_uint64]
+        for f in ("used", "peak", "capacity", "largest_free", "free_blocks", "live_blocks", "failures"):
+            fn = getattr(lib, "inv_pool_" + f)
+            fn.restype, fn.argtypes = C.c_uint64, [C.c_void_p]
         _lib = lib
     return _lib
 
@@ -199,3 +206,58 @@ class TensorView:
 
     def materialize(self) -> torch.Tensor:
         return self.tensor.contiguous()
+
+
+class SlabPool:
+    """One block of memory (pinned when on the host and ``pin`` is set) carved by the native best-fit offset allocator:
+    ``allocate`` returns a tensor view into the slab, ``free`` gives its bytes back and merges them with free neighbours.
+    Unlike ``MemoryPool`` (bump allocation, freed all at once) blocks come and go in any order, which is what staging
+    buffers that live for different numbers of steps need; the slab is pinned once, however many tensors pass through."""
+
+    def __init__(self, capacity: int, device="cpu", pin: bool = False):
+        self.buffer = Buffer(capacity, device, 256, pin)
+        self._h = _native().inv_pool_create(capacity)
+        self._live = {}
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            _native().inv_pool_destroy(self._h)
+            self._h = None
+
+    def allocate(self, shape: Sequence[int], dtype: torch.dtype = torch.float32, alignment: int = 256) -> Optional[torch.Tensor]:
+        """A view of the slab, or None when no free block is large enough."""
+        n = max(1, int(torch.Size(shape).numel()) * torch.empty((), dtype=dtype).element_size())
+        off = _native().inv_pool_alloc(self._h, n, alignment)
+        if off == _FAIL:
+            return None
+        t = self.buffer.view(dtype, shape, off)
+        self._live[t.data_ptr()] = off
+        return t
+
+    def free(self, t: torch.Tensor) -> bool:
+        off = self._live.pop(t.data_ptr(), None)
+        return off is not None and _native().inv_pool_free(self._h, off) >= 0
+
+    def owns(self, t: torch.Tensor) -> bool:
+        return t.data_ptr() in self._live
+
+    def bytes_used(self) -> int:
+        return int(_native().inv_pool_used(self._h))
+
+    def peak_usage(self) -> int:
+        return int(_native().inv_pool_peak(self._h))
+
+    def capacity(self) -> int:
+        return int(_native().inv_pool_capacity(self._h))
+
+    def largest_free(self) -> int:
+        return int(_native().inv_pool_largest_free(self._h))
+
+    def free_blocks(self) -> int:
+        return int(_native().inv_pool_free_blocks(self._h))
+
+    def live_blocks(self) -> int:
+        return int(_native().inv_pool_live_blocks(self._h))
+
+    def failures(self) -> int:
+        return int(_native().inv_pool_failures(self._h))
