@@ -1,5 +1,5 @@
-"""The C++ host runtime under AddressSanitizer + UndefinedBehaviorSanitizer: codecs, container, arena and page tables are
-driven in a child process that loads the instrumented library; any report makes the child exit non-zero."""
+"""The C++ host runtime under AddressSanitizer + UndefinedBehaviorSanitizer: codecs, container, arena, offset pool, sampler and
+importers are driven in a child process that loads the instrumented library; any report makes the child exit non-zero."""
 import os
 import subprocess
 import sys
@@ -65,6 +65,34 @@ for make in (st_file, gguf_file):
                     f.read(name)
         except (ValueError, RuntimeError, MemoryError):
             pass
+# best-fit offset pool under random allocate / free from several threads, then the sampler on edge shapes
+from innova_b200.utils.memory import SlabPool
+from innova_b200.inference.sampler import Sampler, SamplingParams
+sp = SlabPool(1 << 18)
+def churn(seed):
+    r = np.random.default_rng(seed)
+    held = []
+    for _ in range(300):
+        if held and r.random() < 0.45:
+            sp.free(held.pop(int(r.integers(0, len(held)))))
+        else:
+            t = sp.allocate((int(r.integers(1, 3000)),), torch.uint8)
+            if t is not None:
+                t.fill_(seed)
+                held.append(t)
+    for t in held:
+        assert int(t.max()) == seed and int(t.min()) == seed
+        sp.free(t)
+ts = [threading.Thread(target=churn, args=(i + 1,)) for i in range(4)]
+[t.start() for t in ts]; [t.join() for t in ts]
+assert sp.bytes_used() == 0 and sp.free_blocks() == 1
+for V in (1, 2, 7, 1000):
+    for params in (SamplingParams(), SamplingParams(temperature=1.0, top_k=3, top_p=0.5), SamplingParams(temperature=2.0, top_k=10 ** 6, top_p=1.0)):
+        s = Sampler(params, native_cpu=True)
+        out = s.sample(torch.randn(5, V), torch.randint(-1, max(1, V), (5, 4)))
+        assert out.shape == (5,) and int(out.min()) >= 0 and int(out.max()) < V
+big = Sampler(SamplingParams(temperature=1.0), native_cpu=True).sample(torch.randn(40, 32768))
+assert big.shape == (40,)
 print("sanitized run ok")
 """
 
