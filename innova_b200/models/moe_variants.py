@@ -301,3 +301,29 @@ def expert_dropout_mask(num_experts: int, p: float, generator=None) -> torch.Ten
     if not keep.any():
         keep[int(torch.randint(0, num_experts, (1,), generator=generator))] = True
     return keep
+
+
+# ------------------------------------------------------------------------------------------------ one class per variant, under the reference's names
+def _named(variant: str, doc: str):
+    def __init__(self, hidden: int, ffn: int, num_experts: int = 8, top_k: int = 2, **kw):
+        MoEVariantLayer.__init__(self, variant, hidden, ffn, num_experts, top_k, **kw)
+    return type(doc, (MoEVariantLayer,), {"__init__": __init__, "__doc__": f"``MoEVariantLayer`` fixed to the ``{variant}`` routing rule "
+                                                                         f"(reference: class ``{doc}``, include/oil/moe_variants.h:141-674)."})
+
+
+SparseTop1MoE, SparseTop2MoE, SparseTopKMoE = _named("sparse_top1", "SparseTop1MoE"), _named("sparse_top2", "SparseTop2MoE"), _named("sparse_topk", "SparseTopKMoE")
+SparseMoE = SparseTopKMoE
+SoftMoE, HierarchicalMoE, MoMoE, ExpertChoiceMoE = _named("soft_mixture", "SoftMoE"), _named("hierarchical", "HierarchicalMoE"), _named("momoe", "MoMoE"), \
+    _named("expert_choice", "ExpertChoiceMoE")
+HashMoE, CrossLayerMoE, MultiModalMoE, MMoE = _named("hash_routed", "HashMoE"), _named("cross_layer", "CrossLayerMoE"), _named("multimodal", "MultiModalMoE"), \
+    _named("mmoe", "MMoE")
+DeepSeekMoE, BaseLayerMoE, DenseMoE, SharedExpertMoE = _named("deepseek_moe", "DeepSeekMoE"), _named("base_layer", "BaseLayerMoE"), _named("dense_moe", "DenseMoE"), \
+    _named("shared_expert", "SharedExpertMoE")
+ResidualMoE, GatingDropoutMoE, DomainMoE, ProductKeyMoE = _named("residual_moe", "ResidualMoE"), _named("gating_dropout", "GatingDropoutMoE"), \
+    _named("domain_moe", "DomainMoE"), _named("product_key", "ProductKeyMoE")
+AttentionMoE, MLAMoE, MambaMoE = _named("attention_moe", "AttentionMoE"), _named("mla_moe", "MLAMoE"), _named("mamba_moe", "MambaMoE")
+QuantizedINT8MoE, SparkMoE, Oil1MoE, OIL8MoE, OIL4MoE = _named("quantized_int8_moe", "QuantizedINT8MoE"), _named("spark_moe", "SparkMoE"), \
+    _named("oil1_moe", "Oil1MoE"), _named("oil8_moe", "OIL8MoE"), _named("oil4_moe", "OIL4MoE")
+VARIANT_CLASSES = {c.__name__: c for c in (SparseTop1MoE, SparseTop2MoE, SparseTopKMoE, SoftMoE, HierarchicalMoE, MoMoE, ExpertChoiceMoE, HashMoE, CrossLayerMoE,
+                                           MultiModalMoE, MMoE, DeepSeekMoE, BaseLayerMoE, DenseMoE, SharedExpertMoE, ResidualMoE, GatingDropoutMoE, DomainMoE,
+                                           ProductKeyMoE, AttentionMoE, MLAMoE, MambaMoE, QuantizedINT8MoE, SparkMoE, Oil1MoE, OIL8MoE, OIL4MoE)}

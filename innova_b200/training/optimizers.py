@@ -443,5 +443,35 @@ class ChainedLR(Scheduler):
         return lr
 
 
+class WarmupLR(Scheduler):
+    """Linear ramp from ``warmup_start_lr`` to the wrapped schedule's first value over ``warmup_steps``, then the wrapped
+    schedule counted from its own step 0 (reference: ``WarmupScheduler``, src/scheduler.cpp:62-70)."""
+
+    def __init__(self, wrapped: Scheduler, warmup_steps: int, warmup_start_lr: float = 0.0):
+        super().__init__(wrapped.base_lr)
+        self.wrapped, self.warmup_steps, self.warmup_start_lr = wrapped, warmup_steps, warmup_start_lr
+
+    def __call__(self, step):
+        if step < self.warmup_steps:
+            return self.warmup_start_lr + (self.wrapped(0) - self.warmup_start_lr) * step / self.warmup_steps
+        return self.wrapped(step - self.warmup_steps)
+
+
+class LambdaLR(Scheduler):
+    def __init__(self, fn, base_lr: float = 1.0):
+        super().__init__(base_lr)
+        self.fn = fn
+
+    def __call__(self, step):
+        return self.fn(step)
+
+
+# the reference's class names (include/oil/scheduler.h:8-203)
+LRScheduler = Scheduler
+ConstantScheduler, LinearDecayScheduler, CosineDecayScheduler, ExponentialDecayScheduler = ConstantLR, LinearLR, CosineLR, ExponentialLR
+StepDecayScheduler, ReduceLROnPlateauScheduler, OneCycleScheduler, WarmupScheduler = StepLR, ReduceLROnPlateau, OneCycleLR, WarmupLR
+SequentialScheduler, LambdaScheduler, ChainedScheduler, CosineWarmupRestart = SequentialLR, LambdaLR, ChainedLR, CosineRestartLR
+PolyScheduler, MultiStepDecay, LinearWarmupDecay = PolynomialLR, MultiStepLR, WarmupLinearLR
+
 SCHEDULERS = [ConstantLR, StepLR, MultiStepLR, ExponentialLR, CosineLR, CosineRestartLR, LinearLR, PolynomialLR, WarmupCosineLR, WarmupLinearLR,
-              InverseSqrtLR, CyclicLR, OneCycleLR, ReduceLROnPlateau, SequentialLR, ChainedLR]
+              InverseSqrtLR, CyclicLR, OneCycleLR, ReduceLROnPlateau, SequentialLR, ChainedLR, WarmupLR, LambdaLR]

@@ -76,3 +76,11 @@ def test_enhancements():
     MV.merge_experts(bank, 0, 1)
     assert torch.allclose(bank.w_gu[0], 0.5 * (before + bank.w_gu[1]))
     assert MV.expert_dropout_mask(8, 1.0).sum() == 1
+
+
+def test_named_variant_classes_cover_every_variant():
+    from innova_b200.models import moe_variants as mv
+    assert len(mv.VARIANT_CLASSES) == 27 and {c(16, 32, 4).variant for c in mv.VARIANT_CLASSES.values()} == set(mv.VARIANTS)
+    layer = mv.DeepSeekMoE(16, 32, num_experts=4, top_k=2, num_shared=1)
+    y, aux = layer(torch.randn(6, 16))
+    assert isinstance(layer, mv.MoEVariantLayer) and y.shape == (6, 16) and "lb_loss" in aux and mv.SparseMoE is mv.SparseTopKMoE

@@ -25,7 +25,10 @@ def test_optimizer_reduces_quadratic(name):
 
 
 def test_sixteen_schedulers():
-    assert len(O.SCHEDULERS) == 16
+    assert len(O.SCHEDULERS) == 18 and O.CosineDecayScheduler is O.CosineLR and O.LRScheduler is O.Scheduler
+    warm = O.WarmupScheduler(O.CosineDecayScheduler(1.0, 100), 10, 0.1)
+    assert warm(0) == pytest.approx(0.1) and warm(5) == pytest.approx(0.55) and warm(10) == pytest.approx(1.0) and warm(60) == pytest.approx(0.5)
+    assert O.LambdaScheduler(lambda s: 0.5 * s)(4) == 2.0
     assert O.StepLR(1.0, 10, 0.5)(25) == 0.25
     assert O.MultiStepLR(1.0, [5, 10], 0.1)(7) == pytest.approx(0.1)
     assert O.CosineLR(1.0, 100)(50) == pytest.approx(0.5)
