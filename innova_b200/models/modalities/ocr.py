@@ -9,7 +9,6 @@ blocks never read it), and the CRNN's recurrent part is ``nn.LSTM`` (bidirection
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 from typing import List, Sequence, Tuple
 

@@ -11,7 +11,6 @@ as in the reference's raster order.
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 from typing import List, Sequence, Tuple
 

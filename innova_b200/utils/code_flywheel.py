@@ -21,7 +21,7 @@ import os
 import re
 import shutil
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, List, Optional, Sequence, Tuple
 
 from .asi import CppSandbox, CppSandboxResult, SafetyGuardrails

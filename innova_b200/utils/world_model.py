@@ -21,7 +21,7 @@ import math
 import time
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Deque, Dict, List, Optional, Sequence, Tuple, Union
+from typing import Deque, List, Sequence, Tuple, Union
 
 import torch
 
