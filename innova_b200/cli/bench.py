@@ -3,11 +3,14 @@
 
 ``--suite train`` times steps of a 67M-parameter-class decoder (the reference's bench_speed shape) or any preset;
 ``--suite infer`` times prefill + decode; ``--suite native`` runs the train-in-format trainer on synthetic uniform
-tokens (the reference's train_64m run) and reports bits per weight."""
+tokens (the reference's train_64m run) and reports bits per weight; ``--suite quality`` reports the round-trip error of every
+wire format on three weight distributions, ``--suite quant`` the codec's and the blockwise quantiser's throughput, ``--suite
+multimodal`` the forward time of the modality encoders (bench/bench_quality.cpp, bench_oil_quant.cpp, bench_multimodal.cpp)."""
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import sys
 import time
 
@@ -19,9 +22,91 @@ def _sync(dev):
         torch.cuda.synchronize()
 
 
+def quality_suite(a) -> dict:
+    """Round-trip quality of every wire format on three weight distributions (reference: bench/bench_quality.cpp, which
+    reports MSE, cosine similarity and compression ratio per format on random weights): stored bits per weight as written
+    by the codec, MSE, signal-to-noise ratio and cosine similarity."""
+    import numpy as np
+    from ..formats import oil
+    rng = np.random.default_rng(0)
+    n = max(256, a.elements // 256 * 256)
+    data = {"normal": rng.standard_normal(n), "heavy_tailed": rng.standard_t(3, n), "sparse": rng.standard_normal(n) * (rng.random(n) < 0.1)}
+    rows = []
+    for fmt in oil.FORMATS:
+        for name, w in data.items():
+            w32 = w.astype(np.float32)
+            back, nbytes = oil.roundtrip(fmt, w32, 256)
+            back = np.asarray(back, dtype=np.float64).reshape(-1)
+            err = float(np.mean((back - w32) ** 2))
+            power = float(np.mean(w32.astype(np.float64) ** 2))
+            cos = float(np.dot(back, w32) / max(1e-30, np.linalg.norm(back) * np.linalg.norm(w32)))
+            rows.append({"format": fmt, "data": name, "claimed_bpw": oil.format_bpw(fmt), "stored_bpw": 8.0 * nbytes / n, "mse": err,
+                         "snr_db": 10.0 * math.log10(power / err) if err > 0 else float("inf"), "cosine": cos,
+                         "compression": 32.0 / max(1e-9, 8.0 * nbytes / n)})
+    return {"suite": "quality", "elements": n, "rows": rows}
+
+
+def quant_suite(a) -> dict:
+    """Encode + decode throughput of the block codec per format on the host (reference: bench/bench_oil_quant.cpp), in
+    millions of weights per second, and the blockwise quantiser of ``ops.quant`` on the current device."""
+    import numpy as np
+    from ..formats import oil
+    from ..ops import quant
+    rng = np.random.default_rng(0)
+    n = max(256, a.elements // 256 * 256)
+    w = rng.standard_normal(n).astype(np.float32)
+    rows = []
+    for fmt in oil.FORMATS:
+        oil.roundtrip(fmt, w[:4096], 256)
+        t0 = time.perf_counter()
+        for _ in range(max(1, a.steps)):
+            oil.roundtrip(fmt, w, 256)
+        dt = (time.perf_counter() - t0) / max(1, a.steps)
+        rows.append({"format": fmt, "roundtrip_mweights_per_s": n / dt / 1e6})
+    dev = torch.device("cuda" if torch.cuda.is_available() else "cpu")
+    wt = torch.from_numpy(w).to(dev)
+    device_rows = []
+    for fmt in ("oil8", "oil4"):
+        quant.quantize_blockwise(wt, fmt)
+        _sync(dev)
+        t0 = time.perf_counter()
+        for _ in range(max(1, a.steps)):
+            quant.quantize_blockwise(wt, fmt)
+        _sync(dev)
+        device_rows.append({"format": fmt, "device": str(dev), "quantize_mweights_per_s": n / ((time.perf_counter() - t0) / max(1, a.steps)) / 1e6})
+    return {"suite": "quant", "elements": n, "host_codec": rows, "blockwise": device_rows}
+
+
+def multimodal_suite(a) -> dict:
+    """Milliseconds per forward of the modality encoders at small reference shapes (reference: bench/bench_multimodal.cpp)."""
+    from ..models.modalities import AudioEncoder, CRNN, OCRConfig, SplitVideoEncoder, TextConfig, TextEncoder, VideoConfig, VisionEncoder
+    dev = torch.device("cuda" if torch.cuda.is_available() else "cpu")
+    torch.manual_seed(0)
+    h = a.hidden_size if a.hidden_size <= 256 else 128
+    cases = {
+        "vision_vit_64px": (VisionEncoder(64, 8, h, 2, 4, 10).to(dev), lambda m: m.encode(torch.rand(a.batch_size, 3, 64, 64, device=dev))),
+        "audio_1s_16khz": (AudioEncoder(80, h, 2, 4, 256).to(dev), lambda m: m.encode_from_waveform(torch.randn(a.batch_size, 16000, device=dev))),
+        "text_128_tokens": (TextEncoder(TextConfig(1000, h, 2, 4, h // 4, 4 * h, 128)).to(dev), lambda m: m.encode(torch.randint(0, 1000, (a.batch_size, 128), device=dev))),
+        "video_16x64x64": (SplitVideoEncoder(VideoConfig(2, 16, 16, h, 4, h // 4, 1, 8, 4 * h, 32)).to(dev), lambda m: m.encode(torch.rand(16, 64, 64, device=dev))),
+        "ocr_crnn_32x128": (CRNN(OCRConfig(conv_channels=(8, 16, 32), lstm_hidden=64)).to(dev), lambda m: m(torch.rand(a.batch_size, 1, 32, 128, device=dev))),
+    }
+    rows = {}
+    with torch.no_grad():
+        for name, (model, run) in cases.items():
+            for _ in range(max(1, a.warmup)):
+                run(model)
+            _sync(dev)
+            t0 = time.perf_counter()
+            for _ in range(max(1, a.steps)):
+                run(model)
+            _sync(dev)
+            rows[name] = {"ms": 1e3 * (time.perf_counter() - t0) / max(1, a.steps), "params": sum(p.numel() for p in model.parameters())}
+    return {"suite": "multimodal", "device": str(dev), "batch": a.batch_size, "hidden": h, "encoders": rows}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="oil-bench")
-    ap.add_argument("--suite", default="train", choices=["train", "infer", "native"])
+    ap.add_argument("--suite", default="train", choices=["train", "infer", "native", "quality", "quant", "multimodal"])
     ap.add_argument("--preset", default="")
     ap.add_argument("--hidden-size", type=int, default=512)
     ap.add_argument("--num-layers", type=int, default=8)
@@ -33,7 +118,12 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--new-tokens", type=int, default=32)
     ap.add_argument("--device", default="auto")
+    ap.add_argument("--elements", type=int, default=1 << 18, help="weights per distribution (quality / quant suites)")
     a = ap.parse_args(argv)
+    if a.suite in ("quality", "quant", "multimodal"):
+        out = {"quality": quality_suite, "quant": quant_suite, "multimodal": multimodal_suite}[a.suite](a)
+        print(json.dumps(out))
+        return 0
     from ..models import DenseModel, PRESETS, TransformerConfig
     dev = torch.device("cuda" if (a.device == "auto" and torch.cuda.is_available()) else ("cpu" if a.device == "auto" else a.device))
     dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32

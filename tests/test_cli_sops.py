@@ -48,3 +48,19 @@ def test_training_simulation(capsys):
     assert all(r.total_time_ms > 0 for r in measured)
     assert sops.main(["train-sim", "--hidden-in", "32", "--hidden-out", "32", "--batch-size", "2", "--iters", "2"]) == 0
     assert "SOPS TRAINING SIMULATION" in capsys.readouterr().out
+
+
+def test_oil_bench_quality_quant_and_multimodal_suites(capsys):
+    from innova_b200.cli import bench
+    assert bench.main(["--suite", "quality", "--elements", "2048"]) == 0
+    q = json.loads(capsys.readouterr().out)
+    rows = {(r["format"], r["data"]): r for r in q["rows"]}
+    assert len(rows) == 45 and rows[("OIL32", "normal")]["mse"] == 0.0 and rows[("OIL8", "normal")]["snr_db"] > rows[("OIL4", "normal")]["snr_db"] > rows[("OIL2", "normal")]["snr_db"]
+    assert all(r["stored_bpw"] <= r["claimed_bpw"] + 1e-6 for r in q["rows"]) and rows[("OIL4", "normal")]["cosine"] > 0.98
+    assert bench.main(["--suite", "quant", "--elements", "4096", "--steps", "1"]) == 0
+    t = json.loads(capsys.readouterr().out)
+    assert len(t["host_codec"]) == 15 and all(r["roundtrip_mweights_per_s"] > 0 for r in t["host_codec"]) and len(t["blockwise"]) == 2
+    assert bench.main(["--suite", "multimodal", "--batch-size", "1", "--steps", "1", "--warmup", "1", "--hidden-size", "64"]) == 0
+    m = json.loads(capsys.readouterr().out)
+    assert set(m["encoders"]) == {"vision_vit_64px", "audio_1s_16khz", "text_128_tokens", "video_16x64x64", "ocr_crnn_32x128"}
+    assert all(e["ms"] > 0 and e["params"] > 0 for e in m["encoders"].values())
