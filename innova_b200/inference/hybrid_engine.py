@@ -271,3 +271,6 @@ class HybridEngine:
             out.append(self.sample(temperature, top_k))
             self.append_token(out[-1])
         return out
+
+
+Qwen35Engine = HybridEngine      # the reference's name for this engine (include/oil/qwen35_engine.h:10)
