@@ -225,3 +225,60 @@ class OIL4KVCache:
 
     def nbytes(self) -> int:
         return sum(i.numel() for i in self.idx) + sum(c.numel() * 2 for c in self.cb)
+
+
+# ------------------------------------------------------------------------------------------------ block-pool attention on explicit blocks
+class PagedAttention:
+    """A pool of key/value blocks handed out by id and attention over the blocks a block table names (reference:
+    ``PagedAttention``, include/oil/inference_opt.h:17-34, src/inference_opt.cpp:16-112: default 32 tokens x 256 blocks, an
+    online-softmax walk over the table per query row). Here the pool is two tensors ``[max_blocks, block_size, heads, dim]``,
+    ids come from a free list, and ``forward`` gathers the listed blocks and runs one ``scaled_dot_product_attention`` over
+    the first ``context_len`` tokens. The serving path of this package is ``PagedKVCache`` with the paged-decode CUDA
+    kernels; this class is the small explicit-block interface for tools and tests."""
+
+    def __init__(self, head_dim: int, n_heads: int, block_size: int = 32, max_blocks: int = 256, dtype=None, device="cpu"):
+        import torch
+        self.head_dim, self.n_heads, self.block_size, self.max_blocks = head_dim, n_heads, block_size, max_blocks
+        dtype = dtype or torch.float32
+        self.k = torch.zeros(max_blocks, block_size, n_heads, head_dim, dtype=dtype, device=device)
+        self.v = torch.zeros_like(self.k)
+        self._free = list(range(max_blocks - 1, -1, -1))
+        self._active = set()
+
+    def alloc_block(self) -> int:
+        """A free block id, or -1 when the pool is exhausted."""
+        if not self._free:
+            return -1
+        bid = self._free.pop()
+        self._active.add(bid)
+        return bid
+
+    def free_block(self, bid: int) -> None:
+        if bid in self._active:
+            self._active.discard(bid)
+            self._free.append(bid)
+
+    def num_blocks(self) -> int:
+        return len(self._active)
+
+    def available_blocks(self) -> int:
+        return len(self._free)
+
+    def write(self, bid: int, offset: int, k, v) -> None:
+        """``k``, ``v`` [tokens, heads, dim] stored at token ``offset`` of block ``bid``."""
+        n = k.shape[0]
+        assert bid in self._active and offset + n <= self.block_size
+        self.k[bid, offset: offset + n] = k
+        self.v[bid, offset: offset + n] = v
+
+    def forward(self, q, block_table, context_len: int, scale=None):
+        """``q`` [heads, dim] or [rows, heads, dim]; ``block_table`` the block ids in sequence order -> same shape as ``q``."""
+        import torch
+        import torch.nn.functional as F
+        ids = torch.as_tensor(list(block_table), dtype=torch.long, device=self.k.device)
+        keys = self.k[ids].reshape(-1, self.n_heads, self.head_dim)[:context_len].transpose(0, 1)      # [H, T, D]
+        vals = self.v[ids].reshape(-1, self.n_heads, self.head_dim)[:context_len].transpose(0, 1)
+        single = q.dim() == 2
+        qq = (q[None] if single else q).transpose(0, 1).to(keys.dtype)                                  # [H, R, D]
+        out = F.scaled_dot_product_attention(qq[None], keys[None], vals[None], scale=scale)[0].transpose(0, 1)
+        return out[0] if single else out

@@ -451,3 +451,45 @@ class InterfaceSpeculativeDecoder:
             if step.total_proposed == 0:
                 break
         return out[:max_tokens]
+
+
+@dataclass
+class VerificationResult:
+    accepted: List[bool] = field(default_factory=list)
+    first_rejection_pos: int = -1
+    total_accepted: int = 0
+    verify_sops: float = 0.0
+
+
+class SmallBatchVerifier:
+    """Arg-max agreement of up to ``max_batch`` draft rows with the target's rows, stopping at the first disagreement
+    (reference: ``SmallBatchVerifier``, include/oil/speculative_decoder.h:160-185, src/speculative_decoder.cpp:184-236). Both
+    arg-maxes are one batched reduction; the call is recorded as a small-batch event of the given weight format."""
+
+    def __init__(self, max_batch: int = 8):
+        self.max_batch, self.format = max_batch, "OIL4"
+
+    def set_format_index(self, fmt) -> None:
+        self.format = fmt
+
+    def verify(self, draft_logits, target_logits, temperature: float = 1.0) -> VerificationResult:
+        import time
+        t0 = time.perf_counter()
+        d, t = torch.as_tensor(draft_logits, dtype=torch.float32), torch.as_tensor(target_logits, dtype=torch.float32)
+        n = min(self.max_batch, d.shape[0] if d.dim() == 2 else 0, t.shape[0] if t.dim() == 2 else 0)
+        res = VerificationResult(accepted=[False] * n, first_rejection_pos=n)
+        if n == 0 or d.shape[1] != t.shape[1]:
+            res.first_rejection_pos = 0 if n else n
+            return res
+        same = (d[:n].argmax(-1) == t[:n].argmax(-1)).tolist()
+        for i, ok in enumerate(same):
+            if not ok:
+                res.first_rejection_pos = i
+                break
+            res.accepted[i] = True
+            res.total_accepted += 1
+        dt = max(time.perf_counter() - t0, 1e-9)
+        _SOPS.small_batch(self.format, n, dt)
+        from ..utils.telemetry import sops
+        res.verify_sops = sops(n, dt, self.format) / 1e21
+        return res

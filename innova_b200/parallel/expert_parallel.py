@@ -463,3 +463,398 @@ class PipelineScheduler:
     def utilisation(self) -> float:
         """Busy stage-steps over stage-steps: M / (M + S - 1) per drained direction (the pipeline bubble)."""
         return sum(s.busy_steps for s in self.stages) / max(1, self.total_steps * self.num_stages)
+
+
+# ------------------------------------------------------------------------------------------------ host-side routing plan and cluster bookkeeping
+from dataclasses import dataclass as _dc, field as _field
+from typing import Dict as _Dict, List as _List
+
+
+@_dc
+class ClusterNode:
+    node_id: int = -1
+    address: str = ""
+    port: int = 0
+    alive: bool = True
+    num_experts: int = 0
+    capacity_tokens: int = 0
+    load_factor: float = 0.0
+    total_tokens_processed: int = 0
+    total_bytes_sent: int = 0
+    total_bytes_recv: int = 0
+
+
+@_dc
+class ExpertAssignment:
+    expert_id: int = -1
+    node_id: int = -1
+    token_count: int = 0
+    capacity: int = 0
+    avg_weight: float = 0.0
+
+
+@_dc
+class RoutingDecision:
+    expert_indices: torch.Tensor = None          # [T, k]
+    expert_weights: torch.Tensor = None          # [T, k]
+    tokens_per_node: _List[int] = _field(default_factory=list)
+    tokens_per_expert: _List[int] = _field(default_factory=list)
+    load_balance_loss: float = 0.0
+    z_loss: float = 0.0
+    tokens_dropped: int = 0
+    overflow_tokens: int = 0
+
+
+@_dc
+class Transfer:
+    src_node: int
+    dst_node: int
+    expert_id: int
+    token_count: int
+    data_offset: int
+    data_bytes: int
+
+
+@_dc
+class AllToAllPlan:
+    transfers: _List[Transfer] = _field(default_factory=list)
+    total_bytes: int = 0
+    max_peers: int = 0
+    order: torch.Tensor = None                   # assignment indices (token * k + slot) sorted by (destination node, expert)
+    kept: torch.Tensor = None                    # bool per assignment: False where capacity dropped it
+
+
+@_dc
+class EPClusterConfig:
+    hidden_size: int = 4096
+    num_experts: int = 64
+    top_k: int = 2
+    load_balance_coef: float = 0.01
+    z_loss_coef: float = 0.001
+    capacity_factor: float = 1.25
+    max_tokens_per_expert: int = 0
+    chunk_size: int = 1024
+    bytes_per_element: int = 2
+
+
+@_dc
+class ExpertParallelStats:
+    total_tokens_routed: int = 0
+    total_tokens_dropped: int = 0
+    total_comm_bytes: int = 0
+    total_expert_forward_calls: int = 0
+    avg_load_imbalance: float = 0.0
+    max_load_imbalance: float = 0.0
+    node_failures_handled: int = 0
+    expert_redistributions: int = 0
+    total_forward_time_ms: float = 0.0
+    total_comm_time_ms: float = 0.0
+
+
+class ExpertDispatcher:
+    """Routing and the all-to-all plan as host-visible objects (reference: ``ExpertDispatcher``, include/oil/expert_parallel.h:
+    117-143, src/expert_parallel.cpp:275-478): experts are assigned to nodes in contiguous runs, ``route_tokens`` takes the
+    top-k experts per token with weights = softmax over the selected logits and applies the capacity limit in token order,
+    ``plan_all_to_all`` lists one transfer per (destination node, expert) with token and byte counts, ``dispatch_tokens`` /
+    ``gather_results`` reorder rows by that plan and bring weighted results back. All of it is batched tensor code (one sort,
+    bincounts, index_add); the GPU training path does the same steps inside ``csrc/moe_ep.cu`` without leaving the device,
+    and this class is what tools, tests and schedulers use to inspect or simulate a routing."""
+
+    def __init__(self, config: EPClusterConfig = None):
+        self.config = config or EPClusterConfig()
+        self.assignments: _List[ExpertAssignment] = []
+        self.num_nodes = 0
+
+    def assign_experts_to_nodes(self, num_nodes: int) -> None:
+        E = self.config.num_experts
+        per = -(-E // max(1, num_nodes))
+        self.num_nodes = num_nodes
+        self.assignments = [ExpertAssignment(e, min(num_nodes - 1, e // per)) for e in range(E)]
+
+    def get_expert_assignment(self, expert_id: int) -> ExpertAssignment:
+        return self.assignments[expert_id]
+
+    def get_all_assignments(self) -> _List[ExpertAssignment]:
+        return list(self.assignments)
+
+    def redistribute_expert(self, expert_id: int, from_node: int, to_node: int) -> bool:
+        a = self.assignments[expert_id]
+        if a.node_id != from_node:
+            return False
+        a.node_id = to_node
+        return True
+
+    def _owner(self) -> torch.Tensor:
+        return torch.tensor([a.node_id for a in self.assignments], dtype=torch.long)
+
+    def capacity(self, num_tokens: int) -> int:
+        c = self.config
+        if c.max_tokens_per_expert > 0:
+            return c.max_tokens_per_expert
+        return max(1, int(c.capacity_factor * num_tokens * c.top_k / c.num_experts + 0.999999))
+
+    def route_tokens(self, logits: torch.Tensor, num_tokens: int = 0, local_node_id: int = 0, num_nodes: int = 0) -> RoutingDecision:
+        if num_nodes and num_nodes != self.num_nodes:
+            self.assign_experts_to_nodes(num_nodes)
+        c, T = self.config, logits.shape[0]
+        top = logits.float().topk(c.top_k, dim=-1)
+        weights = torch.softmax(top.values, dim=-1)
+        flat_e = top.indices.reshape(-1)
+        cap = self.capacity(T)
+        # position of each assignment among the assignments of its expert, in token order
+        order = torch.argsort(flat_e, stable=True)
+        counts = torch.bincount(flat_e, minlength=c.num_experts)
+        starts = torch.cumsum(counts, 0) - counts
+        rank_in_expert = torch.empty_like(order)
+        rank_in_expert[order] = torch.arange(order.numel()) - starts[flat_e[order]]
+        kept = rank_in_expert < cap
+        weights = weights * kept.view(T, c.top_k)
+        kept_counts = torch.bincount(flat_e[kept], minlength=c.num_experts)
+        owner = self._owner()
+        per_node = torch.zeros(max(1, self.num_nodes), dtype=torch.long).index_add_(0, owner, kept_counts)
+        rd = RoutingDecision(top.indices, weights, per_node.tolist(), kept_counts.tolist())
+        rd.tokens_dropped = rd.overflow_tokens = int((~kept).sum())
+        rd.load_balance_loss, rd.z_loss = self.compute_load_balance(logits, rd)
+        for a, n, w in zip(self.assignments, kept_counts.tolist(), torch.zeros(c.num_experts).index_add_(0, flat_e, weights.reshape(-1)).tolist()):
+            a.token_count, a.capacity, a.avg_weight = n, cap, (w / n if n else 0.0)
+        rd._kept = kept
+        return rd
+
+    def compute_load_balance(self, logits: torch.Tensor, routing: RoutingDecision):
+        """(E * sum_e f_e P_e, mean squared log-sum-exp): f_e the share of assignments on expert e, P_e its mean probability."""
+        E = self.config.num_experts
+        probs = torch.softmax(logits.float(), -1)
+        f = torch.bincount(routing.expert_indices.reshape(-1), minlength=E).float() / max(1, routing.expert_indices.numel())
+        return float(E * (f * probs.mean(0)).sum()), float(torch.logsumexp(logits.float(), -1).square().mean())
+
+    def plan_all_to_all(self, routing: RoutingDecision, local_node_id: int = 0) -> AllToAllPlan:
+        c = self.config
+        flat_e = routing.expert_indices.reshape(-1)
+        kept = getattr(routing, "_kept", torch.ones_like(flat_e, dtype=torch.bool))
+        owner = self._owner()
+        key = owner[flat_e] * c.num_experts + flat_e
+        key = torch.where(kept, key, torch.full_like(key, self.num_nodes * c.num_experts))      # dropped assignments sort last
+        order = torch.argsort(key, stable=True)[: int(kept.sum())]
+        plan = AllToAllPlan(order=order, kept=kept)
+        row_bytes = c.hidden_size * c.bytes_per_element
+        offset = 0
+        for e, n in enumerate(routing.tokens_per_expert):
+            if n:
+                plan.transfers.append(Transfer(local_node_id, int(owner[e]), e, n, 0, n * row_bytes))
+        plan.transfers.sort(key=lambda t: (t.dst_node, t.expert_id))
+        for t in plan.transfers:
+            t.data_offset = offset
+            offset += t.data_bytes
+        plan.total_bytes = sum(t.data_bytes for t in plan.transfers if t.dst_node != local_node_id)
+        plan.max_peers = len({t.dst_node for t in plan.transfers if t.dst_node != local_node_id})
+        return plan
+
+    def dispatch_tokens(self, tokens: torch.Tensor, plan: AllToAllPlan, local_node_id: int = 0) -> torch.Tensor:
+        """Rows of ``tokens`` [T, D] laid out in the plan's order (grouped by destination node, then expert): the send buffer."""
+        k = self.config.top_k
+        return tokens[plan.order // k]
+
+    def gather_results(self, expert_outputs: torch.Tensor, plan: AllToAllPlan, local_node_id: int = 0, routing: RoutingDecision = None,
+                       num_tokens: int = 0) -> torch.Tensor:
+        """Inverse of ``dispatch_tokens``: rows return to their tokens, scaled by the routing weights and summed over the k
+        experts of a token. Without ``routing`` the rows are summed unweighted."""
+        k = self.config.top_k
+        T = num_tokens or (routing.expert_indices.shape[0] if routing is not None else int(plan.order.max()) // k + 1)
+        out = torch.zeros(T, expert_outputs.shape[-1], dtype=expert_outputs.dtype)
+        rows = expert_outputs
+        if routing is not None:
+            rows = rows * routing.expert_weights.reshape(-1)[plan.order].unsqueeze(-1).to(rows.dtype)
+        return out.index_add_(0, plan.order // k, rows)
+
+
+class ExpertParallelManager:
+    """Cluster membership, expert placement and statistics around an ``ExpertDispatcher`` (reference:
+    ``ExpertParallelManager``, include/oil/expert_parallel.h:145-195). Nodes are bookkeeping records (the transport between
+    ranks is the process group or ``TCPCommBackend``); a failed node's experts move to the least loaded live nodes, and
+    ``rebalance_experts`` evens the expert count per live node. ``forward_expert_parallel`` runs the whole route -> plan ->
+    dispatch -> expert -> gather path on one process with callables as experts, which is the oracle the distributed layers
+    are tested against."""
+
+    def __init__(self, config: EPClusterConfig = None):
+        self.config = config or EPClusterConfig()
+        self.dispatcher = ExpertDispatcher(self.config)
+        self.nodes: _List[ClusterNode] = []
+        self._local = -1
+        self.stats = ExpertParallelStats()
+        self._imbalance_samples = 0
+
+    # -- membership
+    def init_cluster(self, local_node_id: int, port: int = 0) -> bool:
+        self._local = local_node_id
+        if not any(n.node_id == local_node_id for n in self.nodes):
+            self.nodes.append(ClusterNode(local_node_id, "127.0.0.1", port))
+        self._replace()
+        return True
+
+    def add_node(self, address: str, port: int) -> int:
+        nid = max((n.node_id for n in self.nodes), default=-1) + 1
+        self.nodes.append(ClusterNode(nid, address, port))
+        self._replace()
+        return nid
+
+    def remove_node(self, node_id: int) -> None:
+        self.nodes = [n for n in self.nodes if n.node_id != node_id]
+        self._replace()
+
+    def leave_cluster(self) -> None:
+        self.nodes, self._local = [], -1
+
+    def is_cluster_active(self) -> bool:
+        return self._local >= 0 and any(n.alive for n in self.nodes)
+
+    def local_node_id(self) -> int:
+        return self._local
+
+    def num_nodes(self) -> int:
+        return len(self.nodes)
+
+    def get_nodes(self) -> _List[ClusterNode]:
+        return list(self.nodes)
+
+    def _replace(self) -> None:
+        """Contiguous placement over the nodes in id order (done whenever membership changes by add / remove)."""
+        self.nodes.sort(key=lambda n: n.node_id)
+        self.dispatcher.assign_experts_to_nodes(max(1, len(self.nodes)))
+        ids = [n.node_id for n in self.nodes] or [0]
+        for a in self.dispatcher.assignments:
+            a.node_id = ids[a.node_id]
+        self.dispatcher.num_nodes = max(ids) + 1
+        self._count()
+
+    def _count(self) -> None:
+        for n in self.nodes:
+            n.num_experts = sum(a.node_id == n.node_id for a in self.dispatcher.assignments)
+
+    # -- failures and balance
+    def handle_node_failure(self, node_id: int) -> _Dict[int, int]:
+        for n in self.nodes:
+            if n.node_id == node_id:
+                n.alive = False
+        self.stats.node_failures_handled += 1
+        return self.redistribute_experts_after_failure(node_id)
+
+    def redistribute_experts_after_failure(self, failed_node: int) -> _Dict[int, int]:
+        """{expert: new node}: each orphaned expert goes to the live node that holds the fewest experts at that moment."""
+        live = [n for n in self.nodes if n.alive]
+        moved: _Dict[int, int] = {}
+        if not live:
+            return moved
+        self._count()
+        load = {n.node_id: n.num_experts for n in live}
+        for a in self.dispatcher.assignments:
+            if a.node_id == failed_node:
+                dst = min(load, key=lambda k: (load[k], k))
+                a.node_id, moved[a.expert_id] = dst, dst
+                load[dst] += 1
+        self.stats.expert_redistributions += len(moved)
+        self._count()
+        return moved
+
+    def rebalance_experts(self) -> int:
+        """Moves experts from the fullest to the emptiest live node until counts differ by at most one; returns the moves."""
+        live = [n.node_id for n in self.nodes if n.alive]
+        moves = 0
+        while live:
+            self._count()
+            load = {i: sum(a.node_id == i for a in self.dispatcher.assignments) for i in live}
+            hi, lo = max(load, key=lambda k: (load[k], -k)), min(load, key=lambda k: (load[k], k))
+            if load[hi] - load[lo] <= 1:
+                break
+            victim = next(a for a in reversed(self.dispatcher.assignments) if a.node_id == hi)
+            victim.node_id = lo
+            moves += 1
+        self.stats.expert_redistributions += moves
+        self._count()
+        return moves
+
+    # -- compute
+    def forward_expert_parallel(self, x: torch.Tensor, router_weight: torch.Tensor, experts, training: bool = True):
+        """``x`` [T, D]; ``experts[e](rows) -> rows``. Returns (output [T, D], RoutingDecision)."""
+        import time as _time
+        t0 = _time.perf_counter()
+        d = self.dispatcher
+        if not d.assignments:
+            d.assign_experts_to_nodes(max(1, len(self.nodes)))
+        logits = x.float() @ router_weight.float().t()
+        rd = d.route_tokens(logits, x.shape[0], max(0, self._local), d.num_nodes)
+        plan = d.plan_all_to_all(rd, max(0, self._local))
+        send = d.dispatch_tokens(x, plan)
+        flat_e = rd.expert_indices.reshape(-1)[plan.order]
+        out_rows = torch.empty_like(send)
+        for e in range(self.config.num_experts):
+            sel = flat_e == e
+            if bool(sel.any()):
+                out_rows[sel] = experts[e](send[sel])
+                self.stats.total_expert_forward_calls += 1
+        y = d.gather_results(out_rows, plan, routing=rd, num_tokens=x.shape[0]).to(x.dtype)
+        s = self.stats
+        s.total_tokens_routed += int(plan.order.numel())
+        s.total_tokens_dropped += rd.tokens_dropped
+        s.total_comm_bytes += plan.total_bytes
+        per = torch.tensor(rd.tokens_per_expert, dtype=torch.float32)
+        imb = float(per.max() / per.mean().clamp_min(1e-9)) if per.numel() else 0.0
+        self._imbalance_samples += 1
+        s.avg_load_imbalance += (imb - s.avg_load_imbalance) / self._imbalance_samples
+        s.max_load_imbalance = max(s.max_load_imbalance, imb)
+        s.total_forward_time_ms += (_time.perf_counter() - t0) * 1e3
+        for n in self.nodes:
+            n.total_tokens_processed += rd.tokens_per_node[n.node_id] if n.node_id < len(rd.tokens_per_node) else 0
+            n.load_factor = n.total_tokens_processed / max(1, s.total_tokens_routed)
+        return y, rd
+
+    def expert_parallel_mlp(self, x: torch.Tensor, router_weight: torch.Tensor, experts) -> torch.Tensor:
+        return self.forward_expert_parallel(x, router_weight, experts, training=False)[0]
+
+    @staticmethod
+    def all_reduce_gradients(grad: torch.Tensor, group=None) -> torch.Tensor:
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(grad, group=group)
+        return grad
+
+    def sync_gradients(self, modules, group=None) -> None:
+        for m in modules:
+            for p in m.parameters():
+                if p.grad is not None:
+                    self.all_reduce_gradients(p.grad, group)
+
+    # -- state
+    def checkpoint_experts(self, experts, path: str) -> bool:
+        try:
+            torch.save({"experts": [e.state_dict() if hasattr(e, "state_dict") else None for e in experts],
+                        "assignments": [(a.expert_id, a.node_id) for a in self.dispatcher.assignments],
+                        "nodes": [vars(n) for n in self.nodes], "stats": vars(self.stats)}, path)
+            return True
+        except OSError:
+            return False
+
+    def restore_experts(self, experts, path: str) -> bool:
+        try:
+            blob = torch.load(path, map_location="cpu", weights_only=False)
+        except (OSError, RuntimeError):
+            return False
+        for e, sd in zip(experts, blob["experts"]):
+            if sd is not None:
+                e.load_state_dict(sd)
+        self.restore_nodes([ClusterNode(**n) for n in blob["nodes"]])
+        self.dispatcher.assignments = [ExpertAssignment(e, n) for e, n in blob["assignments"]]
+        self.dispatcher.num_nodes = max((n for _, n in blob["assignments"]), default=0) + 1
+        self.restore_stats(ExpertParallelStats(**blob["stats"]))
+        self._count()
+        return True
+
+    def get_stats(self) -> ExpertParallelStats:
+        return self.stats
+
+    def reset_stats(self) -> None:
+        self.stats, self._imbalance_samples = ExpertParallelStats(), 0
+
+    def restore_nodes(self, nodes) -> None:
+        self.nodes = list(nodes)
+
+    def restore_stats(self, stats: ExpertParallelStats) -> None:
+        self.stats = stats

@@ -257,3 +257,31 @@ def test_interface_speculative_decoder_matches_plain_greedy_decoding():
     sampler = InterfaceSpeculativeDecoder(SpecConfig(temperature=1.0, top_k=3, top_p=0.5), seed=1)
     draws = {sampler.sample_token([0.0, 4.0, 3.9, -2.0, 3.8]) for _ in range(50)}
     assert draws <= {1, 2} and 1 in draws                     # top_p 0.5 keeps the two most likely of the top three
+
+
+def test_small_batch_verifier_and_block_pool_attention():
+    from innova_b200.inference.kv_cache_ext import PagedAttention
+    from innova_b200.inference.speculative import SmallBatchVerifier
+    from innova_b200.utils.telemetry import sops_global
+    before = sops_global().small_batch_calls
+    draft = torch.tensor([[0.1, 2.0, 0.3], [3.0, 0.0, 0.0], [0.0, 0.0, 1.0], [1.0, 0.0, 0.0]])
+    target = torch.tensor([[0.0, 5.0, 0.0], [2.0, 1.0, 0.0], [0.0, 9.0, 1.0], [1.0, 0.0, 0.0]])
+    r = SmallBatchVerifier(8).verify(draft, target)
+    assert r.accepted == [True, True, False, False] and r.first_rejection_pos == 2 and r.total_accepted == 2 and r.verify_sops > 0
+    assert SmallBatchVerifier(1).verify(draft, target).accepted == [True] and sops_global().small_batch_calls == before + 2
+    assert SmallBatchVerifier().verify(torch.zeros(0, 3), target).accepted == []
+    torch.manual_seed(0)
+    pa = PagedAttention(head_dim=8, n_heads=2, block_size=4, max_blocks=5)
+    k, v = torch.randn(10, 2, 8), torch.randn(10, 2, 8)
+    table = [pa.alloc_block() for _ in range(3)]
+    assert table == [0, 1, 2] and pa.num_blocks() == 3 and pa.available_blocks() == 2
+    for i, bid in enumerate(table):
+        n = min(4, 10 - 4 * i)
+        pa.write(bid, 0, k[4 * i: 4 * i + n], v[4 * i: 4 * i + n])
+    q = torch.randn(2, 8)
+    out = pa.forward(q, table, context_len=10)
+    want = torch.stack([torch.softmax(q[h] @ k[:, h].T / 8 ** 0.5, -1) @ v[:, h] for h in range(2)])
+    assert torch.allclose(out, want, atol=1e-5) and pa.forward(torch.randn(3, 2, 8), table, 10).shape == (3, 2, 8)
+    pa.free_block(1)
+    assert pa.available_blocks() == 3 and pa.alloc_block() == 1
+    assert [pa.alloc_block() for _ in range(3)] == [3, 4, -1]

@@ -109,3 +109,41 @@ def test_convert_from_raw_gguf_and_safetensors(tmp_path):
     r = oil.OILReader(out3)
     assert np.allclose(r.read_tensor("t.f32").numpy(), a[:100])
     assert np.abs(r.read_tensor("t.q8").numpy() - a[:64]).max() < 0.05
+
+
+def test_format_registry_and_planner_objects():
+    import numpy as np
+    import pytest
+    from innova_b200.formats.registry import FormatPlanner, FormatRegistry as R
+    assert len(R.get_all_singles()) == 15 and R.get_single_format(4.2).name == "OIL4" and R.get_single_format(0.1).name in ("OIL1", "OIL1_GRP")
+    assert R.parse_format_name("oil8").bpw == 8.0 and "OIL4_GRP" in R.get_format_table() and len(R.get_all_mixes()) >= 8
+    with pytest.raises(KeyError):
+        R.parse_format_name("nope")
+    rng = np.random.default_rng(0)
+    w = rng.standard_normal(256 * 40).astype(np.float32)
+    w[: 256 * 4] *= 20
+    back, nbytes = R.quantize(w, R.parse_format_name("OIL8"))
+    assert R.actual_bpw(nbytes, w.size) <= 8.0 + 1e-6 and R.evaluate_format_quality(w, "OIL8") < R.evaluate_format_quality(w, "OIL4")
+    g = np.zeros_like(w)
+    g[: 256 * 4] = 1.0                                              # only the large-valued blocks matter to the loss
+    plain, weighted = R.evaluate_format_quality(w, "OIL4"), R.evaluate_format_quality_weighted(w, g, "OIL4", fisher_weight=1.0)
+    assert weighted > plain                                         # those blocks carry the largest absolute errors
+    assert R.compute_average_bpw(["OIL4", "OIL8"]) == 6.0
+    p = FormatPlanner(3.0)
+    assert p.target_bpw() == 3.0 and p.importance_scores() == []
+    p.score_importance(w)
+    plan = p.allocate()
+    assert len(plan.blocks) == 40 and len(p.importance_scores()) == 40 and plan.achieved_bpw <= 3.0 + 1e-6 and sum(plan.counts.values()) == 40
+    bpw = [R.get_all_singles()[b.assigned_format].bpw for b in plan.blocks]
+    assert min(bpw[:4]) >= max(bpw[4:]) and min(bpw[:4]) > sum(bpw[4:]) / 36          # the important blocks get the widest formats
+    assert FormatPlanner.estimate_bpw(plan) == pytest.approx(plan.achieved_bpw)
+    p.score_importance_fisher(w, g)
+    assert p.importance_scores()[0] == pytest.approx(1.0) and p.importance_scores()[10] == 0.0
+    p.set_target_bpw(8.0)
+    assert p.allocate().achieved_bpw > plan.achieved_bpw
+    act = np.ones(256, dtype=np.float32)
+    act[:8] = 50.0
+    p.score_importance(w, act)
+    assert len(p.importance_scores()) == 40
+    with pytest.raises(ValueError):
+        FormatPlanner().allocate()
