@@ -539,3 +539,122 @@ class MTPHeadTrainer:
     @property
     def acceptance_rate(self) -> float:
         return self.accepted / max(1, self.proposed)
+
+
+# ------------------------------------------------------------------------------------------------ step-hook engine with the reference's interface
+@dataclass
+class Theorem11Params:
+    lam: float = 1.0
+    buffer_size: int = 0
+    task_k_samples: int = 0
+    avg_fisher_importance: float = 0.0
+    replay_ratio: float = 0.0
+    temperature: float = 100.0
+
+
+def theorem11_bound(p: Theorem11Params) -> float:
+    """lambda * mean Fisher / |buffer| + replay_ratio * exp(-k / T), clamped to [0, 1]; 1 for an empty buffer or T <= 0
+    (reference: include/oil/continual_engine.h:102-118)."""
+    if p.buffer_size == 0 or p.temperature <= 0.0:
+        return 1.0
+    return min(1.0, max(0.0, p.lam * p.avg_fisher_importance / p.buffer_size + p.replay_ratio * math.exp(-p.task_k_samples / p.temperature)))
+
+
+@dataclass
+class ContinualEngineConfig:
+    replay_capacity: int = 65536
+    ecc_lambda: float = 1.0
+    ecc_alpha: float = 0.01
+    forgetting_temperature: float = 100.0
+    importance_decay: float = 0.99
+    forgetting_check_interval: int = 100
+    stability_lr_factor: float = 0.5
+    plasticity_lr_factor: float = 2.0
+    forgetting_threshold: float = 0.1
+
+
+class ContinualEngine:
+    """Replay buffer + Fisher / anchor state + forgetting benchmark driven by two hooks, for callers that own their training
+    loop (reference: ``ContinualEngine``, include/oil/continual_engine.h:136-170, src/continual_engine.cpp:359-410):
+    ``on_step`` after every optimizer step (Fisher average of the parameters' gradients; every ``forgetting_check_interval``
+    steps the anchors move and the registered tasks are re-evaluated when a loss function was given), ``on_task_boundary``
+    when the task id changes, ``effective_lr`` = base x stability factor x (1 + forgetting / threshold) while the average
+    forgetting is above the threshold, base x plasticity factor otherwise. ``ContinualTrainer`` is the ready-made loop on top
+    of the same parts."""
+
+    def __init__(self, params: Sequence[torch.nn.Parameter], cfg: Optional[ContinualEngineConfig] = None,
+                 eval_loss: Optional[Callable[[object, object], float]] = None):
+        self.cfg = cfg or ContinualEngineConfig()
+        self._replay = CompressedReplayBuffer(self.cfg.replay_capacity)
+        self._ecc = ECCState(params)
+        self._bench = ForgettingBenchmark()
+        self.eval_loss = eval_loss
+        self._task, self._step = 0, 0
+
+    def on_step(self, task_id: Optional[int] = None) -> None:
+        self._step += 1
+        if not self._ecc.initialized:
+            self._ecc.update_anchor()
+        self._ecc.update_fisher(self.cfg.ecc_alpha)
+        if self.should_check_forgetting():
+            self._ecc.update_anchor()
+            self._replay.update_importance(self.cfg.importance_decay)
+            if self.eval_loss is not None:
+                self._bench.evaluate(self.eval_loss)
+
+    def register_eval(self, eval_inputs, eval_targets) -> int:
+        tid = self._bench.register_task(eval_inputs, eval_targets)
+        if self.eval_loss is not None:
+            loss = float(self.eval_loss(eval_inputs, eval_targets))
+            self._bench.record_zero_shot(tid, loss)
+        return tid
+
+    def on_task_boundary(self, new_task_id: int, eval_inputs=None, eval_targets=None) -> None:
+        """The task that ends gets its baseline (the loss now, right after it was learnt); the new task's evaluation set is
+        registered; the anchors and the consolidated Fisher move to the current weights."""
+        if new_task_id == self._task:
+            return
+        if self.eval_loss is not None:
+            for t in self._bench.tasks:
+                if t["baseline"] is None:
+                    t["baseline"] = t["current"] = float(self.eval_loss(t["x"], t["y"]))
+        if eval_inputs is not None or eval_targets is not None:
+            self.register_eval(eval_inputs, eval_targets)
+        self._task = new_task_id
+        self._ecc.update_anchor()
+
+    def penalty(self) -> torch.Tensor:
+        """The quadratic anchor penalty to add to the loss (lambda / 2 * sum F (w - anchor)^2)."""
+        return self._ecc.regularize(self.cfg.ecc_lambda)
+
+    def effective_lr(self, base_lr: float) -> float:
+        fm = self._bench.compute()
+        if fm.avg_forgetting > self.cfg.forgetting_threshold:
+            return base_lr * self.cfg.stability_lr_factor * (1.0 + fm.avg_forgetting / self.cfg.forgetting_threshold)
+        return base_lr * self.cfg.plasticity_lr_factor
+
+    def should_check_forgetting(self) -> bool:
+        return self._step % max(1, self.cfg.forgetting_check_interval) == 0
+
+    def forgetting_bound(self, task_id: int = 0, replay_ratio: float = 0.5) -> float:
+        fisher = [e.fisher for e in self._replay.entries if e.task_id == task_id]
+        return theorem11_bound(Theorem11Params(self.cfg.ecc_lambda, len(self._replay), len(fisher), sum(fisher) / len(fisher) if fisher else 0.0,
+                                               replay_ratio, self.cfg.forgetting_temperature))
+
+    def ecc(self) -> ECCState:
+        return self._ecc
+
+    def benchmark(self) -> ForgettingBenchmark:
+        return self._bench
+
+    def replay(self) -> CompressedReplayBuffer:
+        return self._replay
+
+    def current_task(self) -> int:
+        return self._task
+
+    def current_step(self) -> int:
+        return self._step
+
+    def forgetting_metrics(self) -> ForgettingMetrics:
+        return self._bench.compute()

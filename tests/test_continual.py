@@ -125,3 +125,42 @@ def test_mtp_heads_learn_and_tune_draft_length():
     for _ in range(200):
         tr.update_draft_k(0.1)
     assert tr.draft_k == 1
+
+
+def test_continual_engine_hooks_and_effective_lr():
+    import math
+    import pytest
+    from innova_b200.training.continual import ContinualEngine, ContinualEngineConfig, Theorem11Params, theorem11_bound
+    assert theorem11_bound(Theorem11Params(buffer_size=0)) == 1.0 and theorem11_bound(Theorem11Params(buffer_size=10, temperature=0.0)) == 1.0
+    p = Theorem11Params(lam=2.0, buffer_size=100, task_k_samples=50, avg_fisher_importance=5.0, replay_ratio=0.5, temperature=100.0)
+    assert theorem11_bound(p) == pytest.approx(2.0 * 5.0 / 100 + 0.5 * math.exp(-0.5))
+    assert theorem11_bound(Theorem11Params(lam=1e6, buffer_size=1, avg_fisher_importance=1.0)) == 1.0
+    torch.manual_seed(0)
+    w = torch.nn.Parameter(torch.zeros(4))
+    targets = {0: torch.tensor([1.0, 1.0, 0.0, 0.0]), 1: torch.tensor([-1.0, 1.0, 2.0, 0.0])}
+    loss_on = lambda x, y: float(((w.detach() - y) ** 2).sum())
+    eng = ContinualEngine([w], ContinualEngineConfig(forgetting_check_interval=5, forgetting_threshold=0.05, ecc_alpha=0.5, ecc_lambda=0.0), eval_loss=loss_on)
+    assert eng.register_eval(None, targets[0]) == 0 and eng.benchmark().tasks[0]["zero_shot"] == pytest.approx(2.0)
+    opt = torch.optim.SGD([w], lr=0.2)
+    for _ in range(20):
+        loss = ((w - targets[0]) ** 2).sum() + eng.penalty()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        eng.on_step(0)
+    assert eng.current_step() == 20 and eng.should_check_forgetting() and float(eng.ecc().running[0][0]) > 0 and float(eng.ecc().running[0][3]) == 0
+    assert eng.effective_lr(1.0) == 2.0                                  # nothing forgotten yet: the plasticity factor
+    eng.on_task_boundary(1, None, targets[1])
+    assert eng.current_task() == 1 and eng.benchmark().tasks[0]["baseline"] < 0.01 and len(eng.benchmark().tasks) == 2
+    eng.on_task_boundary(1, None, targets[1])                            # same id again: nothing happens
+    assert len(eng.benchmark().tasks) == 2
+    for _ in range(20):
+        loss = ((w - targets[1]) ** 2).sum()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        eng.on_step(1)
+    fm = eng.forgetting_metrics()
+    assert fm.num_tasks == 2 and fm.avg_forgetting > 3.5                  # task 0's loss went from ~0 to ~(2^2 + 2^2) / ... on the moved weights
+    assert eng.effective_lr(1.0) == pytest.approx(0.5 * (1 + fm.avg_forgetting / 0.05))
+    assert 0.0 <= eng.forgetting_bound(0) <= 1.0 and len(eng.replay()) == 0
