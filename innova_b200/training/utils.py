@@ -1002,3 +1002,48 @@ class ModelSnapshot:
                         st[key] = t.view(p.shape).to(p.device)
                         st.setdefault("step", torch.tensor(float(step)))
             return step, lr
+
+
+# ------------------------------------------------------------------------------------------------ MoE auxiliary losses on dense masks / gates
+def compute_load_balance_loss(expert_mask: torch.Tensor) -> torch.Tensor:
+    """E * sum_e c_e^2 / (sum_e c_e)^2 with c_e the number of assignments on expert e (``expert_mask`` [..., E] of 0/1):
+    1 for a perfectly even split, E when one expert takes everything (reference: src/training_utils.cpp:13-43)."""
+    counts = expert_mask.float().reshape(-1, expert_mask.shape[-1]).sum(0)
+    total = counts.sum()
+    return torch.where(total > 0, expert_mask.shape[-1] * counts.square().sum() / total.square().clamp_min(1e-30), total.new_zeros(()))
+
+
+def compute_z_loss(router_logits: torch.Tensor, reference: bool = False) -> torch.Tensor:
+    """Mean squared log-sum-exp of the router logits over tokens (the ST-MoE z-loss). ``reference=True`` gives the reference's
+    statistic instead: the mean of log(|logit|)^2 over all logits (src/training_utils.cpp:48-64)."""
+    if reference:
+        return torch.log(router_logits.float().abs().clamp_min(1e-10)).square().mean()
+    return torch.logsumexp(router_logits.float(), dim=-1).square().mean()
+
+
+def compute_importance_loss(expert_gates: torch.Tensor) -> torch.Tensor:
+    """Squared coefficient of variation of the per-expert gate mass: Var_e(sum of gates) / (mean_e^2 + 1e-8)
+    (src/training_utils.cpp:69-98)."""
+    imp = expert_gates.float().reshape(-1, expert_gates.shape[-1]).sum(0)
+    return imp.var(unbiased=False) / (imp.mean().square() + 1e-8)
+
+
+@dataclass
+class MoEAuxLosses:
+    load_balance_loss: Optional[torch.Tensor] = None
+    z_loss: Optional[torch.Tensor] = None
+    importance_loss: Optional[torch.Tensor] = None
+    load_balance_weight: float = 0.01
+    z_loss_weight: float = 0.0001
+    importance_weight: float = 0.01
+
+    def total(self) -> torch.Tensor:
+        return self.load_balance_loss + self.z_loss + self.importance_loss
+
+
+def compute_moe_aux_losses(router_logits: torch.Tensor, expert_gates: torch.Tensor, expert_mask: torch.Tensor,
+                           cfg: Optional[MoEAuxLosses] = None, reference_z: bool = False) -> MoEAuxLosses:
+    """The three auxiliary losses, each already multiplied by its weight; all differentiable in the logits and gates."""
+    c = cfg or MoEAuxLosses()
+    return MoEAuxLosses(compute_load_balance_loss(expert_mask) * c.load_balance_weight, compute_z_loss(router_logits, reference_z) * c.z_loss_weight,
+                        compute_importance_loss(expert_gates) * c.importance_weight, c.load_balance_weight, c.z_loss_weight, c.importance_weight)

@@ -95,3 +95,28 @@ def test_sentence_embedder_pools_projects_and_normalises():
     ym = emb(x, mask)
     ref = torch.nn.functional.normalize(x[0, :2].mean(0) @ emb.projection.t(), dim=-1)
     assert torch.allclose(ym[0], ref, atol=1e-5) and torch.allclose(ym[1], y[1], atol=1e-6)
+
+
+def test_moe_aux_losses_on_masks_and_gates():
+    import math
+    import pytest
+    from innova_b200.training.utils import (MoEAuxLosses, compute_importance_loss, compute_load_balance_loss, compute_moe_aux_losses, compute_z_loss)
+    even = torch.eye(4).repeat(2, 3, 1)                                   # [2, 12, 4]: every expert gets the same share
+    one = torch.zeros(2, 12, 4)
+    one[..., 2] = 1
+    assert float(compute_load_balance_loss(even)) == pytest.approx(1.0) and float(compute_load_balance_loss(one)) == pytest.approx(4.0)
+    assert float(compute_load_balance_loss(torch.zeros(2, 3, 4))) == 0.0
+    logits = torch.tensor([[0.0, math.log(3.0)], [1.0, 1.0]])
+    assert float(compute_z_loss(logits)) == pytest.approx((math.log(4.0) ** 2 + (1 + math.log(2.0)) ** 2) / 2)
+    assert float(compute_z_loss(torch.tensor([[math.e, -math.e, 0.0]]), reference=True)) == pytest.approx((1 + 1 + math.log(1e-10) ** 2) / 3)
+    gates = torch.tensor([[[0.5, 0.5], [0.9, 0.1]]])
+    imp = torch.tensor([1.4, 0.6])
+    assert float(compute_importance_loss(gates)) == pytest.approx(float(imp.var(unbiased=False) / (imp.mean() ** 2 + 1e-8)))
+    assert float(compute_importance_loss(torch.full((3, 5, 4), 0.25))) == pytest.approx(0.0, abs=1e-7)
+    rl = torch.randn(2, 6, 4, requires_grad=True)
+    g = torch.softmax(rl, -1)
+    mask = torch.nn.functional.one_hot(g.argmax(-1), 4).float()
+    out = compute_moe_aux_losses(rl, g, mask, MoEAuxLosses(load_balance_weight=0.5, z_loss_weight=0.1, importance_weight=2.0))
+    assert float(out.load_balance_loss) == pytest.approx(0.5 * float(compute_load_balance_loss(mask))) and out.importance_weight == 2.0
+    out.total().backward()
+    assert rl.grad is not None and float(rl.grad.abs().sum()) > 0
