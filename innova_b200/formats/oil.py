@@ -383,3 +383,32 @@ class OILIdxReader:
         if self._names is None:
             self._names = read_idx(self.path)
         return list(self._names)
+
+
+# ------------------------------------------------------------------------------------------------ small helpers with the reference's names
+def quantize_block_all(fmt, w):
+    """One block -> (index bytes, codebook bytes) in wire format ``fmt`` (reference: ``quantize_block_all``, include/oil/block_codec.h)."""
+    return encode_block(fmt, w)
+
+
+def block_claimed_bytes(fmt, n: int) -> int:
+    return claimed_bytes(fmt, n)
+
+
+def block_actual_bpw(fmt, w) -> float:
+    """Bits per weight the codec really stores for this block (payload bytes x 8 / weights)."""
+    idx, cb = encode_block(fmt, w)
+    return 8.0 * (len(idx) + len(cb)) / max(1, _f32(w).size)
+
+
+def format_to_dtype(fmt) -> str:
+    """The storage type a format decodes from: fp32, fp16 or packed indices."""
+    name = FORMATS[format_id(fmt)]
+    return "float32" if name == "OIL32" else "float16" if name.startswith("OIL16") else "uint8"
+
+
+def dtype_size(dtype) -> int:
+    """Bytes per element of a torch dtype or its name."""
+    if isinstance(dtype, str):
+        dtype = getattr(torch, dtype)
+    return torch.empty((), dtype=dtype).element_size()

@@ -618,3 +618,20 @@ class SentenceEmbedder(torch.nn.Module):
             pooled = x.mean(1)
         out = F.normalize(pooled.float() @ self.projection.float().t(), dim=-1).to(x.dtype)
         return out if token_embeddings.dim() == 3 else out[0]
+
+
+def compute_logprobs(logits: torch.Tensor, tokens) -> List[List[float]]:
+    """One row of log-probabilities over the vocabulary per token position (reference: ``compute_logprobs``,
+    include/oil/inference_opt.h:222): ``logits`` [..., S, V]; positions beyond the rows of ``logits`` give empty lists."""
+    n = len(tokens)
+    if n == 0:
+        return []
+    rows = torch.log_softmax(logits.float().reshape(-1, logits.shape[-1]), dim=-1)
+    return [rows[i].tolist() if i < rows.shape[0] else [] for i in range(n)]
+
+
+def token_logprobs(logits: torch.Tensor, tokens) -> List[float]:
+    """The log-probability of each given token at its position (what an API's ``logprobs`` field carries)."""
+    rows = torch.log_softmax(logits.float().reshape(-1, logits.shape[-1]), dim=-1)
+    ids = torch.as_tensor(list(tokens), dtype=torch.long)[: rows.shape[0]]
+    return rows[torch.arange(ids.numel()), ids.clamp(0, rows.shape[1] - 1)].tolist()

@@ -207,3 +207,25 @@ class DynamicExpertPool(nn.Module):
                 g, u = h.chunk(2, -1)
                 out.index_add_(0, tok, (torch.nn.functional.silu(g) * u) @ self.w_down[e].float().t() * w[tok, slot, None])
         return out.to(x.dtype).view_as(x)
+
+
+@dataclass
+class AssignmentBalance:
+    token_counts: List[int]
+    load_balance_loss: float
+    stddev: float
+
+
+def compute_balance(assignments, n_experts: int) -> AssignmentBalance:
+    """Counts per expert of a flat assignment list (ids outside [0, n_experts) are ignored), their standard deviation, and the
+    loss sum_e (c_e - mean)^2 / (mean^2 + 1e-8) / n_experts^2 with mean = len(assignments) / n_experts; an empty list gives
+    loss 1 (reference: include/oil/moe_enhance.h:45-50, src/moe_enhance.cpp:230-264)."""
+    assert n_experts > 0, "compute_balance: n_experts must be > 0"
+    a = torch.as_tensor(list(assignments), dtype=torch.long)
+    if a.numel() == 0:
+        return AssignmentBalance([0] * n_experts, 1.0, 0.0)
+    counts = torch.bincount(a[(a >= 0) & (a < n_experts)], minlength=n_experts).float()
+    mean = a.numel() / n_experts
+    dev2 = (counts - mean).square()
+    return AssignmentBalance([int(c) for c in counts.tolist()], float((dev2 / (mean * mean + 1e-8)).sum() / (n_experts * n_experts)),
+                             float((dev2.sum() / n_experts).sqrt()))

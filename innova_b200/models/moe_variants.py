@@ -327,3 +327,30 @@ QuantizedINT8MoE, SparkMoE, Oil1MoE, OIL8MoE, OIL4MoE = _named("quantized_int8_m
 VARIANT_CLASSES = {c.__name__: c for c in (SparseTop1MoE, SparseTop2MoE, SparseTopKMoE, SoftMoE, HierarchicalMoE, MoMoE, ExpertChoiceMoE, HashMoE, CrossLayerMoE,
                                            MultiModalMoE, MMoE, DeepSeekMoE, BaseLayerMoE, DenseMoE, SharedExpertMoE, ResidualMoE, GatingDropoutMoE, DomainMoE,
                                            ProductKeyMoE, AttentionMoE, MLAMoE, MambaMoE, QuantizedINT8MoE, SparkMoE, Oil1MoE, OIL8MoE, OIL4MoE)}
+
+
+def moe_variant_count() -> int:
+    return len(VARIANTS)
+
+
+def moe_variant_name_by_index(index: int) -> str:
+    return VARIANTS[index] if 0 <= index < len(VARIANTS) else "unknown"
+
+
+def moe_variant_name(variant) -> str:
+    return moe_variant_name_by_index(variant) if isinstance(variant, int) else (variant if variant in VARIANTS else "unknown")
+
+
+def hash_token(token_id: int, range_: int) -> int:
+    """The reference's token hash (src/moe_variants.cpp:21-26): multiply by the 64-bit golden-ratio constant, fold the high
+    bits down, multiply again, reduce modulo ``range_`` (all in unsigned 64-bit arithmetic)."""
+    m = (1 << 64) - 1
+    h = (int(token_id) * 0x9E3779B97F4A7C15) & m
+    h ^= h >> 37
+    h = (h * 0xBF58476D1CE4E5B9) & m
+    return h % int(range_)
+
+
+def create_experts(count: int, hidden: int, ffn_hidden: int, dtype=torch.float32, device=None, seed: int = 0) -> ExpertBank:
+    """``count`` SwiGLU experts as one ``ExpertBank`` (stacked weights: the grouped GEMMs take them without a gather)."""
+    return ExpertBank(count, hidden, ffn_hidden, dtype, device, seed)

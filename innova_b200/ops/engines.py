@@ -497,3 +497,30 @@ def int8_quantize_per_token(src: torch.Tensor) -> Tuple[torch.Tensor, torch.Tens
 def int8_dequantize(q: torch.Tensor, inv_scale) -> torch.Tensor:
     s = torch.as_tensor(inv_scale, device=q.device, dtype=torch.float32)
     return q.float() * (s[..., None] if s.dim() else s)
+
+
+# ------------------------------------------------------------------------------------------------ free-function forms (include/oil/oil_engines.h, int8_quant.h)
+_ENG_E4M3, _ENG_E5M2 = FP8E4M3Engine(), FP8E5M2Engine()
+fp8_e4m3_quantize_tensor, fp8_e4m3_dequant_tensor, fp8_e4m3_quant_gemm = _ENG_E4M3.quantize, _ENG_E4M3.dequantize, _ENG_E4M3.quant_gemm
+fp8_e4m3_quantize_per_channel, fp8_e4m3_dequantize_per_channel = _ENG_E4M3.quantize_per_channel, _ENG_E4M3.dequantize_per_channel
+fp8_e5m2_quantize_tensor, fp8_e5m2_dequant_tensor, fp8_e5m2_quant_gemm = _ENG_E5M2.quantize, _ENG_E5M2.dequantize, _ENG_E5M2.quant_gemm
+fp8_e5m2_quantize_per_channel, fp8_e5m2_dequantize_per_channel = _ENG_E5M2.quantize_per_channel, _ENG_E5M2.dequantize_per_channel
+
+
+def fp8_e4m3_quant_error(x: torch.Tensor) -> float:
+    return compute_quant_error(x, _ENG_E4M3.dequantize(_ENG_E4M3.quantize(x)))
+
+
+def fp8_e4m3_quant_snr(x: torch.Tensor) -> float:
+    return compute_quant_snr(x, _ENG_E4M3.dequantize(_ENG_E4M3.quantize(x)))
+
+
+def fp8_e5m2_quant_error(x: torch.Tensor) -> float:
+    return compute_quant_error(x, _ENG_E5M2.dequantize(_ENG_E5M2.quantize(x)))
+
+
+def fp8_e5m2_quant_snr(x: torch.Tensor) -> float:
+    return compute_quant_snr(x, _ENG_E5M2.dequantize(_ENG_E5M2.quantize(x)))
+
+
+quantize_per_tensor, quantize_per_token, dequantize_per_tensor = int8_quantize_per_tensor, int8_quantize_per_token, int8_dequantize

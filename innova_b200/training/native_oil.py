@@ -241,3 +241,16 @@ class NativeOILTrainer:
             return {"phase": "warmup"}
         return {"phase": "native", **s.counts(), "avg_scale": float(s.scales.mean()), "bits_per_weight": s.bits_per_weight(),
                 "indices_moved": int(s.changed.item())}
+
+
+def native_format_name(fmt) -> str:
+    """"native_oil8" / "native_oil1" / "native_oil4" for the three block formats of the train-in-format store (by name or by the
+    reference's enum value 0 / 1 / 2); "unknown" otherwise."""
+    names = {0: "oil8", 1: "oil1", 2: "oil4"}
+    key = names.get(fmt, str(fmt).lower().replace("native_", ""))
+    return f"native_{key}" if key in ("oil8", "oil1", "oil4") else "unknown"
+
+
+def oil1_value(idx: int) -> float:
+    """Ternary index -> value: 0 -> -1, 1 -> 0, 2 -> +1."""
+    return float(int(idx)) - 1.0

@@ -1047,3 +1047,28 @@ def compute_moe_aux_losses(router_logits: torch.Tensor, expert_gates: torch.Tens
     c = cfg or MoEAuxLosses()
     return MoEAuxLosses(compute_load_balance_loss(expert_mask) * c.load_balance_weight, compute_z_loss(router_logits, reference_z) * c.z_loss_weight,
                         compute_importance_loss(expert_gates) * c.importance_weight, c.load_balance_weight, c.z_loss_weight, c.importance_weight)
+
+
+@torch.no_grad()
+def eval_generation_speed(model, prompt_tokens: int = 32, gen_tokens: int = 32, device=None) -> float:
+    """Generated tokens per second of greedy decoding after a prompt of ``prompt_tokens`` random ids (reference:
+    ``eval_generation_speed``, include/oil/eval.h:47). Uses the package's ``Generator`` (KV cache, paged kernels on a GPU)."""
+    import time
+    from ..inference.generator import Generator
+    dev = torch.device(device) if device is not None else next(model.parameters()).device
+    vocab = int(model.cfg.vocab_size)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, vocab, (1, max(1, prompt_tokens)), generator=g).to(dev)
+    gen = Generator(model, kv_format="bf16", max_batch=1, max_seq=prompt.shape[1] + gen_tokens + 2)
+    if dev.type == "cuda":
+        torch.cuda.synchronize(dev)
+    t0 = time.perf_counter()
+    gen.generate_tokens(prompt, gen_tokens)
+    if dev.type == "cuda":
+        torch.cuda.synchronize(dev)
+    return gen_tokens / max(time.perf_counter() - t0, 1e-9)
+
+
+def collect_dense_params(model) -> List[torch.nn.Parameter]:
+    """Every trainable parameter of a dense model in registration order (reference: ``collect_dense_params``, include/oil/trainer.h)."""
+    return [p for p in model.parameters() if p.requires_grad]

@@ -493,3 +493,24 @@ class RLHFIntegration:
                 learner.update(torch.tensor(p, dtype=torch.float32))
             pipe.metrics.history.append({"round": r, "forgetting_loss": learner.forgetting_loss()})
         return pipe.metrics
+
+
+# ------------------------------------------------------------------------------------------------ helpers of the reference's asi_utils.h
+def greedy_argmax(logits) -> int:
+    return int(torch.as_tensor(logits).reshape(-1).argmax())
+
+
+def to_lower(text: str) -> str:
+    return text.lower()
+
+
+@torch.no_grad()
+def generate_new_tokens(model, ids: Sequence[int], vocab_size: int = 0, max_new: int = 32) -> List[int]:
+    """Greedy continuation of ``ids``: the new tokens only. The context is cut to the model's window from the left."""
+    window = int(getattr(model.cfg, "max_seq_len", 1024))
+    dev = next(model.parameters()).device
+    out: List[int] = []
+    for _ in range(max(0, max_new)):
+        ctx = (list(ids) + out)[-window:]
+        out.append(int(model(torch.tensor([ctx], device=dev))[0, -1].float().argmax()))
+    return out

@@ -188,3 +188,65 @@ class MultiGPUManager:
 
     def memory_in_use(self, idx: int) -> int:
         return sum(b.numel() for b in self._blocks.get(idx, {}).values())
+
+
+# ------------------------------------------------------------------------------------------------ small queries of the reference's backend header
+def backend_name(backend: str) -> str:
+    return {"cpu": "CPU (PyTorch)", "cuda_sm100": "CUDA sm_100a (tcgen05 kernels)", "distributed": "CUDA sm_100a, one process per GPU"}.get(backend, "unknown")
+
+
+def is_cuda_available() -> bool:
+    return torch.cuda.is_available()
+
+
+def is_avx2_available() -> bool:
+    return "avx2" in probe_hardware().cpu_flags
+
+
+def is_avx512_available() -> bool:
+    return "avx512f" in probe_hardware().cpu_flags
+
+
+def is_neon_available() -> bool:
+    import platform
+    return platform.machine().lower() in ("aarch64", "arm64")
+
+
+def is_directx_available() -> bool:
+    return False
+
+
+def is_vulkan_available() -> bool:
+    return False
+
+
+def cpu_memory_total() -> int:
+    try:
+        return os.sysconf("SC_PAGE_SIZE") * os.sysconf("SC_PHYS_PAGES")
+    except (ValueError, OSError):
+        return 0
+
+
+def cpu_memory_free() -> int:
+    try:
+        with open("/proc/meminfo") as f:
+            for line in f:
+                if line.startswith("MemAvailable:"):
+                    return int(line.split()[1]) * 1024
+    except OSError:
+        pass
+    return 0
+
+
+def gpu_memory_free(device: int = 0) -> int:
+    return torch.cuda.mem_get_info(device)[0] if torch.cuda.is_available() else 0
+
+
+def auto_select_backend(model_size_bytes: int = 0) -> str:
+    return select_optimal_backend(probe_hardware(), model_size_bytes)
+
+
+def detect_cpu_isa() -> int:
+    """2 = AVX2 or better, 1 = SSE4.1, 0 = neither (reference: adapters::prod::detect_cpu_isa)."""
+    flags = probe_hardware().cpu_flags
+    return 2 if "avx2" in flags else 1 if "sse4_1" in flags else 0

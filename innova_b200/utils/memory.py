@@ -261,3 +261,15 @@ class SlabPool:
 
     def failures(self) -> int:
         return int(_native().inv_pool_failures(self._h))
+
+
+_THREAD_POOLS: Optional[ThreadLocalPoolRegistry] = None
+
+
+def get_thread_local_pool(capacity: int = 1 << 20) -> MemoryPool:
+    """This thread's host scratch pool from a process-wide registry created on first use (reference: ``get_thread_local_pool``,
+    include/oil/memory.h)."""
+    global _THREAD_POOLS
+    if _THREAD_POOLS is None:
+        _THREAD_POOLS = ThreadLocalPoolRegistry(capacity)
+    return _THREAD_POOLS.get()

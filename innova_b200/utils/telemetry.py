@@ -448,3 +448,71 @@ def sops_global() -> SopsGlobalState:
 
 def sops_report() -> SopsReport:
     return _SOPS_STATE.report()
+
+
+# ------------------------------------------------------------------------------------------------ the hooks as free functions (include/oil/sops_integration.h)
+def sops_hook_training_start():
+    _SOPS_STATE.training_start()
+
+
+def sops_hook_training_stop(fmt, elements: int, seconds: Optional[float] = None):
+    _SOPS_STATE.training_stop(fmt, elements, seconds)
+
+
+def sops_hook_training_stop_mixed(formats, counts, seconds: Optional[float] = None):
+    _SOPS_STATE.training_stop_mixed(formats, counts, seconds)
+
+
+def sops_hook_inference_start():
+    _SOPS_STATE.inference_start()
+
+
+def sops_hook_inference_stop(fmt, elements: int, seconds: Optional[float] = None):
+    _SOPS_STATE.inference_stop(fmt, elements, seconds)
+
+
+def sops_hook_quantize_start():
+    _SOPS_STATE.quantize_start()
+
+
+def sops_hook_quantize_stop(fmt, elements: int, seconds: Optional[float] = None):
+    _SOPS_STATE.quantize_stop(fmt, elements, seconds)
+
+
+def sops_hook_small_batch(fmt, elements: int, seconds: float = 1e-6):
+    _SOPS_STATE.small_batch(fmt, elements, seconds)
+
+
+def sops_hook_stability_plasticity(forgetting_weight, base_lr, stability_factor, plasticity_factor, threshold):
+    return _SOPS_STATE.stability_plasticity(forgetting_weight, base_lr, stability_factor, plasticity_factor, threshold)
+
+
+def sops_hook_draft_length_tune(current_k, acceptance_rate, min_k, max_k, target_rate):
+    return _SOPS_STATE.draft_length_tune(current_k, acceptance_rate, min_k, max_k, target_rate)
+
+
+def sops_hook_speculative_propose(count: int):
+    _SOPS_STATE.speculative_propose(count)
+
+
+def sops_hook_speculative_accept(count: int):
+    _SOPS_STATE.speculative_accept(count)
+
+
+def sops_unit_name(ops_per_s: float) -> str:
+    """The unit a rate is best printed in: SOPS (1e21), mSOPS, uSOPS, nSOPS, pSOPS or fSOPS."""
+    s = ops_per_s / 1e21
+    for unit, scale in (("SOPS", 1.0), ("mSOPS", 1e-3), ("uSOPS", 1e-6), ("nSOPS", 1e-9), ("pSOPS", 1e-12)):
+        if s >= scale:
+            return unit
+    return "fSOPS"
+
+
+def sops_best_value(ops_per_s: float) -> float:
+    """The rate expressed in the unit ``sops_unit_name`` picks."""
+    scale = {"SOPS": 1.0, "mSOPS": 1e-3, "uSOPS": 1e-6, "nSOPS": 1e-9, "pSOPS": 1e-12, "fSOPS": 1e-15}[sops_unit_name(ops_per_s)]
+    return ops_per_s / 1e21 / scale
+
+
+def sops_isa_name() -> str:
+    return "sm_100a" if torch.cuda.is_available() else "host"

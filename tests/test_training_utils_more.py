@@ -120,3 +120,56 @@ def test_moe_aux_losses_on_masks_and_gates():
     assert float(out.load_balance_loss) == pytest.approx(0.5 * float(compute_load_balance_loss(mask))) and out.importance_weight == 2.0
     out.total().backward()
     assert rl.grad is not None and float(rl.grad.abs().sum()) > 0
+
+
+def test_small_helpers_with_the_reference_names(tmp_path):
+    import threading
+    import numpy as np
+    import pytest
+    from innova_b200.formats import oil
+    from innova_b200.inference.serving import compute_logprobs, token_logprobs
+    from innova_b200.models import DenseModel, PRESETS
+    from innova_b200.models.moe_enhance import compute_balance
+    from innova_b200.models.moe_variants import VARIANTS, create_experts, hash_token, moe_variant_count, moe_variant_name, moe_variant_name_by_index
+    from innova_b200.training.native_oil import native_format_name, oil1_value
+    from innova_b200.training.utils import collect_dense_params, eval_generation_speed
+    from innova_b200.utils.asi_ext import generate_new_tokens, greedy_argmax, to_lower
+    from innova_b200.utils.memory import get_thread_local_pool
+    w = np.random.default_rng(0).standard_normal(256).astype(np.float32)
+    idx, cb = oil.quantize_block_all("OIL4", w)
+    assert len(idx) == 128 and oil.block_claimed_bytes("OIL4", 256) >= 128 and len(cb) > 0
+    assert oil.block_actual_bpw("OIL4", w) <= 8.0 * oil.block_claimed_bytes("OIL4", 256) / 256 + 1e-6
+    assert oil.format_to_dtype("OIL32") == "float32" and oil.format_to_dtype("OIL16") == "float16" and oil.format_to_dtype("OIL4") == "uint8"
+    assert oil.dtype_size(torch.bfloat16) == 2 and oil.dtype_size("float32") == 4
+    assert moe_variant_count() == len(VARIANTS) == 27 and moe_variant_name_by_index(0) == "sparse_top1" and moe_variant_name_by_index(99) == "unknown"
+    assert moe_variant_name(3) == VARIANTS[3] and moe_variant_name("oil4_moe") == "oil4_moe" and moe_variant_name("x") == "unknown"
+    m = (1 << 64) - 1
+    h = (12345 * 0x9E3779B97F4A7C15) & m
+    h ^= h >> 37
+    assert hash_token(12345, 64) == ((h * 0xBF58476D1CE4E5B9) & m) % 64 and 0 <= hash_token(-7 & m, 5) < 5
+    bank = create_experts(3, 8, 16)
+    assert bank.w_gu.shape == (3, 32, 8)
+    bal = compute_balance([0, 0, 1, 3, 3, 3, 9, -1], 4)
+    mean = 8 / 4
+    assert bal.token_counts == [2, 1, 0, 3] and bal.stddev == pytest.approx((sum((c - mean) ** 2 for c in (2, 1, 0, 3)) / 4) ** 0.5)
+    assert bal.load_balance_loss == pytest.approx(sum((c - mean) ** 2 / (mean * mean + 1e-8) for c in (2, 1, 0, 3)) / 16)
+    assert compute_balance([], 3).load_balance_loss == 1.0
+    logits = torch.randn(3, 7)
+    lp = compute_logprobs(logits, [1, 2, 3, 4])
+    assert len(lp) == 4 and lp[3] == [] and lp[0] == pytest.approx(torch.log_softmax(logits[0], -1).tolist()) and compute_logprobs(logits, []) == []
+    assert token_logprobs(logits, [1, 2, 3]) == pytest.approx([float(torch.log_softmax(logits[i], -1)[t]) for i, t in enumerate((1, 2, 3))])
+    assert native_format_name(0) == "native_oil8" and native_format_name("oil4") == "native_oil4" and native_format_name(7) == "unknown"
+    assert [oil1_value(i) for i in range(3)] == [-1.0, 0.0, 1.0]
+    model = DenseModel(PRESETS["tiny"](), dtype=torch.float32, device="cpu", seed=0)
+    assert len(collect_dense_params(model)) == len(list(model.parameters())) and eval_generation_speed(model, 4, 4) > 0
+    new = generate_new_tokens(model, [1, 2, 3], max_new=3)
+    assert len(new) == 3 and new[0] == greedy_argmax(model(torch.tensor([[1, 2, 3]]))[0, -1]) and to_lower("AbC") == "abc"
+    pools = {}
+
+    def grab(i):
+        pools[i] = get_thread_local_pool()
+
+    ts = [threading.Thread(target=grab, args=(i,)) for i in range(2)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert pools[0] is not pools[1] and get_thread_local_pool() is get_thread_local_pool()
