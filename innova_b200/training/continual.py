@@ -45,6 +45,15 @@ class _ReplayEntry:
     hits: int = 0
 
 
+@dataclass
+class ReplaySample:
+    """One decompressed replay sample (src/adapters/include/adapters/continual_trainer.h:58-63)."""
+    input: torch.Tensor
+    target: torch.Tensor
+    fisher_weight: float = 1.0
+    task_id: int = 0
+
+
 class CompressedReplayBuffer:
     """Reservoir of past samples; floating-point tensors are stored as OIL4 indices + block scales (about 4.5 bits
     per value), integer tensors (token ids) as they are. Sampling is proportional to the Fisher importance."""
@@ -98,6 +107,20 @@ class CompressedReplayBuffer:
             ws.append(1.0 / float(w[i]))          # importance correction of the biased draw
         ws = torch.tensor(ws)
         return ins, tgs, ws / ws.mean()
+
+    def sample_records(self, batch_size: int) -> List["ReplaySample"]:
+        """The same draw as ``sample_batch``, as one decompressed record per sample."""
+        if not self.entries:
+            return []
+        w = torch.tensor([max(e.fisher, 1e-8) for e in self.entries])
+        pick = torch.multinomial(w, min(batch_size, len(self.entries)), replacement=len(self.entries) < batch_size, generator=self._g)
+        out = []
+        for i in pick.tolist():
+            e = self.entries[i]
+            e.hits += 1
+            out.append(ReplaySample(self._unpack(e.q_input, e.s_input, e.shape_in), self._unpack(e.q_target, e.s_target, e.shape_tg),
+                                    e.fisher, e.task_id))
+        return out
 
     def set_fisher(self, idx: int, importance: float):
         self.entries[idx].fisher = float(importance)
@@ -367,6 +390,14 @@ class DeltaAdapterConfig:
     delta_format: str = "oil4"
 
 
+@dataclass
+class WeightDelta:
+    """One layer's delta of one adapter (src/adapters/include/adapters/delta_adapter.h:19-23)."""
+    delta: torch.Tensor
+    fisher_diag: torch.Tensor
+    importance: float = 0.0
+
+
 class DeltaAdapterHost:
     """Per-task additive deltas on named weights: ``update_delta`` takes an SGD step on the delta, ``merge_deltas``
     adds it to a base weight, frozen adapters ignore updates; deltas of a frozen adapter can be kept quantised."""
@@ -430,6 +461,13 @@ class DeltaAdapterHost:
         lam = a["lambda"] if lam is None else lam
         return 0.5 * lam * float(sum((l["fisher"] * l["delta"].square()).sum() for l in a["layers"].values()))
 
+    def weight_delta(self, aid: int, name: str) -> Optional[WeightDelta]:
+        """The stored delta of one layer; ``importance`` is its Fisher-weighted squared norm."""
+        l = self.adapters[aid]["layers"].get(name)
+        if l is None:
+            return None
+        return WeightDelta(l["delta"], l["fisher"], float((l["fisher"] * l["delta"].square()).sum()))
+
     def total_adapter_params(self) -> int:
         return sum(l["delta"].numel() for a in self.adapters.values() for l in a["layers"].values())
 
@@ -450,6 +488,20 @@ class MTPHeadConfig:
     target_acceptance_rate: float = 0.7
     min_draft_k: int = 1
     max_draft_k: int = 8
+
+
+@dataclass
+class MTPHeadWeights:
+    """One draft head as plain tensors (src/adapters/include/adapters/mtp_head_trainer.h:37-45). ``projection`` is what the
+    head multiplies by (the dequantised values once the head has been quantised); ``quantized_projection`` holds the block
+    indices and ``scale`` the block scales of that quantised form."""
+    projection: torch.Tensor
+    output_bias: torch.Tensor
+    quantized_projection: Optional[torch.Tensor] = None
+    scale: Optional[torch.Tensor] = None
+    is_quantized: bool = False
+    projection_rows: int = 0
+    projection_cols: int = 0
 
 
 class MTPHeadTrainer:
@@ -531,6 +583,16 @@ class MTPHeadTrainer:
             self.draft_k -= 1
         self.draft_k = max(self.cfg.min_draft_k, min(self.cfg.max_draft_k, min(self.cfg.num_heads, self.draft_k)))
         return self.draft_k
+
+    def head_weights(self, i: int) -> MTPHeadWeights:
+        q = self.quantized[i]
+        return MTPHeadWeights(self.proj[i], self.bias[i], None if q is None else q[0], None if q is None else q[1], q is not None,
+                              self.proj[i].shape[0], self.proj[i].shape[1])
+
+    def load_head_weights(self, i: int, w: MTPHeadWeights):
+        self.proj[i] = w.projection.to(self.proj[i].device).float().clone()
+        self.bias[i] = w.output_bias.to(self.bias[i].device).float().clone()
+        self.quantized[i] = (w.quantized_projection, w.scale) if w.is_quantized else None
 
     def record(self, accepted: int, proposed: int):
         self.accepted += accepted

@@ -164,3 +164,35 @@ def test_continual_engine_hooks_and_effective_lr():
     assert fm.num_tasks == 2 and fm.avg_forgetting > 3.5                  # task 0's loss went from ~0 to ~(2^2 + 2^2) / ... on the moved weights
     assert eng.effective_lr(1.0) == pytest.approx(0.5 * (1 + fm.avg_forgetting / 0.05))
     assert 0.0 <= eng.forgetting_bound(0) <= 1.0 and len(eng.replay()) == 0
+
+
+def test_record_views_of_replay_delta_and_mtp_heads():
+    import torch
+    from innova_b200.training import continual as ct
+    buf = ct.CompressedReplayBuffer(capacity=8)
+    for k in range(5):
+        buf.insert(torch.randn(4, 8), torch.tensor([k]), task_id=k % 2, fisher_importance=1.0 + k)
+    recs = buf.sample_records(3)
+    assert len(recs) == 3 and all(isinstance(r, ct.ReplaySample) for r in recs)
+    assert all(r.input.shape == (4, 8) and r.task_id == int(r.target) % 2 and r.fisher_weight == 1.0 + int(r.target) for r in recs)
+    assert ct.CompressedReplayBuffer().sample_records(2) == []
+
+    host = ct.DeltaAdapterHost(ct.DeltaAdapterConfig(quantize_deltas=False))
+    aid = host.create_adapter("t")
+    g = torch.ones(3, 3)
+    host.update_delta(aid, "w", g, lr=0.5)
+    host.accumulate_fisher(aid, "w", g * 2)
+    wd = host.weight_delta(aid, "w")
+    assert torch.equal(wd.delta, -0.5 * g) and abs(wd.importance - 9 * 2 * 0.25) < 1e-6
+    assert host.weight_delta(aid, "missing") is None
+
+    tr = ct.MTPHeadTrainer(ct.MTPHeadConfig(num_heads=2, hidden_size=16, vocab_size=32))
+    hw = tr.head_weights(0)
+    assert (hw.projection_rows, hw.projection_cols, hw.is_quantized) == (32, 16, False)
+    tr.quantize_heads()
+    hq = tr.head_weights(1)
+    assert hq.is_quantized and hq.quantized_projection is not None and hq.scale is not None
+    tr2 = ct.MTPHeadTrainer(ct.MTPHeadConfig(num_heads=2, hidden_size=16, vocab_size=32), seed=7)
+    tr2.load_head_weights(1, hq)
+    h = torch.randn(3, 16)
+    assert torch.equal(tr.propose_tokens(h, 2)[:, 1], tr2.propose_tokens(h, 2)[:, 1])
