@@ -108,6 +108,9 @@ def _pct(xs: List[float], p: float) -> float:
 def bench_quant(layers) -> dict:
     rows, totals = [], {name: {"se": 0.0, "bytes": 0, "seconds": 0.0} for name, _ in CODECS}
     n_total = 0
+    if layers:
+        for _, fn in CODECS:                                   # first use loads the host library: keep that out of the timings
+            fn(layers[0][1][:4096])
     for lname, w in layers:
         var = float(w.var()) or 1e-30
         row = {"name": lname, "elements": int(w.size), "formats": {}}
