@@ -17,6 +17,10 @@ those sections return constants there. Here each one is computed from the data o
                   of their standard deviation;
 * ``moe``         expert utilisation, routing entropy and the active-parameter share of a top-k router on random tokens.
 
+``--codec-set`` swaps the compared codecs for those of the reference's other comparison tools: ``gguf`` (Q4_K and Q8_0,
+src/adapters/tools/bench_compare.cpp), ``bitnet`` (ternary b1.58, one-bit, int4, int8, bench_bitnet_comparison.cpp) and
+``spark-loss`` (the sparse grouped code against BF16, bench_spark_loss.cpp).
+
 Input: ``--input-dir`` with ``*.fp32`` files, or ``--synthetic L`` layers of heavy-tailed random weights.
 """
 from __future__ import annotations
@@ -76,8 +80,78 @@ def oil_mixed_roundtrip(w: np.ndarray, target_bpw: float = MIXED_BPW) -> Tuple[n
     return out.reshape(-1)[:n], stored
 
 
-CODECS: List[Tuple[str, Callable]] = [("OIL Mixed", oil_mixed_roundtrip), ("GGUF Q8_0", q8_0_roundtrip), ("Pure SPARK", _oil_single("SPARK_Q0")),
-                                      ("Pure OIL1", _oil_single("OIL1")), ("FP16", fp16_roundtrip)]
+def _blocks(w: np.ndarray, b: int) -> np.ndarray:
+    pad = (-w.size) % b
+    return (np.concatenate([w, np.zeros(pad, np.float32)]) if pad else w).reshape(-1, b)
+
+
+def q4_k_roundtrip(w: np.ndarray) -> Tuple[np.ndarray, int]:
+    """GGUF Q4_K layout: super-blocks of 256 = 8 sub-blocks of 32 four-bit values ``x = d * ls * q - dmin * lm`` with six-bit
+    sub-block scales ``ls`` and minima ``lm`` and fp16 ``d`` / ``dmin`` (144 bytes per super-block, 4.5 bits per weight).
+    Scales come from the plain min / max of each sub-block, without the iterative refit that llama.cpp adds on top."""
+    n = w.size
+    a = _blocks(w, 256).reshape(-1, 8, 32)
+    lo = np.minimum(a.min(axis=2), 0.0)
+    sc = (a.max(axis=2) - lo) / 15.0
+    mn = -lo
+    d = (sc.max(axis=1) / 63.0).astype(np.float16).astype(np.float32)
+    dmin = (mn.max(axis=1) / 63.0).astype(np.float16).astype(np.float32)
+    ls = np.clip(np.rint(np.divide(sc, d[:, None], out=np.zeros_like(sc), where=d[:, None] > 0)), 0, 63)
+    lm = np.clip(np.rint(np.divide(mn, dmin[:, None], out=np.zeros_like(mn), where=dmin[:, None] > 0)), 0, 63)
+    step = (d[:, None] * ls)[:, :, None]
+    off = (dmin[:, None] * lm)[:, :, None]
+    q = np.clip(np.rint(np.divide(a + off, step, out=np.zeros_like(a), where=step > 0)), 0, 15)
+    return (q * step - off).reshape(-1)[:n].astype(np.float32), a.shape[0] * 144
+
+
+def bitnet_ternary_roundtrip(w: np.ndarray) -> Tuple[np.ndarray, int]:
+    """BitNet b1.58: one absmean scale ``g`` per tensor, weights ``clip(round(w / g), -1, 1)``; two bits per weight stored."""
+    g = float(np.abs(w).mean()) or 1.0
+    return (np.clip(np.rint(w / g), -1, 1) * g).astype(np.float32), (w.size + 3) // 4 + 4
+
+
+def bitnet_binary_roundtrip(w: np.ndarray) -> Tuple[np.ndarray, int]:
+    """One-bit BitNet: ``sign(w - mean) * mean|w - mean|`` per tensor; one bit per weight plus the two scalars."""
+    mu = float(w.mean())
+    c = w - mu
+    return (np.where(c >= 0, 1.0, -1.0) * float(np.abs(c).mean()) + mu).astype(np.float32), (w.size + 7) // 8 + 8
+
+
+def _uniform(bits: int, block: int = 32):
+    qmax = (1 << (bits - 1)) - 1
+
+    def run(w):
+        a = _blocks(w, block)
+        d = np.abs(a).max(axis=1, keepdims=True) / qmax
+        q = np.clip(np.rint(np.divide(a, d, out=np.zeros_like(a), where=d > 0)), -qmax - 1, qmax)
+        return (q * d).reshape(-1)[: w.size].astype(np.float32), a.shape[0] * (4 + block * bits // 8)
+    return run
+
+
+def bf16_roundtrip(w: np.ndarray) -> Tuple[np.ndarray, int]:
+    u = w.view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint32) << 16       # round to nearest even
+    return r.view(np.float32), 2 * w.size
+
+
+CODEC_SETS: Dict[str, List[Tuple[str, Callable]]] = {
+    # src/adapters/tools/bench_full.cpp:446-452
+    "default": [("OIL Mixed", oil_mixed_roundtrip), ("GGUF Q8_0", q8_0_roundtrip), ("Pure SPARK", _oil_single("SPARK_Q0")),
+                ("Pure OIL1", _oil_single("OIL1")), ("FP16", fp16_roundtrip)],
+    # src/adapters/tools/bench_compare.cpp: mixed OIL against GGUF Q4_K_M
+    "gguf": [("OIL Mixed", oil_mixed_roundtrip), ("OIL4_GRP", _oil_single("OIL4_GRP")), ("GGUF Q4_K", q4_k_roundtrip), ("GGUF Q8_0", q8_0_roundtrip)],
+    # src/adapters/tools/bench_bitnet_comparison.cpp: mixed OIL against the BitNet weight codes and uniform int4 / int8
+    "bitnet": [("OIL Mixed", oil_mixed_roundtrip), ("BitNet b1.58", bitnet_ternary_roundtrip), ("BitNet 1-bit", bitnet_binary_roundtrip),
+               ("INT4", _uniform(4)), ("INT8", _uniform(8))],
+    # src/adapters/tools/bench_spark_loss.cpp: the sparse grouped code against the 16-bit reference
+    "spark-loss": [("SPARK_SPARSE_GRP", _oil_single("SPARK_SPARSE_GRP")), ("SPARK_Q0_GRP", _oil_single("SPARK_Q0_GRP")), ("BF16", bf16_roundtrip)],
+}
+CODECS: List[Tuple[str, Callable]] = list(CODEC_SETS["default"])
+
+
+def use_codec_set(name: str):
+    """Select which codecs every section compares."""
+    CODECS[:] = CODEC_SETS[name]
 
 
 # ------------------------------------------------------------------------------------------------ data
@@ -232,11 +306,12 @@ SECTIONS = ("quant", "memory", "latency", "kv", "scaling", "robustness", "moe")
 
 
 def run(a) -> dict:
+    use_codec_set(getattr(a, "codec_set", "default"))
     layers = load_layers(a.input_dir, a.synthetic, a.elements, a.max_layers)
     if not layers:
         raise SystemExit(f"no .fp32 files in {a.input_dir!r}")
     want = SECTIONS if a.mode == "all" else tuple(a.mode.split(","))
-    out = {"tool": "oil-bench-full", "layers": len(layers), "mode": a.mode}
+    out = {"tool": "oil-bench-full", "layers": len(layers), "mode": a.mode, "codecs": [n for n, _ in CODECS]}
     q = bench_quant(layers) if any(s in want for s in ("quant", "memory")) else None
     if "quant" in want:
         out["quant"] = q
@@ -268,6 +343,8 @@ def main(argv=None) -> int:
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--codec-set", default="default", choices=sorted(CODEC_SETS), help="default: Q8_0 / SPARK / OIL1 / FP16; gguf: Q4_K and Q8_0; "
+                    "bitnet: ternary, one-bit, int4, int8; spark-loss: sparse grouped code against BF16")
     a = ap.parse_args(argv)
     out = run(a)
     text = json.dumps(out)

@@ -54,4 +54,33 @@ def test_sections_and_cli(tmp_path):
     moe = r["moe"]
     assert abs(sum(moe["expert_utilization"]) - 1.0) < 1e-5 and moe["routing_entropy"] <= moe["max_entropy"] + 1e-6 and moe["active_params_pct"] == 25.0
     only = bf.run(bf.argparse.Namespace(input_dir=str(d), synthetic=0, elements=0, max_layers=1, mode="moe", seq_len=64, num_layers=2, kv_heads=2, head_dim=16, reps=1))
-    assert set(only) == {"tool", "layers", "mode", "moe"} and only["layers"] == 1
+    assert set(only) == {"tool", "layers", "mode", "codecs", "moe"} and only["layers"] == 1
+
+
+def test_other_codec_sets():
+    rng = np.random.default_rng(5)
+    w = (rng.standard_normal(4096) * 0.05).astype(np.float32)
+    d4, b4 = bf.q4_k_roundtrip(w)
+    assert b4 == 16 * 144 and np.mean((d4 - w) ** 2) < 0.01 * w.var()
+    assert np.mean((bf.q8_0_roundtrip(w)[0] - w) ** 2) < np.mean((d4 - w) ** 2)
+    t, bt = bf.bitnet_ternary_roundtrip(w)
+    g = np.abs(w).mean()
+    assert bt == 1024 + 4 and set(np.unique(np.rint(t / g)).tolist()) <= {-1.0, 0.0, 1.0}
+    b1, bb = bf.bitnet_binary_roundtrip(w)
+    assert bb == 512 + 8 and len(np.unique(b1)) == 2 and np.mean((t - w) ** 2) < np.mean((b1 - w) ** 2)
+    i4, by4 = bf._uniform(4)(w)
+    i8, by8 = bf._uniform(8)(w)
+    assert (by4, by8) == (128 * 20, 128 * 36) and np.mean((i8 - w) ** 2) < np.mean((i4 - w) ** 2)
+    x = np.array([1.0, 1.00390625, 1.01171875, -3.0e-5], np.float32)     # exact, tie to even (down), tie to even (up)
+    assert bf.bf16_roundtrip(x)[0].tolist()[:3] == [1.0, 1.0, 1.015625] and bf.bf16_roundtrip(w)[1] == 8192
+    try:
+        for name in ("gguf", "bitnet", "spark-loss"):
+            a = bf.argparse.Namespace(input_dir="", synthetic=1, elements=4096, max_layers=0, mode="quant,robustness", seq_len=64, num_layers=2,
+                                      kv_heads=2, head_dim=16, reps=1, codec_set=name)
+            r = bf.run(a)
+            assert r["codecs"] == [n for n, _ in bf.CODEC_SETS[name]] and set(r["quant"]["summary"]) == set(r["codecs"])
+            assert set(r["robustness"]["noise_0.05"]) == set(r["codecs"])
+        s = r["quant"]["summary"]
+        assert s["BF16"]["mse"] < s["SPARK_Q0_GRP"]["mse"] and s["BF16"]["bpw"] == 16.0
+    finally:
+        bf.use_codec_set("default")
