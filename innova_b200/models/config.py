@@ -104,6 +104,15 @@ def tiny_dense(**kw) -> TransformerConfig:
     return TransformerConfig(**base)
 
 
+def dense_64m(**kw) -> TransformerConfig:
+    """The 14-layer, d 512 decoder (about 67 M weights, vocab 8192, context 2048) that the reference's train-in-format run and
+    its speed probe use (tools/train_64m.cpp:63-71, tools/bench_speed.cpp:10-14)."""
+    base = dict(vocab_size=8192, hidden_size=512, num_layers=14, num_heads=8, head_dim=64, ffn_hidden_size=2048, max_seq_len=2048,
+                activation="silu", norm="rmsnorm", positions="rope", bias=False)
+    base.update(kw)
+    return TransformerConfig(**base)
+
+
 def llama_7b(**kw) -> TransformerConfig:
     base = dict(vocab_size=32000, hidden_size=4096, num_layers=32, num_heads=32, head_dim=128, ffn_hidden_size=11008, max_seq_len=4096,
                 activation="silu", num_kv_heads=8, norm="rmsnorm", positions="rope", bias=False)
@@ -125,4 +134,4 @@ def moe_24l(**kw) -> TransformerConfig:
     return TransformerConfig(**base)
 
 
-PRESETS = {"gpt2-small": gpt2_small, "tiny": tiny_dense, "llama-7b": llama_7b, "dense-13b": dense_13b, "moe-24l": moe_24l}
+PRESETS = {"gpt2-small": gpt2_small, "tiny": tiny_dense, "dense-64m": dense_64m, "llama-7b": llama_7b, "dense-13b": dense_13b, "moe-24l": moe_24l}
