@@ -59,6 +59,11 @@ class HTTPServer:
         self._thread: Optional[threading.Thread] = None
         self._count_lock = threading.Lock()
         self.started_at = time.time()
+        self._slots: Optional[threading.BoundedSemaphore] = None
+
+    def set_max_workers(self, n: int):
+        """At most ``n`` requests are handled at once; the others wait for a free slot (the reference sizes a thread pool)."""
+        self._slots = threading.BoundedSemaphore(n) if n > 0 else None
 
     # configuration in the reference's spelling
     def set_generate_callback(self, cb): self.generate_cb = cb
@@ -180,10 +185,16 @@ class HTTPServer:
             def _serve(self, method):
                 n = int(self.headers.get("Content-Length", 0) or 0)
                 body = self.rfile.read(min(n, server.max_body_size + 1)) if n else b""
+                slots = server._slots
+                if slots is not None:
+                    slots.acquire()
                 try:
                     status, obj, sse = server.handle(method, self.path, body, self.client_address[0])
                 except Exception as e:
                     status, obj, sse = server._err(500, f"internal error: {e}")
+                finally:
+                    if slots is not None:
+                        slots.release()
                 if sse is not None:
                     self.send_response(200)
                     self.send_header("Content-Type", "text/event-stream")

@@ -39,6 +39,17 @@ def test_quantize_evaluate_finetune_bench(tiny):
                           "--device", "cpu").splitlines()[-1])
     assert ev[0]["task_name"] == "perplexity" and ev[0]["perplexity"] < 200
     assert abs(evq[0]["perplexity"] / ev[0]["perplexity"] - 1) < 0.1          # OIL8 keeps the model
+    # the remaining tasks: windowed classification scores and the ending choice from a JSONL file
+    endings = d / "endings.jsonl"
+    text = open(corpus, encoding="utf-8").read()
+    endings.write_text("\n".join(json.dumps({"ctx": text[k:k + 24], "endings": [text[k + 24:k + 36], "zqxj#@~^|zqxj"], "label": 0}) for k in (0, 40, 80, 120)))
+    full = json.loads(_run("innova_b200.cli.evaluate", "--model", model, "--data", corpus, "--context", "32", "--max-tokens", "300", "--task", "all",
+                           "--batch-size", "4", "--endings", str(endings), "--device", "cpu").splitlines()[-1])
+    by = {r["task_name"]: r for r in full}
+    assert set(by) == {"perplexity", "accuracy", "generation", "classification", "hellaswag"}
+    assert by["classification"]["total"] == 299 and 0 < by["classification"]["f1_score"] <= 1
+    assert abs(by["classification"]["accuracy"] - by["classification"]["correct"] / 299) < 1e-9
+    assert by["hellaswag"]["total"] == 4 and by["hellaswag"]["accuracy"] >= 0.75   # text it was trained on beats noise
     for method, out in (("full", "ft.oil"), ("rank", "a.nrad"), ("slots", "k.kexp")):
         r = json.loads(_run("innova_b200.cli.finetune", "--model", model, "--data", corpus, "--output", str(d / out), "--method", method, "--lr",
                             "1e-3", "--batch-size", "2", "--seq-length", "32", "--max-steps", "4", "--device", "cpu", "--rank", "4").splitlines()[-1])
