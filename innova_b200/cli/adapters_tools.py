@@ -65,8 +65,97 @@ def chat(argv=None, stdin=None, stdout=None):
     return 0
 
 
-def adapt(argv=None):
+_RAW_OF = {"raw_fp32": "fp32", "raw_fp16": "fp16", "raw_fp8_e4m3": "fp8", "raw_fp8_e5m2": "fp8_e5m2"}
+
+
+def load_external(path: str, verbose: bool = False):
+    """Any supported file -> a list of ``AdapterTensor`` (GGUF, safetensors, or one raw dump as a single tensor)."""
+    from ..formats import adapter_core as ac
+    from ..formats.importers import TensorFile, read_raw
+    kind = ac.detect_format(path)
+    if kind in (ac.ExternalFormat.GGUF, ac.ExternalFormat.SAFETENSORS):
+        out = []
+        with TensorFile(path, ac.external_format_name(kind)) as f:
+            for name in f.names:
+                t = f.read(name, flat=True)
+                out.append(ac.AdapterTensor(name, t.numpy(), list(f.shape(name))))
+                if verbose:
+                    print(f"  {name:<48} {list(f.shape(name))}")
+        return kind, out
+    if kind in (ac.ExternalFormat.UNKNOWN, ac.ExternalFormat.OIL):
+        return kind, []
+    raw = read_raw(path, _RAW_OF[ac.external_format_name(kind)])
+    return kind, [ac.AdapterTensor(os.path.splitext(os.path.basename(path))[0], raw.numpy())]
+
+
+def bridge_config_for(bpw: float, fmt: str, block_size: int, adaptive: bool, verbose: bool, output: str):
+    """The reference's flag rules (src/adapters/tools/oil_import.cpp:366-393): a format name wins; 1.75 and 2.0 bits select
+    the adaptive mixes that hit them exactly; any other width selects the nearest single format at or below it."""
+    from ..formats import adapter_core as ac, oil, registry
+    cfg = ac.BridgeConfig(block_size=block_size, adaptive=adaptive, verbose=verbose, output_path=output, target_bpw=bpw)
+    mix_names = {m.name for m in registry.mixes()}
+    if fmt:
+        if fmt in mix_names:
+            cfg.compound, cfg.format = fmt, "OIL2"
+            cfg.target_bpw = next(m.bpw for m in registry.mixes() if m.name == fmt)
+        else:
+            cfg.format, cfg.target_bpw = fmt, oil.format_bpw(fmt)
+        return cfg
+    if abs(bpw - 1.75) < 0.01 and "SPARK_MIX_Q0" in mix_names:
+        cfg.format, cfg.compound = "OIL2", "SPARK_MIX_Q0"
+    elif abs(bpw - 2.0) < 0.01 and "QUAD_SPARK_Q1" in mix_names:
+        cfg.format, cfg.compound = "OIL4", "QUAD_SPARK_Q1"
+    elif not adaptive:
+        dense = [(oil.format_bpw(f), f) for f in ("OIL1", "SPARK_Q0", "OIL2", "OIL4", "OIL8", "OIL16", "OIL32")]
+        cfg.format = max((b, f) for b, f in dense if b <= max(bpw, 1.0))[1]
+        cfg.target_bpw = oil.format_bpw(cfg.format)
+    return cfg
+
+
+def adapt_convert(argv=None):
+    """``oil-adapt --input``: any external file -> mixed-format ``.oil`` through the conversion funnel
+    (src/adapters/tools/oil_adapt.cpp:44-137)."""
+    from ..formats import adapter_core as ac
     ap = argparse.ArgumentParser(prog="oil-adapt")
+    ap.add_argument("--input", required=True)
+    ap.add_argument("--output", required=True)
+    ap.add_argument("--bpw", type=float, default=2.0)
+    ap.add_argument("--format", default="", help="a wire format or a registry mix name; overrides --bpw")
+    ap.add_argument("--block-size", type=int, default=256)
+    ap.add_argument("--adaptive", action="store_true", help="let the registry choose the mix closest to --bpw")
+    ap.add_argument("--verbose", action="store_true")
+    a = ap.parse_args(argv)
+    kind, tensors = load_external(a.input, a.verbose)
+    print(f"OIL ADAPT: input={a.input} format={ac.external_format_name(kind)} -> {a.output} bpw={a.bpw:.2f}")
+    if kind == ac.ExternalFormat.OIL:
+        print("input is already an .oil file: nothing to convert", file=sys.stderr)
+        return 1
+    if not tensors:
+        print(f"failed to load tensors from {a.input}", file=sys.stderr)
+        return 1
+    cfg = bridge_config_for(a.bpw, a.format, a.block_size, a.adaptive, a.verbose, a.output)
+    res = []
+    if not ac.write_oil_mixed(tensors, cfg, res):
+        print("OIL write failed", file=sys.stderr)
+        return 1
+    n = sum(int(t.data.size) for t in tensors)
+    bits = sum(r.achieved_bpw * t.data.size for r, t in zip(res, tensors))
+    print(json.dumps({"tensors": len(tensors), "params": n, "blocks": sum(r.num_blocks for r in res), "claimed_bpw": bits / max(1, n),
+                      "file_bytes": os.path.getsize(a.output), "format": cfg.compound or str(cfg.format)}))
+    return 0
+
+
+def adapt(argv=None):
+    """``oil-adapt``: with ``--input`` the conversion funnel (what the reference's tool of this name does); with ``--model``
+    continual adaptation of a saved model to new text (also installed as ``oil-continual``)."""
+    args = sys.argv[1:] if argv is None else list(argv)
+    if "--input" in args:
+        return adapt_convert(args)
+    return continual(args)
+
+
+def continual(argv=None):
+    ap = argparse.ArgumentParser(prog="oil-continual")
     ap.add_argument("--model", required=True)
     ap.add_argument("--data", required=True)
     ap.add_argument("--replay", default="", help="text of the old domain: seeds the replay buffer and measures forgetting")
