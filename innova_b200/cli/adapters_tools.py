@@ -33,18 +33,29 @@ def _load(path, device="auto"):
 
 def chat(argv=None, stdin=None, stdout=None):
     ap = argparse.ArgumentParser(prog="oil-chat")
-    ap.add_argument("model")
-    ap.add_argument("--max-tokens", type=int, default=128)
-    ap.add_argument("--temperature", type=float, default=0.7)
-    ap.add_argument("--top-k", type=int, default=40)
+    ap.add_argument("model", nargs="+", help="<model.oil>, or <model_dir> <model.oil> with tokenizer.json in the directory")
+    ap.add_argument("--max-tokens", "--max-new", dest="max_tokens", type=int, default=128)
+    ap.add_argument("--temperature", "--temp", dest="temperature", type=float, default=0.7)
+    ap.add_argument("--top-k", "--topk", dest="top_k", type=int, default=40)
     ap.add_argument("--top-p", type=float, default=0.9)
     ap.add_argument("--greedy", action="store_true")
+    ap.add_argument("--raw", action="store_true", help="feed each line as plain text even when the tokenizer has a chat template")
+    ap.add_argument("--system", default="You are a helpful assistant.", help="system turn of the chat template")
+    ap.add_argument("--h-out", default="", help="write the final hidden state of the last prompt position (fp32) to this file")
+    ap.add_argument("--trace-out", default="", help="write the first layer's output at the last prompt position (fp32) to this file")
+    ap.add_argument("--debug-logits", action="store_true", help="print argmax, rms, NaN count and the top five tokens of the first prediction")
     ap.add_argument("--device", default="auto")
     a = ap.parse_args(argv)
     from ..inference.generator import Generator
     from ..inference.sampler import SamplingParams
     stdin, stdout = stdin or sys.stdin, stdout or sys.stdout
-    model, tok, dev = _load(a.model, a.device)
+    model, tok, dev = _load(a.model[-1], a.device)
+    templated = False
+    if len(a.model) > 1 and os.path.exists(os.path.join(a.model[0], "tokenizer.json")):
+        from ..utils.qwen_tokenizer import QwenMessage, QwenTokenizer
+        tok = QwenTokenizer.load_from_dir(a.model[0])
+        templated = not a.raw
+        turns = [QwenMessage("system", a.system)]
     gen = Generator(model, tok, kv_format="oil4" if dev.type == "cuda" else "bf16", max_batch=1)
     sp = SamplingParams() if a.greedy else SamplingParams(temperature=a.temperature, top_k=a.top_k, top_p=a.top_p)
     history = []
@@ -54,15 +65,50 @@ def chat(argv=None, stdin=None, stdout=None):
             break
         if line == "/reset":
             history = []
+            if templated:
+                turns = turns[:1]
             continue
-        history += [min(t, model.cfg.vocab_size - 1) for t in tok.encode(line + "\n")]
+        if templated:                                             # the template is re-applied to the whole conversation each turn
+            turns.append(QwenMessage("user", line))
+            history = [min(t, model.cfg.vocab_size - 1) for t in tok.apply_chat_template(turns, True)]
+        else:
+            history += [min(t, model.cfg.vocab_size - 1) for t in tok.encode(line + "\n")]
         room = model.cfg.max_seq_len - a.max_tokens - 1
         history = history[-max(1, room):]                        # the oldest turns fall out of the context window
+        if a.h_out or a.trace_out or a.debug_logits:
+            _chat_debug(model, tok, history, a, dev)
         new = gen.generate_tokens([history], a.max_tokens, sp, eos_id=getattr(tok, "eos_id", None))[0]
         history += new
-        stdout.write(tok.decode(new) + "\n")
+        text = tok.decode(new)
+        if templated:
+            turns.append(QwenMessage("assistant", text))
+        stdout.write(text + "\n")
         stdout.flush()
     return 0
+
+
+@torch.no_grad()
+def _chat_debug(model, tok, ids, a, dev):
+    """The reference's chat tool dumps the engine's last hidden state and first-layer trace and prints a logits summary after
+    every prefill (src/adapters/tools/oil_chat.cpp:84-125); the same three, on request."""
+    x = torch.tensor([ids], device=dev)
+    if a.trace_out:
+        wpe = model.pos_embeddings.weight if model.pos_embeddings is not None else None
+        from .. import ops
+        h0 = model.layers[0](ops.embedding(x, model.tok_embeddings.weight, wpe), model.rope(dev), None)
+        h0[0, -1].float().cpu().numpy().tofile(a.trace_out)
+        print(f"[trace0 written: {a.trace_out}]", file=sys.stderr)
+    h = model.hidden_states(x)
+    if a.h_out:
+        h[0, -1].float().cpu().numpy().tofile(a.h_out)
+        print(f"[h written: {a.h_out}]", file=sys.stderr)
+    if a.debug_logits:
+        logits = model(x)[0, -1].float()
+        top = logits.topk(5)
+        print(f"[logits] argmax={int(top.indices[0])} mx={float(top.values[0]):.3f} rms={float(logits.square().mean().sqrt()):.3f} "
+              f"nan={int(logits.isnan().sum())}", file=sys.stderr)
+        for q, (i, v) in enumerate(zip(top.indices.tolist(), top.values.tolist())):
+            print(f"[top{q + 1}] {i} {tok.decode([i])!r} {v:.3f}", file=sys.stderr)
 
 
 _RAW_OF = {"raw_fp32": "fp32", "raw_fp16": "fp16", "raw_fp8_e4m3": "fp8", "raw_fp8_e5m2": "fp8_e5m2"}

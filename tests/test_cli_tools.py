@@ -178,6 +178,16 @@ def test_adapters_edition_tools(tiny):
     assert os.path.exists(adapted) and r["replay_buffer"] > 0 and r["old_domain_loss_after"] < r["old_domain_loss_before"] + 1.5
     chat_out = io.StringIO()
     assert T.chat([adapted, "--max-tokens", "4", "--greedy", "--device", "cpu"], stdin=io.StringIO("the quick\n/reset\nbrown\n/quit\n"), stdout=chat_out) == 0
+    # the reference's short flag names, and the debug dumps after the prefill
+    h_out, tr_out, dbg = str(d / "h.bin"), str(d / "t.bin"), io.StringIO()
+    import contextlib
+    import numpy as np
+    with contextlib.redirect_stderr(dbg):
+        assert T.chat([adapted, "--max-new", "2", "--temp", "0.5", "--topk", "3", "--raw", "--h-out", h_out, "--trace-out", tr_out, "--debug-logits",
+                       "--device", "cpu"], stdin=io.StringIO("the quick\n"), stdout=io.StringIO()) == 0
+    hv, tv = np.fromfile(h_out, np.float32), np.fromfile(tr_out, np.float32)
+    assert hv.shape == tv.shape == (64,) and np.isfinite(hv).all() and not np.allclose(hv, tv)
+    assert "[logits] argmax=" in dbg.getvalue() and "nan=0" in dbg.getvalue() and "[top5]" in dbg.getvalue()
     assert len(chat_out.getvalue().splitlines()) >= 2
 
 
