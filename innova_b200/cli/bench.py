@@ -104,8 +104,61 @@ def multimodal_suite(a) -> dict:
     return {"suite": "multimodal", "device": str(dev), "batch": a.batch_size, "hidden": h, "encoders": rows}
 
 
+def kernel_suite(a) -> dict:
+    """``--kernel matmul --size N`` (one square GEMM) or ``--kernel all`` (N and 128 ... 1024), as the reference's tool times its
+    scalar and AVX2 GEMMs (tools/bench.cpp:51-100, 3 warm-up and 20 timed calls): here the package's own ``ops.linear`` on the
+    current device (the tcgen05 GEMM on a GPU, timed with CUDA events; the fp32 fallback on a CPU) next to ``torch.matmul``."""
+    from .. import ops
+    dev = torch.device("cuda" if torch.cuda.is_available() else "cpu")
+    dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    sizes = [a.size] + ([128, 256, 512, 1024] if a.kernel == "all" else [])
+    rows = []
+    for n in sizes:
+        g = torch.Generator().manual_seed(n)
+        x = torch.randn(n, n, generator=g).to(dev, dtype)
+        w = torch.randn(n, n, generator=g).to(dev, dtype)
+        row = {"M": n, "N": n, "K": n, "dtype": str(dtype).replace("torch.", ""), "device": str(dev)}
+        for name, fn in (("ops_linear", lambda: ops.linear(x, w)), ("torch_matmul", lambda: x @ w.t())):
+            for _ in range(3):
+                fn()
+            _sync(dev)
+            if dev.type == "cuda":
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(20):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                dt = e0.elapsed_time(e1) * 1e-3 / 20
+            else:
+                t0 = time.perf_counter()
+                for _ in range(20):
+                    fn()
+                dt = (time.perf_counter() - t0) / 20
+            row[name] = {"us": dt * 1e6, "gflops": 2.0 * n ** 3 / dt * 1e-9}
+        rows.append(row)
+    return {"suite": "kernel", "kernel": a.kernel, "rows": rows}
+
+
+def inference_suite(a) -> dict:
+    """``--inference --model m.oil --prompt p``: greedy generation of 128 tokens through the serving engine (tools/bench.cpp:102-125)."""
+    from ..inference.sampler import SamplingParams
+    from ..inference.serving import InferenceEngine
+    eng = InferenceEngine(a.model, device=None if a.device == "auto" else a.device)
+    n = a.new_tokens if a.new_tokens != 32 else 128
+    t0 = time.perf_counter()
+    text, stats = eng.generate_with_stats(a.prompt, n, SamplingParams())
+    dt = time.perf_counter() - t0
+    return {"suite": "inference", "chars": len(text), "seconds": dt, "new_tokens": stats.new_tokens, "decode_tokens_per_s": stats.decode_tokens_per_sec}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="oil-bench")
+    ap.add_argument("--kernel", default="", choices=["", "matmul", "all"], help="time the GEMM at --size (all: also 128 ... 1024)")
+    ap.add_argument("--size", type=int, default=512)
+    ap.add_argument("--inference", action="store_true", help="time a greedy generation of --model on --prompt")
+    ap.add_argument("--model", default="")
+    ap.add_argument("--prompt", default="Hello")
     ap.add_argument("--suite", default="train", choices=["train", "infer", "native", "quality", "quant", "multimodal"])
     ap.add_argument("--preset", default="")
     ap.add_argument("--hidden-size", type=int, default=512)
@@ -120,6 +173,14 @@ def main(argv=None):
     ap.add_argument("--device", default="auto")
     ap.add_argument("--elements", type=int, default=1 << 18, help="weights per distribution (quality / quant suites)")
     a = ap.parse_args(argv)
+    if a.kernel or a.inference:
+        if a.kernel:
+            print(json.dumps(kernel_suite(a)))
+        if a.inference:
+            if not a.model:
+                ap.error("--inference needs --model")
+            print(json.dumps(inference_suite(a)))
+        return 0
     if a.suite in ("quality", "quant", "multimodal"):
         out = {"quality": quality_suite, "quant": quant_suite, "multimodal": multimodal_suite}[a.suite](a)
         print(json.dumps(out))

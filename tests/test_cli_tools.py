@@ -60,6 +60,11 @@ def test_quantize_evaluate_finetune_bench(tiny):
     n = json.loads(_run("innova_b200.cli.bench", "--suite", "native", "--hidden-size", "64", "--num-layers", "2", "--num-heads", "2", "--vocab-size",
                         "512", "--batch-size", "2", "--seq-length", "32", "--steps", "2", "--warmup", "1", "--device", "cpu").splitlines()[-1])
     assert n["phase"] == "native" and n["bits_per_weight"] < 9
+    both = _run("innova_b200.cli.bench", "--kernel", "all", "--size", "64", "--inference", "--model", model, "--prompt", "the quick", "--new-tokens", "8",
+                "--device", "cpu").splitlines()
+    k, inf = json.loads(both[-2]), json.loads(both[-1])
+    assert [r["M"] for r in k["rows"]] == [64, 128, 256, 512, 1024] and all(r["ops_linear"]["gflops"] > 0 and r["torch_matmul"]["us"] > 0 for r in k["rows"])
+    assert inf["suite"] == "inference" and inf["new_tokens"] == 8 and inf["decode_tokens_per_s"] > 0
 
 
 def test_serve_answers_over_http(tiny):
