@@ -391,6 +391,17 @@ class DeltaAdapterConfig:
 
 
 @dataclass
+class DeltaAdapter:
+    """One task's adapter as a record (src/adapters/include/adapters/delta_adapter.h:14-28); ``DeltaAdapterHost.adapter`` builds it."""
+    task_id: int = 0
+    task_name: str = ""
+    frozen: bool = False
+    layers: Dict[str, "WeightDelta"] = field(default_factory=dict)
+    total_params: int = 0
+    lam: float = 1.0
+
+
+@dataclass
 class WeightDelta:
     """One layer's delta of one adapter (src/adapters/include/adapters/delta_adapter.h:19-23)."""
     delta: torch.Tensor
@@ -468,6 +479,11 @@ class DeltaAdapterHost:
             return None
         return WeightDelta(l["delta"], l["fisher"], float((l["fisher"] * l["delta"].square()).sum()))
 
+    def adapter(self, aid: int) -> DeltaAdapter:
+        a = self.adapters[aid]
+        layers = {n: self.weight_delta(aid, n) for n in a["layers"]}
+        return DeltaAdapter(aid, a["name"], a["frozen"], layers, sum(w.delta.numel() for w in layers.values()), a["lambda"])
+
     def total_adapter_params(self) -> int:
         return sum(l["delta"].numel() for a in self.adapters.values() for l in a["layers"].values())
 
@@ -488,6 +504,18 @@ class MTPHeadConfig:
     target_acceptance_rate: float = 0.7
     min_draft_k: int = 1
     max_draft_k: int = 8
+
+
+@dataclass
+class MTPHeadMetrics:
+    """Running figures of the draft heads (src/adapters/include/adapters/mtp_head_trainer.h:27-35)."""
+    head_losses: List[float] = field(default_factory=list)
+    avg_loss: float = 0.0
+    acceptance_rate: float = 0.0
+    current_draft_k: int = 3
+    total_tokens_accepted: int = 0
+    total_tokens_proposed: int = 0
+    step: int = 0
 
 
 @dataclass
@@ -557,7 +585,13 @@ class MTPHeadTrainer:
             self._adafactor(i, p.t() @ h, p.sum(dim=0))
             self.quantized[i] = None
         self.step += 1
+        self.last_losses = losses
         return losses
+
+    def metrics(self) -> MTPHeadMetrics:
+        ls = list(getattr(self, "last_losses", []))
+        live = [l for l in ls if l > 0]
+        return MTPHeadMetrics(ls, sum(live) / len(live) if live else 0.0, self.acceptance_rate, self.draft_k, self.accepted, self.proposed, self.step)
 
     def quantize_heads(self, fmt: Optional[str] = None):
         for i, p in enumerate(self.proj):

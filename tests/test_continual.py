@@ -196,3 +196,26 @@ def test_record_views_of_replay_delta_and_mtp_heads():
     tr2.load_head_weights(1, hq)
     h = torch.randn(3, 16)
     assert torch.equal(tr.propose_tokens(h, 2)[:, 1], tr2.propose_tokens(h, 2)[:, 1])
+
+
+def test_adapter_record_and_head_metrics():
+    import torch
+    from innova_b200.training import continual as ct
+    host = ct.DeltaAdapterHost(ct.DeltaAdapterConfig(quantize_deltas=False))
+    aid = host.create_adapter("task-a")
+    host.update_delta(aid, "w1", torch.ones(2, 3), lr=1.0)
+    host.update_delta(aid, "w2", torch.ones(4), lr=1.0)
+    rec = host.adapter(aid)
+    assert (rec.task_id, rec.task_name, rec.frozen, rec.total_params, rec.lam) == (aid, "task-a", False, 10, 1.0) and set(rec.layers) == {"w1", "w2"}
+    host.freeze_adapter(aid)
+    assert host.adapter(aid).frozen
+
+    tr = ct.MTPHeadTrainer(ct.MTPHeadConfig(num_heads=2, hidden_size=8, vocab_size=16))
+    m0 = tr.metrics()
+    assert m0.step == 0 and m0.head_losses == [] and m0.avg_loss == 0.0
+    g = torch.Generator().manual_seed(0)
+    tr.train_step(torch.randn(2, 6, 8, generator=g), torch.randint(0, 16, (2, 6), generator=g))
+    tr.record(3, 4)
+    m = tr.metrics()
+    assert m.step == 1 and len(m.head_losses) == 2 and abs(m.avg_loss - sum(m.head_losses) / 2) < 1e-6
+    assert (m.total_tokens_accepted, m.total_tokens_proposed, m.acceptance_rate, m.current_draft_k) == (3, 4, 0.75, tr.draft_k)
